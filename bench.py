@@ -1,0 +1,337 @@
+"""Benchmark of the routed KV-cache hot path: KV tokens/s for route + int8 quantise + append.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one pass over one batch of synthetic tokens: fused gate (logits of the
+gate net's last layer, softmax, top-2, counts, slots) then the routed, quantised
+append into the paged per-expert cache.  Workload at one GPU: 16384 tokens, hidden
+4096, 8 experts top-2, 8 KV heads x 128, int8 symmetric per (token, head) group,
+16-token pages; K/V ~ N(0,1) with 1% of channels scaled x20.  Data is synthetic.
+
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput, `e2e` the
+same step through the public API with pinned host inputs copied in and the routing
+result read back inside the timed region.  `--impl reference` times the CPU port of
+the reference's arithmetic (oracle/) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "kv_tokens_per_s_route_quant_append"
+UNIT = "tokens/s"
+WORKLOAD = dict(workload="route+int8-quant+append", tokens=16384, hidden=4096, experts=8, top_k=2, kv_heads=8,
+                head_dim=128, page_tokens=16, quant="int8-sym-g128", capacity_factor=1.5)
+GATE_BYTES_PER_TOKEN = 4096 * 2 + 8 * 4 + 3 * 2 * 4                      # act in; probs, idx, w, slot out
+APPEND_BYTES_PER_TOKEN = 2 * 1024 * 2 + 16 + 2 * 2 * 1024 + 2 * 16 * 2   # K,V in; idx/slot; 2 copies of codes + scales
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()     # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def synth_inputs(T, H, E, kv_dim, seed, device=None, pin=False):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    act = torch.randn(T, H, generator=g).bfloat16()
+    K = torch.randn(T, kv_dim, generator=g)
+    V = torch.randn(T, kv_dim, generator=g)
+    cols = torch.randperm(kv_dim, generator=g)[: round(0.01 * kv_dim)]
+    K[:, cols] *= 20.0
+    V[:, cols] *= 20.0
+    K, V = K.bfloat16(), V.bfloat16()
+    if pin:
+        return act.pin_memory(), K.pin_memory(), V.pin_memory()
+    if device is not None:
+        return act.to(device), K.to(device), V.to(device)
+    return act, K, V
+
+
+def gate_weights(H, E, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    bound = 1.0 / H ** 0.5                                   # nn.Linear default (Kaiming uniform, a=sqrt(5))
+    w2 = (torch.rand(E, H, generator=g) * 2 - 1) * bound
+    b2 = (torch.rand(E, generator=g) * 2 - 1) * bound
+    return w2.bfloat16(), b2
+
+
+# ----------------------------------------------------------------------------- CPU port (reference arm)
+def cpu_step(act, w2, b2, K, V, E, top_k, cap):
+    from oracle import pikv_oracle as O
+    logits = O.gate_logits(act, w2, b2)
+    probs, idx, tw = O.gate_tail(logits, top_k)
+    slot, counts_k = O.slot_assign_fast(idx, E, cap)
+    out = O.routed_append(K, V, idx, slot, E, cap, 8, True, 128)
+    return out["length"]
+
+
+def cpu_threads():
+    try:
+        from threadpoolctl import threadpool_info
+        return max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_cpu(steps, warmup, tokens):
+    import numpy as np
+    cfg = WORKLOAD
+    H, E, k = cfg["hidden"], cfg["experts"], cfg["top_k"]
+    kv = cfg["kv_heads"] * cfg["head_dim"]
+    act, K, V = synth_inputs(tokens, H, E, kv, 1)
+    w2, b2 = gate_weights(H, E, 7)
+    a, kk, vv = act.float().numpy(), K.float().numpy(), V.float().numpy()
+    w, b = w2.float().numpy(), b2.numpy()
+    cap = int(tokens * cfg["capacity_factor"] * k / E)
+    for _ in range(warmup):
+        cpu_step(a, w, b, kk, vv, E, k, cap)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(a, w, b, kk, vv, E, k, cap)
+    dt = (time.perf_counter() - t0) / steps
+    return tokens / dt, dt
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    tokens = WORKLOAD["tokens"]
+    value, dt = run_cpu(steps, warmup, tokens)
+    cores = cpu_threads()
+    sample = f"{steps} full batches of {tokens} tokens (numpy port of the reference arithmetic; BLAS GEMM threaded)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": dict(WORKLOAD),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    import pikv_b200
+    from pikv_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU port")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    pikv_b200.lib()
+
+    cfg = WORKLOAD
+    T, H, E, k = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["top_k"]
+    n_kv = cfg["kv_heads"]
+    kv = n_kv * cfg["head_dim"]
+    cap = int(T * cfg["capacity_factor"] * k / E)
+    w2, b2 = gate_weights(H, E, 7)
+    w2, b2 = w2.to(dev), b2.to(dev)
+
+    if world > 1:
+        from pikv_b200 import distributed as pd
+        step_fn, sets, extra_cfg = pd.make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs)
+        R = len(sets)
+    else:
+        # R rotating input sets and caches so that no step finds its inputs in L2 (each set is 201 MB)
+        R = 3
+        sets = [synth_inputs(T, H, E, kv, 100 + i, device=dev) for i in range(R)]
+        caches = [pikv_b200.PagedKVCache(E, cap, n_kv, device=dev) for _ in range(R)]
+        outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=cap, want_probs=True) for _ in range(R)]
+        extra_cfg = {"parallelism": "single"}
+
+        def step_fn(i):
+            act, K, V = sets[i % R]
+            g = ops.gate_fused(act, w2, b2, top_k=k, capacity=cap, out=outs[i % R])
+            caches[i % R].append(K, V, g.topk_idx, g.slot)
+            return g
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step_fn(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = pikv_b200.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step_fn(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = pikv_b200.launch_count() - launches0
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = T * world * args.steps / (ms_max * 1e-3)
+
+    # per-kernel time of the two parts, measured live with events on the launching stream
+    roof = None
+    e2e = None
+    cpu = None
+    if world == 1:
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+        barrier()
+        for i in range(args.steps):
+            act, K, V = sets[i % R]
+            ev[i][0].record()
+            g = ops.gate_fused(act, w2, b2, top_k=k, capacity=cap, out=outs[i % R])
+            ev[i][1].record()
+            caches[i % R].append(K, V, g.topk_idx, g.slot)
+            ev[i][2].record()
+        barrier()
+        gate_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+        app_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+        peak, peak_src = measured_peak_gbs()
+        gate_gbs = GATE_BYTES_PER_TOKEN * T / (gate_ms * 1e-3) / 1e9
+        app_gbs = APPEND_BYTES_PER_TOKEN * T / (app_ms * 1e-3) / 1e9
+        step_gbs = (GATE_BYTES_PER_TOKEN + APPEND_BYTES_PER_TOKEN) * T / (ms_max / args.steps * 1e-3) / 1e9
+        dom = "gate" if gate_ms >= app_ms else "append"
+        roof = {"bound": "hbm", "kernel": "gate_fused (gate_act_kernel + gate_finalize_kernel)" if dom == "gate" else "kv_append_quant_kernel",
+                "achieved": gate_gbs if dom == "gate" else app_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                "frac": (gate_gbs if dom == "gate" else app_gbs) / peak, "traffic": None,
+                "gate": {"ms": gate_ms, "GBps": gate_gbs, "frac": gate_gbs / peak, "bytes_per_token": GATE_BYTES_PER_TOKEN},
+                "append": {"ms": app_ms, "GBps": app_gbs, "frac": app_gbs / peak, "bytes_per_token": APPEND_BYTES_PER_TOKEN},
+                "step": {"GBps": step_gbs, "frac": step_gbs / peak}}
+
+        # end to end: pinned host inputs copied in, routing result read back, every step
+        h_sets = [synth_inputs(T, H, E, kv, 200 + i, pin=True) for i in range(2)]
+        d_in = [tuple(torch.empty_like(x, device=dev) for x in h_sets[0]) for _ in range(2)]
+        h_out = [torch.empty(T, k, dtype=torch.int32).pin_memory(), torch.empty(T, k, dtype=torch.float32).pin_memory(),
+                 torch.empty(T, k, dtype=torch.int32).pin_memory(), torch.empty(E, dtype=torch.int32).pin_memory()]
+
+        def e2e_step(i):
+            src, dst = h_sets[i % 2], d_in[i % 2]
+            for s, d in zip(src, dst):
+                d.copy_(s, non_blocking=True)
+            g = ops.gate_fused(dst[0], w2, b2, top_k=k, capacity=cap, out=outs[i % R])
+            caches[i % R].append(dst[1], dst[2], g.topk_idx, g.slot)
+            h_out[0].copy_(g.topk_idx, non_blocking=True)
+            h_out[1].copy_(g.topk_w, non_blocking=True)
+            h_out[2].copy_(g.slot, non_blocking=True)
+            h_out[3].copy_(g.new_len, non_blocking=True)
+
+        for i in range(3):
+            e2e_step(i)
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            e2e_step(i)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
+        h2d = sum(x.numel() * x.element_size() for x in h_sets[0])
+        d2h = sum(x.numel() * x.element_size() for x in h_out)
+        e2e = {"value": T * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms / args.steps}
+        for c in caches:
+            c.check_status()
+    clocks = sampler.stop() if rank == 0 else None
+
+    if world == 1 and not args.no_cpu_baseline:
+        v, dt = run_cpu(3, 1, T)
+        cpu = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
+               "sample": f"3 full batches of {T} tokens on the host (numpy port of the reference arithmetic)"}
+
+    if world > 1:
+        e2e = extra_cfg.pop("e2e", None)
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 in, fp32 math, int8 codes", "data": "synthetic",
+            "config": {**cfg, **extra_cfg, "l2": f"inputs larger than L2, rotated over {R} buffer sets"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-side port timing (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,321 @@
+/*
+ * pikv_b200 - C ABI of the B200 (sm_100a) routed KV-cache kernels.
+ *
+ * One shared object, libpikv_b200.so.  Every entry point takes plain device
+ * pointers and sizes, enqueues its kernels on the stream it is given and
+ * returns immediately with 0 or a negative PIKV_E* code; pikv_last_error()
+ * gives the message for the calling thread.  The library never allocates
+ * device memory (scratch is passed in by the caller, sized by the matching
+ * *_workspace_bytes function), never synchronises the device and has no CPU
+ * fallback.
+ *
+ * The reference project's native boundary is a set of
+ *   extern "C" void launch_<kernel>(const float* ..., int dims..., cudaStream_t)
+ * functions with no return code (core/cuda/pikv_routing_kernel.cu:404-511,
+ * core/cuda/pikv_compression_kernel.cu:463-623,
+ * core/cuda/pikv_scheduling_kernel.cu:504-676) bound from
+ * core/single/pikv_kernels.py.  Each declaration below names the launcher(s)
+ * and the Python operator whose arithmetic it replaces.
+ */
+#ifndef PIKV_B200_H
+#define PIKV_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PIKV_ABI_VERSION 1
+
+/* status codes */
+#define PIKV_OK            0
+#define PIKV_EINVAL       -1  /* bad argument (null pointer, size out of range) */
+#define PIKV_EUNSUPPORTED -2  /* shape / dtype combination not built           */
+#define PIKV_ECUDA        -3  /* a CUDA runtime call failed at launch          */
+#define PIKV_ELIMIT       -4  /* size beyond a documented fixed limit          */
+
+/* element types of activations / K / V inputs */
+#define PIKV_F32  0
+#define PIKV_BF16 1
+
+/* how expert_mask enters the logits (gate) */
+#define PIKV_MASK_NONE    0
+#define PIKV_MASK_SINGLE  1   /* l + (1-mask) * -1e9        core/single/pikv_routing.py:70          */
+#define PIKV_MASK_MODULE  2   /* l + (1-mask) * FLT_LOWEST  core/single/module/pikv_routing.py:133  */
+#define PIKV_MASK_BIAS    3   /* l + mask                   core/single/routing_strategy.py:46      */
+
+/* bits set in the device status word that kernels OR into (never trap) */
+#define PIKV_ST_BAD_SEQ     1u   /* destination sequence id out of range        */
+#define PIKV_ST_BAD_PAGE    2u   /* page-table entry out of range               */
+#define PIKV_ST_ZP_CLAMPED  4u   /* int16 zero point saturated                  */
+#define PIKV_ST_BAD_INDEX   8u   /* gather / scatter index out of range         */
+#define PIKV_ST_WAIT_TIMEOUT 16u /* a bounded in-kernel wait ran out; result invalid */
+
+/* tokens per cache page and the head width the cache kernels are built for */
+#define PIKV_PAGE_TOKENS 16
+#define PIKV_HEAD_DIM    128
+
+typedef void* pikv_stream_t;   /* a cudaStream_t */
+
+int         pikv_abi_version(void);
+const char* pikv_last_error(void);
+/* number of kernels this library has launched in the calling process */
+uint64_t    pikv_launch_count(void);
+
+/* ------------------------------------------------------------------------
+ * Router gate: logits tail + softmax + top-k + load-balance counts + slots.
+ *
+ * Replaces launch_topk_routing_kernel / launch_load_balancing_kernel /
+ * launch_adaptive_routing_kernel / launch_expert_capacity_kernel
+ * (core/cuda/pikv_routing_kernel.cu:404-511) and the PyTorch tail of
+ * BaseRouter.forward (core/single/pikv_routing.py:65-79,155), the running
+ * per-expert position loop of core/single/module/pikv_routing.py:88-104 and
+ * its usage counters (:154-160).
+ *
+ * Either `act`+`w2` (the gate net's last Linear: logits = act . w2^T + b2,
+ * fp32 accumulate) or `logits_in` is given.  Then, per token:
+ *   l = l / temperature ; l *= correction[e] ; mask ; p = softmax(l)
+ *   top-k of p (ties: lowest expert index) ; w = p_top / (sum p_top + eps)
+ * and, over the batch in (token, k) order, slot = slot_base[e] + running
+ * count of earlier selections of e, or -1 once slot >= capacity.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    const void*  act;          /* [T,H] dtype, or NULL                          */
+    const void*  w2;           /* [E,H] dtype                                   */
+    const float* b2;           /* [E] or NULL                                   */
+    const float* logits_in;    /* [T,E] fp32, used when act == NULL             */
+    int32_t dtype, T, H, E, top_k;
+    const float* expert_mask;  /* [E] or NULL                                   */
+    int32_t mask_mode;
+    const float* correction;   /* [E] or NULL                                   */
+    float temperature;         /* 1.0 = off                                     */
+    float renorm_eps;
+    int32_t capacity;          /* slots per expert; <=0: no limit               */
+    const int32_t* slot_base;  /* [E] current length per expert, or NULL        */
+    /* outputs (any may be NULL except topk_idx) */
+    float*   probs;            /* [T,E]                                         */
+    int32_t* topk_idx;         /* [T,k]                                         */
+    float*   topk_w;           /* [T,k]                                         */
+    int32_t* slot;             /* [T,k]                                         */
+    int32_t* counts_k;         /* [k,E] selections of e in column j (dropped or not) */
+    float*   prob_sum;         /* [E] sum over tokens of p[t,e]                 */
+    int32_t* new_len;          /* [E] min(slot_base + count, capacity)          */
+    void*    workspace;        /* pikv_gate_workspace_bytes(T,E,top_k)          */
+    size_t   workspace_bytes;
+} pikv_gate_params;
+
+size_t pikv_gate_workspace_bytes(int32_t T, int32_t E, int32_t top_k);
+int    pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream);
+
+/* Dense [T,E,capacity] dispatch / combine tensors (zero-filled by this call)
+ * for callers that read them.  position_mode 0: slot as given (running count,
+ * core/single/module/pikv_routing.py:93-104); 1: the positions
+ * core/single/pikv_routing.py:107-128 produces ("number of earlier k-columns
+ * in which this expert was chosen by any token"), from counts_k. */
+int pikv_dispatch_scatter(const int32_t* topk_idx, const float* topk_w, const int32_t* slot,
+                          const int32_t* counts_k, int32_t T, int32_t E, int32_t top_k,
+                          int32_t capacity, int32_t position_mode,
+                          float* dispatch, float* combine, pikv_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Routed KV append fused with per-(token, head) group quantisation.
+ *
+ * Replaces launch_quantization_compression_kernel
+ * (core/cuda/pikv_compression_kernel.cu:485-505) and the row insert of
+ * launch_lru_cache_management_kernel (core/cuda/pikv_scheduling_kernel.cu:504-525);
+ * arithmetic = QuantizedCompressor._quantize_tensor
+ * (core/single/module/pikv_compression.py:945-1012) applied to each
+ * [1, 128] slice, row placement = CacheSchedulingManager.update_cache
+ * (core/single/cache_scheduling.py:430-436) per destination sequence.
+ *
+ * Cache layout (all pools indexed by physical page id):
+ *   codes  [pages][n_kv][16 tokens][128 * bits / 8] bytes; inside one token row
+ *          the 16-byte chunk c is stored at chunk (c ^ (token_in_page & 7))
+ *          for 8-bit codes, and the 8-byte unit u at unit (u ^ (token_in_page & 4))
+ *          for 4-bit codes (two codes per byte, low nibble = even channel)
+ *   scale  [pages][n_kv][16] bf16
+ *   zp     [pages][n_kv][16] int16 (asymmetric only)
+ * A "sequence" is whatever owns a page-table row: an expert, a decode stream,
+ * or an (expert, stream) pair.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    const void* k;             /* [T, n_kv*128] dtype                           */
+    const void* v;
+    int32_t dtype, T, n_kv, top_k;
+    const int32_t* dst_seq;    /* [T,k] destination sequence (= topk_idx)       */
+    const int32_t* slot;       /* [T,k] position in that sequence, <0 = dropped */
+    const int32_t* page_table; /* [num_seqs, max_pages] physical page ids       */
+    int32_t num_seqs, max_pages, num_pages;
+    int32_t bits, symmetric;   /* (8,1) (8,0) (4,1) (4,0)                       */
+    void* k_codes; void* v_codes;
+    void* k_scale; void* v_scale;   /* bf16                                     */
+    void* k_zp;    void* v_zp;      /* int16, asymmetric only                   */
+    uint32_t* status;          /* device word, OR-ed with PIKV_ST_* (may be NULL) */
+} pikv_append_params;
+
+int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t stream);
+
+/* Read rows back in logical order, dequantised: out[i] = (code - zp) * scale for
+ * sequence seq[i], position pos[i]; out is [n, n_kv*128] fp32, codes_out
+ * (optional) [n, n_kv*128] int8 unpacked codes.  Used by tests, checkpointing
+ * and the host-side read path (PiKVMoE's cached rows). */
+int pikv_cache_gather(const int32_t* seq, const int32_t* pos, int32_t n,
+                      const int32_t* page_table, int32_t num_seqs, int32_t max_pages, int32_t num_pages,
+                      int32_t n_kv, int32_t bits,
+                      const void* codes, const void* scale, const void* zp,
+                      float* out, int8_t* codes_out, uint32_t* status, pikv_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Block-wide fake quantisation: every column group of width group_size is
+ * one block with min/max over ALL rows.  Bit-exact drop-in arithmetic of
+ * QuantizedCompressor.forward (core/single/pikv_compression.py:474-506,
+ * core/single/module/pikv_compression.py:1014-1051); replaces
+ * launch_quantization_compression_kernel.
+ *   qmin/qmax: code range; symmetric selects the scale formula.
+ *   params_in (optional, [G][2] = scale, zero point): static mode, skip the
+ *   statistics pass.  params_out (optional) [G][2].  sq_err (optional) [G]:
+ *   sum over the block of (x - dq)^2 (mean = / (N*width)).
+ * ---------------------------------------------------------------------- */
+size_t pikv_quant_block_workspace_bytes(int32_t N, int32_t H, int32_t group_size);
+int pikv_quant_block(const void* x, int32_t dtype, int32_t N, int32_t H, int32_t group_size,
+                     int32_t qmin, int32_t qmax, int32_t symmetric,
+                     const float* params_in, float* params_out,
+                     float* dq_out, float* q_out, float* sq_err,
+                     void* workspace, size_t workspace_bytes, pikv_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * H2O scoring and eviction.
+ *
+ * pikv_h2o_accumulate: acc[idx] += w ; ts[idx] = now
+ *   (H2OScheduler.update_attention_scores, core/single/cache_scheduling.py:69-73;
+ *   decay != 1 multiplies all n scores first, core/single/module/pikv_scheduling.py:119-125;
+ *   replaces launch_cache_access_update_kernel, core/cuda/pikv_scheduling_kernel.cu:614-627).
+ *   idx == NULL means idx = 0..m-1.  Indices must be distinct.
+ * pikv_h2o_select: per segment keep the num_heavy largest scores and the
+ *   num_recent largest timestamps, ties to the lowest index
+ *   (H2OScheduler.select_eviction_candidates, core/single/cache_scheduling.py:75-99).
+ *   acc, ts: [segments, stride]; seg_len[s] <= stride valid entries (NULL: all n).
+ *   evict_mask [segments, stride] uint8 (1 = evict; entries past the length = 1),
+ *   keep_idx [segments, keep_stride] ascending, kept_count [segments].
+ * pikv_h2o_compact: copy the kept rows of a paged cache, in ascending order,
+ *   to positions 0..kept-1 of the destination sequences' pages, together with
+ *   their scores and timestamps (CacheSchedulingManager.update_cache evict
+ *   branch, core/single/cache_scheduling.py:418-424; replaces
+ *   launch_cache_compaction_kernel, core/cuda/pikv_scheduling_kernel.cu:629-652).
+ *   A sequence owns n_kv segments (one per KV head) when per_head != 0 and
+ *   segment s = seq * n_kv + head; otherwise one segment per sequence.
+ *   Source and destination pages must not overlap.
+ * ---------------------------------------------------------------------- */
+int pikv_h2o_accumulate(float* acc, float* ts, int32_t n, const int32_t* idx, const float* w, int32_t m,
+                        float now, float decay, uint32_t* status, pikv_stream_t stream);
+
+int pikv_h2o_select(const float* acc, const float* ts, int32_t segments, int32_t stride,
+                    const int32_t* seg_len, int32_t n, int32_t num_heavy, int32_t num_recent,
+                    uint8_t* evict_mask, int32_t* keep_idx, int32_t keep_stride, int32_t* kept_count,
+                    pikv_stream_t stream);
+
+typedef struct {
+    const int32_t* keep_idx;   /* [segments, keep_stride]                        */
+    const int32_t* kept_count; /* [segments]                                     */
+    int32_t keep_stride, num_seqs, n_kv, per_head, bits;
+    const int32_t* src_page_table; const int32_t* dst_page_table;  /* [num_seqs, max_pages] */
+    int32_t max_pages, num_pages;
+    const void* src_k_codes; const void* src_v_codes; const void* src_k_scale; const void* src_v_scale;
+    const void* src_k_zp; const void* src_v_zp;
+    void* dst_k_codes; void* dst_v_codes; void* dst_k_scale; void* dst_v_scale;
+    void* dst_k_zp; void* dst_v_zp;
+    const float* src_acc; const float* src_ts;   /* [segments, score_stride] or NULL */
+    float* dst_acc; float* dst_ts;
+    int32_t score_stride;
+    uint32_t* status;
+} pikv_compact_params;
+
+int pikv_h2o_compact(const pikv_compact_params* p, pikv_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Decode attention over the int8 paged cache, dequantised in registers.
+ *
+ * out[b,h,:] = softmax(q[b,h,:] . K[b,h/g]^T / sqrt(128)) V[b,h/g] with
+ * K = code * scale (core/single/module/pikv_compression.py:1006), arithmetic
+ * of PiKVAttention._compute_attention (core/single/pikv_attention.py:117-123,
+ * 163,188).  g = n_q / n_kv query heads share one KV head.  The context is
+ * split over `splits` CTAs per (stream, KV head); partial results go to
+ * `workspace` and a second kernel merges them.
+ *   q, out: [B, n_q, 128] bf16.  seq_ids [B] (NULL: b) selects the page-table
+ *   row, seq_len [B] its valid length.
+ *   lse (optional) [B, n_q] fp32 log-sum-exp of the scaled scores.
+ *   scores (optional) [B, n_q, score_stride] fp32 raw scaled scores, consumed by
+ *   pikv_h2o_accumulate_attn.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    const void* q; void* out;
+    int32_t B, n_q, n_kv;
+    const int32_t* seq_ids; const int32_t* seq_len;
+    const int32_t* page_table; int32_t num_seqs, max_pages, num_pages;
+    const void* k_codes; const void* v_codes; const void* k_scale; const void* v_scale;
+    int32_t splits;            /* <=0: library picks                             */
+    float* lse;
+    float* scores; int32_t score_stride;
+    void* workspace; size_t workspace_bytes;
+    uint32_t* status;
+} pikv_decode_params;
+
+size_t pikv_decode_attn_workspace_bytes(int32_t B, int32_t n_q, int32_t n_kv, int32_t max_ctx, int32_t splits);
+int    pikv_decode_attn_default_splits(int32_t B, int32_t n_kv, int32_t max_ctx);
+int    pikv_decode_attn_q8(const pikv_decode_params* p, pikv_stream_t stream);
+
+/* acc[b, kvh, pos] += sum over the g query heads of exp(score - lse): the H2O
+ * accumulated-attention increment (core/single/pikv_moe.py:241-245 column sums
+ * fed to core/single/cache_scheduling.py:69-73).  acc: [B*n_kv, acc_stride]. */
+int pikv_h2o_accumulate_attn(const float* scores, int32_t score_stride, const float* lse,
+                             const int32_t* seq_len, int32_t B, int32_t n_q, int32_t n_kv,
+                             float* acc, int32_t acc_stride, pikv_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Low-rank projection on tcgen05 tensor cores (bf16 operands, fp32 accumulate
+ * in tensor memory): y[M,N] = act(x[M,K] . w[N,K]^T + bias).
+ * Projection (N = rank, relu=1) and reconstruction (K = rank, relu=0) of
+ * SVDCompressor.forward (core/single/pikv_compression.py:336-349), the
+ * encoder/decoder layers of PyramidCompressor (:101-127) and the cache
+ * compressor's two Linears (core/single/kv_cache_compression.py:38-39);
+ * replaces launch_svd_compression_kernel / launch_pyramid_compression_kernel
+ * (core/cuda/pikv_compression_kernel.cu:507-553).
+ *   x, w bf16 row-major (K contiguous), K % 64 == 0, N % 16 == 0, N <= 256 per
+ *   call column block (larger N is tiled internally); out bf16 or fp32.
+ *   residual (optional) [M,N] bf16 added after the activation.
+ * ---------------------------------------------------------------------- */
+int pikv_lowrank_project(const void* x, const void* w, const float* bias, const void* residual,
+                         void* out, int32_t out_dtype, int32_t M, int32_t N, int32_t K, int32_t relu,
+                         pikv_stream_t stream);
+/* Reads and clears the sticky device error word of the projection kernel (non-zero: a
+ * bounded mbarrier wait ran out and the output is invalid).  Copies from the device, so
+ * it waits for the work queued before it. */
+int pikv_lowrank_error_state(void);
+
+/* ------------------------------------------------------------------------
+ * Expert-sharded exchange helpers (token all-to-all over NVLink via NCCL runs
+ * in the host layer between these two calls).
+ * pikv_a2a_pack quantises each routed (token, j) K/V row and writes a
+ * fixed-size record into the send buffer, grouped by destination rank in
+ * (token, j) order; pikv_a2a_unpack stores received records into the local
+ * paged cache.  Replaces the replicate-everything + all_reduce design of
+ * DistributedPiKVMoE.forward (core/distributed/distributed_pikv.py:174-194).
+ * Record (int8 symmetric): header {int32 seq, int32 slot} + K codes
+ * [n_kv*128] + V codes [n_kv*128] + K scales [n_kv] bf16 + V scales [n_kv] bf16.
+ * ---------------------------------------------------------------------- */
+size_t pikv_a2a_record_bytes(int32_t n_kv);
+int pikv_a2a_pack(const void* k, const void* v, int32_t dtype, int32_t T, int32_t n_kv, int32_t top_k,
+                  const int32_t* dst_seq, const int32_t* slot, const int32_t* dst_rank,
+                  const int32_t* send_pos, /* [T,k] record index in the send buffer, <0 = skip */
+                  void* send_buf, pikv_stream_t stream);
+int pikv_a2a_unpack(const void* recv_buf, int32_t n_records, int32_t n_kv,
+                    const int32_t* page_table, int32_t num_seqs, int32_t max_pages, int32_t num_pages,
+                    void* k_codes, void* v_codes, void* k_scale, void* v_scale,
+                    uint32_t* status, pikv_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PIKV_B200_H */

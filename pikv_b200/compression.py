@@ -1,0 +1,220 @@
+"""Compressors with the surface of core/single/pikv_compression.py.
+
+QuantizedCompressor keeps the reference's block-wide semantics bit for bit
+(every column group is one block whose min/max run over all rows) on the
+two-pass CUDA kernel.  SVDCompressor and PyramidCompressor run their Linear
+layers on the tcgen05 projection kernel when the input is bf16 and the shapes
+fit it, otherwise as fp32 torch GEMMs (cuBLAS), which is what fp32 parity at
+1e-5 needs.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+
+
+class BaseCompressor(nn.Module):
+    """core/single/pikv_compression.py:7-48."""
+
+    def __init__(self, hidden_size: int, compression_ratio: float = 0.5):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.compression_ratio = compression_ratio
+
+    def forward(self, keys, values, importance=None):
+        return keys, values
+
+    def get_compression_stats(self) -> Dict[str, float]:
+        return {"compression_ratio": self.compression_ratio, "memory_reduction": 1.0 - self.compression_ratio}
+
+
+def _linear(layer: nn.Linear, x: torch.Tensor, relu: bool) -> torch.Tensor:
+    """One Linear (+ReLU): tcgen05 kernel for bf16 inputs whose shapes fit, cuBLAS otherwise."""
+    K, N = layer.in_features, layer.out_features
+    if x.dtype == torch.bfloat16 and x.is_cuda and K % 64 == 0 and N % 16 == 0 and (N <= 256 or N % 256 == 0):
+        lead = x.shape[:-1]
+        y = ops.lowrank_project(x.reshape(-1, K), layer.weight.detach().to(torch.bfloat16), layer.bias, relu=relu)
+        return y.view(*lead, N)
+    y = F.linear(x, layer.weight.to(x.dtype), None if layer.bias is None else layer.bias.to(x.dtype))
+    return F.relu(y) if relu else y
+
+
+class PyramidCompressor(BaseCompressor):
+    """core/single/pikv_compression.py:50-242."""
+
+    def __init__(self, hidden_size: int, compression_ratio: float = 0.5, num_levels: int = 3, decay_factor: float = 0.8):
+        super().__init__(hidden_size, compression_ratio)
+        self.num_levels = num_levels
+        self.decay_factor = decay_factor
+        self.encoder_layers = nn.ModuleList()
+        self.decoder_layers = nn.ModuleList()
+        current = hidden_size
+        for _ in range(num_levels):
+            out = max(int(current * compression_ratio), 1)
+            self.encoder_layers.append(nn.Linear(current, out))
+            self.decoder_layers.append(nn.Linear(out, current))
+            current = out
+            compression_ratio *= decay_factor
+        for m in self.modules():
+            if isinstance(m, nn.Linear):
+                nn.init.xavier_normal_(m.weight)
+                nn.init.zeros_(m.bias)
+        self.register_buffer("compression_stats", torch.zeros(4))
+        self.register_buffer("sample_count", torch.tensor(0.0))
+
+    def _chain(self, x: torch.Tensor, levels: int) -> torch.Tensor:
+        for i in range(levels):
+            x = _linear(self.encoder_layers[i], x, True)
+        for i in range(levels - 1, -1, -1):
+            x = _linear(self.decoder_layers[i], x, True)
+        return x
+
+    def forward(self, keys: torch.Tensor, values: torch.Tensor, importance: Optional[torch.Tensor] = None):
+        batch_size, seq_len, hidden_size = keys.shape
+        if importance is not None:
+            order = torch.argsort(importance.reshape(-1), descending=True)
+            sizes, remaining = [], order.numel()
+            for i in range(self.num_levels):
+                if i == self.num_levels - 1:
+                    sizes.append(remaining)
+                else:
+                    s = int(remaining * (1 - self.decay_factor) * (self.decay_factor ** i))
+                    sizes.append(s)
+                    remaining -= s
+            fk, fv = keys.reshape(-1, hidden_size), values.reshape(-1, hidden_size)
+            ck, cv = torch.zeros_like(fk), torch.zeros_like(fv)
+            start = 0
+            for level, size in enumerate(sizes):
+                if size <= 0:
+                    continue
+                ix = order[start:start + size]
+                ck[ix] = self._chain(fk[ix], level)
+                cv[ix] = self._chain(fv[ix], level)
+                start += size
+            ck, cv = ck.reshape(keys.shape), cv.reshape(values.shape)
+        else:
+            ck, cv = self._chain(keys, self.num_levels), self._chain(values, self.num_levels)
+        with torch.no_grad():
+            if keys.numel() > 0:
+                ratio = ck.numel() / keys.numel()
+                st = self.compression_stats
+                n = float(self._host_samples()) + 1.0
+                st[0] += ratio
+                st[1] = st[0] / n
+                st[2] = torch.clamp(st[2], min=ratio)
+                st[3] = torch.where(st[3] == 0, torch.full_like(st[3], ratio), torch.clamp(st[3], max=ratio))
+                self.sample_count += 1
+                self._samples = n
+        return ck, cv
+
+    def _host_samples(self) -> float:
+        if getattr(self, "_samples", None) is None:
+            self._samples = float(self.sample_count.item())
+        return self._samples
+
+    def get_compression_stats(self) -> Dict[str, float]:
+        s = self.compression_stats.tolist()
+        return {"compression_ratio": s[1], "max_compression_ratio": s[2], "min_compression_ratio": s[3],
+                "memory_reduction": 1.0 - s[1], "num_samples": self.sample_count.item()}
+
+
+class SVDCompressor(BaseCompressor):
+    """core/single/pikv_compression.py:244-366.  The reference's adaptive rank never takes effect in
+    this variant (its statistics update raises and is swallowed, :310-324), so the configured rank
+    is always used; the same holds here."""
+
+    def __init__(self, hidden_size: int, rank: int = 64, adaptive_rank: bool = False):
+        super().__init__(hidden_size, rank / hidden_size)
+        self.rank = rank
+        self.adaptive_rank = adaptive_rank
+        self.key_projector = nn.Linear(hidden_size, rank)
+        self.key_reconstructor = nn.Linear(rank, hidden_size)
+        self.value_projector = nn.Linear(hidden_size, rank)
+        self.value_reconstructor = nn.Linear(rank, hidden_size)
+        for m in self.modules():
+            if isinstance(m, nn.Linear):
+                nn.init.orthogonal_(m.weight)
+                nn.init.zeros_(m.bias)
+        self.register_buffer("energy_preserved", torch.zeros(1))
+        self.register_buffer("effective_rank", torch.zeros(1))
+        self.register_buffer("sample_count", torch.tensor(0.0))
+
+    def project(self, x: torch.Tensor, which: str = "key") -> torch.Tensor:
+        """relu(projector(x)): the rank-`rank` latent that a cache would store."""
+        return _linear(self.key_projector if which == "key" else self.value_projector, x, True)
+
+    def reconstruct(self, latent: torch.Tensor, which: str = "key") -> torch.Tensor:
+        return _linear(self.key_reconstructor if which == "key" else self.value_reconstructor, latent, False)
+
+    def forward(self, keys: torch.Tensor, values: torch.Tensor, importance: Optional[torch.Tensor] = None):
+        rk = self.reconstruct(self.project(keys, "key"), "key")
+        rv = self.reconstruct(self.project(values, "value"), "value")
+        with torch.no_grad():
+            self.sample_count += 1
+        return rk, rv
+
+    def get_compression_stats(self) -> Dict[str, float]:
+        stats = super().get_compression_stats()
+        stats.update({"effective_rank": self.effective_rank.item(), "energy_preserved": self.energy_preserved.item(),
+                      "adaptive_rank": self.adaptive_rank, "rank": self.rank, "num_samples": self.sample_count.item()})
+        return stats
+
+
+class QuantizedCompressor(BaseCompressor):
+    """core/single/pikv_compression.py:368-516 (asymmetric, codes 0 .. 2^bits-1)."""
+
+    symmetric = False
+
+    def __init__(self, hidden_size: int, bits: int = 8, group_size: int = 128, dynamic_quantization: bool = True):
+        super().__init__(hidden_size, bits / 32)
+        self.bits = bits
+        self.group_size = min(group_size, hidden_size)
+        self.dynamic_quantization = dynamic_quantization
+        self.register_buffer("scale", torch.ones(1))
+        self.register_buffer("zero_point", torch.zeros(1))
+        self.calibrated = False
+        self.register_buffer("quantization_error", torch.zeros(1))
+        self.register_buffer("sample_count", torch.tensor(0.0))
+
+    def _qrange(self) -> Tuple[int, int]:
+        return 0, 2 ** self.bits - 1
+
+    def _run(self, flat: torch.Tensor, params_in):
+        qmin, qmax = self._qrange()
+        return ops.quant_block(flat, self.group_size, qmin, qmax, self.symmetric, params_in=params_in)
+
+    def _static_params(self, keys_flat: torch.Tensor, groups: int):
+        # the first block quantised (keys, group 0) fixes one scale / zero point for everything after
+        if not self.calibrated:
+            qmin, qmax = self._qrange()
+            first = keys_flat[:, : self.group_size].contiguous()
+            _, _, p, _ = ops.quant_block(first, self.group_size, qmin, qmax, self.symmetric, want_err=False)
+            self.scale = p[0, 0].clone()
+            self.zero_point = p[0, 1].clone()
+            self.calibrated = True
+        return torch.stack([self.scale.reshape(()), self.zero_point.reshape(())]).float().repeat(groups, 1).contiguous()
+
+    def forward(self, keys: torch.Tensor, values: torch.Tensor, importance: Optional[torch.Tensor] = None):
+        shape = keys.shape
+        kf = keys.reshape(-1, shape[-1])
+        vf = values.reshape(-1, shape[-1])
+        groups = (shape[-1] + self.group_size - 1) // self.group_size
+        params_in = None if self.dynamic_quantization else self._static_params(kf, groups)
+        dk, _, _, _ = self._run(kf, params_in)
+        dv, _, _, err = self._run(vf, params_in)
+        with torch.no_grad():
+            last_w = shape[-1] - (groups - 1) * self.group_size
+            self.quantization_error = err[-1] / float(vf.shape[0] * last_w)   # the last block quantised: values, last group
+            self.sample_count += 2 * groups
+        return dk.to(keys.dtype).reshape(shape), dv.to(values.dtype).reshape(shape)
+
+    def get_compression_stats(self) -> Dict[str, float]:
+        stats = super().get_compression_stats()
+        stats.update({"bits": self.bits, "quantization_error": float(self.quantization_error),
+                      "group_size": self.group_size, "num_samples": self.sample_count.item()})
+        return stats

@@ -1,0 +1,164 @@
+// Expert-sharded exchange helpers: quantise-and-pack routed K/V rows into fixed-size
+// records ordered by destination rank, and store received records into the local paged
+// cache.  The exchange itself (NCCL all-to-all over NVLink) runs between the two calls;
+// both kernels only touch local memory.
+//
+// Record (int8 symmetric), 16-byte aligned:
+//   int32 seq, int32 slot, 8 bytes pad | K codes [n_kv*128] | V codes [n_kv*128]
+//   | K scales [n_kv] bf16 | V scales [n_kv] bf16 | pad to 16
+#include "common.cuh"
+
+namespace pikv {
+
+constexpr int PT = PIKV_PAGE_TOKENS;
+
+__host__ __device__ inline size_t a2a_record_bytes(int n_kv) {
+    size_t b = 16 + (size_t)2 * n_kv * 128 + (size_t)4 * n_kv;
+    return (b + 15) / 16 * 16;
+}
+
+template <typename TIn>
+__device__ __forceinline__ void a2a_load16(const TIn* p, float (&x)[16]);
+template <>
+__device__ __forceinline__ void a2a_load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[16]) {
+    uint4 a = ld_stream_16(p), b = ld_stream_16(p + 8);
+    bf16x2_to_f32(a.x, x[0], x[1]);   bf16x2_to_f32(a.y, x[2], x[3]);
+    bf16x2_to_f32(a.z, x[4], x[5]);   bf16x2_to_f32(a.w, x[6], x[7]);
+    bf16x2_to_f32(b.x, x[8], x[9]);   bf16x2_to_f32(b.y, x[10], x[11]);
+    bf16x2_to_f32(b.z, x[12], x[13]); bf16x2_to_f32(b.w, x[14], x[15]);
+}
+template <>
+__device__ __forceinline__ void a2a_load16<float>(const float* p, float (&x)[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 a = ld_stream_16(p + 4 * i);
+        x[4 * i] = __uint_as_float(a.x); x[4 * i + 1] = __uint_as_float(a.y);
+        x[4 * i + 2] = __uint_as_float(a.z); x[4 * i + 3] = __uint_as_float(a.w);
+    }
+}
+
+// one 8-lane group per (token, K|V, head); codes are written once per destination record
+template <typename TIn>
+__global__ void __launch_bounds__(256) a2a_pack_kernel(const TIn* k, const TIn* v, int T, int n_kv, int top_k,
+                                                      const int* dst_seq, const int* slot, const int* send_pos,
+                                                      uint8_t* send_buf) {
+    const int sub = threadIdx.x & 7;
+    const long long group = ((long long)blockIdx.x * 256 + threadIdx.x) >> 3;
+    const int per_tok = 2 * n_kv;
+    const bool active = group < (long long)T * per_tok;
+    const int t = active ? (int)(group / per_tok) : 0;
+    const int rr = active ? (int)(group % per_tok) : 0;
+    const int which = rr / n_kv, head = rr % n_kv;
+    float x[16];
+    if (active) a2a_load16<TIn>((which ? v : k) + ((size_t)t * n_kv + head) * 128 + sub * 16, x);
+    else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = 0.f;
+    }
+    float mn = x[0], mx = x[0];
+#pragma unroll
+    for (int i = 1; i < 16; ++i) { mn = fminf(mn, x[i]); mx = fmaxf(mx, x[i]); }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if (!active) return;
+    const QParams qp = quant_params(mn, mx, -128, 127, true);
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc |= ((uint32_t)((int)quant_code(x[4 * i + c], qp, -128.f, 127.f) & 0xff)) << (8 * c);
+        w[i] = acc;
+    }
+    const size_t rec = a2a_record_bytes(n_kv);
+    for (int j = 0; j < top_k; ++j) {
+        const int sp = send_pos[(size_t)t * top_k + j];
+        if (sp < 0) continue;
+        uint8_t* r = send_buf + (size_t)sp * rec;
+        if (which == 0 && head == 0 && sub == 0) {
+            reinterpret_cast<int*>(r)[0] = dst_seq[(size_t)t * top_k + j];
+            reinterpret_cast<int*>(r)[1] = slot[(size_t)t * top_k + j];
+        }
+        *reinterpret_cast<uint4*>(r + 16 + ((size_t)which * n_kv + head) * 128 + sub * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+        if (sub == 0)
+            reinterpret_cast<uint16_t*>(r + 16 + (size_t)2 * n_kv * 128)[which * n_kv + head] = f32_to_bf16_bits(qp.scale);
+    }
+}
+
+__global__ void __launch_bounds__(256) a2a_unpack_kernel(const uint8_t* recv_buf, int n_records, int n_kv,
+                                                        const int* page_table, int num_seqs, int max_pages,
+                                                        int num_pages, uint8_t* k_codes, uint8_t* v_codes,
+                                                        uint16_t* k_scale, uint16_t* v_scale, unsigned* status) {
+    const int sub = threadIdx.x & 7;
+    const long long group = ((long long)blockIdx.x * 256 + threadIdx.x) >> 3;
+    const int per = 2 * n_kv;
+    if (group >= (long long)n_records * per) return;
+    const int i = (int)(group / per), rr = (int)(group % per);
+    const int which = rr / n_kv, head = rr % n_kv;
+    const size_t rec = a2a_record_bytes(n_kv);
+    const uint8_t* r = recv_buf + (size_t)i * rec;
+    const int seq = reinterpret_cast<const int*>(r)[0], s = reinterpret_cast<const int*>(r)[1];
+    if (s < 0) return;
+    if (seq < 0 || seq >= num_seqs || s / PT >= max_pages) {
+        if (status && sub == 0) atomicOr(status, PIKV_ST_BAD_SEQ);
+        return;
+    }
+    const int page = page_table[(size_t)seq * max_pages + s / PT];
+    if (page < 0 || page >= num_pages) {
+        if (status && sub == 0) atomicOr(status, PIKV_ST_BAD_PAGE);
+        return;
+    }
+    const int row = s % PT;
+    const size_t prow = ((size_t)page * n_kv + head) * PT + row;
+    const uint4 w = *reinterpret_cast<const uint4*>(r + 16 + ((size_t)which * n_kv + head) * 128 + sub * 16);
+    uint8_t* dst = (which ? v_codes : k_codes) + prow * 128;
+    *reinterpret_cast<uint4*>(dst + 16 * swz8_chunk(row, sub)) = w;
+    if (sub == 0)
+        (which ? v_scale : k_scale)[prow] = reinterpret_cast<const uint16_t*>(r + 16 + (size_t)2 * n_kv * 128)[which * n_kv + head];
+}
+
+}  // namespace pikv
+
+using namespace pikv;
+
+extern "C" size_t pikv_a2a_record_bytes(int32_t n_kv) { return n_kv > 0 ? a2a_record_bytes(n_kv) : 0; }
+
+extern "C" int pikv_a2a_pack(const void* k, const void* v, int32_t dtype, int32_t T, int32_t n_kv, int32_t top_k,
+                             const int32_t* dst_seq, const int32_t* slot, const int32_t* dst_rank,
+                             const int32_t* send_pos, void* send_buf, pikv_stream_t stream) {
+    (void)dst_rank;   // the record order is already encoded in send_pos
+    PIKV_REQUIRE(T >= 0 && n_kv > 0 && top_k > 0, PIKV_EINVAL, "a2a_pack: bad sizes");
+    if (T == 0) return PIKV_OK;
+    PIKV_REQUIRE(k && v && dst_seq && slot && send_pos && send_buf, PIKV_EINVAL, "a2a_pack: null pointer");
+    PIKV_REQUIRE(dtype == PIKV_BF16 || dtype == PIKV_F32, PIKV_EINVAL, "a2a_pack: bad dtype %d", dtype);
+    const long long lanes = (long long)T * 2 * n_kv * 8;
+    const int grid = (int)ceil_div64(lanes, 256);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == PIKV_BF16)
+        a2a_pack_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
+                                                             static_cast<const __nv_bfloat16*>(v), T, n_kv, top_k, dst_seq,
+                                                             slot, send_pos, static_cast<uint8_t*>(send_buf));
+    else
+        a2a_pack_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(k), static_cast<const float*>(v), T, n_kv,
+                                                     top_k, dst_seq, slot, send_pos, static_cast<uint8_t*>(send_buf));
+    count_launch(1);
+    return check_launch("a2a_pack_kernel");
+}
+
+extern "C" int pikv_a2a_unpack(const void* recv_buf, int32_t n_records, int32_t n_kv, const int32_t* page_table,
+                               int32_t num_seqs, int32_t max_pages, int32_t num_pages, void* k_codes, void* v_codes,
+                               void* k_scale, void* v_scale, uint32_t* status, pikv_stream_t stream) {
+    PIKV_REQUIRE(n_records >= 0 && n_kv > 0, PIKV_EINVAL, "a2a_unpack: bad sizes");
+    if (n_records == 0) return PIKV_OK;
+    PIKV_REQUIRE(recv_buf && page_table && k_codes && v_codes && k_scale && v_scale, PIKV_EINVAL, "a2a_unpack: null pointer");
+    const long long lanes = (long long)n_records * 2 * n_kv * 8;
+    a2a_unpack_kernel<<<(int)ceil_div64(lanes, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(recv_buf), n_records, n_kv, page_table, num_seqs, max_pages, num_pages,
+        static_cast<uint8_t*>(k_codes), static_cast<uint8_t*>(v_codes), static_cast<uint16_t*>(k_scale),
+        static_cast<uint16_t*>(v_scale), status);
+    count_launch(1);
+    return check_launch("a2a_unpack_kernel");
+}

@@ -1,0 +1,169 @@
+"""Paged, quantised KV store in HBM and the kernels that write and read it.
+
+A *sequence* owns one row of the page table: an expert's cache (routed append),
+a decode stream, or an (expert, stream) pair on an expert-sharded GPU.  Pages
+hold 16 tokens.  Pools (indexed by physical page id):
+
+    k_codes, v_codes  uint8 [pages, n_kv, 16, 128*bits/8]   (chunk-swizzled rows)
+    k_scale, v_scale  bf16  [pages, n_kv, 16]
+    k_zp, v_zp        int16 [pages, n_kv, 16]                (asymmetric only)
+
+The row placement follows CacheSchedulingManager.update_cache
+(core/single/cache_scheduling.py:430-436: contiguous rows, truncation at
+capacity); the arithmetic of the stored codes is QuantizedCompressor.
+_quantize_tensor (core/single/module/pikv_compression.py:945-1012) per
+(token, head) slice of 128 channels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import AppendParams, CompactParams, DecodeParams, PikvError, check, lib
+from .ops import _p, _req, _stream, _workspace, _dtype_code, PAGE_TOKENS, HEAD_DIM
+
+
+class PagedKVCache(torch.nn.Module):
+    """Page pools + page table + per-sequence lengths, all registered buffers
+    (so state_dict() carries the cache)."""
+
+    def __init__(self, num_seqs: int, capacity: int, n_kv: int, bits: int = 8, symmetric: bool = True,
+                 device="cuda", num_pages: Optional[int] = None, identity_table: bool = True):
+        super().__init__()
+        if bits not in (4, 8):
+            raise ValueError("bits must be 4 or 8")
+        self.num_seqs, self.n_kv, self.bits, self.symmetric = num_seqs, n_kv, bits, bool(symmetric)
+        self.max_pages = (capacity + PAGE_TOKENS - 1) // PAGE_TOKENS
+        self.capacity = capacity
+        self.num_pages = num_pages if num_pages is not None else num_seqs * self.max_pages
+        row = HEAD_DIM * bits // 8
+        dev = torch.device(device)
+        z = lambda *s, dtype: torch.zeros(*s, dtype=dtype, device=dev)
+        self.register_buffer("k_codes", z(self.num_pages, n_kv, PAGE_TOKENS, row, dtype=torch.uint8))
+        self.register_buffer("v_codes", z(self.num_pages, n_kv, PAGE_TOKENS, row, dtype=torch.uint8))
+        self.register_buffer("k_scale", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.bfloat16))
+        self.register_buffer("v_scale", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.bfloat16))
+        if not self.symmetric:
+            self.register_buffer("k_zp", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.int16))
+            self.register_buffer("v_zp", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.int16))
+        else:
+            self.k_zp = self.v_zp = None
+        if identity_table:
+            if self.num_pages < num_seqs * self.max_pages:
+                raise ValueError("identity page table needs num_seqs * max_pages pages")
+            pt = torch.arange(num_seqs * self.max_pages, dtype=torch.int32, device=dev).view(num_seqs, self.max_pages)
+        else:
+            pt = torch.full((num_seqs, self.max_pages), -1, dtype=torch.int32, device=dev)
+        self.register_buffer("page_table", pt)
+        self.register_buffer("length", z(num_seqs, dtype=torch.int32))
+        self.register_buffer("status", z(1, dtype=torch.int32))
+
+    # -- writes --------------------------------------------------------------------
+    def append(self, k: torch.Tensor, v: torch.Tensor, dst_seq: torch.Tensor, slot: torch.Tensor) -> None:
+        """Quantise and store k, v [T, n_kv*128] at (dst_seq[t,j], slot[t,j]); slot < 0 is skipped.
+        Does not touch `length` (the gate's new_len, or the caller, owns it)."""
+        k = _req(k, "k")
+        v = _req(v, "v", k.dtype)
+        T = k.shape[0]
+        if k.shape[1] != self.n_kv * HEAD_DIM or v.shape != k.shape:
+            raise PikvError(f"k/v must be [T, {self.n_kv * HEAD_DIM}], got {tuple(k.shape)} / {tuple(v.shape)}")
+        dst_seq = _req(dst_seq, "dst_seq", torch.int32)
+        slot = _req(slot, "slot", torch.int32)
+        if dst_seq.dim() == 1:
+            dst_seq, slot = dst_seq[:, None], slot[:, None]
+        p = AppendParams()
+        p.k, p.v, p.dtype, p.T, p.n_kv, p.top_k = _p(k), _p(v), _dtype_code(k, "k"), T, self.n_kv, dst_seq.shape[1]
+        p.dst_seq, p.slot, p.page_table = _p(dst_seq), _p(slot), _p(self.page_table)
+        p.num_seqs, p.max_pages, p.num_pages = self.num_seqs, self.max_pages, self.num_pages
+        p.bits, p.symmetric = self.bits, int(self.symmetric)
+        p.k_codes, p.v_codes, p.k_scale, p.v_scale = _p(self.k_codes), _p(self.v_codes), _p(self.k_scale), _p(self.v_scale)
+        p.k_zp, p.v_zp = _p(self.k_zp), _p(self.v_zp)
+        p.status = _p(self.status)
+        check(lib().pikv_kv_append_quant(C.byref(p), _stream()), "pikv_kv_append_quant")
+
+    # -- reads ---------------------------------------------------------------------
+    def gather(self, seq: torch.Tensor, pos: torch.Tensor, which: str = "k", codes: bool = False):
+        """Dequantised rows [n, n_kv*128] fp32 (and int8 codes when codes=True) in logical order."""
+        seq = _req(seq, "seq", torch.int32)
+        pos = _req(pos, "pos", torch.int32)
+        n = seq.numel()
+        dev = seq.device
+        out = torch.empty(n, self.n_kv * HEAD_DIM, dtype=torch.float32, device=dev)
+        cod = torch.empty(n, self.n_kv * HEAD_DIM, dtype=torch.int8, device=dev) if codes else None
+        pool, sc, zp = (self.k_codes, self.k_scale, self.k_zp) if which == "k" else (self.v_codes, self.v_scale, self.v_zp)
+        check(lib().pikv_cache_gather(_p(seq), _p(pos), n, _p(self.page_table), self.num_seqs, self.max_pages,
+                                      self.num_pages, self.n_kv, self.bits, _p(pool), _p(sc), _p(zp), _p(out), _p(cod),
+                                      _p(self.status), _stream()), "pikv_cache_gather")
+        return (out, cod) if codes else out
+
+    def decode_attention(self, q: torch.Tensor, seq_ids: Optional[torch.Tensor] = None,
+                         seq_len: Optional[torch.Tensor] = None, splits: int = 0, want_lse: bool = False,
+                         scores: Optional[torch.Tensor] = None):
+        """softmax(q K^T / sqrt(128)) V over each stream's cached context; q [B, n_q, 128] bf16."""
+        if self.bits != 8 or not self.symmetric:
+            raise PikvError("decode_attention reads int8 symmetric caches")
+        q = _req(q, "q", torch.bfloat16)
+        B, n_q, d = q.shape
+        if d != HEAD_DIM:
+            raise PikvError(f"head dim must be {HEAD_DIM}")
+        if seq_ids is not None:
+            seq_ids = _req(seq_ids, "seq_ids", torch.int32)
+        if seq_len is None:
+            seq_len = self.length if seq_ids is None else self.length[seq_ids.long()]
+        seq_len = _req(seq_len, "seq_len", torch.int32)
+        dev = q.device
+        out = torch.empty_like(q)
+        lse = torch.empty(B, n_q, dtype=torch.float32, device=dev) if (want_lse or scores is not None) else None
+        if splits <= 0:
+            splits = lib().pikv_decode_attn_default_splits(B, self.n_kv, self.max_pages * PAGE_TOKENS)
+        ws = _workspace(dev, lib().pikv_decode_attn_workspace_bytes(B, n_q, self.n_kv, self.capacity, splits), "dec")
+        p = DecodeParams()
+        p.q, p.out, p.B, p.n_q, p.n_kv = _p(q), _p(out), B, n_q, self.n_kv
+        p.seq_ids, p.seq_len, p.page_table = _p(seq_ids), _p(seq_len), _p(self.page_table)
+        p.num_seqs, p.max_pages, p.num_pages = self.num_seqs, self.max_pages, self.num_pages
+        p.k_codes, p.v_codes, p.k_scale, p.v_scale = _p(self.k_codes), _p(self.v_codes), _p(self.k_scale), _p(self.v_scale)
+        p.splits, p.lse = splits, _p(lse)
+        p.scores, p.score_stride = _p(scores), (scores.shape[-1] if scores is not None else 0)
+        p.workspace, p.workspace_bytes, p.status = _p(ws), ws.numel(), _p(self.status)
+        check(lib().pikv_decode_attn_q8(C.byref(p), _stream()), "pikv_decode_attn_q8")
+        return (out, lse) if (want_lse or scores is not None) else out
+
+    # -- eviction ------------------------------------------------------------------
+    def compact_into(self, dst: "PagedKVCache", keep_idx: torch.Tensor, kept_count: torch.Tensor, per_head: bool,
+                     src_acc=None, src_ts=None, dst_acc=None, dst_ts=None) -> None:
+        """Copy the kept rows (ascending original order) to positions 0.. of `dst`'s sequences."""
+        keep_idx = _req(keep_idx, "keep_idx", torch.int32)
+        kept_count = _req(kept_count, "kept_count", torch.int32)
+        p = CompactParams()
+        p.keep_idx, p.kept_count, p.keep_stride = _p(keep_idx), _p(kept_count), keep_idx.shape[1]
+        p.num_seqs, p.n_kv, p.per_head, p.bits = self.num_seqs, self.n_kv, int(per_head), self.bits
+        p.src_page_table, p.dst_page_table = _p(self.page_table), _p(dst.page_table)
+        p.max_pages, p.num_pages = min(self.max_pages, dst.max_pages), min(self.num_pages, dst.num_pages)
+        if self.max_pages != dst.max_pages:
+            raise PikvError("compact_into: source and destination must share the page-table width")
+        p.src_k_codes, p.src_v_codes, p.src_k_scale, p.src_v_scale = _p(self.k_codes), _p(self.v_codes), _p(self.k_scale), _p(self.v_scale)
+        p.src_k_zp, p.src_v_zp = _p(self.k_zp), _p(self.v_zp)
+        p.dst_k_codes, p.dst_v_codes, p.dst_k_scale, p.dst_v_scale = _p(dst.k_codes), _p(dst.v_codes), _p(dst.k_scale), _p(dst.v_scale)
+        p.dst_k_zp, p.dst_v_zp = _p(dst.k_zp), _p(dst.v_zp)
+        p.src_acc, p.src_ts, p.dst_acc, p.dst_ts = _p(src_acc), _p(src_ts), _p(dst_acc), _p(dst_ts)
+        p.score_stride = src_acc.shape[-1] if src_acc is not None else 0
+        p.status = _p(self.status)
+        check(lib().pikv_h2o_compact(C.byref(p), _stream()), "pikv_h2o_compact")
+
+    def unpack_records(self, recv_buf: torch.Tensor, n_records: int) -> None:
+        """Store records received from the token all-to-all (see ops.a2a_pack) into the pages."""
+        if self.bits != 8 or not self.symmetric:
+            raise PikvError("records carry int8 symmetric codes")
+        recv_buf = _req(recv_buf, "recv_buf", torch.uint8)
+        check(lib().pikv_a2a_unpack(_p(recv_buf), n_records, self.n_kv, _p(self.page_table), self.num_seqs,
+                                    self.max_pages, self.num_pages, _p(self.k_codes), _p(self.v_codes), _p(self.k_scale),
+                                    _p(self.v_scale), _p(self.status), _stream()), "pikv_a2a_unpack")
+
+    def check_status(self) -> None:
+        """Raise if any kernel flagged a bad index, page or a wait that ran out (synchronises)."""
+        s = int(self.status.item())
+        if s:
+            raise PikvError(f"cache status word = {s:#x} (see PIKV_ST_* in include/pikv_b200.h)")

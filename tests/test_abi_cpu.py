@@ -1,0 +1,69 @@
+"""The C-ABI library loads and exports every symbol the header declares (no GPU needed)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    from pikv_b200 import build
+    path = build.build()
+    assert os.path.exists(path)
+    return ctypes.CDLL(path)
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "pikv_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pikv_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(built_lib):
+    names = header_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(built_lib, n), f"{n} declared in include/pikv_b200.h but not exported"
+
+
+def test_binding_table_matches_header():
+    from pikv_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == header_symbols()
+
+
+def test_version_and_pure_host_entry_points(built_lib):
+    from pikv_b200 import _lib
+    lib = _lib.lib()
+    assert lib.pikv_abi_version() == _lib.ABI_VERSION
+    assert lib.pikv_gate_workspace_bytes(16384, 8, 2) > 0
+    assert lib.pikv_quant_block_workspace_bytes(1024, 256, 1) > 0
+    # 16 header + K,V codes + scales, rounded to 16 bytes
+    assert lib.pikv_a2a_record_bytes(8) == 16 + 2 * 8 * 128 + 4 * 8
+    assert lib.pikv_decode_attn_workspace_bytes(64, 32, 8, 32768, 8) == 64 * 32 * 8 * 130 * 4
+
+
+def test_argument_errors_are_reported_without_a_gpu(built_lib):
+    from pikv_b200 import _lib
+    lib = _lib.lib()
+    p = _lib.GateParams()
+    assert lib.pikv_gate_fused(ctypes.byref(p), None) == -1          # PIKV_EINVAL: T, E, top_k = 0
+    assert b"positive" in lib.pikv_last_error()
+    p.T, p.E, p.top_k = 4, 100, 2
+    assert lib.pikv_gate_fused(ctypes.byref(p), None) == -4          # PIKV_ELIMIT: E > 64
+    a = _lib.AppendParams()
+    a.T, a.n_kv, a.top_k = 4, 8, 2
+    assert lib.pikv_kv_append_quant(ctypes.byref(a), None) == -1
+    assert lib.pikv_lowrank_project(None, None, None, None, None, 1, 128, 64, 1024, 1, None) == -1
+
+
+def test_operators_refuse_cpu_tensors(built_lib):
+    import torch
+    import pikv_b200
+    with pytest.raises(pikv_b200.PikvError):
+        pikv_b200.ops.gate_fused(logits=torch.randn(4, 8), top_k=2)
+    r = pikv_b200.TopKBalancedRouter(32, 4)
+    with pytest.raises(pikv_b200.PikvError):
+        r(torch.randn(1, 4, 32))

@@ -1,0 +1,424 @@
+"""GPU parity: quantised routed append, block-wide fake quantisation, H2O select / compact,
+decode attention, record pack / unpack - against the oracle and the reference's golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden, sub
+from oracle import pikv_oracle as O
+
+pytestmark = pytest.mark.gpu
+F32 = np.float32
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
+
+
+def rel(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-12)
+
+
+def outlier_kv(T, H, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, H, generator=g)
+    cols = torch.randperm(H, generator=g)[: max(1, round(0.01 * H))]
+    x[:, cols] *= 20.0
+    return x.bfloat16()
+
+
+def read_all(cache, lens, which):
+    E, cap = cache.num_seqs, cache.capacity
+    seq = np.repeat(np.arange(E), cap).astype(np.int32)
+    pos = np.tile(np.arange(cap), E).astype(np.int32)
+    valid = pos < lens[seq]
+    dev = cache.k_codes.device
+    dq, codes = cache.gather(torch.from_numpy(seq[valid]).to(dev), torch.from_numpy(pos[valid]).to(dev), which, codes=True)
+    return seq[valid], pos[valid], dq.cpu().numpy(), codes.cpu().numpy()
+
+
+# ---------------------------------------------------------------- append
+@pytest.mark.parametrize("bits,sym", [(8, True), (4, False), (8, False), (4, True)])
+@pytest.mark.parametrize("T,E,k,n_kv", [(300, 4, 2, 2), (2048, 8, 2, 8), (17, 3, 1, 1)])
+def test_append_codes_bit_exact(dev, bits, sym, T, E, k, n_kv):
+    import pikv_b200
+    H = n_kv * 128
+    K, V = outlier_kv(T, H, 1), outlier_kv(T, H, 2)
+    rng = np.random.default_rng(T)
+    idx = np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+    cap = max(16, int(T * 1.2 * k / E))                       # tight: some pairs are dropped
+    slot, counts_k = O.slot_assign_fast(idx, E, cap)
+    cache = pikv_b200.PagedKVCache(E, cap, n_kv, bits=bits, symmetric=sym, device=dev)
+    cache.append(K.to(dev), V.to(dev), torch.from_numpy(idx).to(dev), torch.from_numpy(slot).to(dev))
+    torch.cuda.synchronize()
+    cache.check_status()
+    ref = O.routed_append(K.float().numpy(), V.float().numpy(), idx, slot, E, cap, bits, sym, 128)
+    lens = ref["length"]
+    for which in ("k", "v"):
+        s, p, dq, codes = read_all(cache, lens, which)
+        np.testing.assert_array_equal(codes.astype(F32), ref[f"{which}_codes"][s, p])
+        # stored scale = bf16(fp32 scale); stored zero point exact
+        sc = O.bf16_round(ref[f"{which}_scale"][s, p])
+        want = O.dequant_token_groups(ref[f"{which}_codes"][s, p], sc, ref[f"{which}_zp"][s, p], 128)
+        np.testing.assert_array_equal(dq, want)
+        # and the bf16 scale costs < 2^-8 relative against the reference's own dequantised values
+        full = O.dequant_token_groups(ref[f"{which}_codes"][s, p], ref[f"{which}_scale"][s, p], ref[f"{which}_zp"][s, p], 128)
+        assert np.abs(dq - full).max() <= np.abs(full).max() * 2.0 ** -8
+
+
+def test_append_matches_reference_slices(dev):
+    """Codes of the reference's own _quantize_tensor on [1,128] slices (golden), including an all-zero
+    slice, a constant slice and a slice with a large offset."""
+    import pikv_b200
+    g = load_golden("quant_slices")
+    x = torch.from_numpy(g["x"]).bfloat16()
+    T = x.shape[0]
+    idx = torch.zeros(T, 1, dtype=torch.int32)
+    slot = torch.arange(T, dtype=torch.int32)[:, None]
+    for tag, bits, sym in (("int8_sym", 8, True), ("int4_asym", 4, False), ("int8_asym", 8, False), ("int4_sym", 4, True)):
+        cache = pikv_b200.PagedKVCache(1, 16, 2, bits=bits, symmetric=sym, device=dev)
+        cache.append(x.to(dev), x.to(dev), idx.to(dev), slot.to(dev))
+        _, codes = cache.gather(idx[:, 0].to(dev), slot[:, 0].to(dev), "k", codes=True)
+        np.testing.assert_array_equal(codes.cpu().numpy().astype(F32), g[f"{tag}/q"])
+        np.testing.assert_array_equal(cache.k_codes.cpu().numpy(), cache.v_codes.cpu().numpy())
+        cache.check_status()
+
+
+def test_append_fp32_input_and_empty(dev):
+    import pikv_b200
+    cache = pikv_b200.PagedKVCache(2, 32, 1, device=dev)
+    x = torch.randn(20, 128)
+    idx = torch.zeros(20, 1, dtype=torch.int32)
+    slot = torch.arange(20, dtype=torch.int32)[:, None]
+    cache.append(x.to(dev), x.to(dev), idx.to(dev), slot.to(dev))
+    q, sc, zp = O.quant_token_groups(x.numpy(), 8, 128, True)
+    _, codes = cache.gather(idx[:, 0].to(dev), slot[:, 0].to(dev), "k", codes=True)
+    np.testing.assert_array_equal(codes.cpu().numpy().astype(F32), q)
+    cache.append(x[:0].to(dev), x[:0].to(dev), idx[:0].to(dev), slot[:0].to(dev))     # empty batch is a no-op
+    cache.check_status()
+
+
+def test_append_flags_bad_destination(dev):
+    import pikv_b200
+    cache = pikv_b200.PagedKVCache(2, 32, 1, device=dev)
+    x = torch.randn(4, 128, device=dev).bfloat16()
+    idx = torch.tensor([[0], [7], [1], [0]], dtype=torch.int32, device=dev)       # 7 is not a sequence
+    slot = torch.tensor([[0], [0], [0], [1]], dtype=torch.int32, device=dev)
+    cache.append(x, x, idx, slot)
+    with pytest.raises(pikv_b200.PikvError):
+        cache.check_status()
+
+
+def test_full_size_append_properties(dev):
+    """Config-2 sized run checked through size-independent properties: slots are a bijection onto
+    [0, len) per expert; decode(encode(x)) is within half a quantisation step of x; K of a token is
+    identical in both of its experts."""
+    import pikv_b200
+    from pikv_b200 import ops
+    T, H, E, k, n_kv = 16384, 4096, 8, 2, 8
+    torch.manual_seed(0)
+    act = torch.randn(T, H, device=dev).bfloat16()
+    w2 = (torch.randn(E, H, device=dev) / 64).bfloat16()
+    K, V = outlier_kv(T, n_kv * 128, 3).to(dev), outlier_kv(T, n_kv * 128, 4).to(dev)
+    cap = O.capacity(T, 1.5, k, E)
+    g = ops.gate_fused(act, w2, None, top_k=k, capacity=cap)
+    cache = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
+    cache.append(K, V, g.topk_idx, g.slot)
+    cache.length.copy_(g.new_len)
+    cache.check_status()
+    idx, slot = g.topk_idx.cpu().numpy(), g.slot.cpu().numpy()
+    lens = g.new_len.cpu().numpy()
+    assert lens.sum() == (slot >= 0).sum()
+    for e in range(E):
+        s = np.sort(slot[(idx == e) & (slot >= 0)])
+        np.testing.assert_array_equal(s, np.arange(lens[e]))
+    ok = slot >= 0
+    t_ix, j_ix = np.nonzero(ok)
+    pick = np.random.default_rng(0).choice(len(t_ix), 4096, replace=False)
+    seq = torch.from_numpy(idx[t_ix[pick], j_ix[pick]].astype(np.int32)).to(dev)
+    pos = torch.from_numpy(slot[t_ix[pick], j_ix[pick]].astype(np.int32)).to(dev)
+    dq = cache.gather(seq, pos, "k").cpu().numpy().reshape(-1, n_kv, 128)
+    src = K.float().cpu().numpy()[t_ix[pick]].reshape(-1, n_kv, 128)
+    step = np.abs(src).max(-1, keepdims=True) * 2 / 255
+    assert (np.abs(dq - src) <= step * (0.5 + 2.0 ** -7) + 1e-7).all()
+    both = np.nonzero(ok.all(axis=1))[0][:512]
+    a = cache.gather(g.topk_idx[both, 0].contiguous(), g.slot[both, 0].contiguous(), "v", codes=True)[1]
+    b = cache.gather(g.topk_idx[both, 1].contiguous(), g.slot[both, 1].contiguous(), "v", codes=True)[1]
+    assert torch.equal(a, b)
+
+
+# ---------------------------------------------------------------- block-wide fake quantisation
+@pytest.mark.parametrize("tag,bits,gs,sym,single", [
+    ("single_b8g1", 8, 1, False, True), ("single_b4g16", 4, 16, False, True), ("single_b8g64", 8, 64, False, True),
+    ("module_b8g32s", 8, 32, True, False), ("module_b4g32a", 4, 32, False, False),
+    ("module_b4g16s", 4, 16, True, False), ("module_b8g64a", 8, 64, False, False)])
+def test_quant_block_matches_reference(dev, tag, bits, gs, sym, single):
+    import pikv_b200
+    from pikv_b200.module import compression as mc
+    g = load_golden("quant_block")
+    k, v = torch.from_numpy(g["keys"]).to(dev), torch.from_numpy(g["values"]).to(dev)
+    qc = (pikv_b200.QuantizedCompressor(64, bits=bits, group_size=gs) if single
+          else mc.QuantizedCompressor(64, bits=bits, group_size=gs, symmetric=sym)).to(dev)
+    dk, dv = qc(k, v)
+    np.testing.assert_array_equal(dk.cpu().numpy(), g[f"{tag}/dq_keys"])
+    np.testing.assert_array_equal(dv.cpu().numpy(), g[f"{tag}/dq_values"])
+    assert rel(float(qc.quantization_error), float(g[f"{tag}/quantization_error"])) < 1e-5
+    if single:
+        assert float(qc.sample_count) == float(g[f"{tag}/sample_count"])
+
+
+def test_quant_block_static_mode_matches_reference(dev):
+    import pikv_b200
+    g = load_golden("quant_block")
+    qc = pikv_b200.QuantizedCompressor(64, bits=8, group_size=16, dynamic_quantization=False).to(dev)
+    dk, dv = qc(torch.from_numpy(g["keys"]).to(dev), torch.from_numpy(g["values"]).to(dev))
+    np.testing.assert_array_equal(dk.cpu().numpy(), g["single_static/dq_keys"])
+    np.testing.assert_array_equal(dv.cpu().numpy(), g["single_static/dq_values"])
+    assert float(qc.scale) == float(g["single_static/scale"])
+
+
+def test_quant_block_large_bf16(dev):
+    from pikv_b200 import ops
+    x = outlier_kv(4099, 1024, 7)
+    dq, q, params, err = ops.quant_block(x.to(dev), 128, -128, 127, True, want_codes=True)
+    rdq, rq, rs, rz, _ = O.quant_block_forward(x.float().numpy(), 8, 128, True)
+    np.testing.assert_array_equal(q.cpu().numpy(), rq)
+    np.testing.assert_array_equal(dq.cpu().numpy(), rdq)
+    np.testing.assert_array_equal(params[:, 0].cpu().numpy(), rs)
+
+
+# ---------------------------------------------------------------- H2O
+def test_h2o_select_matches_reference_and_oracle(dev):
+    import pikv_b200
+    from pikv_b200 import ops
+    g = load_golden("h2o_select")
+    n = int(g["n"])
+    sch = pikv_b200.H2OScheduler(256, 16, heavy_ratio=0.1, recent_ratio=0.05).to(dev)
+    sch.attention_accumulator.copy_(torch.from_numpy(g["acc"]))
+    sch.access_timestamps.copy_(torch.from_numpy(g["ts"]))
+    keys = torch.zeros(n, 16, device=dev)
+    mask = sch.select_eviction_candidates(keys, keys, {})
+    np.testing.assert_array_equal(mask.cpu().numpy(), g["evict_mask"])
+    kept = int(sch.last_kept_count.item())
+    np.testing.assert_array_equal(sch.last_keep_idx[:kept].cpu().numpy(), np.nonzero(~g["evict_mask"])[0])
+
+
+@pytest.mark.parametrize("n,nh,nr,levels", [(1000, 100, 50, 0), (32768, 1792, 256, 0), (32768, 1792, 256, 8),
+                                            (5000, 1, 1, 3), (777, 777, 5, 0), (60000, 3000, 100, 16)])
+def test_h2o_select_segments_and_ties(dev, n, nh, nr, levels):
+    from pikv_b200 import ops
+    rng = np.random.default_rng(n + levels)
+    S = 5
+    acc = rng.random((S, n)).astype(F32) - 0.25
+    if levels:
+        acc = np.floor(acc * levels).astype(F32) / levels           # heavy ties
+    ts = np.tile(np.arange(n, dtype=F32), (S, 1))
+    ts[1] = rng.permutation(n).astype(F32)
+    ts[2] = np.floor(ts[2] / 7)                                      # tied timestamps
+    mask, keep, cnt = ops.h2o_select(torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev), nh, nr)
+    for s in range(S):
+        ev, ki = O.h2o_select(acc[s], ts[s], nh, nr)
+        np.testing.assert_array_equal(mask[s].cpu().numpy(), ev)
+        assert int(cnt[s]) == len(ki)
+        np.testing.assert_array_equal(keep[s, : len(ki)].cpu().numpy(), ki)
+
+
+def test_h2o_select_ragged_lengths(dev):
+    from pikv_b200 import ops
+    rng = np.random.default_rng(1)
+    lens = np.array([0, 1, 16, 100, 512], np.int32)
+    acc = rng.random((5, 512)).astype(F32)
+    ts = np.tile(np.arange(512, dtype=F32), (5, 1))
+    mask, keep, cnt = ops.h2o_select(torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev), 20, 10,
+                                     seg_len=torch.from_numpy(lens).to(dev))
+    for s, n in enumerate(lens):
+        ev = np.ones(512, bool)
+        if n:
+            ev[:n], ki = O.h2o_select(acc[s, :n], ts[s, :n], 20, 10)
+        else:
+            ki = np.zeros(0, np.int32)
+        np.testing.assert_array_equal(mask[s].cpu().numpy(), ev)
+        np.testing.assert_array_equal(keep[s, : len(ki)].cpu().numpy(), ki)
+        assert int(cnt[s]) == len(ki)
+
+
+def test_h2o_accumulate(dev):
+    import pikv_b200
+    sch = pikv_b200.H2OScheduler(128, 8).to(dev)
+    acc, ts, t = np.zeros(128, F32), np.zeros(128, F32), 0
+    rng = np.random.default_rng(2)
+    for _ in range(4):
+        ix = rng.permutation(128)[:40]
+        w = rng.random(40).astype(F32)
+        sch.update_attention_scores(torch.from_numpy(ix).to(dev), torch.from_numpy(w).to(dev))
+        t = O.h2o_update(acc, ts, t, ix, w)
+    np.testing.assert_array_equal(sch.attention_accumulator.cpu().numpy(), acc)
+    np.testing.assert_array_equal(sch.access_timestamps.cpu().numpy(), ts)
+    assert int(sch.current_time) == 4
+
+
+def test_manager_sequence_matches_reference(dev):
+    import pikv_b200
+    g = load_golden("h2o_manager")
+    mgr = pikv_b200.CacheSchedulingManager(64, 8, pikv_b200.SchedulingPolicy.H2O).to(dev)
+    for s in range(5):
+        c = sub(g, f"s{s}")
+        mgr.scheduler.attention_accumulator.copy_(torch.from_numpy(c["acc"]))
+        mgr.scheduler.access_timestamps.copy_(torch.from_numpy(c["ts"]))
+        mgr.update_cache(torch.from_numpy(c["keys_in"]).to(dev), torch.from_numpy(c["values_in"]).to(dev))
+        size = int(c["size"])
+        assert int(mgr.cache_size_current) == size
+        np.testing.assert_array_equal(mgr.cache_keys[:size].cpu().numpy(), c["cache_keys"][:size])
+        np.testing.assert_array_equal(mgr.cache_values[:size].cpu().numpy(), c["cache_values"][:size])
+        assert int(mgr.scheduler.eviction_count) == int(c["evictions"])
+
+
+# ---------------------------------------------------------------- decode attention
+def fill_stream_cache(dev, B, n_kv, ctx, lens, seed):
+    import pikv_b200
+    torch.manual_seed(seed)
+    cache = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)
+    # shuffle the physical pages so the page table is really used
+    perm = torch.randperm(cache.num_pages, device=dev).to(torch.int32)
+    cache.page_table.copy_(perm.view(B, -1))
+    K = torch.randn(B * ctx, n_kv * 128).bfloat16()
+    V = torch.randn(B * ctx, n_kv * 128).bfloat16()
+    seq = torch.arange(B, dtype=torch.int32).repeat_interleave(ctx)[:, None]
+    pos = torch.arange(ctx, dtype=torch.int32).repeat(B)[:, None]
+    cache.append(K.to(dev), V.to(dev), seq.to(dev), pos.to(dev))
+    cache.length.copy_(torch.from_numpy(lens).to(dev))
+    kd = cache.gather(seq[:, 0].to(dev), pos[:, 0].to(dev), "k").cpu().numpy().reshape(B, ctx, n_kv, 128).transpose(0, 2, 1, 3)
+    vd = cache.gather(seq[:, 0].to(dev), pos[:, 0].to(dev), "v").cpu().numpy().reshape(B, ctx, n_kv, 128).transpose(0, 2, 1, 3)
+    return cache, kd, vd
+
+
+@pytest.mark.parametrize("B,n_q,n_kv,ctx,splits", [(2, 8, 2, 100, 1), (3, 8, 2, 1000, 3), (2, 4, 4, 257, 2),
+                                                    (2, 16, 2, 640, 0), (1, 32, 8, 4096, 4), (4, 2, 2, 48, 5)])
+def test_decode_attention_matches_oracle(dev, B, n_q, n_kv, ctx, splits):
+    rng = np.random.default_rng(ctx)
+    lens = rng.integers(1, ctx + 1, B).astype(np.int32)
+    lens[0] = ctx
+    cache, kd, vd = fill_stream_cache(dev, B, n_kv, ctx, lens, ctx)
+    q = torch.randn(B, n_q, 128).bfloat16()
+    out, lse = cache.decode_attention(q.to(dev), splits=splits, want_lse=True)
+    cache.check_status()
+    want, _ = O.decode_attention(q.float().numpy(), kd, vd, lens)
+    got = out.float().cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
+    # log-sum-exp of the scaled scores
+    for b in range(B):
+        g = n_q // n_kv
+        for h in range(n_q):
+            s = (q[b, h].float().numpy() @ kd[b, h // g, : lens[b]].T) / np.sqrt(128.0)
+            ref = np.log(np.exp(s - s.max()).sum()) + s.max()
+            assert abs(float(lse[b, h]) - ref) < 1e-3 * max(1.0, abs(ref))
+
+
+def test_decode_attention_reference_mha_fixture(dev):
+    """1:1 heads, the reference's own _compute_attention output; the cache adds only int8 error."""
+    g = load_golden("attention_decode")
+    import pikv_b200
+    q = torch.from_numpy(g["q"][:, 0])
+    B, heads, d = q.shape
+    # the fixture has 16-wide heads; embed them in the first 16 of 128 channels (zeros elsewhere do not
+    # change q.k, and the 1/sqrt(d) factor is re-scaled through q)
+    ctx = g["k"].shape[1]
+    K = torch.zeros(B * ctx, heads * 128)
+    V = torch.zeros(B * ctx, heads * 128)
+    kk = torch.from_numpy(g["k"]).reshape(B * ctx, heads, 16)
+    vv = torch.from_numpy(g["v"]).reshape(B * ctx, heads, 16)
+    K.view(-1, heads, 128)[:, :, :16] = kk
+    V.view(-1, heads, 128)[:, :, :16] = vv
+    qq = torch.zeros(B, heads, 128)
+    qq[:, :, :16] = q * (128.0 / 16.0) ** 0.5
+    cache = pikv_b200.PagedKVCache(B, ctx, heads, device=dev)
+    seq = torch.arange(B, dtype=torch.int32).repeat_interleave(ctx)[:, None].to(dev)
+    pos = torch.arange(ctx, dtype=torch.int32).repeat(B)[:, None].to(dev)
+    cache.append(K.to(dev), V.to(dev), seq, pos)
+    cache.length.fill_(ctx)
+    out = cache.decode_attention(qq.bfloat16().to(dev)).float().cpu().numpy()[:, :, :16]
+    want = g["context"][:, 0]
+    assert np.abs(out - want).max() <= 3e-2 * np.abs(want).max()     # int8 cache + bf16 q/out vs the fp32 reference
+
+
+def test_decode_scores_feed_h2o_accumulate(dev):
+    from pikv_b200 import ops
+    B, n_q, n_kv, ctx = 2, 8, 2, 300
+    lens = np.array([300, 123], np.int32)
+    cache, kd, vd = fill_stream_cache(dev, B, n_kv, ctx, lens, 11)
+    q = torch.randn(B, n_q, 128).bfloat16()
+    scores = torch.zeros(B, n_q, ctx, device=dev)
+    out, lse = cache.decode_attention(q.to(dev), splits=2, scores=scores)
+    acc = torch.zeros(B * n_kv, ctx, device=dev)
+    ops.h2o_accumulate_attn(scores, lse, cache.length, n_kv, acc)
+    _, psum = O.decode_attention(q.float().numpy(), kd, vd, lens)
+    got = acc.cpu().numpy().reshape(B, n_kv, ctx)
+    assert np.abs(got - psum).max() < 1e-4
+    assert np.abs(got.sum(-1) - n_q // n_kv).max() < 1e-3           # probabilities of each query head sum to 1
+
+
+# ---------------------------------------------------------------- compaction
+@pytest.mark.parametrize("per_head", [True, False])
+def test_h2o_compact_moves_rows_and_scores(dev, per_head):
+    import pikv_b200
+    from pikv_b200 import ops
+    B, n_kv, ctx = 3, 2, 200
+    lens = np.array([200, 150, 64], np.int32)
+    cache, kd, vd = fill_stream_cache(dev, B, n_kv, ctx, lens, 5)
+    segs = B * n_kv if per_head else B
+    rng = np.random.default_rng(0)
+    acc = rng.random((segs, ctx)).astype(F32)
+    ts = np.tile(np.arange(ctx, dtype=F32), (segs, 1))
+    seg_len = np.repeat(lens, n_kv) if per_head else lens
+    mask, keep, cnt = ops.h2o_select(torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev), 40, 8,
+                                     seg_len=torch.from_numpy(seg_len.astype(np.int32)).to(dev))
+    dst = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)
+    dacc = torch.zeros(segs, ctx, device=dev)
+    dts = torch.zeros(segs, ctx, device=dev)
+    cache.compact_into(dst, keep, cnt, per_head, torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev), dacc, dts)
+    cache.check_status()
+    for s in range(segs):
+        b = s // n_kv if per_head else s
+        heads = [s % n_kv] if per_head else list(range(n_kv))
+        ev, ki = O.h2o_select(acc[s, : seg_len[s]], ts[s, : seg_len[s]], 40, 8)
+        n = len(ki)
+        seq = torch.full((n,), b, dtype=torch.int32, device=dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        gk = dst.gather(seq, pos, "k").cpu().numpy().reshape(n, n_kv, 128)
+        gv = dst.gather(seq, pos, "v").cpu().numpy().reshape(n, n_kv, 128)
+        for h in heads:
+            np.testing.assert_array_equal(gk[:, h], kd[b, h, ki])
+            np.testing.assert_array_equal(gv[:, h], vd[b, h, ki])
+        np.testing.assert_array_equal(dacc[s, :n].cpu().numpy(), acc[s, ki])
+        np.testing.assert_array_equal(dts[s, :n].cpu().numpy(), ts[s, ki])
+
+
+# ---------------------------------------------------------------- exchange records
+def test_a2a_pack_unpack_equals_direct_append(dev):
+    import pikv_b200
+    from pikv_b200 import ops
+    T, E, k, n_kv = 500, 4, 2, 2
+    K, V = outlier_kv(T, n_kv * 128, 8).to(dev), outlier_kv(T, n_kv * 128, 9).to(dev)
+    rng = np.random.default_rng(4)
+    idx = np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+    cap = 300
+    slot, _ = O.slot_assign_fast(idx, E, cap)
+    direct = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
+    direct.append(K, V, torch.from_numpy(idx).to(dev), torch.from_numpy(slot).to(dev))
+    # records in (destination, token, j) order, as the exchange would deliver them
+    flat_ok = (slot >= 0).reshape(-1)
+    order = np.argsort(idx.reshape(-1) // 2, kind="stable")            # two "ranks" own two experts each
+    order = order[flat_ok[order]]
+    send_pos = np.full(T * k, -1, np.int32)
+    send_pos[order] = np.arange(len(order), dtype=np.int32)
+    buf = ops.a2a_pack(K, V, n_kv, torch.from_numpy(idx).to(dev), torch.from_numpy(slot).to(dev),
+                       torch.from_numpy(send_pos.reshape(T, k)).to(dev), len(order))
+    via = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
+    via.unpack_records(buf, len(order))
+    via.check_status()
+    for name in ("k_codes", "v_codes", "k_scale", "v_scale"):
+        assert torch.equal(getattr(direct, name), getattr(via, name)), name

@@ -1,0 +1,209 @@
+"""GPU parity: the fused gate kernel and the router classes against the oracle and the
+reference's golden vectors.  Integer outputs must be bit-exact; probabilities and
+weights within 1e-5 relative (fp32)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden, sub
+from oracle import pikv_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F32 = np.float32
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
+
+
+def rel(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-12)
+
+
+def check_gate(g, logits, k, cap, E, **tail):
+    """Everything the kernel derives from given logits must equal the oracle's."""
+    probs, idx, tw = O.gate_tail(logits, k, **tail)
+    gi = g.topk_idx.cpu().numpy()
+    # identical logits -> identical experts, except where two probabilities are closer than fp32 exp noise
+    same = (gi == idx).all(axis=1)
+    margin = O.topk_margin(probs, k)
+    assert (same | (margin < 1e-6)).all(), f"{(~same).sum()} tokens differ beyond the near-tie margin"
+    assert rel(g.probs.cpu().numpy(), probs) < 1e-5
+    ok = same
+    assert rel(g.topk_w.cpu().numpy()[ok], tw[ok]) < 1e-5
+    slot, counts_k = O.slot_assign_fast(gi, E, cap if cap > 0 else 1 << 30)
+    np.testing.assert_array_equal(g.slot.cpu().numpy(), slot)
+    np.testing.assert_array_equal(g.counts_k.cpu().numpy(), counts_k)
+    assert rel(g.prob_sum.cpu().numpy(), probs.sum(0)) < 1e-5
+    want_len = np.minimum(counts_k.sum(0), cap) if cap > 0 else counts_k.sum(0)
+    np.testing.assert_array_equal(g.new_len.cpu().numpy(), want_len)
+    return int((~same).sum())
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 4, 2), (37, 4, 2), (1024, 8, 2), (5000, 64, 2), (777, 16, 4), (300, 64, 8),
+                                   (16384, 8, 2)])
+def test_gate_from_logits(dev, T, E, k):
+    from pikv_b200 import ops
+    rng = np.random.default_rng(T + E)
+    logits = rng.standard_normal((T, E)).astype(F32) * 2
+    cap = O.capacity(T, 1.5, k, E)
+    g = ops.gate_fused(logits=torch.from_numpy(logits).to(dev), top_k=k, capacity=cap)
+    check_gate(g, logits, k, cap, E)
+
+
+def test_gate_mask_correction_temperature(dev):
+    from pikv_b200 import ops, _lib
+    rng = np.random.default_rng(3)
+    T, E, k = 2000, 8, 2
+    logits = rng.standard_normal((T, E)).astype(F32)
+    mask = np.array([1, 1, 0, 1, 1, 0, 1, 1], F32)
+    corr = (rng.random(E) + 0.5).astype(F32)
+    lt = torch.from_numpy(logits).to(dev)
+    for mode, name in ((_lib.MASK_SINGLE, "single"), (_lib.MASK_MODULE, "module")):
+        g = ops.gate_fused(logits=lt, top_k=k, expert_mask=torch.from_numpy(mask).to(dev), mask_mode=mode,
+                           correction=torch.from_numpy(corr).to(dev), capacity=0, renorm_eps=1e-8)
+        check_gate(g, logits, k, 0, E, expert_mask=mask, mask_mode=name, correction=corr, renorm_eps=1e-8)
+        assert not np.isin(g.topk_idx.cpu().numpy(), [2, 5]).any()      # masked experts are never chosen
+    bias = rng.standard_normal(E).astype(F32)
+    g = ops.gate_fused(logits=lt, top_k=k, expert_mask=torch.from_numpy(bias).to(dev), mask_mode=_lib.MASK_BIAS,
+                       temperature=0.7)
+    check_gate(g, logits, k, 0, E, expert_mask=bias, mask_mode="bias", temperature=0.7)
+
+
+def test_gate_ties_go_to_lowest_index(dev):
+    from pikv_b200 import ops
+    logits = np.zeros((64, 8), F32)
+    logits[:, 5] = 1.0
+    logits[10, :] = 0.0                      # fully tied row
+    g = ops.gate_fused(logits=torch.from_numpy(logits).to(dev), top_k=3)
+    gi = g.topk_idx.cpu().numpy()
+    np.testing.assert_array_equal(gi[0], [5, 0, 1])
+    np.testing.assert_array_equal(gi[10], [0, 1, 2])
+    _, idx, _ = O.gate_tail(logits, 3)
+    np.testing.assert_array_equal(gi, idx)
+
+
+def test_gate_slot_base_and_capacity_drop(dev):
+    from pikv_b200 import ops
+    rng = np.random.default_rng(5)
+    T, E, k, cap = 600, 4, 2, 200
+    logits = rng.standard_normal((T, E)).astype(F32)
+    base = np.array([0, 150, 199, 200], np.int32)
+    g = ops.gate_fused(logits=torch.from_numpy(logits).to(dev), top_k=k, capacity=cap,
+                       slot_base=torch.from_numpy(base).to(dev))
+    gi = g.topk_idx.cpu().numpy()
+    pos, counts_k = O.slot_assign_fast(gi, E, 1 << 30)
+    want = pos + base[gi]
+    want = np.where(want < cap, want, -1)
+    np.testing.assert_array_equal(g.slot.cpu().numpy(), want)
+    np.testing.assert_array_equal(g.new_len.cpu().numpy(), np.minimum(base + counts_k.sum(0), cap))
+    assert (want[gi == 3] == -1).all()       # expert 3 was already full
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,E", [(256, 256, 4), (1000, 512, 8), (300, 1024, 64), (130, 72, 16)])
+def test_gate_from_activations(dev, dtype, T, H, E):
+    from pikv_b200 import ops
+    torch.manual_seed(T + H)
+    act = torch.relu(torch.randn(T, H)).to(dtype)
+    w2 = (torch.randn(E, H) / H ** 0.5).to(dtype)
+    b2 = torch.randn(E) * 0.1
+    k = 2
+    cap = O.capacity(T, 1.5, k, E)
+    g = ops.gate_fused(act.to(dev), w2.to(dev), b2.to(dev), top_k=k, capacity=cap)
+    logits = O.gate_logits(act.float().numpy(), w2.float().numpy(), b2.numpy())
+    probs, idx, tw = O.gate_tail(logits, k)
+    gi = g.topk_idx.cpu().numpy()
+    same = (gi == idx).all(axis=1)
+    margin = O.topk_margin(probs, k)
+    # the GEMM's fp32 accumulation order differs from the CPU's: only near-ties may flip
+    assert (same | (margin < 1e-4)).all()
+    assert (~same).sum() <= max(1, T // 200)
+    assert rel(g.probs.cpu().numpy(), probs) < 2e-5
+    slot, counts_k = O.slot_assign_fast(gi, E, cap)
+    np.testing.assert_array_equal(g.slot.cpu().numpy(), slot)
+    np.testing.assert_array_equal(g.counts_k.cpu().numpy(), counts_k)
+
+
+def test_gate_is_deterministic(dev):
+    from pikv_b200 import ops
+    torch.manual_seed(9)
+    act = torch.randn(4096, 512, device=dev).bfloat16()
+    w2 = torch.randn(8, 512, device=dev).bfloat16()
+    a = ops.gate_fused(act, w2, None, top_k=2, capacity=1536)
+    b = ops.gate_fused(act, w2, None, top_k=2, capacity=1536)
+    for x, y in ((a.probs, b.probs), (a.slot, b.slot), (a.prob_sum, b.prob_sum), (a.topk_w, b.topk_w)):
+        assert torch.equal(x, y)
+
+
+# ---------------------------------------------------------------- router classes vs the reference's outputs
+def load_sd(module, weights, dev):
+    sd = {k: torch.from_numpy(np.array(v)) for k, v in weights.items()}
+    module.load_state_dict(sd)
+    return module.to(dev)
+
+
+def test_base_router_matches_reference(dev):
+    import pikv_b200
+    g = load_golden("router_base_single")
+    r = load_sd(pikv_b200.BaseRouter(64, 4, 2), sub(g, "weights"), dev)
+    x = torch.from_numpy(g["x"]).to(dev)
+    for tag, mask in (("", None), ("_m", torch.from_numpy(g["mask"]).to(dev))):
+        d, c, p, aux = r(x, mask)
+        assert rel(p.cpu().numpy(), g["probs" + tag]) < 1e-5
+        np.testing.assert_array_equal(d.cpu().numpy(), g["dispatch" + tag])
+        assert rel(c.cpu().numpy(), g["combine" + tag]) < 1e-5
+        assert abs(float(aux) - float(g["aux" + tag])) < 1e-5 * max(1.0, abs(float(g["aux" + tag])))
+
+
+@pytest.mark.parametrize("mode", ["entropy", "cv", "l2"])
+def test_topk_balanced_router_matches_reference(dev, mode):
+    import pikv_b200
+    g = load_golden("router_topk_balanced_single")
+    s = sub(g, mode)
+    r = load_sd(pikv_b200.TopKBalancedRouter(64, 4, 2, balance_coefficient=0.01, balance_mode=mode), sub(s, "weights"), dev)
+    d, c, p, aux = r(torch.from_numpy(g["x"]).to(dev))
+    assert rel(p.cpu().numpy(), s["probs"]) < 1e-5
+    np.testing.assert_array_equal(d.cpu().numpy(), s["dispatch"])
+    assert rel(c.cpu().numpy(), s["combine"]) < 1e-5
+    assert abs(float(aux) - float(s["aux"])) < 2e-5
+
+
+def test_pikv_router_state_machine_matches_reference(dev):
+    import pikv_b200
+    g = load_golden("router_pikv_single")
+    r = load_sd(pikv_b200.PiKVRouter(64, 4, 2, cache_update_interval=2), sub(g, "weights"), dev)
+    kv = torch.from_numpy(g["kv"]).to(dev)
+    with torch.no_grad():
+        for i in range(3):
+            c = sub(g, f"call{i}")
+            d, cmb, p, aux, imp = r(torch.from_numpy(c["x"]).to(dev), kv_states=kv if i == 1 else None)
+            assert rel(p.cpu().numpy(), c["probs"]) < 2e-5
+            assert rel(imp.cpu().numpy(), c["importance"]) < 1e-5
+            np.testing.assert_array_equal(d.cpu().numpy(), c["dispatch"])
+            assert rel(cmb.cpu().numpy(), c["combine"]) < 2e-5
+            assert rel(r.cache_usage_history.cpu().numpy(), c["history"]) < 1e-5
+            assert rel(r.cache_correction_factor.detach().cpu().numpy(), c["factor"]) < 1e-5
+            assert abs(float(aux) - float(c["aux"])) < 2e-5
+    assert int(r.update_counter) == 3
+
+
+def test_module_running_slots_match_reference_dispatch(dev):
+    """The kernel's slot output reproduces the dense tensors core/single/module builds."""
+    from pikv_b200 import ops
+    g = load_golden("router_base_module")
+    logits = g["logits"].reshape(-1, 4)
+    cap = O.capacity(24, 1.0, 2, 4)
+    res = ops.gate_fused(logits=torch.from_numpy(logits).to(dev), top_k=2, capacity=cap, renorm_eps=1e-8)
+    d, c = ops.dispatch_scatter(res, 4, cap, position_mode=0)
+    np.testing.assert_array_equal(d.cpu().numpy(), g["dispatch"].reshape(24, 4, cap))
+    assert rel(c.cpu().numpy(), g["combine"].reshape(24, 4, cap)) < 1e-5
+    np.testing.assert_array_equal(res.counts.cpu().numpy(), g["usage"].astype(np.int64))
+    p_mean = res.prob_sum.cpu().numpy() / 24
+    f = res.counts.cpu().numpy() / 48.0
+    assert abs(float((p_mean * f).sum() * 4) - float(g["aux"])) < 1e-5
