@@ -108,6 +108,10 @@ typedef struct {
 
 size_t pikv_gate_workspace_bytes(int32_t T, int32_t E, int32_t top_k);
 int    pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream);
+/* bf16 activations run on the tcgen05 kernel (TMA + tensor memory), fp32 ones on the SIMT
+ * kernel.  Reads and clears the tensor-core kernel's sticky error word (non-zero: a bounded
+ * mbarrier wait ran out and the outputs are invalid); waits for the work queued before it. */
+int    pikv_gate_error_state(void);
 
 /* Dense [T,E,capacity] dispatch / combine tensors (zero-filled by this call)
  * for callers that read them.  position_mode 0: slot as given (running count,
@@ -282,7 +286,7 @@ int pikv_h2o_accumulate_attn(const float* scores, int32_t score_stride, const fl
  * compressor's two Linears (core/single/kv_cache_compression.py:38-39);
  * replaces launch_svd_compression_kernel / launch_pyramid_compression_kernel
  * (core/cuda/pikv_compression_kernel.cu:507-553).
- *   x, w bf16 row-major (K contiguous), K % 64 == 0, N % 16 == 0, N <= 256 per
+ *   x, w bf16 row-major (K contiguous), K % 16 == 0, N % 16 == 0, N <= 256 per
  *   call column block (larger N is tiled internally); out bf16 or fp32.
  *   residual (optional) [M,N] bf16 added after the activation.
  * ---------------------------------------------------------------------- */

@@ -79,6 +79,7 @@ SIGNATURES = {
     "pikv_launch_count": (u64, []),
     "pikv_gate_workspace_bytes": (sz, [i32, i32, i32]),
     "pikv_gate_fused": (i32, [C.POINTER(GateParams), vp]),
+    "pikv_gate_error_state": (i32, []),
     "pikv_dispatch_scatter": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_kv_append_quant": (i32, [C.POINTER(AppendParams), vp]),
     "pikv_cache_gather": (i32, [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),

@@ -36,7 +36,7 @@ class BaseCompressor(nn.Module):
 def _linear(layer: nn.Linear, x: torch.Tensor, relu: bool) -> torch.Tensor:
     """One Linear (+ReLU): tcgen05 kernel for bf16 inputs whose shapes fit, cuBLAS otherwise."""
     K, N = layer.in_features, layer.out_features
-    if x.dtype == torch.bfloat16 and x.is_cuda and K % 64 == 0 and N % 16 == 0 and (N <= 256 or N % 256 == 0):
+    if x.dtype == torch.bfloat16 and x.is_cuda and K % 16 == 0 and N % 16 == 0 and (N <= 256 or N % 256 == 0):
         lead = x.shape[:-1]
         y = ops.lowrank_project(x.reshape(-1, K), layer.weight.detach().to(torch.bfloat16), layer.bias, relu=relu)
         return y.view(*lead, N)

@@ -65,12 +65,14 @@ __global__ void __launch_bounds__(256) a2a_pack_kernel(const TIn* k, const TIn* 
     }
     if (!active) return;
     const QParams qp = quant_params(mn, mx, -128, 127, true);
+    const float inv = __frcp_rn(qp.scale);
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         uint32_t acc = 0;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) acc |= ((uint32_t)((int)quant_code(x[4 * i + c], qp, -128.f, 127.f) & 0xff)) << (8 * c);
+        for (int c = 0; c < 4; ++c)
+            acc |= ((uint32_t)((int)quant_code_fast(x[4 * i + c], qp, inv, -128.f, 127.f) & 0xff)) << (8 * c);
         w[i] = acc;
     }
     const size_t rec = a2a_record_bytes(n_kv);

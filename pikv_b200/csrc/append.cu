@@ -84,9 +84,10 @@ __global__ void __launch_bounds__(APPEND_THREADS) kv_append_quant_kernel(AppendD
     }
     if (!active) return;
     const QParams qp = quant_params(mn, mx, QMIN, QMAX, SYM);
+    const float inv = __frcp_rn(qp.scale);
     int q[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = (int)quant_code(x[i], qp, (float)QMIN, (float)QMAX);
+    for (int i = 0; i < 16; ++i) q[i] = (int)quant_code_fast(x[i], qp, inv, (float)QMIN, (float)QMAX);
 
     // pack
     uint32_t w[4];

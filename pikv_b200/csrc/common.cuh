@@ -93,6 +93,17 @@ __device__ __forceinline__ QParams quant_params(float x_min, float x_max, int qm
 __device__ __forceinline__ float quant_code(float x, QParams p, float qmin, float qmax) {
     return fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(x, p.scale), p.zp)), qmin), qmax);
 }
+// Same code as quant_code without a division per element: y ~ x * (1/scale) + zp is within a
+// few ulp of the exactly rounded x / scale + zp, so rint(y) can only differ from the reference
+// when y sits next to a .5 boundary; exactly those elements (and any non-finite y) take the
+// IEEE-division path.  inv = __frcp_rn(scale).
+__device__ __forceinline__ float quant_code_fast(float x, QParams p, float inv, float qmin, float qmax) {
+    const float y = __fadd_rn(__fmul_rn(x, inv), p.zp);
+    float q = rintf(y);
+    const float d = fabsf(__fsub_rn(y, q));          // distance to the nearest integer, <= 0.5
+    if (!(d < 0.499f) || !(fabsf(y) < 1.0e6f)) q = rintf(__fadd_rn(__fdiv_rn(x, p.scale), p.zp));
+    return fminf(fmaxf(q, qmin), qmax);
+}
 __device__ __forceinline__ float dequant_code(float q, QParams p) {
     return __fmul_rn(__fsub_rn(q, p.zp), p.scale);
 }

@@ -7,116 +7,10 @@
 //   gate_finalize   each CTA turns its local ranks into global slots from the exclusive
 //                   prefix of the per-CTA counts; CTA 0 also reduces the totals.
 // Results are therefore run-to-run bit-identical.
-#include "common.cuh"
+#include "gate_common.cuh"
+#include <stdlib.h>
 
 namespace pikv {
-
-constexpr int GATE_THREADS = 256;
-constexpr int GATE_WARPS = GATE_THREADS / 32;
-constexpr int GATE_MAX_CTAS = 1024;
-constexpr int GATE_MAX_CHUNK = 4096;   // tokens per CTA
-constexpr int GATE_MAX_K = 8;
-constexpr int GATE_MAX_E = 64;
-
-struct GateDev {
-    const void* act;
-    const void* w2;
-    const float* b2;
-    const float* logits_in;
-    int T, H, E, k;
-    const float* mask;
-    int mask_mode;
-    const float* corr;
-    float temperature, eps;
-    int capacity;
-    const int* slot_base;
-    float* probs;
-    int* topk_idx;
-    float* topk_w;
-    int* slot;
-    int* counts_k;
-    float* prob_sum;
-    int* new_len;
-    int chunk, G;
-    int* cta_cnt;     // [G][E]
-    int* cta_cnt_k;   // [G][k][E]
-    float* cta_psum;  // [G][E]
-};
-
-// ---- per-token tail: everything after the logits ---------------------------------
-// l[] holds the token's logits (entries >= E are ignored).  Writes the token's outputs
-// and returns the probabilities in l[].
-template <int EP>
-__device__ __forceinline__ void token_tail(float (&l)[EP], const GateDev& g, int t, uint8_t* sel_row) {
-    const int E = g.E;
-#pragma unroll
-    for (int e = 0; e < EP; ++e) {
-        if (e < E) {
-            float x = l[e];
-            if (g.temperature != 1.0f) x = __fdiv_rn(x, g.temperature);
-            if (g.corr) x = __fmul_rn(x, g.corr[e]);
-            if (g.mask_mode == PIKV_MASK_SINGLE)
-                x = __fadd_rn(x, __fmul_rn(__fsub_rn(1.0f, g.mask[e]), -1e9f));
-            else if (g.mask_mode == PIKV_MASK_MODULE)
-                x = __fadd_rn(x, __fmul_rn(__fsub_rn(1.0f, g.mask[e]), -3.402823466e+38f));
-            else if (g.mask_mode == PIKV_MASK_BIAS)
-                x = __fadd_rn(x, g.mask[e]);
-            l[e] = x;
-        } else {
-            l[e] = -INFINITY;
-        }
-    }
-    float m = l[0];
-#pragma unroll
-    for (int e = 1; e < EP; ++e) m = fmaxf(m, l[e]);
-    float s = 0.f;
-#pragma unroll
-    for (int e = 0; e < EP; ++e) {
-        float p = (e < E) ? expf(l[e] - m) : 0.f;
-        l[e] = p;
-        s += p;
-    }
-#pragma unroll
-    for (int e = 0; e < EP; ++e) l[e] = __fdiv_rn(l[e], s);
-    if (g.probs) {
-#pragma unroll
-        for (int e = 0; e < EP; ++e)
-            if (e < E) g.probs[(size_t)t * E + e] = l[e];
-    }
-    // top-k on the probabilities; strict '>' keeps the lowest index on ties
-    unsigned long long taken = 0ull;
-    int idx[GATE_MAX_K];
-    float val[GATE_MAX_K];
-    float wsum = 0.f;
-#pragma unroll
-    for (int j = 0; j < GATE_MAX_K; ++j) {
-        if (j < g.k) {
-            float best = -1.f;
-            int bi = 0;
-#pragma unroll
-            for (int e = 0; e < EP; ++e) {
-                bool free_e = !((taken >> e) & 1ull);
-                if (e < E && free_e && l[e] > best) {
-                    best = l[e];
-                    bi = e;
-                }
-            }
-            taken |= 1ull << bi;
-            idx[j] = bi;
-            val[j] = best;
-            wsum += best;
-        }
-    }
-    const float denom = __fadd_rn(wsum, g.eps);
-#pragma unroll
-    for (int j = 0; j < GATE_MAX_K; ++j) {
-        if (j < g.k) {
-            g.topk_idx[(size_t)t * g.k + j] = idx[j];
-            if (g.topk_w) g.topk_w[(size_t)t * g.k + j] = __fdiv_rn(val[j], denom);
-            sel_row[j] = (uint8_t)idx[j];
-        }
-    }
-}
 
 // ---- per-CTA ranking of its (token, k) pairs, in order ----------------------------
 // sel[0..npairs) holds the expert of every pair of this CTA's chunk.  Writes the local
@@ -440,7 +334,10 @@ extern "C" int pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream) 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
     const int E = g.E;
-    if (g.act != nullptr) {
+    const char* force_simt = getenv("PIKV_GATE_SIMT");   // testing aid: run bf16 through the SIMT kernel too
+    if (g.act != nullptr && g.w2 != nullptr && gate_tc_supported(g, p->dtype) && !(force_simt && force_simt[0] == '1')) {
+        rc = gate_tc_launch(g, st);
+    } else if (g.act != nullptr) {
         PIKV_REQUIRE(g.w2 != nullptr, PIKV_EINVAL, "gate: w2 is required with act");
         PIKV_REQUIRE(g.H > 0 && g.H % 8 == 0, PIKV_EUNSUPPORTED, "gate: H=%d must be a positive multiple of 8", g.H);
         PIKV_REQUIRE(p->dtype == PIKV_F32 || p->dtype == PIKV_BF16, PIKV_EINVAL, "gate: bad dtype %d", p->dtype);

@@ -71,10 +71,11 @@ __global__ void __launch_bounds__(QB_COLS) qb_apply_kernel(const TIn* x, int N, 
     p.zp = params[2 * g + 1];
     const int r0 = rb * rows_per, r1 = min(N, r0 + rows_per);
     float err = 0.f;
+    const float inv = __frcp_rn(p.scale);
     for (int r = r0; r < r1; ++r) {
         const size_t o = (size_t)r * H + col;
         const float v = ldx<TIn>(x + o);
-        const float q = quant_code(v, p, qmin, qmax);
+        const float q = quant_code_fast(v, p, inv, qmin, qmax);
         const float dq = dequant_code(q, p);
         if (dq_out) dq_out[o] = dq;
         if (q_out) q_out[o] = q;

@@ -60,6 +60,8 @@ def test_append_codes_bit_exact(dev, bits, sym, T, E, k, n_kv):
     lens = ref["length"]
     for which in ("k", "v"):
         s, p, dq, codes = read_all(cache, lens, which)
+        if not sym:
+            codes = codes.view(np.uint8)        # asymmetric codes are unsigned bytes
         np.testing.assert_array_equal(codes.astype(F32), ref[f"{which}_codes"][s, p])
         # stored scale = bf16(fp32 scale); stored zero point exact
         sc = O.bf16_round(ref[f"{which}_scale"][s, p])
@@ -83,7 +85,10 @@ def test_append_matches_reference_slices(dev):
         cache = pikv_b200.PagedKVCache(1, 16, 2, bits=bits, symmetric=sym, device=dev)
         cache.append(x.to(dev), x.to(dev), idx.to(dev), slot.to(dev))
         _, codes = cache.gather(idx[:, 0].to(dev), slot[:, 0].to(dev), "k", codes=True)
-        np.testing.assert_array_equal(codes.cpu().numpy().astype(F32), g[f"{tag}/q"])
+        codes = codes.cpu().numpy()
+        if not sym:
+            codes = codes.view(np.uint8)
+        np.testing.assert_array_equal(codes.astype(F32), g[f"{tag}/q"])
         np.testing.assert_array_equal(cache.k_codes.cpu().numpy(), cache.v_codes.cpu().numpy())
         cache.check_status()
 

@@ -130,6 +130,54 @@ def test_gate_from_activations(dev, dtype, T, H, E):
     np.testing.assert_array_equal(g.counts_k.cpu().numpy(), counts_k)
 
 
+def test_gate_bf16_simt_and_tensor_core_paths_agree(dev, monkeypatch):
+    """bf16 activations normally take the tcgen05 kernel; the SIMT kernel must give the same experts
+    and slots (near-ties aside) and probabilities within fp32 accumulation noise."""
+    import pikv_b200
+    from pikv_b200 import ops
+    torch.manual_seed(21)
+    T, H, E = 3000, 1024, 8
+    act = torch.relu(torch.randn(T, H, device=dev)).bfloat16()
+    w2 = (torch.randn(E, H, device=dev) / 32).bfloat16()
+    tc = ops.gate_fused(act, w2, None, top_k=2, capacity=1200)
+    torch.cuda.synchronize()
+    assert pikv_b200.lib().pikv_gate_error_state() == 0
+    monkeypatch.setenv("PIKV_GATE_SIMT", "1")
+    simt = ops.gate_fused(act, w2, None, top_k=2, capacity=1200)
+    monkeypatch.delenv("PIKV_GATE_SIMT")
+    same = (tc.topk_idx == simt.topk_idx).all(dim=1)
+    assert int((~same).sum()) <= 3
+    assert torch.allclose(tc.probs, simt.probs, rtol=1e-4, atol=1e-7)
+    if bool(same.all()):
+        assert torch.equal(tc.slot, simt.slot) and torch.equal(tc.counts_k, simt.counts_k)
+
+
+@pytest.mark.parametrize("T,H,E,k", [(128, 64, 8, 2), (129, 4096, 8, 2), (16384, 4096, 8, 2), (1000, 4096, 64, 2),
+                                     (5000, 200, 20, 4), (200000, 128, 8, 2)])
+def test_gate_tensor_core_shapes(dev, T, H, E, k):
+    """Ragged tiles, hidden sizes that are not multiples of 64, padded expert counts, several tiles per CTA."""
+    import pikv_b200
+    from pikv_b200 import ops
+    torch.manual_seed(T)
+    act = torch.relu(torch.randn(T, H, device=dev)).bfloat16()
+    w2 = (torch.randn(E, H, device=dev) / H ** 0.5).bfloat16()
+    b2 = torch.randn(E, device=dev) * 0.1
+    cap = O.capacity(T, 1.25, k, E)
+    g = ops.gate_fused(act, w2, b2, top_k=k, capacity=cap)
+    torch.cuda.synchronize()
+    assert pikv_b200.lib().pikv_gate_error_state() == 0
+    logits = (act.float() @ w2.float().T + b2).cpu().numpy()
+    probs, idx, tw = O.gate_tail(logits, k)
+    gi = g.topk_idx.cpu().numpy()
+    same = (gi == idx).all(axis=1)
+    assert (same | (O.topk_margin(probs, k) < 1e-4)).all()
+    assert rel(g.probs.cpu().numpy(), probs) < 2e-5
+    slot, counts_k = O.slot_assign_fast(gi, E, cap)
+    np.testing.assert_array_equal(g.slot.cpu().numpy(), slot)
+    np.testing.assert_array_equal(g.counts_k.cpu().numpy(), counts_k)
+    assert rel(g.prob_sum.cpu().numpy(), probs.sum(0)) < 1e-4
+
+
 def test_gate_is_deterministic(dev):
     from pikv_b200 import ops
     torch.manual_seed(9)

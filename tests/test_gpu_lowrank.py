@@ -12,6 +12,12 @@ pytestmark = pytest.mark.gpu
 F32 = np.float32
 
 
+@pytest.fixture(autouse=True)
+def _no_grad():
+    with torch.no_grad():
+        yield
+
+
 @pytest.fixture(scope="module")
 def dev():
     if not torch.cuda.is_available():
@@ -29,7 +35,7 @@ def state(dev, weights):
 
 
 @pytest.mark.parametrize("M,N,K,relu", [(128, 64, 64, True), (128, 64, 1024, True), (1000, 32, 1024, True),
-                                        (4096, 16, 1024, False), (300, 1024, 64, False), (513, 256, 128, True),
+                                        (4096, 16, 1024, False), (300, 1024, 64, False), (700, 1024, 32, False), (260, 256, 16, True), (513, 256, 128, True),
                                         (8192, 64, 1024, True)])
 def test_lowrank_project_matches_oracle(dev, M, N, K, relu):
     import pikv_b200
