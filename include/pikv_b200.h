@@ -49,7 +49,6 @@ extern "C" {
 /* bits set in the device status word that kernels OR into (never trap) */
 #define PIKV_ST_BAD_SEQ     1u   /* destination sequence id out of range        */
 #define PIKV_ST_BAD_PAGE    2u   /* page-table entry out of range               */
-#define PIKV_ST_ZP_CLAMPED  4u   /* int16 zero point saturated                  */
 #define PIKV_ST_BAD_INDEX   8u   /* gather / scatter index out of range         */
 #define PIKV_ST_WAIT_TIMEOUT 16u /* a bounded in-kernel wait ran out; result invalid */
 
@@ -140,7 +139,8 @@ int pikv_dispatch_scatter(const int32_t* topk_idx, const float* topk_w, const in
  *          for 8-bit codes, and the 8-byte unit u at unit (u ^ (token_in_page & 4))
  *          for 4-bit codes (two codes per byte, low nibble = even channel)
  *   scale  [pages][n_kv][16] bf16
- *   zp     [pages][n_kv][16] int16 (asymmetric only)
+ *   zp     [pages][n_kv][16] fp32 (asymmetric only; the reference's zero point is an
+ *          integer-valued fp32 that a constant group drives to millions, so it is kept exact)
  * A "sequence" is whatever owns a page-table row: an expert, a decode stream,
  * or an (expert, stream) pair.
  * ---------------------------------------------------------------------- */
@@ -155,7 +155,7 @@ typedef struct {
     int32_t bits, symmetric;   /* (8,1) (8,0) (4,1) (4,0)                       */
     void* k_codes; void* v_codes;
     void* k_scale; void* v_scale;   /* bf16                                     */
-    void* k_zp;    void* v_zp;      /* int16, asymmetric only                   */
+    void* k_zp;    void* v_zp;      /* fp32, asymmetric only                    */
     uint32_t* status;          /* device word, OR-ed with PIKV_ST_* (may be NULL) */
 } pikv_append_params;
 

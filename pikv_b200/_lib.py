@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "libpikv_b200.so")
 
 PIKV_F32, PIKV_BF16 = 0, 1
 MASK_NONE, MASK_SINGLE, MASK_MODULE, MASK_BIAS = 0, 1, 2, 3
-ST_BAD_SEQ, ST_BAD_PAGE, ST_ZP_CLAMPED, ST_BAD_INDEX, ST_WAIT_TIMEOUT = 1, 2, 4, 8, 16
+ST_BAD_SEQ, ST_BAD_PAGE, ST_BAD_INDEX, ST_WAIT_TIMEOUT = 1, 2, 8, 16
 PAGE_TOKENS = 16
 HEAD_DIM = 128
 ABI_VERSION = 1

@@ -23,7 +23,7 @@ struct AppendDev {
     int num_seqs, max_pages, num_pages;
     uint8_t* codes[2];
     uint16_t* scale[2];
-    int16_t* zp[2];
+    float* zp[2];
     unsigned* status;
 };
 
@@ -106,13 +106,6 @@ __global__ void __launch_bounds__(APPEND_THREADS) kv_append_quant_kernel(AppendD
         }
     }
     const uint16_t scale_bits = f32_to_bf16_bits(qp.scale);
-    int zp_i = 0;
-    bool zp_clamped = false;
-    if (!SYM) {
-        float z = fminf(fmaxf(qp.zp, -32768.f), 32767.f);
-        zp_clamped = (z != qp.zp);
-        zp_i = (int)z;
-    }
 
     for (int j = 0; j < a.top_k; ++j) {
         const int s = a.slot[(size_t)t * a.top_k + j];
@@ -137,20 +130,17 @@ __global__ void __launch_bounds__(APPEND_THREADS) kv_append_quant_kernel(AppendD
         }
         if (sub == 0) {
             a.scale[which][prow] = scale_bits;
-            if (!SYM) {
-                a.zp[which][prow] = (int16_t)zp_i;
-                if (zp_clamped && a.status) atomicOr(a.status, PIKV_ST_ZP_CLAMPED);
-            }
+            if (!SYM) a.zp[which][prow] = qp.zp;
         }
     }
 }
 
 // ---- logical read-back ----------------------------------------------------------------
 // One 8-lane group per (row i, head): un-swizzle, unpack, dequantise with the stored
-// bf16 scale / int16 zero point.
+// bf16 scale / fp32 zero point.
 __global__ void cache_gather_kernel(const int* seq, const int* pos, int n, const int* page_table, int num_seqs,
                                     int max_pages, int num_pages, int n_kv, int bits, const uint8_t* codes,
-                                    const uint16_t* scale, const int16_t* zp, float* out, int8_t* codes_out,
+                                    const uint16_t* scale, const float* zp, float* out, int8_t* codes_out,
                                     unsigned* status) {
     const int sub = threadIdx.x & 7;
     const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
@@ -169,7 +159,7 @@ __global__ void cache_gather_kernel(const int* seq, const int* pos, int n, const
     const int row = p % PT;
     const size_t prow = ((size_t)page * n_kv + head) * PT + row;
     const float sc = bf16_bits_to_f32(scale[prow]);
-    const float z = zp ? (float)zp[prow] : 0.f;
+    const float z = zp ? zp[prow] : 0.f;
     int q[16];
     if (bits == 8) {
         uint4 w = *reinterpret_cast<const uint4*>(codes + prow * D + 16 * swz8_chunk(row, sub));
@@ -228,7 +218,7 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
     a.codes[0] = static_cast<uint8_t*>(p->k_codes); a.codes[1] = static_cast<uint8_t*>(p->v_codes);
     a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
-    a.zp[0] = static_cast<int16_t*>(p->k_zp); a.zp[1] = static_cast<int16_t*>(p->v_zp);
+    a.zp[0] = static_cast<float*>(p->k_zp); a.zp[1] = static_cast<float*>(p->v_zp);
     a.status = p->status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (p->dtype == PIKV_BF16) return launch_append<__nv_bfloat16>(a, p->bits, p->symmetric, st);
@@ -247,7 +237,7 @@ extern "C" int pikv_cache_gather(const int32_t* seq, const int32_t* pos, int32_t
     const long long lanes = (long long)n * n_kv * 8;
     cache_gather_kernel<<<(int)ceil_div64(lanes, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         seq, pos, n, page_table, num_seqs, max_pages, num_pages, n_kv, bits, static_cast<const uint8_t*>(codes),
-        static_cast<const uint16_t*>(scale), static_cast<const int16_t*>(zp), out, codes_out, status);
+        static_cast<const uint16_t*>(scale), static_cast<const float*>(zp), out, codes_out, status);
     count_launch(1);
     return check_launch("cache_gather_kernel");
 }

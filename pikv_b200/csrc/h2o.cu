@@ -247,8 +247,8 @@ __global__ void __launch_bounds__(256) h2o_compact_kernel(CompactDev c) {
         static_cast<uint16_t*>(p.dst_k_scale)[dprow] = static_cast<const uint16_t*>(p.src_k_scale)[sprow];
         static_cast<uint16_t*>(p.dst_v_scale)[dprow] = static_cast<const uint16_t*>(p.src_v_scale)[sprow];
         if (p.src_k_zp && p.dst_k_zp) {
-            static_cast<int16_t*>(p.dst_k_zp)[dprow] = static_cast<const int16_t*>(p.src_k_zp)[sprow];
-            static_cast<int16_t*>(p.dst_v_zp)[dprow] = static_cast<const int16_t*>(p.src_v_zp)[sprow];
+            static_cast<float*>(p.dst_k_zp)[dprow] = static_cast<const float*>(p.src_k_zp)[sprow];
+            static_cast<float*>(p.dst_v_zp)[dprow] = static_cast<const float*>(p.src_v_zp)[sprow];
         }
         if (hs == 0) {
             if (p.src_acc && p.dst_acc)

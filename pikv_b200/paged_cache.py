@@ -6,7 +6,7 @@ hold 16 tokens.  Pools (indexed by physical page id):
 
     k_codes, v_codes  uint8 [pages, n_kv, 16, 128*bits/8]   (chunk-swizzled rows)
     k_scale, v_scale  bf16  [pages, n_kv, 16]
-    k_zp, v_zp        int16 [pages, n_kv, 16]                (asymmetric only)
+    k_zp, v_zp        fp32  [pages, n_kv, 16]                (asymmetric only)
 
 The row placement follows CacheSchedulingManager.update_cache
 (core/single/cache_scheduling.py:430-436: contiguous rows, truncation at
@@ -47,8 +47,8 @@ class PagedKVCache(torch.nn.Module):
         self.register_buffer("k_scale", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.bfloat16))
         self.register_buffer("v_scale", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.bfloat16))
         if not self.symmetric:
-            self.register_buffer("k_zp", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.int16))
-            self.register_buffer("v_zp", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.int16))
+            self.register_buffer("k_zp", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.float32))
+            self.register_buffer("v_zp", z(self.num_pages, n_kv, PAGE_TOKENS, dtype=torch.float32))
         else:
             self.k_zp = self.v_zp = None
         if identity_table:
