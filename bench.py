@@ -33,6 +33,8 @@ WORKLOAD = dict(workload="route+int8-quant+append", tokens=16384, hidden=4096, e
                 head_dim=128, page_tokens=16, quant="int8-sym-g128", capacity_factor=1.5)
 GATE_BYTES_PER_TOKEN = 4096 * 2 + 8 * 4 + 3 * 2 * 4                      # act in; probs, idx, w, slot out
 APPEND_BYTES_PER_TOKEN = 2 * 1024 * 2 + 16 + 2 * 2 * 1024 + 2 * 16 * 2   # K,V in; idx/slot; 2 copies of codes + scales
+# DRAM bytes per launch (read + write) at 16384 tokens, from the ncu captures summarised under profiles/
+TRAFFIC = {"gate": 138.9e6, "append": 118.6e6}
 
 
 def measured_peak_gbs():
@@ -126,7 +128,6 @@ def cpu_threads():
 
 
 def run_cpu(steps, warmup, tokens):
-    import numpy as np
     cfg = WORKLOAD
     H, E, k = cfg["hidden"], cfg["experts"], cfg["top_k"]
     kv = cfg["kv_heads"] * cfg["head_dim"]
@@ -187,85 +188,125 @@ def gpu_arm(args):
     T, H, E, k = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["top_k"]
     n_kv = cfg["kv_heads"]
     kv = n_kv * cfg["head_dim"]
-    cap = int(T * cfg["capacity_factor"] * k / E)
     w2, b2 = gate_weights(H, E, 7)
     w2, b2 = w2.to(dev), b2.to(dev)
-
-    if world > 1:
-        from pikv_b200 import distributed as pd
-        step_fn, sets, extra_cfg = pd.make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs)
-        R = len(sets)
-    else:
-        # R rotating input sets and caches so that no step finds its inputs in L2 (each set is 201 MB)
-        R = 3
-        sets = [synth_inputs(T, H, E, kv, 100 + i, device=dev) for i in range(R)]
-        caches = [pikv_b200.PagedKVCache(E, cap, n_kv, device=dev) for _ in range(R)]
-        outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=cap, want_probs=True) for _ in range(R)]
-        extra_cfg = {"parallelism": "single"}
-
-        def step_fn(i):
-            act, K, V = sets[i % R]
-            g = ops.gate_fused(act, w2, b2, top_k=k, capacity=cap, out=outs[i % R])
-            caches[i % R].append(K, V, g.topk_idx, g.slot)
-            return g
+    steps, warmup = args.steps, max(args.warmup, 3)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        step_fn(i)
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
+    def capture(fn):
+        """CUDA graph of the C-ABI calls `fn` makes (they allocate nothing and never synchronise)."""
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        n0 = pikv_b200.launch_count()
+        with torch.cuda.graph(graph):
+            fn()
+        return graph, pikv_b200.launch_count() - n0
+
+    def timed(replay, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(n):
+            replay(i)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1)
+
+    def single_gpu_workload(tokens):
+        """R rotating input sets and caches so that no step finds its inputs in L2 (one set is 201 MB at
+        16384 tokens, L2 is 126 MB)."""
+        cap = int(tokens * cfg["capacity_factor"] * k / E)
+        R = 3
+        sets = [synth_inputs(tokens, H, E, kv, 100 + i, device=dev) for i in range(R)]
+        caches = [pikv_b200.PagedKVCache(E, cap, n_kv, device=dev) for _ in range(R)]
+        outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=cap, want_probs=True) for _ in range(R)]
+
+        def gate(i):
+            return ops.gate_fused(sets[i][0], w2, b2, top_k=k, capacity=cap, out=outs[i])
+
+        def append(i):
+            caches[i].append(sets[i][1], sets[i][2], outs[i].topk_idx, outs[i].slot)
+
+        def step(i):
+            gate(i)
+            append(i)
+
+        return dict(R=R, cap=cap, sets=sets, caches=caches, outs=outs, gate=gate, append=append, step=step)
+
+    def kernel_times(w, n):
+        """Average device time of the gate and of the append, each replayed as its own graph, with events
+        on the launching stream in between."""
+        gg = [capture(lambda i=i: w["gate"](i))[0] for i in range(w["R"])]
+        ga = [capture(lambda i=i: w["append"](i))[0] for i in range(w["R"])]
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n)]
+        for i in range(3):
+            gg[i % w["R"]].replay()
+            ga[i % w["R"]].replay()
+        barrier()
+        for i in range(n):
+            ev[i][0].record()
+            gg[i % w["R"]].replay()
+            ev[i][1].record()
+            ga[i % w["R"]].replay()
+            ev[i][2].record()
+        barrier()
+        return (sum(e[0].elapsed_time(e[1]) for e in ev) / n, sum(e[1].elapsed_time(e[2]) for e in ev) / n)
+
+    roof = e2e = cpu = large = None
+    if world > 1:
+        from pikv_b200 import distributed as pd
+        step_fn, extra_cfg = pd.make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs)
+        for i in range(warmup):
+            step_fn(i)
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        n0 = pikv_b200.launch_count()
+        ms = timed(step_fn, steps)
+        launches = pikv_b200.launch_count() - n0
+        R = extra_cfg.pop("buffer_sets", 1)
+        e2e = extra_cfg.pop("e2e", None)
+        launch_mode = "eager C-ABI calls + NCCL all-to-all"
+    else:
+        wl = single_gpu_workload(T)
+        R = wl["R"]
+        graphs = [capture(lambda i=i: wl["step"](i)) for i in range(R)]
+        for i in range(warmup):
+            graphs[i % R][0].replay()
+        sampler = ClockSampler(local)
         sampler.start()
-    launches0 = pikv_b200.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        step_fn(i)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = pikv_b200.launch_count() - launches0
+        ms = timed(lambda i: graphs[i % R][0].replay(), steps)
+        launches = graphs[0][1] * steps
+        extra_cfg = {"parallelism": "single"}
+        launch_mode = "one CUDA graph replay per step (captured C-ABI calls)"
     t = torch.tensor([ms], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
-    value = T * world * args.steps / (ms_max * 1e-3)
+    value = T * world * steps / (ms_max * 1e-3)
 
-    # per-kernel time of the two parts, measured live with events on the launching stream
-    roof = None
-    e2e = None
-    cpu = None
     if world == 1:
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-        barrier()
-        for i in range(args.steps):
-            act, K, V = sets[i % R]
-            ev[i][0].record()
-            g = ops.gate_fused(act, w2, b2, top_k=k, capacity=cap, out=outs[i % R])
-            ev[i][1].record()
-            caches[i % R].append(K, V, g.topk_idx, g.slot)
-            ev[i][2].record()
-        barrier()
-        gate_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-        app_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
         peak, peak_src = measured_peak_gbs()
+        gate_ms, app_ms = kernel_times(wl, steps)
         gate_gbs = GATE_BYTES_PER_TOKEN * T / (gate_ms * 1e-3) / 1e9
         app_gbs = APPEND_BYTES_PER_TOKEN * T / (app_ms * 1e-3) / 1e9
-        step_gbs = (GATE_BYTES_PER_TOKEN + APPEND_BYTES_PER_TOKEN) * T / (ms_max / args.steps * 1e-3) / 1e9
+        step_gbs = (GATE_BYTES_PER_TOKEN + APPEND_BYTES_PER_TOKEN) * T / (ms_max / steps * 1e-3) / 1e9
         dom = "gate" if gate_ms >= app_ms else "append"
-        roof = {"bound": "hbm", "kernel": "gate_fused (gate_act_kernel + gate_finalize_kernel)" if dom == "gate" else "kv_append_quant_kernel",
+        roof = {"bound": "hbm",
+                "kernel": "gate_tc_kernel (+ gate_finalize_kernel)" if dom == "gate" else "kv_append_quant_kernel",
                 "achieved": gate_gbs if dom == "gate" else app_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                "frac": (gate_gbs if dom == "gate" else app_gbs) / peak, "traffic": None,
+                "frac": (gate_gbs if dom == "gate" else app_gbs) / peak, "traffic": TRAFFIC.get(dom),
                 "gate": {"ms": gate_ms, "GBps": gate_gbs, "frac": gate_gbs / peak, "bytes_per_token": GATE_BYTES_PER_TOKEN},
                 "append": {"ms": app_ms, "GBps": app_gbs, "frac": app_gbs / peak, "bytes_per_token": APPEND_BYTES_PER_TOKEN},
                 "step": {"GBps": step_gbs, "frac": step_gbs / peak}}
 
-        # end to end: pinned host inputs copied in, routing result read back, every step
+        # end to end: pinned host inputs copied in, routing result read back, every step (eager calls)
+        cap, caches, outs = wl["cap"], wl["caches"], wl["outs"]
         h_sets = [synth_inputs(T, H, E, kv, 200 + i, pin=True) for i in range(2)]
         d_in = [tuple(torch.empty_like(x, device=dev) for x in h_sets[0]) for _ in range(2)]
         h_out = [torch.empty(T, k, dtype=torch.int32).pin_memory(), torch.empty(T, k, dtype=torch.float32).pin_memory(),
@@ -273,8 +314,8 @@ def gpu_arm(args):
 
         def e2e_step(i):
             src, dst = h_sets[i % 2], d_in[i % 2]
-            for s, d in zip(src, dst):
-                d.copy_(s, non_blocking=True)
+            for s_, d_ in zip(src, dst):
+                d_.copy_(s_, non_blocking=True)
             g = ops.gate_fused(dst[0], w2, b2, top_k=k, capacity=cap, out=outs[i % R])
             caches[i % R].append(dst[1], dst[2], g.topk_idx, g.slot)
             h_out[0].copy_(g.topk_idx, non_blocking=True)
@@ -284,19 +325,32 @@ def gpu_arm(args):
 
         for i in range(3):
             e2e_step(i)
-        barrier()
-        e0.record()
-        for i in range(args.steps):
-            e2e_step(i)
-        e1.record()
-        barrier()
-        e2e_ms = e0.elapsed_time(e1)
+        e2e_ms = timed(e2e_step, steps)
         h2d = sum(x.numel() * x.element_size() for x in h_sets[0])
         d2h = sum(x.numel() * x.element_size() for x in h_out)
-        e2e = {"value": T * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": e2e_ms / args.steps}
+        e2e = {"value": T * steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms / steps}
         for c in caches:
             c.check_status()
+        assert pikv_b200.lib().pikv_gate_error_state() == 0, "a bounded wait in the gate kernel ran out"
+        del wl, graphs, h_sets, d_in, caches, outs
+        torch.cuda.empty_cache()
+
+        if not args.no_large:
+            # the same step at 8x the tokens: launch overhead and tail effects no longer matter
+            T8 = 8 * T
+            w8 = single_gpu_workload(T8)
+            g8 = [capture(lambda i=i: w8["step"](i))[0] for i in range(w8["R"])]
+            for i in range(3):
+                g8[i % w8["R"]].replay()
+            steps8 = max(3, steps // 4)
+            ms8 = timed(lambda i: g8[i % w8["R"]].replay(), steps8)
+            gate8, app8 = kernel_times(w8, steps8)
+            large = {"tokens": T8, "value": T8 * steps8 / (ms8 * 1e-3), "unit": UNIT, "ms_per_step": ms8 / steps8,
+                     "gate_frac": GATE_BYTES_PER_TOKEN * T8 / (gate8 * 1e-3) / 1e9 / peak,
+                     "append_frac": APPEND_BYTES_PER_TOKEN * T8 / (app8 * 1e-3) / 1e9 / peak,
+                     "step_frac": (GATE_BYTES_PER_TOKEN + APPEND_BYTES_PER_TOKEN) * T8 / (ms8 / steps8 * 1e-3) / 1e9 / peak}
+            del w8, g8
     clocks = sampler.stop() if rank == 0 else None
 
     if world == 1 and not args.no_cpu_baseline:
@@ -304,15 +358,14 @@ def gpu_arm(args):
         cpu = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
                "sample": f"3 full batches of {T} tokens on the host (numpy port of the reference arithmetic)"}
 
-    if world > 1:
-        e2e = extra_cfg.pop("e2e", None)
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16 in, fp32 math, int8 codes", "data": "synthetic",
             "config": {**cfg, **extra_cfg, "l2": f"inputs larger than L2, rotated over {R} buffer sets"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "launch": launch_mode, "roofline": roof,
+            "cpu_baseline": cpu, "large_batch": large,
         }
         print(json.dumps(line))
     if world > 1:
@@ -326,6 +379,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-side port timing (profiling runs)")
+    ap.add_argument("--no-large", action="store_true", help="skip the 8x-token secondary measurement")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

@@ -6,7 +6,7 @@
 // Record (int8 symmetric), 16-byte aligned:
 //   int32 seq, int32 slot, 8 bytes pad | K codes [n_kv*128] | V codes [n_kv*128]
 //   | K scales [n_kv] bf16 | V scales [n_kv] bf16 | pad to 16
-#include "common.cuh"
+#include "quant_group.cuh"
 
 namespace pikv {
 
@@ -15,26 +15,6 @@ constexpr int PT = PIKV_PAGE_TOKENS;
 __host__ __device__ inline size_t a2a_record_bytes(int n_kv) {
     size_t b = 16 + (size_t)2 * n_kv * 128 + (size_t)4 * n_kv;
     return (b + 15) / 16 * 16;
-}
-
-template <typename TIn>
-__device__ __forceinline__ void a2a_load16(const TIn* p, float (&x)[16]);
-template <>
-__device__ __forceinline__ void a2a_load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[16]) {
-    uint4 a = ld_stream_16(p), b = ld_stream_16(p + 8);
-    bf16x2_to_f32(a.x, x[0], x[1]);   bf16x2_to_f32(a.y, x[2], x[3]);
-    bf16x2_to_f32(a.z, x[4], x[5]);   bf16x2_to_f32(a.w, x[6], x[7]);
-    bf16x2_to_f32(b.x, x[8], x[9]);   bf16x2_to_f32(b.y, x[10], x[11]);
-    bf16x2_to_f32(b.z, x[12], x[13]); bf16x2_to_f32(b.w, x[14], x[15]);
-}
-template <>
-__device__ __forceinline__ void a2a_load16<float>(const float* p, float (&x)[16]) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint4 a = ld_stream_16(p + 4 * i);
-        x[4 * i] = __uint_as_float(a.x); x[4 * i + 1] = __uint_as_float(a.y);
-        x[4 * i + 2] = __uint_as_float(a.z); x[4 * i + 3] = __uint_as_float(a.w);
-    }
 }
 
 // one 8-lane group per (token, K|V, head); codes are written once per destination record
@@ -50,31 +30,13 @@ __global__ void __launch_bounds__(256) a2a_pack_kernel(const TIn* k, const TIn* 
     const int rr = active ? (int)(group % per_tok) : 0;
     const int which = rr / n_kv, head = rr % n_kv;
     float x[16];
-    if (active) a2a_load16<TIn>((which ? v : k) + ((size_t)t * n_kv + head) * 128 + sub * 16, x);
-    else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = 0.f;
-    }
-    float mn = x[0], mx = x[0];
-#pragma unroll
-    for (int i = 1; i < 16; ++i) { mn = fminf(mn, x[i]); mx = fmaxf(mx, x[i]); }
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    }
+    qg_load16<TIn>((which ? v : k) + ((size_t)t * n_kv + head) * 128 + sub * 16, x);
+    float mn, mx;
+    qg_group_minmax(x, mn, mx);
     if (!active) return;
-    const QParams qp = quant_params(mn, mx, -128, 127, true);
-    const float inv = __frcp_rn(qp.scale);
+    QParams qp;
     uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t acc = 0;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-            acc |= ((uint32_t)((int)quant_code_fast(x[4 * i + c], qp, inv, -128.f, 127.f) & 0xff)) << (8 * c);
-        w[i] = acc;
-    }
+    qg_quantize16<8, true>(x, mn, mx, qp, w);
     const size_t rec = a2a_record_bytes(n_kv);
     for (int j = 0; j < top_k; ++j) {
         const int sp = send_pos[(size_t)t * top_k + j];

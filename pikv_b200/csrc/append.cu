@@ -1,11 +1,11 @@
 // Routed KV append fused with per-(token, head) quantisation, and the logical read-back.
 //
-// Work unit = one (token, K|V, head) group of 128 channels, handled by 8 lanes that each
-// own 16 consecutive channels: two 16-byte loads of bf16 in, one 16-byte (int8) or 8-byte
-// (int4) store of codes out per destination.  The 8 lanes of a group write one full
+// Work unit = the K and the V slice of one (token, head): two groups of 128 channels handled
+// by 8 lanes that each own 16 consecutive channels of both: four 16-byte loads of bf16 in,
+// one 16-byte (int8) or 8-byte (int4) store of codes per tensor and destination out.  The 8 lanes of a group write one full
 // 128-byte row of the destination page, so stores are whole lines even though the
 // destinations are scattered.  The group statistics are a 3-step xor shuffle.
-#include "common.cuh"
+#include "quant_group.cuh"
 
 namespace pikv {
 
@@ -16,7 +16,7 @@ constexpr int PT = PIKV_PAGE_TOKENS;    // 16 tokens per page
 struct AppendDev {
     const void* k;
     const void* v;
-    int T, n_kv, top_k;
+    int T, n_kv, top_k, log2_nkv;
     const int* dst_seq;
     const int* slot;
     const int* page_table;
@@ -27,85 +27,40 @@ struct AppendDev {
     unsigned* status;
 };
 
-template <typename TIn>
-__device__ __forceinline__ void load16(const TIn* p, float (&x)[16]);
-template <>
-__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[16]) {
-    uint4 a = ld_stream_16(p);
-    uint4 b = ld_stream_16(p + 8);
-    bf16x2_to_f32(a.x, x[0], x[1]);   bf16x2_to_f32(a.y, x[2], x[3]);
-    bf16x2_to_f32(a.z, x[4], x[5]);   bf16x2_to_f32(a.w, x[6], x[7]);
-    bf16x2_to_f32(b.x, x[8], x[9]);   bf16x2_to_f32(b.y, x[10], x[11]);
-    bf16x2_to_f32(b.z, x[12], x[13]); bf16x2_to_f32(b.w, x[14], x[15]);
-}
-template <>
-__device__ __forceinline__ void load16<float>(const float* p, float (&x)[16]) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint4 a = ld_stream_16(p + 4 * i);
-        x[4 * i + 0] = __uint_as_float(a.x); x[4 * i + 1] = __uint_as_float(a.y);
-        x[4 * i + 2] = __uint_as_float(a.z); x[4 * i + 3] = __uint_as_float(a.w);
-    }
-}
-
+// One 8-lane group per (token, head): both the K and the V slice of that head, so four
+// 16-byte loads are in flight per lane and the destination lookup is shared.
 template <typename TIn, int BITS, bool SYM>
 __global__ void __launch_bounds__(APPEND_THREADS) kv_append_quant_kernel(AppendDev a) {
-    constexpr int QMIN = SYM ? -(1 << (BITS - 1)) : 0;
-    constexpr int QMAX = SYM ? (1 << (BITS - 1)) - 1 : (1 << BITS) - 1;
     constexpr int ROW_BYTES = D * BITS / 8;
     const int sub = threadIdx.x & 7;                       // lane within the group
-    const long long group = ((long long)blockIdx.x * APPEND_THREADS + threadIdx.x) >> 3;
-    const int per_tok = 2 * a.n_kv;
-    const long long total = (long long)a.T * per_tok;
-    const bool active = group < total;
-    const int t = active ? (int)(group / per_tok) : 0;
-    const int r = active ? (int)(group % per_tok) : 0;
-    const int which = r / a.n_kv;                          // 0 = K, 1 = V
-    const int head = r % a.n_kv;
-
-    float x[16];
-    if (active) {
-        const TIn* src = static_cast<const TIn*>(which ? a.v : a.k) + ((size_t)t * a.n_kv + head) * D + sub * 16;
-        load16<TIn>(src, x);
+    const unsigned pair = (blockIdx.x * (unsigned)APPEND_THREADS + threadIdx.x) >> 3;
+    const unsigned total = (unsigned)a.T * (unsigned)a.n_kv;
+    const bool active = pair < total;
+    unsigned t, head;
+    if (a.log2_nkv >= 0) {
+        t = pair >> a.log2_nkv;
+        head = pair & ((1u << a.log2_nkv) - 1u);
     } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = 0.f;
+        t = pair / (unsigned)a.n_kv;
+        head = pair % (unsigned)a.n_kv;
     }
-    float mn = x[0], mx = x[0];
-#pragma unroll
-    for (int i = 1; i < 16; ++i) {
-        mn = fminf(mn, x[i]);
-        mx = fmaxf(mx, x[i]);
+    if (!active) t = 0, head = 0;
+
+    float xk[16], xv[16];
+    {
+        const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
+        qg_load16<TIn>(static_cast<const TIn*>(a.k) + off, xk);
+        qg_load16<TIn>(static_cast<const TIn*>(a.v) + off, xv);
     }
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    }
+    float kmn, kmx, vmn, vmx;
+    qg_group_minmax(xk, kmn, kmx);
+    qg_group_minmax(xv, vmn, vmx);
     if (!active) return;
-    const QParams qp = quant_params(mn, mx, QMIN, QMAX, SYM);
-    const float inv = __frcp_rn(qp.scale);
-    int q[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = (int)quant_code_fast(x[i], qp, inv, (float)QMIN, (float)QMAX);
-
-    // pack
-    uint32_t w[4];
-    if (BITS == 8) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            w[i] = (uint32_t)(q[4 * i] & 0xff) | ((uint32_t)(q[4 * i + 1] & 0xff) << 8) |
-                   ((uint32_t)(q[4 * i + 2] & 0xff) << 16) | ((uint32_t)(q[4 * i + 3] & 0xff) << 24);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            uint32_t v = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v |= (uint32_t)(q[8 * i + j] & 0xf) << (4 * j);
-            w[i] = v;
-        }
-    }
-    const uint16_t scale_bits = f32_to_bf16_bits(qp.scale);
+    QParams kq, vq;
+    uint32_t kw[4], vw[4];
+    qg_quantize16<BITS, SYM>(xk, kmn, kmx, kq, kw);
+    qg_quantize16<BITS, SYM>(xv, vmn, vmx, vq, vw);
+    const uint16_t ks_bits = f32_to_bf16_bits(kq.scale), vs_bits = f32_to_bf16_bits(vq.scale);
 
     for (int j = 0; j < a.top_k; ++j) {
         const int s = a.slot[(size_t)t * a.top_k + j];
@@ -122,15 +77,22 @@ __global__ void __launch_bounds__(APPEND_THREADS) kv_append_quant_kernel(AppendD
         }
         const int row = s % PT;
         const size_t prow = ((size_t)page * a.n_kv + head) * PT + row;
-        uint8_t* dst = a.codes[which] + prow * ROW_BYTES;
         if (BITS == 8) {
-            *reinterpret_cast<uint4*>(dst + 16 * swz8_chunk(row, sub)) = make_uint4(w[0], w[1], w[2], w[3]);
+            const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
+            *reinterpret_cast<uint4*>(a.codes[0] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+            *reinterpret_cast<uint4*>(a.codes[1] + o) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
         } else {
-            *reinterpret_cast<uint2*>(dst + 8 * swz4_unit(row, sub)) = make_uint2(w[0], w[1]);
+            const size_t o = prow * ROW_BYTES + 8 * swz4_unit(row, sub);
+            *reinterpret_cast<uint2*>(a.codes[0] + o) = make_uint2(kw[0], kw[1]);
+            *reinterpret_cast<uint2*>(a.codes[1] + o) = make_uint2(vw[0], vw[1]);
         }
         if (sub == 0) {
-            a.scale[which][prow] = scale_bits;
-            if (!SYM) a.zp[which][prow] = qp.zp;
+            a.scale[0][prow] = ks_bits;
+            a.scale[1][prow] = vs_bits;
+            if (!SYM) {
+                a.zp[0][prow] = kq.zp;
+                a.zp[1][prow] = vq.zp;
+            }
         }
     }
 }
@@ -188,7 +150,7 @@ __global__ void cache_gather_kernel(const int* seq, const int* pos, int n, const
 
 template <typename TIn>
 static int launch_append(const AppendDev& a, int bits, int symmetric, cudaStream_t st) {
-    const long long lanes = (long long)a.T * 2 * a.n_kv * 8;
+    const long long lanes = (long long)a.T * a.n_kv * 8;
     const int grid = (int)ceil_div64(lanes, APPEND_THREADS);
     if (bits == 8 && symmetric) kv_append_quant_kernel<TIn, 8, true><<<grid, APPEND_THREADS, 0, st>>>(a);
     else if (bits == 8) kv_append_quant_kernel<TIn, 8, false><<<grid, APPEND_THREADS, 0, st>>>(a);
@@ -213,7 +175,11 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     PIKV_REQUIRE(p->dtype == PIKV_BF16 || p->dtype == PIKV_F32, PIKV_EINVAL, "append: bad dtype %d", p->dtype);
     PIKV_REQUIRE(p->num_seqs > 0 && p->max_pages > 0 && p->num_pages > 0, PIKV_EINVAL, "append: bad cache geometry");
     AppendDev a;
+    PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28), PIKV_ELIMIT, "append: T * n_kv must stay below 2^28 per call");
     a.k = p->k; a.v = p->v; a.T = p->T; a.n_kv = p->n_kv; a.top_k = p->top_k;
+    a.log2_nkv = -1;
+    for (int b = 0; b < 16; ++b)
+        if ((1 << b) == p->n_kv) a.log2_nkv = b;
     a.dst_seq = p->dst_seq; a.slot = p->slot; a.page_table = p->page_table;
     a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
     a.codes[0] = static_cast<uint8_t*>(p->k_codes); a.codes[1] = static_cast<uint8_t*>(p->v_codes);

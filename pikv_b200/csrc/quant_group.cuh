@@ -1,0 +1,110 @@
+// Per-(token, head) group quantisation shared by the append and the exchange-pack kernels.
+//
+// A group of 128 channels is held by 8 lanes, 16 channels each.  Codes are bit-identical to
+// QuantizedCompressor._quantize_tensor (core/single/module/pikv_compression.py:965-1006) on the
+// [1,128] slice, but without a division per element:
+//   t = fma(x, 1/scale, zp + 1.5*2^23)   rounds x/scale + zp to the nearest integer (ties to even)
+//                                        in the add itself; the integer sits in t's low mantissa bits
+//   e = fma(x, 1/scale, zp - r)          residual against that integer r
+// |e| well below 0.5 proves that the reference's own rounding sequence
+// rint(fl(fl(x/scale) + zp)) lands on the same integer (all quantities differ by < 1e-3 while
+// |x/scale| < 4096); any element closer than that to a tie, or a group outside that range, makes
+// the thread redo its 16 elements with the IEEE division sequence.
+#pragma once
+#include "common.cuh"
+
+namespace pikv {
+
+constexpr float QG_MAGIC = 12582912.0f;          // 1.5 * 2^23
+constexpr int QG_MAGIC_BITS = 0x4B400000;
+
+template <typename TIn>
+__device__ __forceinline__ void qg_load16(const TIn* p, float (&x)[16]);
+template <>
+__device__ __forceinline__ void qg_load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[16]) {
+    uint4 a = ld_stream_16(p);
+    uint4 b = ld_stream_16(p + 8);
+    bf16x2_to_f32(a.x, x[0], x[1]);   bf16x2_to_f32(a.y, x[2], x[3]);
+    bf16x2_to_f32(a.z, x[4], x[5]);   bf16x2_to_f32(a.w, x[6], x[7]);
+    bf16x2_to_f32(b.x, x[8], x[9]);   bf16x2_to_f32(b.y, x[10], x[11]);
+    bf16x2_to_f32(b.z, x[12], x[13]); bf16x2_to_f32(b.w, x[14], x[15]);
+}
+template <>
+__device__ __forceinline__ void qg_load16<float>(const float* p, float (&x)[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 a = ld_stream_16(p + 4 * i);
+        x[4 * i + 0] = __uint_as_float(a.x); x[4 * i + 1] = __uint_as_float(a.y);
+        x[4 * i + 2] = __uint_as_float(a.z); x[4 * i + 3] = __uint_as_float(a.w);
+    }
+}
+
+// min / max of the 128-channel group this lane belongs to (8 consecutive lanes)
+__device__ __forceinline__ void qg_group_minmax(const float (&x)[16], float& mn, float& mx) {
+    mn = x[0];
+    mx = x[0];
+#pragma unroll
+    for (int i = 1; i < 16; ++i) {
+        mn = fminf(mn, x[i]);
+        mx = fmaxf(mx, x[i]);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+}
+
+__device__ __forceinline__ uint32_t qg_pack4_s8(int n0, int n1, int n2, int n3) {
+    uint32_t hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(n3), "r"(n2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(n1), "r"(n0), "r"(hi));
+    return out;
+}
+__device__ __forceinline__ uint32_t qg_pack4_u8(int n0, int n1, int n2, int n3) {
+    uint32_t hi, out;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(n3), "r"(n2), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(n1), "r"(n0), "r"(hi));
+    return out;
+}
+
+// Quantise this lane's 16 channels.  Returns the packed codes in w (4 words for 8 bits, 2 for 4).
+template <int BITS, bool SYM>
+__device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, float mx, QParams& qp, uint32_t (&w)[4]) {
+    constexpr int QMIN = SYM ? -(1 << (BITS - 1)) : 0;
+    constexpr int QMAX = SYM ? (1 << (BITS - 1)) - 1 : (1 << BITS) - 1;
+    qp = quant_params(mn, mx, QMIN, QMAX, SYM);
+    const float inv = __frcp_rn(qp.scale);
+    int n[16];
+    bool slow = !(fmaxf(fabsf(mn), fabsf(mx)) * inv < 4096.0f) || !(fabsf(qp.zp) < 4096.0f);
+    const float c0 = qp.zp + QG_MAGIC;               // exact: zp is an integer below 2^12 here
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float t = __fmaf_rn(x[i], inv, c0);
+        const float r = __fsub_rn(t, QG_MAGIC);
+        const float e = __fmaf_rn(x[i], inv, __fsub_rn(qp.zp, r));
+        slow = slow || !(fabsf(e) < 0.499f);
+        n[i] = __float_as_int(t) - QG_MAGIC_BITS;
+    }
+    if (slow) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) n[i] = (int)rintf(__fadd_rn(__fdiv_rn(x[i], qp.scale), qp.zp));
+    }
+    if (BITS == 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            w[i] = SYM ? qg_pack4_s8(n[4 * i], n[4 * i + 1], n[4 * i + 2], n[4 * i + 3])
+                       : qg_pack4_u8(n[4 * i], n[4 * i + 1], n[4 * i + 2], n[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t v = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v |= (uint32_t)(min(max(n[8 * i + j], QMIN), QMAX) & 0xf) << (4 * j);
+            w[i] = v;
+        }
+        w[2] = w[3] = 0;
+    }
+}
+
+}  // namespace pikv

@@ -149,8 +149,8 @@ def test_full_size_append_properties(dev):
     dq = cache.gather(seq, pos, "k").cpu().numpy().reshape(-1, n_kv, 128)
     src = K.float().cpu().numpy()[t_ix[pick]].reshape(-1, n_kv, 128)
     step = np.abs(src).max(-1, keepdims=True) * 2 / 255
-    # half a step from rounding + up to 127 * 2^-9 of a step from storing the scale as bf16
-    assert (np.abs(dq - src) <= step * 0.76 + 1e-7).all()
+    # half a step from rounding + up to 127 * 2^-8 of a step from storing the scale as bf16 (8 significant bits)
+    assert (np.abs(dq - src) <= step * (0.5 + 127 / 256) + 1e-6).all()
     both = np.nonzero(ok.all(axis=1))[0][:512]
     a = cache.gather(g.topk_idx[both, 0].contiguous(), g.slot[both, 0].contiguous(), "v", codes=True)[1]
     b = cache.gather(g.topk_idx[both, 1].contiguous(), g.slot[both, 1].contiguous(), "v", codes=True)[1]
