@@ -12,6 +12,7 @@ namespace pikv {
 constexpr int APPEND_THREADS = 256;
 constexpr int D = PIKV_HEAD_DIM;        // 128 channels per group
 constexpr int PT = PIKV_PAGE_TOKENS;    // 16 tokens per page
+constexpr int APPEND_MAX_K = 8;          // destinations per token
 
 struct AppendDev {
     const void* k;
@@ -30,7 +31,7 @@ struct AppendDev {
 // One 8-lane group per (token, head): both the K and the V slice of that head, so four
 // 16-byte loads are in flight per lane and the destination lookup is shared.
 template <typename TIn, int BITS, bool SYM>
-__global__ void __launch_bounds__(APPEND_THREADS) kv_append_quant_kernel(AppendDev a) {
+__global__ void __launch_bounds__(APPEND_THREADS, 4) kv_append_quant_kernel(AppendDev a) {
     constexpr int ROW_BYTES = D * BITS / 8;
     const int sub = threadIdx.x & 7;                       // lane within the group
     const unsigned pair = (blockIdx.x * (unsigned)APPEND_THREADS + threadIdx.x) >> 3;
@@ -46,6 +47,29 @@ __global__ void __launch_bounds__(APPEND_THREADS) kv_append_quant_kernel(AppendD
     }
     if (!active) t = 0, head = 0;
 
+    // destinations first: slot -> page is a chain of dependent loads that does not need K or V, so it
+    // runs while the K / V loads are in flight
+    int dst[APPEND_MAX_K];   // physical row index (page, head, token-in-page), -1 = nothing to write
+#pragma unroll
+    for (int j = 0; j < APPEND_MAX_K; ++j) {
+        dst[j] = -1;
+        if (j < a.top_k && active) {
+            const int s = a.slot[(size_t)t * a.top_k + j];
+            if (s >= 0) {
+                const int seq = a.dst_seq[(size_t)t * a.top_k + j];
+                if (seq < 0 || seq >= a.num_seqs || (s / PT) >= a.max_pages) {
+                    if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_SEQ);
+                } else {
+                    const int page = a.page_table[(size_t)seq * a.max_pages + s / PT];
+                    if (page < 0 || page >= a.num_pages) {
+                        if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_PAGE);
+                    } else {
+                        dst[j] = (page * a.n_kv + (int)head) * PT + (s % PT);
+                    }
+                }
+            }
+        }
+    }
     float xk[16], xv[16];
     {
         const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
@@ -62,21 +86,11 @@ __global__ void __launch_bounds__(APPEND_THREADS) kv_append_quant_kernel(AppendD
     qg_quantize16<BITS, SYM>(xv, vmn, vmx, vq, vw);
     const uint16_t ks_bits = f32_to_bf16_bits(kq.scale), vs_bits = f32_to_bf16_bits(vq.scale);
 
-    for (int j = 0; j < a.top_k; ++j) {
-        const int s = a.slot[(size_t)t * a.top_k + j];
-        if (s < 0) continue;
-        const int seq = a.dst_seq[(size_t)t * a.top_k + j];
-        if (seq < 0 || seq >= a.num_seqs || (s / PT) >= a.max_pages) {
-            if (a.status && sub == 0) atomicOr(a.status, PIKV_ST_BAD_SEQ);
-            continue;
-        }
-        const int page = a.page_table[(size_t)seq * a.max_pages + s / PT];
-        if (page < 0 || page >= a.num_pages) {
-            if (a.status && sub == 0) atomicOr(a.status, PIKV_ST_BAD_PAGE);
-            continue;
-        }
-        const int row = s % PT;
-        const size_t prow = ((size_t)page * a.n_kv + head) * PT + row;
+#pragma unroll
+    for (int j = 0; j < APPEND_MAX_K; ++j) {
+        if (dst[j] < 0) continue;
+        const int row = dst[j] % PT;
+        const size_t prow = (size_t)dst[j];
         if (BITS == 8) {
             const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
             *reinterpret_cast<uint4*>(a.codes[0] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
@@ -167,6 +181,7 @@ using namespace pikv;
 extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t stream) {
     PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "append: null params");
     PIKV_REQUIRE(p->T >= 0 && p->n_kv > 0 && p->top_k > 0, PIKV_EINVAL, "append: bad sizes");
+    PIKV_REQUIRE(p->top_k <= APPEND_MAX_K, PIKV_ELIMIT, "append: top_k=%d exceeds %d", p->top_k, APPEND_MAX_K);
     if (p->T == 0) return PIKV_OK;
     PIKV_REQUIRE(p->k && p->v && p->dst_seq && p->slot && p->page_table, PIKV_EINVAL, "append: null input pointer");
     PIKV_REQUIRE(p->k_codes && p->v_codes && p->k_scale && p->v_scale, PIKV_EINVAL, "append: null cache pointer");
@@ -177,6 +192,7 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     AppendDev a;
     PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28), PIKV_ELIMIT, "append: T * n_kv must stay below 2^28 per call");
     a.k = p->k; a.v = p->v; a.T = p->T; a.n_kv = p->n_kv; a.top_k = p->top_k;
+    PIKV_REQUIRE((long long)p->num_pages * p->n_kv * PT < (1ll << 31), PIKV_ELIMIT, "append: page pool too large for 32-bit row indices");
     a.log2_nkv = -1;
     for (int b = 0; b < 16; ++b)
         if ((1 << b) == p->n_kv) a.log2_nkv = b;

@@ -198,12 +198,34 @@ __global__ void __launch_bounds__(GATE_THREADS) gate_logits_kernel(GateDev g) {
 }
 
 // ---- finalize: local ranks -> global slots; totals --------------------------------
+// Threads are laid out as (expert e, part): part p sums the per-CTA counters of CTAs p, p+parts, ...
+// so the reads of one prefix are spread over 256/EP2 threads and overlap; parts are combined in a
+// fixed order (the float sums stay run-to-run identical).
 __global__ void __launch_bounds__(GATE_THREADS) gate_finalize_kernel(GateDev g) {
     __shared__ int base_s[GATE_MAX_E];
+    __shared__ int part_i[GATE_THREADS];
+    __shared__ float part_f[GATE_THREADS];
     const int tid = threadIdx.x, cta = blockIdx.x, E = g.E;
+    int ep2 = 8;
+    while (ep2 < E) ep2 <<= 1;
+    const int parts = GATE_THREADS / ep2;
+    const int e = tid & (ep2 - 1), part = tid / ep2;
+    {
+        int s0 = 0, s1 = 0;
+        if (e < E) {
+            int c = part;
+            for (; c + parts < cta; c += 2 * parts) {
+                s0 += g.cta_cnt[(size_t)c * E + e];
+                s1 += g.cta_cnt[(size_t)(c + parts) * E + e];
+            }
+            if (c < cta) s0 += g.cta_cnt[(size_t)c * E + e];
+        }
+        part_i[tid] = s0 + s1;
+    }
+    __syncthreads();
     if (tid < E) {
         int b = g.slot_base ? g.slot_base[tid] : 0;
-        for (int c = 0; c < cta; ++c) b += g.cta_cnt[(size_t)c * E + tid];
+        for (int p = 0; p < parts; ++p) b += part_i[p * ep2 + tid];
         base_s[tid] = b;
     }
     __syncthreads();
@@ -212,30 +234,40 @@ __global__ void __launch_bounds__(GATE_THREADS) gate_finalize_kernel(GateDev g) 
     if (g.slot) {
         const size_t off = (size_t)chunk_start * g.k;
         for (int p = tid; p < ntok * g.k; p += GATE_THREADS) {
-            int e = g.topk_idx[off + p];
-            int s = base_s[e] + g.slot[off + p];
+            int ee = g.topk_idx[off + p];
+            int s = base_s[ee] + g.slot[off + p];
             g.slot[off + p] = (g.capacity <= 0 || s < g.capacity) ? s : -1;
         }
     }
-    if (cta == 0) {
-        for (int i = tid; i < g.k * E; i += GATE_THREADS) {
-            int j = i / E, e = i % E;
-            int s = 0;
-            for (int c = 0; c < g.G; ++c) s += g.cta_cnt_k[((size_t)c * g.k + j) * E + e];
-            if (g.counts_k) g.counts_k[i] = s;
-        }
+    if (cta != 0) return;
+    // totals over all CTAs: per-column counts, probability sums, new lengths
+    int tot = 0;
+    for (int j = 0; j < g.k; ++j) {
+        int s = 0;
+        if (e < E)
+            for (int c = part; c < g.G; c += parts) s += g.cta_cnt_k[((size_t)c * g.k + j) * E + e];
+        __syncthreads();
+        part_i[tid] = s;
+        __syncthreads();
         if (tid < E) {
-            float ps = 0.f;
-            int tot = 0;
-            for (int c = 0; c < g.G; ++c) {
-                ps += g.cta_psum[(size_t)c * E + tid];
-                tot += g.cta_cnt[(size_t)c * E + tid];
-            }
-            if (g.prob_sum) g.prob_sum[tid] = ps;
-            if (g.new_len) {
-                int n = (g.slot_base ? g.slot_base[tid] : 0) + tot;
-                g.new_len[tid] = (g.capacity > 0 && n > g.capacity) ? g.capacity : n;
-            }
+            int cnt = 0;
+            for (int p = 0; p < parts; ++p) cnt += part_i[p * ep2 + tid];
+            if (g.counts_k) g.counts_k[j * E + tid] = cnt;
+            tot += cnt;
+        }
+    }
+    float ps = 0.f;
+    if (e < E)
+        for (int c = part; c < g.G; c += parts) ps += g.cta_psum[(size_t)c * E + e];
+    part_f[tid] = ps;
+    __syncthreads();
+    if (tid < E) {
+        float sum = 0.f;
+        for (int p = 0; p < parts; ++p) sum += part_f[p * ep2 + tid];
+        if (g.prob_sum) g.prob_sum[tid] = sum;
+        if (g.new_len) {
+            int n = (g.slot_base ? g.slot_base[tid] : 0) + tot;
+            g.new_len[tid] = (g.capacity > 0 && n > g.capacity) ? g.capacity : n;
         }
     }
 }
