@@ -30,7 +30,7 @@ struct AppendDev {
 
 // One 8-lane group per (token, head): both the K and the V slice of that head, so four
 // 16-byte loads are in flight per lane and the destination lookup is shared.
-template <typename TIn, int BITS, bool SYM>
+template <typename TIn, int BITS, bool SYM, int TOPK>
 __global__ void __launch_bounds__(APPEND_THREADS, 4) kv_append_quant_kernel(AppendDev a) {
     constexpr int ROW_BYTES = D * BITS / 8;
     const int sub = threadIdx.x & 7;                       // lane within the group
@@ -49,9 +49,9 @@ __global__ void __launch_bounds__(APPEND_THREADS, 4) kv_append_quant_kernel(Appe
 
     // destinations first: slot -> page is a chain of dependent loads that does not need K or V, so it
     // runs while the K / V loads are in flight
-    int dst[APPEND_MAX_K];   // physical row index (page, head, token-in-page), -1 = nothing to write
+    int dst[TOPK];   // physical row index (page, head, token-in-page), -1 = nothing to write
 #pragma unroll
-    for (int j = 0; j < APPEND_MAX_K; ++j) {
+    for (int j = 0; j < TOPK; ++j) {
         dst[j] = -1;
         if (j < a.top_k && active) {
             const int s = a.slot[(size_t)t * a.top_k + j];
@@ -84,10 +84,10 @@ __global__ void __launch_bounds__(APPEND_THREADS, 4) kv_append_quant_kernel(Appe
     uint32_t kw[4], vw[4];
     qg_quantize16<BITS, SYM>(xk, kmn, kmx, kq, kw);
     qg_quantize16<BITS, SYM>(xv, vmn, vmx, vq, vw);
-    const uint16_t ks_bits = f32_to_bf16_bits(kq.scale), vs_bits = f32_to_bf16_bits(vq.scale);
+    const uint16_t ks_bits = qg_bf16_bits(kq.scale), vs_bits = qg_bf16_bits(vq.scale);
 
 #pragma unroll
-    for (int j = 0; j < APPEND_MAX_K; ++j) {
+    for (int j = 0; j < TOPK; ++j) {
         if (dst[j] < 0) continue;
         const int row = dst[j] % PT;
         const size_t prow = (size_t)dst[j];
@@ -166,10 +166,18 @@ template <typename TIn>
 static int launch_append(const AppendDev& a, int bits, int symmetric, cudaStream_t st) {
     const long long lanes = (long long)a.T * a.n_kv * 8;
     const int grid = (int)ceil_div64(lanes, APPEND_THREADS);
-    if (bits == 8 && symmetric) kv_append_quant_kernel<TIn, 8, true><<<grid, APPEND_THREADS, 0, st>>>(a);
-    else if (bits == 8) kv_append_quant_kernel<TIn, 8, false><<<grid, APPEND_THREADS, 0, st>>>(a);
-    else if (symmetric) kv_append_quant_kernel<TIn, 4, true><<<grid, APPEND_THREADS, 0, st>>>(a);
-    else kv_append_quant_kernel<TIn, 4, false><<<grid, APPEND_THREADS, 0, st>>>(a);
+#define PIKV_APPEND_LAUNCH(BITS, SYM)                                                                   \
+    do {                                                                                                \
+        if (a.top_k <= 1) kv_append_quant_kernel<TIn, BITS, SYM, 1><<<grid, APPEND_THREADS, 0, st>>>(a);      \
+        else if (a.top_k <= 2) kv_append_quant_kernel<TIn, BITS, SYM, 2><<<grid, APPEND_THREADS, 0, st>>>(a); \
+        else if (a.top_k <= 4) kv_append_quant_kernel<TIn, BITS, SYM, 4><<<grid, APPEND_THREADS, 0, st>>>(a); \
+        else kv_append_quant_kernel<TIn, BITS, SYM, 8><<<grid, APPEND_THREADS, 0, st>>>(a);                   \
+    } while (0)
+    if (bits == 8 && symmetric) PIKV_APPEND_LAUNCH(8, true);
+    else if (bits == 8) PIKV_APPEND_LAUNCH(8, false);
+    else if (symmetric) PIKV_APPEND_LAUNCH(4, true);
+    else PIKV_APPEND_LAUNCH(4, false);
+#undef PIKV_APPEND_LAUNCH
     count_launch(1);
     return check_launch("kv_append_quant_kernel");
 }

@@ -22,8 +22,9 @@ template <typename TIn>
 __device__ __forceinline__ void qg_load16(const TIn* p, float (&x)[16]);
 template <>
 __device__ __forceinline__ void qg_load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[16]) {
-    uint4 a = ld_stream_16(p);
-    uint4 b = ld_stream_16(p + 8);
+    // the lane's two 16-byte halves share one 32-byte sector: let the first load allocate it in L1
+    uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+    uint4 b = __ldg(reinterpret_cast<const uint4*>(p + 8));
     bf16x2_to_f32(a.x, x[0], x[1]);   bf16x2_to_f32(a.y, x[2], x[3]);
     bf16x2_to_f32(a.z, x[4], x[5]);   bf16x2_to_f32(a.w, x[6], x[7]);
     bf16x2_to_f32(b.x, x[8], x[9]);   bf16x2_to_f32(b.y, x[10], x[11]);
@@ -68,9 +69,55 @@ __device__ __forceinline__ uint32_t qg_pack4_u8(int n0, int n1, int n2, int n3) 
     return out;
 }
 
+// fp32 -> bf16 bits, round to nearest even, integer pipe only (finite inputs)
+__device__ __forceinline__ uint16_t qg_bf16_bits(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+
+// Symmetric 8-bit codes of this lane's 16 channels, the hot case.  x / scale is bracketed by
+// x * inv_lo and x * inv_hi (inv = 1/scale moved 2^-20 either way, far more than the 2^-24 of the
+// reciprocal and of the reference's division); adding 1.5 * 2^23 inside the fma rounds each to the
+// nearest integer, ties to even, exactly like rint.  When both ends give the same integer, so
+// does the reference; the xor of the two bit patterns accumulates the exceptions, and a thread
+// with any redoes its 16 channels with the IEEE division.  The integer is the low byte of the
+// float's bit pattern, so four codes are packed with three byte permutes; only +128 (x = +absmax,
+// 127.5 rounding to even) needs the clamp.
+__device__ __forceinline__ void qg_quantize16_s8(const float (&x)[16], float mn, float mx, QParams& qp, uint32_t (&w)[4]) {
+    qp = quant_params(mn, mx, -128, 127, true);
+    const float inv = __frcp_rn(qp.scale);
+    const float inv_lo = inv * 0.99999905f, inv_hi = inv * 1.00000095f;
+    uint32_t t[16];
+    uint32_t diff = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float tl = __fmaf_rn(x[i], inv_lo, QG_MAGIC);
+        const float th = __fmaf_rn(x[i], inv_hi, QG_MAGIC);
+        diff |= __float_as_uint(tl) ^ __float_as_uint(th);
+        t[i] = __float_as_uint(fminf(tl, QG_MAGIC + 127.0f));
+    }
+    if (diff != 0u || !(inv < 3.0e38f)) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float q = fminf(fmaxf(rintf(__fdiv_rn(x[i], qp.scale)), -128.f), 127.f);
+            t[i] = (uint32_t)(int)q;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = __byte_perm(t[4 * i], t[4 * i + 1], 0x0040);
+        const uint32_t hi = __byte_perm(t[4 * i + 2], t[4 * i + 3], 0x0040);
+        w[i] = __byte_perm(lo, hi, 0x5410);
+    }
+}
+
 // Quantise this lane's 16 channels.  Returns the packed codes in w (4 words for 8 bits, 2 for 4).
 template <int BITS, bool SYM>
 __device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, float mx, QParams& qp, uint32_t (&w)[4]) {
+    if (BITS == 8 && SYM) {
+        qg_quantize16_s8(x, mn, mx, qp, w);
+        return;
+    }
     constexpr int QMIN = SYM ? -(1 << (BITS - 1)) : 0;
     constexpr int QMAX = SYM ? (1 << (BITS - 1)) - 1 : (1 << BITS) - 1;
     qp = quant_params(mn, mx, QMIN, QMAX, SYM);
