@@ -29,14 +29,10 @@ __global__ void __launch_bounds__(256) a2a_pack_kernel(const TIn* k, const TIn* 
     const int t = active ? (int)(group / per_tok) : 0;
     const int rr = active ? (int)(group % per_tok) : 0;
     const int which = rr / n_kv, head = rr % n_kv;
-    float x[16];
-    qg_load16<TIn>((which ? v : k) + ((size_t)t * n_kv + head) * 128 + sub * 16, x);
-    float mn, mx;
-    qg_group_minmax(x, mn, mx);
-    if (!active) return;
     QParams qp;
     uint32_t w[4];
-    qg_quantize16<8, true>(x, mn, mx, qp, w);
+    GroupQuant<TIn, 8, true>::run((which ? v : k) + ((size_t)t * n_kv + head) * 128 + sub * 16, qp, w);
+    if (!active) return;
     const size_t rec = a2a_record_bytes(n_kv);
     for (int j = 0; j < top_k; ++j) {
         const int sp = send_pos[(size_t)t * top_k + j];

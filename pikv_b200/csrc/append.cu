@@ -70,20 +70,14 @@ __global__ void __launch_bounds__(APPEND_THREADS, 4) kv_append_quant_kernel(Appe
             }
         }
     }
-    float xk[16], xv[16];
-    {
-        const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
-        qg_load16<TIn>(static_cast<const TIn*>(a.k) + off, xk);
-        qg_load16<TIn>(static_cast<const TIn*>(a.v) + off, xv);
-    }
-    float kmn, kmx, vmn, vmx;
-    qg_group_minmax(xk, kmn, kmx);
-    qg_group_minmax(xv, vmn, vmx);
-    if (!active) return;
     QParams kq, vq;
     uint32_t kw[4], vw[4];
-    qg_quantize16<BITS, SYM>(xk, kmn, kmx, kq, kw);
-    qg_quantize16<BITS, SYM>(xv, vmn, vmx, vq, vw);
+    {
+        const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
+        GroupQuant<TIn, BITS, SYM>::run(static_cast<const TIn*>(a.k) + off, kq, kw);
+        GroupQuant<TIn, BITS, SYM>::run(static_cast<const TIn*>(a.v) + off, vq, vw);
+    }
+    if (!active) return;
     const uint16_t ks_bits = qg_bf16_bits(kq.scale), vs_bits = qg_bf16_bits(vq.scale);
 
 #pragma unroll

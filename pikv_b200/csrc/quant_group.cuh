@@ -154,4 +154,82 @@ __device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, fl
     }
 }
 
+// ---- bf16 in, symmetric 8-bit out: statistics on the packed words --------------------------
+// fp32 min/max issue at a fraction of the integer rate on sm_100, so the group statistics are
+// taken on the raw bf16 pairs with integer ops: |x| is a mask, max|x| a packed unsigned 16-bit
+// max (bf16 magnitudes order like their bit patterns), and "all 128 channels equal" (the
+// reference's x_max == x_min case, which moves x_max up by 1e-5) an xor/or chain.
+__device__ __forceinline__ void qg_quantize16_s8_bf16(const uint4& a, const uint4& b, QParams& qp, uint32_t (&w)[4]) {
+    const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t m = ww[0] & 0x7fff7fffu;
+    uint32_t d = ww[0] ^ __byte_perm(ww[0], 0, 0x1032);          // low half vs high half of word 0
+#pragma unroll
+    for (int i = 1; i < 8; ++i) {
+        m = __vmaxu2(m, ww[i] & 0x7fff7fffu);
+        d |= ww[0] ^ ww[i];
+    }
+    uint32_t amax = max(m & 0xffffu, m >> 16);                   // bf16 bits of this lane's max |x|
+    const uint32_t first = __shfl_sync(0xffffffffu, ww[0], threadIdx.x & 24);   // word 0 of the group's lane 0
+    d |= ww[0] ^ first;
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        d |= __shfl_xor_sync(0xffffffffu, d, o);
+    }
+    float abs_max = __uint_as_float(amax << 16);
+    if (d == 0u || amax == 0u) {
+        // every channel holds the same value c (or +-0): x_min = c, x_max = c + 1e-5
+        const float c = (amax == 0u) ? 0.0f : __uint_as_float(first << 16);
+        abs_max = fmaxf(fabsf(c), fabsf(__fadd_rn(c, 1e-5f)));
+    }
+    qp.scale = __fdiv_rn(__fmul_rn(2.0f, abs_max), 255.0f);
+    qp.zp = 0.0f;
+    const float inv = __frcp_rn(qp.scale);
+    const float inv_lo = inv * 0.99999905f, inv_hi = inv * 1.00000095f;
+    uint32_t t[16];
+    uint32_t diff = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float x = __uint_as_float((i & 1) ? (ww[i >> 1] & 0xffff0000u) : (ww[i >> 1] << 16));
+        const float tl = __fmaf_rn(x, inv_lo, QG_MAGIC);
+        const float th = __fmaf_rn(x, inv_hi, QG_MAGIC);
+        diff |= __float_as_uint(tl) ^ __float_as_uint(th);
+        t[i] = (uint32_t)min(__float_as_int(tl), QG_MAGIC_BITS + 127);   // positive floats order like ints
+    }
+    if (diff != 0u || !(inv < 3.0e38f)) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float x = __uint_as_float((i & 1) ? (ww[i >> 1] & 0xffff0000u) : (ww[i >> 1] << 16));
+            const float q = fminf(fmaxf(rintf(__fdiv_rn(x, qp.scale)), -128.f), 127.f);
+            t[i] = (uint32_t)(int)q;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = __byte_perm(t[4 * i], t[4 * i + 1], 0x0040);
+        const uint32_t hi = __byte_perm(t[4 * i + 2], t[4 * i + 3], 0x0040);
+        w[i] = __byte_perm(lo, hi, 0x5410);
+    }
+}
+
+// Load + statistics + codes of one group slice (16 channels of this lane), any combination.
+// All 32 lanes must call it (the statistics shuffle across the 8 lanes of a group).
+template <typename TIn, int BITS, bool SYM>
+struct GroupQuant {
+    static __device__ __forceinline__ void run(const TIn* src, QParams& qp, uint32_t (&w)[4]) {
+        float x[16], mn, mx;
+        qg_load16<TIn>(src, x);
+        qg_group_minmax(x, mn, mx);
+        qg_quantize16<BITS, SYM>(x, mn, mx, qp, w);
+    }
+};
+template <>
+struct GroupQuant<__nv_bfloat16, 8, true> {
+    static __device__ __forceinline__ void run(const __nv_bfloat16* src, QParams& qp, uint32_t (&w)[4]) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(src));
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(src + 8));
+        qg_quantize16_s8_bf16(a, b, qp, w);
+    }
+};
+
 }  // namespace pikv
