@@ -154,18 +154,50 @@ __device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, fl
     }
 }
 
-// ---- bf16 in, symmetric 8-bit out: statistics on the packed words --------------------------
-// fp32 min/max issue at a fraction of the integer rate on sm_100, so the group statistics are
-// taken on the raw bf16 pairs with integer ops: |x| is a mask, max|x| a packed unsigned 16-bit
-// max (bf16 magnitudes order like their bit patterns), and "all 128 channels equal" (the
-// reference's x_max == x_min case, which moves x_max up by 1e-5) an xor/or chain.
+// ---- bf16 in, symmetric 8-bit out: everything up to the fma on the packed words -------------
+// The group statistics are taken on the raw bf16 pairs with integer ops: |x| is a mask, max|x| a
+// packed unsigned 16-bit max (bf16 magnitudes order like their bit patterns), and "all 128
+// channels equal" (the reference's x_max == x_min case, which moves x_max up by 1e-5) an xor/or
+// chain.
+//
+// The elements that carry the group's max |x| sit exactly on the 127.5 rounding boundary
+// (absmax / (2 absmax / 255)), so the bracket test would flag one lane of every group.  They are
+// taken out analytically instead: their magnitude is first clamped to the next smaller bf16
+// value (|v| ~ 127.0 or 127.25: rounds to +-127 with a wide margin; every other element is
+// already at or below that value and is untouched), which is the right code for +absmax
+// (127.5 or 128 both clamp to 127) and for -absmax when M = rint(fl(absmax / scale)) is 127.  When
+// M is 128 the negative ones must read -128: the elements the clamp changed are known from
+// m ^ m' (x ^ (x-1) always has bit 0 set), and clearing bit 0 of their code byte turns 0x81 into
+// 0x80.
+// the reference's own sequence, one IEEE division per element; kept out of line because it is rare
+static __device__ __noinline__ uint4 qg_exact_s8_bf16(uint4 a, uint4 b, float scale) {
+    const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int e = 4 * i + c;
+            const float x = __uint_as_float((e & 1) ? (ww[e >> 1] & 0xffff0000u) : (ww[e >> 1] << 16));
+            const int q = (int)fminf(fmaxf(rintf(__fdiv_rn(x, scale)), -128.f), 127.f);
+            acc |= ((uint32_t)q & 0xffu) << (8 * c);
+        }
+        out[i] = acc;
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
 __device__ __forceinline__ void qg_quantize16_s8_bf16(const uint4& a, const uint4& b, QParams& qp, uint32_t (&w)[4]) {
     const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    uint32_t m = ww[0] & 0x7fff7fffu;
+    uint32_t mag[8];
+    mag[0] = ww[0] & 0x7fff7fffu;
+    uint32_t m = mag[0];
     uint32_t d = ww[0] ^ __byte_perm(ww[0], 0, 0x1032);          // low half vs high half of word 0
 #pragma unroll
     for (int i = 1; i < 8; ++i) {
-        m = __vmaxu2(m, ww[i] & 0x7fff7fffu);
+        mag[i] = ww[i] & 0x7fff7fffu;
+        m = __vmaxu2(m, mag[i]);
         d |= ww[0] ^ ww[i];
     }
     uint32_t amax = max(m & 0xffffu, m >> 16);                   // bf16 bits of this lane's max |x|
@@ -176,8 +208,9 @@ __device__ __forceinline__ void qg_quantize16_s8_bf16(const uint4& a, const uint
         amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         d |= __shfl_xor_sync(0xffffffffu, d, o);
     }
+    const bool all_equal = (d == 0u) || (amax == 0u);
     float abs_max = __uint_as_float(amax << 16);
-    if (d == 0u || amax == 0u) {
+    if (all_equal) {
         // every channel holds the same value c (or +-0): x_min = c, x_max = c + 1e-5
         const float c = (amax == 0u) ? 0.0f : __uint_as_float(first << 16);
         abs_max = fmaxf(fabsf(c), fabsf(__fadd_rn(c, 1e-5f)));
@@ -186,29 +219,35 @@ __device__ __forceinline__ void qg_quantize16_s8_bf16(const uint4& a, const uint
     qp.zp = 0.0f;
     const float inv = __frcp_rn(qp.scale);
     const float inv_lo = inv * 0.99999905f, inv_hi = inv * 1.00000095f;
+    const bool m128 = rintf(__fdiv_rn(abs_max, qp.scale)) > 127.5f;   // code of -absmax is -128, not -127
+    const uint32_t pred = (amax - 1u) * 0x00010001u;              // next smaller magnitude, both halves
     uint32_t t[16];
+    uint32_t fix[8];                                              // bit 0 / bit 16: a negative max element
     uint32_t diff = 0;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float x = __uint_as_float((i & 1) ? (ww[i >> 1] & 0xffff0000u) : (ww[i >> 1] << 16));
-        const float tl = __fmaf_rn(x, inv_lo, QG_MAGIC);
-        const float th = __fmaf_rn(x, inv_hi, QG_MAGIC);
-        diff |= __float_as_uint(tl) ^ __float_as_uint(th);
-        t[i] = (uint32_t)min(__float_as_int(tl), QG_MAGIC_BITS + 127);   // positive floats order like ints
-    }
-    if (diff != 0u || !(inv < 3.0e38f)) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float x = __uint_as_float((i & 1) ? (ww[i >> 1] & 0xffff0000u) : (ww[i >> 1] << 16));
-            const float q = fminf(fmaxf(rintf(__fdiv_rn(x, qp.scale)), -128.f), 127.f);
-            t[i] = (uint32_t)(int)q;
-        }
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t mc = __vminu2(mag[i], pred);
+        const uint32_t wc = mc | (ww[i] & 0x80008000u);
+        fix[i] = (mag[i] ^ mc) & (ww[i] >> 15) & 0x00010001u;
+        const float x0 = __uint_as_float(wc << 16), x1 = __uint_as_float(wc & 0xffff0000u);
+        const float l0 = __fmaf_rn(x0, inv_lo, QG_MAGIC), h0 = __fmaf_rn(x0, inv_hi, QG_MAGIC);
+        const float l1 = __fmaf_rn(x1, inv_lo, QG_MAGIC), h1 = __fmaf_rn(x1, inv_hi, QG_MAGIC);
+        diff |= (__float_as_uint(l0) ^ __float_as_uint(h0)) | (__float_as_uint(l1) ^ __float_as_uint(h1));
+        t[2 * i] = __float_as_uint(l0);
+        t[2 * i + 1] = __float_as_uint(l1);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t lo = __byte_perm(t[4 * i], t[4 * i + 1], 0x0040);
         const uint32_t hi = __byte_perm(t[4 * i + 2], t[4 * i + 3], 0x0040);
-        w[i] = __byte_perm(lo, hi, 0x5410);
+        uint32_t packed = __byte_perm(lo, hi, 0x5410);
+        if (m128) packed &= ~__byte_perm(fix[2 * i], fix[2 * i + 1], 0x6420);
+        w[i] = packed;
+    }
+    if (diff != 0u || all_equal || !(inv < 3.0e38f)) {
+        // rare: some element is within 2^-20 of a rounding tie, or the group is constant
+        const uint4 r = qg_exact_s8_bf16(a, b, qp.scale);
+        w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
     }
 }
 
