@@ -154,21 +154,49 @@ __device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, fl
     }
 }
 
-// ---- bf16 in, symmetric 8-bit out: everything up to the fma on the packed words -------------
-// The group statistics are taken on the raw bf16 pairs with integer ops: |x| is a mask, max|x| a
-// packed unsigned 16-bit max (bf16 magnitudes order like their bit patterns), and "all 128
+// ---- bf16 in, symmetric 8-bit out ------------------------------------------------------------
+// Statistics on the raw bf16 pairs: |x| is a mask, max|x| a packed bf16x2 max, and "all 128
 // channels equal" (the reference's x_max == x_min case, which moves x_max up by 1e-5) an xor/or
 // chain.
 //
-// The elements that carry the group's max |x| sit exactly on the 127.5 rounding boundary
-// (absmax / (2 absmax / 255)), so the bracket test would flag one lane of every group.  They are
-// taken out analytically instead: their magnitude is first clamped to the next smaller bf16
-// value (|v| ~ 127.0 or 127.25: rounds to +-127 with a wide margin; every other element is
-// already at or below that value and is untouched), which is the right code for +absmax
-// (127.5 or 128 both clamp to 127) and for -absmax when M = rint(fl(absmax / scale)) is 127.  When
-// M is 128 the negative ones must read -128: the elements the clamp changed are known from
-// m ^ m' (x ^ (x-1) always has bit 0 set), and clearing bit 0 of their code byte turns 0x81 into
-// 0x80.
+// Codes: bf16 inputs make x / scale land exactly on a .5 tie in about one element in 400 (ratios of
+// small integers), and the group's max sits on 127.5 by construction, so the code depends on how
+// the reference's fp32 division rounds: the quotient has to be the correctly rounded one.  It is
+// formed without a per-element reciprocal: y = RN(1/scale) once per lane, then
+//   q = x*y ; r = fma(-scale, q, x) ; q = fma(r, y, q) ; r = fma(-scale, q, x) ; q = fma(r, y, q)
+// (two exact-remainder refinements: the second one is correctly rounded, Markstein), and
+// q + 1.5*2^23 rounds to the nearest integer, ties to even, exactly like rint.  All six steps are
+// packed two elements per instruction (fma/mul/add.f32x2).
+typedef unsigned long long qg_f2;   // two fp32 in one 64-bit register pair
+__device__ __forceinline__ qg_f2 qg_pk(float lo, float hi) {
+    qg_f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ qg_f2 qg_pku(uint32_t lo, uint32_t hi) {
+    qg_f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void qg_unpku(qg_f2 v, uint32_t& lo, uint32_t& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ qg_f2 qg_fma2(qg_f2 a, qg_f2 b, qg_f2 c) {
+    qg_f2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ qg_f2 qg_mul2(qg_f2 a, qg_f2 b) {
+    qg_f2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ qg_f2 qg_add2(qg_f2 a, qg_f2 b) {
+    qg_f2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // the reference's own sequence, one IEEE division per element; kept out of line because it is rare
 static __device__ __noinline__ uint4 qg_exact_s8_bf16(uint4 a, uint4 b, float scale) {
     const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -190,14 +218,12 @@ static __device__ __noinline__ uint4 qg_exact_s8_bf16(uint4 a, uint4 b, float sc
 
 __device__ __forceinline__ void qg_quantize16_s8_bf16(const uint4& a, const uint4& b, QParams& qp, uint32_t (&w)[4]) {
     const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    uint32_t mag[8];
-    mag[0] = ww[0] & 0x7fff7fffu;
-    uint32_t m = mag[0];
+    uint32_t m = ww[0] & 0x7fff7fffu;
     uint32_t d = ww[0] ^ __byte_perm(ww[0], 0, 0x1032);          // low half vs high half of word 0
 #pragma unroll
     for (int i = 1; i < 8; ++i) {
-        mag[i] = ww[i] & 0x7fff7fffu;
-        m = __vmaxu2(m, mag[i]);
+        const uint32_t mi = ww[i] & 0x7fff7fffu;
+        asm("max.bf16x2 %0, %0, %1;" : "+r"(m) : "r"(mi));
         d |= ww[0] ^ ww[i];
     }
     uint32_t amax = max(m & 0xffffu, m >> 16);                   // bf16 bits of this lane's max |x|
@@ -217,37 +243,34 @@ __device__ __forceinline__ void qg_quantize16_s8_bf16(const uint4& a, const uint
     }
     qp.scale = __fdiv_rn(__fmul_rn(2.0f, abs_max), 255.0f);
     qp.zp = 0.0f;
-    const float inv = __frcp_rn(qp.scale);
-    const float inv_lo = inv * 0.99999905f, inv_hi = inv * 1.00000095f;
-    const bool m128 = rintf(__fdiv_rn(abs_max, qp.scale)) > 127.5f;   // code of -absmax is -128, not -127
-    const uint32_t pred = (amax - 1u) * 0x00010001u;              // next smaller magnitude, both halves
+    if (!(abs_max > 1.0e-30f && abs_max < 1.0e30f)) {
+        // denormal / overflowing scale: the refinement's remainders are not exact there
+        const uint4 r = qg_exact_s8_bf16(a, b, qp.scale);
+        w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
+        return;
+    }
+    const float y = __frcp_rn(qp.scale);
+    const qg_f2 y2 = qg_pk(y, y), ns2 = qg_pk(-qp.scale, -qp.scale), magic2 = qg_pk(QG_MAGIC, QG_MAGIC);
     uint32_t t[16];
-    uint32_t fix[8];                                              // bit 0 / bit 16: a negative max element
-    uint32_t diff = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const uint32_t mc = __vminu2(mag[i], pred);
-        const uint32_t wc = mc | (ww[i] & 0x80008000u);
-        fix[i] = (mag[i] ^ mc) & (ww[i] >> 15) & 0x00010001u;
-        const float x0 = __uint_as_float(wc << 16), x1 = __uint_as_float(wc & 0xffff0000u);
-        const float l0 = __fmaf_rn(x0, inv_lo, QG_MAGIC), h0 = __fmaf_rn(x0, inv_hi, QG_MAGIC);
-        const float l1 = __fmaf_rn(x1, inv_lo, QG_MAGIC), h1 = __fmaf_rn(x1, inv_hi, QG_MAGIC);
-        diff |= (__float_as_uint(l0) ^ __float_as_uint(h0)) | (__float_as_uint(l1) ^ __float_as_uint(h1));
-        t[2 * i] = __float_as_uint(l0);
-        t[2 * i + 1] = __float_as_uint(l1);
+        const qg_f2 x2 = qg_pku(ww[i] << 16, ww[i] & 0xffff0000u);
+        qg_f2 q = qg_mul2(x2, y2);
+        qg_f2 r = qg_fma2(ns2, q, x2);
+        q = qg_fma2(r, y2, q);
+        r = qg_fma2(ns2, q, x2);
+        q = qg_fma2(r, y2, q);                       // RN(x / scale)
+        q = qg_add2(q, magic2);                      // rint, integer in the low mantissa bits
+        uint32_t lo, hi;
+        qg_unpku(q, lo, hi);
+        t[2 * i] = (uint32_t)min((int)lo, QG_MAGIC_BITS + 127);     // +128 (x = +absmax) clamps to 127
+        t[2 * i + 1] = (uint32_t)min((int)hi, QG_MAGIC_BITS + 127);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const uint32_t lo = __byte_perm(t[4 * i], t[4 * i + 1], 0x0040);
         const uint32_t hi = __byte_perm(t[4 * i + 2], t[4 * i + 3], 0x0040);
-        uint32_t packed = __byte_perm(lo, hi, 0x5410);
-        if (m128) packed &= ~__byte_perm(fix[2 * i], fix[2 * i + 1], 0x6420);
-        w[i] = packed;
-    }
-    if (diff != 0u || all_equal || !(inv < 3.0e38f)) {
-        // rare: some element is within 2^-20 of a rounding tie, or the group is constant
-        const uint4 r = qg_exact_s8_bf16(a, b, qp.scale);
-        w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
+        w[i] = __byte_perm(lo, hi, 0x5410);
     }
 }
 
