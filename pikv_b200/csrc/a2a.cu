@@ -31,7 +31,9 @@ __global__ void __launch_bounds__(256) a2a_pack_kernel(const TIn* k, const TIn* 
     const int which = rr / n_kv, head = rr % n_kv;
     QParams qp;
     uint32_t w[4];
-    GroupQuant<TIn, 8, true>::run((which ? v : k) + ((size_t)t * n_kv + head) * 128 + sub * 16, qp, w);
+    typename GroupQuant<TIn, 8, true>::Raw raw;
+    GroupQuant<TIn, 8, true>::load((which ? v : k) + ((size_t)t * n_kv + head) * 128 + sub * 16, raw);
+    GroupQuant<TIn, 8, true>::quant(raw, qp, w);
     if (!active) return;
     const size_t rec = a2a_record_bytes(n_kv);
     for (int j = 0; j < top_k; ++j) {

@@ -28,31 +28,34 @@ struct AppendDev {
     unsigned* status;
 };
 
-// One 8-lane group per (token, head): both the K and the V slice of that head, so four
-// 16-byte loads are in flight per lane and the destination lookup is shared.
+// One 8-lane group per (token, head) item: both the K and the V slice of that head.  The grid is
+// persistent (a few CTAs per SM) and every group walks its items with a stride of the whole grid;
+// the loads of the next item (four 16-byte K/V loads and the slot -> page lookups, a chain of
+// dependent loads) are issued before the current item is quantised and stored, so eight 16-byte
+// loads per lane are in flight most of the time.
 template <typename TIn, int BITS, bool SYM, int TOPK>
-__global__ void __launch_bounds__(APPEND_THREADS, 4) kv_append_quant_kernel(AppendDev a) {
-    constexpr int ROW_BYTES = D * BITS / 8;
-    const int sub = threadIdx.x & 7;                       // lane within the group
-    const unsigned pair = (blockIdx.x * (unsigned)APPEND_THREADS + threadIdx.x) >> 3;
-    const unsigned total = (unsigned)a.T * (unsigned)a.n_kv;
-    const bool active = pair < total;
-    unsigned t, head;
-    if (a.log2_nkv >= 0) {
-        t = pair >> a.log2_nkv;
-        head = pair & ((1u << a.log2_nkv) - 1u);
-    } else {
-        t = pair / (unsigned)a.n_kv;
-        head = pair % (unsigned)a.n_kv;
-    }
-    if (!active) t = 0, head = 0;
-
-    // destinations first: slot -> page is a chain of dependent loads that does not need K or V, so it
-    // runs while the K / V loads are in flight
+struct AppendItem {
+    typename GroupQuant<TIn, BITS, SYM>::Raw k, v;
     int dst[TOPK];   // physical row index (page, head, token-in-page), -1 = nothing to write
+};
+
+template <typename TIn, int BITS, bool SYM, int TOPK>
+__device__ __forceinline__ void append_fetch(const AppendDev& a, unsigned pair, unsigned total, int sub,
+                                             AppendItem<TIn, BITS, SYM, TOPK>& it) {
+    const bool active = pair < total;
+    unsigned t = 0, head = 0;
+    if (active) {
+        if (a.log2_nkv >= 0) {
+            t = pair >> a.log2_nkv;
+            head = pair & ((1u << a.log2_nkv) - 1u);
+        } else {
+            t = pair / (unsigned)a.n_kv;
+            head = pair % (unsigned)a.n_kv;
+        }
+    }
 #pragma unroll
     for (int j = 0; j < TOPK; ++j) {
-        dst[j] = -1;
+        it.dst[j] = -1;
         if (j < a.top_k && active) {
             const int s = a.slot[(size_t)t * a.top_k + j];
             if (s >= 0) {
@@ -64,44 +67,64 @@ __global__ void __launch_bounds__(APPEND_THREADS, 4) kv_append_quant_kernel(Appe
                     if (page < 0 || page >= a.num_pages) {
                         if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_PAGE);
                     } else {
-                        dst[j] = (page * a.n_kv + (int)head) * PT + (s % PT);
+                        it.dst[j] = (page * a.n_kv + (int)head) * PT + (s % PT);
                     }
                 }
             }
         }
     }
-    QParams kq, vq;
-    uint32_t kw[4], vw[4];
-    {
-        const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
-        GroupQuant<TIn, BITS, SYM>::run(static_cast<const TIn*>(a.k) + off, kq, kw);
-        GroupQuant<TIn, BITS, SYM>::run(static_cast<const TIn*>(a.v) + off, vq, vw);
-    }
-    if (!active) return;
-    const uint16_t ks_bits = qg_bf16_bits(kq.scale), vs_bits = qg_bf16_bits(vq.scale);
+    const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
+    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.k) + off, it.k);
+    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.v) + off, it.v);
+}
 
+template <typename TIn, int BITS, bool SYM, int TOPK>
+__global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(AppendDev a) {
+    constexpr int ROW_BYTES = D * BITS / 8;
+    const int sub = threadIdx.x & 7;                       // lane within the group
+    const unsigned stride = gridDim.x * (unsigned)(APPEND_THREADS / 8);
+    const unsigned total = (unsigned)a.T * (unsigned)a.n_kv;
+    unsigned pair = (blockIdx.x * (unsigned)APPEND_THREADS + threadIdx.x) >> 3;
+    // the four groups of a warp hold consecutive items: the loop condition is warp-uniform
+    unsigned warp_first = (blockIdx.x * (unsigned)APPEND_THREADS + (threadIdx.x & ~31u)) >> 3;
+
+    AppendItem<TIn, BITS, SYM, TOPK> cur, nxt;
+    if (warp_first < total) append_fetch<TIn, BITS, SYM, TOPK>(a, pair, total, sub, cur);
+    while (warp_first < total) {
+        const bool more = warp_first + stride < total;
+        if (more) append_fetch<TIn, BITS, SYM, TOPK>(a, pair + stride, total, sub, nxt);
+
+        QParams kq, vq;
+        uint32_t kw[4], vw[4];
+        GroupQuant<TIn, BITS, SYM>::quant(cur.k, kq, kw);
+        GroupQuant<TIn, BITS, SYM>::quant(cur.v, vq, vw);
+        const uint16_t ks_bits = qg_bf16_bits(kq.scale), vs_bits = qg_bf16_bits(vq.scale);
 #pragma unroll
-    for (int j = 0; j < TOPK; ++j) {
-        if (dst[j] < 0) continue;
-        const int row = dst[j] % PT;
-        const size_t prow = (size_t)dst[j];
-        if (BITS == 8) {
-            const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
-            *reinterpret_cast<uint4*>(a.codes[0] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
-            *reinterpret_cast<uint4*>(a.codes[1] + o) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
-        } else {
-            const size_t o = prow * ROW_BYTES + 8 * swz4_unit(row, sub);
-            *reinterpret_cast<uint2*>(a.codes[0] + o) = make_uint2(kw[0], kw[1]);
-            *reinterpret_cast<uint2*>(a.codes[1] + o) = make_uint2(vw[0], vw[1]);
-        }
-        if (sub == 0) {
-            a.scale[0][prow] = ks_bits;
-            a.scale[1][prow] = vs_bits;
-            if (!SYM) {
-                a.zp[0][prow] = kq.zp;
-                a.zp[1][prow] = vq.zp;
+        for (int j = 0; j < TOPK; ++j) {
+            if (cur.dst[j] < 0) continue;
+            const int row = cur.dst[j] % PT;
+            const size_t prow = (size_t)cur.dst[j];
+            if (BITS == 8) {
+                const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
+                *reinterpret_cast<uint4*>(a.codes[0] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+                *reinterpret_cast<uint4*>(a.codes[1] + o) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
+            } else {
+                const size_t o = prow * ROW_BYTES + 8 * swz4_unit(row, sub);
+                *reinterpret_cast<uint2*>(a.codes[0] + o) = make_uint2(kw[0], kw[1]);
+                *reinterpret_cast<uint2*>(a.codes[1] + o) = make_uint2(vw[0], vw[1]);
+            }
+            if (sub == 0) {
+                a.scale[0][prow] = ks_bits;
+                a.scale[1][prow] = vs_bits;
+                if (!SYM) {
+                    a.zp[0][prow] = kq.zp;
+                    a.zp[1][prow] = vq.zp;
+                }
             }
         }
+        if (more) cur = nxt;
+        pair += stride;
+        warp_first += stride;
     }
 }
 
@@ -159,7 +182,9 @@ __global__ void cache_gather_kernel(const int* seq, const int* pos, int n, const
 template <typename TIn>
 static int launch_append(const AppendDev& a, int bits, int symmetric, cudaStream_t st) {
     const long long lanes = (long long)a.T * a.n_kv * 8;
-    const int grid = (int)ceil_div64(lanes, APPEND_THREADS);
+    // persistent: at most three resident CTAs per SM, each group strides over its items
+    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 3;
+    const int grid = (int)(want < cap_ctas ? want : cap_ctas);
 #define PIKV_APPEND_LAUNCH(BITS, SYM)                                                                   \
     do {                                                                                                \
         if (a.top_k <= 1) kv_append_quant_kernel<TIn, BITS, SYM, 1><<<grid, APPEND_THREADS, 0, st>>>(a);      \

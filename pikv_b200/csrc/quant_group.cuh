@@ -274,23 +274,29 @@ __device__ __forceinline__ void qg_quantize16_s8_bf16(const uint4& a, const uint
     }
 }
 
-// Load + statistics + codes of one group slice (16 channels of this lane), any combination.
-// All 32 lanes must call it (the statistics shuffle across the 8 lanes of a group).
+// Load and quantisation of one group slice (16 channels of this lane), split so that a kernel can
+// issue the loads of its next item before it quantises the current one.  All 32 lanes must call
+// quant() together (the statistics shuffle across the 8 lanes of a group).
 template <typename TIn, int BITS, bool SYM>
 struct GroupQuant {
-    static __device__ __forceinline__ void run(const TIn* src, QParams& qp, uint32_t (&w)[4]) {
-        float x[16], mn, mx;
-        qg_load16<TIn>(src, x);
-        qg_group_minmax(x, mn, mx);
-        qg_quantize16<BITS, SYM>(x, mn, mx, qp, w);
+    struct Raw { float x[16]; };
+    static __device__ __forceinline__ void load(const TIn* src, Raw& r) { qg_load16<TIn>(src, r.x); }
+    static __device__ __forceinline__ void quant(const Raw& r, QParams& qp, uint32_t (&w)[4]) {
+        float mn, mx;
+        qg_group_minmax(r.x, mn, mx);
+        qg_quantize16<BITS, SYM>(r.x, mn, mx, qp, w);
     }
 };
 template <>
 struct GroupQuant<__nv_bfloat16, 8, true> {
-    static __device__ __forceinline__ void run(const __nv_bfloat16* src, QParams& qp, uint32_t (&w)[4]) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(src));
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(src + 8));
-        qg_quantize16_s8_bf16(a, b, qp, w);
+    struct Raw { uint4 a, b; };
+    static __device__ __forceinline__ void load(const __nv_bfloat16* src, Raw& r) {
+        // the lane's two 16-byte halves share one 32-byte sector: the first load allocates it in L1
+        r.a = __ldg(reinterpret_cast<const uint4*>(src));
+        r.b = __ldg(reinterpret_cast<const uint4*>(src + 8));
+    }
+    static __device__ __forceinline__ void quant(const Raw& r, QParams& qp, uint32_t (&w)[4]) {
+        qg_quantize16_s8_bf16(r.a, r.b, qp, w);
     }
 };
 
