@@ -29,100 +29,129 @@ struct AppendDev {
 };
 
 // One 8-lane group per (token, head) item: both the K and the V slice of that head.  The grid is
-// persistent (a few CTAs per SM) and every group walks its items with a stride of the whole grid;
-// the loads of the next item (four 16-byte K/V loads and the slot -> page lookups, a chain of
-// dependent loads) are issued before the current item is quantised and stored, so eight 16-byte
-// loads per lane are in flight most of the time.
-template <typename TIn, int BITS, bool SYM, int TOPK>
-struct AppendItem {
-    typename GroupQuant<TIn, BITS, SYM>::Raw k, v;
-    int dst[TOPK];   // physical row index (page, head, token-in-page), -1 = nothing to write
+// persistent (three CTAs per SM) and every group walks its items with a stride of the whole grid
+// in a three-deep software pipeline, so that no load is consumed in the iteration that issued it:
+//   item i+2   slot / destination-sequence loads
+//   item i+1   page-table loads (addresses from the values fetched one iteration earlier) and the
+//              four 16-byte K/V loads
+//   item i     statistics, codes, stores
+template <int TOPK>
+struct AppendRoute {
+    int s[TOPK];     // slot, -1 = dropped
+    int q[TOPK];     // destination sequence
 };
 
-template <typename TIn, int BITS, bool SYM, int TOPK>
-__device__ __forceinline__ void append_fetch(const AppendDev& a, unsigned pair, unsigned total, int sub,
-                                             AppendItem<TIn, BITS, SYM, TOPK>& it) {
-    const bool active = pair < total;
-    unsigned t = 0, head = 0;
-    if (active) {
-        if (a.log2_nkv >= 0) {
-            t = pair >> a.log2_nkv;
-            head = pair & ((1u << a.log2_nkv) - 1u);
-        } else {
-            t = pair / (unsigned)a.n_kv;
-            head = pair % (unsigned)a.n_kv;
-        }
+__device__ __forceinline__ void append_split(const AppendDev& a, unsigned pair, unsigned& t, unsigned& head) {
+    if (a.log2_nkv >= 0) {
+        t = pair >> a.log2_nkv;
+        head = pair & ((1u << a.log2_nkv) - 1u);
+    } else {
+        t = pair / (unsigned)a.n_kv;
+        head = pair % (unsigned)a.n_kv;
     }
+}
+
+template <int TOPK>
+__device__ __forceinline__ void append_stage_route(const AppendDev& a, unsigned pair, unsigned total, AppendRoute<TOPK>& r) {
+    unsigned t = 0, head = 0;
+    const bool active = pair < total;
+    if (active) append_split(a, pair, t, head);
 #pragma unroll
     for (int j = 0; j < TOPK; ++j) {
-        it.dst[j] = -1;
-        if (j < a.top_k && active) {
-            const int s = a.slot[(size_t)t * a.top_k + j];
-            if (s >= 0) {
-                const int seq = a.dst_seq[(size_t)t * a.top_k + j];
-                if (seq < 0 || seq >= a.num_seqs || (s / PT) >= a.max_pages) {
-                    if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_SEQ);
-                } else {
-                    const int page = a.page_table[(size_t)seq * a.max_pages + s / PT];
-                    if (page < 0 || page >= a.num_pages) {
-                        if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_PAGE);
-                    } else {
-                        it.dst[j] = (page * a.n_kv + (int)head) * PT + (s % PT);
-                    }
-                }
+        const bool on = active && j < a.top_k;
+        r.s[j] = on ? __ldg(a.slot + (size_t)t * a.top_k + j) : -1;
+        r.q[j] = on ? __ldg(a.dst_seq + (size_t)t * a.top_k + j) : 0;
+    }
+}
+
+template <typename TIn, int BITS, bool SYM, int TOPK>
+__device__ __forceinline__ void append_stage_load(const AppendDev& a, unsigned pair, unsigned total, int sub,
+                                                  const AppendRoute<TOPK>& r, int (&page)[TOPK],
+                                                  typename GroupQuant<TIn, BITS, SYM>::Raw& k,
+                                                  typename GroupQuant<TIn, BITS, SYM>::Raw& v) {
+    unsigned t = 0, head = 0;
+    if (pair < total) append_split(a, pair, t, head);
+#pragma unroll
+    for (int j = 0; j < TOPK; ++j) {
+        page[j] = -1;
+        if (r.s[j] >= 0) {
+            if (r.q[j] < 0 || r.q[j] >= a.num_seqs || (r.s[j] / PT) >= a.max_pages) {
+                if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_SEQ);
+            } else {
+                page[j] = __ldg(a.page_table + (size_t)r.q[j] * a.max_pages + r.s[j] / PT);
             }
         }
     }
     const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
-    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.k) + off, it.k);
-    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.v) + off, it.v);
+    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.k) + off, k);
+    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.v) + off, v);
 }
 
 template <typename TIn, int BITS, bool SYM, int TOPK>
 __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(AppendDev a) {
     constexpr int ROW_BYTES = D * BITS / 8;
+    using GQ = GroupQuant<TIn, BITS, SYM>;
     const int sub = threadIdx.x & 7;                       // lane within the group
     const unsigned stride = gridDim.x * (unsigned)(APPEND_THREADS / 8);
     const unsigned total = (unsigned)a.T * (unsigned)a.n_kv;
     unsigned pair = (blockIdx.x * (unsigned)APPEND_THREADS + threadIdx.x) >> 3;
     // the four groups of a warp hold consecutive items: the loop condition is warp-uniform
     unsigned warp_first = (blockIdx.x * (unsigned)APPEND_THREADS + (threadIdx.x & ~31u)) >> 3;
+    if (warp_first >= total) return;
 
-    AppendItem<TIn, BITS, SYM, TOPK> cur, nxt;
-    if (warp_first < total) append_fetch<TIn, BITS, SYM, TOPK>(a, pair, total, sub, cur);
+    AppendRoute<TOPK> r0, r1, r2;
+    int pg0[TOPK], pg1[TOPK];
+    typename GQ::Raw k0, v0, k1, v1;
+    // prologue: item 0 fully fetched, item 1 routed
+    append_stage_route<TOPK>(a, pair, total, r0);
+    append_stage_route<TOPK>(a, pair + stride, total, r1);
+    append_stage_load<TIn, BITS, SYM, TOPK>(a, pair, total, sub, r0, pg0, k0, v0);
+
     while (warp_first < total) {
-        const bool more = warp_first + stride < total;
-        if (more) append_fetch<TIn, BITS, SYM, TOPK>(a, pair + stride, total, sub, nxt);
+        append_stage_route<TOPK>(a, pair + 2 * stride, total, r2);
+        if (warp_first + stride < total) append_stage_load<TIn, BITS, SYM, TOPK>(a, pair + stride, total, sub, r1, pg1, k1, v1);
 
         QParams kq, vq;
         uint32_t kw[4], vw[4];
-        GroupQuant<TIn, BITS, SYM>::quant(cur.k, kq, kw);
-        GroupQuant<TIn, BITS, SYM>::quant(cur.v, vq, vw);
+        GQ::quant(k0, kq, kw);
+        GQ::quant(v0, vq, vw);
         const uint16_t ks_bits = qg_bf16_bits(kq.scale), vs_bits = qg_bf16_bits(vq.scale);
+        if (pair < total) {
+            unsigned t, head;
+            append_split(a, pair, t, head);
 #pragma unroll
-        for (int j = 0; j < TOPK; ++j) {
-            if (cur.dst[j] < 0) continue;
-            const int row = cur.dst[j] % PT;
-            const size_t prow = (size_t)cur.dst[j];
-            if (BITS == 8) {
-                const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
-                *reinterpret_cast<uint4*>(a.codes[0] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
-                *reinterpret_cast<uint4*>(a.codes[1] + o) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
-            } else {
-                const size_t o = prow * ROW_BYTES + 8 * swz4_unit(row, sub);
-                *reinterpret_cast<uint2*>(a.codes[0] + o) = make_uint2(kw[0], kw[1]);
-                *reinterpret_cast<uint2*>(a.codes[1] + o) = make_uint2(vw[0], vw[1]);
-            }
-            if (sub == 0) {
-                a.scale[0][prow] = ks_bits;
-                a.scale[1][prow] = vs_bits;
-                if (!SYM) {
-                    a.zp[0][prow] = kq.zp;
-                    a.zp[1][prow] = vq.zp;
+            for (int j = 0; j < TOPK; ++j) {
+                if (r0.s[j] < 0 || pg0[j] < 0) continue;
+                if (pg0[j] >= a.num_pages) {
+                    if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_PAGE);
+                    continue;
+                }
+                const int row = r0.s[j] % PT;
+                const size_t prow = ((size_t)pg0[j] * a.n_kv + head) * PT + row;
+                if (BITS == 8) {
+                    const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
+                    *reinterpret_cast<uint4*>(a.codes[0] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+                    *reinterpret_cast<uint4*>(a.codes[1] + o) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
+                } else {
+                    const size_t o = prow * ROW_BYTES + 8 * swz4_unit(row, sub);
+                    *reinterpret_cast<uint2*>(a.codes[0] + o) = make_uint2(kw[0], kw[1]);
+                    *reinterpret_cast<uint2*>(a.codes[1] + o) = make_uint2(vw[0], vw[1]);
+                }
+                if (sub == 0) {
+                    a.scale[0][prow] = ks_bits;
+                    a.scale[1][prow] = vs_bits;
+                    if (!SYM) {
+                        a.zp[0][prow] = kq.zp;
+                        a.zp[1][prow] = vq.zp;
+                    }
                 }
             }
         }
-        if (more) cur = nxt;
+        // rotate the pipeline
+        r0 = r1; r1 = r2;
+        k0 = k1; v0 = v1;
+#pragma unroll
+        for (int j = 0; j < TOPK; ++j) pg0[j] = pg1[j];
         pair += stride;
         warp_first += stride;
     }
