@@ -372,6 +372,87 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------- secondary workloads
+def fill_stream_cache(pikv_b200, torch, dev, B, n_kv, ctx, seed=0):
+    """int8 cache of B streams x ctx tokens, written through the append kernel stream by stream."""
+    cache = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    pos = torch.arange(ctx, dtype=torch.int32, device=dev)[:, None].contiguous()
+    for b in range(B):
+        K = torch.randn(ctx, n_kv * 128, generator=g, device=dev).bfloat16()
+        V = torch.randn(ctx, n_kv * 128, generator=g, device=dev).bfloat16()
+        cache.append(K, V, torch.full((ctx, 1), b, dtype=torch.int32, device=dev), pos)
+    cache.length.fill_(ctx)
+    return cache
+
+
+def secondary_arm(args):
+    """Decode attention / H2O select / low-rank projection at BASELINE.json's sizes: one JSON line each,
+    same keys as the main line (metric names differ)."""
+    import torch
+    import pikv_b200
+    from pikv_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    peak, peak_src = measured_peak_gbs()
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def timed(fn, n):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def emit(metric, unit, value, ms, cfg, roof, launches):
+        print(json.dumps({"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": steps, "warmup": warmup,
+                          "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                          "data": "synthetic", "config": cfg, "roofline": roof, "gpu_launches": launches}))
+
+    if args.workload == "decode":
+        B, n_q, n_kv, ctx = args.streams, 32, 8, args.context
+        cache = fill_stream_cache(pikv_b200, torch, dev, B, n_kv, ctx)
+        q = torch.randn(B, n_q, 128, device=dev).bfloat16()
+        n0 = pikv_b200.launch_count()
+        ms = timed(lambda: cache.decode_attention(q, splits=args.splits), steps)
+        launches = (pikv_b200.launch_count() - n0) * steps // (steps + warmup)
+        cache.check_status()
+        by = B * n_kv * (2 * ctx * 128 + 2 * ctx * 2) + 2 * B * n_q * 128 * 2
+        gbs = by / (ms * 1e-3) / 1e9
+        emit("decode_attention_GBps", "GB/s", gbs, ms,
+             {"workload": "int8 decode attention", "streams": B, "q_heads": n_q, "kv_heads": n_kv, "context": ctx,
+              "l2": "cache far larger than L2"},
+             {"bound": "hbm", "kernel": "decode_attn_q8_kernel", "achieved": gbs, "peak": peak, "peak_source": peak_src,
+              "unit": "GB/s", "frac": gbs / peak, "traffic": None, "bytes": by}, launches)
+        # budgeted step: H2O keeps 2048 tokens (256 recent + 1792 heavy) per (stream, KV head)
+        acc = torch.rand(B * n_kv, ctx, device=dev)
+        ts = torch.arange(ctx, dtype=torch.float32, device=dev).repeat(B * n_kv, 1)
+        ms_sel = timed(lambda: ops.h2o_select(acc, ts, 1792, 256), steps)
+        by_sel = 2 * 4 * ctx * B * n_kv + B * n_kv * (ctx + 2048 * 4)
+        emit("h2o_select_GBps", "GB/s", by_sel / (ms_sel * 1e-3) / 1e9, ms_sel,
+             {"workload": "H2O segmented top-k", "segments": B * n_kv, "length": ctx, "heavy": 1792, "recent": 256},
+             {"bound": "hbm", "kernel": "h2o_select_kernel", "achieved": by_sel / (ms_sel * 1e-3) / 1e9, "peak": peak,
+              "peak_source": peak_src, "unit": "GB/s", "frac": by_sel / (ms_sel * 1e-3) / 1e9 / peak, "traffic": None}, steps)
+    elif args.workload == "lowrank":
+        M, K = args.rows, 1024
+        x = torch.randn(M, K, device=dev).bfloat16()
+        for r in (64, 32, 16):
+            w = torch.nn.init.orthogonal_(torch.empty(K, K))[:r].contiguous().to(dev).bfloat16()
+            ms = timed(lambda: ops.lowrank_project(x, w, None, relu=True), steps)
+            by = M * K * 2 + M * r * 2
+            gbs, tf = by / (ms * 1e-3) / 1e9, 2.0 * M * K * r / (ms * 1e-3) / 1e12
+            emit("lowrank_project_GBps", "GB/s", gbs, ms,
+                 {"workload": "low-rank KV projection", "rows": M, "hidden": K, "rank": r},
+                 {"bound": "hbm", "kernel": "lowrank_gemm_kernel", "achieved": gbs, "peak": peak, "peak_source": peak_src,
+                  "unit": "GB/s", "frac": gbs / peak, "traffic": None, "TFLOPs": tf}, steps)
+        assert pikv_b200.lib().pikv_lowrank_error_state() == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -380,9 +461,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-side port timing (profiling runs)")
     ap.add_argument("--no-large", action="store_true", help="skip the 8x-token secondary measurement")
+    ap.add_argument("--workload", default="append", choices=["append", "decode", "lowrank"],
+                    help="append = the headline route+quantise+append step; the others print lines for the other kernels")
+    ap.add_argument("--streams", type=int, default=64)
+    ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--rows", type=int, default=262144)
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+    elif args.workload != "append":
+        secondary_arm(args)
     else:
         gpu_arm(args)
 
