@@ -310,12 +310,21 @@ int pikv_lowrank_error_state(void);
  * [n_kv*128] + V codes [n_kv*128] + K scales [n_kv] bf16 + V scales [n_kv] bf16.
  * ---------------------------------------------------------------------- */
 size_t pikv_a2a_record_bytes(int32_t n_kv);
+/* Record index of (token, j): send_pos[t,j] when send_pos is given, else seq_prefix[dst_seq] + slot
+ * (records grouped by destination sequence, (token, j) order inside a sequence - with experts owned
+ * in contiguous blocks that is also grouped by destination rank).  slot < 0 or send_pos < 0 skips. */
 int pikv_a2a_pack(const void* k, const void* v, int32_t dtype, int32_t T, int32_t n_kv, int32_t top_k,
-                  const int32_t* dst_seq, const int32_t* slot, const int32_t* dst_rank,
-                  const int32_t* send_pos, /* [T,k] record index in the send buffer, <0 = skip */
-                  void* send_buf, pikv_stream_t stream);
+                  const int32_t* dst_seq, const int32_t* slot, const int32_t* seq_prefix,
+                  const int32_t* send_pos, void* send_buf, pikv_stream_t stream);
+/* Stores records into the local cache at sequence (header.seq - seq_offset) and position
+ * header.slot + seg_base[segment, local sequence], where segment s covers records
+ * [seg_start[s], seg_start[s+1]) (one segment per source rank; seg_start / seg_base may be NULL:
+ * no offset).  Records whose final position is >= capacity (> 0) are dropped silently, like the
+ * truncation of core/single/cache_scheduling.py:431-435. */
 int pikv_a2a_unpack(const void* recv_buf, int32_t n_records, int32_t n_kv,
                     const int32_t* page_table, int32_t num_seqs, int32_t max_pages, int32_t num_pages,
+                    int32_t seq_offset, int32_t capacity,
+                    const int32_t* seg_start, const int32_t* seg_base, int32_t n_seg,
                     void* k_codes, void* v_codes, void* k_scale, void* v_scale,
                     uint32_t* status, pikv_stream_t stream);
 

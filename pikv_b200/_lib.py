@@ -96,7 +96,7 @@ SIGNATURES = {
     "pikv_lowrank_error_state": (i32, []),
     "pikv_a2a_record_bytes": (sz, [i32]),
     "pikv_a2a_pack": (i32, [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp]),
-    "pikv_a2a_unpack": (i32, [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp]),
+    "pikv_a2a_unpack": (i32, [vp, i32, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp]),
 }
 
 _LIB = None

@@ -1,0 +1,147 @@
+"""Expert-sharded routed KV cache: one process per GPU, token all-to-all over NCCL.
+
+The reference's expert-parallel model replicates the router and every token on
+every rank, lets each rank run its contiguous block of experts on all tokens and
+sums the results with one all_reduce (core/distributed/distributed_pikv.py:91-96,
+174-194).  Here tokens are data-parallel: every rank gates its own tokens, packs
+the quantised K/V rows of each routed (token, expert) pair into fixed-size records
+ordered by destination, and one all_to_all_single moves each record to the rank
+that owns the expert (contiguous blocks, as in the reference), where it is stored
+into that rank's paged cache.
+
+Slot order on the owner is (source rank, token, k) lexicographic, which equals the
+single-GPU order when the global batch is split contiguously over the ranks: the
+N-GPU cache holds exactly the rows, codes and slots of the 1-GPU cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .paged_cache import PagedKVCache
+
+
+def experts_per_rank(num_experts: int, world: int) -> int:
+    """Contiguous expert blocks, core/distributed/distributed_pikv.py:91-96."""
+    if num_experts % world != 0:
+        raise ValueError(f"{num_experts} experts do not split evenly over {world} ranks")
+    return num_experts // world
+
+
+@dataclass
+class ExchangePlan:
+    send_splits: np.ndarray   # [world] records this rank sends to each rank
+    recv_splits: np.ndarray   # [world] records this rank receives from each rank
+    seq_prefix: np.ndarray    # [E] first record index of each expert in this rank's send buffer
+    seg_start: np.ndarray     # [world+1] first received record of each source rank
+    seg_base: np.ndarray      # [world, E_local] slot of the first record of (source, local expert)
+    new_len: np.ndarray       # [E_local] lengths after the step
+    n_send: int
+    n_recv: int
+
+
+def plan_exchange(counts_all: np.ndarray, rank: int, lengths: np.ndarray, capacity: int) -> ExchangePlan:
+    """Everything the exchange needs, from the all-gathered per-rank expert counts.
+
+    counts_all [world, E]: selections of expert e by the tokens of each rank (what the gate counts).
+    lengths [E_local]: current length of this rank's experts.  Pure host arithmetic (numpy)."""
+    counts_all = np.asarray(counts_all, np.int64)
+    world, E = counts_all.shape
+    per = experts_per_rank(E, world)
+    mine = counts_all[rank]
+    send_splits = mine.reshape(world, per).sum(1)
+    lo, hi = rank * per, (rank + 1) * per
+    recv_counts = counts_all[:, lo:hi]                       # [source, local expert]
+    recv_splits = recv_counts.sum(1)
+    seq_prefix = np.concatenate([[0], np.cumsum(mine)[:-1]])
+    seg_start = np.concatenate([[0], np.cumsum(recv_splits)])
+    seg_base = np.asarray(lengths, np.int64)[None, :] + np.cumsum(recv_counts, axis=0) - recv_counts
+    new_len = np.minimum(np.asarray(lengths, np.int64) + recv_counts.sum(0), capacity)
+    return ExchangePlan(send_splits.astype(np.int64), recv_splits.astype(np.int64), seq_prefix.astype(np.int32),
+                        seg_start.astype(np.int32), seg_base.astype(np.int32), new_len.astype(np.int32),
+                        int(send_splits.sum()), int(recv_splits.sum()))
+
+
+class ExpertShardedKVCache:
+    """This rank's slice of the routed cache plus the exchange that feeds it."""
+
+    def __init__(self, num_experts: int, capacity: int, n_kv: int, device, group=None, max_records: int = 0):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.num_experts, self.n_kv, self.capacity = num_experts, n_kv, capacity
+        self.per = experts_per_rank(num_experts, self.world)
+        self.device = torch.device(device)
+        self.cache = PagedKVCache(self.per, capacity, n_kv, device=self.device)
+        self.rec = ops.a2a_record_bytes(n_kv)
+        self._lengths = np.zeros(self.per, np.int64)
+        self._send = self._recv = None
+        self.max_records = max_records
+        self.last_plan: Optional[ExchangePlan] = None
+
+    def _buffers(self, n_send: int, n_recv: int):
+        need_s, need_r = max(n_send, 1, self.max_records) * self.rec, max(n_recv, 1, self.max_records) * self.rec
+        if self._send is None or self._send.numel() < need_s:
+            self._send = torch.empty(need_s, dtype=torch.uint8, device=self.device)
+        if self._recv is None or self._recv.numel() < need_r:
+            self._recv = torch.empty(need_r, dtype=torch.uint8, device=self.device)
+        return self._send, self._recv
+
+    def route_append(self, act: torch.Tensor, w2: torch.Tensor, b2: Optional[torch.Tensor], k: torch.Tensor,
+                     v: torch.Tensor, top_k: int = 2, out: Optional[ops.GateResult] = None) -> ops.GateResult:
+        """Gate this rank's tokens, exchange the quantised rows, store what this rank owns."""
+        g = ops.gate_fused(act, w2, b2, top_k=top_k, capacity=0, out=out)       # slot = rank inside (this rank, expert)
+        counts = g.counts_k.sum(0).to(torch.int32)
+        if self.world > 1:
+            gathered = torch.empty(self.world, self.num_experts, dtype=torch.int32, device=self.device)
+            dist.all_gather_into_tensor(gathered, counts, group=self.group)
+        else:
+            gathered = counts[None]
+        plan = plan_exchange(gathered.cpu().numpy(), self.rank, self._lengths, self.capacity)   # one host read per step
+        self.last_plan = plan
+        send, recv = self._buffers(plan.n_send, plan.n_recv)
+        to_dev = lambda a: torch.from_numpy(a).to(self.device, non_blocking=True)
+        ops.a2a_pack(k, v, self.n_kv, g.topk_idx, g.slot, plan.n_send, seq_prefix=to_dev(plan.seq_prefix), out=send)
+        if self.world > 1:
+            dist.all_to_all_single(recv[: plan.n_recv * self.rec], send[: plan.n_send * self.rec],
+                                   output_split_sizes=(plan.recv_splits * self.rec).tolist(),
+                                   input_split_sizes=(plan.send_splits * self.rec).tolist(), group=self.group)
+        else:
+            recv = send
+        self.cache.unpack_records(recv, plan.n_recv, seq_offset=self.rank * self.per,
+                                  seg_start=to_dev(plan.seg_start), seg_base=to_dev(plan.seg_base.reshape(-1)))
+        self._lengths = plan.new_len.astype(np.int64)
+        self.cache.length.copy_(to_dev(plan.new_len))
+        return g
+
+    def reset(self):
+        self._lengths[:] = 0
+        self.cache.length.zero_()
+
+
+def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs):
+    """The benchmark step at `world` GPUs: every rank routes its own batch of cfg['tokens'] tokens
+    (weak scaling) into the expert-sharded cache.  The cache is emptied every step so that steps
+    are identical."""
+    T, H, E, k = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["top_k"]
+    n_kv = cfg["kv_heads"]
+    kv = n_kv * cfg["head_dim"]
+    cap = int(T * world * cfg["capacity_factor"] * k / E)
+    R = 2
+    sets = [synth_inputs(T, H, E, kv, 1000 * rank + i, device=dev) for i in range(R)]
+    shard = ExpertShardedKVCache(E, cap, n_kv, dev, max_records=int(T * k * 1.5))
+    outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(R)]
+
+    def step(i):
+        act, K, V = sets[i % R]
+        shard.reset()
+        shard.route_append(act, w2, b2, K, V, top_k=k, out=outs[i % R])
+
+    extra = {"parallelism": f"tokens data-parallel, {E} experts sharded {E // world} per GPU, token all-to-all (NCCL)",
+             "buffer_sets": R}
+    return step, extra

@@ -237,14 +237,23 @@ def a2a_record_bytes(n_kv: int) -> int:
 
 
 def a2a_pack(k: torch.Tensor, v: torch.Tensor, n_kv: int, dst_seq: torch.Tensor, slot: torch.Tensor,
-             send_pos: torch.Tensor, n_records: int) -> torch.Tensor:
-    """Quantise (int8 symmetric, per token and head) and pack routed rows into records."""
+             n_records: int, send_pos: Optional[torch.Tensor] = None, seq_prefix: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Quantise (int8 symmetric, per token and head) and pack routed rows into records.  The record
+    index of (token, j) is send_pos[t,j], or seq_prefix[dst_seq[t,j]] + slot[t,j] when send_pos is None."""
     k = _req(k, "k")
     v = _req(v, "v", k.dtype)
     T = k.shape[0]
     top_k = dst_seq.shape[1]
-    buf = torch.zeros(max(n_records, 1) * a2a_record_bytes(n_kv), dtype=torch.uint8, device=k.device)
+    nbytes = max(n_records, 1) * a2a_record_bytes(n_kv)
+    buf = out if out is not None else torch.empty(nbytes, dtype=torch.uint8, device=k.device)
+    if buf.numel() < nbytes:
+        raise PikvError("a2a_pack: output buffer too small")
+    if send_pos is not None:
+        send_pos = _req(send_pos, "send_pos", torch.int32)
+    if seq_prefix is not None:
+        seq_prefix = _req(seq_prefix, "seq_prefix", torch.int32)
     check(lib().pikv_a2a_pack(_p(k), _p(v), _dtype_code(k, "k"), T, n_kv, top_k, _p(_req(dst_seq, "dst_seq", torch.int32)),
-                              _p(_req(slot, "slot", torch.int32)), None, _p(_req(send_pos, "send_pos", torch.int32)),
-                              _p(buf), _stream()), "pikv_a2a_pack")
+                              _p(_req(slot, "slot", torch.int32)), _p(seq_prefix), _p(send_pos), _p(buf), _stream()),
+          "pikv_a2a_pack")
     return buf

@@ -153,14 +153,23 @@ class PagedKVCache(torch.nn.Module):
         p.status = _p(self.status)
         check(lib().pikv_h2o_compact(C.byref(p), _stream()), "pikv_h2o_compact")
 
-    def unpack_records(self, recv_buf: torch.Tensor, n_records: int) -> None:
-        """Store records received from the token all-to-all (see ops.a2a_pack) into the pages."""
+    def unpack_records(self, recv_buf: torch.Tensor, n_records: int, seq_offset: int = 0,
+                       seg_start: Optional[torch.Tensor] = None, seg_base: Optional[torch.Tensor] = None) -> None:
+        """Store records received from the token all-to-all (see ops.a2a_pack) into the pages.  Record
+        sequence ids are global: seq_offset is subtracted.  seg_start [S+1] / seg_base [S, num_seqs] add a
+        per-(source segment, sequence) base to the record's slot; positions >= capacity are dropped."""
         if self.bits != 8 or not self.symmetric:
             raise PikvError("records carry int8 symmetric codes")
         recv_buf = _req(recv_buf, "recv_buf", torch.uint8)
+        n_seg = 0
+        if seg_start is not None:
+            seg_start = _req(seg_start, "seg_start", torch.int32)
+            seg_base = _req(seg_base, "seg_base", torch.int32)
+            n_seg = seg_start.numel() - 1
         check(lib().pikv_a2a_unpack(_p(recv_buf), n_records, self.n_kv, _p(self.page_table), self.num_seqs,
-                                    self.max_pages, self.num_pages, _p(self.k_codes), _p(self.v_codes), _p(self.k_scale),
-                                    _p(self.v_scale), _p(self.status), _stream()), "pikv_a2a_unpack")
+                                    self.max_pages, self.num_pages, seq_offset, self.capacity, _p(seg_start), _p(seg_base),
+                                    n_seg, _p(self.k_codes), _p(self.v_codes), _p(self.k_scale), _p(self.v_scale),
+                                    _p(self.status), _stream()), "pikv_a2a_unpack")
 
     def check_status(self) -> None:
         """Raise if any kernel flagged a bad index, page or a wait that ran out (synchronises)."""

@@ -421,10 +421,32 @@ def test_a2a_pack_unpack_equals_direct_append(dev):
     order = order[flat_ok[order]]
     send_pos = np.full(T * k, -1, np.int32)
     send_pos[order] = np.arange(len(order), dtype=np.int32)
-    buf = ops.a2a_pack(K, V, n_kv, torch.from_numpy(idx).to(dev), torch.from_numpy(slot).to(dev),
-                       torch.from_numpy(send_pos.reshape(T, k)).to(dev), len(order))
+    buf = ops.a2a_pack(K, V, n_kv, torch.from_numpy(idx).to(dev), torch.from_numpy(slot).to(dev), len(order),
+                       send_pos=torch.from_numpy(send_pos.reshape(T, k)).to(dev))
     via = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
     via.unpack_records(buf, len(order))
     via.check_status()
     for name in ("k_codes", "v_codes", "k_scale", "v_scale"):
         assert torch.equal(getattr(direct, name), getattr(via, name)), name
+
+
+def test_sharded_cache_single_rank_equals_direct_append(dev):
+    """World size 1: gate -> pack -> (no exchange) -> unpack must leave exactly the cache the direct
+    route + append leaves."""
+    import pikv_b200
+    from pikv_b200 import ops
+    from pikv_b200.distributed import ExpertShardedKVCache
+    T, H, E, k, n_kv, cap = 3000, 512, 8, 2, 2, 700          # capacity forces drops on the owner side
+    torch.manual_seed(3)
+    act = torch.randn(T, H, device=dev).bfloat16()
+    w2 = (torch.randn(E, H, device=dev) / 20).bfloat16()
+    K, V = outlier_kv(T, n_kv * 128, 5).to(dev), outlier_kv(T, n_kv * 128, 6).to(dev)
+    g = ops.gate_fused(act, w2, None, top_k=k, capacity=cap)
+    direct = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
+    direct.append(K, V, g.topk_idx, g.slot)
+    shard = ExpertShardedKVCache(E, cap, n_kv, dev)
+    shard.route_append(act, w2, None, K, V, top_k=k)
+    shard.cache.check_status()
+    for name in ("k_codes", "v_codes", "k_scale", "v_scale"):
+        assert torch.equal(getattr(direct, name), getattr(shard.cache, name)), name
+    assert torch.equal(shard.cache.length, g.new_len)

@@ -1,0 +1,67 @@
+"""Two-GPU check of the expert-sharded exchange: the union of the two ranks' caches equals the cache a
+single GPU builds from the concatenated batch.  Skipped with fewer than two GPUs."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from pikv_b200.distributed import ExpertShardedKVCache
+        T, H, E, k, n_kv = 2048, 512, 8, 2, 2
+        cap = 900
+        g = torch.Generator().manual_seed(7)
+        act = torch.randn(T, H, generator=g).bfloat16()
+        K = torch.randn(T, n_kv * 128, generator=g).bfloat16()
+        V = torch.randn(T, n_kv * 128, generator=g).bfloat16()
+        w2 = (torch.randn(E, H, generator=g) / 20).bfloat16().to(dev)
+        per = T // world
+        sl = slice(rank * per, (rank + 1) * per)
+        shard = ExpertShardedKVCache(E, cap, n_kv, dev)
+        shard.route_append(act[sl].to(dev), w2, None, K[sl].to(dev), V[sl].to(dev), top_k=k)
+        torch.cuda.synchronize()
+        shard.cache.check_status()
+        torch.save({n: getattr(shard.cache, n).cpu() for n in ("k_codes", "v_codes", "k_scale", "v_scale", "length")},
+                   os.path.join(tmp, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_cache_equals_single_gpu_cache(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import pikv_b200
+    from pikv_b200 import ops
+    world = 2
+    mp.spawn(_worker, args=(world, 29600 + os.getpid() % 1000, str(tmp_path)), nprocs=world, join=True)
+    dev = torch.device("cuda:0")
+    T, H, E, k, n_kv, cap = 2048, 512, 8, 2, 2, 900
+    g = torch.Generator().manual_seed(7)
+    act = torch.randn(T, H, generator=g).bfloat16().to(dev)
+    K = torch.randn(T, n_kv * 128, generator=g).bfloat16().to(dev)
+    V = torch.randn(T, n_kv * 128, generator=g).bfloat16().to(dev)
+    w2 = (torch.randn(E, H, generator=g) / 20).bfloat16().to(dev)
+    res = ops.gate_fused(act, w2, None, top_k=k, capacity=cap)
+    single = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
+    single.append(K, V, res.topk_idx, res.slot)
+    per = E // world
+    pages = single.max_pages
+    for r in range(world):
+        got = torch.load(tmp_path / f"rank{r}.pt")
+        for n in ("k_codes", "v_codes", "k_scale", "v_scale"):
+            want = getattr(single, n)[r * per * pages:(r + 1) * per * pages].cpu()
+            assert torch.equal(got[n], want), (r, n)
+        assert torch.equal(got["length"], res.new_len[r * per:(r + 1) * per].cpu())
