@@ -161,6 +161,36 @@ typedef struct {
 
 int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Expert-sharded routed append: quantise and store straight into the page pools of
+ * the GPU that owns each destination sequence, through peer-mapped pointers (plain
+ * stores over NVLink; no staging buffer, no multicast).  Replaces the
+ * replicate-everything + all_reduce of DistributedPiKVMoE.forward
+ * (core/distributed/distributed_pikv.py:174-194) for the cache-append side.
+ *   base: k, v, dst_seq (GLOBAL sequence ids, owner = id / seqs_per_rank), slot (rank
+ *   of the row inside (this GPU, sequence), i.e. the gate's slot with capacity 0),
+ *   page_table = [num_seqs = world * seqs_per_rank][max_pages] with page ids local to
+ *   the owner, num_pages = pages per GPU; bf16 in, int8 symmetric out; the pool
+ *   pointers of `base` are ignored.
+ *   slot_base [num_seqs]: position of this GPU's first row in every sequence (from
+ *   pikv_shard_plan); rows landing at >= capacity are dropped.
+ *   peer_*[r]: the pools of rank r as seen from this GPU (own pools at r = rank).
+ * The caller orders the step against the other GPUs (all ranks must finish the call
+ * before any rank reads the rows, e.g. a barrier collective on the same stream).
+ * pikv_shard_plan turns the all-gathered selection counts [world][E] into slot_base
+ * for this rank and advances len_all [E] (kept identically on every rank).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    pikv_append_params base;
+    int32_t world, seqs_per_rank, capacity;
+    const int32_t* slot_base;
+    void* peer_k_codes[8]; void* peer_v_codes[8]; void* peer_k_scale[8]; void* peer_v_scale[8];
+} pikv_append_sharded_params;
+
+int pikv_kv_append_sharded(const pikv_append_sharded_params* p, pikv_stream_t stream);
+int pikv_shard_plan(const int32_t* gathered, int32_t world, int32_t E, int32_t rank, int32_t capacity,
+                    int32_t* len_all, int32_t* slot_base, pikv_stream_t stream);
+
 /* Read rows back in logical order, dequantised: out[i] = (code - zp) * scale for
  * sequence seq[i], position pos[i]; out is [n, n_kv*128] fp32, codes_out
  * (optional) [n, n_kv*128] int8 unpacked codes.  Used by tests, checkpointing

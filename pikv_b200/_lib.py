@@ -47,6 +47,13 @@ class AppendParams(C.Structure):
     ]
 
 
+class AppendShardedParams(C.Structure):
+    _fields_ = [
+        ("base", AppendParams), ("world", i32), ("seqs_per_rank", i32), ("capacity", i32), ("slot_base", vp),
+        ("peer_k_codes", vp * 8), ("peer_v_codes", vp * 8), ("peer_k_scale", vp * 8), ("peer_v_scale", vp * 8),
+    ]
+
+
 class CompactParams(C.Structure):
     _fields_ = [
         ("keep_idx", vp), ("kept_count", vp),
@@ -82,6 +89,8 @@ SIGNATURES = {
     "pikv_gate_error_state": (i32, []),
     "pikv_dispatch_scatter": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_kv_append_quant": (i32, [C.POINTER(AppendParams), vp]),
+    "pikv_kv_append_sharded": (i32, [C.POINTER(AppendShardedParams), vp]),
+    "pikv_shard_plan": (i32, [vp, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_cache_gather": (i32, [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "pikv_quant_block_workspace_bytes": (sz, [i32, i32, i32]),
     "pikv_quant_block": (i32, [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp]),

@@ -26,6 +26,11 @@ struct AppendDev {
     uint16_t* scale[2];
     float* zp[2];
     unsigned* status;
+    // expert-sharded variant: destination pools live on the rank that owns the sequence
+    int world, per, capacity;
+    const int* slot_base;        // [num_seqs] added to the slot
+    uint8_t* pcodes[2][8];       // [K|V][rank] peer-mapped code pools
+    uint16_t* pscale[2][8];
 };
 
 // One 8-lane group per (token, head) item: both the K and the V slice of that head.  The grid is
@@ -64,9 +69,9 @@ __device__ __forceinline__ void append_stage_route(const AppendDev& a, unsigned 
     }
 }
 
-template <typename TIn, int BITS, bool SYM, int TOPK>
+template <typename TIn, int BITS, bool SYM, int TOPK, bool SHARDED>
 __device__ __forceinline__ void append_stage_load(const AppendDev& a, unsigned pair, unsigned total, int sub,
-                                                  const AppendRoute<TOPK>& r, int (&page)[TOPK],
+                                                  AppendRoute<TOPK>& r, int (&page)[TOPK],
                                                   typename GroupQuant<TIn, BITS, SYM>::Raw& k,
                                                   typename GroupQuant<TIn, BITS, SYM>::Raw& v) {
     unsigned t = 0, head = 0;
@@ -74,6 +79,11 @@ __device__ __forceinline__ void append_stage_load(const AppendDev& a, unsigned p
 #pragma unroll
     for (int j = 0; j < TOPK; ++j) {
         page[j] = -1;
+        if (SHARDED && r.s[j] >= 0 && r.q[j] >= 0 && r.q[j] < a.num_seqs) {
+            // slot on the owner = this rank's base for the sequence + rank inside (this rank, sequence)
+            const int sf = r.s[j] + __ldg(a.slot_base + r.q[j]);
+            r.s[j] = (a.capacity > 0 && sf >= a.capacity) ? -1 : sf;
+        }
         if (r.s[j] >= 0) {
             if (r.q[j] < 0 || r.q[j] >= a.num_seqs || (r.s[j] / PT) >= a.max_pages) {
                 if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_SEQ);
@@ -87,7 +97,7 @@ __device__ __forceinline__ void append_stage_load(const AppendDev& a, unsigned p
     GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.v) + off, v);
 }
 
-template <typename TIn, int BITS, bool SYM, int TOPK>
+template <typename TIn, int BITS, bool SYM, int TOPK, bool SHARDED>
 __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(AppendDev a) {
     constexpr int ROW_BYTES = D * BITS / 8;
     using GQ = GroupQuant<TIn, BITS, SYM>;
@@ -105,11 +115,12 @@ __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(Appe
     // prologue: item 0 fully fetched, item 1 routed
     append_stage_route<TOPK>(a, pair, total, r0);
     append_stage_route<TOPK>(a, pair + stride, total, r1);
-    append_stage_load<TIn, BITS, SYM, TOPK>(a, pair, total, sub, r0, pg0, k0, v0);
+    append_stage_load<TIn, BITS, SYM, TOPK, SHARDED>(a, pair, total, sub, r0, pg0, k0, v0);
 
     while (warp_first < total) {
         append_stage_route<TOPK>(a, pair + 2 * stride, total, r2);
-        if (warp_first + stride < total) append_stage_load<TIn, BITS, SYM, TOPK>(a, pair + stride, total, sub, r1, pg1, k1, v1);
+        if (warp_first + stride < total)
+            append_stage_load<TIn, BITS, SYM, TOPK, SHARDED>(a, pair + stride, total, sub, r1, pg1, k1, v1);
 
         QParams kq, vq;
         uint32_t kw[4], vw[4];
@@ -128,6 +139,18 @@ __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(Appe
                 }
                 const int row = r0.s[j] % PT;
                 const size_t prow = ((size_t)pg0[j] * a.n_kv + head) * PT + row;
+                if (SHARDED) {
+                    // the owner's pools, mapped into this GPU's address space: plain stores over NVLink
+                    const int owner = r0.q[j] / a.per;
+                    const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
+                    *reinterpret_cast<uint4*>(a.pcodes[0][owner] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+                    *reinterpret_cast<uint4*>(a.pcodes[1][owner] + o) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
+                    if (sub == 0) {
+                        a.pscale[0][owner][prow] = ks_bits;
+                        a.pscale[1][owner][prow] = vs_bits;
+                    }
+                    continue;
+                }
                 if (BITS == 8) {
                     const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
                     *reinterpret_cast<uint4*>(a.codes[0] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
@@ -216,10 +239,10 @@ static int launch_append(const AppendDev& a, int bits, int symmetric, cudaStream
     const int grid = (int)(want < cap_ctas ? want : cap_ctas);
 #define PIKV_APPEND_LAUNCH(BITS, SYM)                                                                   \
     do {                                                                                                \
-        if (a.top_k <= 1) kv_append_quant_kernel<TIn, BITS, SYM, 1><<<grid, APPEND_THREADS, 0, st>>>(a);      \
-        else if (a.top_k <= 2) kv_append_quant_kernel<TIn, BITS, SYM, 2><<<grid, APPEND_THREADS, 0, st>>>(a); \
-        else if (a.top_k <= 4) kv_append_quant_kernel<TIn, BITS, SYM, 4><<<grid, APPEND_THREADS, 0, st>>>(a); \
-        else kv_append_quant_kernel<TIn, BITS, SYM, 8><<<grid, APPEND_THREADS, 0, st>>>(a);                   \
+        if (a.top_k <= 1) kv_append_quant_kernel<TIn, BITS, SYM, 1, false><<<grid, APPEND_THREADS, 0, st>>>(a);      \
+        else if (a.top_k <= 2) kv_append_quant_kernel<TIn, BITS, SYM, 2, false><<<grid, APPEND_THREADS, 0, st>>>(a); \
+        else if (a.top_k <= 4) kv_append_quant_kernel<TIn, BITS, SYM, 4, false><<<grid, APPEND_THREADS, 0, st>>>(a); \
+        else kv_append_quant_kernel<TIn, BITS, SYM, 8, false><<<grid, APPEND_THREADS, 0, st>>>(a);                   \
     } while (0)
     if (bits == 8 && symmetric) PIKV_APPEND_LAUNCH(8, true);
     else if (bits == 8) PIKV_APPEND_LAUNCH(8, false);
@@ -258,9 +281,83 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
     a.zp[0] = static_cast<float*>(p->k_zp); a.zp[1] = static_cast<float*>(p->v_zp);
     a.status = p->status;
+    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr;
+    for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (p->dtype == PIKV_BF16) return launch_append<__nv_bfloat16>(a, p->bits, p->symmetric, st);
     return launch_append<float>(a, p->bits, p->symmetric, st);
+}
+
+// ---- expert-sharded append: plan + launch -----------------------------------------------------------
+// One CTA: from the all-gathered per-rank selection counts, the slot at which this rank's first row
+// of every sequence lands on its owner (rows are ordered by source rank), and the new lengths.
+__global__ void shard_plan_kernel(const int* gathered, int world, int E, int rank, int capacity, int* len_all,
+                                  int* slot_base) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= E) return;
+    int before = 0, total = 0;
+    for (int s = 0; s < world; ++s) {
+        const int c = gathered[s * E + e];
+        if (s < rank) before += c;
+        total += c;
+    }
+    const int len = len_all[e];
+    slot_base[e] = len + before;
+    const int n = len + total;
+    len_all[e] = (capacity > 0 && n > capacity) ? capacity : n;
+}
+
+extern "C" int pikv_shard_plan(const int32_t* gathered, int32_t world, int32_t E, int32_t rank, int32_t capacity,
+                               int32_t* len_all, int32_t* slot_base, pikv_stream_t stream) {
+    PIKV_REQUIRE(gathered && len_all && slot_base, PIKV_EINVAL, "shard_plan: null pointer");
+    PIKV_REQUIRE(world > 0 && E > 0 && rank >= 0 && rank < world, PIKV_EINVAL, "shard_plan: bad sizes");
+    shard_plan_kernel<<<ceil_div(E, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(gathered, world, E, rank, capacity,
+                                                                                       len_all, slot_base);
+    count_launch(1);
+    return check_launch("shard_plan_kernel");
+}
+
+extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv_stream_t stream) {
+    PIKV_REQUIRE(sp != nullptr, PIKV_EINVAL, "append_sharded: null params");
+    const pikv_append_params* p = &sp->base;
+    PIKV_REQUIRE(p->T >= 0 && p->n_kv > 0 && p->top_k > 0 && p->top_k <= APPEND_MAX_K, PIKV_EINVAL, "append_sharded: bad sizes");
+    if (p->T == 0) return PIKV_OK;
+    PIKV_REQUIRE(p->k && p->v && p->dst_seq && p->slot && p->page_table && sp->slot_base, PIKV_EINVAL,
+                 "append_sharded: null input pointer");
+    PIKV_REQUIRE(p->dtype == PIKV_BF16 && p->bits == 8 && p->symmetric, PIKV_EUNSUPPORTED,
+                 "append_sharded: bf16 inputs, int8 symmetric codes only");
+    PIKV_REQUIRE(sp->world >= 1 && sp->world <= 8 && sp->seqs_per_rank > 0 && p->num_seqs == sp->world * sp->seqs_per_rank,
+                 PIKV_EINVAL, "append_sharded: world must be 1..8 and num_seqs = world * seqs_per_rank");
+    PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28), PIKV_ELIMIT, "append_sharded: T * n_kv must stay below 2^28");
+    AppendDev a;
+    a.k = p->k; a.v = p->v; a.T = p->T; a.n_kv = p->n_kv; a.top_k = p->top_k;
+    a.log2_nkv = -1;
+    for (int b = 0; b < 16; ++b)
+        if ((1 << b) == p->n_kv) a.log2_nkv = b;
+    a.dst_seq = p->dst_seq; a.slot = p->slot; a.page_table = p->page_table;
+    a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
+    a.codes[0] = a.codes[1] = nullptr; a.scale[0] = a.scale[1] = nullptr; a.zp[0] = a.zp[1] = nullptr;
+    a.status = p->status;
+    a.world = sp->world; a.per = sp->seqs_per_rank; a.capacity = sp->capacity; a.slot_base = sp->slot_base;
+    for (int r = 0; r < 8; ++r) {
+        const bool on = r < sp->world;
+        PIKV_REQUIRE(!on || (sp->peer_k_codes[r] && sp->peer_v_codes[r] && sp->peer_k_scale[r] && sp->peer_v_scale[r]),
+                     PIKV_EINVAL, "append_sharded: null pool pointer for rank %d", r);
+        a.pcodes[0][r] = on ? static_cast<uint8_t*>(sp->peer_k_codes[r]) : nullptr;
+        a.pcodes[1][r] = on ? static_cast<uint8_t*>(sp->peer_v_codes[r]) : nullptr;
+        a.pscale[0][r] = on ? static_cast<uint16_t*>(sp->peer_k_scale[r]) : nullptr;
+        a.pscale[1][r] = on ? static_cast<uint16_t*>(sp->peer_v_scale[r]) : nullptr;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long lanes = (long long)a.T * a.n_kv * 8;
+    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 3;
+    const int grid = (int)(want < cap_ctas ? want : cap_ctas);
+    if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, true><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, true><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else if (a.top_k <= 4) kv_append_quant_kernel<__nv_bfloat16, 8, true, 4, true><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, true><<<grid, APPEND_THREADS, 0, st>>>(a);
+    count_launch(1);
+    return check_launch("kv_append_quant_kernel (sharded)");
 }
 
 extern "C" int pikv_cache_gather(const int32_t* seq, const int32_t* pos, int32_t n, const int32_t* page_table,

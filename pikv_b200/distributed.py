@@ -124,24 +124,116 @@ class ExpertShardedKVCache:
         self.cache.length.zero_()
 
 
-def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs):
+class PeerShardedKVCache:
+    """Expert-sharded cache whose append kernel stores straight into the owner GPU's pages.
+
+    Every rank's page pools live in one symmetric-memory allocation, so each rank holds a
+    peer-mapped pointer to every other rank's pools (NVLink, NVSwitch).  A step is: gate the local
+    tokens -> all-gather the E selection counts (NCCL, stream-ordered, no host read) -> a one-CTA
+    plan kernel (slot of this rank's first row in every sequence, new lengths) -> the quantise +
+    append kernel, whose stores for remote sequences cross NVLink as plain 16-byte stores ->
+    a symmetric-memory barrier so that every rank's rows have landed.  Nothing on the step
+    touches the host, and no copy of a row is staged in HBM: per-GPU HBM traffic is that of the
+    single-GPU step.  No multicast object is created (plain peer pointers only).
+    """
+
+    def __init__(self, num_experts: int, capacity: int, n_kv: int, device, group=None):
+        import ctypes as C
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib
+        self._C, self._lib = C, _lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("one box: at most 8 ranks")
+        self.num_experts, self.n_kv, self.capacity = num_experts, n_kv, capacity
+        self.per = experts_per_rank(num_experts, self.world)
+        self.device = torch.device(device)
+        # the local cache object gives the layout; its pools are then re-homed into symmetric memory
+        self.cache = PagedKVCache(self.per, capacity, n_kv, device=self.device)
+        names = ("k_codes", "v_codes", "k_scale", "v_scale")
+        sizes = [getattr(self.cache, n).numel() * getattr(self.cache, n).element_size() for n in names]
+        offs = np.concatenate([[0], np.cumsum([(b + 255) // 256 * 256 for b in sizes])])
+        self._buf = symm.empty(int(offs[-1]), dtype=torch.uint8, device=self.device)
+        self._buf.zero_()
+        self._hdl = symm.rendezvous(self._buf, self.group)
+        self._peer = {n: [int(self._hdl.buffer_ptrs[r]) + int(offs[i]) for r in range(self.world)]
+                      for i, n in enumerate(names)}
+        for i, n in enumerate(names):
+            old = getattr(self.cache, n)
+            view = self._buf[int(offs[i]): int(offs[i]) + sizes[i]].view(old.dtype).view(old.shape)
+            setattr(self.cache, n, view)
+        mp = self.cache.max_pages
+        table = (torch.arange(num_experts, device=self.device) % self.per)[:, None] * mp + torch.arange(mp, device=self.device)
+        self.global_table = table.to(torch.int32).contiguous()
+        self.len_all = torch.zeros(num_experts, dtype=torch.int32, device=self.device)
+        self.slot_base = torch.zeros(num_experts, dtype=torch.int32, device=self.device)
+        self.gathered = torch.zeros(self.world, num_experts, dtype=torch.int32, device=self.device)
+        self.counts = torch.zeros(num_experts, dtype=torch.int32, device=self.device)
+
+    def route_append(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None,
+                     sync: bool = True) -> ops.GateResult:
+        C, L = self._C, self._lib
+        g = ops.gate_fused(act, w2, b2, top_k=top_k, capacity=0, out=out)
+        torch.sum(g.counts_k, dim=0, dtype=torch.int32, out=self.counts)
+        dist.all_gather_into_tensor(self.gathered, self.counts, group=self.group)
+        st = ops._stream()
+        L.check(L.lib().pikv_shard_plan(ops._p(self.gathered), self.world, self.num_experts, self.rank, self.capacity,
+                                        ops._p(self.len_all), ops._p(self.slot_base), st), "pikv_shard_plan")
+        sp = L.AppendShardedParams()
+        b = sp.base
+        k, v = ops._req(k, "k", torch.bfloat16), ops._req(v, "v", torch.bfloat16)
+        b.k, b.v, b.dtype, b.T, b.n_kv, b.top_k = ops._p(k), ops._p(v), L.PIKV_BF16, k.shape[0], self.n_kv, top_k
+        b.dst_seq, b.slot, b.page_table = ops._p(g.topk_idx), ops._p(g.slot), ops._p(self.global_table)
+        b.num_seqs, b.max_pages, b.num_pages = self.num_experts, self.cache.max_pages, self.cache.num_pages
+        b.bits, b.symmetric, b.status = 8, 1, ops._p(self.cache.status)
+        sp.world, sp.seqs_per_rank, sp.capacity, sp.slot_base = self.world, self.per, self.capacity, ops._p(self.slot_base)
+        for r in range(self.world):
+            sp.peer_k_codes[r], sp.peer_v_codes[r] = self._peer["k_codes"][r], self._peer["v_codes"][r]
+            sp.peer_k_scale[r], sp.peer_v_scale[r] = self._peer["k_scale"][r], self._peer["v_scale"][r]
+        L.check(L.lib().pikv_kv_append_sharded(C.byref(sp), st), "pikv_kv_append_sharded")
+        if sync:
+            self.barrier()
+        lo = self.rank * self.per
+        self.cache.length.copy_(self.len_all[lo: lo + self.per])
+        return g
+
+    def barrier(self):
+        """All ranks' append kernels are complete (and their remote stores visible) after this point
+        of the stream: a device-side barrier over the symmetric memory's signal pads, no host sync."""
+        self._hdl.barrier(channel=0)
+
+    def reset(self):
+        self.len_all.zero_()
+        self.cache.length.zero_()
+
+
+def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "peer"):
     """The benchmark step at `world` GPUs: every rank routes its own batch of cfg['tokens'] tokens
-    (weak scaling) into the expert-sharded cache.  The cache is emptied every step so that steps
-    are identical."""
+    (weak scaling) into the expert-sharded cache.  mode "peer": the append kernel stores into the
+    owner GPU's pages over NVLink; mode "a2a": pack -> NCCL all_to_all -> unpack.  The cache is
+    emptied every step so that steps are identical."""
     T, H, E, k = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["top_k"]
     n_kv = cfg["kv_heads"]
     kv = n_kv * cfg["head_dim"]
     cap = int(T * world * cfg["capacity_factor"] * k / E)
     R = 2
     sets = [synth_inputs(T, H, E, kv, 1000 * rank + i, device=dev) for i in range(R)]
-    shard = ExpertShardedKVCache(E, cap, n_kv, dev, max_records=int(T * k * 1.5))
     outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(R)]
+    if mode == "peer":
+        shard = PeerShardedKVCache(E, cap, n_kv, dev)
+        how = "append kernel stores into the owner GPU's pages over NVLink (peer pointers)"
+    else:
+        shard = ExpertShardedKVCache(E, cap, n_kv, dev, max_records=int(T * k * 1.5))
+        how = "pack -> NCCL all_to_all -> unpack"
 
     def step(i):
         act, K, V = sets[i % R]
         shard.reset()
         shard.route_append(act, w2, b2, K, V, top_k=k, out=outs[i % R])
 
-    extra = {"parallelism": f"tokens data-parallel, {E} experts sharded {E // world} per GPU, token all-to-all (NCCL)",
+    extra = {"parallelism": f"tokens data-parallel, {E} experts sharded {E // world} per GPU; {how}",
              "buffer_sets": R}
     return step, extra

@@ -13,14 +13,14 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, tmp):
+def _worker(rank, world, port, tmp, mode="a2a"):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        from pikv_b200.distributed import ExpertShardedKVCache
+        from pikv_b200.distributed import ExpertShardedKVCache, PeerShardedKVCache
         T, H, E, k, n_kv = 2048, 512, 8, 2, 2
         cap = 900
         g = torch.Generator().manual_seed(7)
@@ -30,8 +30,10 @@ def _worker(rank, world, port, tmp):
         w2 = (torch.randn(E, H, generator=g) / 20).bfloat16().to(dev)
         per = T // world
         sl = slice(rank * per, (rank + 1) * per)
-        shard = ExpertShardedKVCache(E, cap, n_kv, dev)
+        shard = (PeerShardedKVCache if mode == "peer" else ExpertShardedKVCache)(E, cap, n_kv, dev)
         shard.route_append(act[sl].to(dev), w2, None, K[sl].to(dev), V[sl].to(dev), top_k=k)
+        if mode == "peer":      # a second step on top of the first: lengths and bases carry over
+            shard.route_append(act[sl].to(dev), w2, None, K[sl].to(dev), V[sl].to(dev), top_k=k)
         torch.cuda.synchronize()
         shard.cache.check_status()
         torch.save({n: getattr(shard.cache, n).cpu() for n in ("k_codes", "v_codes", "k_scale", "v_scale", "length")},
@@ -40,13 +42,14 @@ def _worker(rank, world, port, tmp):
         dist.destroy_process_group()
 
 
-def test_two_gpu_cache_equals_single_gpu_cache(tmp_path):
+@pytest.mark.parametrize("mode", ["a2a", "peer"])
+def test_two_gpu_cache_equals_single_gpu_cache(tmp_path, mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import pikv_b200
     from pikv_b200 import ops
     world = 2
-    mp.spawn(_worker, args=(world, 29600 + os.getpid() % 1000, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, 29600 + os.getpid() % 1000, str(tmp_path), mode), nprocs=world, join=True)
     dev = torch.device("cuda:0")
     T, H, E, k, n_kv, cap = 2048, 512, 8, 2, 2, 900
     g = torch.Generator().manual_seed(7)
@@ -57,6 +60,9 @@ def test_two_gpu_cache_equals_single_gpu_cache(tmp_path):
     res = ops.gate_fused(act, w2, None, top_k=k, capacity=cap)
     single = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
     single.append(K, V, res.topk_idx, res.slot)
+    if mode == "peer":          # the same batch appended twice, as the workers did
+        res = ops.gate_fused(act, w2, None, top_k=k, capacity=cap, slot_base=res.new_len)
+        single.append(K, V, res.topk_idx, res.slot)
     per = E // world
     pages = single.max_pages
     for r in range(world):
