@@ -264,20 +264,12 @@ def gpu_arm(args):
         R = extra_cfg.pop("buffer_sets", 1)
         for i in range(warmup):
             step_fn(i)
-        launch_mode = "eager C-ABI calls + NCCL"
+        # launched eagerly: capturing the step (NCCL all-gather + symmetric-memory barrier) in a CUDA
+        # graph hung on the 2-GPU boxes of this pool, so multi-GPU steps are not captured
+        launch_mode = "eager C-ABI calls + NCCL all-gather + peer barrier" if args.shard_mode == "peer" else \
+            "eager C-ABI calls + NCCL all_to_all"
         replay = step_fn
         per_step = None
-        if args.shard_mode == "peer" and not args.no_graph:
-            # the whole step (kernels, NCCL all-gather, symmetric-memory barrier) is stream-ordered and
-            # host-free, so it is captured once per buffer set and replayed
-            try:
-                graphs = [capture(lambda i=i: step_fn(i)) for i in range(R)]
-                per_step = graphs[0][1]
-                replay = lambda i: graphs[i % R][0].replay()
-                launch_mode = "one CUDA graph replay per step (kernels + NCCL all-gather + peer barrier)"
-            except Exception as exc:                       # capture not supported by this NCCL / torch build
-                launch_mode += f" (graph capture unavailable: {type(exc).__name__})"
-                torch.cuda.synchronize()
         for i in range(warmup):
             replay(i)
         sampler = ClockSampler(local)
@@ -484,7 +476,6 @@ def main():
     ap.add_argument("--rows", type=int, default=262144)
     ap.add_argument("--shard-mode", default="peer", choices=["peer", "a2a"],
                     help="multi-GPU: peer = append kernel stores into the owner's pages over NVLink; a2a = pack + NCCL all_to_all")
-    ap.add_argument("--no-graph", action="store_true", help="multi-GPU: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

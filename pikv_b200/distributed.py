@@ -173,32 +173,63 @@ class PeerShardedKVCache:
         self.gathered = torch.zeros(self.world, num_experts, dtype=torch.int32, device=self.device)
         self.counts = torch.zeros(num_experts, dtype=torch.int32, device=self.device)
 
-    def route_append(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None,
-                     sync: bool = True) -> ops.GateResult:
+    def prepare(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None):
+        """Bind one set of buffers to a step and return `run()`: the argument blocks are built once, so a
+        call of run() is six enqueues (gate, count sum, all-gather, plan, append, barrier) and no host
+        arithmetic.  The buffers must stay alive and in place while run() is used."""
         C, L = self._C, self._lib
-        g = ops.gate_fused(act, w2, b2, top_k=top_k, capacity=0, out=out)
-        torch.sum(g.counts_k, dim=0, dtype=torch.int32, out=self.counts)
-        dist.all_gather_into_tensor(self.gathered, self.counts, group=self.group)
-        st = ops._stream()
-        L.check(L.lib().pikv_shard_plan(ops._p(self.gathered), self.world, self.num_experts, self.rank, self.capacity,
-                                        ops._p(self.len_all), ops._p(self.slot_base), st), "pikv_shard_plan")
+        act, w2 = ops._req(act, "act", torch.bfloat16), ops._req(w2, "w2", torch.bfloat16)
+        k, v = ops._req(k, "k", torch.bfloat16), ops._req(v, "v", torch.bfloat16)
+        T, H = act.shape
+        E = self.num_experts
+        if out is None:
+            out = ops.gate_fused(act, w2, b2, top_k=top_k, capacity=0)
+        ws = ops._workspace(self.device, L.lib().pikv_gate_workspace_bytes(T, E, top_k), "gate")
+        b2f = None if b2 is None else ops._req(b2.to(torch.float32), "b2", torch.float32)
+        gp = L.GateParams()
+        gp.act, gp.w2, gp.b2, gp.dtype = ops._p(act), ops._p(w2), ops._p(b2f), L.PIKV_BF16
+        gp.T, gp.H, gp.E, gp.top_k, gp.temperature, gp.capacity = T, H, E, top_k, 1.0, 0
+        gp.probs, gp.topk_idx, gp.topk_w, gp.slot = ops._p(out.probs), ops._p(out.topk_idx), ops._p(out.topk_w), ops._p(out.slot)
+        gp.counts_k, gp.prob_sum, gp.new_len = ops._p(out.counts_k), ops._p(out.prob_sum), ops._p(out.new_len)
+        gp.workspace, gp.workspace_bytes = ops._p(ws), ws.numel()
         sp = L.AppendShardedParams()
         b = sp.base
-        k, v = ops._req(k, "k", torch.bfloat16), ops._req(v, "v", torch.bfloat16)
-        b.k, b.v, b.dtype, b.T, b.n_kv, b.top_k = ops._p(k), ops._p(v), L.PIKV_BF16, k.shape[0], self.n_kv, top_k
-        b.dst_seq, b.slot, b.page_table = ops._p(g.topk_idx), ops._p(g.slot), ops._p(self.global_table)
-        b.num_seqs, b.max_pages, b.num_pages = self.num_experts, self.cache.max_pages, self.cache.num_pages
+        b.k, b.v, b.dtype, b.T, b.n_kv, b.top_k = ops._p(k), ops._p(v), L.PIKV_BF16, T, self.n_kv, top_k
+        b.dst_seq, b.slot, b.page_table = ops._p(out.topk_idx), ops._p(out.slot), ops._p(self.global_table)
+        b.num_seqs, b.max_pages, b.num_pages = E, self.cache.max_pages, self.cache.num_pages
         b.bits, b.symmetric, b.status = 8, 1, ops._p(self.cache.status)
         sp.world, sp.seqs_per_rank, sp.capacity, sp.slot_base = self.world, self.per, self.capacity, ops._p(self.slot_base)
         for r in range(self.world):
             sp.peer_k_codes[r], sp.peer_v_codes[r] = self._peer["k_codes"][r], self._peer["v_codes"][r]
             sp.peer_k_scale[r], sp.peer_v_scale[r] = self._peer["k_scale"][r], self._peer["v_scale"][r]
-        L.check(L.lib().pikv_kv_append_sharded(C.byref(sp), st), "pikv_kv_append_sharded")
-        if sync:
-            self.barrier()
+        lib, keep = L.lib(), (act, w2, b2f, k, v, out, ws)
+        gathered, counts, len_all, slot_base = ops._p(self.gathered), self.counts, ops._p(self.len_all), ops._p(self.slot_base)
+
+        def run(sync: bool = True):
+            st = ops._stream()
+            L.check(lib.pikv_gate_fused(C.byref(gp), st), "pikv_gate_fused")
+            torch.sum(out.counts_k, dim=0, dtype=torch.int32, out=counts)
+            dist.all_gather_into_tensor(self.gathered, counts, group=self.group)
+            L.check(lib.pikv_shard_plan(gathered, self.world, E, self.rank, self.capacity, len_all, slot_base, st),
+                    "pikv_shard_plan")
+            L.check(lib.pikv_kv_append_sharded(C.byref(sp), st), "pikv_kv_append_sharded")
+            if sync:
+                self.barrier()
+            return out
+
+        run._keep = keep
+        return run
+
+    def route_append(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None,
+                     sync: bool = True) -> ops.GateResult:
+        g = self.prepare(act, w2, b2, k, v, top_k, out)(sync)
+        self.sync_lengths()
+        return g
+
+    def sync_lengths(self):
+        """Copy this rank's slice of the replicated length table into the local cache object."""
         lo = self.rank * self.per
         self.cache.length.copy_(self.len_all[lo: lo + self.per])
-        return g
 
     def barrier(self):
         """All ranks' append kernels are complete (and their remote stores visible) after this point
@@ -207,7 +238,6 @@ class PeerShardedKVCache:
 
     def reset(self):
         self.len_all.zero_()
-        self.cache.length.zero_()
 
 
 def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "peer"):
@@ -225,14 +255,19 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
     if mode == "peer":
         shard = PeerShardedKVCache(E, cap, n_kv, dev)
         how = "append kernel stores into the owner GPU's pages over NVLink (peer pointers)"
+        runs = [shard.prepare(sets[i][0], w2, b2, sets[i][1], sets[i][2], top_k=k, out=outs[i]) for i in range(R)]
+
+        def step(i):
+            shard.reset()
+            runs[i % R]()
     else:
         shard = ExpertShardedKVCache(E, cap, n_kv, dev, max_records=int(T * k * 1.5))
         how = "pack -> NCCL all_to_all -> unpack"
 
-    def step(i):
-        act, K, V = sets[i % R]
-        shard.reset()
-        shard.route_append(act, w2, b2, K, V, top_k=k, out=outs[i % R])
+        def step(i):
+            act, K, V = sets[i % R]
+            shard.reset()
+            shard.route_append(act, w2, b2, K, V, top_k=k, out=outs[i % R])
 
     extra = {"parallelism": f"tokens data-parallel, {E} experts sharded {E // world} per GPU; {how}",
              "buffer_sets": R}
