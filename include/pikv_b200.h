@@ -300,6 +300,20 @@ size_t pikv_decode_attn_workspace_bytes(int32_t B, int32_t n_q, int32_t n_kv, in
 int    pikv_decode_attn_default_splits(int32_t B, int32_t n_kv, int32_t max_ctx);
 int    pikv_decode_attn_q8(const pikv_decode_params* p, pikv_stream_t stream);
 
+/* Same computation for callers that cannot allocate device memory at the point where they need
+ * attention (a server that gave all of HBM to its own pool at start-up, a plug-in inside an
+ * allocator-free region, code inside a stream capture).  It has no counterpart in the reference.
+ * The split partials go to an 8 MiB array built into the library (held by every GPU that loads it,
+ * until exit) instead of `workspace`, which is ignored; the call makes no cudaMalloc / cudaFree and
+ * calls no allocating routine.  B * n_q * splits * 520 bytes must fit in
+ * pikv_decode_attn_static_scratch_bytes() (config 3, 64 x 32 x 7 splits, does), otherwise
+ * PIKV_ELIMIT.  The first call on each device looks the array's address up
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on a device
+ * share the array: it needs no clearing (every partial a launch reads was written by that launch),
+ * but two calls whose kernels overlap on the GPU (different streams) race on it. */
+size_t pikv_decode_attn_static_scratch_bytes(void);
+int    pikv_decode_attn_q8_static(const pikv_decode_params* p, pikv_stream_t stream);
+
 /* acc[b, kvh, pos] += sum over the g query heads of exp(score - lse): the H2O
  * accumulated-attention increment (core/single/pikv_moe.py:241-245 column sums
  * fed to core/single/cache_scheduling.py:69-73).  acc: [B*n_kv, acc_stride]. */

@@ -100,6 +100,8 @@ SIGNATURES = {
     "pikv_decode_attn_workspace_bytes": (sz, [i32, i32, i32, i32, i32]),
     "pikv_decode_attn_default_splits": (i32, [i32, i32, i32]),
     "pikv_decode_attn_q8": (i32, [C.POINTER(DecodeParams), vp]),
+    "pikv_decode_attn_static_scratch_bytes": (sz, []),
+    "pikv_decode_attn_q8_static": (i32, [C.POINTER(DecodeParams), vp]),
     "pikv_h2o_accumulate_attn": (i32, [vp, i32, vp, vp, i32, i32, i32, vp, i32, vp]),
     "pikv_lowrank_project": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "pikv_lowrank_error_state": (i32, []),

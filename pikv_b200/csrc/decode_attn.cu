@@ -16,6 +16,8 @@
 // memory; with more than one split a second kernel merges the splits.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace pikv {
 
 constexpr int DA_WARPS = 4;
@@ -426,3 +428,59 @@ extern "C" int pikv_decode_attn_q8(const pikv_decode_params* p, pikv_stream_t st
     count_launch(launches);
     return rc;
 }
+
+// ---- decode attention for callers that must not allocate --------------------------------------------
+// Some hosts of this library cannot call cudaMalloc when they need attention: a serving process that
+// handed all of HBM to its own page pool at start-up, a plug-in that runs inside someone else's
+// allocator-free region, code between cudaStreamBeginCapture and EndCapture.  For them the split-KV
+// partials live in this fixed array inside the library image.  Every GPU that loads the library keeps
+// these 8 MiB until the process exits, and every call on a device shares them.
+constexpr size_t DA_STATIC_SCRATCH_BYTES = (size_t)8 << 20;
+static __device__ __align__(256) unsigned char g_decode_static_scratch[DA_STATIC_SCRATCH_BYTES];
+
+// In host code the array's name is only a handle; the device address comes from the runtime, once per
+// device, with that device current.
+static int decode_static_scratch_ptr(void** out) {
+    static void* ptrs[64];
+    static bool have[64];
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("decode_attn_static: cannot identify the current device");
+        return PIKV_ECUDA;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!have[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("decode_attn_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return PIKV_ECUDA;
+        }
+        ptrs[dev] = p;
+        have[dev] = true;
+    }
+    *out = ptrs[dev];
+    return PIKV_OK;
+}
+
+extern "C" size_t pikv_decode_attn_static_scratch_bytes(void) { return DA_STATIC_SCRATCH_BYTES; }
+
+extern "C" int pikv_decode_attn_q8_static(const pikv_decode_params* p, pikv_stream_t stream) {
+    PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "decode_attn_static: null params");
+    PIKV_REQUIRE(p->B > 0 && p->n_q > 0 && p->n_kv > 0 && p->max_pages > 0, PIKV_EINVAL, "decode_attn_static: bad sizes");
+    pikv_decode_params q = *p;
+    q.splits = p->splits > 0 ? p->splits : pick_splits(p->B, p->n_kv, p->max_pages * PIKV_PAGE_TOKENS);
+    const size_t need = q.splits > 1 ? (size_t)p->B * p->n_q * q.splits * (128 + 2) * sizeof(float) : 0;
+    PIKV_REQUIRE(need <= DA_STATIC_SCRATCH_BYTES, PIKV_ELIMIT,
+                 "decode_attn_static: %d streams x %d query heads x %d splits need %zu bytes of split scratch, the built-in "
+                 "array holds %zu; lower `splits` or use pikv_decode_attn_q8 with your own workspace",
+                 p->B, p->n_q, q.splits, need, DA_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    const int rc = decode_static_scratch_ptr(&scratch);
+    if (rc != PIKV_OK) return rc;
+    q.workspace = scratch;
+    q.workspace_bytes = DA_STATIC_SCRATCH_BYTES;
+    return pikv_decode_attn_q8(&q, stream);
+}
+
