@@ -207,12 +207,16 @@ def gpu_arm(args):
             fn()
         return graph, pikv_b200.launch_count() - n0
 
-    def timed(replay, n):
+    def timed(replay, n, hooks=None):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
+        if hooks:
+            hooks["begin"]()      # side streams start after the start event
         for i in range(n):
             replay(i)
+        if hooks:
+            hooks["end"]()        # and the stop event waits for them
         e1.record()
         barrier()
         return e0.elapsed_time(e1)
@@ -262,6 +266,7 @@ def gpu_arm(args):
         from pikv_b200 import distributed as pd
         step_fn, extra_cfg = pd.make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode=args.shard_mode)
         R = extra_cfg.pop("buffer_sets", 1)
+        hooks = extra_cfg.pop("hooks", None)
         for i in range(warmup):
             step_fn(i)
         # launched eagerly: capturing the step (NCCL all-gather + symmetric-memory barrier) in a CUDA
@@ -276,7 +281,7 @@ def gpu_arm(args):
         if rank == 0:
             sampler.start()
         n0 = pikv_b200.launch_count()
-        ms = timed(replay, steps)
+        ms = timed(replay, steps, hooks)
         launches = per_step * steps if per_step is not None else pikv_b200.launch_count() - n0
         e2e = extra_cfg.pop("e2e", None)
     else:

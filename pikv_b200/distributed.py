@@ -252,14 +252,33 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
     R = 2
     sets = [synth_inputs(T, H, E, kv, 1000 * rank + i, device=dev) for i in range(R)]
     outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(R)]
+    hooks = {"begin": lambda: None, "end": lambda: None}
     if mode == "peer":
-        shard = PeerShardedKVCache(E, cap, n_kv, dev)
-        how = "append kernel stores into the owner GPU's pages over NVLink (peer pointers)"
-        runs = [shard.prepare(sets[i][0], w2, b2, sets[i][1], sets[i][2], top_k=k, out=outs[i]) for i in range(R)]
+        # two steps in flight on two streams, each with its own cache instance (own pools, own barrier
+        # pads): the gate of one step overlaps the all-gather, the NVLink stores and the barrier of the
+        # previous one
+        lanes = 2
+        shards = [PeerShardedKVCache(E, cap, n_kv, dev) for _ in range(lanes)]
+        streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)]
+        how = "append kernel stores into the owner GPU's pages over NVLink (peer pointers); 2 steps in flight"
+        runs = [[shards[l].prepare(sets[i][0], w2, b2, sets[i][1], sets[i][2], top_k=k, out=outs[i]) for i in range(R)]
+                for l in range(lanes)]
 
         def step(i):
-            shard.reset()
-            runs[i % R]()
+            lane = i % lanes
+            with torch.cuda.stream(streams[lane]):
+                shards[lane].reset()
+                runs[lane][i % R]()
+
+        def begin():
+            for st in streams:
+                st.wait_stream(torch.cuda.current_stream())
+
+        def end():
+            for st in streams:
+                torch.cuda.current_stream().wait_stream(st)
+
+        hooks = {"begin": begin, "end": end}
     else:
         shard = ExpertShardedKVCache(E, cap, n_kv, dev, max_records=int(T * k * 1.5))
         how = "pack -> NCCL all_to_all -> unpack"
@@ -270,5 +289,5 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
             shard.route_append(act, w2, b2, K, V, top_k=k, out=outs[i % R])
 
     extra = {"parallelism": f"tokens data-parallel, {E} experts sharded {E // world} per GPU; {how}",
-             "buffer_sets": R}
+             "buffer_sets": R, "hooks": hooks}
     return step, extra
