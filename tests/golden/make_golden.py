@@ -297,6 +297,40 @@ def lowrank_fixtures(ref_single_c, ref_module_c, ref_cachec):
     save("cache_pyramid", keys=k, values=v, importance=imp, weights=sd(cc), ck=ck, cv=cv, nk=nk, nv=nv)
 
 
+def moe_fixture(reference):
+    """PiKVMoE (config 1: [8,128,256] fp32, 4 experts, top-2, caches 128..88) built after manual_seed(0),
+    two forwards, plain ring caches and H2O-scheduled caches.  Only slices of the [8,128,50257] logits
+    are kept.  core/single/distillation.py:9 imports itself, so the module is loaded with that line left
+    out (in memory; the reference tree is not touched)."""
+    import types
+    import core.single  # noqa: F401
+    path = os.path.join(reference, "core", "single", "distillation.py")
+    lines = open(path).read().split("\n")
+    mod = types.ModuleType("core.single.distillation")
+    mod.__package__, mod.__file__ = "core.single", path
+    sys.modules["core.single.distillation"] = mod
+    exec(compile("\n".join(l for i, l in enumerate(lines) if i != 8), path, "exec"), mod.__dict__)
+    from core.single.pikv_moe import PiKVMoE
+    from core.single.cache_scheduling import SchedulingPolicy
+    out = {}
+    for tag, kw in (("plain", {}), ("h2o", dict(use_cache_scheduling=True, cache_scheduling_policy=SchedulingPolicy.H2O))):
+        torch.manual_seed(0)
+        m = PiKVMoE(**kw)
+        m.eval()
+        g = torch.Generator().manual_seed(1)
+        with torch.no_grad():
+            for step in range(2):
+                x = torch.randn(8, 128, 256, generator=g)
+                logits = m(x)
+                out[f"{tag}/logits_head{step}"] = logits[:, :, :48].numpy().copy()
+                out[f"{tag}/logits_stride{step}"] = logits[:, ::16, ::997].numpy().copy()
+                out[f"{tag}/logits_absmax{step}"] = np.float32(logits.abs().max())
+        out[f"{tag}/cache_ptrs"] = m.cache_ptrs.numpy().copy()
+        out[f"{tag}/n_params"] = np.int64(sum(p.numel() for p in m.parameters()))
+        out[f"{tag}/param_sum"] = np.float64(sum(p.double().sum().item() for p in m.parameters()))
+    save("pikv_moe_c1", **out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -313,6 +347,8 @@ def main():
     h2o_fixtures(cache_scheduling)
     attention_fixture(pikv_attention)
     lowrank_fixtures(pikv_compression, m_compression, kv_cache_compression)
+    torch.set_num_threads(4)
+    moe_fixture(args.reference)
 
 
 if __name__ == "__main__":

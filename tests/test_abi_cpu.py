@@ -67,3 +67,19 @@ def test_operators_refuse_cpu_tensors(built_lib):
     r = pikv_b200.TopKBalancedRouter(32, 4)
     with pytest.raises(pikv_b200.PikvError):
         r(torch.randn(1, 4, 32))
+
+
+def test_pikv_moe_builds_with_the_reference_weights_for_a_seed():
+    """Same constructor order as core/single/pikv_moe.py: after manual_seed(0) the drop-in holds the
+    reference's parameters (count and sum recorded by the fixture generator).  No GPU involved."""
+    import numpy as np
+    import torch
+    from conftest import load_golden
+    from pikv_b200.moe import PiKVMoE
+    from pikv_b200.scheduling import SchedulingPolicy
+    g = load_golden("pikv_moe_c1")
+    for tag, kw in (("plain", {}), ("h2o", dict(use_cache_scheduling=True, cache_scheduling_policy=SchedulingPolicy.H2O))):
+        torch.manual_seed(0)
+        m = PiKVMoE(**kw)
+        assert sum(p.numel() for p in m.parameters()) == int(g[f"{tag}/n_params"])
+        assert abs(sum(p.double().sum().item() for p in m.parameters()) - float(g[f"{tag}/param_sum"])) < 1e-6
