@@ -237,8 +237,8 @@ def gpu_arm(args):
             caches[i].append(sets[i][1], sets[i][2], outs[i].topk_idx, outs[i].slot)
 
         def step(i):
-            gate(i)
-            append(i)
+            # one call: the gate kernel, then the append kernel that also finishes the slot scan
+            caches[i].route_append(sets[i][0], w2, b2, sets[i][1], sets[i][2], top_k=k, capacity=cap, out=outs[i])
 
         return dict(R=R, cap=cap, sets=sets, caches=caches, outs=outs, gate=gate, append=append, step=step)
 

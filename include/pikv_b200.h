@@ -161,6 +161,14 @@ typedef struct {
 
 int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t stream);
 
+/* Gate + append as one call: pikv_gate_fused followed by pikv_kv_append_quant with
+ * dst_seq = the gate's topk_idx and slot = the gate's slot (those two fields of `append` are
+ * ignored), same outputs.  For bf16 K/V and int8 symmetric codes the stand-alone slot
+ * finalisation is folded into the append kernel (every CTA rebuilds the prefix of the
+ * gate's per-chunk counters in shared memory), which saves a launch and a dependent kernel
+ * boundary; other combinations run the two entry points back to back. */
+int pikv_route_append(const pikv_gate_params* gate, const pikv_append_params* append, pikv_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Expert-sharded routed append: quantise and store straight into the page pools of
  * the GPU that owns each destination sequence, through peer-mapped pointers (plain

@@ -89,6 +89,7 @@ SIGNATURES = {
     "pikv_gate_error_state": (i32, []),
     "pikv_dispatch_scatter": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_kv_append_quant": (i32, [C.POINTER(AppendParams), vp]),
+    "pikv_route_append": (i32, [C.POINTER(GateParams), C.POINTER(AppendParams), vp]),
     "pikv_kv_append_sharded": (i32, [C.POINTER(AppendShardedParams), vp]),
     "pikv_shard_plan": (i32, [vp, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_cache_gather": (i32, [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),

@@ -6,6 +6,7 @@
 // 128-byte row of the destination page, so stores are whole lines even though the
 // destinations are scattered.  The group statistics are a 3-step xor shuffle.
 #include "quant_group.cuh"
+#include "gate_common.cuh"
 
 namespace pikv {
 
@@ -31,6 +32,16 @@ struct AppendDev {
     const int* slot_base;        // [num_seqs] added to the slot
     uint8_t* pcodes[2][8];       // [K|V][rank] peer-mapped code pools
     uint16_t* pscale[2][8];
+    // fused route + append: the gate left chunk-local ranks in `slot` and per-chunk counters behind
+    const int* g_cta_cnt;        // [G][E]
+    const int* g_cta_cnt_k;      // [G][k][E]
+    const float* g_cta_psum;     // [G][E]
+    const int* g_slot_base;      // [E] or null
+    int gG, gchunk, gE, gcap;
+    int* g_slot_out;             // [T][k] final slots
+    int* g_counts_k;
+    float* g_prob_sum;
+    int* g_new_len;
 };
 
 // One 8-lane group per (token, head) item: both the K and the V slice of that head.  The grid is
@@ -69,20 +80,36 @@ __device__ __forceinline__ void append_stage_route(const AppendDev& a, unsigned 
     }
 }
 
-template <typename TIn, int BITS, bool SYM, int TOPK, bool SHARDED>
-__device__ __forceinline__ void append_stage_load(const AppendDev& a, unsigned pair, unsigned total, int sub,
-                                                  AppendRoute<TOPK>& r, int (&page)[TOPK],
-                                                  typename GroupQuant<TIn, BITS, SYM>::Raw& k,
-                                                  typename GroupQuant<TIn, BITS, SYM>::Raw& v) {
+// K / V loads of an item: independent of the routing
+template <typename TIn, int BITS, bool SYM>
+__device__ __forceinline__ void append_stage_kv(const AppendDev& a, unsigned pair, unsigned total, int sub,
+                                                typename GroupQuant<TIn, BITS, SYM>::Raw& k,
+                                                typename GroupQuant<TIn, BITS, SYM>::Raw& v) {
+    unsigned t = 0, head = 0;
+    if (pair < total) append_split(a, pair, t, head);
+    const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
+    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.k) + off, k);
+    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.v) + off, v);
+}
+
+// final slot (MODE 1: + this rank's base on the owner; MODE 2: + exclusive prefix of the gate's
+// per-chunk counters, from shared memory) and the page-table load
+template <int TOPK, int MODE>
+__device__ __forceinline__ void append_stage_page(const AppendDev& a, unsigned pair, unsigned total, int sub,
+                                                  AppendRoute<TOPK>& r, int (&page)[TOPK], const int* base_s) {
     unsigned t = 0, head = 0;
     if (pair < total) append_split(a, pair, t, head);
 #pragma unroll
     for (int j = 0; j < TOPK; ++j) {
         page[j] = -1;
-        if (SHARDED && r.s[j] >= 0 && r.q[j] >= 0 && r.q[j] < a.num_seqs) {
-            // slot on the owner = this rank's base for the sequence + rank inside (this rank, sequence)
+        if (MODE == 1 && r.s[j] >= 0 && r.q[j] >= 0 && r.q[j] < a.num_seqs) {
             const int sf = r.s[j] + __ldg(a.slot_base + r.q[j]);
             r.s[j] = (a.capacity > 0 && sf >= a.capacity) ? -1 : sf;
+        }
+        if (MODE == 2 && r.s[j] >= 0 && r.q[j] >= 0 && r.q[j] < a.gE) {
+            const int sf = r.s[j] + base_s[(t / (unsigned)a.gchunk) * a.gE + r.q[j]];
+            r.s[j] = (a.gcap > 0 && sf >= a.gcap) ? -1 : sf;
+            if (head == 0 && sub == 0 && a.g_slot_out) a.g_slot_out[(size_t)t * a.top_k + j] = r.s[j];
         }
         if (r.s[j] >= 0) {
             if (r.q[j] < 0 || r.q[j] >= a.num_seqs || (r.s[j] / PT) >= a.max_pages) {
@@ -92,35 +119,83 @@ __device__ __forceinline__ void append_stage_load(const AppendDev& a, unsigned p
             }
         }
     }
-    const size_t off = ((size_t)t * a.n_kv + head) * D + sub * 16;
-    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.k) + off, k);
-    GroupQuant<TIn, BITS, SYM>::load(static_cast<const TIn*>(a.v) + off, v);
 }
 
-template <typename TIn, int BITS, bool SYM, int TOPK, bool SHARDED>
+// MODE 0: slots as given.  MODE 1: expert-sharded (peer pools, per-rank slot base).  MODE 2: fused with
+// the gate (chunk-local ranks + per-chunk counters -> final slots, totals by CTA 0).
+template <typename TIn, int BITS, bool SYM, int TOPK, int MODE>
 __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(AppendDev a) {
     constexpr int ROW_BYTES = D * BITS / 8;
+    constexpr bool SHARDED = MODE == 1;
     using GQ = GroupQuant<TIn, BITS, SYM>;
+    extern __shared__ int base_s[];                        // MODE 2: [G][E] first slot of every chunk
     const int sub = threadIdx.x & 7;                       // lane within the group
     const unsigned stride = gridDim.x * (unsigned)(APPEND_THREADS / 8);
     const unsigned total = (unsigned)a.T * (unsigned)a.n_kv;
     unsigned pair = (blockIdx.x * (unsigned)APPEND_THREADS + threadIdx.x) >> 3;
     // the four groups of a warp hold consecutive items: the loop condition is warp-uniform
     unsigned warp_first = (blockIdx.x * (unsigned)APPEND_THREADS + (threadIdx.x & ~31u)) >> 3;
-    if (warp_first >= total) return;
+    const bool any = warp_first < total;
 
     AppendRoute<TOPK> r0, r1, r2;
     int pg0[TOPK], pg1[TOPK];
     typename GQ::Raw k0, v0, k1, v1;
-    // prologue: item 0 fully fetched, item 1 routed
-    append_stage_route<TOPK>(a, pair, total, r0);
-    append_stage_route<TOPK>(a, pair + stride, total, r1);
-    append_stage_load<TIn, BITS, SYM, TOPK, SHARDED>(a, pair, total, sub, r0, pg0, k0, v0);
+    // prologue: the loads that need nothing from the gate go out first
+    if (any) {
+        append_stage_route<TOPK>(a, pair, total, r0);
+        append_stage_route<TOPK>(a, pair + stride, total, r1);
+        append_stage_kv<TIn, BITS, SYM>(a, pair, total, sub, k0, v0);
+    }
+    if (MODE == 2) {
+        // exclusive prefix over the gate's chunks, per expert: warp w scans experts w, w+8, ...
+        const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+        const int G = a.gG, E = a.gE;
+        for (int i = tid; i < G * E; i += APPEND_THREADS) base_s[i] = __ldg(a.g_cta_cnt + i);
+        __syncthreads();
+        for (int e = warp; e < E; e += APPEND_THREADS / 32) {
+            int carry = a.g_slot_base ? __ldg(a.g_slot_base + e) : 0;
+            const int start = carry;
+            for (int c0 = 0; c0 < G; c0 += 32) {
+                const int c = c0 + lane;
+                const int v = c < G ? base_s[c * E + e] : 0;
+                int inc = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int n = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += n;
+                }
+                if (c < G) base_s[c * E + e] = carry + inc - v;
+                carry += __shfl_sync(0xffffffffu, inc, 31);
+            }
+            if (blockIdx.x == 0 && lane == 0 && a.g_new_len)
+                a.g_new_len[e] = (a.gcap > 0 && carry > a.gcap) ? a.gcap : carry;
+            (void)start;
+        }
+        __syncthreads();
+        if (blockIdx.x == 0) {
+            // totals of the routing step, fixed summation order
+            for (int i = tid; i < a.top_k * E; i += APPEND_THREADS) {
+                int sum = 0;
+                const int j = i / E, e = i % E;
+                for (int c = 0; c < G; ++c) sum += __ldg(a.g_cta_cnt_k + ((size_t)c * a.top_k + j) * E + e);
+                if (a.g_counts_k) a.g_counts_k[i] = sum;
+            }
+            if (tid < E && a.g_prob_sum) {
+                float ps = 0.f;
+                for (int c = 0; c < G; ++c) ps += __ldg(a.g_cta_psum + (size_t)c * E + tid);
+                a.g_prob_sum[tid] = ps;
+            }
+        }
+    }
+    if (!any) return;
+    append_stage_page<TOPK, MODE>(a, pair, total, sub, r0, pg0, base_s);
 
     while (warp_first < total) {
         append_stage_route<TOPK>(a, pair + 2 * stride, total, r2);
-        if (warp_first + stride < total)
-            append_stage_load<TIn, BITS, SYM, TOPK, SHARDED>(a, pair + stride, total, sub, r1, pg1, k1, v1);
+        if (warp_first + stride < total) {
+            append_stage_kv<TIn, BITS, SYM>(a, pair + stride, total, sub, k1, v1);
+            append_stage_page<TOPK, MODE>(a, pair + stride, total, sub, r1, pg1, base_s);
+        }
 
         QParams kq, vq;
         uint32_t kw[4], vw[4];
@@ -231,6 +306,14 @@ __global__ void cache_gather_kernel(const int* seq, const int* pos, int n, const
     }
 }
 
+static void append_clear_gate(AppendDev& a) {
+    a.g_cta_cnt = a.g_cta_cnt_k = a.g_slot_base = nullptr;
+    a.g_cta_psum = nullptr;
+    a.gG = a.gchunk = a.gE = a.gcap = 0;
+    a.g_slot_out = a.g_counts_k = a.g_new_len = nullptr;
+    a.g_prob_sum = nullptr;
+}
+
 template <typename TIn>
 static int launch_append(const AppendDev& a, int bits, int symmetric, cudaStream_t st) {
     const long long lanes = (long long)a.T * a.n_kv * 8;
@@ -239,10 +322,10 @@ static int launch_append(const AppendDev& a, int bits, int symmetric, cudaStream
     const int grid = (int)(want < cap_ctas ? want : cap_ctas);
 #define PIKV_APPEND_LAUNCH(BITS, SYM)                                                                   \
     do {                                                                                                \
-        if (a.top_k <= 1) kv_append_quant_kernel<TIn, BITS, SYM, 1, false><<<grid, APPEND_THREADS, 0, st>>>(a);      \
-        else if (a.top_k <= 2) kv_append_quant_kernel<TIn, BITS, SYM, 2, false><<<grid, APPEND_THREADS, 0, st>>>(a); \
-        else if (a.top_k <= 4) kv_append_quant_kernel<TIn, BITS, SYM, 4, false><<<grid, APPEND_THREADS, 0, st>>>(a); \
-        else kv_append_quant_kernel<TIn, BITS, SYM, 8, false><<<grid, APPEND_THREADS, 0, st>>>(a);                   \
+        if (a.top_k <= 1) kv_append_quant_kernel<TIn, BITS, SYM, 1, 0><<<grid, APPEND_THREADS, 0, st>>>(a);      \
+        else if (a.top_k <= 2) kv_append_quant_kernel<TIn, BITS, SYM, 2, 0><<<grid, APPEND_THREADS, 0, st>>>(a); \
+        else if (a.top_k <= 4) kv_append_quant_kernel<TIn, BITS, SYM, 4, 0><<<grid, APPEND_THREADS, 0, st>>>(a); \
+        else kv_append_quant_kernel<TIn, BITS, SYM, 8, 0><<<grid, APPEND_THREADS, 0, st>>>(a);                   \
     } while (0)
     if (bits == 8 && symmetric) PIKV_APPEND_LAUNCH(8, true);
     else if (bits == 8) PIKV_APPEND_LAUNCH(8, false);
@@ -283,9 +366,71 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     a.status = p->status;
     a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr;
     for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
+    append_clear_gate(a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (p->dtype == PIKV_BF16) return launch_append<__nv_bfloat16>(a, p->bits, p->symmetric, st);
     return launch_append<float>(a, p->bits, p->symmetric, st);
+}
+
+// ---- fused route + append ---------------------------------------------------------------------------
+// Gate kernel, then the append kernel finishes the gate's slot scan itself: every append CTA rebuilds the
+// exclusive prefix of the per-chunk counters in shared memory while its first K/V loads are in flight,
+// adds it to the chunk-local ranks, writes the final slots back and stores the rows.  One launch and one
+// dependent kernel boundary less than pikv_gate_fused + pikv_kv_append_quant, identical results.
+extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_params* ap, pikv_stream_t stream) {
+    PIKV_REQUIRE(gp != nullptr && ap != nullptr, PIKV_EINVAL, "route_append: null params");
+    PIKV_REQUIRE(gp->slot != nullptr && gp->topk_idx != nullptr, PIKV_EINVAL, "route_append: the gate's topk_idx and slot outputs are required");
+    PIKV_REQUIRE(ap->T == gp->T && ap->top_k == gp->top_k && ap->num_seqs == gp->E, PIKV_EINVAL,
+                 "route_append: gate and append disagree on T, top_k or the number of sequences");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    pikv_append_params plain = *ap;
+    plain.dst_seq = gp->topk_idx;
+    plain.slot = gp->slot;
+    GateDev g;
+    const bool fusable = ap->dtype == PIKV_BF16 && ap->bits == 8 && ap->symmetric;
+    if (!fusable) {
+        const int rc = gate_run(gp, st, true, nullptr);
+        return rc != PIKV_OK ? rc : pikv_kv_append_quant(&plain, stream);
+    }
+    int rc = gate_run(gp, st, false, &g);
+    if (rc != PIKV_OK) return rc;
+    const size_t smem = (size_t)g.G * g.E * sizeof(int);
+    if (smem > 40 * 1024) {
+        // too many chunks for the shared-memory prefix table: finish the scan with the stand-alone kernel
+        rc = gate_run(gp, st, true, nullptr);
+        return rc != PIKV_OK ? rc : pikv_kv_append_quant(&plain, stream);
+    }
+    const pikv_append_params* p = &plain;
+    PIKV_REQUIRE(p->T > 0 && p->n_kv > 0 && p->top_k > 0 && p->top_k <= APPEND_MAX_K, PIKV_EINVAL, "route_append: bad sizes");
+    PIKV_REQUIRE(p->k && p->v && p->page_table && p->k_codes && p->v_codes && p->k_scale && p->v_scale, PIKV_EINVAL,
+                 "route_append: null pointer");
+    PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28) && (long long)p->num_pages * p->n_kv * PT < (1ll << 31), PIKV_ELIMIT,
+                 "route_append: problem too large for one call");
+    AppendDev a;
+    a.k = p->k; a.v = p->v; a.T = p->T; a.n_kv = p->n_kv; a.top_k = p->top_k;
+    a.log2_nkv = -1;
+    for (int b = 0; b < 16; ++b)
+        if ((1 << b) == p->n_kv) a.log2_nkv = b;
+    a.dst_seq = p->dst_seq; a.slot = p->slot; a.page_table = p->page_table;
+    a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
+    a.codes[0] = static_cast<uint8_t*>(p->k_codes); a.codes[1] = static_cast<uint8_t*>(p->v_codes);
+    a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
+    a.zp[0] = a.zp[1] = nullptr;
+    a.status = p->status;
+    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr;
+    for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
+    a.g_cta_cnt = g.cta_cnt; a.g_cta_cnt_k = g.cta_cnt_k; a.g_cta_psum = g.cta_psum; a.g_slot_base = g.slot_base;
+    a.gG = g.G; a.gchunk = g.chunk; a.gE = g.E; a.gcap = g.capacity;
+    a.g_slot_out = g.slot; a.g_counts_k = g.counts_k; a.g_prob_sum = g.prob_sum; a.g_new_len = g.new_len;
+    const long long lanes = (long long)a.T * a.n_kv * 8;
+    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 3;
+    const int grid = (int)(want < cap_ctas ? want : cap_ctas);
+    if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, 2><<<grid, APPEND_THREADS, smem, st>>>(a);
+    else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, 2><<<grid, APPEND_THREADS, smem, st>>>(a);
+    else if (a.top_k <= 4) kv_append_quant_kernel<__nv_bfloat16, 8, true, 4, 2><<<grid, APPEND_THREADS, smem, st>>>(a);
+    else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, 2><<<grid, APPEND_THREADS, smem, st>>>(a);
+    count_launch(1);
+    return check_launch("kv_append_quant_kernel (fused with the gate)");
 }
 
 // ---- expert-sharded append: plan + launch -----------------------------------------------------------
@@ -348,14 +493,15 @@ extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv
         a.pscale[0][r] = on ? static_cast<uint16_t*>(sp->peer_k_scale[r]) : nullptr;
         a.pscale[1][r] = on ? static_cast<uint16_t*>(sp->peer_v_scale[r]) : nullptr;
     }
+    append_clear_gate(a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const long long lanes = (long long)a.T * a.n_kv * 8;
     long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 3;
     const int grid = (int)(want < cap_ctas ? want : cap_ctas);
-    if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, true><<<grid, APPEND_THREADS, 0, st>>>(a);
-    else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, true><<<grid, APPEND_THREADS, 0, st>>>(a);
-    else if (a.top_k <= 4) kv_append_quant_kernel<__nv_bfloat16, 8, true, 4, true><<<grid, APPEND_THREADS, 0, st>>>(a);
-    else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, true><<<grid, APPEND_THREADS, 0, st>>>(a);
+    if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, 1><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, 1><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else if (a.top_k <= 4) kv_append_quant_kernel<__nv_bfloat16, 8, true, 4, 1><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, 1><<<grid, APPEND_THREADS, 0, st>>>(a);
     count_launch(1);
     return check_launch("kv_append_quant_kernel (sharded)");
 }

@@ -337,7 +337,11 @@ extern "C" size_t pikv_gate_workspace_bytes(int32_t T, int32_t E, int32_t top_k)
     return (size_t)GATE_MAX_CTAS * (size_t)E * (size_t)(top_k + 2) * 4;
 }
 
-extern "C" int pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream) {
+namespace pikv {
+// Runs the gate kernel; with finalize = false the slot output holds ranks local to each CTA's chunk
+// and the per-CTA counters stay in the workspace (*out describes them) for a consumer that finishes
+// the scan itself.
+int gate_run(const pikv_gate_params* p, cudaStream_t st, bool finalize, GateDev* out) {
     PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "gate: null params");
     PIKV_REQUIRE(p->T > 0 && p->E > 0 && p->top_k > 0, PIKV_EINVAL, "gate: T, E, top_k must be positive");
     PIKV_REQUIRE(p->E <= GATE_MAX_E, PIKV_ELIMIT, "gate: E=%d exceeds %d", p->E, GATE_MAX_E);
@@ -363,7 +367,6 @@ extern "C" int pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream) 
     g.cta_cnt = ws;
     g.cta_cnt_k = ws + (size_t)GATE_MAX_CTAS * g.E;
     g.cta_psum = reinterpret_cast<float*>(ws + (size_t)GATE_MAX_CTAS * g.E * (g.k + 1));
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     int rc;
     const int E = g.E;
     const char* force_simt = getenv("PIKV_GATE_SIMT");   // testing aid: run bf16 through the SIMT kernel too
@@ -389,9 +392,19 @@ extern "C" int pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream) 
         else rc = launch_logits<64>(g, st);
     }
     if (rc != PIKV_OK) return rc;
+    if (out) *out = g;
+    if (!finalize) {
+        count_launch(1);
+        return PIKV_OK;
+    }
     gate_finalize_kernel<<<g.G, GATE_THREADS, 0, st>>>(g);
     count_launch(2);
     return check_launch("gate_finalize_kernel");
+}
+}  // namespace pikv
+
+extern "C" int pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream) {
+    return gate_run(p, static_cast<cudaStream_t>(stream), true, nullptr);
 }
 
 extern "C" int pikv_dispatch_scatter(const int32_t* topk_idx, const float* topk_w, const int32_t* slot,

@@ -112,6 +112,9 @@ __device__ __forceinline__ void token_tail(float (&l)[EP], const GateDev& g, int
     }
 }
 
+// the gate without (finalize = false) or with its slot finalisation; see gate.cu
+int gate_run(const pikv_gate_params* p, cudaStream_t st, bool finalize, GateDev* out);
+
 // tensor-core path (gate_tc.cu): bf16 activations through TMA + tcgen05
 bool gate_tc_supported(const GateDev& g, int dtype);
 int gate_tc_launch(GateDev& g, cudaStream_t st);   // sets g.chunk and g.G for the finalize kernel

@@ -84,6 +84,51 @@ class PagedKVCache(torch.nn.Module):
         p.status = _p(self.status)
         check(lib().pikv_kv_append_quant(C.byref(p), _stream()), "pikv_kv_append_quant")
 
+    def route_append(self, act: torch.Tensor, w2: torch.Tensor, b2: Optional[torch.Tensor], k: torch.Tensor,
+                     v: torch.Tensor, top_k: int = 2, capacity: Optional[int] = None,
+                     out: Optional["ops.GateResult"] = None, slot_base: Optional[torch.Tensor] = None,
+                     want_probs: bool = True):
+        """Gate the tokens and append their quantised K/V rows in one call (pikv_route_append): the
+        same results as ops.gate_fused followed by append(), with the slot finalisation folded into the
+        append kernel.  Sequences are the experts.  Returns the gate result."""
+        from . import ops
+        act = _req(act, "act")
+        w2 = _req(w2, "w2", act.dtype)
+        k = _req(k, "k")
+        v = _req(v, "v", k.dtype)
+        T, H = act.shape
+        E = w2.shape[0]
+        if E != self.num_seqs:
+            raise PikvError(f"the cache has {self.num_seqs} sequences, the gate {E} experts")
+        cap = self.capacity if capacity is None else capacity
+        dev = act.device
+        if out is None:
+            f32, i32 = dict(dtype=torch.float32, device=dev), dict(dtype=torch.int32, device=dev)
+            out = ops.GateResult(probs=torch.empty(T, E, **f32) if want_probs else None,
+                                 topk_idx=torch.empty(T, top_k, **i32), topk_w=torch.empty(T, top_k, **f32),
+                                 slot=torch.empty(T, top_k, **i32), counts_k=torch.empty(top_k, E, **i32),
+                                 prob_sum=torch.empty(E, **f32), new_len=torch.empty(E, **i32))
+        ws = _workspace(dev, lib().pikv_gate_workspace_bytes(T, E, top_k), "gate")
+        b2f = None if b2 is None else _req(b2.to(torch.float32), "b2", torch.float32)
+        gp = _lib.GateParams()
+        gp.act, gp.w2, gp.b2, gp.dtype = _p(act), _p(w2), _p(b2f), _dtype_code(act, "act")
+        gp.T, gp.H, gp.E, gp.top_k, gp.temperature, gp.capacity = T, H, E, top_k, 1.0, int(cap)
+        if slot_base is not None:
+            slot_base = _req(slot_base, "slot_base", torch.int32)
+        gp.slot_base = _p(slot_base)
+        gp.probs, gp.topk_idx, gp.topk_w, gp.slot = _p(out.probs), _p(out.topk_idx), _p(out.topk_w), _p(out.slot)
+        gp.counts_k, gp.prob_sum, gp.new_len = _p(out.counts_k), _p(out.prob_sum), _p(out.new_len)
+        gp.workspace, gp.workspace_bytes = _p(ws), ws.numel()
+        ap = AppendParams()
+        ap.k, ap.v, ap.dtype, ap.T, ap.n_kv, ap.top_k = _p(k), _p(v), _dtype_code(k, "k"), T, self.n_kv, top_k
+        ap.page_table = _p(self.page_table)
+        ap.num_seqs, ap.max_pages, ap.num_pages = self.num_seqs, self.max_pages, self.num_pages
+        ap.bits, ap.symmetric = self.bits, int(self.symmetric)
+        ap.k_codes, ap.v_codes, ap.k_scale, ap.v_scale = _p(self.k_codes), _p(self.v_codes), _p(self.k_scale), _p(self.v_scale)
+        ap.k_zp, ap.v_zp, ap.status = _p(self.k_zp), _p(self.v_zp), _p(self.status)
+        check(lib().pikv_route_append(C.byref(gp), C.byref(ap), _stream()), "pikv_route_append")
+        return out
+
     # -- reads ---------------------------------------------------------------------
     def gather(self, seq: torch.Tensor, pos: torch.Tensor, which: str = "k", codes: bool = False):
         """Dequantised rows [n, n_kv*128] fp32 (and int8 codes when codes=True) in logical order."""

@@ -450,3 +450,31 @@ def test_sharded_cache_single_rank_equals_direct_append(dev):
     for name in ("k_codes", "v_codes", "k_scale", "v_scale"):
         assert torch.equal(getattr(direct, name), getattr(shard.cache, name)), name
     assert torch.equal(shard.cache.length, g.new_len)
+
+
+@pytest.mark.parametrize("T,H,E,k,n_kv,cap", [(16384, 4096, 8, 2, 8, 6144), (3000, 512, 8, 2, 2, 700), (129, 256, 64, 4, 1, 40),
+                                              (70000, 128, 16, 1, 1, 0)])
+def test_fused_route_append_equals_gate_then_append(dev, T, H, E, k, n_kv, cap):
+    """pikv_route_append (slot finalisation folded into the append kernel) against the two separate
+    entry points: slots, counts, lengths, probabilities and every byte of the cache."""
+    import pikv_b200
+    from pikv_b200 import ops
+    torch.manual_seed(T)
+    act = torch.relu(torch.randn(T, H, device=dev)).bfloat16()
+    w2 = (torch.randn(E, H, device=dev) / H ** 0.5).bfloat16()
+    b2 = torch.randn(E, device=dev) * 0.1
+    K, V = outlier_kv(T, n_kv * 128, 5).to(dev), outlier_kv(T, n_kv * 128, 6).to(dev)
+    size = cap if cap > 0 else T
+    base = torch.randint(0, 5, (E,), dtype=torch.int32, device=dev)
+    g = ops.gate_fused(act, w2, b2, top_k=k, capacity=cap, slot_base=base)
+    two = pikv_b200.PagedKVCache(E, size + 8, n_kv, device=dev)
+    two.append(K, V, g.topk_idx, g.slot)
+    one = pikv_b200.PagedKVCache(E, size + 8, n_kv, device=dev)
+    f = one.route_append(act, w2, b2, K, V, top_k=k, capacity=cap, slot_base=base)
+    one.check_status()
+    assert torch.equal(f.topk_idx, g.topk_idx) and torch.equal(f.slot, g.slot)
+    assert torch.equal(f.counts_k, g.counts_k) and torch.equal(f.new_len, g.new_len)
+    assert torch.equal(f.probs, g.probs) and torch.equal(f.topk_w, g.topk_w)
+    assert torch.allclose(f.prob_sum, g.prob_sum, rtol=1e-5)
+    for name in ("k_codes", "v_codes", "k_scale", "v_scale"):
+        assert torch.equal(getattr(one, name), getattr(two, name)), name
