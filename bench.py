@@ -207,6 +207,53 @@ def gpu_arm(args):
             fn()
         return graph, pikv_b200.launch_count() - n0
 
+    def capture_pipelined(w, n):
+        """One graph of n consecutive steps of the software-pipelined schedule, starting at buffer set 0:
+        the gates' scoring kernels run back to back on a side stream, their slot finalisations on a second
+        one, the appends on the capture stream; append(i) waits for gate(i), gate(i) for the append that
+        last used its buffer set.  gate(0) ran before the graph (the previous
+        replay issued it), gate(n) is issued for the next replay, so a replay holds n gates and n appends
+        and one kernel's ramp-up and tail fill with the other's traffic.  n must be a multiple of the
+        number of buffer sets, or the last window of the run."""
+        R = w["R"]
+        side, fin = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        for i in range(R):
+            w["score"](i)                # allocates each result's own gate workspace before the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        n0 = pikv_b200.launch_count()
+        with torch.cuda.graph(graph):
+            cur = torch.cuda.current_stream()
+            side.wait_stream(cur)
+            appended = []
+            for i in range(n):
+                if i + 1 - R >= 0:
+                    side.wait_event(appended[i + 1 - R])       # buffer set (i+1) % R is free again
+                with torch.cuda.stream(side):
+                    w["score"]((i + 1) % R)                    # pikv_gate_fused, phase 1: the scoring kernel
+                    scored = torch.cuda.Event()
+                    scored.record(side)
+                fin.wait_event(scored)
+                with torch.cuda.stream(fin):
+                    w["slots"]((i + 1) % R)                    # phase 2: the short slot finalisation
+                    gated = torch.cuda.Event()
+                    gated.record(fin)
+                w["pappend"](i % R)                            # pikv_kv_append_quant
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                appended.append(ev)
+                cur.wait_event(gated)                          # append(i+1) needs gate(i+1)
+            cur.wait_stream(side)
+            cur.wait_stream(fin)
+        return graph, pikv_b200.launch_count() - n0
+
+    def run_pipelined(w, window, tail):
+        """replay(i) for timed(): step i is the first of a window -> replay that window's graph."""
+        def replay(i, total):
+            if i % window[2] == 0:
+                (window if total - i >= window[2] else tail)[0].replay()
+        return replay
+
     def timed(replay, n, hooks=None):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -240,7 +287,19 @@ def gpu_arm(args):
             # one call: the gate kernel, then the append kernel that also finishes the slot scan
             caches[i].route_append(sets[i][0], w2, b2, sets[i][1], sets[i][2], top_k=k, capacity=cap, out=outs[i])
 
-        return dict(R=R, cap=cap, sets=sets, caches=caches, outs=outs, gate=gate, append=append, step=step)
+        def score(i):
+            return ops.gate_fused(sets[i][0], w2, b2, top_k=k, capacity=cap, out=pouts[i], phase=1)
+
+        def slots(i):
+            return ops.gate_fused(sets[i][0], w2, b2, top_k=k, capacity=cap, out=pouts[i], phase=2)
+
+        def pappend(i):
+            caches[i].append(sets[i][1], sets[i][2], pouts[i].topk_idx, pouts[i].slot)
+
+        # results of the pipelined schedule: each owns its gate workspace (several batches are in flight)
+        pouts = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=cap, want_probs=True) for _ in range(R)]
+        return dict(R=R, cap=cap, sets=sets, caches=caches, outs=outs, gate=gate, append=append, step=step,
+                    score=score, slots=slots, pappend=pappend)
 
     def kernel_times(w, n):
         """Average device time of the gate and of the append, each replayed as its own graph, with events
@@ -287,15 +346,32 @@ def gpu_arm(args):
     else:
         wl = single_gpu_workload(T)
         R = wl["R"]
+        # serial schedule: one stream, gate then append (pikv_route_append), one graph per step
         graphs = [capture(lambda i=i: wl["step"](i)) for i in range(R)]
         for i in range(warmup):
             graphs[i % R][0].replay()
+        serial_ms = timed(lambda i: graphs[i % R][0].replay(), steps) / steps
         sampler = ClockSampler(local)
-        sampler.start()
-        ms = timed(lambda i: graphs[i % R][0].replay(), steps)
-        launches = graphs[0][1] * steps
-        extra_cfg = {"parallelism": "single"}
-        launch_mode = "one CUDA graph replay per step (captured C-ABI calls)"
+        if args.schedule == "pipelined":
+            # batch i+1 is gated while batch i is appended; K replays = K gates + K appends
+            W = 2 * R
+            window = capture_pipelined(wl, W) + (W,)
+            tail = capture_pipelined(wl, steps % W) + (steps % W,) if steps % W else window
+            wl["score"](0), wl["slots"](0)
+            for i in range(max(1, warmup // W)):
+                window[0].replay()
+            sampler.start()
+            replay = run_pipelined(wl, window, tail)
+            ms = timed(lambda i: replay(i, steps), steps)
+            launches = window[1] * (steps // W) + (tail[1] if steps % W else 0)
+            launch_mode = (f"CUDA graphs of {W} steps (captured C-ABI calls): gates on one stream, appends on another, "
+                           "append(i) after gate(i)")
+        else:
+            sampler.start()
+            ms = timed(lambda i: graphs[i % R][0].replay(), steps)
+            launches = graphs[0][1] * steps
+            launch_mode = "one CUDA graph replay per step (captured C-ABI calls, one stream)"
+        extra_cfg = {"parallelism": "single", "schedule": args.schedule}
     t = torch.tensor([ms], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -346,17 +422,28 @@ def gpu_arm(args):
             c.check_status()
         assert pikv_b200.lib().pikv_gate_error_state() == 0, "a bounded wait in the gate kernel ran out"
         del wl, graphs, h_sets, d_in, caches, outs
+        window = tail = None
         torch.cuda.empty_cache()
 
         if not args.no_large:
             # the same step at 8x the tokens: launch overhead and tail effects no longer matter
             T8 = 8 * T
             w8 = single_gpu_workload(T8)
-            g8 = [capture(lambda i=i: w8["step"](i))[0] for i in range(w8["R"])]
-            for i in range(3):
-                g8[i % w8["R"]].replay()
             steps8 = max(3, steps // 4)
-            ms8 = timed(lambda i: g8[i % w8["R"]].replay(), steps8)
+            if args.schedule == "pipelined":
+                W8 = w8["R"]
+                steps8 = -(-steps8 // W8) * W8
+                win8 = capture_pipelined(w8, W8) + (W8,)
+                w8["score"](0), w8["slots"](0)
+                win8[0].replay()
+                replay8 = run_pipelined(w8, win8, win8)
+                ms8 = timed(lambda i: replay8(i, steps8), steps8)
+                g8 = win8
+            else:
+                g8 = [capture(lambda i=i: w8["step"](i))[0] for i in range(w8["R"])]
+                for i in range(3):
+                    g8[i % w8["R"]].replay()
+                ms8 = timed(lambda i: g8[i % w8["R"]].replay(), steps8)
             gate8, app8 = kernel_times(w8, steps8)
             large = {"tokens": T8, "value": T8 * steps8 / (ms8 * 1e-3), "unit": UNIT, "ms_per_step": ms8 / steps8,
                      "gate_frac": GATE_BYTES_PER_TOKEN * T8 / (gate8 * 1e-3) / 1e9 / peak,
@@ -379,6 +466,9 @@ def gpu_arm(args):
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "launch": launch_mode, "roofline": roof,
             "cpu_baseline": cpu, "large_batch": large,
         }
+        if world == 1:
+            line["serial_schedule"] = {"ms_per_step": serial_ms, "value": T / (serial_ms * 1e-3), "unit": UNIT,
+                                       "launch": "pikv_route_append on one stream, one graph per step"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -472,6 +562,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the host-side port timing (profiling runs)")
+    ap.add_argument("--schedule", choices=("pipelined", "serial"), default="pipelined",
+                    help="single GPU: gate of batch i+1 overlapped with the append of batch i, or strictly serial")
     ap.add_argument("--no-large", action="store_true", help="skip the 8x-token secondary measurement")
     ap.add_argument("--workload", default="append", choices=["append", "decode", "lowrank"],
                     help="append = the headline route+quantise+append step; the others print lines for the other kernels")

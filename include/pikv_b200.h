@@ -103,7 +103,19 @@ typedef struct {
     int32_t* new_len;          /* [E] min(slot_base + count, capacity)          */
     void*    workspace;        /* pikv_gate_workspace_bytes(T,E,top_k)          */
     size_t   workspace_bytes;
+    int32_t  phase;            /* PIKV_GATE_WHOLE (0), _SCORE or _SLOTS, see below */
 } pikv_gate_params;
+
+/* The gate is two kernels: scoring (logits, softmax, top-k, ranks local to each CTA's chunk of
+ * tokens, per-chunk counters) and the slot finalisation (prefix over the chunks -> slot,
+ * counts_k, prob_sum, new_len).  phase = PIKV_GATE_SCORE launches only the first and leaves
+ * slot holding chunk-local ranks; PIKV_GATE_SLOTS, called later with the same parameters and
+ * the same workspace (the caller orders it after the first: same stream or an event), only
+ * the second.  For callers that keep the scoring kernels of consecutive batches back to back
+ * on one stream and run the short finalisation beside them on another. */
+#define PIKV_GATE_WHOLE 0
+#define PIKV_GATE_SCORE 1
+#define PIKV_GATE_SLOTS 2
 
 size_t pikv_gate_workspace_bytes(int32_t T, int32_t E, int32_t top_k);
 int    pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream);

@@ -33,7 +33,7 @@ class GateParams(C.Structure):
         ("expert_mask", vp), ("mask_mode", i32), ("correction", vp),
         ("temperature", f32), ("renorm_eps", f32), ("capacity", i32), ("slot_base", vp),
         ("probs", vp), ("topk_idx", vp), ("topk_w", vp), ("slot", vp), ("counts_k", vp),
-        ("prob_sum", vp), ("new_len", vp), ("workspace", vp), ("workspace_bytes", sz),
+        ("prob_sum", vp), ("new_len", vp), ("workspace", vp), ("workspace_bytes", sz), ("phase", i32),
     ]
 
 

@@ -124,7 +124,7 @@ __device__ __forceinline__ void append_stage_page(const AppendDev& a, unsigned p
 // MODE 0: slots as given.  MODE 1: expert-sharded (peer pools, per-rank slot base).  MODE 2: fused with
 // the gate (chunk-local ranks + per-chunk counters -> final slots, totals by CTA 0).
 template <typename TIn, int BITS, bool SYM, int TOPK, int MODE>
-__global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(AppendDev a) {
+__device__ __forceinline__ void kv_append_body(const AppendDev& a) {
     constexpr int ROW_BYTES = D * BITS / 8;
     constexpr bool SHARDED = MODE == 1;
     using GQ = GroupQuant<TIn, BITS, SYM>;
@@ -142,9 +142,9 @@ __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(Appe
     typename GQ::Raw k0, v0, k1, v1;
     // prologue: the loads that need nothing from the gate go out first
     if (any) {
+        append_stage_kv<TIn, BITS, SYM>(a, pair, total, sub, k0, v0);
         append_stage_route<TOPK>(a, pair, total, r0);
         append_stage_route<TOPK>(a, pair + stride, total, r1);
-        append_stage_kv<TIn, BITS, SYM>(a, pair, total, sub, k0, v0);
     }
     if (MODE == 2) {
         // exclusive prefix over the gate's chunks, per expert: warp w scans experts w, w+8, ...
@@ -154,7 +154,6 @@ __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(Appe
         __syncthreads();
         for (int e = warp; e < E; e += APPEND_THREADS / 32) {
             int carry = a.g_slot_base ? __ldg(a.g_slot_base + e) : 0;
-            const int start = carry;
             for (int c0 = 0; c0 < G; c0 += 32) {
                 const int c = c0 + lane;
                 const int v = c < G ? base_s[c * E + e] : 0;
@@ -169,21 +168,39 @@ __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(Appe
             }
             if (blockIdx.x == 0 && lane == 0 && a.g_new_len)
                 a.g_new_len[e] = (a.gcap > 0 && carry > a.gcap) ? a.gcap : carry;
-            (void)start;
         }
         __syncthreads();
-        if (blockIdx.x == 0) {
-            // totals of the routing step, fixed summation order
-            for (int i = tid; i < a.top_k * E; i += APPEND_THREADS) {
-                int sum = 0;
-                const int j = i / E, e = i % E;
-                for (int c = 0; c < G; ++c) sum += __ldg(a.g_cta_cnt_k + ((size_t)c * a.top_k + j) * E + e);
-                if (a.g_counts_k) a.g_counts_k[i] = sum;
+        // totals of the routing step: one (column, expert) count or one expert's probability sum per CTA,
+        // every thread a fixed subset of the chunks and a fixed reduction tree (run-to-run identical bits)
+        __shared__ float tot_f[APPEND_THREADS / 32];
+        __shared__ int tot_i[APPEND_THREADS / 32];
+        const int n_cnt = a.top_k * E;
+        for (int item = blockIdx.x; item < n_cnt + E; item += gridDim.x) {
+            int si = 0;
+            float sf = 0.f;
+            if (item < n_cnt) {
+                const int j = item / E, e = item % E;
+                for (int c = tid; c < G; c += APPEND_THREADS) si += __ldg(a.g_cta_cnt_k + ((size_t)c * a.top_k + j) * E + e);
+            } else {
+                for (int c = tid; c < G; c += APPEND_THREADS) sf += __ldg(a.g_cta_psum + (size_t)c * E + (item - n_cnt));
             }
-            if (tid < E && a.g_prob_sum) {
-                float ps = 0.f;
-                for (int c = 0; c < G; ++c) ps += __ldg(a.g_cta_psum + (size_t)c * E + tid);
-                a.g_prob_sum[tid] = ps;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                si += __shfl_xor_sync(0xffffffffu, si, o);
+                sf += __shfl_xor_sync(0xffffffffu, sf, o);
+            }
+            __syncthreads();
+            if (lane == 0) tot_i[warp] = si, tot_f[warp] = sf;
+            __syncthreads();
+            if (tid == 0) {
+                int ti = 0;
+                float tf = 0.f;
+                for (int w = 0; w < APPEND_THREADS / 32; ++w) ti += tot_i[w], tf += tot_f[w];
+                if (item < n_cnt) {
+                    if (a.g_counts_k) a.g_counts_k[item] = ti;
+                } else if (a.g_prob_sum) {
+                    a.g_prob_sum[item - n_cnt] = tf;
+                }
             }
         }
     }
@@ -253,6 +270,11 @@ __global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(Appe
         pair += stride;
         warp_first += stride;
     }
+}
+
+template <typename TIn, int BITS, bool SYM, int TOPK, int MODE>
+__global__ void __launch_bounds__(APPEND_THREADS, 3) kv_append_quant_kernel(AppendDev a) {
+    kv_append_body<TIn, BITS, SYM, TOPK, MODE>(a);
 }
 
 // ---- logical read-back ----------------------------------------------------------------
@@ -375,31 +397,41 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
 // ---- fused route + append ---------------------------------------------------------------------------
 // Gate kernel, then the append kernel finishes the gate's slot scan itself: every append CTA rebuilds the
 // exclusive prefix of the per-chunk counters in shared memory while its first K/V loads are in flight,
-// adds it to the chunk-local ranks, writes the final slots back and stores the rows.  One launch and one
-// dependent kernel boundary less than pikv_gate_fused + pikv_kv_append_quant, identical results.
-extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_params* ap, pikv_stream_t stream) {
+// adds it to the chunk-local ranks (kept in the gate's workspace), writes the final slots to the gate's slot
+// output and stores the rows.  One launch and one dependent kernel boundary less than pikv_gate_fused +
+// pikv_kv_append_quant, identical results.
+static bool route_fusable(const pikv_gate_params* gp, const pikv_append_params* ap) {
+    if (!(ap->dtype == PIKV_BF16 && ap->bits == 8 && ap->symmetric)) return false;
+    GateDev g;
+    if (gate_run(gp, nullptr, GATE_RANKS_TO_WS, &g) != PIKV_OK) return false;   // the gate launch reports the error
+    return (size_t)g.G * g.E * sizeof(int) <= 40 * 1024;                                // prefix table in shared memory
+}
+
+static int route_check(const pikv_gate_params* gp, const pikv_append_params* ap, pikv_append_params* plain) {
     PIKV_REQUIRE(gp != nullptr && ap != nullptr, PIKV_EINVAL, "route_append: null params");
+    PIKV_REQUIRE(gp->phase == PIKV_GATE_WHOLE, PIKV_EINVAL, "route_append: the gate's phase must be PIKV_GATE_WHOLE");
     PIKV_REQUIRE(gp->slot != nullptr && gp->topk_idx != nullptr, PIKV_EINVAL, "route_append: the gate's topk_idx and slot outputs are required");
     PIKV_REQUIRE(ap->T == gp->T && ap->top_k == gp->top_k && ap->num_seqs == gp->E, PIKV_EINVAL,
                  "route_append: gate and append disagree on T, top_k or the number of sequences");
+    *plain = *ap;
+    plain->dst_seq = gp->topk_idx;
+    plain->slot = gp->slot;
+    return PIKV_OK;
+}
+
+extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_params* ap, pikv_stream_t stream) {
+    pikv_append_params plain;
+    int rc = route_check(gp, ap, &plain);
+    if (rc != PIKV_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    pikv_append_params plain = *ap;
-    plain.dst_seq = gp->topk_idx;
-    plain.slot = gp->slot;
-    GateDev g;
-    const bool fusable = ap->dtype == PIKV_BF16 && ap->bits == 8 && ap->symmetric;
-    if (!fusable) {
-        const int rc = gate_run(gp, st, true, nullptr);
+    if (!route_fusable(gp, ap)) {
+        rc = gate_run(gp, st, GATE_DO_SCORE | GATE_DO_SLOTS, nullptr);
         return rc != PIKV_OK ? rc : pikv_kv_append_quant(&plain, stream);
     }
-    int rc = gate_run(gp, st, false, &g);
+    GateDev g;
+    rc = gate_run(gp, st, GATE_DO_SCORE | GATE_RANKS_TO_WS, &g);
     if (rc != PIKV_OK) return rc;
     const size_t smem = (size_t)g.G * g.E * sizeof(int);
-    if (smem > 40 * 1024) {
-        // too many chunks for the shared-memory prefix table: finish the scan with the stand-alone kernel
-        rc = gate_run(gp, st, true, nullptr);
-        return rc != PIKV_OK ? rc : pikv_kv_append_quant(&plain, stream);
-    }
     const pikv_append_params* p = &plain;
     PIKV_REQUIRE(p->T > 0 && p->n_kv > 0 && p->top_k > 0 && p->top_k <= APPEND_MAX_K, PIKV_EINVAL, "route_append: bad sizes");
     PIKV_REQUIRE(p->k && p->v && p->page_table && p->k_codes && p->v_codes && p->k_scale && p->v_scale, PIKV_EINVAL,
@@ -411,7 +443,7 @@ extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_p
     a.log2_nkv = -1;
     for (int b = 0; b < 16; ++b)
         if ((1 << b) == p->n_kv) a.log2_nkv = b;
-    a.dst_seq = p->dst_seq; a.slot = p->slot; a.page_table = p->page_table;
+    a.dst_seq = p->dst_seq; a.page_table = p->page_table;
     a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
     a.codes[0] = static_cast<uint8_t*>(p->k_codes); a.codes[1] = static_cast<uint8_t*>(p->v_codes);
     a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
@@ -421,7 +453,8 @@ extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_p
     for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
     a.g_cta_cnt = g.cta_cnt; a.g_cta_cnt_k = g.cta_cnt_k; a.g_cta_psum = g.cta_psum; a.g_slot_base = g.slot_base;
     a.gG = g.G; a.gchunk = g.chunk; a.gE = g.E; a.gcap = g.capacity;
-    a.g_slot_out = g.slot; a.g_counts_k = g.counts_k; a.g_prob_sum = g.prob_sum; a.g_new_len = g.new_len;
+    a.slot = g.slot;               // chunk-local ranks, in the gate's workspace
+    a.g_slot_out = gp->slot; a.g_counts_k = g.counts_k; a.g_prob_sum = g.prob_sum; a.g_new_len = g.new_len;
     const long long lanes = (long long)a.T * a.n_kv * 8;
     long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 3;
     const int grid = (int)(want < cap_ctas ? want : cap_ctas);

@@ -332,16 +332,13 @@ static int launch_logits(const GateDev& g, cudaStream_t st) {
 using namespace pikv;
 
 extern "C" size_t pikv_gate_workspace_bytes(int32_t T, int32_t E, int32_t top_k) {
-    (void)T;
-    if (E <= 0 || top_k <= 0) return 0;
-    return (size_t)GATE_MAX_CTAS * (size_t)E * (size_t)(top_k + 2) * 4;
+    if (T <= 0 || E <= 0 || top_k <= 0) return 0;
+    // per-CTA counters, then T*top_k chunk-local ranks (used when a consumer finishes the slot scan)
+    return (size_t)GATE_MAX_CTAS * (size_t)E * (size_t)(top_k + 2) * 4 + (size_t)T * (size_t)top_k * 4;
 }
 
 namespace pikv {
-// Runs the gate kernel; with finalize = false the slot output holds ranks local to each CTA's chunk
-// and the per-CTA counters stay in the workspace (*out describes them) for a consumer that finishes
-// the scan itself.
-int gate_run(const pikv_gate_params* p, cudaStream_t st, bool finalize, GateDev* out) {
+int gate_run(const pikv_gate_params* p, cudaStream_t st, int what, GateDev* out) {
     PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "gate: null params");
     PIKV_REQUIRE(p->T > 0 && p->E > 0 && p->top_k > 0, PIKV_EINVAL, "gate: T, E, top_k must be positive");
     PIKV_REQUIRE(p->E <= GATE_MAX_E, PIKV_ELIMIT, "gate: E=%d exceeds %d", p->E, GATE_MAX_E);
@@ -367,10 +364,20 @@ int gate_run(const pikv_gate_params* p, cudaStream_t st, bool finalize, GateDev*
     g.cta_cnt = ws;
     g.cta_cnt_k = ws + (size_t)GATE_MAX_CTAS * g.E;
     g.cta_psum = reinterpret_cast<float*>(ws + (size_t)GATE_MAX_CTAS * g.E * (g.k + 1));
+    if (what & GATE_RANKS_TO_WS) g.slot = ws + (size_t)GATE_MAX_CTAS * g.E * (g.k + 2);
     int rc;
     const int E = g.E;
     const char* force_simt = getenv("PIKV_GATE_SIMT");   // testing aid: run bf16 through the SIMT kernel too
-    if (g.act != nullptr && g.w2 != nullptr && gate_tc_supported(g, p->dtype) && !(force_simt && force_simt[0] == '1')) {
+    const bool use_tc = g.act != nullptr && g.w2 != nullptr && gate_tc_supported(g, p->dtype) && !(force_simt && force_simt[0] == '1');
+    if (!(what & GATE_DO_SCORE)) {
+        if (use_tc) gate_tc_geometry(g);
+        if (out) *out = g;
+        if (!(what & GATE_DO_SLOTS)) return PIKV_OK;
+        gate_finalize_kernel<<<g.G, GATE_THREADS, 0, st>>>(g);
+        count_launch(1);
+        return check_launch("gate_finalize_kernel");
+    }
+    if (use_tc) {
         rc = gate_tc_launch(g, st);
     } else if (g.act != nullptr) {
         PIKV_REQUIRE(g.w2 != nullptr, PIKV_EINVAL, "gate: w2 is required with act");
@@ -393,7 +400,7 @@ int gate_run(const pikv_gate_params* p, cudaStream_t st, bool finalize, GateDev*
     }
     if (rc != PIKV_OK) return rc;
     if (out) *out = g;
-    if (!finalize) {
+    if (!(what & GATE_DO_SLOTS)) {
         count_launch(1);
         return PIKV_OK;
     }
@@ -404,7 +411,11 @@ int gate_run(const pikv_gate_params* p, cudaStream_t st, bool finalize, GateDev*
 }  // namespace pikv
 
 extern "C" int pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream) {
-    return gate_run(p, static_cast<cudaStream_t>(stream), true, nullptr);
+    PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "gate: null params");
+    PIKV_REQUIRE(p->phase >= PIKV_GATE_WHOLE && p->phase <= PIKV_GATE_SLOTS, PIKV_EINVAL, "gate: bad phase %d", p->phase);
+    const int what = p->phase == PIKV_GATE_SCORE ? GATE_DO_SCORE : p->phase == PIKV_GATE_SLOTS ? GATE_DO_SLOTS
+                                                                                              : (GATE_DO_SCORE | GATE_DO_SLOTS);
+    return gate_run(p, static_cast<cudaStream_t>(stream), what, nullptr);
 }
 
 extern "C" int pikv_dispatch_scatter(const int32_t* topk_idx, const float* topk_w, const int32_t* slot,

@@ -112,11 +112,15 @@ __device__ __forceinline__ void token_tail(float (&l)[EP], const GateDev& g, int
     }
 }
 
-// the gate without (finalize = false) or with its slot finalisation; see gate.cu
-int gate_run(const pikv_gate_params* p, cudaStream_t st, bool finalize, GateDev* out);
+// what gate_run does: launch the scoring kernel, launch the slot finalisation, and whether the chunk-local
+// ranks go to the workspace instead of the caller's slot array (for a consumer that finishes the scan
+// itself).  With neither launch flag it only validates and fills *out (geometry, workspace layout).
+enum : int { GATE_DO_SCORE = 1, GATE_DO_SLOTS = 2, GATE_RANKS_TO_WS = 4 };
+int gate_run(const pikv_gate_params* p, cudaStream_t st, int what, GateDev* out);
 
 // tensor-core path (gate_tc.cu): bf16 activations through TMA + tcgen05
 bool gate_tc_supported(const GateDev& g, int dtype);
+void gate_tc_geometry(GateDev& g);                  // sets g.chunk and g.G
 int gate_tc_launch(GateDev& g, cudaStream_t st);   // sets g.chunk and g.G for the finalize kernel
 
 }  // namespace pikv

@@ -31,7 +31,9 @@ struct GateTcArgs {
     int stages, tmem_cols, tiles, tiles_per_cta;
 };
 
-template <int EP>
+// EP: expert columns of the MMA (multiple of 16); EL <= EP: columns the per-token tail looks at (8 when E <= 8,
+// which halves the serial softmax / top-k work of the four epilogue warps)
+template <int EP, int EL>
 __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_constant__ CUtensorMap tm_act,
                                                              const __grid_constant__ CUtensorMap tm_w,
                                                              GateTcArgs a) {
@@ -139,13 +141,14 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
             const int slot = lt & 1;
             if (!lr_mbar_wait(tfull0 + 8 * slot, ((uint32_t)lt >> 1) & 1u)) { failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float l[EP];
+            float l[EL];
 #pragma unroll
-            for (int c = 0; c < EP; c += 16) {
+            for (int c = 0; c < EL; c += 16) {
                 float v[16];
                 lr_tmem_ld16(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(slot * EP + c), v);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) l[c + i] = v[i];
+                for (int i = 0; i < 16; ++i)
+                    if (c + i < EL) l[c + i] = v[i];
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(tempty0 + 8 * slot);          // this thread's row is out of tensor memory
@@ -154,13 +157,13 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
             if (valid) {
                 if (g.b2) {
 #pragma unroll
-                    for (int e = 0; e < EP; ++e)
+                    for (int e = 0; e < EL; ++e)
                         if (e < g.E) l[e] += __ldg(g.b2 + e);
                 }
-                token_tail<EP>(l, g, chunk_start + lt_tok, sel + (size_t)lt_tok * g.k);
+                token_tail<EL>(l, g, chunk_start + lt_tok, sel + (size_t)lt_tok * g.k);
             }
 #pragma unroll
-            for (int e = 0; e < EP; ++e) {
+            for (int e = 0; e < EL; ++e) {
                 const float s = warp_sum(valid ? l[e] : 0.f);
                 if (lane == 0) psum_w[ew * EP + e] += s;
             }
@@ -220,13 +223,19 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
     }
 }
 
-template <int EP>
+// one CTA per 128-token tile until the grid limit, then whole tiles per CTA
+void gate_tc_geometry(GateDev& g) {
+    const int tiles = ceil_div(g.T, LR_BM);
+    g.chunk = ceil_div(tiles, GATE_MAX_CTAS) * LR_BM;
+    g.G = ceil_div(g.T, g.chunk);
+}
+
+template <int EP, int EL>
 static int launch_gate_tc(GateDev& g, cudaStream_t st) {
     GateTcArgs a;
+    gate_tc_geometry(g);
     a.tiles = ceil_div(g.T, LR_BM);
-    a.tiles_per_cta = ceil_div(a.tiles, GATE_MAX_CTAS);
-    g.chunk = a.tiles_per_cta * LR_BM;
-    g.G = ceil_div(g.T, g.chunk);
+    a.tiles_per_cta = g.chunk / LR_BM;
     a.g = g;
     CUtensorMap tm_act, tm_w;
     int rc = make_tmap(&tm_act, g.act, g.T, g.H, LR_BM);
@@ -243,7 +252,7 @@ static int launch_gate_tc(GateDev& g, cudaStream_t st) {
     while (cols < 2 * EP) cols <<= 1;
     a.tmem_cols = cols;
     const size_t smem = (size_t)a.stages * stage + tail;
-    auto kern = gate_tc_kernel<EP>;
+    auto kern = gate_tc_kernel<EP, EL>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("gate_tc smem attribute");
     kern<<<g.G, GT_THREADS, smem, st>>>(tm_act, tm_w, a);
@@ -257,9 +266,10 @@ bool gate_tc_supported(const GateDev& g, int dtype) {
 }
 
 int gate_tc_launch(GateDev& g, cudaStream_t st) {
-    if (g.E <= 16) return launch_gate_tc<16>(g, st);
-    if (g.E <= 32) return launch_gate_tc<32>(g, st);
-    return launch_gate_tc<64>(g, st);
+    if (g.E <= 8) return launch_gate_tc<16, 8>(g, st);
+    if (g.E <= 16) return launch_gate_tc<16, 16>(g, st);
+    if (g.E <= 32) return launch_gate_tc<32, 32>(g, st);
+    return launch_gate_tc<64, 64>(g, st);
 }
 
 }  // namespace pikv

@@ -67,6 +67,7 @@ class GateResult:
     counts_k: torch.Tensor             # [k,E] int32
     prob_sum: torch.Tensor             # [E] fp32
     new_len: torch.Tensor              # [E] int32
+    workspace: Optional[torch.Tensor] = None   # gate scratch owned by this result (route_append)
 
     @property
     def counts(self) -> torch.Tensor:
@@ -78,10 +79,12 @@ def gate_fused(act: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = 
                expert_mask: Optional[torch.Tensor] = None, mask_mode: int = _lib.MASK_SINGLE,
                correction: Optional[torch.Tensor] = None, temperature: float = 1.0, renorm_eps: float = 0.0,
                capacity: int = 0, slot_base: Optional[torch.Tensor] = None, want_probs: bool = True,
-               out: Optional[GateResult] = None) -> GateResult:
+               out: Optional[GateResult] = None, phase: int = 0) -> GateResult:
     """Fused gate tail; see pikv_gate_fused in include/pikv_b200.h.
 
-    Give either (act [T,H], w2 [E,H], b2 [E]) or logits [T,E] fp32.
+    Give either (act [T,H], w2 [E,H], b2 [E]) or logits [T,E] fp32.  phase 1 (scoring kernel only) and
+    phase 2 (slot finalisation only, same arguments, ordered after phase 1 by the caller) keep their state
+    in out.workspace, which is allocated on first use and must not be shared between batches in flight.
     """
     if logits is not None:
         logits = _req(logits, "logits", torch.float32)
@@ -104,7 +107,14 @@ def gate_fused(act: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = 
             slot=torch.empty(T, top_k, **i32), counts_k=torch.empty(top_k, E, **i32),
             prob_sum=torch.empty(E, **f32), new_len=torch.empty(E, **i32))
     nws = lib().pikv_gate_workspace_bytes(T, E, top_k)
-    ws = _workspace(dev, nws, "gate")
+    if phase != 0 or out.workspace is not None:
+        if out.workspace is None or out.workspace.numel() < nws:
+            if phase == 2:
+                raise PikvError("gate phase 2 needs the result (and workspace) of the phase 1 call")
+            out.workspace = torch.empty(nws, dtype=torch.uint8, device=dev)
+        ws = out.workspace
+    else:
+        ws = _workspace(dev, nws, "gate")
     keep = []
 
     def f(t):
@@ -127,7 +137,7 @@ def gate_fused(act: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = 
     p.slot_base = _p(slot_base)
     p.probs, p.topk_idx, p.topk_w, p.slot = _p(out.probs), _p(out.topk_idx), _p(out.topk_w), _p(out.slot)
     p.counts_k, p.prob_sum, p.new_len = _p(out.counts_k), _p(out.prob_sum), _p(out.new_len)
-    p.workspace, p.workspace_bytes = _p(ws), ws.numel()
+    p.workspace, p.workspace_bytes, p.phase = _p(ws), ws.numel(), int(phase)
     check(lib().pikv_gate_fused(C.byref(p), _stream()), "pikv_gate_fused")
     return out
 

@@ -84,13 +84,7 @@ class PagedKVCache(torch.nn.Module):
         p.status = _p(self.status)
         check(lib().pikv_kv_append_quant(C.byref(p), _stream()), "pikv_kv_append_quant")
 
-    def route_append(self, act: torch.Tensor, w2: torch.Tensor, b2: Optional[torch.Tensor], k: torch.Tensor,
-                     v: torch.Tensor, top_k: int = 2, capacity: Optional[int] = None,
-                     out: Optional["ops.GateResult"] = None, slot_base: Optional[torch.Tensor] = None,
-                     want_probs: bool = True):
-        """Gate the tokens and append their quantised K/V rows in one call (pikv_route_append): the
-        same results as ops.gate_fused followed by append(), with the slot finalisation folded into the
-        append kernel.  Sequences are the experts.  Returns the gate result."""
+    def _route_params(self, act, w2, b2, k, v, top_k, capacity, out, slot_base, want_probs):
         from . import ops
         act = _req(act, "act")
         w2 = _req(w2, "w2", act.dtype)
@@ -108,7 +102,10 @@ class PagedKVCache(torch.nn.Module):
                                  topk_idx=torch.empty(T, top_k, **i32), topk_w=torch.empty(T, top_k, **f32),
                                  slot=torch.empty(T, top_k, **i32), counts_k=torch.empty(top_k, E, **i32),
                                  prob_sum=torch.empty(E, **f32), new_len=torch.empty(E, **i32))
-        ws = _workspace(dev, lib().pikv_gate_workspace_bytes(T, E, top_k), "gate")
+        need = lib().pikv_gate_workspace_bytes(T, E, top_k)
+        if out.workspace is None or out.workspace.numel() < need:
+            # owned by the result, so calls on different streams never share gate scratch
+            out.workspace = torch.empty(need, dtype=torch.uint8, device=dev)
         b2f = None if b2 is None else _req(b2.to(torch.float32), "b2", torch.float32)
         gp = _lib.GateParams()
         gp.act, gp.w2, gp.b2, gp.dtype = _p(act), _p(w2), _p(b2f), _dtype_code(act, "act")
@@ -118,7 +115,7 @@ class PagedKVCache(torch.nn.Module):
         gp.slot_base = _p(slot_base)
         gp.probs, gp.topk_idx, gp.topk_w, gp.slot = _p(out.probs), _p(out.topk_idx), _p(out.topk_w), _p(out.slot)
         gp.counts_k, gp.prob_sum, gp.new_len = _p(out.counts_k), _p(out.prob_sum), _p(out.new_len)
-        gp.workspace, gp.workspace_bytes = _p(ws), ws.numel()
+        gp.workspace, gp.workspace_bytes = _p(out.workspace), out.workspace.numel()
         ap = AppendParams()
         ap.k, ap.v, ap.dtype, ap.T, ap.n_kv, ap.top_k = _p(k), _p(v), _dtype_code(k, "k"), T, self.n_kv, top_k
         ap.page_table = _p(self.page_table)
@@ -126,6 +123,16 @@ class PagedKVCache(torch.nn.Module):
         ap.bits, ap.symmetric = self.bits, int(self.symmetric)
         ap.k_codes, ap.v_codes, ap.k_scale, ap.v_scale = _p(self.k_codes), _p(self.v_codes), _p(self.k_scale), _p(self.v_scale)
         ap.k_zp, ap.v_zp, ap.status = _p(self.k_zp), _p(self.v_zp), _p(self.status)
+        return gp, ap, out, (act, w2, b2f, k, v, slot_base)
+
+    def route_append(self, act: torch.Tensor, w2: torch.Tensor, b2: Optional[torch.Tensor], k: torch.Tensor,
+                     v: torch.Tensor, top_k: int = 2, capacity: Optional[int] = None,
+                     out: Optional["ops.GateResult"] = None, slot_base: Optional[torch.Tensor] = None,
+                     want_probs: bool = True):
+        """Gate the tokens and append their quantised K/V rows in one call (pikv_route_append): the
+        same results as ops.gate_fused followed by append(), with the slot finalisation folded into the
+        append kernel.  Sequences are the experts.  Returns the gate result."""
+        gp, ap, out, keep = self._route_params(act, w2, b2, k, v, top_k, capacity, out, slot_base, want_probs)
         check(lib().pikv_route_append(C.byref(gp), C.byref(ap), _stream()), "pikv_route_append")
         return out
 

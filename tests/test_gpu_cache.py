@@ -478,3 +478,4 @@ def test_fused_route_append_equals_gate_then_append(dev, T, H, E, k, n_kv, cap):
     assert torch.allclose(f.prob_sum, g.prob_sum, rtol=1e-5)
     for name in ("k_codes", "v_codes", "k_scale", "v_scale"):
         assert torch.equal(getattr(one, name), getattr(two, name)), name
+

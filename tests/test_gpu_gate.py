@@ -255,3 +255,32 @@ def test_module_running_slots_match_reference_dispatch(dev):
     p_mean = res.prob_sum.cpu().numpy() / 24
     f = res.counts.cpu().numpy() / 48.0
     assert abs(float((p_mean * f).sum() * 4) - float(g["aux"])) < 1e-5
+
+
+def test_gate_phases_on_two_streams(dev):
+    """Scoring (phase 1) on one stream, slot finalisation (phase 2) on another after an event: the same
+    result as the whole gate, for several batches in flight with their own workspaces."""
+    from pikv_b200 import ops
+    T, H, E, k = 5000, 512, 8, 2
+    torch.manual_seed(3)
+    w2 = (torch.randn(E, H, device=dev) / H ** 0.5).bfloat16()
+    b2 = torch.randn(E, device=dev) * 0.1
+    acts = [torch.relu(torch.randn(T, H, device=dev)).bfloat16() for _ in range(3)]
+    base = torch.randint(0, 9, (E,), dtype=torch.int32, device=dev)
+    want = [ops.gate_fused(a, w2, b2, top_k=k, capacity=1700, slot_base=base) for a in acts]
+    s1, s2 = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    torch.cuda.synchronize()
+    got = []
+    for a in acts:
+        with torch.cuda.stream(s1):
+            g = ops.gate_fused(a, w2, b2, top_k=k, capacity=1700, slot_base=base, phase=1)
+            ev = torch.cuda.Event()
+            ev.record(s1)
+        s2.wait_event(ev)
+        with torch.cuda.stream(s2):
+            ops.gate_fused(a, w2, b2, top_k=k, capacity=1700, slot_base=base, phase=2, out=g)
+        got.append(g)
+    torch.cuda.synchronize()
+    for w, g in zip(want, got):
+        for name in ("probs", "topk_idx", "topk_w", "slot", "counts_k", "prob_sum", "new_len"):
+            assert torch.equal(getattr(w, name), getattr(g, name)), name
