@@ -34,7 +34,8 @@ WORKLOAD = dict(workload="route+int8-quant+append", tokens=16384, hidden=4096, e
 GATE_BYTES_PER_TOKEN = 4096 * 2 + 8 * 4 + 3 * 2 * 4                      # act in; probs, idx, w, slot out
 APPEND_BYTES_PER_TOKEN = 2 * 1024 * 2 + 16 + 2 * 2 * 1024 + 2 * 16 * 2   # K,V in; idx/slot; 2 copies of codes + scales
 # DRAM bytes per launch (read + write) at 16384 tokens, from the ncu captures summarised under profiles/
-TRAFFIC = {"gate": 138.9e6, "append": 118.6e6}
+# (the append's 67.4 MB of reads arrive in full; of its 68 MB of writes 21.6 MB had left the 126 MB L2 at kernel end)
+TRAFFIC = {"gate": 139.2e6, "append": 89.0e6}
 
 
 def measured_peak_gbs():
@@ -272,7 +273,7 @@ def gpu_arm(args):
         """R rotating input sets and caches so that no step finds its inputs in L2 (one set is 201 MB at
         16384 tokens, L2 is 126 MB)."""
         cap = int(tokens * cfg["capacity_factor"] * k / E)
-        R = 3
+        R = 6 if tokens <= 32768 else 3     # more sets in flight let the gates run further ahead of the appends
         sets = [synth_inputs(tokens, H, E, kv, 100 + i, device=dev) for i in range(R)]
         caches = [pikv_b200.PagedKVCache(E, cap, n_kv, device=dev) for _ in range(R)]
         outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=cap, want_probs=True) for _ in range(R)]
@@ -302,23 +303,21 @@ def gpu_arm(args):
                     score=score, slots=slots, pappend=pappend)
 
     def kernel_times(w, n):
-        """Average device time of the gate and of the append, each replayed as its own graph, with events
-        on the launching stream in between."""
-        gg = [capture(lambda i=i: w["gate"](i))[0] for i in range(w["R"])]
-        ga = [capture(lambda i=i: w["append"](i))[0] for i in range(w["R"])]
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n)]
-        for i in range(3):
-            gg[i % w["R"]].replay()
-            ga[i % w["R"]].replay()
-        barrier()
-        for i in range(n):
-            ev[i][0].record()
-            gg[i % w["R"]].replay()
-            ev[i][1].record()
-            ga[i % w["R"]].replay()
-            ev[i][2].record()
-        barrier()
-        return (sum(e[0].elapsed_time(e[1]) for e in ev) / n, sum(e[1].elapsed_time(e[2]) for e in ev) / n)
+        """Average device time per launch of the gate's scoring kernel, of its slot finalisation and of the
+        append: each kernel is captured R times back to back (one launch per buffer set, so every launch
+        reads cold inputs) and the graph is timed with events on the launching stream."""
+        R_ = w["R"]
+        out = []
+        for name in ("score", "slots", "pappend"):
+            for i in range(R_):
+                w["score"](i)                              # valid gate state for the later phases
+                if name == "pappend":
+                    w["slots"](i)                          # the append is timed on final slots
+            graph = capture(lambda: [w[name](i) for i in range(R_)])[0]
+            reps = max(2, -(-n // R_))
+            graph.replay()
+            out.append(timed(lambda i: graph.replay(), reps) / (reps * R_))
+        return out
 
     roof = e2e = cpu = large = None
     if world > 1:
@@ -380,17 +379,18 @@ def gpu_arm(args):
 
     if world == 1:
         peak, peak_src = measured_peak_gbs()
-        gate_ms, app_ms = kernel_times(wl, steps)
+        gate_ms, fin_ms, app_ms = kernel_times(wl, steps)
         gate_gbs = GATE_BYTES_PER_TOKEN * T / (gate_ms * 1e-3) / 1e9
         app_gbs = APPEND_BYTES_PER_TOKEN * T / (app_ms * 1e-3) / 1e9
         step_gbs = (GATE_BYTES_PER_TOKEN + APPEND_BYTES_PER_TOKEN) * T / (ms_max / steps * 1e-3) / 1e9
         dom = "gate" if gate_ms >= app_ms else "append"
         roof = {"bound": "hbm",
-                "kernel": "gate_tc_kernel (+ gate_finalize_kernel)" if dom == "gate" else "kv_append_quant_kernel",
+                "kernel": "gate_tc_kernel" if dom == "gate" else "kv_append_quant_kernel",
                 "achieved": gate_gbs if dom == "gate" else app_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                 "frac": (gate_gbs if dom == "gate" else app_gbs) / peak, "traffic": TRAFFIC.get(dom),
                 "gate": {"ms": gate_ms, "GBps": gate_gbs, "frac": gate_gbs / peak, "bytes_per_token": GATE_BYTES_PER_TOKEN},
                 "append": {"ms": app_ms, "GBps": app_gbs, "frac": app_gbs / peak, "bytes_per_token": APPEND_BYTES_PER_TOKEN},
+                "finalize": {"ms": fin_ms},
                 "step": {"GBps": step_gbs, "frac": step_gbs / peak}}
 
         # end to end: pinned host inputs copied in, routing result read back, every step (eager calls)
@@ -444,7 +444,7 @@ def gpu_arm(args):
                 for i in range(3):
                     g8[i % w8["R"]].replay()
                 ms8 = timed(lambda i: g8[i % w8["R"]].replay(), steps8)
-            gate8, app8 = kernel_times(w8, steps8)
+            gate8, _, app8 = kernel_times(w8, steps8)
             large = {"tokens": T8, "value": T8 * steps8 / (ms8 * 1e-3), "unit": UNIT, "ms_per_step": ms8 / steps8,
                      "gate_frac": GATE_BYTES_PER_TOKEN * T8 / (gate8 * 1e-3) / 1e9 / peak,
                      "append_frac": APPEND_BYTES_PER_TOKEN * T8 / (app8 * 1e-3) / 1e9 / peak,
