@@ -211,6 +211,31 @@ int pikv_kv_append_sharded(const pikv_append_sharded_params* p, pikv_stream_t st
 int pikv_shard_plan(const int32_t* gathered, int32_t world, int32_t E, int32_t rank, int32_t capacity,
                     int32_t* len_all, int32_t* slot_base, pikv_stream_t stream);
 
+/* The all-gather of the selection counts and pikv_shard_plan as ONE kernel over peer memory, so
+ * that a sharded step is made of this library's kernels only (no collective library call, nothing
+ * on the host): every rank stores its counts into slot (step % PIKV_XCHG_RING) of every rank's
+ * gather buffer over NVLink, raises the step number in every rank's flag word, waits (about two
+ * seconds at most, then PIKV_ST_WAIT_TIMEOUT is raised in *status and the step's rows are dropped)
+ * for all ranks' flags and computes slot_base / len_all.  All ranks must call it once per step, in
+ * the same order.  gather [PIKV_XCHG_RING][world][E] int32 and flags [PIKV_XCHG_RING][world] uint32
+ * live in memory every rank has mapped (peer_*[r] = rank r's copy as seen from this GPU) and start
+ * zeroed, as does *seq, this rank's step counter.  start_empty != 0: lengths restart from zero.
+ * Replaces the exchange of DistributedPiKVMoE.forward (core/distributed/distributed_pikv.py:174-194)
+ * for the routing counts. */
+#define PIKV_XCHG_RING 4
+typedef struct {
+    const int32_t* counts_k;   /* [top_k][E], this rank's gate output             */
+    int32_t top_k, E, world, rank, capacity, start_empty;
+    int32_t*  peer_gather[8];
+    uint32_t* peer_flags[8];
+    uint32_t* seq;
+    int32_t*  len_all;         /* [E] replicated lengths, advanced identically on every rank */
+    int32_t*  slot_base;       /* [E] out: position of this rank's first row in every sequence */
+    uint32_t* status;          /* may be NULL */
+} pikv_shard_exchange_params;
+
+int pikv_shard_exchange_plan(const pikv_shard_exchange_params* p, pikv_stream_t stream);
+
 /* Read rows back in logical order, dequantised: out[i] = (code - zp) * scale for
  * sequence seq[i], position pos[i]; out is [n, n_kv*128] fp32, codes_out
  * (optional) [n, n_kv*128] int8 unpacked codes.  Used by tests, checkpointing

@@ -54,6 +54,17 @@ class AppendShardedParams(C.Structure):
     ]
 
 
+class ShardExchangeParams(C.Structure):
+    _fields_ = [
+        ("counts_k", vp), ("top_k", i32), ("E", i32), ("world", i32), ("rank", i32), ("capacity", i32),
+        ("start_empty", i32), ("peer_gather", vp * 8), ("peer_flags", vp * 8), ("seq", vp), ("len_all", vp),
+        ("slot_base", vp), ("status", vp),
+    ]
+
+
+XCHG_RING = 4
+
+
 class CompactParams(C.Structure):
     _fields_ = [
         ("keep_idx", vp), ("kept_count", vp),
@@ -92,6 +103,7 @@ SIGNATURES = {
     "pikv_route_append": (i32, [C.POINTER(GateParams), C.POINTER(AppendParams), vp]),
     "pikv_kv_append_sharded": (i32, [C.POINTER(AppendShardedParams), vp]),
     "pikv_shard_plan": (i32, [vp, i32, i32, i32, i32, vp, vp, vp]),
+    "pikv_shard_exchange_plan": (i32, [C.POINTER(ShardExchangeParams), vp]),
     "pikv_cache_gather": (i32, [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "pikv_quant_block_workspace_bytes": (sz, [i32, i32, i32]),
     "pikv_quant_block": (i32, [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp]),

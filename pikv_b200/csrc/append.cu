@@ -495,6 +495,87 @@ extern "C" int pikv_shard_plan(const int32_t* gathered, int32_t world, int32_t E
     return check_launch("shard_plan_kernel");
 }
 
+// ---- count exchange + plan in one kernel, over peer memory ---------------------------------------------
+// Each rank owns a ring of PIKV_XCHG_RING gather slots [world][E] and flags [world] in memory every peer
+// has mapped.  One CTA per rank: sum this rank's selection counts over the k columns, store them into
+// slot (step % ring) of EVERY rank's gather buffer (plain stores over NVLink), fence, raise the step
+// number in every rank's flag word; then wait, with a limit, until all ranks' flags of that slot show
+// this step, and compute slot_base / len_all from the local copy as shard_plan_kernel does.  A rank can
+// be at most one step ahead of the slowest (its next plan needs that rank's next counts), so a ring of
+// four never overwrites unread counts.  If the wait runs out, every slot_base is set to the capacity (all
+// rows of the step are dropped) and PIKV_ST_WAIT_TIMEOUT is raised: nothing hangs.
+constexpr unsigned XCHG_SPINS = 1u << 21;     // x 1 us sleep: about two seconds
+
+__global__ void __launch_bounds__(256) shard_exchange_plan_kernel(pikv_shard_exchange_params p) {
+    __shared__ unsigned step_s;
+    __shared__ int ok_s;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        step_s = *p.seq + 1u;
+        *p.seq = step_s;
+        ok_s = 1;
+    }
+    __syncthreads();
+    const unsigned step = step_s;
+    const int ring = (int)(step % PIKV_XCHG_RING);
+    const int E = p.E, W = p.world;
+    for (int e = tid; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int j = 0; j < p.top_k; ++j) c += p.counts_k[j * E + e];
+        for (int r = 0; r < W; ++r) p.peer_gather[r][((size_t)ring * W + p.rank) * E + e] = c;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < W) {
+        unsigned* flag = p.peer_flags[tid] + ring * W + p.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+    }
+    if (tid < W) {
+        const unsigned* mine = p.peer_flags[p.rank] + ring * W + tid;
+        unsigned seen = 0, spins = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if (seen == step || ++spins >= XCHG_SPINS) break;
+            __nanosleep(1000);
+        }
+        if (seen != step) {
+            ok_s = 0;
+            if (p.status) atomicOr(p.status, PIKV_ST_WAIT_TIMEOUT);
+        }
+    }
+    __syncthreads();
+    const bool ok = ok_s != 0;
+    const int* gathered = p.peer_gather[p.rank] + (size_t)ring * W * E;
+    for (int e = tid; e < E; e += blockDim.x) {
+        int before = 0, total = 0;
+        for (int s = 0; s < W; ++s) {
+            const int c = __ldcg(gathered + s * E + e);   // written by peers: read at L2
+            if (s < p.rank) before += c;
+            total += c;
+        }
+        const int len = p.start_empty ? 0 : p.len_all[e];
+        if (!ok) {
+            p.slot_base[e] = p.capacity > 0 ? p.capacity : 0x3fffffff;
+            continue;
+        }
+        p.slot_base[e] = len + before;
+        const int n = len + total;
+        p.len_all[e] = (p.capacity > 0 && n > p.capacity) ? p.capacity : n;
+    }
+}
+
+extern "C" int pikv_shard_exchange_plan(const pikv_shard_exchange_params* p, pikv_stream_t stream) {
+    PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "shard_exchange_plan: null params");
+    PIKV_REQUIRE(p->counts_k && p->seq && p->len_all && p->slot_base, PIKV_EINVAL, "shard_exchange_plan: null pointer");
+    PIKV_REQUIRE(p->world >= 1 && p->world <= 8 && p->rank >= 0 && p->rank < p->world && p->E > 0 && p->top_k > 0,
+                 PIKV_EINVAL, "shard_exchange_plan: bad sizes");
+    for (int r = 0; r < p->world; ++r)
+        PIKV_REQUIRE(p->peer_gather[r] && p->peer_flags[r], PIKV_EINVAL, "shard_exchange_plan: null peer buffer for rank %d", r);
+    shard_exchange_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(*p);
+    count_launch(1);
+    return check_launch("shard_exchange_plan_kernel");
+}
+
 extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv_stream_t stream) {
     PIKV_REQUIRE(sp != nullptr, PIKV_EINVAL, "append_sharded: null params");
     const pikv_append_params* p = &sp->base;

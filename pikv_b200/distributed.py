@@ -129,10 +129,11 @@ class PeerShardedKVCache:
 
     Every rank's page pools live in one symmetric-memory allocation, so each rank holds a
     peer-mapped pointer to every other rank's pools (NVLink, NVSwitch).  A step is: gate the local
-    tokens -> all-gather the E selection counts (NCCL, stream-ordered, no host read) -> a one-CTA
-    plan kernel (slot of this rank's first row in every sequence, new lengths) -> the quantise +
-    append kernel, whose stores for remote sequences cross NVLink as plain 16-byte stores ->
-    a symmetric-memory barrier so that every rank's rows have landed.  Nothing on the step
+    tokens -> one one-CTA kernel that exchanges the E selection counts with every rank through
+    peer memory (stores + flags, bounded wait) and plans the step (slot of this rank's first row in
+    every sequence, new lengths) -> the quantise + append kernel, whose stores for remote sequences
+    cross NVLink as plain 16-byte stores -> (before anybody reads the rows) a symmetric-memory
+    barrier.  The step is three of this library's kernels and no collective-library call; nothing
     touches the host, and no copy of a row is staged in HBM: per-GPU HBM traffic is that of the
     single-GPU step.  No multicast object is created (plain peer pointers only).
     """
@@ -155,12 +156,19 @@ class PeerShardedKVCache:
         self.cache = PagedKVCache(self.per, capacity, n_kv, device=self.device)
         names = ("k_codes", "v_codes", "k_scale", "v_scale")
         sizes = [getattr(self.cache, n).numel() * getattr(self.cache, n).element_size() for n in names]
+        ring = _lib.XCHG_RING
+        sizes += [ring * self.world * num_experts * 4, ring * self.world * 4]      # count exchange: gather, flags
         offs = np.concatenate([[0], np.cumsum([(b + 255) // 256 * 256 for b in sizes])])
         self._buf = symm.empty(int(offs[-1]), dtype=torch.uint8, device=self.device)
         self._buf.zero_()
+        torch.cuda.synchronize(self.device)      # flags are zero on every rank before any peer can raise one
         self._hdl = symm.rendezvous(self._buf, self.group)
         self._peer = {n: [int(self._hdl.buffer_ptrs[r]) + int(offs[i]) for r in range(self.world)]
                       for i, n in enumerate(names)}
+        self._peer_gather = [int(self._hdl.buffer_ptrs[r]) + int(offs[4]) for r in range(self.world)]
+        self._peer_flags = [int(self._hdl.buffer_ptrs[r]) + int(offs[5]) for r in range(self.world)]
+        self.seq = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._start_empty = False
         for i, n in enumerate(names):
             old = getattr(self.cache, n)
             view = self._buf[int(offs[i]): int(offs[i]) + sizes[i]].view(old.dtype).view(old.shape)
@@ -175,8 +183,8 @@ class PeerShardedKVCache:
 
     def prepare(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None):
         """Bind one set of buffers to a step and return `run()`: the argument blocks are built once, so a
-        call of run() is six enqueues (gate, count sum, all-gather, plan, append, barrier) and no host
-        arithmetic.  The buffers must stay alive and in place while run() is used."""
+        call of run() is three C-ABI calls (gate, count exchange + plan, append), plus the barrier when
+        asked, and no host arithmetic.  The buffers must stay alive and in place while run() is used."""
         C, L = self._C, self._lib
         act, w2 = ops._req(act, "act", torch.bfloat16), ops._req(w2, "w2", torch.bfloat16)
         k, v = ops._req(k, "k", torch.bfloat16), ops._req(v, "v", torch.bfloat16)
@@ -202,16 +210,18 @@ class PeerShardedKVCache:
         for r in range(self.world):
             sp.peer_k_codes[r], sp.peer_v_codes[r] = self._peer["k_codes"][r], self._peer["v_codes"][r]
             sp.peer_k_scale[r], sp.peer_v_scale[r] = self._peer["k_scale"][r], self._peer["v_scale"][r]
+        xp = L.ShardExchangeParams()
+        xp.counts_k, xp.top_k, xp.E, xp.world, xp.rank, xp.capacity = ops._p(out.counts_k), top_k, E, self.world, self.rank, self.capacity
+        for r in range(self.world):
+            xp.peer_gather[r], xp.peer_flags[r] = self._peer_gather[r], self._peer_flags[r]
+        xp.seq, xp.len_all, xp.slot_base, xp.status = ops._p(self.seq), ops._p(self.len_all), ops._p(self.slot_base), ops._p(self.cache.status)
         lib, keep = L.lib(), (act, w2, b2f, k, v, out, ws)
-        gathered, counts, len_all, slot_base = ops._p(self.gathered), self.counts, ops._p(self.len_all), ops._p(self.slot_base)
 
         def run(sync: bool = True):
             st = ops._stream()
             L.check(lib.pikv_gate_fused(C.byref(gp), st), "pikv_gate_fused")
-            torch.sum(out.counts_k, dim=0, dtype=torch.int32, out=counts)
-            dist.all_gather_into_tensor(self.gathered, counts, group=self.group)
-            L.check(lib.pikv_shard_plan(gathered, self.world, E, self.rank, self.capacity, len_all, slot_base, st),
-                    "pikv_shard_plan")
+            xp.start_empty, self._start_empty = int(self._start_empty), False
+            L.check(lib.pikv_shard_exchange_plan(C.byref(xp), st), "pikv_shard_exchange_plan")
             L.check(lib.pikv_kv_append_sharded(C.byref(sp), st), "pikv_kv_append_sharded")
             if sync:
                 self.barrier()
@@ -237,7 +247,8 @@ class PeerShardedKVCache:
         self._hdl.barrier(channel=0)
 
     def reset(self):
-        self.len_all.zero_()
+        """Empty the cache: the next step plans from zero lengths (no kernel is enqueued for this)."""
+        self._start_empty = True
 
 
 def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "peer"):
@@ -254,9 +265,9 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
     outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(R)]
     hooks = {"begin": lambda: None, "end": lambda: None}
     if mode == "peer":
-        # two steps in flight on two streams, each with its own cache instance (own pools, own barrier
-        # pads): the gate of one step overlaps the all-gather, the NVLink stores and the barrier of the
-        # previous one
+        # two steps in flight on two streams, each with its own cache instance (own pools, own exchange
+        # ring): the gate of one step overlaps the count exchange and the NVLink stores of the previous
+        # one.  Nobody reads rows between the appends, so the cross-GPU barrier runs once, at the end.
         lanes = 2
         shards = [PeerShardedKVCache(E, cap, n_kv, dev) for _ in range(lanes)]
         streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)]
@@ -268,14 +279,16 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
             lane = i % lanes
             with torch.cuda.stream(streams[lane]):
                 shards[lane].reset()
-                runs[lane][i % R]()
+                runs[lane][i % R](sync=False)
 
         def begin():
             for st in streams:
                 st.wait_stream(torch.cuda.current_stream())
 
         def end():
-            for st in streams:
+            for shard, st in zip(shards, streams):
+                with torch.cuda.stream(st):
+                    shard.barrier()
                 torch.cuda.current_stream().wait_stream(st)
 
         hooks = {"begin": begin, "end": end}
