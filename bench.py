@@ -475,9 +475,10 @@ def gpu_arm(args):
 
 
 # ----------------------------------------------------------------------------- secondary workloads
-def fill_stream_cache(pikv_b200, torch, dev, B, n_kv, ctx, seed=0):
-    """int8 cache of B streams x ctx tokens, written through the append kernel stream by stream."""
-    cache = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)
+def fill_stream_cache(pikv_b200, torch, dev, B, n_kv, ctx, seed=0, bits=8):
+    """int8-symmetric (or 4-bit asymmetric) cache of B streams x ctx tokens, written through the append
+    kernel stream by stream."""
+    cache = pikv_b200.PagedKVCache(B, ctx, n_kv, bits=bits, symmetric=(bits == 8), device=dev)
     g = torch.Generator(device=dev).manual_seed(seed)
     pos = torch.arange(ctx, dtype=torch.int32, device=dev)[:, None].contiguous()
     for b in range(B):
@@ -518,18 +519,20 @@ def secondary_arm(args):
 
     if args.workload == "decode":
         B, n_q, n_kv, ctx = args.streams, 32, 8, args.context
-        cache = fill_stream_cache(pikv_b200, torch, dev, B, n_kv, ctx)
+        cache = fill_stream_cache(pikv_b200, torch, dev, B, n_kv, ctx, bits=args.bits)
         q = torch.randn(B, n_q, 128, device=dev).bfloat16()
         n0 = pikv_b200.launch_count()
         ms = timed(lambda: cache.decode_attention(q, splits=args.splits), steps)
         launches = (pikv_b200.launch_count() - n0) * steps // (steps + warmup)
         cache.check_status()
-        by = B * n_kv * (2 * ctx * 128 + 2 * ctx * 2) + 2 * B * n_q * 128 * 2
+        # codes + bf16 scales (+ fp32 zero points for the 4-bit asymmetric cache) + q and out
+        per_tok = 2 * 128 + 2 * 2 if args.bits == 8 else 2 * 64 + 2 * 2 + 2 * 4
+        by = B * n_kv * ctx * per_tok + 2 * B * n_q * 128 * 2
         gbs = by / (ms * 1e-3) / 1e9
         emit("decode_attention_GBps", "GB/s", gbs, ms,
-             {"workload": "int8 decode attention", "streams": B, "q_heads": n_q, "kv_heads": n_kv, "context": ctx,
-              "l2": "cache far larger than L2"},
-             {"bound": "hbm", "kernel": "decode_attn_q8_kernel", "achieved": gbs, "peak": peak, "peak_source": peak_src,
+             {"workload": f"int{args.bits} decode attention", "streams": B, "q_heads": n_q, "kv_heads": n_kv, "context": ctx,
+              "l2": "cache far larger than L2", "context_tokens_per_s": B * ctx / (ms * 1e-3)},
+             {"bound": "hbm", "kernel": f"decode_attn_q{args.bits}_kernel", "achieved": gbs, "peak": peak, "peak_source": peak_src,
               "unit": "GB/s", "frac": gbs / peak, "traffic": None, "bytes": by}, launches)
         # budgeted step: H2O keeps 2048 tokens (256 recent + 1792 heavy) per (stream, KV head)
         acc = torch.rand(B * n_kv, ctx, device=dev)
@@ -570,6 +573,7 @@ def main():
     ap.add_argument("--streams", type=int, default=64)
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--bits", type=int, default=8, choices=[4, 8], help="decode workload: cache code width")
     ap.add_argument("--rows", type=int, default=262144)
     ap.add_argument("--shard-mode", default="peer", choices=["peer", "a2a"],
                     help="multi-GPU: peer = append kernel stores into the owner's pages over NVLink; a2a = pack + NCCL all_to_all")

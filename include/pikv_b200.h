@@ -339,11 +339,15 @@ typedef struct {
     float* scores; int32_t score_stride;
     void* workspace; size_t workspace_bytes;
     uint32_t* status;
+    const void* k_zp; const void* v_zp;   /* fp32 zero points, 4-bit asymmetric cache only */
 } pikv_decode_params;
 
 size_t pikv_decode_attn_workspace_bytes(int32_t B, int32_t n_q, int32_t n_kv, int32_t max_ctx, int32_t splits);
 int    pikv_decode_attn_default_splits(int32_t B, int32_t n_kv, int32_t max_ctx);
 int    pikv_decode_attn_q8(const pikv_decode_params* p, pikv_stream_t stream);
+/* The same over the 4-bit asymmetric cache (K = (code - zp) * scale, codes 0..15, two per byte):
+ * half the code bytes per token; k_zp / v_zp are required. */
+int    pikv_decode_attn_q4(const pikv_decode_params* p, pikv_stream_t stream);
 
 /* Same computation for callers that cannot allocate device memory at the point where they need
  * attention (a server that gave all of HBM to its own pool at start-up, a plug-in inside an

@@ -86,7 +86,7 @@ class DecodeParams(C.Structure):
         ("num_seqs", i32), ("max_pages", i32), ("num_pages", i32),
         ("k_codes", vp), ("v_codes", vp), ("k_scale", vp), ("v_scale", vp),
         ("splits", i32), ("lse", vp), ("scores", vp), ("score_stride", i32),
-        ("workspace", vp), ("workspace_bytes", sz), ("status", vp),
+        ("workspace", vp), ("workspace_bytes", sz), ("status", vp), ("k_zp", vp), ("v_zp", vp),
     ]
 
 
@@ -113,6 +113,7 @@ SIGNATURES = {
     "pikv_decode_attn_workspace_bytes": (sz, [i32, i32, i32, i32, i32]),
     "pikv_decode_attn_default_splits": (i32, [i32, i32, i32]),
     "pikv_decode_attn_q8": (i32, [C.POINTER(DecodeParams), vp]),
+    "pikv_decode_attn_q4": (i32, [C.POINTER(DecodeParams), vp]),
     "pikv_decode_attn_static_scratch_bytes": (sz, []),
     "pikv_decode_attn_q8_static": (i32, [C.POINTER(DecodeParams), vp]),
     "pikv_h2o_accumulate_attn": (i32, [vp, i32, vp, vp, i32, i32, i32, vp, i32, vp]),

@@ -154,9 +154,11 @@ class PagedKVCache(torch.nn.Module):
     def decode_attention(self, q: torch.Tensor, seq_ids: Optional[torch.Tensor] = None,
                          seq_len: Optional[torch.Tensor] = None, splits: int = 0, want_lse: bool = False,
                          scores: Optional[torch.Tensor] = None):
-        """softmax(q K^T / sqrt(128)) V over each stream's cached context; q [B, n_q, 128] bf16."""
-        if self.bits != 8 or not self.symmetric:
-            raise PikvError("decode_attention reads int8 symmetric caches")
+        """softmax(q K^T / sqrt(128)) V over each stream's cached context; q [B, n_q, 128] bf16.  Reads
+        int8 symmetric (pikv_decode_attn_q8) and 4-bit asymmetric (pikv_decode_attn_q4) caches."""
+        q8 = self.bits == 8 and self.symmetric
+        if not q8 and not (self.bits == 4 and not self.symmetric):
+            raise PikvError("decode_attention reads int8 symmetric and 4-bit asymmetric caches")
         q = _req(q, "q", torch.bfloat16)
         B, n_q, d = q.shape
         if d != HEAD_DIM:
@@ -180,7 +182,11 @@ class PagedKVCache(torch.nn.Module):
         p.splits, p.lse = splits, _p(lse)
         p.scores, p.score_stride = _p(scores), (scores.shape[-1] if scores is not None else 0)
         p.workspace, p.workspace_bytes, p.status = _p(ws), ws.numel(), _p(self.status)
-        check(lib().pikv_decode_attn_q8(C.byref(p), _stream()), "pikv_decode_attn_q8")
+        if q8:
+            check(lib().pikv_decode_attn_q8(C.byref(p), _stream()), "pikv_decode_attn_q8")
+        else:
+            p.k_zp, p.v_zp = _p(self.k_zp), _p(self.v_zp)
+            check(lib().pikv_decode_attn_q4(C.byref(p), _stream()), "pikv_decode_attn_q4")
         return (out, lse) if (want_lse or scores is not None) else out
 
     # -- eviction ------------------------------------------------------------------

@@ -284,15 +284,18 @@ def test_manager_sequence_matches_reference(dev):
 
 
 # ---------------------------------------------------------------- decode attention
-def fill_stream_cache(dev, B, n_kv, ctx, lens, seed):
+def fill_stream_cache(dev, B, n_kv, ctx, lens, seed, bits=8, symmetric=True, shift=0.0):
     import pikv_b200
     torch.manual_seed(seed)
-    cache = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)
+    cache = pikv_b200.PagedKVCache(B, ctx, n_kv, bits=bits, symmetric=symmetric, device=dev)
     # shuffle the physical pages so the page table is really used
     perm = torch.randperm(cache.num_pages, device=dev).to(torch.int32)
     cache.page_table.copy_(perm.view(B, -1))
-    K = torch.randn(B * ctx, n_kv * 128).bfloat16()
-    V = torch.randn(B * ctx, n_kv * 128).bfloat16()
+    K = (torch.randn(B * ctx, n_kv * 128) + shift).bfloat16()
+    V = (torch.randn(B * ctx, n_kv * 128) * (1.0 + shift) - shift).bfloat16()
+    if shift:
+        K[min(5, B * ctx - 1)] = 3.0      # constant rows: the reference's zero point runs into the millions
+        V[min(7, B * ctx - 1)] = -2.0
     seq = torch.arange(B, dtype=torch.int32).repeat_interleave(ctx)[:, None]
     pos = torch.arange(ctx, dtype=torch.int32).repeat(B)[:, None]
     cache.append(K.to(dev), V.to(dev), seq.to(dev), pos.to(dev))
@@ -321,6 +324,29 @@ def test_decode_attention_matches_oracle(dev, B, n_q, n_kv, ctx, splits):
         for h in range(n_q):
             s = (q[b, h].float().numpy() @ kd[b, h // g, : lens[b]].T) / np.sqrt(128.0)
             ref = np.log(np.exp(s - s.max()).sum()) + s.max()
+            assert abs(float(lse[b, h]) - ref) < 1e-3 * max(1.0, abs(ref))
+
+
+@pytest.mark.parametrize("B,n_q,n_kv,ctx,splits", [(2, 8, 2, 100, 1), (3, 8, 2, 1000, 3), (2, 4, 4, 257, 2),
+                                                    (2, 16, 2, 640, 0), (1, 32, 8, 4096, 4), (4, 2, 2, 48, 5)])
+def test_decode_attention_q4_matches_oracle(dev, B, n_q, n_kv, ctx, splits):
+    """4-bit asymmetric cache: the oracle attends over the dequantised (code - zp) * scale rows, so only the
+    kernel's arithmetic (f16 operands, zero point carried beside the tensor-core sums) is under test."""
+    rng = np.random.default_rng(ctx + 1)
+    lens = rng.integers(1, ctx + 1, B).astype(np.int32)
+    lens[0] = ctx
+    cache, kd, vd = fill_stream_cache(dev, B, n_kv, ctx, lens, ctx, bits=4, symmetric=False, shift=0.75)
+    q = torch.randn(B, n_q, 128).bfloat16()
+    out, lse = cache.decode_attention(q.to(dev), splits=splits, want_lse=True)
+    cache.check_status()
+    want, _ = O.decode_attention(q.float().numpy(), kd, vd, lens)
+    got = out.float().cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
+    g = n_q // n_kv
+    for b in range(B):
+        for h in range(n_q):
+            sc = (q[b, h].float().numpy() @ kd[b, h // g, : lens[b]].T) / np.sqrt(128.0)
+            ref = np.log(np.exp(sc - sc.max()).sum()) + sc.max()
             assert abs(float(lse[b, h]) - ref) < 1e-3 * max(1.0, abs(ref))
 
 
