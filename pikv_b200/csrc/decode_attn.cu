@@ -1,19 +1,16 @@
-// Decode attention over the int8 paged cache, dequantised in registers.
+// Decode attention over the quantised paged cache (8-bit symmetric or 4-bit asymmetric codes),
+// dequantised in registers.
 //
-// Grid (split, kv head, stream); 4 warps per CTA, each warp streams whole pages
-// (16 tokens x 128 channels of K and of V = 2 x 2 KiB plus 2 x 32 B of scales) of its
-// split through a private 4-stage ring in shared memory filled by bulk async copies
-// (cp.async.bulk + mbarrier transaction counts), so the bytes in flight do not depend on
-// registers.  Per page a warp does
-//   S[q, pos]   = Q[q, :] . Kcode[pos, :]      8 + 8 mma.m16n8k16 (f16 x f16 -> f32)
-//   s           = S * kscale[pos] * 2^e / sqrt(d)   (fp32, log2 domain for exp2f)
-//   online softmax over the positions, P kept in registers as the B operand of
-//   O^T[c, q]  += (Vcode[pos, c] * vscale[pos]) . P[q, pos]      8 mma.m16n8k16
-// int8 codes become f16 exactly with one byte-permute and one subtract per pair
-// (0x6400 | (code ^ 0x80) is 1024 + code + 128 in f16).  Q is scaled by a power of two so
-// that it is exact in f16.  The cache's chunk swizzle makes every 16-byte shared-memory
-// read of a fragment conflict-free.  Partial (O, m, l) of the 4 warps are merged in shared
-// memory; with more than one split a second kernel merges the splits.
+// Grid (split, kv head, stream); 4 warps per CTA, each warp streams whole pages (16 tokens x 128
+// channels of K and of V plus their scales and, for 4 bits, zero points) of its split through a
+// private ring in shared memory filled by bulk async copies (cp.async.bulk + mbarrier transaction
+// counts), so the bytes in flight do not depend on registers.  Per page a warp runs 8 + 8
+// mma.m16n8k16 (f16 x f16 -> f32) and an online softmax in the log2 domain; see decode_attn_kernel.
+// Codes become f16 exactly with one byte-permute (bytes: 0x6400 | (code ^ 0x80) is 1024 + code + 128)
+// or one AND-OR (nibbles: 0x6400 | n is 1024 + n).  Q is scaled by a power of two so that it is exact
+// in f16.  The cache's swizzle makes the 16-byte shared-memory reads of a fragment conflict-free.
+// Partial (O, m, l) of the 4 warps are merged in shared memory; with more than one split a second
+// kernel merges the splits.
 #include "common.cuh"
 
 #include <mutex>
@@ -22,9 +19,6 @@ namespace pikv {
 
 constexpr int DA_WARPS = 4;
 constexpr int DA_THREADS = DA_WARPS * 32;
-constexpr int DA_STAGES = 4;
-constexpr int DA_PAGE_BYTES = 16 * 128;                 // one page of one head, K or V
-constexpr int DA_STAGE_BYTES = 2 * DA_PAGE_BYTES + 64;  // K, V, 16 K scales, 16 V scales
 constexpr int DA_MAX_GROUP = 8;
 constexpr unsigned DA_WAIT_LIMIT = 1u << 24;            // mbarrier polls before giving up
 
@@ -97,15 +91,58 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
-    __half2 h = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-    return *reinterpret_cast<uint32_t*>(&h);
+
+// Geometry of one stage of a warp's ring: a page of one head.
+//   8 bit: 16 rows x 128 B of K, of V, 16 + 16 bf16 scales
+//   4 bit: 16 rows x 64 B (two codes per byte, low nibble = even channel, 8-byte units swizzled by
+//          row & 4), scales, 16 + 16 fp32 zero points
+template <int BITS> struct DAGeom;
+template <> struct DAGeom<8> { static constexpr int STAGES = 4, ROW = 128, PAGE = 16 * 128, STAGE = 2 * PAGE + 64; };
+template <> struct DAGeom<4> { static constexpr int STAGES = 6, ROW = 64, PAGE = 16 * 64, STAGE = 2 * PAGE + 64 + 128; };
+constexpr int DA_PBUF_BYTES = DA_MAX_GROUP * 16 * 2;    // per warp: P of one page, [head][position] f16
+
+template <int BITS>
+constexpr size_t da_smem_bytes() {
+    return (size_t)DA_WARPS * DAGeom<BITS>::STAGES * DAGeom<BITS>::STAGE + DA_WARPS * DAGeom<BITS>::STAGES * sizeof(uint64_t) +
+           DA_WARPS * DA_PBUF_BYTES;
 }
 
-__global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_q8_kernel(DecodeDev d) {
+// nibbles at bits SHIFT and SHIFT + 16 of w -> (1024 + n, 1024 + n') as two f16: one shift and one AND-OR
+template <int SHIFT>
+__device__ __forceinline__ uint32_t nib_pair_biased(uint32_t w) {
+    return ((w >> SHIFT) & 0x000f000fu) | 0x64006400u;
+}
+// ... and with the 1024 taken off again (exact)
+template <int SHIFT>
+__device__ __forceinline__ uint32_t nib_pair(uint32_t w) {
+    const uint32_t x = nib_pair_biased<SHIFT>(w);
+    __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&x), __half2half2(__ushort_as_half(0x6400)));
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+// two bytes of w selected by SEL -> (1024 + b, 1024 + b') as two f16
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t bytes_to_h2_biased(uint32_t w) { return __byte_perm(w, 0x64646464u, SEL); }
+
+// The legacy mma.sync path is what bounds this kernel on this GPU (one m16n8k16 holds a sub-core's tensor
+// pipe for about 32 cycles), so the shapes are chosen to waste as few of its rows as possible:
+//   S^T[pos, head] = Kcode[pos, :] . Q[head, :]    A = the page's 16 positions (all rows used), B = Q^T:
+//                                                  8 mma per page
+//   O^T[ch, head] += Vcode^T[ch, pos] . P'^T[pos, head]   A = 16 channels x 16 positions, 8 mma per page
+// The softmax runs on S^T (a thread owns positions r, r+8 of heads 2j, 2j+1); P goes through 256 bytes of
+// shared memory to become the B operand of the second product.  Nothing but exact integers enters the
+// tensor cores on the cache side:
+//   q . x   = kscale * (q . code - zp * sum(q))                        (zp = 0 for the 8-bit cache)
+//   P . x_c = sum_pos P' * (bias + code_c) - sum_pos P' * (bias + zp),  P' = P * vscale
+// where bias is what the byte/nibble -> f16 trick leaves on (1152 = 1024 + 128 for bytes, 1024 for
+// nibbles).  The second sum is the same for every channel: it is carried like the softmax denominator
+// (corr) and subtracted at the end.
+template <int BITS>
+__global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d) {
+    using GEO = DAGeom<BITS>;
+    constexpr int STAGES = GEO::STAGES, STAGE_BYTES = GEO::STAGE, PAGE_BYTES = GEO::PAGE, ROW = GEO::ROW;
     extern __shared__ __align__(128) unsigned char smem[];
-    // [warp][stage] rings, then the barriers
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)DA_WARPS * DA_STAGES * DA_STAGE_BYTES);
+    // [warp][stage] rings, the barriers, the P buffers
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)DA_WARPS * STAGES * STAGE_BYTES);
     __shared__ float ml_s[DA_WARPS][DA_MAX_GROUP][2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -123,11 +160,12 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_q8_kernel(DecodeDev
     // this warp's pages: p_begin + warp + DA_WARPS * i
     const int my_pages = (p_end - p_begin - warp + DA_WARPS - 1) / DA_WARPS;
 
-    unsigned char* ring = smem + (size_t)warp * DA_STAGES * DA_STAGE_BYTES;
-    const uint32_t bar0 = smem_u32(bars + warp * DA_STAGES);
+    unsigned char* ring = smem + (size_t)warp * STAGES * STAGE_BYTES;
+    __half* pbuf = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(bars + DA_WARPS * STAGES) + warp * DA_PBUF_BYTES);
+    const uint32_t bar0 = smem_u32(bars + warp * STAGES);
     if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < DA_STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -135,27 +173,32 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_q8_kernel(DecodeDev
 
     const int* pt_row = d.page_table + (size_t)(seq_ok ? seq : 0) * d.max_pages;
     auto issue = [&](int i) {   // lane 0 only: load this warp's i-th page into stage i % STAGES
-        const int s = i % DA_STAGES;
+        const int s = i % STAGES;
         int page = pt_row[p_begin + warp + DA_WARPS * i];
         if (page < 0 || page >= d.num_pages) {
             if (d.status) atomicOr(d.status, PIKV_ST_BAD_PAGE);
             page = 0;
         }
         const size_t prow = ((size_t)page * d.n_kv + h) * PIKV_PAGE_TOKENS;
-        const uint32_t dst = smem_u32(ring + (size_t)s * DA_STAGE_BYTES);
+        const uint32_t dst = smem_u32(ring + (size_t)s * STAGE_BYTES);
         const uint32_t bar = bar0 + 8 * s;
-        mbar_expect_tx(bar, DA_STAGE_BYTES);
-        bulk_g2s(dst, d.k_codes + prow * 128, DA_PAGE_BYTES, bar);
-        bulk_g2s(dst + DA_PAGE_BYTES, d.v_codes + prow * 128, DA_PAGE_BYTES, bar);
-        bulk_g2s(dst + 2 * DA_PAGE_BYTES, d.k_scale + prow, 32, bar);
-        bulk_g2s(dst + 2 * DA_PAGE_BYTES + 32, d.v_scale + prow, 32, bar);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        bulk_g2s(dst, d.k_codes + prow * ROW, PAGE_BYTES, bar);
+        bulk_g2s(dst + PAGE_BYTES, d.v_codes + prow * ROW, PAGE_BYTES, bar);
+        bulk_g2s(dst + 2 * PAGE_BYTES, d.k_scale + prow, 32, bar);
+        bulk_g2s(dst + 2 * PAGE_BYTES + 32, d.v_scale + prow, 32, bar);
+        if (BITS == 4) {
+            bulk_g2s(dst + 2 * PAGE_BYTES + 64, d.k_zp + prow, 64, bar);
+            bulk_g2s(dst + 2 * PAGE_BYTES + 128, d.v_zp + prow, 64, bar);
+        }
     };
     if (lane == 0)
-        for (int i = 0; i < min(my_pages, DA_STAGES); ++i) issue(i);
+        for (int i = 0; i < min(my_pages, STAGES); ++i) issue(i);
 
-    // ---- Q fragments: thread (r, j) holds Q[head r][32j .. 32j+32) as 16 f16 pairs ----
+    // ---- Q as the B operand: thread (r, j) holds Q[head r][32j .. 32j+32) as 16 f16 pairs ----
     uint32_t qf[16];
-    float qmul = 0.f;   // 2^e / sqrt(d) * log2(e): turns the integer dot product into log2-domain scores
+    float qm0, qm1;           // per head 2j, 2j+1: 2^e / sqrt(d) * log2(e), integer dot product -> log2-domain score
+    float qs0 = 0.f, qs1 = 0.f;   // 4 bit: sum of the query over its 128 channels
     {
         float qv[32];
         if (r < G) {
@@ -178,11 +221,28 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_q8_kernel(DecodeDev
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
         int e = 0;
-        if (amax > 32768.f) e = ilogbf(amax) - 14;
+        if (amax > 32768.f) e = ilogbf(amax) - 14;     // a power of two keeps the bf16 query exact in f16
         const float down = ldexpf(1.0f, -e);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) qf[i] = pack_h2(qv[2 * i] * down, qv[2 * i + 1] * down);
-        qmul = ldexpf(1.0f, e) * 0.08838834764831845f * 1.4426950408889634f;
+        for (int i = 0; i < 16; ++i) {
+            // 8 bit: consecutive channel pairs; 4 bit: pairs (c, c + 4) inside each group of 8, the order in
+            // which nib_pair() takes nibbles out of a word
+            const int c = BITS == 8 ? 2 * i : 8 * (i >> 2) + (i & 3);
+            const int c2 = BITS == 8 ? c + 1 : c + 4;
+            qf[i] = pack_h2(qv[c] * down, qv[c2] * down);
+        }
+        const float qmul = ldexpf(1.0f, e) * 0.08838834764831845f * 1.4426950408889634f;
+        qm0 = __shfl_sync(0xffffffffu, qmul, 8 * j);          // lane of (head 2j, j = 0)
+        qm1 = __shfl_sync(0xffffffffu, qmul, 8 * j + 4);
+        if (BITS == 4) {
+            float qs = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) qs += qv[i] * down;
+            qs += __shfl_xor_sync(0xffffffffu, qs, 1);
+            qs += __shfl_xor_sync(0xffffffffu, qs, 2);
+            qs0 = __shfl_sync(0xffffffffu, qs, 8 * j);
+            qs1 = __shfl_sync(0xffffffffu, qs, 8 * j + 4);
+        }
     }
 
     float o[8][4];
@@ -190,431 +250,193 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_q8_kernel(DecodeDev
     for (int m = 0; m < 8; ++m)
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[m][c] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    // running max, denominator and carried bias term of heads 2j and 2j+1 (this thread's share of the positions)
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f, corr0 = 0.f, corr1 = 0.f;
     bool timed_out = false;
     int i = 0;
 
     for (; i < my_pages; ++i) {
-        const int s = i % DA_STAGES;
-        const uint32_t parity = (uint32_t)(i / DA_STAGES) & 1u;
+        const int s = i % STAGES;
+        const uint32_t parity = (uint32_t)(i / STAGES) & 1u;
         if (!mbar_wait(bar0 + 8 * s, parity)) {
             timed_out = true;
             break;
         }
-        const unsigned char* st = ring + (size_t)s * DA_STAGE_BYTES;
+        const unsigned char* st = ring + (size_t)s * STAGE_BYTES;
         const int page_idx = p_begin + warp + DA_WARPS * i;
         const int pos0 = page_idx * PIKV_PAGE_TOKENS;
 
-        // ---- S = Q . K^T for the page's 16 positions (two blocks of 8) ----
-        float sacc[2][4];
+        // ---- S^T = Kcode . Q^T: rows r and r+8 of the page against all heads, two accumulator chains ----
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        if (BITS == 8) {
+            const unsigned char* klo = st + r * 128;
+            const unsigned char* khi = st + (r + 8) * 128;           // same swizzle key: (r + 8) & 7 = r
+            const uint4 la = *reinterpret_cast<const uint4*>(klo + 16 * ((2 * j) ^ r));
+            const uint4 lb = *reinterpret_cast<const uint4*>(klo + 16 * ((2 * j + 1) ^ r));
+            const uint4 ha = *reinterpret_cast<const uint4*>(khi + 16 * ((2 * j) ^ r));
+            const uint4 hb = *reinterpret_cast<const uint4*>(khi + 16 * ((2 * j + 1) ^ r));
+            const uint32_t wl[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+            const uint32_t wh[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
 #pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
-            sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
-            const int row = 8 * nb + r;
-            const unsigned char* krow = st + row * 128;
-            uint4 ka = *reinterpret_cast<const uint4*>(krow + 16 * ((2 * j) ^ r));
-            uint4 kb = *reinterpret_cast<const uint4*>(krow + 16 * ((2 * j + 1) ^ r));
-            uint32_t kw[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+            for (int kk = 0; kk < 8; ++kk) {
+                const uint32_t a = wl[kk] ^ 0x80808080u, c = wh[kk] ^ 0x80808080u;
+                mma_f16((kk & 1) ? sb : sa, bytes_to_h2<0x4140>(a), bytes_to_h2<0x4140>(c), bytes_to_h2<0x4342>(a),
+                        bytes_to_h2<0x4342>(c), qf[2 * kk], qf[2 * kk + 1]);
+            }
+        } else {
+            const unsigned char* klo = st + r * 64;
+            const unsigned char* khi = st + (r + 8) * 64;            // (r + 8) & 4 = r & 4
+            const uint4 lq = *reinterpret_cast<const uint4*>(klo + 8 * ((2 * j) ^ (r & 4)));
+            const uint4 hq = *reinterpret_cast<const uint4*>(khi + 8 * ((2 * j) ^ (r & 4)));
+            const uint32_t wl[4] = {lq.x, lq.y, lq.z, lq.w};
+            const uint32_t wh[4] = {hq.x, hq.y, hq.z, hq.w};
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                const uint32_t w = kw[ks] ^ 0x80808080u;
-                mma_f16(sacc[nb], qf[2 * ks], 0u, qf[2 * ks + 1], 0u, bytes_to_h2<0x4140>(w), bytes_to_h2<0x4342>(w));
+            for (int wq = 0; wq < 4; ++wq) {
+                mma_f16(sa, nib_pair<0>(wl[wq]), nib_pair<0>(wh[wq]), nib_pair<4>(wl[wq]), nib_pair<4>(wh[wq]), qf[4 * wq],
+                        qf[4 * wq + 1]);
+                mma_f16(sb, nib_pair<8>(wl[wq]), nib_pair<8>(wh[wq]), nib_pair<12>(wl[wq]), nib_pair<12>(wh[wq]),
+                        qf[4 * wq + 2], qf[4 * wq + 3]);
             }
         }
-        // scales of positions {2j, 2j+1} and {8+2j, 9+2j}
-        const uint32_t* ksc = reinterpret_cast<const uint32_t*>(st + 2 * DA_PAGE_BYTES);
-        const uint32_t* vsc = reinterpret_cast<const uint32_t*>(st + 2 * DA_PAGE_BYTES + 32);
-        float ks0, ks1, ks2, ks3;
-        bf16x2_to_f32(ksc[j], ks0, ks1);
-        bf16x2_to_f32(ksc[4 + j], ks2, ks3);
-        float t[4];
-        t[0] = sacc[0][0] * (ks0 * qmul);
-        t[1] = sacc[0][1] * (ks1 * qmul);
-        t[2] = sacc[1][0] * (ks2 * qmul);
-        t[3] = sacc[1][1] * (ks3 * qmul);
-        const int pp[4] = {2 * j, 2 * j + 1, 8 + 2 * j, 9 + 2 * j};
+        // this thread: positions r (t[0], t[1]) and r+8 (t[2], t[3]) of heads 2j, 2j+1
+        const uint16_t* ksc = reinterpret_cast<const uint16_t*>(st + 2 * PAGE_BYTES);
+        const uint16_t* vsc = reinterpret_cast<const uint16_t*>(st + 2 * PAGE_BYTES + 32);
+        const float ks_lo = __uint_as_float((uint32_t)ksc[r] << 16), ks_hi = __uint_as_float((uint32_t)ksc[r + 8] << 16);
+        float t[4] = {sa[0] + sb[0], sa[1] + sb[1], sa[2] + sb[2], sa[3] + sb[3]};
+        float vw_lo = 0.f, vw_hi = 0.f;      // 4 bit: bias + zero point of V at the two positions
+        if (BITS == 4) {
+            const float* kzp = reinterpret_cast<const float*>(st + 2 * PAGE_BYTES + 64);
+            const float* vzp = reinterpret_cast<const float*>(st + 2 * PAGE_BYTES + 128);
+            const float z_lo = kzp[r], z_hi = kzp[r + 8];
+            t[0] -= z_lo * qs0; t[1] -= z_lo * qs1; t[2] -= z_hi * qs0; t[3] -= z_hi * qs1;
+            vw_lo = 1024.f + vzp[r];
+            vw_hi = 1024.f + vzp[r + 8];
+        }
+        t[0] *= ks_lo * qm0; t[1] *= ks_lo * qm1; t[2] *= ks_hi * qm0; t[3] *= ks_hi * qm1;
         if (pos0 + PIKV_PAGE_TOKENS > len) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (pos0 + pp[c] >= len) t[c] = -INFINITY;
+            if (pos0 + r >= len) t[0] = t[1] = -INFINITY;
+            if (pos0 + r + 8 >= len) t[2] = t[3] = -INFINITY;
         }
-        if (d.scores && r < G) {
-            float* srow = d.scores + ((size_t)b * d.n_q + (size_t)h * G + r) * d.score_stride + pos0;
+        if (d.scores) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (pos0 + pp[c] < len && pos0 + pp[c] < d.score_stride) srow[pp[c]] = t[c] * 0.6931471805599453f;
+            for (int c = 0; c < 4; ++c) {
+                const int hh = 2 * j + (c & 1), pp = r + 8 * (c >> 1);
+                if (hh < G && pos0 + pp < len && pos0 + pp < d.score_stride)
+                    d.scores[((size_t)b * d.n_q + (size_t)h * G + hh) * d.score_stride + pos0 + pp] = t[c] * 0.6931471805599453f;
+            }
         }
-        // ---- online softmax (log2 domain) ----
-        float mx = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = exp2f(m_run - m_use);
-        float p[4];
+        // ---- online softmax (log2 domain); the 8 lanes with the same j hold the 16 positions of a head pair ----
+        float mx0 = fmaxf(t[0], t[2]), mx1 = fmaxf(t[1], t[3]);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) p[c] = exp2f(t[c] - m_use);
-        l_run = l_run * alpha + ((p[0] + p[1]) + (p[2] + p[3]));
-        m_run = m_new;
-        const uint32_t pb0 = pack_h2(p[0], p[1]), pb1 = pack_h2(p[2], p[3]);
+        for (int sh = 4; sh < 32; sh <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+        }
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = (mn0 == -INFINITY) ? 0.f : mn0, mu1 = (mn1 == -INFINITY) ? 0.f : mn1;
+        const float al0 = exp2f(m0 - mu0), al1 = exp2f(m1 - mu1);
+        const float p0 = exp2f(t[0] - mu0), p1 = exp2f(t[1] - mu1), p2 = exp2f(t[2] - mu0), p3 = exp2f(t[3] - mu1);
+        l0 = l0 * al0 + (p0 + p2);
+        l1 = l1 * al1 + (p1 + p3);
+        m0 = mn0;
+        m1 = mn1;
+        // P' = P * vscale, rounded to f16 as the tensor cores will see it
+        const float vs_lo = __uint_as_float((uint32_t)vsc[r] << 16), vs_hi = __uint_as_float((uint32_t)vsc[r + 8] << 16);
+        const __half h0 = __float2half_rn(p0 * vs_lo), h1 = __float2half_rn(p1 * vs_lo);
+        const __half h2 = __float2half_rn(p2 * vs_hi), h3 = __float2half_rn(p3 * vs_hi);
+        if (BITS == 8) {
+            corr0 = corr0 * al0 + (__half2float(h0) + __half2float(h2));      // x 1152 at the end
+            corr1 = corr1 * al1 + (__half2float(h1) + __half2float(h3));
+        } else {
+            corr0 = corr0 * al0 + (__half2float(h0) * vw_lo + __half2float(h2) * vw_hi);
+            corr1 = corr1 * al1 + (__half2float(h1) * vw_lo + __half2float(h3) * vw_hi);
+        }
+        pbuf[(2 * j) * 16 + r] = h0;
+        pbuf[(2 * j + 1) * 16 + r] = h1;
+        pbuf[(2 * j) * 16 + r + 8] = h2;
+        pbuf[(2 * j + 1) * 16 + r + 8] = h3;
         // rescale O: this thread's columns are query heads 2j and 2j+1
-        const float al0 = __shfl_sync(0xffffffffu, alpha, (2 * j) * 4);
-        const float al1 = __shfl_sync(0xffffffffu, alpha, (2 * j + 1) * 4);
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
             o[m][0] *= al0; o[m][1] *= al1; o[m][2] *= al0; o[m][3] *= al1;
         }
-        // ---- O^T += (Vcode * vscale)^T . P^T ----
-        const unsigned char* vbase = st + DA_PAGE_BYTES;
-        uint4 v0 = *reinterpret_cast<const uint4*>(vbase + pp[0] * 128 + 16 * (r ^ (pp[0] & 7)));
-        uint4 v1 = *reinterpret_cast<const uint4*>(vbase + pp[1] * 128 + 16 * (r ^ (pp[1] & 7)));
-        uint4 v2 = *reinterpret_cast<const uint4*>(vbase + pp[2] * 128 + 16 * (r ^ (pp[2] & 7)));
-        uint4 v3 = *reinterpret_cast<const uint4*>(vbase + pp[3] * 128 + 16 * (r ^ (pp[3] & 7)));
-        const uint32_t vw0[4] = {v0.x ^ 0x80808080u, v0.y ^ 0x80808080u, v0.z ^ 0x80808080u, v0.w ^ 0x80808080u};
-        const uint32_t vw1[4] = {v1.x ^ 0x80808080u, v1.y ^ 0x80808080u, v1.z ^ 0x80808080u, v1.w ^ 0x80808080u};
-        const uint32_t vw2[4] = {v2.x ^ 0x80808080u, v2.y ^ 0x80808080u, v2.z ^ 0x80808080u, v2.w ^ 0x80808080u};
-        const uint32_t vw3[4] = {v3.x ^ 0x80808080u, v3.y ^ 0x80808080u, v3.z ^ 0x80808080u, v3.w ^ 0x80808080u};
-        float vs0, vs1, vs2, vs3;
-        bf16x2_to_f32(vsc[j], vs0, vs1);
-        bf16x2_to_f32(vsc[4 + j], vs2, vs3);
-        const uint32_t vsa = pack_h2(vs0, vs1), vsb = pack_h2(vs2, vs3);
+        __syncwarp();
+        // B operand of the second product: P'[head r][positions 2j, 2j+1] and [2j+8, 2j+9]
+        const uint32_t pb0 = *reinterpret_cast<const uint32_t*>(pbuf + r * 16 + 2 * j);
+        const uint32_t pb1 = *reinterpret_cast<const uint32_t*>(pbuf + r * 16 + 2 * j + 8);
+        // ---- O^T += (bias + Vcode)^T . P'^T ----
+        const unsigned char* vbase = st + PAGE_BYTES;
+        const int pp[4] = {2 * j, 2 * j + 1, 8 + 2 * j, 9 + 2 * j};
+        if (BITS == 8) {
+            const uint4 v0 = *reinterpret_cast<const uint4*>(vbase + pp[0] * 128 + 16 * (r ^ (pp[0] & 7)));
+            const uint4 v1 = *reinterpret_cast<const uint4*>(vbase + pp[1] * 128 + 16 * (r ^ (pp[1] & 7)));
+            const uint4 v2 = *reinterpret_cast<const uint4*>(vbase + pp[2] * 128 + 16 * (r ^ (pp[2] & 7)));
+            const uint4 v3 = *reinterpret_cast<const uint4*>(vbase + pp[3] * 128 + 16 * (r ^ (pp[3] & 7)));
+            const uint32_t vw0[4] = {v0.x, v0.y, v0.z, v0.w}, vw1[4] = {v1.x, v1.y, v1.z, v1.w};
+            const uint32_t vw2[4] = {v2.x, v2.y, v2.z, v2.w}, vw3[4] = {v3.x, v3.y, v3.z, v3.w};
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            const int wi = m >> 1;
-            // bytes (2*(m&1)) and (2*(m&1)+1) of the two positions of a pair, interleaved
-            const uint32_t ta = (m & 1) ? __byte_perm(vw0[wi], vw1[wi], 0x7362) : __byte_perm(vw0[wi], vw1[wi], 0x5140);
-            const uint32_t tb = (m & 1) ? __byte_perm(vw2[wi], vw3[wi], 0x7362) : __byte_perm(vw2[wi], vw3[wi], 0x5140);
-            const uint32_t a0 = hmul2_u32(bytes_to_h2<0x4140>(ta), vsa);   // channel 16r+2m,   positions 2j, 2j+1
-            const uint32_t a1 = hmul2_u32(bytes_to_h2<0x4342>(ta), vsa);   // channel 16r+2m+1
-            const uint32_t a2 = hmul2_u32(bytes_to_h2<0x4140>(tb), vsb);   // channel 16r+2m,   positions 8+2j, 9+2j
-            const uint32_t a3 = hmul2_u32(bytes_to_h2<0x4342>(tb), vsb);
-            mma_f16(o[m], a0, a1, a2, a3, pb0, pb1);
+            for (int m = 0; m < 8; ++m) {
+                const int wi = m >> 1;
+                // bytes (2*(m&1)) and (2*(m&1)+1) of the two positions of a pair, interleaved, then code + 128
+                const uint32_t ta = ((m & 1) ? __byte_perm(vw0[wi], vw1[wi], 0x7362) : __byte_perm(vw0[wi], vw1[wi], 0x5140)) ^ 0x80808080u;
+                const uint32_t tb = ((m & 1) ? __byte_perm(vw2[wi], vw3[wi], 0x7362) : __byte_perm(vw2[wi], vw3[wi], 0x5140)) ^ 0x80808080u;
+                // channel 16r+2m (a0, a2) and 16r+2m+1 (a1, a3); positions 2j, 2j+1 (a0, a1) and 8+2j, 9+2j (a2, a3)
+                mma_f16(o[m], bytes_to_h2_biased<0x4140>(ta), bytes_to_h2_biased<0x4342>(ta), bytes_to_h2_biased<0x4140>(tb),
+                        bytes_to_h2_biased<0x4342>(tb), pb0, pb1);
+            }
+        } else {
+            // channels 16r .. 16r+15 of the four positions: one 8-byte unit each
+            const uint2 v0 = *reinterpret_cast<const uint2*>(vbase + pp[0] * 64 + 8 * (r ^ (pp[0] & 4)));
+            const uint2 v1 = *reinterpret_cast<const uint2*>(vbase + pp[1] * 64 + 8 * (r ^ (pp[1] & 4)));
+            const uint2 v2 = *reinterpret_cast<const uint2*>(vbase + pp[2] * 64 + 8 * (r ^ (pp[2] & 4)));
+            const uint2 v3 = *reinterpret_cast<const uint2*>(vbase + pp[3] * 64 + 8 * (r ^ (pp[3] & 4)));
+#pragma unroll
+            for (int hb = 0; hb < 4; ++hb) {
+                // bytes 2hb', 2hb'+1 of word wq of both positions of a pair: (p.b, p.b', p'.b, p'.b')
+                const int wq = hb >> 1;
+                const uint32_t sel = (hb & 1) ? 0x7632u : 0x5410u;
+                const uint32_t ga = __byte_perm(wq ? v0.y : v0.x, wq ? v1.y : v1.x, sel);
+                const uint32_t gb = __byte_perm(wq ? v2.y : v2.x, wq ? v3.y : v3.x, sel);
+                const int m = 2 * hb;   // byte m of the unit: channels 16r+2m (low nibble), 16r+2m+1 (high nibble)
+                mma_f16(o[m], nib_pair_biased<0>(ga), nib_pair_biased<4>(ga), nib_pair_biased<0>(gb), nib_pair_biased<4>(gb), pb0, pb1);
+                mma_f16(o[m + 1], nib_pair_biased<8>(ga), nib_pair_biased<12>(ga), nib_pair_biased<8>(gb), nib_pair_biased<12>(gb), pb0,
+                        pb1);
+            }
         }
         __syncwarp();
-        if (lane == 0 && i + DA_STAGES < my_pages) issue(i + DA_STAGES);
+        if (lane == 0 && i + STAGES < my_pages) issue(i + STAGES);
     }
     if (timed_out) {
         // give the copies already issued one more bounded chance to land before the ring is reused
         if (lane == 0 && d.status) atomicOr(d.status, PIKV_ST_WAIT_TIMEOUT);
-        for (int ii = i; ii < min(my_pages, i + DA_STAGES); ++ii)
-            (void)mbar_wait(bar0 + 8 * (ii % DA_STAGES), (uint32_t)(ii / DA_STAGES) & 1u);
+        for (int ii = i; ii < min(my_pages, i + STAGES); ++ii)
+            (void)mbar_wait(bar0 + 8 * (ii % STAGES), (uint32_t)(ii / STAGES) & 1u);
     }
 
-    // ---- merge the 4 warps ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    __syncthreads();   // every warp is done with its ring; reuse it as the merge buffer
-    float* mo = reinterpret_cast<float*>(smem);   // [warp][q][128]
-    if (j == 0 && r < DA_MAX_GROUP) {
-        ml_s[warp][r][0] = m_run;
-        ml_s[warp][r][1] = l_run;
+    // ---- denominators and the carried bias term: sum over the 8 lanes of a head pair ----
+#pragma unroll
+    for (int sh = 4; sh < 32; sh <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
+        corr0 += __shfl_xor_sync(0xffffffffu, corr0, sh);
+        corr1 += __shfl_xor_sync(0xffffffffu, corr1, sh);
+    }
+    if (BITS == 8) {
+        corr0 *= 1152.f;
+        corr1 *= 1152.f;
     }
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
-        const int ch = 16 * r + 2 * m;
-        float* base = mo + (size_t)warp * DA_MAX_GROUP * 128;
-        base[(2 * j) * 128 + ch] = o[m][0];
-        base[(2 * j + 1) * 128 + ch] = o[m][1];
-        base[(2 * j) * 128 + ch + 1] = o[m][2];
-        base[(2 * j + 1) * 128 + ch + 1] = o[m][3];
-    }
-    __syncthreads();
-    const int ch = tid;   // 128 threads = 128 channels
-    for (int qh = 0; qh < G; ++qh) {
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < DA_WARPS; ++w) M = fmaxf(M, ml_s[w][qh][0]);
-        float acc = 0.f, l = 0.f;
-#pragma unroll
-        for (int w = 0; w < DA_WARPS; ++w) {
-            const float mw = ml_s[w][qh][0];
-            const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-            acc += mo[((size_t)w * DA_MAX_GROUP + qh) * 128 + ch] * sc;
-            l += ml_s[w][qh][1] * sc;
-        }
-        const size_t bq = (size_t)b * d.n_q + (size_t)h * G + qh;
-        if (d.splits == 1) {
-            d.out[bq * 128 + ch] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-            if (ch == 0 && d.lse) d.lse[bq] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
-        } else {
-            d.part_o[(bq * d.splits + split) * 128 + ch] = acc;
-            if (ch == 0) {
-                d.part_ml[(bq * d.splits + split) * 2 + 0] = M;
-                d.part_ml[(bq * d.splits + split) * 2 + 1] = l;
-            }
-        }
-    }
-}
-
-// ---- 4-bit asymmetric cache ---------------------------------------------------------------------------
-// Same structure over half the bytes.  A page of one head is 16 rows of 64 bytes (two codes per byte,
-// low nibble = even channel, 8-byte units swizzled by row & 4) plus bf16 scales and fp32 zero points.
-// The zero point never enters the tensor-core operands: with x = (code - zp) * scale,
-//   q . x   = scale * (q . code - zp * sum(q))            (sum(q) once per query head)
-//   P . x_c = sum_pos P * scale * code_c - sum_pos P * scale * zp
-// and the second sum does not depend on the channel: it is carried like the softmax denominator and
-// subtracted from every channel at the end.  Nibbles become f16 exactly (0x6400 | n is 1024 + n).
-constexpr int DA4_STAGES = 6;
-constexpr int DA4_PAGE_BYTES = 16 * 64;
-constexpr int DA4_STAGE_BYTES = 2 * DA4_PAGE_BYTES + 64 + 128;   // K, V, scales (2 x 32 B), zero points (2 x 64 B)
-
-template <uint32_t SEL>
-__device__ __forceinline__ uint32_t nibs_to_h2(uint32_t u) {
-    uint32_t x = __byte_perm(u, 0x64646464u, SEL);                  // (1024 + n, 1024 + n')
-    __half2 h = __hsub2(*reinterpret_cast<__half2*>(&x), __half2half2(__ushort_as_half(0x6400)));
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-
-__global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_q4_kernel(DecodeDev d) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    // [warp][stage] rings, then the barriers
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)DA_WARPS * DA4_STAGES * DA4_STAGE_BYTES);
-    __shared__ float ml_s[DA_WARPS][DA_MAX_GROUP][2];
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = lane >> 2, j = lane & 3;
-    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int G = d.G;
-    const int seq = d.seq_ids ? d.seq_ids[b] : b;
-    const bool seq_ok = seq >= 0 && seq < d.num_seqs;
-    int len = seq_ok ? d.seq_len[b] : 0;
-    len = max(0, min(len, d.max_pages * PIKV_PAGE_TOKENS));
-    if (!seq_ok && tid == 0 && d.status) atomicOr(d.status, PIKV_ST_BAD_SEQ);
-    const int pages_total = (len + PIKV_PAGE_TOKENS - 1) / PIKV_PAGE_TOKENS;
-    const int pps = (pages_total + d.splits - 1) / d.splits;
-    const int p_begin = min(pages_total, split * pps), p_end = min(pages_total, p_begin + pps);
-    // this warp's pages: p_begin + warp + DA_WARPS * i
-    const int my_pages = (p_end - p_begin - warp + DA_WARPS - 1) / DA_WARPS;
-
-    unsigned char* ring = smem + (size_t)warp * DA4_STAGES * DA4_STAGE_BYTES;
-    const uint32_t bar0 = smem_u32(bars + warp * DA4_STAGES);
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < DA4_STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncthreads();
-
-    const int* pt_row = d.page_table + (size_t)(seq_ok ? seq : 0) * d.max_pages;
-    auto issue = [&](int i) {   // lane 0 only: load this warp's i-th page into stage i % STAGES
-        const int s = i % DA4_STAGES;
-        int page = pt_row[p_begin + warp + DA_WARPS * i];
-        if (page < 0 || page >= d.num_pages) {
-            if (d.status) atomicOr(d.status, PIKV_ST_BAD_PAGE);
-            page = 0;
-        }
-        const size_t prow = ((size_t)page * d.n_kv + h) * PIKV_PAGE_TOKENS;
-        const uint32_t dst = smem_u32(ring + (size_t)s * DA4_STAGE_BYTES);
-        const uint32_t bar = bar0 + 8 * s;
-        mbar_expect_tx(bar, DA4_STAGE_BYTES);
-        bulk_g2s(dst, d.k_codes + prow * 64, DA4_PAGE_BYTES, bar);
-        bulk_g2s(dst + DA4_PAGE_BYTES, d.v_codes + prow * 64, DA4_PAGE_BYTES, bar);
-        bulk_g2s(dst + 2 * DA4_PAGE_BYTES, d.k_scale + prow, 32, bar);
-        bulk_g2s(dst + 2 * DA4_PAGE_BYTES + 32, d.v_scale + prow, 32, bar);
-        bulk_g2s(dst + 2 * DA4_PAGE_BYTES + 64, d.k_zp + prow, 64, bar);
-        bulk_g2s(dst + 2 * DA4_PAGE_BYTES + 128, d.v_zp + prow, 64, bar);
-    };
-    if (lane == 0)
-        for (int i = 0; i < min(my_pages, DA4_STAGES); ++i) issue(i);
-
-    // ---- Q fragments: thread (r, j) holds Q[head r][32j .. 32j+32) as 16 f16 pairs ----
-    uint32_t qf[16];
-    float qmul = 0.f;   // 2^e / sqrt(d) * log2(e): turns the integer dot product into log2-domain scores
-    float qsum = 0.f;
-    {
-        float qv[32];
-        if (r < G) {
-            const __nv_bfloat16* qp = d.q + ((size_t)b * d.n_q + (size_t)h * G + r) * 128 + 32 * j;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint4 w = __ldg(reinterpret_cast<const uint4*>(qp) + i);
-                bf16x2_to_f32(w.x, qv[8 * i + 0], qv[8 * i + 1]);
-                bf16x2_to_f32(w.y, qv[8 * i + 2], qv[8 * i + 3]);
-                bf16x2_to_f32(w.z, qv[8 * i + 4], qv[8 * i + 5]);
-                bf16x2_to_f32(w.w, qv[8 * i + 6], qv[8 * i + 7]);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) qv[i] = 0.f;
-        }
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(qv[i]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        int e = 0;
-        if (amax > 32768.f) e = ilogbf(amax) - 14;
-        const float down = ldexpf(1.0f, -e);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) qf[i] = pack_h2(qv[2 * i] * down, qv[2 * i + 1] * down);
-        qmul = ldexpf(1.0f, e) * 0.08838834764831845f * 1.4426950408889634f;
-        // sum of the (scaled, f16-exact) query over all 128 channels of head r
-        float qs = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) qs += qv[i] * down;
-        qs += __shfl_xor_sync(0xffffffffu, qs, 1);
-        qs += __shfl_xor_sync(0xffffffffu, qs, 2);
-        qsum = qs;
-    }
-    float corr = 0.f;    // sum over positions of P * vscale * vzp for head r (this thread's 4 positions per page)
-
-    float o[8][4];
-#pragma unroll
-    for (int m = 0; m < 8; ++m)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) o[m][c] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    bool timed_out = false;
-    int i = 0;
-
-    for (; i < my_pages; ++i) {
-        const int s = i % DA4_STAGES;
-        const uint32_t parity = (uint32_t)(i / DA4_STAGES) & 1u;
-        if (!mbar_wait(bar0 + 8 * s, parity)) {
-            timed_out = true;
-            break;
-        }
-        const unsigned char* st = ring + (size_t)s * DA4_STAGE_BYTES;
-        const int page_idx = p_begin + warp + DA_WARPS * i;
-        const int pos0 = page_idx * PIKV_PAGE_TOKENS;
-
-        // ---- S = Q . K^T for the page's 16 positions (two blocks of 8) ----
-        float sacc[2][4];
-#pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
-            sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
-            const int row = 8 * nb + r;
-            const unsigned char* krow = st + row * 64;
-            // channels 32j .. 32j+31 of this row: units 2j, 2j+1 (the swizzle keeps the pair together)
-            uint4 kq = *reinterpret_cast<const uint4*>(krow + 8 * ((2 * j) ^ (row & 4)));
-            const uint32_t kw[4] = {kq.x, kq.y, kq.z, kq.w};
-#pragma unroll
-            for (int wq = 0; wq < 4; ++wq) {
-                const uint32_t lo = kw[wq] & 0x0f0f0f0fu, hi = (kw[wq] >> 4) & 0x0f0f0f0fu;
-                const uint32_t u01 = __byte_perm(lo, hi, 0x5140);   // (ch0, ch1, ch2, ch3) of this word
-                const uint32_t u23 = __byte_perm(lo, hi, 0x7362);   // (ch4, ch5, ch6, ch7)
-                mma_f16(sacc[nb], qf[4 * wq], 0u, qf[4 * wq + 1], 0u, nibs_to_h2<0x4140>(u01), nibs_to_h2<0x4342>(u01));
-                mma_f16(sacc[nb], qf[4 * wq + 2], 0u, qf[4 * wq + 3], 0u, nibs_to_h2<0x4140>(u23), nibs_to_h2<0x4342>(u23));
-            }
-        }
-        // scales of positions {2j, 2j+1} and {8+2j, 9+2j}
-        const uint32_t* ksc = reinterpret_cast<const uint32_t*>(st + 2 * DA4_PAGE_BYTES);
-        const uint32_t* vsc = reinterpret_cast<const uint32_t*>(st + 2 * DA4_PAGE_BYTES + 32);
-        const float* kzp = reinterpret_cast<const float*>(st + 2 * DA4_PAGE_BYTES + 64);
-        const float* vzp = reinterpret_cast<const float*>(st + 2 * DA4_PAGE_BYTES + 128);
-        float ks0, ks1, ks2, ks3;
-        bf16x2_to_f32(ksc[j], ks0, ks1);
-        bf16x2_to_f32(ksc[4 + j], ks2, ks3);
-        float t[4];
-        const int pp[4] = {2 * j, 2 * j + 1, 8 + 2 * j, 9 + 2 * j};
-        t[0] = (sacc[0][0] - kzp[pp[0]] * qsum) * (ks0 * qmul);
-        t[1] = (sacc[0][1] - kzp[pp[1]] * qsum) * (ks1 * qmul);
-        t[2] = (sacc[1][0] - kzp[pp[2]] * qsum) * (ks2 * qmul);
-        t[3] = (sacc[1][1] - kzp[pp[3]] * qsum) * (ks3 * qmul);
-        if (pos0 + PIKV_PAGE_TOKENS > len) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (pos0 + pp[c] >= len) t[c] = -INFINITY;
-        }
-        if (d.scores && r < G) {
-            float* srow = d.scores + ((size_t)b * d.n_q + (size_t)h * G + r) * d.score_stride + pos0;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (pos0 + pp[c] < len && pos0 + pp[c] < d.score_stride) srow[pp[c]] = t[c] * 0.6931471805599453f;
-        }
-        // ---- online softmax (log2 domain) ----
-        float mx = fmaxf(fmaxf(t[0], t[1]), fmaxf(t[2], t[3]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = exp2f(m_run - m_use);
-        float p[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) p[c] = exp2f(t[c] - m_use);
-        l_run = l_run * alpha + ((p[0] + p[1]) + (p[2] + p[3]));
-        m_run = m_new;
-        const uint32_t pb0 = pack_h2(p[0], p[1]), pb1 = pack_h2(p[2], p[3]);
-        // rescale O: this thread's columns are query heads 2j and 2j+1
-        const float al0 = __shfl_sync(0xffffffffu, alpha, (2 * j) * 4);
-        const float al1 = __shfl_sync(0xffffffffu, alpha, (2 * j + 1) * 4);
-#pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            o[m][0] *= al0; o[m][1] *= al1; o[m][2] *= al0; o[m][3] *= al1;
-        }
-        // ---- O^T += (Vcode * vscale)^T . P^T ----
-        const unsigned char* vbase = st + DA4_PAGE_BYTES;
-        // channels 16r .. 16r+15 of this thread's four positions: one 8-byte unit each
-        uint2 v0 = *reinterpret_cast<const uint2*>(vbase + pp[0] * 64 + 8 * (r ^ (pp[0] & 4)));
-        uint2 v1 = *reinterpret_cast<const uint2*>(vbase + pp[1] * 64 + 8 * (r ^ (pp[1] & 4)));
-        uint2 v2 = *reinterpret_cast<const uint2*>(vbase + pp[2] * 64 + 8 * (r ^ (pp[2] & 4)));
-        uint2 v3 = *reinterpret_cast<const uint2*>(vbase + pp[3] * 64 + 8 * (r ^ (pp[3] & 4)));
-        const uint32_t vw[4][2] = {{v0.x, v0.y}, {v1.x, v1.y}, {v2.x, v2.y}, {v3.x, v3.y}};
-        uint32_t vlo[4][2], vhi[4][2];
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int wq = 0; wq < 2; ++wq) {
-                vlo[c][wq] = vw[c][wq] & 0x0f0f0f0fu;            // even channels
-                vhi[c][wq] = (vw[c][wq] >> 4) & 0x0f0f0f0fu;     // odd channels
-            }
-        float vs0, vs1, vs2, vs3;
-        bf16x2_to_f32(vsc[j], vs0, vs1);
-        bf16x2_to_f32(vsc[4 + j], vs2, vs3);
-        const uint32_t vsa = pack_h2(vs0, vs1), vsb = pack_h2(vs2, vs3);
-        // the zero-point term, with the probabilities as the tensor cores see them (rounded to f16)
-        {
-            const __half2 pa = *reinterpret_cast<const __half2*>(&pb0), pbh = *reinterpret_cast<const __half2*>(&pb1);
-            const __half2 sa = *reinterpret_cast<const __half2*>(&vsa), sb = *reinterpret_cast<const __half2*>(&vsb);
-            const float c_page = __low2float(pa) * __low2float(sa) * vzp[pp[0]] + __high2float(pa) * __high2float(sa) * vzp[pp[1]] +
-                                 __low2float(pbh) * __low2float(sb) * vzp[pp[2]] + __high2float(pbh) * __high2float(sb) * vzp[pp[3]];
-            corr = corr * alpha + c_page;
-        }
-#pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            // byte m of the unit holds channels 16r+2m (low nibble) and 16r+2m+1 (high nibble)
-            const int wq = m >> 2;
-            const uint32_t sel = (m & 2) ? ((m & 1) ? 0x7373u : 0x6262u) : ((m & 1) ? 0x5151u : 0x4040u);
-            const uint32_t ea = __byte_perm(vlo[0][wq], vlo[1][wq], sel);   // (p0, p1, p0, p1) of the even channel
-            const uint32_t oa = __byte_perm(vhi[0][wq], vhi[1][wq], sel);
-            const uint32_t eb = __byte_perm(vlo[2][wq], vlo[3][wq], sel);
-            const uint32_t ob = __byte_perm(vhi[2][wq], vhi[3][wq], sel);
-            const uint32_t a0 = hmul2_u32(nibs_to_h2<0x4140>(ea), vsa);   // channel 16r+2m,   positions 2j, 2j+1
-            const uint32_t a1 = hmul2_u32(nibs_to_h2<0x4140>(oa), vsa);   // channel 16r+2m+1
-            const uint32_t a2 = hmul2_u32(nibs_to_h2<0x4140>(eb), vsb);   // channel 16r+2m,   positions 8+2j, 9+2j
-            const uint32_t a3 = hmul2_u32(nibs_to_h2<0x4140>(ob), vsb);
-            mma_f16(o[m], a0, a1, a2, a3, pb0, pb1);
-        }
-        __syncwarp();
-        if (lane == 0 && i + DA4_STAGES < my_pages) issue(i + DA4_STAGES);
-    }
-    if (timed_out) {
-        // give the copies already issued one more bounded chance to land before the ring is reused
-        if (lane == 0 && d.status) atomicOr(d.status, PIKV_ST_WAIT_TIMEOUT);
-        for (int ii = i; ii < min(my_pages, i + DA4_STAGES); ++ii)
-            (void)mbar_wait(bar0 + 8 * (ii % DA4_STAGES), (uint32_t)(ii / DA4_STAGES) & 1u);
-    }
-
-    // ---- zero-point term of P.V: per query head, the same for every channel ----
-    corr += __shfl_xor_sync(0xffffffffu, corr, 1);
-    corr += __shfl_xor_sync(0xffffffffu, corr, 2);
-    {
-        const float c0 = __shfl_sync(0xffffffffu, corr, (2 * j) * 4);
-        const float c1 = __shfl_sync(0xffffffffu, corr, (2 * j + 1) * 4);
-#pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            o[m][0] -= c0; o[m][1] -= c1; o[m][2] -= c0; o[m][3] -= c1;
-        }
+        o[m][0] -= corr0; o[m][1] -= corr1; o[m][2] -= corr0; o[m][3] -= corr1;
     }
     // ---- merge the 4 warps ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
     __syncthreads();   // every warp is done with its ring; reuse it as the merge buffer
     float* mo = reinterpret_cast<float*>(smem);   // [warp][q][128]
-    if (j == 0 && r < DA_MAX_GROUP) {
-        ml_s[warp][r][0] = m_run;
-        ml_s[warp][r][1] = l_run;
+    if (r == 0) {
+        ml_s[warp][2 * j][0] = m0;
+        ml_s[warp][2 * j][1] = l0;
+        ml_s[warp][2 * j + 1][0] = m1;
+        ml_s[warp][2 * j + 1][1] = l1;
     }
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
@@ -725,18 +547,18 @@ static int decode_attn_launch(const pikv_decode_params* p, pikv_stream_t stream,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     dim3 grid(d.splits, p->n_kv, p->B);
     if (bits == 8) {
-        const size_t smem = (size_t)DA_WARPS * DA_STAGES * DA_STAGE_BYTES + DA_WARPS * DA_STAGES * sizeof(uint64_t);
-        if (cudaFuncSetAttribute(decode_attn_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        const size_t smem = da_smem_bytes<8>();
+        if (cudaFuncSetAttribute(decode_attn_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("decode_attn smem attribute");
-        decode_attn_q8_kernel<<<grid, DA_THREADS, smem, st>>>(d);
+        decode_attn_kernel<8><<<grid, DA_THREADS, smem, st>>>(d);
     } else {
-        const size_t smem = (size_t)DA_WARPS * DA4_STAGES * DA4_STAGE_BYTES + DA_WARPS * DA4_STAGES * sizeof(uint64_t);
-        if (cudaFuncSetAttribute(decode_attn_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        const size_t smem = da_smem_bytes<4>();
+        if (cudaFuncSetAttribute(decode_attn_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("decode_attn smem attribute");
-        decode_attn_q4_kernel<<<grid, DA_THREADS, smem, st>>>(d);
+        decode_attn_kernel<4><<<grid, DA_THREADS, smem, st>>>(d);
     }
     int launches = 1;
-    int rc = check_launch(bits == 8 ? "decode_attn_q8_kernel" : "decode_attn_q4_kernel");
+    int rc = check_launch(bits == 8 ? "decode_attn_kernel<8>" : "decode_attn_kernel<4>");
     if (rc != PIKV_OK) return rc;
     if (d.splits > 1) {
         decode_merge_kernel<<<p->B * p->n_q, 128, 0, st>>>(d);
