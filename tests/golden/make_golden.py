@@ -31,7 +31,12 @@ def sd(module):
     return {k: npy(v).copy() for k, v in module.state_dict().items()}
 
 
+ONLY = None      # --only NAME: write just that fixture (the others are recomputed but left alone)
+
+
 def save(name, **arrays):
+    if ONLY is not None and name != ONLY:
+        return
     flat = {}
     for k, v in arrays.items():
         if isinstance(v, dict):
@@ -127,6 +132,13 @@ def router_fixtures(ref_single, ref_module, ref_strategy):
         d, c, p, aux, imp = mp(x2)
     save("router_pikv_module", x=x2, weights=w0, dispatch=d, combine=c, probs=p, aux=aux, importance=imp,
          usage=mp.expert_usage_count)
+    torch.manual_seed(8)
+    ma = ref_module.AdaptiveRouter(H2, E2, 2, importance_threshold=0.5)
+    w0 = sd(ma)
+    with torch.no_grad():
+        d, c, p, aux, imp = ma(x2)
+    save("router_adaptive_module", x=x2, weights=w0, dispatch=d, combine=c, probs=p, aux=aux, importance=imp,
+         usage=ma.expert_usage_count, history=ma.importance_history, history_idx=ma.importance_idx)
 
     # R5: routing_strategy.AdaptiveRouter (the router PiKVMoE wires up)
     torch.manual_seed(6)
@@ -334,7 +346,10 @@ def moe_fixture(reference):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default=None, help="write just this fixture")
     args = ap.parse_args()
+    global ONLY
+    ONLY = args.only
     sys.dont_write_bytecode = True
     sys.path.insert(0, args.reference)
     torch.set_num_threads(1)

@@ -241,6 +241,38 @@ def test_pikv_router_state_machine_matches_reference(dev):
     assert int(r.update_counter) == 3
 
 
+def test_module_pikv_router_matches_reference(dev):
+    """core/single/module PiKVRouter: cache-aware logit adjustment, predicted top-k, running-count slots."""
+    from pikv_b200 import module as M
+    g = load_golden("router_pikv_module")
+    r = load_sd(M.PiKVRouter(32, 4, 2), sub(g, "weights"), dev)
+    with torch.no_grad():
+        d, c, p, aux, imp = r(torch.from_numpy(g["x"]).to(dev))
+    assert rel(p.cpu().numpy(), g["probs"]) < 1e-5
+    assert rel(imp.cpu().numpy(), g["importance"]) < 1e-5
+    np.testing.assert_array_equal(d.cpu().numpy(), g["dispatch"])
+    assert rel(c.cpu().numpy(), g["combine"]) < 1e-5
+    assert abs(float(aux) - float(g["aux"])) < 1e-5
+    np.testing.assert_array_equal(r.expert_usage_count.cpu().numpy(), g["usage"])
+
+
+def test_module_adaptive_router_matches_reference(dev):
+    """core/single/module AdaptiveRouter: importance-weighted combine tensor and the importance ring."""
+    from pikv_b200 import module as M
+    g = load_golden("router_adaptive_module")
+    r = load_sd(M.AdaptiveRouter(32, 4, 2, importance_threshold=0.5), sub(g, "weights"), dev)
+    with torch.no_grad():
+        d, c, p, aux, imp = r(torch.from_numpy(g["x"]).to(dev))
+    assert rel(p.cpu().numpy(), g["probs"]) < 1e-5
+    assert rel(imp.cpu().numpy(), g["importance"]) < 1e-5
+    np.testing.assert_array_equal(d.cpu().numpy(), g["dispatch"])
+    assert rel(c.cpu().numpy(), g["combine"]) < 1e-5
+    assert abs(float(aux) - float(g["aux"])) < 1e-5
+    np.testing.assert_array_equal(r.expert_usage_count.cpu().numpy(), g["usage"])
+    assert rel(r.importance_history.cpu().numpy(), g["history"]) < 1e-5
+    assert int(r.importance_idx) == int(g["history_idx"])
+
+
 def test_module_running_slots_match_reference_dispatch(dev):
     """The kernel's slot output reproduces the dense tensors core/single/module builds."""
     from pikv_b200 import ops
