@@ -43,6 +43,78 @@ class BaseCompressor(nn.Module):
         self.compression_count.zero_()
 
 
+class PyramidCompressor(BaseCompressor):
+    """core/single/module/pikv_compression.py:106-260: per level an encoder (Linear, LayerNorm, ReLU) and a
+    decoder (Linear, LayerNorm); a token of level L runs encoders 0..L, decoders L..0 and adds the result
+    to itself.  Levels come from importance thresholds linspace(0.8, 0.2, num_levels)."""
+
+    def __init__(self, hidden_size: int, compression_ratio: float = 0.5, num_levels: int = 3, decay_factor: float = 0.8,
+                 use_adaptive_levels: bool = True):
+        super().__init__(hidden_size, compression_ratio)
+        self.num_levels = num_levels
+        self.decay_factor = decay_factor
+        self.use_adaptive_levels = use_adaptive_levels
+        self.compression_layers = nn.ModuleList()
+        size, ratio = hidden_size, compression_ratio
+        for _ in range(num_levels):
+            out = max(int(size * ratio), 1)
+            self.compression_layers.append(nn.ModuleDict({
+                "encoder": nn.Sequential(nn.Linear(size, out), nn.LayerNorm(out), nn.ReLU()),
+                "decoder": nn.Sequential(nn.Linear(out, size), nn.LayerNorm(size)),
+            }))
+            size, ratio = out, ratio * decay_factor
+        self.register_buffer("importance_thresholds", torch.linspace(0.8, 0.2, num_levels))
+        for layer in self.compression_layers:
+            for seq in layer.values():
+                for m in seq:
+                    if isinstance(m, nn.Linear):
+                        nn.init.xavier_normal_(m.weight)
+                        nn.init.zeros_(m.bias)
+
+    def _assign_compression_levels(self, importance: torch.Tensor) -> torch.Tensor:
+        """:167-184.  Level 0 marks "not assigned yet" in the reference's loop, so a token gets the first level
+        L >= 1 (below the last) whose threshold it reaches, and the last level otherwise; with one level
+        everything stays at 0."""
+        levels = torch.full_like(importance, self.num_levels - 1, dtype=torch.long)
+        for level in range(self.num_levels - 2, 0, -1):
+            levels = torch.where(importance >= self.importance_thresholds[level], torch.full_like(levels, level), levels)
+        return levels
+
+    def _chain(self, x: torch.Tensor, level: int) -> torch.Tensor:
+        y = x
+        for i in range(level + 1):
+            enc = self.compression_layers[i]["encoder"]
+            y = torch.relu(enc[1](_linear(enc[0], y, relu=False)))
+        for i in range(level, -1, -1):
+            dec = self.compression_layers[i]["decoder"]
+            y = dec[1](_linear(dec[0], y, relu=False))
+        return x + y
+
+    def _apply_pyramid_compression(self, x: torch.Tensor, levels: torch.Tensor) -> torch.Tensor:
+        out = torch.zeros_like(x)
+        for level in range(self.num_levels):
+            mask = levels == level
+            idx = mask.reshape(-1).nonzero(as_tuple=True)[0]
+            if idx.numel() == 0:
+                continue
+            flat = x.reshape(-1, x.shape[-1])
+            out.view(-1, x.shape[-1])[idx] = self._chain(flat[idx], level)
+        return out
+
+    def forward(self, keys: torch.Tensor, values: torch.Tensor, importance: Optional[torch.Tensor] = None):
+        b, s, _ = keys.shape
+        if importance is None:
+            importance = torch.full((b, s), 0.5, device=keys.device)
+        levels = self._assign_compression_levels(importance)
+        ck = self._apply_pyramid_compression(keys, levels)
+        cv = self._apply_pyramid_compression(values, levels)
+        original = keys.numel() + values.numel()
+        share = torch.bincount(levels.reshape(-1), minlength=self.num_levels).float() / levels.numel()
+        avg = sum((self.decay_factor ** lv) * float(share[lv]) for lv in range(self.num_levels))
+        self._update_stats(original, int(original * avg))
+        return ck, cv
+
+
 class QuantizedCompressor(BaseCompressor):
     """core/single/module/pikv_compression.py:918-1060."""
 

@@ -306,6 +306,15 @@ def lowrank_fixtures(ref_single_c, ref_module_c, ref_cachec):
     with torch.no_grad():
         ck, cv = cc(k, v, imp)
         nk, nv = cc(k, v)
+    torch.manual_seed(14)
+    pm = ref_module_c.PyramidCompressor(64, compression_ratio=0.5, num_levels=3)
+    impm = torch.rand(2, 10)
+    wpm = sd(pm)
+    with torch.no_grad():
+        mk, mv = pm(k, v, impm)
+        nk2, nv2 = pm(k, v)
+    save("pyramid_module", keys=k, values=v, importance=impm, weights=wpm, ck=mk, cv=mv, nk=nk2, nv=nv2,
+         levels=pm._assign_compression_levels(impm), stats=np.array([float(pm.total_compressed_size)]))
     save("cache_pyramid", keys=k, values=v, importance=imp, weights=sd(cc), ck=ck, cv=cv, nk=nk, nv=nv)
 
 

@@ -92,6 +92,22 @@ def test_pyramid_compressor_fp32_matches_reference(dev):
     assert rel(ik.cpu().numpy(), g["imp_keys"]) < 1e-5 and rel(iv.cpu().numpy(), g["imp_values"]) < 1e-5
 
 
+def test_module_pyramid_compressor_matches_reference(dev):
+    """core/single/module PyramidCompressor: LayerNorm encoders/decoders, threshold levels, residual."""
+    from pikv_b200.module import PyramidCompressor
+    g = load_golden("pyramid_module")
+    c = PyramidCompressor(64, compression_ratio=0.5, num_levels=3).to(dev)
+    c.load_state_dict(state(dev, sub(g, "weights")))
+    k, v = torch.from_numpy(g["keys"]).to(dev), torch.from_numpy(g["values"]).to(dev)
+    imp = torch.from_numpy(g["importance"]).to(dev)
+    np.testing.assert_array_equal(c._assign_compression_levels(imp).cpu().numpy(), g["levels"])
+    ck, cv = c(k, v, imp)
+    assert rel(ck.cpu().numpy(), g["ck"]) < 1e-5 and rel(cv.cpu().numpy(), g["cv"]) < 1e-5
+    nk, nv = c(k, v)
+    assert rel(nk.cpu().numpy(), g["nk"]) < 1e-5 and rel(nv.cpu().numpy(), g["nv"]) < 1e-5
+    assert float(c.total_compressed_size) == float(g["stats"][0])
+
+
 def test_svd_compressor_bf16_runs_on_tensor_cores(dev):
     """Config-4 shaped (scaled down): [tokens, 1024] bf16 -> rank 64/32/16 -> 1024, against the fp32 oracle."""
     import pikv_b200
