@@ -1,8 +1,8 @@
 // H2O scoring and eviction: score accumulate, segmented top-k select, page compaction.
 //
 // Select: one CTA per segment.  The segment's scores are staged once in shared memory as
-// order-preserving 32-bit keys; the m-th largest key is found by a 4-pass 8-bit radix
-// select; elements above it are kept, and of the elements equal to it the ones with the
+// order-preserving 32-bit keys; the m-th largest key is found by an 8-bit radix select over
+// the bits in which the segment's keys differ; elements above it are kept, and of the elements equal to it the ones with the
 // lowest indices are kept until m are taken (an in-order ballot scan).  The same routine
 // runs on the timestamps; both results are OR-ed into one keep bitmap from which the
 // evict mask and the ascending kept-index list are written.
@@ -22,14 +22,60 @@ __device__ __forceinline__ uint32_t order_key(float f) {
 struct SelShared {
     int hist[256];
     int warp_tot[SEL_WARPS];
+    uint32_t warp_or[SEL_WARPS], warp_and[SEL_WARPS];
+    int width;            // number of low key bits in which the segment's keys differ
     uint32_t prefix;      // key bits fixed so far
     int remaining;        // how many still to take among keys matching the prefix
+    int eq_total;         // size of the bin chosen by the last pass (after the last digit: keys equal to the threshold)
+    int cand_n;           // entries in the candidate list
     int total;
 };
 
+constexpr int SEL_CAND_CAP = 4096;     // candidate list (keys that matched the first digit), shared memory
+
+// One pass of the radix select finished: warp 0 finds the bin holding the rem-th largest key among the
+// keys that matched so far and narrows prefix / remaining; eq_total = size of that bin.
+__device__ __forceinline__ void select_pick_bin(SelShared& sh, uint32_t prefix, int shift, int lane) {
+    // lane handles bins [lane*8, lane*8+8); scan from the top bin down
+    int local[8], sum = 0;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        local[b] = sh.hist[lane * 8 + b];
+        sum += local[b];
+    }
+    // suffix sum over lanes: above = number of keys in bins owned by higher lanes
+    int suffix = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_down_sync(0xffffffffu, suffix, o);
+        if (lane + o < 32) suffix += v;
+    }
+    const int above = suffix - sum;
+    const int rem = sh.remaining;
+    // the target bin is the highest bin d with count(bins > d) < rem <= count(bins >= d)
+    int cum = above;
+    int found = -1, found_above = 0, found_cnt = 0;
+#pragma unroll
+    for (int b = 7; b >= 0; --b) {
+        if (found < 0 && cum < rem && rem <= cum + local[b]) {
+            found = lane * 8 + b;
+            found_above = cum;
+            found_cnt = local[b];
+        }
+        cum += local[b];
+    }
+    if (found >= 0) {
+        sh.prefix = prefix | ((uint32_t)found << shift);
+        sh.remaining = rem - found_above;
+        sh.eq_total = found_cnt;
+    }
+}
+
 // Marks in keepw (one bit per element) the m largest of src[0..n), ties to the lowest index.
+// STAGED: the keys fit in shared memory; they are read four at a time, and after the first digit only the
+// keys of the chosen bin (a short list) are looked at again.
 template <bool STAGED>
-__device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32_t* keys, uint32_t* keepw,
+__device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32_t* keys, uint32_t* cand, uint32_t* keepw,
                              SelShared& sh) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (m <= 0) return;
@@ -41,64 +87,125 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
         __syncthreads();
         return;
     }
-    if (STAGED) {
-        for (int i = tid; i < n; i += SEL_THREADS) keys[i] = order_key(src[i]);
+    const int n4 = STAGED ? n / 4 : 0;                       // whole groups of four keys
+    const uint4* keys4 = reinterpret_cast<const uint4*>(keys);
+    // stage the keys and find the bits in which they differ at all: the scores of one segment share
+    // their leading (sign / exponent) bits, and a radix digit taken from those would send most keys to one
+    // or two bins.  The digits start at the first differing bit.
+    uint32_t any = 0u, all = 0xffffffffu;
+    if (STAGED && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        const float4* src4 = reinterpret_cast<const float4*>(src);
+        for (int i = tid; i < n4; i += SEL_THREADS) {
+            const float4 f = src4[i];
+            const uint4 u = make_uint4(order_key(f.x), order_key(f.y), order_key(f.z), order_key(f.w));
+            reinterpret_cast<uint4*>(keys)[i] = u;
+            any |= u.x | u.y | u.z | u.w;
+            all &= u.x & u.y & u.z & u.w;
+        }
+        for (int i = 4 * n4 + tid; i < n; i += SEL_THREADS) {
+            const uint32_t u = order_key(src[i]);
+            keys[i] = u;
+            any |= u;
+            all &= u;
+        }
+    } else {
+        for (int i = tid; i < n; i += SEL_THREADS) {
+            const uint32_t u = order_key(src[i]);
+            if (STAGED) keys[i] = u;
+            any |= u;
+            all &= u;
+        }
     }
-    if (tid == 0) {
-        sh.prefix = 0;
-        sh.remaining = m;
+    any = __reduce_or_sync(0xffffffffu, any);
+    all = __reduce_and_sync(0xffffffffu, all);
+    if (lane == 0) {
+        sh.warp_or[warp] = any;
+        sh.warp_and[warp] = all;
     }
     __syncthreads();
-    // radix select, most significant byte first
-    for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
+    if (tid == 0) {
+        uint32_t o = 0u, a = 0xffffffffu;
+        for (int w = 0; w < SEL_WARPS; ++w) {
+            o |= sh.warp_or[w];
+            a &= sh.warp_and[w];
+        }
+        const int width = 32 - __clz(o ^ a);                 // bits [width-1 .. 0] vary; 0: all keys equal
+        sh.width = width;
+        sh.prefix = width >= 32 ? 0u : (a & (0xffffffffu << width));
+        sh.remaining = m;
+        sh.eq_total = n;
+        sh.cand_n = 0;
+    }
+    __syncthreads();
+    // radix select over the varying bits, most significant digit first, 8 bits at a time
+    bool use_list = false;
+    int pass = 0;
+    for (int top = sh.width; top > 0; ++pass) {
+        const int bits = min(8, top);
+        const int shift = top - bits;
         for (int i = tid; i < 256; i += SEL_THREADS) sh.hist[i] = 0;
         __syncthreads();
         const uint32_t prefix = sh.prefix;
-        const uint32_t himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-        for (int i = tid; i < n; i += SEL_THREADS) {
-            uint32_t u = STAGED ? keys[i] : order_key(src[i]);
-            if ((u & himask) == prefix) atomicAdd(&sh.hist[(u >> shift) & 0xff], 1);
-        }
-        __syncthreads();
-        if (warp == 0) {
-            // lane handles bins [lane*8, lane*8+8); scan from the top bin down
-            int local[8], sum = 0;
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                local[b] = sh.hist[lane * 8 + b];
-                sum += local[b];
+        const uint32_t himask = top >= 32 ? 0u : (0xffffffffu << top);
+        const uint32_t dmask = (1u << bits) - 1u;
+        if (use_list) {
+            const int cn = sh.cand_n;
+            for (int i = tid; i < cn; i += SEL_THREADS) {
+                const uint32_t u = cand[i];
+                if ((u & himask) == prefix) atomicAdd(&sh.hist[(u >> shift) & dmask], 1);
             }
-            // suffix sum over lanes: above = number of keys in bins owned by higher lanes
-            int suffix = sum;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                int v = __shfl_down_sync(0xffffffffu, suffix, o);
-                if (lane + o < 32) suffix += v;
-            }
-            const int above = suffix - sum;
-            const int rem = sh.remaining;
-            // the target bin is the highest bin d with count(bins > d) < rem <= count(bins >= d)
-            int cum = above;
-            int found = -1, found_above = 0;
-#pragma unroll
-            for (int b = 7; b >= 0; --b) {
-                if (found < 0 && cum < rem && rem <= cum + local[b]) {
-                    found = lane * 8 + b;
-                    found_above = cum;
+        } else if (STAGED) {
+            // second pass with a short chosen bin: the matching keys also go to the candidate list
+            const bool fill = pass == 1 && sh.eq_total <= SEL_CAND_CAP;
+            auto one = [&](uint32_t u) {
+                if ((u & himask) == prefix) {
+                    atomicAdd(&sh.hist[(u >> shift) & dmask], 1);
+                    if (fill) cand[atomicAdd(&sh.cand_n, 1)] = u;
                 }
-                cum += local[b];
+            };
+            for (int i = tid; i < n4; i += SEL_THREADS) {
+                const uint4 u = keys4[i];
+                one(u.x); one(u.y); one(u.z); one(u.w);
             }
-            if (found >= 0) {
-                sh.prefix = prefix | ((uint32_t)found << shift);
-                sh.remaining = rem - found_above;
+            for (int i = 4 * n4 + tid; i < n; i += SEL_THREADS) one(keys[i]);
+            use_list = fill;
+        } else {
+            for (int i = tid; i < n; i += SEL_THREADS) {
+                const uint32_t u = order_key(src[i]);
+                if ((u & himask) == prefix) atomicAdd(&sh.hist[(u >> shift) & dmask], 1);
             }
         }
         __syncthreads();
+        if (warp == 0) select_pick_bin(sh, prefix, shift, lane);
+        __syncthreads();
+        top = shift;
     }
     const uint32_t kth = sh.prefix;      // the m-th largest key
     const int need_eq = sh.remaining;    // how many keys equal to kth to keep (lowest indices)
-    // in-order count of equal keys: warp w owns the contiguous range [w*per, (w+1)*per)
+    if (STAGED && need_eq == sh.eq_total) {
+        // every key equal to the threshold is kept: one pass, four keys per thread, eight lanes per keep word
+        const int n4r = (n + 3) / 4;
+        for (int i0 = 0; i0 < n4r; i0 += SEL_THREADS) {
+            const int i = i0 + tid;
+            uint32_t nib = 0u;
+            if (i < n4) {
+                const uint4 u = keys4[i];
+                nib = (u.x >= kth ? 1u : 0u) | (u.y >= kth ? 2u : 0u) | (u.z >= kth ? 4u : 0u) | (u.w >= kth ? 8u : 0u);
+            } else if (i < n4r) {
+                for (int e = 0; e < 4; ++e)
+                    if (4 * i + e < n && keys[4 * i + e] >= kth) nib |= 1u << e;
+            }
+            uint32_t word = nib << (4 * (lane & 7));
+            word |= __shfl_xor_sync(0xffffffffu, word, 1);
+            word |= __shfl_xor_sync(0xffffffffu, word, 2);
+            word |= __shfl_xor_sync(0xffffffffu, word, 4);
+            if ((lane & 7) == 0 && word && i < n4r) keepw[i >> 3] |= word;
+        }
+        __syncthreads();
+        return;
+    }
+    // ties at the threshold of which only some are kept: in-order count of equal keys; warp w owns the
+    // contiguous range [w*per, (w+1)*per)
     const int tiles = (n + 31) / 32;
     const int tiles_per = (tiles + SEL_WARPS - 1) / SEL_WARPS;
     const int t0 = warp * tiles_per, t1 = min(tiles, t0 + tiles_per);
@@ -143,15 +250,17 @@ __global__ void __launch_bounds__(SEL_THREADS) h2o_select_kernel(const float* ac
     n = max(0, min(n, stride));
     const int words_cap = (stride + 31) / 32;
     uint32_t* keepw = reinterpret_cast<uint32_t*>(smem_raw);
-    uint32_t* keys = keepw + words_cap;
+    // keys start on a 16-byte boundary (they are read four at a time); the candidate list follows them
+    uint32_t* keys = keepw + ((words_cap + 3) & ~3);
+    uint32_t* cand = keys + (STAGED ? ((stride + 3) & ~3) : 0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int w = tid; w < words_cap; w += SEL_THREADS) keepw[w] = 0u;
     __syncthreads();
     const float* a = acc + (size_t)seg * stride;
     const float* t = ts + (size_t)seg * stride;
     if (n > 0) {
-        select_top_m<STAGED>(a, n, min(num_heavy, n), keys, keepw, sh);
-        select_top_m<STAGED>(t, n, min(num_recent, n), keys, keepw, sh);
+        select_top_m<STAGED>(a, n, min(num_heavy, n), keys, cand, keepw, sh);
+        select_top_m<STAGED>(t, n, min(num_recent, n), keys, cand, keepw, sh);
     }
     // outputs: evict mask bytes and ascending kept indices
     const int tiles = (stride + 31) / 32;
@@ -309,7 +418,7 @@ extern "C" int pikv_h2o_select(const float* acc, const float* ts, int32_t segmen
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t words = (size_t)(stride + 31) / 32 * 4;
     if (stride <= SEL_SMEM_KEYS) {
-        size_t smem = words + (size_t)stride * 4;
+        size_t smem = ((words + 15) & ~(size_t)15) + (size_t)((stride + 3) & ~3) * 4 + (size_t)SEL_CAND_CAP * 4;
         auto kern = h2o_select_kernel<true>;
         if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("h2o_select smem attribute");
