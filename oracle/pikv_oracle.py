@@ -580,6 +580,58 @@ def cache_pyramid_compression(x, importance, w1, b1, w2, b2):
 # --------------------------------------------------------------------------
 # D - expert-parallel combine
 # --------------------------------------------------------------------------
+def module_adaptive_top_k(x, importance, w0, b0, w1, b1, top_k: int) -> int:
+    """core/single/module/pikv_routing.py:345-363: k for the whole batch = 1 + argmax of a softmax MLP on
+    [mean hidden state, mean importance] (softmax is monotone, so the argmax of the logits)."""
+    feats = np.concatenate([x.reshape(-1, x.shape[-1]).mean(0), [importance.mean()]]).astype(F32)
+    h = np.maximum(feats @ w0.T + b0, 0)
+    return min(int(np.argmax(h @ w1.T + b1)) + 1, top_k)
+
+
+def module_cache_adjustment(x, hit_rates, w0, b0, w1, b1):
+    """core/single/module/pikv_routing.py:453-479: tanh MLP on [mean over the sequence, cache hit rates],
+    one row per batch element, broadcast over the sequence."""
+    b = x.shape[0]
+    inp = np.concatenate([x.mean(1), np.broadcast_to(hit_rates, (b, hit_rates.shape[0]))], axis=1).astype(F32)
+    return np.tanh(np.maximum(inp @ w0.T + b0, 0) @ w1.T + b1).astype(F32)
+
+
+def module_pyramid_levels(importance, thresholds):
+    """core/single/module/pikv_compression.py:167-184.  Level 0 doubles as "unassigned" in that loop, so a
+    token ends at the first level L >= 1 below the last whose threshold it reaches, else at the last."""
+    n = len(thresholds)
+    levels = np.full(importance.shape, n - 1, np.int64)
+    for level in range(n - 2, 0, -1):
+        levels = np.where(importance >= thresholds[level], level, levels)
+    return levels
+
+
+def layer_norm(x, g, b, eps=1e-5):
+    mu = x.mean(-1, keepdims=True)
+    var = ((x - mu) ** 2).mean(-1, keepdims=True)
+    return ((x - mu) / np.sqrt(var + eps) * g + b).astype(F32)
+
+
+def module_pyramid(x2d, levels_flat, layers):
+    """core/single/module/pikv_compression.py:186-229.  layers[i] = dict(enc_w, enc_b, enc_g, enc_beta, dec_w,
+    dec_b, dec_g, dec_beta): a token of level L runs encoders 0..L (Linear, LayerNorm, ReLU), decoders L..0
+    (Linear, LayerNorm) and adds the result to itself."""
+    out = np.zeros_like(x2d)
+    for level in range(len(layers)):
+        idx = np.nonzero(levels_flat == level)[0]
+        if idx.size == 0:
+            continue
+        y = x2d[idx]
+        for i in range(level + 1):
+            L = layers[i]
+            y = np.maximum(layer_norm(y @ L["enc_w"].T + L["enc_b"], L["enc_g"], L["enc_beta"]), 0)
+        for i in range(level, -1, -1):
+            L = layers[i]
+            y = layer_norm(y @ L["dec_w"].T + L["dec_b"], L["dec_g"], L["dec_beta"])
+        out[idx] = x2d[idx] + y
+    return out
+
+
 def expert_parallel_combine(expert_outputs, routing_probs, world_size: int):
     """sum over ranks of sum over local experts of out_e * p[..., e].
 

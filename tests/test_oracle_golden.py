@@ -108,6 +108,66 @@ def test_base_router_module_running_slots():
     assert (slot < 0).sum() == 48 - int(d.sum())
 
 
+def _module_router_tail(g, w, logits, k, importance=None, threshold=None):
+    x = g["x"]
+    tokens = x.shape[0] * x.shape[1]
+    probs, idx, tw = O.gate_tail(logits.reshape(-1, 4), k, renorm_eps=1e-8)
+    close(probs, g["probs"].reshape(-1, 4))
+    cap = O.capacity(tokens, 1.5, k, 4)
+    d, c = O.dispatch_combine_module(idx, tw, 4, cap)
+    if importance is not None:
+        c = c * (1.0 + (importance.reshape(-1) > threshold).astype(F32))[:, None, None]
+    np.testing.assert_array_equal(d, g["dispatch"].reshape(tokens, 4, cap))
+    close(c, g["combine"].reshape(tokens, 4, cap))
+    close(O.aux_loss_module(probs, idx, 4), g["aux"], 1e-5, 1e-6)
+    _, counts_k = O.slot_assign(idx, 4, cap)
+    np.testing.assert_array_equal(counts_k.sum(0), g["usage"].astype(np.int64))
+
+
+def test_module_pikv_router():
+    g = load_golden("router_pikv_module")
+    w = sub(g, "weights")
+    x = g["x"]
+    imp = sigmoid(mlp(x, w, "importance_predictor"))[..., 0]
+    close(imp, g["importance"])
+    k = O.module_adaptive_top_k(x, imp, w["top_k_predictor.0.weight"], w["top_k_predictor.0.bias"],
+                                w["top_k_predictor.2.weight"], w["top_k_predictor.2.bias"], 2)
+    adj = O.module_cache_adjustment(x, w["cache_hit_rates"], w["cache_router_adjustment.0.weight"],
+                                    w["cache_router_adjustment.0.bias"], w["cache_router_adjustment.2.weight"],
+                                    w["cache_router_adjustment.2.bias"])
+    logits = mlp(x, w, "router") + adj[:, None, :]
+    _module_router_tail(g, w, logits, k)
+
+
+def test_module_adaptive_router():
+    g = load_golden("router_adaptive_module")
+    w = sub(g, "weights")
+    x = g["x"]
+    imp = sigmoid(mlp(x, w, "importance_predictor"))[..., 0]
+    close(imp, g["importance"])
+    k = O.module_adaptive_top_k(x, imp, w["top_k_predictor.0.weight"], w["top_k_predictor.0.bias"],
+                                w["top_k_predictor.2.weight"], w["top_k_predictor.2.bias"], 2)
+    _module_router_tail(g, w, mlp(x, w, "router"), k, imp, 0.5)
+    n = imp.size
+    close(g["history"][:n], imp.reshape(-1))
+    assert int(g["history_idx"]) == n
+
+
+def test_module_pyramid():
+    g = load_golden("pyramid_module")
+    w = sub(g, "weights")
+    levels = O.module_pyramid_levels(g["importance"], w["importance_thresholds"])
+    np.testing.assert_array_equal(levels, g["levels"])
+    layers = [dict(enc_w=w[f"compression_layers.{i}.encoder.0.weight"], enc_b=w[f"compression_layers.{i}.encoder.0.bias"],
+                   enc_g=w[f"compression_layers.{i}.encoder.1.weight"], enc_beta=w[f"compression_layers.{i}.encoder.1.bias"],
+                   dec_w=w[f"compression_layers.{i}.decoder.0.weight"], dec_b=w[f"compression_layers.{i}.decoder.0.bias"],
+                   dec_g=w[f"compression_layers.{i}.decoder.1.weight"], dec_beta=w[f"compression_layers.{i}.decoder.1.bias"])
+              for i in range(3)]
+    close(O.module_pyramid(g["keys"].reshape(-1, 64), levels.reshape(-1), layers), g["ck"].reshape(-1, 64), 1e-4, 1e-5)
+    uniform = O.module_pyramid_levels(np.full((2, 10), 0.5, F32), w["importance_thresholds"])
+    close(O.module_pyramid(g["values"].reshape(-1, 64), uniform.reshape(-1), layers), g["nv"].reshape(-1, 64), 1e-4, 1e-5)
+
+
 def test_strategy_adaptive_router():
     g = load_golden("router_strategy_adaptive")
     w = sub(g, "weights")
