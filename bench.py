@@ -185,7 +185,12 @@ def gpu_arm(args):
         dist.init_process_group("nccl", device_id=dev)
     pikv_b200.lib()
 
-    cfg = WORKLOAD
+    cfg = dict(WORKLOAD)
+    app_bytes = APPEND_BYTES_PER_TOKEN
+    if args.bits == 4:
+        # config 2's second format: 4-bit asymmetric codes, bf16 scales and fp32 zero points per (token, head)
+        cfg.update(workload="route+int4-quant+append", quant="int4-asym-g128")
+        app_bytes = 2 * 1024 * 2 + 16 + 2 * 2 * 512 + 2 * 16 * (2 + 4)
     T, H, E, k = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["top_k"]
     n_kv = cfg["kv_heads"]
     kv = n_kv * cfg["head_dim"]
@@ -275,7 +280,7 @@ def gpu_arm(args):
         cap = int(tokens * cfg["capacity_factor"] * k / E)
         R = 6 if tokens <= 32768 else 3     # more sets in flight let the gates run further ahead of the appends
         sets = [synth_inputs(tokens, H, E, kv, 100 + i, device=dev) for i in range(R)]
-        caches = [pikv_b200.PagedKVCache(E, cap, n_kv, device=dev) for _ in range(R)]
+        caches = [pikv_b200.PagedKVCache(E, cap, n_kv, bits=args.bits, symmetric=(args.bits == 8), device=dev) for _ in range(R)]
         outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=cap, want_probs=True) for _ in range(R)]
 
         def gate(i):
@@ -381,15 +386,15 @@ def gpu_arm(args):
         peak, peak_src = measured_peak_gbs()
         gate_ms, fin_ms, app_ms = kernel_times(wl, steps)
         gate_gbs = GATE_BYTES_PER_TOKEN * T / (gate_ms * 1e-3) / 1e9
-        app_gbs = APPEND_BYTES_PER_TOKEN * T / (app_ms * 1e-3) / 1e9
-        step_gbs = (GATE_BYTES_PER_TOKEN + APPEND_BYTES_PER_TOKEN) * T / (ms_max / steps * 1e-3) / 1e9
+        app_gbs = app_bytes * T / (app_ms * 1e-3) / 1e9
+        step_gbs = (GATE_BYTES_PER_TOKEN + app_bytes) * T / (ms_max / steps * 1e-3) / 1e9
         dom = "gate" if gate_ms >= app_ms else "append"
         roof = {"bound": "hbm",
                 "kernel": "gate_tc_kernel" if dom == "gate" else "kv_append_quant_kernel",
                 "achieved": gate_gbs if dom == "gate" else app_gbs, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                 "frac": (gate_gbs if dom == "gate" else app_gbs) / peak, "traffic": TRAFFIC.get(dom),
                 "gate": {"ms": gate_ms, "GBps": gate_gbs, "frac": gate_gbs / peak, "bytes_per_token": GATE_BYTES_PER_TOKEN},
-                "append": {"ms": app_ms, "GBps": app_gbs, "frac": app_gbs / peak, "bytes_per_token": APPEND_BYTES_PER_TOKEN},
+                "append": {"ms": app_ms, "GBps": app_gbs, "frac": app_gbs / peak, "bytes_per_token": app_bytes},
                 "finalize": {"ms": fin_ms},
                 "step": {"GBps": step_gbs, "frac": step_gbs / peak}}
 
@@ -447,8 +452,8 @@ def gpu_arm(args):
             gate8, _, app8 = kernel_times(w8, steps8)
             large = {"tokens": T8, "value": T8 * steps8 / (ms8 * 1e-3), "unit": UNIT, "ms_per_step": ms8 / steps8,
                      "gate_frac": GATE_BYTES_PER_TOKEN * T8 / (gate8 * 1e-3) / 1e9 / peak,
-                     "append_frac": APPEND_BYTES_PER_TOKEN * T8 / (app8 * 1e-3) / 1e9 / peak,
-                     "step_frac": (GATE_BYTES_PER_TOKEN + APPEND_BYTES_PER_TOKEN) * T8 / (ms8 / steps8 * 1e-3) / 1e9 / peak}
+                     "append_frac": app_bytes * T8 / (app8 * 1e-3) / 1e9 / peak,
+                     "step_frac": (GATE_BYTES_PER_TOKEN + app_bytes) * T8 / (ms8 / steps8 * 1e-3) / 1e9 / peak}
             del w8, g8
     clocks = sampler.stop() if rank == 0 else None
 
@@ -461,7 +466,7 @@ def gpu_arm(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 in, fp32 math, int8 codes", "data": "synthetic",
+            "dtype": f"bf16 in, fp32 math, int{args.bits} codes", "data": "synthetic",
             "config": {**cfg, **extra_cfg, "l2": f"inputs larger than L2, rotated over {R} buffer sets"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "launch": launch_mode, "roofline": roof,
             "cpu_baseline": cpu, "large_batch": large,
@@ -573,7 +578,7 @@ def main():
     ap.add_argument("--streams", type=int, default=64)
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--bits", type=int, default=8, choices=[4, 8], help="decode workload: cache code width")
+    ap.add_argument("--bits", type=int, default=8, choices=[4, 8], help="cache code width: 8 = int8 symmetric, 4 = 4-bit asymmetric (append and decode workloads)")
     ap.add_argument("--rows", type=int, default=262144)
     ap.add_argument("--shard-mode", default="peer", choices=["peer", "a2a"],
                     help="multi-GPU: peer = append kernel stores into the owner's pages over NVLink; a2a = pack + NCCL all_to_all")

@@ -2,14 +2,11 @@
 //
 // A group of 128 channels is held by 8 lanes, 16 channels each.  Codes are bit-identical to
 // QuantizedCompressor._quantize_tensor (core/single/module/pikv_compression.py:965-1006) on the
-// [1,128] slice, but without a division per element:
-//   t = fma(x, 1/scale, zp + 1.5*2^23)   rounds x/scale + zp to the nearest integer (ties to even)
-//                                        in the add itself; the integer sits in t's low mantissa bits
-//   e = fma(x, 1/scale, zp - r)          residual against that integer r
-// |e| well below 0.5 proves that the reference's own rounding sequence
-// rint(fl(fl(x/scale) + zp)) lands on the same integer (all quantities differ by < 1e-3 while
-// |x/scale| < 4096); any element closer than that to a tie, or a group outside that range, makes
-// the thread redo its 16 elements with the IEEE division sequence.
+// [1,128] slice, i.e. to rint(fl(fl(x / scale) + zp)), but without a division per element: the
+// correctly rounded quotient comes from one reciprocal per lane and two exact-remainder fma
+// refinements, and adding 1.5 * 2^23 rounds to the nearest integer (ties to even) while leaving the
+// integer in the low mantissa bits.  Groups outside the range where that is exact (denormal or huge
+// scales, the multi-million zero point of a constant group) take the IEEE division.
 #pragma once
 #include "common.cuh"
 
@@ -111,62 +108,6 @@ __device__ __forceinline__ void qg_quantize16_s8(const float (&x)[16], float mn,
     }
 }
 
-// Quantise this lane's 16 channels.  Returns the packed codes in w (4 words for 8 bits, 2 for 4).
-template <int BITS, bool SYM>
-__device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, float mx, QParams& qp, uint32_t (&w)[4]) {
-    if (BITS == 8 && SYM) {
-        qg_quantize16_s8(x, mn, mx, qp, w);
-        return;
-    }
-    constexpr int QMIN = SYM ? -(1 << (BITS - 1)) : 0;
-    constexpr int QMAX = SYM ? (1 << (BITS - 1)) - 1 : (1 << BITS) - 1;
-    qp = quant_params(mn, mx, QMIN, QMAX, SYM);
-    const float inv = __frcp_rn(qp.scale);
-    int n[16];
-    bool slow = !(fmaxf(fabsf(mn), fabsf(mx)) * inv < 4096.0f) || !(fabsf(qp.zp) < 4096.0f);
-    const float c0 = qp.zp + QG_MAGIC;               // exact: zp is an integer below 2^12 here
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float t = __fmaf_rn(x[i], inv, c0);
-        const float r = __fsub_rn(t, QG_MAGIC);
-        const float e = __fmaf_rn(x[i], inv, __fsub_rn(qp.zp, r));
-        slow = slow || !(fabsf(e) < 0.499f);
-        n[i] = __float_as_int(t) - QG_MAGIC_BITS;
-    }
-    if (slow) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) n[i] = (int)rintf(__fadd_rn(__fdiv_rn(x[i], qp.scale), qp.zp));
-    }
-    if (BITS == 8) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            w[i] = SYM ? qg_pack4_s8(n[4 * i], n[4 * i + 1], n[4 * i + 2], n[4 * i + 3])
-                       : qg_pack4_u8(n[4 * i], n[4 * i + 1], n[4 * i + 2], n[4 * i + 3]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            uint32_t v = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v |= (uint32_t)(min(max(n[8 * i + j], QMIN), QMAX) & 0xf) << (4 * j);
-            w[i] = v;
-        }
-        w[2] = w[3] = 0;
-    }
-}
-
-// ---- bf16 in, symmetric 8-bit out ------------------------------------------------------------
-// Statistics on the raw bf16 pairs: |x| is a mask, max|x| a packed bf16x2 max, and "all 128
-// channels equal" (the reference's x_max == x_min case, which moves x_max up by 1e-5) an xor/or
-// chain.
-//
-// Codes: bf16 inputs make x / scale land exactly on a .5 tie in about one element in 400 (ratios of
-// small integers), and the group's max sits on 127.5 by construction, so the code depends on how
-// the reference's fp32 division rounds: the quotient has to be the correctly rounded one.  It is
-// formed without a per-element reciprocal: y = RN(1/scale) once per lane, then
-//   q = x*y ; r = fma(-scale, q, x) ; q = fma(r, y, q) ; r = fma(-scale, q, x) ; q = fma(r, y, q)
-// (two exact-remainder refinements: the second one is correctly rounded, Markstein), and
-// q + 1.5*2^23 rounds to the nearest integer, ties to even, exactly like rint.  All six steps are
-// packed two elements per instruction (fma/mul/add.f32x2).
 typedef unsigned long long qg_f2;   // two fp32 in one 64-bit register pair
 __device__ __forceinline__ qg_f2 qg_pk(float lo, float hi) {
     qg_f2 r;
@@ -197,6 +138,91 @@ __device__ __forceinline__ qg_f2 qg_add2(qg_f2 a, qg_f2 b) {
     return d;
 }
 
+// Quantise this lane's 16 channels.  Returns the packed codes in w (4 words for 8 bits, 2 for 4).
+template <int BITS, bool SYM>
+__device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, float mx, QParams& qp, uint32_t (&w)[4]) {
+    if (BITS == 8 && SYM) {
+        qg_quantize16_s8(x, mn, mx, qp, w);
+        return;
+    }
+    constexpr int QMIN = SYM ? -(1 << (BITS - 1)) : 0;
+    constexpr int QMAX = SYM ? (1 << (BITS - 1)) - 1 : (1 << BITS) - 1;
+    qp = quant_params(mn, mx, QMIN, QMAX, SYM);
+    // rint(fl(fl(x / scale) + zp)), the reference's sequence, without a division per element: the correctly
+    // rounded quotient from y = RN(1 / scale) and two exact-remainder refinements (see the 8-bit symmetric
+    // routine below), the fp32 add of zp, and 1.5 * 2^23 added to round to the nearest integer, ties to
+    // even; two elements per instruction.  Outside the range where the remainders are exact and the sum
+    // fits the trick (tiny / huge scales, the multi-million zero point of a constant group) every
+    // element takes the IEEE division.
+    const float amax = fmaxf(fabsf(mn), fabsf(mx));
+    const bool fast = qp.scale > 1.0e-30f && qp.scale < 1.0e30f && amax < 1.0e30f && fabsf(qp.zp) < 1048576.0f &&
+                      amax < 1048576.0f * qp.scale;
+    int n[16];
+    if (fast) {
+        const float y = __frcp_rn(qp.scale);
+        const qg_f2 y2 = qg_pk(y, y), ns2 = qg_pk(-qp.scale, -qp.scale), magic2 = qg_pk(QG_MAGIC, QG_MAGIC);
+        const qg_f2 zp2 = qg_pk(qp.zp, qp.zp);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const qg_f2 x2 = qg_pk(x[2 * i], x[2 * i + 1]);
+            qg_f2 q = qg_mul2(x2, y2);
+            qg_f2 r = qg_fma2(ns2, q, x2);
+            q = qg_fma2(r, y2, q);
+            r = qg_fma2(ns2, q, x2);
+            q = qg_fma2(r, y2, q);                       // RN(x / scale)
+            q = qg_add2(q, zp2);                         // RN(. + zp)
+            q = qg_add2(q, magic2);                      // rint, integer in the low mantissa bits
+            uint32_t lo, hi;
+            qg_unpku(q, lo, hi);
+            n[2 * i] = (int)lo - QG_MAGIC_BITS;
+            n[2 * i + 1] = (int)hi - QG_MAGIC_BITS;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) n[i] = (int)rintf(__fadd_rn(__fdiv_rn(x[i], qp.scale), qp.zp));
+    }
+    if (BITS == 8) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            w[i] = SYM ? qg_pack4_s8(n[4 * i], n[4 * i + 1], n[4 * i + 2], n[4 * i + 3])
+                       : qg_pack4_u8(n[4 * i], n[4 * i + 1], n[4 * i + 2], n[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!SYM) {
+                // codes 0..15: four per word by the saturating byte pack, then neighbouring bytes merged
+                // into nibbles (low nibble = even channel) and the four merged bytes gathered
+                int c[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) c[j] = min(max(n[8 * i + j], 0), 15);
+                uint32_t a = qg_pack4_u8(c[0], c[1], c[2], c[3]), b = qg_pack4_u8(c[4], c[5], c[6], c[7]);
+                a |= a >> 4;
+                b |= b >> 4;
+                w[i] = __byte_perm(a, b, 0x6420);
+            } else {
+                uint32_t v = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v |= (uint32_t)(min(max(n[8 * i + j], QMIN), QMAX) & 0xf) << (4 * j);
+                w[i] = v;
+            }
+        }
+        w[2] = w[3] = 0;
+    }
+}
+
+// ---- bf16 in, symmetric 8-bit out ------------------------------------------------------------
+// Statistics on the raw bf16 pairs: |x| is a mask, max|x| a packed bf16x2 max, and "all 128
+// channels equal" (the reference's x_max == x_min case, which moves x_max up by 1e-5) an xor/or
+// chain.
+//
+// Codes: bf16 inputs make x / scale land exactly on a .5 tie in about one element in 400 (ratios of
+// small integers), and the group's max sits on 127.5 by construction, so the code depends on how
+// the reference's fp32 division rounds: the quotient has to be the correctly rounded one.  It is
+// formed without a per-element reciprocal: y = RN(1/scale) once per lane, then
+//   q = x*y ; r = fma(-scale, q, x) ; q = fma(r, y, q) ; r = fma(-scale, q, x) ; q = fma(r, y, q)
+// (two exact-remainder refinements: the second one is correctly rounded, Markstein), and
+// q + 1.5*2^23 rounds to the nearest integer, ties to even, exactly like rint.  All six steps are
+// packed two elements per instruction (fma/mul/add.f32x2).
 // the reference's own sequence, one IEEE division per element; kept out of line because it is rare
 static __device__ __noinline__ uint4 qg_exact_s8_bf16(uint4 a, uint4 b, float scale) {
     const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};

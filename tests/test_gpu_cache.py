@@ -505,3 +505,23 @@ def test_fused_route_append_equals_gate_then_append(dev, T, H, E, k, n_kv, cap):
     for name in ("k_codes", "v_codes", "k_scale", "v_scale"):
         assert torch.equal(getattr(one, name), getattr(two, name)), name
 
+
+
+def test_cache_checkpoint_round_trip(dev):
+    """The cache's state (pages, scales, page table, lengths) travels through state_dict / torch.save and
+    decodes to the same bits afterwards (the reference checkpoints only a mean vector per expert,
+    core/single/pikv_moe.py:456-505)."""
+    import io
+    import pikv_b200
+    B, n_q, n_kv, ctx = 3, 8, 2, 300
+    lens = np.array([300, 17, 160], np.int32)
+    cache, _, _ = fill_stream_cache(dev, B, n_kv, ctx, lens, 21)
+    q = torch.randn(B, n_q, 128, device=dev).bfloat16()
+    want = cache.decode_attention(q, splits=2)
+    buf = io.BytesIO()
+    torch.save(cache.state_dict(), buf)
+    buf.seek(0)
+    fresh = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)
+    fresh.load_state_dict(torch.load(buf, map_location=dev))
+    assert torch.equal(fresh.page_table, cache.page_table) and torch.equal(fresh.length, cache.length)
+    assert torch.equal(fresh.decode_attention(q, splits=2), want)
