@@ -205,6 +205,10 @@ typedef struct {
     int32_t world, seqs_per_rank, capacity;
     const int32_t* slot_base;
     void* peer_k_codes[8]; void* peer_v_codes[8]; void* peer_k_scale[8]; void* peer_v_scale[8];
+    int32_t rank;              /* this GPU's rank (used when which != 0)                 */
+    int32_t which;             /* 0: every destination; 1: only sequences this rank owns;
+                                  2: only the other ranks' (two launches on two streams keep
+                                  the NVLink-bound stores from holding back the local ones) */
 } pikv_append_sharded_params;
 
 int pikv_kv_append_sharded(const pikv_append_sharded_params* p, pikv_stream_t stream);

@@ -51,6 +51,7 @@ class AppendShardedParams(C.Structure):
     _fields_ = [
         ("base", AppendParams), ("world", i32), ("seqs_per_rank", i32), ("capacity", i32), ("slot_base", vp),
         ("peer_k_codes", vp * 8), ("peer_v_codes", vp * 8), ("peer_k_scale", vp * 8), ("peer_v_scale", vp * 8),
+        ("rank", i32), ("which", i32),
     ]
 
 

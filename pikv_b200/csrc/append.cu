@@ -29,6 +29,7 @@ struct AppendDev {
     unsigned* status;
     // expert-sharded variant: destination pools live on the rank that owns the sequence
     int world, per, capacity;
+    int rank, which;             // which: 0 every destination, 1 only this rank's sequences, 2 only the other ranks'
     const int* slot_base;        // [num_seqs] added to the slot
     uint8_t* pcodes[2][8];       // [K|V][rank] peer-mapped code pools
     uint16_t* pscale[2][8];
@@ -105,6 +106,8 @@ __device__ __forceinline__ void append_stage_page(const AppendDev& a, unsigned p
         if (MODE == 1 && r.s[j] >= 0 && r.q[j] >= 0 && r.q[j] < a.num_seqs) {
             const int sf = r.s[j] + __ldg(a.slot_base + r.q[j]);
             r.s[j] = (a.capacity > 0 && sf >= a.capacity) ? -1 : sf;
+            const bool mine = r.q[j] / a.per == a.rank;
+            if ((a.which == 1 && !mine) || (a.which == 2 && mine)) r.s[j] = -1;
         }
         if (MODE == 2 && r.s[j] >= 0 && r.q[j] >= 0 && r.q[j] < a.gE) {
             const int sf = r.s[j] + base_s[(t / (unsigned)a.gchunk) * a.gE + r.q[j]];
@@ -386,7 +389,7 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
     a.zp[0] = static_cast<float*>(p->k_zp); a.zp[1] = static_cast<float*>(p->v_zp);
     a.status = p->status;
-    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr;
+    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr; a.rank = 0; a.which = 0;
     for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
     append_clear_gate(a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -449,7 +452,7 @@ extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_p
     a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
     a.zp[0] = a.zp[1] = nullptr;
     a.status = p->status;
-    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr;
+    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr; a.rank = 0; a.which = 0;
     for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
     a.g_cta_cnt = g.cta_cnt; a.g_cta_cnt_k = g.cta_cnt_k; a.g_cta_psum = g.cta_psum; a.g_slot_base = g.slot_base;
     a.gG = g.G; a.gchunk = g.chunk; a.gE = g.E; a.gcap = g.capacity;
@@ -598,6 +601,9 @@ extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv
     a.codes[0] = a.codes[1] = nullptr; a.scale[0] = a.scale[1] = nullptr; a.zp[0] = a.zp[1] = nullptr;
     a.status = p->status;
     a.world = sp->world; a.per = sp->seqs_per_rank; a.capacity = sp->capacity; a.slot_base = sp->slot_base;
+    PIKV_REQUIRE(sp->which >= 0 && sp->which <= 2 && (sp->which == 0 || (sp->rank >= 0 && sp->rank < sp->world)), PIKV_EINVAL,
+                 "append_sharded: which must be 0..2 (and rank valid when it is not 0)");
+    a.rank = sp->rank; a.which = sp->which;
     for (int r = 0; r < 8; ++r) {
         const bool on = r < sp->world;
         PIKV_REQUIRE(!on || (sp->peer_k_codes[r] && sp->peer_v_codes[r] && sp->peer_k_scale[r] && sp->peer_v_scale[r]),

@@ -10,7 +10,8 @@
 
 namespace pikv {
 
-constexpr int SEL_THREADS = 1024;
+constexpr int SEL_THREADS = 1024;          // keys staged in shared memory: one CTA per SM
+constexpr int SEL_THREADS_STREAM = 512;    // keys re-read from memory: small CTAs, several per SM
 constexpr int SEL_WARPS = SEL_THREADS / 32;
 constexpr int SEL_SMEM_KEYS = 49152;   // keys staged in shared memory up to this length
 
@@ -72,49 +73,50 @@ __device__ __forceinline__ void select_pick_bin(SelShared& sh, uint32_t prefix, 
 }
 
 // Marks in keepw (one bit per element) the m largest of src[0..n), ties to the lowest index.
-// STAGED: the keys fit in shared memory; they are read four at a time, and after the first digit only the
-// keys of the chosen bin (a short list) are looked at again.
-template <bool STAGED>
+// STAGED: the keys are copied to shared memory once and read from there; otherwise every scan reads the
+// scores again (from L2 after the first one), which needs almost no shared memory and lets two CTAs share
+// an SM.  Either way four keys are read at a time, and after the first digit only the keys of the chosen
+// bin (a short list in shared memory) are looked at again.
+template <bool STAGED, int NT>
 __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32_t* keys, uint32_t* cand, uint32_t* keepw,
                              SelShared& sh) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (m <= 0) return;
     if (m >= n) {
-        for (int w = tid; w < (n + 31) / 32; w += SEL_THREADS) {
+        for (int w = tid; w < (n + 31) / 32; w += NT) {
             int rem = n - w * 32;
             keepw[w] |= rem >= 32 ? 0xffffffffu : ((1u << rem) - 1u);
         }
         __syncthreads();
         return;
     }
-    const int n4 = STAGED ? n / 4 : 0;                       // whole groups of four keys
+    const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+    const float4* src4 = reinterpret_cast<const float4*>(src);
     const uint4* keys4 = reinterpret_cast<const uint4*>(keys);
-    // stage the keys and find the bits in which they differ at all: the scores of one segment share
-    // their leading (sign / exponent) bits, and a radix digit taken from those would send most keys to one
-    // or two bins.  The digits start at the first differing bit.
+    const int n4 = (STAGED || aligned) ? n / 4 : 0;          // whole groups of four keys
+    auto global4 = [&](int i) {
+        const float4 f = __ldg(src4 + i);
+        return make_uint4(order_key(f.x), order_key(f.y), order_key(f.z), order_key(f.w));
+    };
+    auto key4 = [&](int i) { return STAGED ? keys4[i] : global4(i); };
+    auto key1 = [&](int i) { return STAGED ? keys[i] : order_key(__ldg(src + i)); };
+    // first scan: find the bits in which the keys differ at all (and stage them).  The scores of one segment
+    // share their leading (sign / exponent) bits, and a radix digit taken from those would send most keys to
+    // one or two bins.  The digits start at the first differing bit.
     uint32_t any = 0u, all = 0xffffffffu;
-    if (STAGED && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-        const float4* src4 = reinterpret_cast<const float4*>(src);
-        for (int i = tid; i < n4; i += SEL_THREADS) {
-            const float4 f = src4[i];
-            const uint4 u = make_uint4(order_key(f.x), order_key(f.y), order_key(f.z), order_key(f.w));
-            reinterpret_cast<uint4*>(keys)[i] = u;
+    if (aligned) {
+        for (int i = tid; i < n / 4; i += NT) {
+            const uint4 u = global4(i);
+            if (STAGED) reinterpret_cast<uint4*>(keys)[i] = u;
             any |= u.x | u.y | u.z | u.w;
             all &= u.x & u.y & u.z & u.w;
         }
-        for (int i = 4 * n4 + tid; i < n; i += SEL_THREADS) {
-            const uint32_t u = order_key(src[i]);
-            keys[i] = u;
-            any |= u;
-            all &= u;
-        }
-    } else {
-        for (int i = tid; i < n; i += SEL_THREADS) {
-            const uint32_t u = order_key(src[i]);
-            if (STAGED) keys[i] = u;
-            any |= u;
-            all &= u;
-        }
+    }
+    for (int i = (aligned ? 4 * (n / 4) : 0) + tid; i < n; i += NT) {
+        const uint32_t u = order_key(src[i]);
+        if (STAGED) keys[i] = u;
+        any |= u;
+        all &= u;
     }
     any = __reduce_or_sync(0xffffffffu, any);
     all = __reduce_and_sync(0xffffffffu, all);
@@ -125,7 +127,7 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
     __syncthreads();
     if (tid == 0) {
         uint32_t o = 0u, a = 0xffffffffu;
-        for (int w = 0; w < SEL_WARPS; ++w) {
+        for (int w = 0; w < (NT / 32); ++w) {
             o |= sh.warp_or[w];
             a &= sh.warp_and[w];
         }
@@ -143,18 +145,18 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
     for (int top = sh.width; top > 0; ++pass) {
         const int bits = min(8, top);
         const int shift = top - bits;
-        for (int i = tid; i < 256; i += SEL_THREADS) sh.hist[i] = 0;
+        for (int i = tid; i < 256; i += NT) sh.hist[i] = 0;
         __syncthreads();
         const uint32_t prefix = sh.prefix;
         const uint32_t himask = top >= 32 ? 0u : (0xffffffffu << top);
         const uint32_t dmask = (1u << bits) - 1u;
         if (use_list) {
             const int cn = sh.cand_n;
-            for (int i = tid; i < cn; i += SEL_THREADS) {
+            for (int i = tid; i < cn; i += NT) {
                 const uint32_t u = cand[i];
                 if ((u & himask) == prefix) atomicAdd(&sh.hist[(u >> shift) & dmask], 1);
             }
-        } else if (STAGED) {
+        } else {
             // second pass with a short chosen bin: the matching keys also go to the candidate list
             const bool fill = pass == 1 && sh.eq_total <= SEL_CAND_CAP;
             auto one = [&](uint32_t u) {
@@ -163,17 +165,12 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
                     if (fill) cand[atomicAdd(&sh.cand_n, 1)] = u;
                 }
             };
-            for (int i = tid; i < n4; i += SEL_THREADS) {
-                const uint4 u = keys4[i];
+            for (int i = tid; i < n4; i += NT) {
+                const uint4 u = key4(i);
                 one(u.x); one(u.y); one(u.z); one(u.w);
             }
-            for (int i = 4 * n4 + tid; i < n; i += SEL_THREADS) one(keys[i]);
+            for (int i = 4 * n4 + tid; i < n; i += NT) one(key1(i));
             use_list = fill;
-        } else {
-            for (int i = tid; i < n; i += SEL_THREADS) {
-                const uint32_t u = order_key(src[i]);
-                if ((u & himask) == prefix) atomicAdd(&sh.hist[(u >> shift) & dmask], 1);
-            }
         }
         __syncthreads();
         if (warp == 0) select_pick_bin(sh, prefix, shift, lane);
@@ -182,18 +179,18 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
     }
     const uint32_t kth = sh.prefix;      // the m-th largest key
     const int need_eq = sh.remaining;    // how many keys equal to kth to keep (lowest indices)
-    if (STAGED && need_eq == sh.eq_total) {
+    if (need_eq == sh.eq_total && (n4 == n / 4)) {
         // every key equal to the threshold is kept: one pass, four keys per thread, eight lanes per keep word
         const int n4r = (n + 3) / 4;
-        for (int i0 = 0; i0 < n4r; i0 += SEL_THREADS) {
+        for (int i0 = 0; i0 < n4r; i0 += NT) {
             const int i = i0 + tid;
             uint32_t nib = 0u;
             if (i < n4) {
-                const uint4 u = keys4[i];
+                const uint4 u = key4(i);
                 nib = (u.x >= kth ? 1u : 0u) | (u.y >= kth ? 2u : 0u) | (u.z >= kth ? 4u : 0u) | (u.w >= kth ? 8u : 0u);
             } else if (i < n4r) {
                 for (int e = 0; e < 4; ++e)
-                    if (4 * i + e < n && keys[4 * i + e] >= kth) nib |= 1u << e;
+                    if (4 * i + e < n && key1(4 * i + e) >= kth) nib |= 1u << e;
             }
             uint32_t word = nib << (4 * (lane & 7));
             word |= __shfl_xor_sync(0xffffffffu, word, 1);
@@ -207,14 +204,14 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
     // ties at the threshold of which only some are kept: in-order count of equal keys; warp w owns the
     // contiguous range [w*per, (w+1)*per)
     const int tiles = (n + 31) / 32;
-    const int tiles_per = (tiles + SEL_WARPS - 1) / SEL_WARPS;
+    const int tiles_per = (tiles + (NT / 32) - 1) / (NT / 32);
     const int t0 = warp * tiles_per, t1 = min(tiles, t0 + tiles_per);
     int eq_cnt = 0;
     for (int t = t0; t < t1; ++t) {
         const int i = t * 32 + lane;
         uint32_t u = 0;
         bool in = i < n;
-        if (in) u = STAGED ? keys[i] : order_key(src[i]);
+        if (in) u = key1(i);
         eq_cnt += __popc(__ballot_sync(0xffffffffu, in && u == kth));
     }
     if (lane == 0) sh.warp_tot[warp] = eq_cnt;
@@ -225,7 +222,7 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
         const int i = t * 32 + lane;
         uint32_t u = 0;
         bool in = i < n;
-        if (in) u = STAGED ? keys[i] : order_key(src[i]);
+        if (in) u = key1(i);
         const bool gt = in && u > kth;
         const bool eq = in && u == kth;
         const unsigned eqb = __ballot_sync(0xffffffffu, eq);
@@ -238,8 +235,8 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
     __syncthreads();
 }
 
-template <bool STAGED>
-__global__ void __launch_bounds__(SEL_THREADS) h2o_select_kernel(const float* acc, const float* ts, int stride,
+template <bool STAGED, int NT>
+__global__ void __launch_bounds__(NT) h2o_select_kernel(const float* acc, const float* ts, int stride,
                                                                  const int* seg_len, int n_all, int num_heavy,
                                                                  int num_recent, uint8_t* evict_mask, int* keep_idx,
                                                                  int keep_stride, int* kept_count) {
@@ -252,19 +249,19 @@ __global__ void __launch_bounds__(SEL_THREADS) h2o_select_kernel(const float* ac
     uint32_t* keepw = reinterpret_cast<uint32_t*>(smem_raw);
     // keys start on a 16-byte boundary (they are read four at a time); the candidate list follows them
     uint32_t* keys = keepw + ((words_cap + 3) & ~3);
-    uint32_t* cand = keys + (STAGED ? ((stride + 3) & ~3) : 0);
+    uint32_t* cand = keys + (STAGED ? ((stride + 3) & ~3) : 0);   // unstaged: the list follows the bitmap
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int w = tid; w < words_cap; w += SEL_THREADS) keepw[w] = 0u;
+    for (int w = tid; w < words_cap; w += NT) keepw[w] = 0u;
     __syncthreads();
     const float* a = acc + (size_t)seg * stride;
     const float* t = ts + (size_t)seg * stride;
     if (n > 0) {
-        select_top_m<STAGED>(a, n, min(num_heavy, n), keys, cand, keepw, sh);
-        select_top_m<STAGED>(t, n, min(num_recent, n), keys, cand, keepw, sh);
+        select_top_m<STAGED, NT>(a, n, min(num_heavy, n), keys, cand, keepw, sh);
+        select_top_m<STAGED, NT>(t, n, min(num_recent, n), keys, cand, keepw, sh);
     }
     // outputs: evict mask bytes and ascending kept indices
     const int tiles = (stride + 31) / 32;
-    const int tiles_per = (tiles + SEL_WARPS - 1) / SEL_WARPS;
+    const int tiles_per = (tiles + (NT / 32) - 1) / (NT / 32);
     const int t0 = warp * tiles_per, t1 = min(tiles, t0 + tiles_per);
     int cnt = 0;
     for (int tt = t0; tt < t1; ++tt) cnt += __popc(keepw[tt]);
@@ -285,7 +282,7 @@ __global__ void __launch_bounds__(SEL_THREADS) h2o_select_kernel(const float* ac
     }
     if (tid == 0 && kept_count) {
         int tot = 0;
-        for (int w = 0; w < SEL_WARPS; ++w) tot += sh.warp_tot[w];
+        for (int w = 0; w < (NT / 32); ++w) tot += sh.warp_tot[w];
         kept_count[seg] = tot;
     }
 }
@@ -417,19 +414,24 @@ extern "C" int pikv_h2o_select(const float* acc, const float* ts, int32_t segmen
     PIKV_REQUIRE(keep_idx == nullptr || keep_stride > 0, PIKV_EINVAL, "h2o_select: keep_stride");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t words = (size_t)(stride + 31) / 32 * 4;
-    if (stride <= SEL_SMEM_KEYS) {
+    // keys staged in shared memory whenever the segment fits (183 us against 191 us for 512 segments of 32768
+    // with the re-reading variant, which serves longer segments); PIKV_H2O_STAGED=0 forces the latter (testing aid)
+    const char* force = getenv("PIKV_H2O_STAGED");
+    const bool staged = stride <= SEL_SMEM_KEYS && !(force && force[0] == '0');
+    if (staged) {
         size_t smem = ((words + 15) & ~(size_t)15) + (size_t)((stride + 3) & ~3) * 4 + (size_t)SEL_CAND_CAP * 4;
-        auto kern = h2o_select_kernel<true>;
+        auto kern = h2o_select_kernel<true, SEL_THREADS>;
         if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("h2o_select smem attribute");
         kern<<<segments, SEL_THREADS, smem, st>>>(acc, ts, stride, seg_len, n, num_heavy, num_recent, evict_mask,
                                                   keep_idx, keep_stride, kept_count);
     } else {
         PIKV_REQUIRE(words <= 200 * 1024, PIKV_ELIMIT, "h2o_select: stride=%d too long", stride);
-        auto kern = h2o_select_kernel<false>;
-        if (words > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)words) != cudaSuccess)
+        const size_t smem = ((words + 15) & ~(size_t)15) + (size_t)SEL_CAND_CAP * 4;
+        auto kern = h2o_select_kernel<false, SEL_THREADS_STREAM>;
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("h2o_select smem attribute");
-        kern<<<segments, SEL_THREADS, words, st>>>(acc, ts, stride, seg_len, n, num_heavy, num_recent, evict_mask,
+        kern<<<segments, SEL_THREADS_STREAM, smem, st>>>(acc, ts, stride, seg_len, n, num_heavy, num_recent, evict_mask,
                                                    keep_idx, keep_stride, kept_count);
     }
     count_launch(1);

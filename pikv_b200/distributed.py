@@ -181,7 +181,7 @@ class PeerShardedKVCache:
         self.gathered = torch.zeros(self.world, num_experts, dtype=torch.int32, device=self.device)
         self.counts = torch.zeros(num_experts, dtype=torch.int32, device=self.device)
 
-    def prepare(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None):
+    def prepare(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None, split: bool = False):
         """Bind one set of buffers to a step and return `run()`: the argument blocks are built once, so a
         call of run() is three C-ABI calls (gate, count exchange + plan, append), plus the barrier when
         asked, and no host arithmetic.  The buffers must stay alive and in place while run() is used."""
@@ -210,6 +210,15 @@ class PeerShardedKVCache:
         for r in range(self.world):
             sp.peer_k_codes[r], sp.peer_v_codes[r] = self._peer["k_codes"][r], self._peer["v_codes"][r]
             sp.peer_k_scale[r], sp.peer_v_scale[r] = self._peer["k_scale"][r], self._peer["v_scale"][r]
+        sp.rank, sp.which = self.rank, 0
+        sp_local = sp_remote = None
+        if split and self.world > 1:
+            # the rows of this rank's own sequences and the rows that cross NVLink as two launches on two
+            # streams: remote stores back up when the link is the bottleneck, and a launch that also holds
+            # local rows would stall those behind them
+            sp_local, sp_remote = type(sp).from_buffer_copy(sp), type(sp).from_buffer_copy(sp)
+            sp_local.which, sp_remote.which = 1, 2
+            side = torch.cuda.Stream(device=self.device)
         xp = L.ShardExchangeParams()
         xp.counts_k, xp.top_k, xp.E, xp.world, xp.rank, xp.capacity = ops._p(out.counts_k), top_k, E, self.world, self.rank, self.capacity
         for r in range(self.world):
@@ -222,7 +231,15 @@ class PeerShardedKVCache:
             L.check(lib.pikv_gate_fused(C.byref(gp), st), "pikv_gate_fused")
             xp.start_empty, self._start_empty = int(self._start_empty), False
             L.check(lib.pikv_shard_exchange_plan(C.byref(xp), st), "pikv_shard_exchange_plan")
-            L.check(lib.pikv_kv_append_sharded(C.byref(sp), st), "pikv_kv_append_sharded")
+            if sp_local is None:
+                L.check(lib.pikv_kv_append_sharded(C.byref(sp), st), "pikv_kv_append_sharded")
+            else:
+                cur = torch.cuda.current_stream()
+                side.wait_stream(cur)
+                with torch.cuda.stream(side):
+                    L.check(lib.pikv_kv_append_sharded(C.byref(sp_remote), ops._stream()), "pikv_kv_append_sharded")
+                L.check(lib.pikv_kv_append_sharded(C.byref(sp_local), st), "pikv_kv_append_sharded")
+                cur.wait_stream(side)
             if sync:
                 self.barrier()
             return out
