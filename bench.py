@@ -330,14 +330,15 @@ def gpu_arm(args):
         step_fn, extra_cfg = pd.make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode=args.shard_mode)
         R = extra_cfg.pop("buffer_sets", 1)
         hooks = extra_cfg.pop("hooks", None)
-        for i in range(warmup):
+        # NVLink needs sustained traffic before it runs at speed: the first multi-GPU run on an idle box
+        # measured 1.8-3.6x slower with a handful of warm-up steps.  A fixed count (every rank must run the
+        # same number of steps: the count exchange numbers them), well under a second.
+        for i in range(max(warmup, 8000)):
             step_fn(i)
-        # launched eagerly: capturing the step (NCCL all-gather + symmetric-memory barrier) in a CUDA
-        # graph hung on the 2-GPU boxes of this pool, so multi-GPU steps are not captured
-        launch_mode = "eager C-ABI calls + NCCL all-gather + peer barrier" if args.shard_mode == "peer" else \
-            "eager C-ABI calls + NCCL all_to_all"
+        launch_mode = "C-ABI calls only (gate, count exchange + plan, sharded append, scale push), two lanes" \
+            if args.shard_mode == "peer" else "eager C-ABI calls + NCCL all_to_all"
         replay = step_fn
-        per_step = None
+        per_step = extra_cfg.pop("launches_per_step", None)     # kernels inside a replayed graph
         for i in range(warmup):
             replay(i)
         sampler = ClockSampler(local)

@@ -207,11 +207,30 @@ typedef struct {
     void* peer_k_codes[8]; void* peer_v_codes[8]; void* peer_k_scale[8]; void* peer_v_scale[8];
     int32_t rank;              /* this GPU's rank (used when which != 0)                 */
     int32_t which;             /* 0: every destination; 1: only sequences this rank owns;
-                                  2: only the other ranks' (two launches on two streams keep
-                                  the NVLink-bound stores from holding back the local ones) */
+                                  2: only the other ranks'                                */
+    void* mirror_k_scale;      /* optional, both or neither: local bf16 [world][pool entries] */
+    void* mirror_v_scale;      /* buffers; the scales of rows stored on OTHER GPUs go there (at
+                                  the offset they have in the owner's pool) instead of over the
+                                  link, and pikv_shard_push_scales ships them afterwards         */
 } pikv_append_sharded_params;
 
 int pikv_kv_append_sharded(const pikv_append_sharded_params* p, pikv_stream_t stream);
+
+/* NVLink moves packets, not bytes: a 2-byte scale store costs about as much as a 128-byte row
+ * store (measured: one side store per row takes the row stores from 692 to 430 GB/s).  With scale
+ * mirrors the sharded append keeps the scales of remote rows in local memory, and this call, on the
+ * same stream after it, ships them 32 bytes (one page of one head) at a time: this rank's rows of
+ * sequence e are the slots [slot_base[e], slot_base[e] + sum_j counts_k[j][e]), cut at capacity. */
+typedef struct {
+    const int32_t* counts_k;   /* [top_k][E], this rank's gate output               */
+    const int32_t* slot_base;  /* [E], from pikv_shard_exchange_plan / pikv_shard_plan */
+    const int32_t* page_table; /* [E][max_pages], page ids local to the owner          */
+    int32_t top_k, E, world, rank, seqs_per_rank, capacity, n_kv, max_pages, num_pages;
+    const void* mirror_k_scale; const void* mirror_v_scale;
+    void* peer_k_scale[8]; void* peer_v_scale[8];
+} pikv_shard_push_params;
+
+int pikv_shard_push_scales(const pikv_shard_push_params* p, pikv_stream_t stream);
 int pikv_shard_plan(const int32_t* gathered, int32_t world, int32_t E, int32_t rank, int32_t capacity,
                     int32_t* len_all, int32_t* slot_base, pikv_stream_t stream);
 

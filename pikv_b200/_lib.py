@@ -51,7 +51,16 @@ class AppendShardedParams(C.Structure):
     _fields_ = [
         ("base", AppendParams), ("world", i32), ("seqs_per_rank", i32), ("capacity", i32), ("slot_base", vp),
         ("peer_k_codes", vp * 8), ("peer_v_codes", vp * 8), ("peer_k_scale", vp * 8), ("peer_v_scale", vp * 8),
-        ("rank", i32), ("which", i32),
+        ("rank", i32), ("which", i32), ("mirror_k_scale", vp), ("mirror_v_scale", vp),
+    ]
+
+
+class ShardPushParams(C.Structure):
+    _fields_ = [
+        ("counts_k", vp), ("slot_base", vp), ("page_table", vp),
+        ("top_k", i32), ("E", i32), ("world", i32), ("rank", i32), ("seqs_per_rank", i32), ("capacity", i32),
+        ("n_kv", i32), ("max_pages", i32), ("num_pages", i32),
+        ("mirror_k_scale", vp), ("mirror_v_scale", vp), ("peer_k_scale", vp * 8), ("peer_v_scale", vp * 8),
     ]
 
 
@@ -105,6 +114,7 @@ SIGNATURES = {
     "pikv_kv_append_sharded": (i32, [C.POINTER(AppendShardedParams), vp]),
     "pikv_shard_plan": (i32, [vp, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_shard_exchange_plan": (i32, [C.POINTER(ShardExchangeParams), vp]),
+    "pikv_shard_push_scales": (i32, [C.POINTER(ShardPushParams), vp]),
     "pikv_cache_gather": (i32, [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "pikv_quant_block_workspace_bytes": (sz, [i32, i32, i32]),
     "pikv_quant_block": (i32, [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp]),

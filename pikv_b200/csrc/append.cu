@@ -33,6 +33,8 @@ struct AppendDev {
     const int* slot_base;        // [num_seqs] added to the slot
     uint8_t* pcodes[2][8];       // [K|V][rank] peer-mapped code pools
     uint16_t* pscale[2][8];
+    uint16_t* mirror[2];         // local [world][pool] copies that take the scales of remote rows (or null)
+    size_t mirror_stride;        // entries per rank in a mirror
     // fused route + append: the gate left chunk-local ranks in `slot` and per-chunk counters behind
     const int* g_cta_cnt;        // [G][E]
     const int* g_cta_cnt_k;      // [G][k][E]
@@ -241,8 +243,15 @@ __device__ __forceinline__ void kv_append_body(const AppendDev& a) {
                     *reinterpret_cast<uint4*>(a.pcodes[0][owner] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
                     *reinterpret_cast<uint4*>(a.pcodes[1][owner] + o) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
                     if (sub == 0) {
-                        a.pscale[0][owner][prow] = ks_bits;
-                        a.pscale[1][owner][prow] = vs_bits;
+                        // a 2-byte store costs the link as much as a 128-byte one: with mirrors the scales of
+                        // remote rows stay here and shard_push_scales_kernel ships them 32 bytes at a time
+                        if (a.mirror[0] != nullptr && owner != a.rank) {
+                            a.mirror[0][(size_t)owner * a.mirror_stride + prow] = ks_bits;
+                            a.mirror[1][(size_t)owner * a.mirror_stride + prow] = vs_bits;
+                        } else {
+                            a.pscale[0][owner][prow] = ks_bits;
+                            a.pscale[1][owner][prow] = vs_bits;
+                        }
                     }
                     continue;
                 }
@@ -390,6 +399,7 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     a.zp[0] = static_cast<float*>(p->k_zp); a.zp[1] = static_cast<float*>(p->v_zp);
     a.status = p->status;
     a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr; a.rank = 0; a.which = 0;
+    a.mirror[0] = a.mirror[1] = nullptr; a.mirror_stride = 0;
     for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
     append_clear_gate(a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -453,6 +463,7 @@ extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_p
     a.zp[0] = a.zp[1] = nullptr;
     a.status = p->status;
     a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr; a.rank = 0; a.which = 0;
+    a.mirror[0] = a.mirror[1] = nullptr; a.mirror_stride = 0;
     for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
     a.g_cta_cnt = g.cta_cnt; a.g_cta_cnt_k = g.cta_cnt_k; a.g_cta_psum = g.cta_psum; a.g_slot_base = g.slot_base;
     a.gG = g.G; a.gchunk = g.chunk; a.gE = g.E; a.gcap = g.capacity;
@@ -579,6 +590,68 @@ extern "C" int pikv_shard_exchange_plan(const pikv_shard_exchange_params* p, pik
     return check_launch("shard_exchange_plan_kernel");
 }
 
+// ---- scales of the rows this rank stored on other GPUs --------------------------------------------------
+// The append left them in the local mirrors, at the offsets they have in the owner's pools.  This rank's
+// rows of sequence e occupy the slots [slot_base[e], slot_base[e] + count[e]) (cut at the capacity), i.e.
+// whole pages except at the two ends, and one (page, head) holds its 16 scales in 32 contiguous bytes: one
+// thread ships one (sequence, page, head) run, K and V, as two 16-byte stores when the page is whole and
+// entry by entry at the ends (the neighbouring entries there belong to other ranks).
+__global__ void __launch_bounds__(256) shard_push_scales_kernel(pikv_shard_push_params p) {
+    const int e = blockIdx.x;
+    const int owner = e / p.seqs_per_rank;
+    if (owner == p.rank) return;
+    int cnt = 0;
+    for (int j = 0; j < p.top_k; ++j) cnt += p.counts_k[j * p.E + e];
+    const int a = p.slot_base[e];
+    int b = a + cnt;
+    if (p.capacity > 0) b = min(b, p.capacity);
+    if (b <= a) return;
+    const int p0 = a / PT, p1 = (b - 1) / PT;
+    const size_t mirror_stride = (size_t)p.num_pages * p.n_kv * PT;
+    const uint16_t* mk = static_cast<const uint16_t*>(p.mirror_k_scale) + (size_t)owner * mirror_stride;
+    const uint16_t* mv = static_cast<const uint16_t*>(p.mirror_v_scale) + (size_t)owner * mirror_stride;
+    uint16_t* dk = static_cast<uint16_t*>(p.peer_k_scale[owner]);
+    uint16_t* dv = static_cast<uint16_t*>(p.peer_v_scale[owner]);
+    const int runs = (p1 - p0 + 1) * p.n_kv;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < runs; i += gridDim.y * blockDim.x) {
+        const int pi = p0 + i / p.n_kv, head = i % p.n_kv;
+        if (pi >= p.max_pages) continue;
+        const int page = p.page_table[(size_t)e * p.max_pages + pi];
+        if (page < 0 || page >= p.num_pages) continue;      // the append kernel has already raised PIKV_ST_BAD_PAGE
+        const int lo = max(a - pi * PT, 0), hi = min(b - pi * PT, PT);
+        const size_t off = ((size_t)page * p.n_kv + head) * PT;
+        if (lo == 0 && hi == PT) {
+            const uint4* sk = reinterpret_cast<const uint4*>(mk + off);
+            const uint4* sv = reinterpret_cast<const uint4*>(mv + off);
+            uint4* tk = reinterpret_cast<uint4*>(dk + off);
+            uint4* tv = reinterpret_cast<uint4*>(dv + off);
+            tk[0] = sk[0]; tk[1] = sk[1];
+            tv[0] = sv[0]; tv[1] = sv[1];
+        } else {
+            for (int r = lo; r < hi; ++r) {
+                dk[off + r] = mk[off + r];
+                dv[off + r] = mv[off + r];
+            }
+        }
+    }
+}
+
+extern "C" int pikv_shard_push_scales(const pikv_shard_push_params* p, pikv_stream_t stream) {
+    PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "shard_push_scales: null params");
+    PIKV_REQUIRE(p->counts_k && p->slot_base && p->page_table && p->mirror_k_scale && p->mirror_v_scale, PIKV_EINVAL,
+                 "shard_push_scales: null pointer");
+    PIKV_REQUIRE(p->world >= 1 && p->world <= 8 && p->rank >= 0 && p->rank < p->world && p->seqs_per_rank > 0 &&
+                     p->E == p->world * p->seqs_per_rank && p->top_k > 0 && p->n_kv > 0 && p->max_pages > 0 && p->num_pages > 0,
+                 PIKV_EINVAL, "shard_push_scales: bad sizes");
+    for (int r = 0; r < p->world; ++r)
+        PIKV_REQUIRE(p->peer_k_scale[r] && p->peer_v_scale[r], PIKV_EINVAL, "shard_push_scales: null pool pointer for rank %d", r);
+    if (p->world == 1) return PIKV_OK;
+    dim3 grid(p->E, 4);
+    shard_push_scales_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*p);
+    count_launch(1);
+    return check_launch("shard_push_scales_kernel");
+}
+
 extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv_stream_t stream) {
     PIKV_REQUIRE(sp != nullptr, PIKV_EINVAL, "append_sharded: null params");
     const pikv_append_params* p = &sp->base;
@@ -604,6 +677,12 @@ extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv
     PIKV_REQUIRE(sp->which >= 0 && sp->which <= 2 && (sp->which == 0 || (sp->rank >= 0 && sp->rank < sp->world)), PIKV_EINVAL,
                  "append_sharded: which must be 0..2 (and rank valid when it is not 0)");
     a.rank = sp->rank; a.which = sp->which;
+    PIKV_REQUIRE((sp->mirror_k_scale == nullptr) == (sp->mirror_v_scale == nullptr), PIKV_EINVAL,
+                 "append_sharded: give both scale mirrors or neither");
+    PIKV_REQUIRE(sp->mirror_k_scale == nullptr || (sp->rank >= 0 && sp->rank < sp->world), PIKV_EINVAL,
+                 "append_sharded: rank is required with scale mirrors");
+    a.mirror[0] = static_cast<uint16_t*>(sp->mirror_k_scale); a.mirror[1] = static_cast<uint16_t*>(sp->mirror_v_scale);
+    a.mirror_stride = (size_t)p->num_pages * p->n_kv * PT;
     for (int r = 0; r < 8; ++r) {
         const bool on = r < sp->world;
         PIKV_REQUIRE(!on || (sp->peer_k_codes[r] && sp->peer_v_codes[r] && sp->peer_k_scale[r] && sp->peer_v_scale[r]),
@@ -616,7 +695,9 @@ extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv
     append_clear_gate(a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const long long lanes = (long long)a.T * a.n_kv * 8;
-    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 3;
+    // two CTAs per SM (the link, not the SMs, bounds this launch): a gate CTA of the next step still fits beside them
+    const char* per_sm = getenv("PIKV_SHARDED_CTAS_PER_SM");
+    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * (per_sm ? atoi(per_sm) : 2);
     const int grid = (int)(want < cap_ctas ? want : cap_ctas);
     if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, 1><<<grid, APPEND_THREADS, 0, st>>>(a);
     else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, 1><<<grid, APPEND_THREADS, 0, st>>>(a);

@@ -168,6 +168,11 @@ class PeerShardedKVCache:
         self._peer_gather = [int(self._hdl.buffer_ptrs[r]) + int(offs[4]) for r in range(self.world)]
         self._peer_flags = [int(self._hdl.buffer_ptrs[r]) + int(offs[5]) for r in range(self.world)]
         self.seq = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # scales of rows stored on other GPUs wait here (same offsets as in the owner's pool) and cross the
+        # link 32 bytes at a time after the append, instead of as one 2-byte packet per row
+        entries = self.cache.k_scale.numel()
+        self.mirror_k = torch.zeros(self.world, entries, dtype=torch.bfloat16, device=self.device) if self.world > 1 else None
+        self.mirror_v = torch.zeros(self.world, entries, dtype=torch.bfloat16, device=self.device) if self.world > 1 else None
         self._start_empty = False
         for i, n in enumerate(names):
             old = getattr(self.cache, n)
@@ -183,8 +188,8 @@ class PeerShardedKVCache:
 
     def prepare(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None, split: bool = False):
         """Bind one set of buffers to a step and return `run()`: the argument blocks are built once, so a
-        call of run() is three C-ABI calls (gate, count exchange + plan, append), plus the barrier when
-        asked, and no host arithmetic.  The buffers must stay alive and in place while run() is used."""
+        call of run() is four C-ABI calls (gate, count exchange + plan, append, scale push), plus the barrier
+        when asked, and no host arithmetic.  The buffers must stay alive and in place while run() is used."""
         C, L = self._C, self._lib
         act, w2 = ops._req(act, "act", torch.bfloat16), ops._req(w2, "w2", torch.bfloat16)
         k, v = ops._req(k, "k", torch.bfloat16), ops._req(v, "v", torch.bfloat16)
@@ -211,6 +216,14 @@ class PeerShardedKVCache:
             sp.peer_k_codes[r], sp.peer_v_codes[r] = self._peer["k_codes"][r], self._peer["v_codes"][r]
             sp.peer_k_scale[r], sp.peer_v_scale[r] = self._peer["k_scale"][r], self._peer["v_scale"][r]
         sp.rank, sp.which = self.rank, 0
+        sp.mirror_k_scale, sp.mirror_v_scale = ops._p(self.mirror_k), ops._p(self.mirror_v)
+        pp = L.ShardPushParams()
+        pp.counts_k, pp.slot_base, pp.page_table = ops._p(out.counts_k), ops._p(self.slot_base), ops._p(self.global_table)
+        pp.top_k, pp.E, pp.world, pp.rank, pp.seqs_per_rank, pp.capacity = top_k, E, self.world, self.rank, self.per, self.capacity
+        pp.n_kv, pp.max_pages, pp.num_pages = self.n_kv, self.cache.max_pages, self.cache.num_pages
+        pp.mirror_k_scale, pp.mirror_v_scale = ops._p(self.mirror_k), ops._p(self.mirror_v)
+        for r in range(self.world):
+            pp.peer_k_scale[r], pp.peer_v_scale[r] = self._peer["k_scale"][r], self._peer["v_scale"][r]
         sp_local = sp_remote = None
         if split and self.world > 1:
             # the rows of this rank's own sequences and the rows that cross NVLink as two launches on two
@@ -240,6 +253,8 @@ class PeerShardedKVCache:
                     L.check(lib.pikv_kv_append_sharded(C.byref(sp_remote), ops._stream()), "pikv_kv_append_sharded")
                 L.check(lib.pikv_kv_append_sharded(C.byref(sp_local), st), "pikv_kv_append_sharded")
                 cur.wait_stream(side)
+            if self.world > 1:
+                L.check(lib.pikv_shard_push_scales(C.byref(pp), st), "pikv_shard_push_scales")
             if sync:
                 self.barrier()
             return out
@@ -277,26 +292,57 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
     n_kv = cfg["kv_heads"]
     kv = n_kv * cfg["head_dim"]
     cap = int(T * world * cfg["capacity_factor"] * k / E)
-    R = 2
+    import os
+    R = int(os.environ.get("PIKV_BENCH_LANES", "4")) if mode == "peer" else 2
     sets = [synth_inputs(T, H, E, kv, 1000 * rank + i, device=dev) for i in range(R)]
     outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(R)]
     hooks = {"begin": lambda: None, "end": lambda: None}
     if mode == "peer":
-        # two steps in flight on two streams, each with its own cache instance (own pools, own exchange
+        # several steps in flight (four by default), one stream each, each with its own cache instance (own pools, own exchange
         # ring): the gate of one step overlaps the count exchange and the NVLink stores of the previous
         # one.  Nobody reads rows between the appends, so the cross-GPU barrier runs once, at the end.
-        lanes = 2
+        import os
+        lanes = int(os.environ.get("PIKV_BENCH_LANES", "4"))
         shards = [PeerShardedKVCache(E, cap, n_kv, dev) for _ in range(lanes)]
         streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)]
-        how = "append kernel stores into the owner GPU's pages over NVLink (peer pointers); 2 steps in flight"
+        how = f"append kernel stores into the owner GPU's pages over NVLink (peer pointers); {lanes} steps in flight"
         runs = [[shards[l].prepare(sets[i][0], w2, b2, sets[i][1], sets[i][2], top_k=k, out=outs[i]) for i in range(R)]
                 for l in range(lanes)]
+
+        import os
+        graphs, launches_per_step = None, None
+        if os.environ.get("PIKV_BENCH_MULTI_EAGER", "0") != "1":
+            # a lane's step is four kernels of this library and nothing else (no collective-library call, no
+            # host read), so it is captured once per (lane, buffer set) and replayed: one launch per step.
+            # Every rank runs and captures in the same order (the count exchange numbers its steps).
+            for lane in range(lanes):
+                for i in range(R):
+                    with torch.cuda.stream(streams[lane]):
+                        shards[lane].reset()
+                        runs[lane][i](sync=False)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graphs = [[None] * R for _ in range(lanes)]
+            from . import _lib
+            n0 = _lib.launch_count()
+            for lane in range(lanes):
+                for i in range(R):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=streams[lane]):
+                        shards[lane].reset()
+                        runs[lane][i](sync=False)
+                    graphs[lane][i] = g
+            launches_per_step = (_lib.launch_count() - n0) // (lanes * R)
+            how += "; each lane's step replayed as one CUDA graph"
 
         def step(i):
             lane = i % lanes
             with torch.cuda.stream(streams[lane]):
-                shards[lane].reset()
-                runs[lane][i % R](sync=False)
+                if graphs is not None:
+                    graphs[lane][i % R].replay()
+                else:
+                    shards[lane].reset()
+                    runs[lane][i % R](sync=False)
 
         def begin():
             for st in streams:
@@ -320,4 +366,6 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
 
     extra = {"parallelism": f"tokens data-parallel, {E} experts sharded {E // world} per GPU; {how}",
              "buffer_sets": R, "hooks": hooks}
+    if mode == "peer" and launches_per_step is not None:
+        extra["launches_per_step"] = launches_per_step
     return step, extra
