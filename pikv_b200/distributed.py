@@ -263,8 +263,8 @@ class PeerShardedKVCache:
         return run
 
     def route_append(self, act, w2, b2, k, v, top_k: int = 2, out: Optional[ops.GateResult] = None,
-                     sync: bool = True) -> ops.GateResult:
-        g = self.prepare(act, w2, b2, k, v, top_k, out)(sync)
+                     sync: bool = True, split: bool = False) -> ops.GateResult:
+        g = self.prepare(act, w2, b2, k, v, top_k, out, split)(sync)
         self.sync_lengths()
         return g
 

@@ -30,10 +30,12 @@ def _worker(rank, world, port, tmp, mode="a2a"):
         w2 = (torch.randn(E, H, generator=g) / 20).bfloat16().to(dev)
         per = T // world
         sl = slice(rank * per, (rank + 1) * per)
-        shard = (PeerShardedKVCache if mode == "peer" else ExpertShardedKVCache)(E, cap, n_kv, dev)
-        shard.route_append(act[sl].to(dev), w2, None, K[sl].to(dev), V[sl].to(dev), top_k=k)
-        if mode == "peer":      # a second step on top of the first: lengths and bases carry over
-            shard.route_append(act[sl].to(dev), w2, None, K[sl].to(dev), V[sl].to(dev), top_k=k)
+        peer = mode.startswith("peer")
+        shard = (PeerShardedKVCache if peer else ExpertShardedKVCache)(E, cap, n_kv, dev)
+        extra = {"split": True} if mode == "peer_split" else {}     # local and remote rows as two launches
+        shard.route_append(act[sl].to(dev), w2, None, K[sl].to(dev), V[sl].to(dev), top_k=k, **extra)
+        if peer:                # a second step on top of the first: lengths and bases carry over
+            shard.route_append(act[sl].to(dev), w2, None, K[sl].to(dev), V[sl].to(dev), top_k=k, **extra)
         torch.cuda.synchronize()
         shard.cache.check_status()
         torch.save({n: getattr(shard.cache, n).cpu() for n in ("k_codes", "v_codes", "k_scale", "v_scale", "length")},
@@ -42,7 +44,7 @@ def _worker(rank, world, port, tmp, mode="a2a"):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["a2a", "peer"])
+@pytest.mark.parametrize("mode", ["a2a", "peer", "peer_split"])
 def test_two_gpu_cache_equals_single_gpu_cache(tmp_path, mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -60,7 +62,7 @@ def test_two_gpu_cache_equals_single_gpu_cache(tmp_path, mode):
     res = ops.gate_fused(act, w2, None, top_k=k, capacity=cap)
     single = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
     single.append(K, V, res.topk_idx, res.slot)
-    if mode == "peer":          # the same batch appended twice, as the workers did
+    if mode.startswith("peer"):  # the same batch appended twice, as the workers did
         res = ops.gate_fused(act, w2, None, top_k=k, capacity=cap, slot_base=res.new_len)
         single.append(K, V, res.topk_idx, res.slot)
     per = E // world
