@@ -211,9 +211,8 @@ __device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, fl
 }
 
 // ---- bf16 in, symmetric 8-bit out ------------------------------------------------------------
-// Statistics on the raw bf16 pairs: |x| is a mask, max|x| a packed bf16x2 max, and "all 128
-// channels equal" (the reference's x_max == x_min case, which moves x_max up by 1e-5) an xor/or
-// chain.
+// Statistics on the raw bf16 pairs: one packed max and one packed min per word give max |x| and
+// "all 128 channels equal" (the reference's x_max == x_min case, which moves x_max up by 1e-5).
 //
 // Codes: bf16 inputs make x / scale land exactly on a .5 tie in about one element in 400 (ratios of
 // small integers), and the group's max sits on 127.5 by construction, so the code depends on how
@@ -244,27 +243,26 @@ static __device__ __noinline__ uint4 qg_exact_s8_bf16(uint4 a, uint4 b, float sc
 
 __device__ __forceinline__ void qg_quantize16_s8_bf16(const uint4& a, const uint4& b, QParams& qp, uint32_t (&w)[4]) {
     const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    uint32_t m = ww[0] & 0x7fff7fffu;
-    uint32_t d = ww[0] ^ __byte_perm(ww[0], 0, 0x1032);          // low half vs high half of word 0
+    // signed max and min of the packed pairs: max |x| is the larger magnitude of the two, and the group is
+    // constant exactly when they are equal as numbers (+0 and -0 included)
+    uint32_t hi2 = ww[0], lo2 = ww[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) {
-        const uint32_t mi = ww[i] & 0x7fff7fffu;
-        asm("max.bf16x2 %0, %0, %1;" : "+r"(m) : "r"(mi));
-        d |= ww[0] ^ ww[i];
+        asm("max.bf16x2 %0, %0, %1;" : "+r"(hi2) : "r"(ww[i]));
+        asm("min.bf16x2 %0, %0, %1;" : "+r"(lo2) : "r"(ww[i]));
     }
-    uint32_t amax = max(m & 0xffffu, m >> 16);                   // bf16 bits of this lane's max |x|
-    const uint32_t first = __shfl_sync(0xffffffffu, ww[0], threadIdx.x & 24);   // word 0 of the group's lane 0
-    d |= ww[0] ^ first;
+    float gmax = fmaxf(__uint_as_float(hi2 << 16), __uint_as_float(hi2 & 0xffff0000u));
+    float gmin = fminf(__uint_as_float(lo2 << 16), __uint_as_float(lo2 & 0xffff0000u));
 #pragma unroll
     for (int o = 1; o < 8; o <<= 1) {
-        amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        d |= __shfl_xor_sync(0xffffffffu, d, o);
+        gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
+        gmin = fminf(gmin, __shfl_xor_sync(0xffffffffu, gmin, o));
     }
-    const bool all_equal = (d == 0u) || (amax == 0u);
-    float abs_max = __uint_as_float(amax << 16);
+    const bool all_equal = gmax == gmin;
+    float abs_max = fmaxf(fabsf(gmax), fabsf(gmin));
     if (all_equal) {
         // every channel holds the same value c (or +-0): x_min = c, x_max = c + 1e-5
-        const float c = (amax == 0u) ? 0.0f : __uint_as_float(first << 16);
+        const float c = gmin;
         abs_max = fmaxf(fabsf(c), fabsf(__fadd_rn(c, 1e-5f)));
     }
     qp.scale = __fdiv_rn(__fmul_rn(2.0f, abs_max), 255.0f);
