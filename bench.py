@@ -333,12 +333,12 @@ def gpu_arm(args):
         # NVLink needs sustained traffic before it runs at speed: the first multi-GPU run on an idle box
         # measured 1.8-3.6x slower with a handful of warm-up steps.  A fixed count (every rank must run the
         # same number of steps: the count exchange numbers them), well under a second.
-        for i in range(max(warmup, 8000)):
+        for i in range(max(warmup, int(os.environ.get("PIKV_BENCH_MULTI_WARMUP", "8000")))):
             step_fn(i)
-        launch_mode = "C-ABI calls only (gate, count exchange + plan, sharded append, scale push), two lanes" \
+        launch_mode = "C-ABI calls only (gate, count exchange + plan, sharded append, scale push), one CUDA graph per lane step" \
             if args.shard_mode == "peer" else "eager C-ABI calls + NCCL all_to_all"
-        replay = step_fn
         per_step = extra_cfg.pop("launches_per_step", None)     # kernels inside a replayed graph
+        replay = step_fn
         for i in range(warmup):
             replay(i)
         sampler = ClockSampler(local)
@@ -347,7 +347,15 @@ def gpu_arm(args):
         n0 = pikv_b200.launch_count()
         ms = timed(replay, steps, hooks)
         launches = per_step * steps if per_step is not None else pikv_b200.launch_count() - n0
-        e2e = extra_cfg.pop("e2e", None)
+        e2e_io = extra_cfg.pop("e2e_io", None)
+        if e2e_io is not None:
+            e2e_step, h2d, d2h = e2e_io
+            for i in range(R):
+                e2e_step(i)
+            e2e_ms = torch.tensor([timed(e2e_step, steps, hooks)], device=dev)
+            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+            e2e = {"value": T * world * steps / (float(e2e_ms.item()) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+                   "d2h_bytes_per_step": d2h * world, "ms_per_step": float(e2e_ms.item()) / steps}
     else:
         wl = single_gpu_workload(T)
         R = wl["R"]
@@ -496,7 +504,7 @@ def fill_stream_cache(pikv_b200, torch, dev, B, n_kv, ctx, seed=0, bits=8):
 
 
 def secondary_arm(args):
-    """Decode attention / H2O select / low-rank projection at BASELINE.json's sizes: one JSON line each,
+    """Decode attention / H2O select / low-rank projection at the sizes of the reference's headline configurations: one JSON line each,
     same keys as the main line (metric names differ)."""
     import torch
     import pikv_b200

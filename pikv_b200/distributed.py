@@ -293,16 +293,16 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
     kv = n_kv * cfg["head_dim"]
     cap = int(T * world * cfg["capacity_factor"] * k / E)
     import os
-    R = int(os.environ.get("PIKV_BENCH_LANES", "4")) if mode == "peer" else 2
+    R = int(os.environ.get("PIKV_BENCH_LANES", "6")) if mode == "peer" else 2
     sets = [synth_inputs(T, H, E, kv, 1000 * rank + i, device=dev) for i in range(R)]
     outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(R)]
     hooks = {"begin": lambda: None, "end": lambda: None}
     if mode == "peer":
-        # several steps in flight (four by default), one stream each, each with its own cache instance (own pools, own exchange
+        # several steps in flight (six by default), one stream each, each with its own cache instance (own pools, own exchange
         # ring): the gate of one step overlaps the count exchange and the NVLink stores of the previous
         # one.  Nobody reads rows between the appends, so the cross-GPU barrier runs once, at the end.
         import os
-        lanes = int(os.environ.get("PIKV_BENCH_LANES", "4"))
+        lanes = int(os.environ.get("PIKV_BENCH_LANES", "6"))
         shards = [PeerShardedKVCache(E, cap, n_kv, dev) for _ in range(lanes)]
         streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)]
         how = f"append kernel stores into the owner GPU's pages over NVLink (peer pointers); {lanes} steps in flight"
@@ -333,6 +333,9 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
                         runs[lane][i](sync=False)
                     graphs[lane][i] = g
             launches_per_step = (_lib.launch_count() - n0) // (lanes * R)
+            # (one graph per lane step, not one graph for several lanes: the lanes' exchange kernels wait for
+            # their peers, and the parallel branches of a single graph did not run concurrently on every
+            # rank, so such a graph ran into the bounded waits)
             how += "; each lane's step replayed as one CUDA graph"
 
         def step(i):
@@ -355,7 +358,28 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
                 torch.cuda.current_stream().wait_stream(st)
 
         hooks = {"begin": begin, "end": end}
+
+        # end to end: the step's inputs come from pinned host memory and its routing result goes back, on
+        # the lane's stream, every step
+        h_sets = [tuple(x.cpu().pin_memory() for x in sets[i]) for i in range(R)]
+        h_outs = [tuple(torch.empty_like(x, device="cpu").pin_memory()
+                        for x in (outs[i].topk_idx, outs[i].topk_w, outs[i].slot, outs[i].new_len)) for i in range(R)]
+
+        def e2e_step(i):
+            lane = i % lanes
+            with torch.cuda.stream(streams[lane]):
+                for dst, src in zip(sets[i % R], h_sets[i % R]):
+                    dst.copy_(src, non_blocking=True)
+            step(i)
+            with torch.cuda.stream(streams[lane]):
+                o = outs[i % R]
+                for dst, src in zip(h_outs[i % R], (o.topk_idx, o.topk_w, o.slot, o.new_len)):
+                    dst.copy_(src, non_blocking=True)
+
+        e2e_io = (e2e_step, sum(x.numel() * x.element_size() for x in h_sets[0]),
+                  sum(x.numel() * x.element_size() for x in h_outs[0]))
     else:
+        e2e_io = None
         shard = ExpertShardedKVCache(E, cap, n_kv, dev, max_records=int(T * k * 1.5))
         how = "pack -> NCCL all_to_all -> unpack"
 
@@ -368,4 +392,6 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
              "buffer_sets": R, "hooks": hooks}
     if mode == "peer" and launches_per_step is not None:
         extra["launches_per_step"] = launches_per_step
+    if e2e_io is not None:
+        extra["e2e_io"] = e2e_io
     return step, extra

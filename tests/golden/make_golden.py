@@ -354,7 +354,7 @@ def moe_fixture(reference):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference (NoakLiu/PiKV)")
     ap.add_argument("--only", default=None, help="write just this fixture")
     args = ap.parse_args()
     global ONLY
