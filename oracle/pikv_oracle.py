@@ -632,6 +632,37 @@ def module_pyramid(x2d, levels_flat, layers):
     return out
 
 
+def shard_slot_base(counts_all: np.ndarray, rank: int, lengths: np.ndarray, cap: int):
+    """Expert-sharded append, one step: counts_all [world, E] are every rank's selection counts.  Rows of a
+    sequence are ordered by source rank, so this rank's first row of sequence e lands at
+    lengths[e] + sum of the lower ranks' counts; the sequence grows by the total, cut at the capacity.
+    (Placement rule of core/single/cache_scheduling.py:430-436 per destination sequence, exchange of
+    core/distributed/distributed_pikv.py:174-194.)  Returns (slot_base [E], new_lengths [E])."""
+    counts_all = np.asarray(counts_all, np.int64)
+    base = np.asarray(lengths, np.int64) + counts_all[:rank].sum(0)
+    new_len = np.asarray(lengths, np.int64) + counts_all.sum(0)
+    if cap > 0:
+        new_len = np.minimum(new_len, cap)
+    return base, new_len
+
+
+def scale_push_runs(slot_base: np.ndarray, counts: np.ndarray, cap: int, owner_of, rank: int, page_tokens: int = 16):
+    """The (sequence, page, first row, end row) runs of scales this rank ships to other GPUs after a sharded
+    append: its rows of sequence e are the slots [slot_base[e], slot_base[e] + counts[e]) cut at the
+    capacity; sequences it owns itself are skipped."""
+    runs = []
+    for e in range(len(counts)):
+        if owner_of(e) == rank:
+            continue
+        a = int(slot_base[e])
+        b = a + int(counts[e])
+        if cap > 0:
+            b = min(b, cap)
+        for p in range(a // page_tokens, (b - 1) // page_tokens + 1 if b > a else 0):
+            runs.append((e, p, max(a - p * page_tokens, 0), min(b - p * page_tokens, page_tokens)))
+    return runs
+
+
 def expert_parallel_combine(expert_outputs, routing_probs, world_size: int):
     """sum over ranks of sum over local experts of out_e * p[..., e].
 

@@ -91,3 +91,72 @@ def test_plan_exchange_shapes():
     np.testing.assert_array_equal(p.seg_start, [0, 2, 6])
     np.testing.assert_array_equal(p.seg_base, [[5, 0], [5, 2]])
     np.testing.assert_array_equal(p.new_len, [8, 2])              # 5 + 4 = 9 truncated at capacity 8
+
+
+def _peer_worker(rank, world, port, T, E, k, cap, tmp):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from pikv_b200.distributed import experts_per_rank
+        from oracle import pikv_oracle as O
+        per = experts_per_rank(E, world)
+        per_rank = T // world
+        lengths = np.zeros(E, np.int64)
+        final_steps, runs_steps = [], []
+        for step in range(2):                                               # two steps: lengths carry over
+            idx = _routing(T, E, k, step)[rank * per_rank:(rank + 1) * per_rank]
+            local_slot, counts_k = O.slot_assign_fast(idx, E, 1 << 30)
+            counts = counts_k.sum(0)
+            gathered = [torch.zeros(E, dtype=torch.int64) for _ in range(world)]
+            dist.all_gather(gathered, torch.from_numpy(counts.astype(np.int64)))
+            base, lengths_new = O.shard_slot_base(torch.stack(gathered).numpy(), rank, lengths, cap)
+            final = base[idx] + local_slot
+            final[final >= cap] = -1
+            final_steps.append(final)
+            runs_steps.append(np.array(O.scale_push_runs(base, counts, cap, lambda e: e // per, rank), np.int64).reshape(-1, 4))
+            lengths = lengths_new
+        np.save(os.path.join(tmp, f"peer_final{rank}.npy"), np.stack(final_steps))
+        np.save(os.path.join(tmp, f"peer_len{rank}.npy"), lengths)
+        for i, r in enumerate(runs_steps):
+            np.save(os.path.join(tmp, f"peer_runs{rank}_{i}.npy"), r)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_exchange_slots_equal_single_process(tmp_path):
+    """The slot arithmetic of the peer-store variant (count exchange, slot base per rank, scale runs) on two
+    gloo ranks against the single-process slot assignment over the concatenated batch."""
+    from oracle import pikv_oracle as O
+    world, T, E, k, cap = 2, 600, 8, 2, 260
+    mp.spawn(_peer_worker, args=(world, 29800 + os.getpid() % 1000, T, E, k, cap, str(tmp_path)), nprocs=world, join=True)
+    lengths = np.zeros(E, np.int64)
+    per, per_rank = E // world, T // world
+    for step in range(2):
+        idx = _routing(T, E, k, step)
+        # single process: running count per expert over (token, k) order, on top of the lengths so far
+        slot = np.full((T, k), -1, np.int64)
+        run = lengths.copy()
+        for t in range(T):
+            for j in range(k):
+                e = idx[t, j]
+                slot[t, j] = run[e] if run[e] < cap else -1
+                run[e] += 1
+        got = np.concatenate([np.load(tmp_path / f"peer_final{r}.npy")[step] for r in range(world)])
+        np.testing.assert_array_equal(got, slot)
+        # scale runs: every remote (expert, slot) a rank wrote appears in exactly one of its runs, nothing else does
+        for r in range(world):
+            mine = set()
+            part = slice(r * per_rank, (r + 1) * per_rank)
+            for e, s_ in zip(idx[part].reshape(-1), slot[part].reshape(-1)):
+                if s_ >= 0 and e // per != r:
+                    mine.add((int(e), int(s_)))
+            covered = set()
+            for e, p, lo, hi in np.load(tmp_path / f"peer_runs{r}_{step}.npy"):
+                for row in range(lo, hi):
+                    assert (int(e), int(p * 16 + row)) not in covered
+                    covered.add((int(e), int(p * 16 + row)))
+            assert covered == mine
+        lengths = np.minimum(run, cap)
+    for r in range(world):
+        np.testing.assert_array_equal(np.load(tmp_path / f"peer_len{r}.npy"), lengths)
