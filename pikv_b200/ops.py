@@ -188,9 +188,11 @@ def h2o_accumulate(acc: torch.Tensor, ts: torch.Tensor, idx: Optional[torch.Tens
 
 
 def h2o_select(acc: torch.Tensor, ts: torch.Tensor, num_heavy: int, num_recent: int,
-               seg_len: Optional[torch.Tensor] = None, n: Optional[int] = None, want_idx: bool = True):
+               seg_len: Optional[torch.Tensor] = None, n: Optional[int] = None, want_idx: bool = True,
+               as_bool: bool = True):
     """acc, ts: [segments, stride] fp32.  Returns (evict_mask bool [segments,stride], keep_idx int32
-    [segments, min(stride, heavy+recent)] ascending (unused tail undefined), kept_count int32 [segments])."""
+    [segments, min(stride, heavy+recent)] ascending (unused tail undefined), kept_count int32 [segments]).
+    as_bool=False returns the kernel's uint8 mask as it is (no conversion kernel)."""
     acc = _req(acc, "acc", torch.float32)
     ts = _req(ts, "ts", torch.float32)
     if acc.dim() == 1:
@@ -206,7 +208,7 @@ def h2o_select(acc: torch.Tensor, ts: torch.Tensor, num_heavy: int, num_recent: 
         seg_len = _req(seg_len, "seg_len", torch.int32)
     check(lib().pikv_h2o_select(_p(acc), _p(ts), S, stride, _p(seg_len), n, num_heavy, num_recent, _p(mask), _p(keep),
                                 ks, _p(cnt), _stream()), "pikv_h2o_select")
-    return mask.bool(), keep, cnt
+    return (mask.bool() if as_bool else mask), keep, cnt
 
 
 def h2o_accumulate_attn(scores: torch.Tensor, lse: torch.Tensor, seq_len: Optional[torch.Tensor], n_kv: int,
