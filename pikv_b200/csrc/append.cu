@@ -348,6 +348,24 @@ static void append_clear_gate(AppendDev& a) {
     a.g_prob_sum = nullptr;
 }
 
+// the part of the launch arguments every variant shares: inputs, geometry, local pools; no sharding, no gate
+static void append_fill_common(const pikv_append_params* p, AppendDev& a) {
+    a.k = p->k; a.v = p->v; a.T = p->T; a.n_kv = p->n_kv; a.top_k = p->top_k;
+    a.log2_nkv = -1;
+    for (int b = 0; b < 16; ++b)
+        if ((1 << b) == p->n_kv) a.log2_nkv = b;
+    a.dst_seq = p->dst_seq; a.slot = p->slot; a.page_table = p->page_table;
+    a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
+    a.codes[0] = static_cast<uint8_t*>(p->k_codes); a.codes[1] = static_cast<uint8_t*>(p->v_codes);
+    a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
+    a.zp[0] = static_cast<float*>(p->k_zp); a.zp[1] = static_cast<float*>(p->v_zp);
+    a.status = p->status;
+    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr; a.rank = 0; a.which = 0;
+    a.mirror[0] = a.mirror[1] = nullptr; a.mirror_stride = 0;
+    for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
+    append_clear_gate(a);
+}
+
 template <typename TIn>
 static int launch_append(const AppendDev& a, int bits, int symmetric, cudaStream_t st) {
     const long long lanes = (long long)a.T * a.n_kv * 8;
@@ -385,23 +403,10 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     PIKV_REQUIRE(p->symmetric || (p->k_zp && p->v_zp), PIKV_EINVAL, "append: asymmetric needs zero-point pools");
     PIKV_REQUIRE(p->dtype == PIKV_BF16 || p->dtype == PIKV_F32, PIKV_EINVAL, "append: bad dtype %d", p->dtype);
     PIKV_REQUIRE(p->num_seqs > 0 && p->max_pages > 0 && p->num_pages > 0, PIKV_EINVAL, "append: bad cache geometry");
-    AppendDev a;
     PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28), PIKV_ELIMIT, "append: T * n_kv must stay below 2^28 per call");
-    a.k = p->k; a.v = p->v; a.T = p->T; a.n_kv = p->n_kv; a.top_k = p->top_k;
     PIKV_REQUIRE((long long)p->num_pages * p->n_kv * PT < (1ll << 31), PIKV_ELIMIT, "append: page pool too large for 32-bit row indices");
-    a.log2_nkv = -1;
-    for (int b = 0; b < 16; ++b)
-        if ((1 << b) == p->n_kv) a.log2_nkv = b;
-    a.dst_seq = p->dst_seq; a.slot = p->slot; a.page_table = p->page_table;
-    a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
-    a.codes[0] = static_cast<uint8_t*>(p->k_codes); a.codes[1] = static_cast<uint8_t*>(p->v_codes);
-    a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
-    a.zp[0] = static_cast<float*>(p->k_zp); a.zp[1] = static_cast<float*>(p->v_zp);
-    a.status = p->status;
-    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr; a.rank = 0; a.which = 0;
-    a.mirror[0] = a.mirror[1] = nullptr; a.mirror_stride = 0;
-    for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
-    append_clear_gate(a);
+    AppendDev a;
+    append_fill_common(p, a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (p->dtype == PIKV_BF16) return launch_append<__nv_bfloat16>(a, p->bits, p->symmetric, st);
     return launch_append<float>(a, p->bits, p->symmetric, st);
@@ -452,19 +457,8 @@ extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_p
     PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28) && (long long)p->num_pages * p->n_kv * PT < (1ll << 31), PIKV_ELIMIT,
                  "route_append: problem too large for one call");
     AppendDev a;
-    a.k = p->k; a.v = p->v; a.T = p->T; a.n_kv = p->n_kv; a.top_k = p->top_k;
-    a.log2_nkv = -1;
-    for (int b = 0; b < 16; ++b)
-        if ((1 << b) == p->n_kv) a.log2_nkv = b;
-    a.dst_seq = p->dst_seq; a.page_table = p->page_table;
-    a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
-    a.codes[0] = static_cast<uint8_t*>(p->k_codes); a.codes[1] = static_cast<uint8_t*>(p->v_codes);
-    a.scale[0] = static_cast<uint16_t*>(p->k_scale); a.scale[1] = static_cast<uint16_t*>(p->v_scale);
+    append_fill_common(p, a);
     a.zp[0] = a.zp[1] = nullptr;
-    a.status = p->status;
-    a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr; a.rank = 0; a.which = 0;
-    a.mirror[0] = a.mirror[1] = nullptr; a.mirror_stride = 0;
-    for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
     a.g_cta_cnt = g.cta_cnt; a.g_cta_cnt_k = g.cta_cnt_k; a.g_cta_psum = g.cta_psum; a.g_slot_base = g.slot_base;
     a.gG = g.G; a.gchunk = g.chunk; a.gE = g.E; a.gcap = g.capacity;
     a.slot = g.slot;               // chunk-local ranks, in the gate's workspace
@@ -665,14 +659,8 @@ extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv
                  PIKV_EINVAL, "append_sharded: world must be 1..8 and num_seqs = world * seqs_per_rank");
     PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28), PIKV_ELIMIT, "append_sharded: T * n_kv must stay below 2^28");
     AppendDev a;
-    a.k = p->k; a.v = p->v; a.T = p->T; a.n_kv = p->n_kv; a.top_k = p->top_k;
-    a.log2_nkv = -1;
-    for (int b = 0; b < 16; ++b)
-        if ((1 << b) == p->n_kv) a.log2_nkv = b;
-    a.dst_seq = p->dst_seq; a.slot = p->slot; a.page_table = p->page_table;
-    a.num_seqs = p->num_seqs; a.max_pages = p->max_pages; a.num_pages = p->num_pages;
-    a.codes[0] = a.codes[1] = nullptr; a.scale[0] = a.scale[1] = nullptr; a.zp[0] = a.zp[1] = nullptr;
-    a.status = p->status;
+    append_fill_common(p, a);
+    a.codes[0] = a.codes[1] = nullptr; a.scale[0] = a.scale[1] = nullptr; a.zp[0] = a.zp[1] = nullptr;   // peer pools only
     a.world = sp->world; a.per = sp->seqs_per_rank; a.capacity = sp->capacity; a.slot_base = sp->slot_base;
     PIKV_REQUIRE(sp->which >= 0 && sp->which <= 2 && (sp->which == 0 || (sp->rank >= 0 && sp->rank < sp->world)), PIKV_EINVAL,
                  "append_sharded: which must be 0..2 (and rank valid when it is not 0)");
@@ -692,12 +680,11 @@ extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv
         a.pscale[0][r] = on ? static_cast<uint16_t*>(sp->peer_k_scale[r]) : nullptr;
         a.pscale[1][r] = on ? static_cast<uint16_t*>(sp->peer_v_scale[r]) : nullptr;
     }
-    append_clear_gate(a);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const long long lanes = (long long)a.T * a.n_kv * 8;
-    // two CTAs per SM (the link, not the SMs, bounds this launch): a gate CTA of the next step still fits beside them
-    const char* per_sm = getenv("PIKV_SHARDED_CTAS_PER_SM");
-    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * (per_sm ? atoi(per_sm) : 2);
+    // two CTAs per SM: the link, not the SMs, bounds this launch (one, two and three per SM measured within 5 %),
+    // and kernels of the other steps in flight still find room beside them
+    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 2;
     const int grid = (int)(want < cap_ctas ? want : cap_ctas);
     if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, 1><<<grid, APPEND_THREADS, 0, st>>>(a);
     else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, 1><<<grid, APPEND_THREADS, 0, st>>>(a);
