@@ -570,7 +570,7 @@ def secondary_arm(args):
                  {"bound": "hbm", "kernel": "h2o_compact_kernel", "achieved": by_c / (ms_c * 1e-3) / 1e9, "peak": peak,
                   "peak_source": peak_src, "unit": "GB/s", "frac": by_c / (ms_c * 1e-3) / 1e9 / peak, "traffic": None}, steps)
             dst.length.fill_(2048)
-            ms_b = timed(lambda: dst.decode_attention(q, splits=args.splits), steps)
+            ms_b = timed(lambda: dst.decode_attention(q, splits=args.splits, max_ctx=2048), steps)
             by_b = B * n_kv * 2048 * per_tok + 2 * B * n_q * 128 * 2
             emit("decode_attention_budgeted_GBps", "GB/s", by_b / (ms_b * 1e-3) / 1e9, ms_b,
                  {"workload": "int8 decode attention over the H2O budget", "streams": B, "context": 2048},

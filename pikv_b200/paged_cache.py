@@ -153,8 +153,10 @@ class PagedKVCache(torch.nn.Module):
 
     def decode_attention(self, q: torch.Tensor, seq_ids: Optional[torch.Tensor] = None,
                          seq_len: Optional[torch.Tensor] = None, splits: int = 0, want_lse: bool = False,
-                         scores: Optional[torch.Tensor] = None):
-        """softmax(q K^T / sqrt(128)) V over each stream's cached context; q [B, n_q, 128] bf16.  Reads
+                         scores: Optional[torch.Tensor] = None, max_ctx: Optional[int] = None):
+        """softmax(q K^T / sqrt(128)) V over each stream's cached context; q [B, n_q, 128] bf16.  max_ctx: the
+        longest context in the batch if the caller knows it (the split count is chosen from it without a host
+        read of the lengths; default: the cache's capacity).  Reads
         int8 symmetric (pikv_decode_attn_q8) and 4-bit asymmetric (pikv_decode_attn_q4) caches."""
         q8 = self.bits == 8 and self.symmetric
         if not q8 and not (self.bits == 4 and not self.symmetric):
@@ -172,7 +174,7 @@ class PagedKVCache(torch.nn.Module):
         out = torch.empty_like(q)
         lse = torch.empty(B, n_q, dtype=torch.float32, device=dev) if (want_lse or scores is not None) else None
         if splits <= 0:
-            splits = lib().pikv_decode_attn_default_splits(B, self.n_kv, self.max_pages * PAGE_TOKENS)
+            splits = lib().pikv_decode_attn_default_splits(B, self.n_kv, max_ctx or self.max_pages * PAGE_TOKENS)
         ws = _workspace(dev, lib().pikv_decode_attn_workspace_bytes(B, n_q, self.n_kv, self.capacity, splits), "dec")
         p = DecodeParams()
         p.q, p.out, p.B, p.n_q, p.n_kv = _p(q), _p(out), B, n_q, self.n_kv
