@@ -55,6 +55,8 @@ class ClockSampler:
         self.rows, self.proc, self.index = [], None, index
 
     def start(self):
+        if os.environ.get("PIKV_BENCH_NO_CLOCKS") == "1":      # testing aid: run without the nvidia-smi poller
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -330,11 +332,23 @@ def gpu_arm(args):
         step_fn, extra_cfg = pd.make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode=args.shard_mode)
         R = extra_cfg.pop("buffer_sets", 1)
         hooks = extra_cfg.pop("hooks", None)
-        # NVLink needs sustained traffic before it runs at speed: the first multi-GPU run on an idle box
-        # measured 1.8-3.6x slower with a handful of warm-up steps.  A fixed count (every rank must run the
-        # same number of steps: the count exchange numbers them), well under a second.
-        for i in range(max(warmup, int(os.environ.get("PIKV_BENCH_MULTI_WARMUP", "8000")))):
-            step_fn(i)
+        # The first multi-GPU process on an idle box starts out 2-7x slower than later ones and recovers only
+        # after tens of seconds of traffic (N=2: 142-578 us per step with a short warm-up, 111 us after 27 s,
+        # 75 us after 45 s, which is also what a second process gets).  So untimed blocks of steps run for 45 s
+        # first; every rank stops after the same block (the decision comes from the all-reduced clock).
+        warm_s = float(os.environ.get("PIKV_BENCH_MULTI_WARMUP_S", "45"))
+        t_begin, base, block = time.time(), steps, 2000
+        while True:
+            hooks["begin"]() if hooks else None
+            for i in range(block):
+                step_fn(base + i)                 # indices past the timed range
+            hooks["end"]() if hooks else None
+            torch.cuda.synchronize()
+            tb = torch.tensor([time.time() - t_begin], device=dev)
+            dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+            base += block
+            if float(tb[0]) > warm_s:
+                break
         launch_mode = "C-ABI calls only (gate, count exchange + plan, sharded append, scale push), one CUDA graph per lane step" \
             if args.shard_mode == "peer" else "eager C-ABI calls + NCCL all_to_all"
         per_step = extra_cfg.pop("launches_per_step", None)     # kernels inside a replayed graph
