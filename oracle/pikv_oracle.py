@@ -632,6 +632,46 @@ def module_pyramid(x2d, levels_flat, layers):
     return out
 
 
+def evict_lowest(scores: np.ndarray, num_to_evict: int, cache_len: int) -> np.ndarray:
+    """bool [cache_len]: the num_to_evict lowest scores (ties: lowest index first) among the scored entries;
+    torch.topk(largest=False) of core/single/cache_scheduling.py:195,245,280,343 with a defined tie order."""
+    mask = np.zeros(cache_len, bool)
+    order = np.argsort(np.asarray(scores, F32), kind="stable")
+    mask[order[:num_to_evict]] = True
+    return mask
+
+
+def streaming_llm_mask(cache_len: int, cache_size: int, start_size: int, recent_size: int) -> np.ndarray:
+    """core/single/cache_scheduling.py:114-133."""
+    mask = np.zeros(cache_len, bool)
+    if cache_len <= cache_size:
+        return mask
+    mask[start_size:max(start_size, cache_len - recent_size)] = True
+    return mask
+
+
+def lru_plus_priority(access_times, access_frequency, importance, frequency_weight=0.3, importance_weight=0.4):
+    """core/single/cache_scheduling.py:311-327."""
+    t, f = np.asarray(access_times, F32), np.asarray(access_frequency, F32)
+    rec = F32(1.0 - frequency_weight - importance_weight)
+    return (rec * (t / (t.max() + F32(1e-8))) + F32(frequency_weight) * (f / (f.max() + F32(1e-8))) +
+            F32(importance_weight) * np.asarray(importance, F32)).astype(F32)
+
+
+def quest_utility(quality, frequency, last_access, global_time: int, decay: float = 0.95):
+    """core/single/cache_scheduling.py:164-176."""
+    age = (F32(global_time) - np.asarray(last_access, F32)).astype(F32)
+    return (np.asarray(quality, F32) * np.asarray(frequency, F32) * np.power(F32(decay), age).astype(F32)).astype(F32)
+
+
+def quest_mask(utility, threshold: float, cache_len: int, cache_size: int) -> np.ndarray:
+    """core/single/cache_scheduling.py:178-203: everything under the threshold (a mask as long as the scored
+    entries), or the lowest num_to_evict when those are too few."""
+    below = np.asarray(utility, F32) < F32(threshold)
+    n_ev = cache_len - cache_size
+    return evict_lowest(utility, n_ev, cache_len) if below.sum() < n_ev else below
+
+
 def shard_slot_base(counts_all: np.ndarray, rank: int, lengths: np.ndarray, cap: int):
     """Expert-sharded append, one step: counts_all [world, E] are every rank's selection counts.  Rows of a
     sequence are ordered by source rank, so this rank's first row of sequence e lands at

@@ -10,11 +10,13 @@ from . import ops  # noqa: F401
 from .paged_cache import PagedKVCache  # noqa: F401
 from .routing import BaseRouter, TopKBalancedRouter, AdaptiveRouter, PiKVRouter  # noqa: F401
 from .compression import BaseCompressor, PyramidCompressor, SVDCompressor, QuantizedCompressor  # noqa: F401
-from .scheduling import SchedulingPolicy, H2OScheduler, CacheSchedulingManager  # noqa: F401
+from .scheduling import (SchedulingPolicy, H2OScheduler, StreamingLLMScheduler, QUESTScheduler, FlexGenScheduler,  # noqa: F401
+                         LRUScheduler, LRUPlusScheduler, CacheSchedulingManager)
 
 __all__ = [
     "PikvError", "lib", "launch_count", "ops", "PagedKVCache",
     "BaseRouter", "TopKBalancedRouter", "AdaptiveRouter", "PiKVRouter",
     "BaseCompressor", "PyramidCompressor", "SVDCompressor", "QuantizedCompressor",
-    "SchedulingPolicy", "H2OScheduler", "CacheSchedulingManager",
+    "SchedulingPolicy", "H2OScheduler", "StreamingLLMScheduler", "QUESTScheduler", "FlexGenScheduler", "LRUScheduler",
+    "LRUPlusScheduler", "CacheSchedulingManager",
 ]

@@ -266,6 +266,63 @@ def h2o_fixtures(ref_sched):
     save("h2o_manager", **out)
 
 
+def policy_fixtures(ref_sched):
+    """The other eviction policies, called directly with more rows than cache_size (through the manager they
+    never see that): buffers hold cache_size scores, so only the first cache_size rows can be chosen."""
+    torch.manual_seed(77)
+    C, H, n = 48, 8, 64
+    keys = torch.randn(n, H)
+    out = {"keys": keys}
+
+    def tie_free(scale=1.0):
+        return (torch.randperm(C).float() + torch.rand(C) * 0.5) * scale
+
+    st = ref_sched.StreamingLLMScheduler(C, H, start_size=4, recent_size=20)
+    out["streaming/mask"] = st.select_eviction_candidates(keys, keys, {})
+    out["streaming/small"] = st.select_eviction_candidates(keys[:40], keys[:40], {})
+    lru = ref_sched.LRUScheduler(C, H)
+    lru.access_times.copy_(tie_free())
+    out["lru/access_times"] = lru.access_times
+    out["lru/mask"] = lru.select_eviction_candidates(keys, keys, {})
+    lp = ref_sched.LRUPlusScheduler(C, H)
+    lp.access_times.copy_(tie_free())
+    lp.access_frequency.copy_(tie_free())
+    lp.importance_scores.copy_(torch.rand(C))
+    for k in ("access_times", "access_frequency", "importance_scores"):
+        out[f"lru_plus/{k}"] = getattr(lp, k)
+    out["lru_plus/priority"] = lp.compute_priority_scores(n)
+    out["lru_plus/mask"] = lp.select_eviction_candidates(keys, keys, {})
+    fg = ref_sched.FlexGenScheduler(C, H)
+    fg.access_frequency.copy_(tie_free())
+    fg.access_cost.copy_(torch.rand(C) + 0.5)
+    out["flexgen/access_frequency"], out["flexgen/access_cost"] = fg.access_frequency, fg.access_cost
+    out["flexgen/mask"] = fg.select_eviction_candidates(keys, keys, {})
+    for tag, thr in (("few", 0.001), ("many", 5.0)):        # under the threshold: too few / enough
+        q = ref_sched.QUESTScheduler(C, H, quality_threshold=thr)
+        q.quality_scores.copy_(torch.rand(C) * 0.9 + 0.1)
+        q.usage_frequency.copy_(tie_free(0.25) + 1.0)
+        q.last_access_time.copy_(torch.randperm(C).float())
+        q.global_time.fill_(C)
+        for k in ("quality_scores", "usage_frequency", "last_access_time"):
+            out[f"quest_{tag}/{k}"] = getattr(q, k)
+        out[f"quest_{tag}/utility"] = q.compute_utility_scores(n)
+        out[f"quest_{tag}/mask"] = q.select_eviction_candidates(keys, keys, {})
+    # the update methods (whether they run at all under this torch is part of the record)
+    for name, fn in (("lru", lambda: ref_sched.LRUScheduler(C, H).update_access_time(torch.tensor([1, 2]))),
+                     ("flexgen", lambda: ref_sched.FlexGenScheduler(C, H).update_access_patterns(torch.tensor([1, 2]), torch.tensor([2.0, 3.0])))):
+        try:
+            fn()
+            out[f"{name}/update_raises"] = np.array(0)
+        except Exception:
+            out[f"{name}/update_raises"] = np.array(1)
+    # through the manager these policies never evict: the cache fills up and stops
+    mgr = ref_sched.CacheSchedulingManager(16, H, ref_sched.SchedulingPolicy.LRU)
+    for i in range(3):
+        mgr.update_cache(keys[None, 7 * i: 7 * i + 7], keys[None, 7 * i: 7 * i + 7])
+    out["manager_lru/keys"], out["manager_lru/size"] = mgr.cache_keys, mgr.cache_size_current
+    save("eviction_policies", **out)
+
+
 def attention_fixture(ref_attn):
     torch.manual_seed(30)
     att = ref_attn.PiKVAttention(hidden_size=64, num_heads=4, dropout=0.0)
@@ -369,6 +426,7 @@ def main():
     router_fixtures(pikv_routing, m_routing, routing_strategy)
     quant_fixtures(pikv_compression, m_compression)
     h2o_fixtures(cache_scheduling)
+    policy_fixtures(cache_scheduling)
     attention_fixture(pikv_attention)
     lowrank_fixtures(pikv_compression, m_compression, kv_cache_compression)
     torch.set_num_threads(4)

@@ -525,3 +525,48 @@ def test_cache_checkpoint_round_trip(dev):
     fresh.load_state_dict(torch.load(buf, map_location=dev))
     assert torch.equal(fresh.page_table, cache.page_table) and torch.equal(fresh.length, cache.length)
     assert torch.equal(fresh.decode_attention(q, splits=2), want)
+
+
+def test_other_eviction_policies_match_reference(dev):
+    """StreamingLLM / LRU / LRU+ / FlexGen / QUEST select_eviction_candidates against the reference's masks
+    (tie-free buffers); the lowest-m choice runs on the segmented select kernel."""
+    import pikv_b200
+    g = load_golden("eviction_policies")
+    C, H, n = 48, 8, 64
+    keys = torch.from_numpy(g["keys"]).to(dev)
+
+    def t(name):
+        return torch.from_numpy(g[name]).to(dev)
+
+    st = pikv_b200.StreamingLLMScheduler(C, H, start_size=4, recent_size=20).to(dev)
+    np.testing.assert_array_equal(st.select_eviction_candidates(keys, keys, {}).cpu().numpy(), g["streaming/mask"])
+    np.testing.assert_array_equal(st.select_eviction_candidates(keys[:40], keys[:40], {}).cpu().numpy(), g["streaming/small"])
+    lru = pikv_b200.LRUScheduler(C, H).to(dev)
+    lru.access_times.copy_(t("lru/access_times"))
+    before = pikv_b200.launch_count()
+    np.testing.assert_array_equal(lru.select_eviction_candidates(keys, keys, {}).cpu().numpy(), g["lru/mask"])
+    assert pikv_b200.launch_count() > before
+    lp = pikv_b200.LRUPlusScheduler(C, H).to(dev)
+    for k in ("access_times", "access_frequency", "importance_scores"):
+        getattr(lp, k).copy_(t(f"lru_plus/{k}"))
+    assert np.abs(lp.compute_priority_scores(n).cpu().numpy() - g["lru_plus/priority"]).max() < 1e-6
+    np.testing.assert_array_equal(lp.select_eviction_candidates(keys, keys, {}).cpu().numpy(), g["lru_plus/mask"])
+    fg = pikv_b200.FlexGenScheduler(C, H).to(dev)
+    fg.access_frequency.copy_(t("flexgen/access_frequency"))
+    fg.access_cost.copy_(t("flexgen/access_cost"))
+    np.testing.assert_array_equal(fg.select_eviction_candidates(keys, keys, {}).cpu().numpy(), g["flexgen/mask"])
+    for tag, thr in (("few", 0.001), ("many", 5.0)):
+        q = pikv_b200.QUESTScheduler(C, H, quality_threshold=thr).to(dev)
+        for k in ("quality_scores", "usage_frequency", "last_access_time"):
+            getattr(q, k).copy_(t(f"quest_{tag}/{k}"))
+        q.global_time.fill_(C)
+        np.testing.assert_array_equal(q.select_eviction_candidates(keys, keys, {}).cpu().numpy(), g[f"quest_{tag}/mask"])
+    # update methods run (the reference's LRU one raises under this torch: it stores an int64 time into a float
+    # buffer) and the manager with such a policy fills up and stops
+    lru.update_access_time(torch.tensor([1, 2], device=dev))
+    assert float(lru.access_times[1]) == 0.0 and int(lru.global_time) == 1
+    mgr = pikv_b200.CacheSchedulingManager(16, H, pikv_b200.SchedulingPolicy.LRU).to(dev)
+    for i in range(3):
+        mgr.update_cache(keys[None, 7 * i: 7 * i + 7], keys[None, 7 * i: 7 * i + 7])
+    assert int(mgr.cache_size_current) == int(g["manager_lru/size"])
+    np.testing.assert_array_equal(mgr.cache_keys.cpu().numpy(), g["manager_lru/keys"])

@@ -234,6 +234,27 @@ def test_h2o_ties_lowest_index():
     np.testing.assert_array_equal(keep, [1, 2, 5])
 
 
+def test_eviction_policies():
+    g = load_golden("eviction_policies")
+    C, n = 48, 64
+    np.testing.assert_array_equal(O.streaming_llm_mask(n, C, 4, 20), g["streaming/mask"])
+    np.testing.assert_array_equal(O.streaming_llm_mask(40, C, 4, 20), g["streaming/small"])
+    np.testing.assert_array_equal(O.evict_lowest(g["lru/access_times"], n - C, n), g["lru/mask"])
+    pr = O.lru_plus_priority(g["lru_plus/access_times"], g["lru_plus/access_frequency"], g["lru_plus/importance_scores"])
+    close(pr, g["lru_plus/priority"])
+    np.testing.assert_array_equal(O.evict_lowest(pr, n - C, n), g["lru_plus/mask"])
+    np.testing.assert_array_equal(O.evict_lowest(g["flexgen/access_frequency"] / g["flexgen/access_cost"], n - C, n),
+                                  g["flexgen/mask"])
+    for tag, thr in (("few", 0.001), ("many", 5.0)):
+        u = O.quest_utility(g[f"quest_{tag}/quality_scores"], g[f"quest_{tag}/usage_frequency"],
+                            g[f"quest_{tag}/last_access_time"], C)
+        close(u, g[f"quest_{tag}/utility"])
+        np.testing.assert_array_equal(O.quest_mask(u, thr, n, C), g[f"quest_{tag}/mask"])
+    # through the manager the cache only fills up: 16 of the 21 offered rows, in order
+    assert int(g["manager_lru/size"]) == 16
+    np.testing.assert_array_equal(g["manager_lru/keys"], g["keys"][:16])
+
+
 def test_h2o_manager_sequence():
     g = load_golden("h2o_manager")
     ck = np.zeros((64, 8), F32)
