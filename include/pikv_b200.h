@@ -116,6 +116,9 @@ typedef struct {
 #define PIKV_GATE_WHOLE 0
 #define PIKV_GATE_SCORE 1
 #define PIKV_GATE_SLOTS 2
+/* OR-ed into phase: run bf16 activations through the fp32-product SIMT kernel instead of the tensor-core
+ * one (the tests compare the two kernels with it; callers have no reason to set it). */
+#define PIKV_GATE_FORCE_SIMT 0x100
 
 size_t pikv_gate_workspace_bytes(int32_t T, int32_t E, int32_t top_k);
 int    pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream);
@@ -243,9 +246,16 @@ int pikv_shard_plan(const int32_t* gathered, int32_t world, int32_t E, int32_t r
  * the same order.  gather [PIKV_XCHG_RING][world][E] int32 and flags [PIKV_XCHG_RING][world] uint32
  * live in memory every rank has mapped (peer_*[r] = rank r's copy as seen from this GPU) and start
  * zeroed, as does *seq, this rank's step counter.  start_empty != 0: lengths restart from zero.
+ * Failure is shared: a rank whose wait ran out marks itself failed (top bit of *seq) and sets the top
+ * bit of the flags it raises from then on; a rank that sees that bit fails at once, drops its rows and
+ * raises PIKV_ST_WAIT_TIMEOUT too.  So within one more step every rank's status word shows the failure;
+ * from the failing step on the sharded cache is invalid on every rank, until a step with start_empty
+ * (which clears the marks) restarts it.  wait_limit_us: microseconds a wait may take (<= 0: the
+ * default, PIKV_DEFAULT_WAIT_US).
  * Replaces the exchange of DistributedPiKVMoE.forward (core/distributed/distributed_pikv.py:174-194)
  * for the routing counts. */
 #define PIKV_XCHG_RING 4
+#define PIKV_DEFAULT_WAIT_US 2000000
 typedef struct {
     const int32_t* counts_k;   /* [top_k][E], this rank's gate output             */
     int32_t top_k, E, world, rank, capacity, start_empty;
@@ -255,9 +265,26 @@ typedef struct {
     int32_t*  len_all;         /* [E] replicated lengths, advanced identically on every rank */
     int32_t*  slot_base;       /* [E] out: position of this rank's first row in every sequence */
     uint32_t* status;          /* may be NULL */
+    int32_t   wait_limit_us;
 } pikv_shard_exchange_params;
 
 int pikv_shard_exchange_plan(const pikv_shard_exchange_params* p, pikv_stream_t stream);
+
+/* Barrier across the ranks over peer-mapped flag words (flags [world] uint32 per rank, zeroed at start;
+ * *seq this rank's barrier counter, zeroed): when the kernel ends on a rank, everything queued before the
+ * barrier call on every rank's stream has completed, peer stores included.  The wait is bounded like every
+ * other wait of this library (PIKV_ST_WAIT_TIMEOUT in *status, the kernel returns).  Stands in for the
+ * implicit synchronisation of the all_reduce in DistributedPiKVMoE.forward
+ * (core/distributed/distributed_pikv.py:196). */
+typedef struct {
+    int32_t world, rank;
+    uint32_t* peer_flags[8];
+    uint32_t* seq;
+    uint32_t* status;          /* may be NULL */
+    int32_t   wait_limit_us;   /* <= 0: PIKV_DEFAULT_WAIT_US */
+} pikv_peer_barrier_params;
+
+int pikv_peer_barrier(const pikv_peer_barrier_params* p, pikv_stream_t stream);
 
 /* Read rows back in logical order, dequantised: out[i] = (code - zp) * scale for
  * sequence seq[i], position pos[i]; out is [n, n_kv*128] fp32, codes_out

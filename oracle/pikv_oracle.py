@@ -672,6 +672,31 @@ def quest_mask(utility, threshold: float, cache_len: int, cache_size: int) -> np
     return evict_lowest(utility, n_ev, cache_len) if below.sum() < n_ev else below
 
 
+def adakv_mask(scores: np.ndarray, cache_len: int, cache_size: int, compression_ratio: float) -> np.ndarray:
+    """AdaKVScheduler.select_eviction_candidates, core/single/module/pikv_scheduling.py:644-666: keep the
+    int(cache_len * (1 - ratio)) highest scores (safeguarded head first, then the rest: one top-k), lowest
+    index first among equals; rows without a score (past len(scores)) are evicted."""
+    mask = np.zeros(cache_len, bool)
+    if cache_len <= cache_size:
+        return mask
+    mask[:] = True
+    keep = int(cache_len * (1 - compression_ratio))
+    order = np.argsort(-np.asarray(scores[:cache_len], F32), kind="stable")[:keep]
+    mask[order] = False
+    return mask
+
+
+def duo_attention_mask(cache_len: int, cache_size: int, sink_size: int, recent_size: int) -> np.ndarray:
+    """DuoAttentionScheduler.select_eviction_candidates, core/single/module/pikv_scheduling.py:687-701."""
+    mask = np.zeros(cache_len, bool)
+    if cache_len <= cache_size:
+        return mask
+    mask[:] = True
+    mask[:sink_size] = False
+    mask[-recent_size:] = False
+    return mask
+
+
 def shard_slot_base(counts_all: np.ndarray, rank: int, lengths: np.ndarray, cap: int):
     """Expert-sharded append, one step: counts_all [world, E] are every rank's selection counts.  Rows of a
     sequence are ordered by source rank, so this rank's first row of sequence e lands at

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libpikv_b200.so")
 
 PIKV_F32, PIKV_BF16 = 0, 1
 MASK_NONE, MASK_SINGLE, MASK_MODULE, MASK_BIAS = 0, 1, 2, 3
+GATE_WHOLE, GATE_SCORE, GATE_SLOTS, GATE_FORCE_SIMT = 0, 1, 2, 0x100
 ST_BAD_SEQ, ST_BAD_PAGE, ST_BAD_INDEX, ST_WAIT_TIMEOUT = 1, 2, 8, 16
 PAGE_TOKENS = 16
 HEAD_DIM = 128
@@ -68,11 +69,16 @@ class ShardExchangeParams(C.Structure):
     _fields_ = [
         ("counts_k", vp), ("top_k", i32), ("E", i32), ("world", i32), ("rank", i32), ("capacity", i32),
         ("start_empty", i32), ("peer_gather", vp * 8), ("peer_flags", vp * 8), ("seq", vp), ("len_all", vp),
-        ("slot_base", vp), ("status", vp),
+        ("slot_base", vp), ("status", vp), ("wait_limit_us", i32),
     ]
 
 
+class PeerBarrierParams(C.Structure):
+    _fields_ = [("world", i32), ("rank", i32), ("peer_flags", vp * 8), ("seq", vp), ("status", vp), ("wait_limit_us", i32)]
+
+
 XCHG_RING = 4
+XCHG_FAILED = 0x80000000
 
 
 class CompactParams(C.Structure):
@@ -114,6 +120,7 @@ SIGNATURES = {
     "pikv_kv_append_sharded": (i32, [C.POINTER(AppendShardedParams), vp]),
     "pikv_shard_plan": (i32, [vp, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_shard_exchange_plan": (i32, [C.POINTER(ShardExchangeParams), vp]),
+    "pikv_peer_barrier": (i32, [C.POINTER(PeerBarrierParams), vp]),
     "pikv_shard_push_scales": (i32, [C.POINTER(ShardPushParams), vp]),
     "pikv_cache_gather": (i32, [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "pikv_quant_block_workspace_bytes": (sz, [i32, i32, i32]),

@@ -510,21 +510,45 @@ extern "C" int pikv_shard_plan(const int32_t* gathered, int32_t world, int32_t E
 // number in every rank's flag word; then wait, with a limit, until all ranks' flags of that slot show
 // this step, and compute slot_base / len_all from the local copy as shard_plan_kernel does.  A rank can
 // be at most one step ahead of the slowest (its next plan needs that rank's next counts), so a ring of
-// four never overwrites unread counts.  If the wait runs out, every slot_base is set to the capacity (all
-// rows of the step are dropped) and PIKV_ST_WAIT_TIMEOUT is raised: nothing hangs.
-constexpr unsigned XCHG_SPINS = 1u << 21;     // x 1 us sleep: about two seconds
+// four never overwrites unread counts.
+// Failure: if the wait runs out, every slot_base is set to the capacity (all rows of the step are
+// dropped), PIKV_ST_WAIT_TIMEOUT is raised and the rank marks itself failed (top bit of *seq).  A failed
+// rank keeps publishing, with the top bit of its flag set; a rank that sees that bit fails the same way
+// at once.  So within one more step every rank's status word shows the failure, and from the failing step
+// on the cache is invalid on all of them until a step with start_empty clears the marks.
+constexpr unsigned XCHG_FAILED = 0x80000000u;
 
-__global__ void __launch_bounds__(256) shard_exchange_plan_kernel(pikv_shard_exchange_params p) {
-    __shared__ unsigned step_s;
-    __shared__ int ok_s;
+__device__ __forceinline__ void peer_flag_store(unsigned* flag, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned peer_flag_load(const unsigned* flag) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    return v;
+}
+// polls (1 us apart) until the low 31 bits of *flag reach `want`; returns the last value seen
+__device__ __forceinline__ unsigned peer_flag_wait(const unsigned* flag, unsigned want, unsigned limit_us) {
+    unsigned seen = 0;
+    for (unsigned spins = 0;; ++spins) {
+        seen = peer_flag_load(flag);
+        if ((seen & ~XCHG_FAILED) == want || spins >= limit_us) break;
+        __nanosleep(1000);
+    }
+    return seen;
+}
+static unsigned wait_limit(int32_t limit_us) { return limit_us > 0 ? (unsigned)limit_us : PIKV_DEFAULT_WAIT_US; }
+
+__global__ void __launch_bounds__(256) shard_exchange_plan_kernel(pikv_shard_exchange_params p, unsigned limit_us) {
+    __shared__ unsigned step_s, failed_s;
     const int tid = threadIdx.x;
     if (tid == 0) {
-        step_s = *p.seq + 1u;
-        *p.seq = step_s;
-        ok_s = 1;
+        const unsigned prev = *p.seq;
+        step_s = (prev & ~XCHG_FAILED) + 1u;
+        failed_s = p.start_empty ? 0u : (prev & XCHG_FAILED);
     }
     __syncthreads();
-    const unsigned step = step_s;
+    const unsigned step = step_s & ~XCHG_FAILED;
+    const unsigned was_failed = failed_s;
     const int ring = (int)(step % PIKV_XCHG_RING);
     const int E = p.E, W = p.world;
     for (int e = tid; e < E; e += blockDim.x) {
@@ -535,24 +559,16 @@ __global__ void __launch_bounds__(256) shard_exchange_plan_kernel(pikv_shard_exc
     __threadfence_system();
     __syncthreads();
     if (tid < W) {
-        unsigned* flag = p.peer_flags[tid] + ring * W + p.rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
-    }
-    if (tid < W) {
-        const unsigned* mine = p.peer_flags[p.rank] + ring * W + tid;
-        unsigned seen = 0, spins = 0;
-        for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-            if (seen == step || ++spins >= XCHG_SPINS) break;
-            __nanosleep(1000);
-        }
-        if (seen != step) {
-            ok_s = 0;
-            if (p.status) atomicOr(p.status, PIKV_ST_WAIT_TIMEOUT);
-        }
+        peer_flag_store(p.peer_flags[tid] + ring * W + p.rank, step | was_failed);
+        const unsigned seen = peer_flag_wait(p.peer_flags[p.rank] + ring * W + tid, step, limit_us);
+        if ((seen & ~XCHG_FAILED) != step || (seen & XCHG_FAILED)) atomicOr(&failed_s, XCHG_FAILED);
     }
     __syncthreads();
-    const bool ok = ok_s != 0;
+    const bool ok = failed_s == 0;
+    if (tid == 0) {
+        *p.seq = step | failed_s;
+        if (!ok && p.status) atomicOr(p.status, PIKV_ST_WAIT_TIMEOUT);
+    }
     const int* gathered = p.peer_gather[p.rank] + (size_t)ring * W * E;
     for (int e = tid; e < E; e += blockDim.x) {
         int before = 0, total = 0;
@@ -564,6 +580,7 @@ __global__ void __launch_bounds__(256) shard_exchange_plan_kernel(pikv_shard_exc
         const int len = p.start_empty ? 0 : p.len_all[e];
         if (!ok) {
             p.slot_base[e] = p.capacity > 0 ? p.capacity : 0x3fffffff;
+            if (p.start_empty) p.len_all[e] = 0;
             continue;
         }
         p.slot_base[e] = len + before;
@@ -579,9 +596,40 @@ extern "C" int pikv_shard_exchange_plan(const pikv_shard_exchange_params* p, pik
                  PIKV_EINVAL, "shard_exchange_plan: bad sizes");
     for (int r = 0; r < p->world; ++r)
         PIKV_REQUIRE(p->peer_gather[r] && p->peer_flags[r], PIKV_EINVAL, "shard_exchange_plan: null peer buffer for rank %d", r);
-    shard_exchange_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(*p);
+    shard_exchange_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(*p, wait_limit(p->wait_limit_us));
     count_launch(1);
     return check_launch("shard_exchange_plan_kernel");
+}
+
+// ---- barrier over peer memory --------------------------------------------------------------------------
+// Every rank raises its step number in every rank's flag word and waits, with a limit, for all of them:
+// the kernels queued before it on this stream on every rank (and their stores into peer memory) are complete
+// when it returns.  A wait that runs out raises PIKV_ST_WAIT_TIMEOUT and returns; nothing spins for ever.
+__global__ void __launch_bounds__(32) peer_barrier_kernel(pikv_peer_barrier_params p, unsigned limit_us) {
+    const int tid = threadIdx.x;
+    const unsigned step = (*p.seq & ~XCHG_FAILED) + 1u;
+    __threadfence_system();
+    __syncwarp();
+    bool ok = true;
+    if (tid < p.world) {
+        peer_flag_store(p.peer_flags[tid] + p.rank, step);
+        ok = (peer_flag_wait(p.peer_flags[p.rank] + tid, step, limit_us) & ~XCHG_FAILED) == step;
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (tid == 0) {
+        *p.seq = step;
+        if (!ok && p.status) atomicOr(p.status, PIKV_ST_WAIT_TIMEOUT);
+    }
+}
+
+extern "C" int pikv_peer_barrier(const pikv_peer_barrier_params* p, pikv_stream_t stream) {
+    PIKV_REQUIRE(p != nullptr && p->seq != nullptr, PIKV_EINVAL, "peer_barrier: null params");
+    PIKV_REQUIRE(p->world >= 1 && p->world <= 8 && p->rank >= 0 && p->rank < p->world, PIKV_EINVAL, "peer_barrier: bad sizes");
+    for (int r = 0; r < p->world; ++r)
+        PIKV_REQUIRE(p->peer_flags[r] != nullptr, PIKV_EINVAL, "peer_barrier: null flag buffer for rank %d", r);
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(*p, wait_limit(p->wait_limit_us));
+    count_launch(1);
+    return check_launch("peer_barrier_kernel");
 }
 
 // ---- scales of the rows this rank stored on other GPUs --------------------------------------------------

@@ -367,8 +367,7 @@ int gate_run(const pikv_gate_params* p, cudaStream_t st, int what, GateDev* out)
     if (what & GATE_RANKS_TO_WS) g.slot = ws + (size_t)GATE_MAX_CTAS * g.E * (g.k + 2);
     int rc;
     const int E = g.E;
-    const char* force_simt = getenv("PIKV_GATE_SIMT");   // testing aid: run bf16 through the SIMT kernel too
-    const bool use_tc = g.act != nullptr && g.w2 != nullptr && gate_tc_supported(g, p->dtype) && !(force_simt && force_simt[0] == '1');
+    const bool use_tc = g.act != nullptr && g.w2 != nullptr && gate_tc_supported(g, p->dtype) && !(p->phase & PIKV_GATE_FORCE_SIMT);
     if (!(what & GATE_DO_SCORE)) {
         if (use_tc) gate_tc_geometry(g);
         if (out) *out = g;
@@ -412,9 +411,10 @@ int gate_run(const pikv_gate_params* p, cudaStream_t st, int what, GateDev* out)
 
 extern "C" int pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream) {
     PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "gate: null params");
-    PIKV_REQUIRE(p->phase >= PIKV_GATE_WHOLE && p->phase <= PIKV_GATE_SLOTS, PIKV_EINVAL, "gate: bad phase %d", p->phase);
-    const int what = p->phase == PIKV_GATE_SCORE ? GATE_DO_SCORE : p->phase == PIKV_GATE_SLOTS ? GATE_DO_SLOTS
-                                                                                              : (GATE_DO_SCORE | GATE_DO_SLOTS);
+    const int phase = p->phase & ~PIKV_GATE_FORCE_SIMT;
+    PIKV_REQUIRE(phase >= PIKV_GATE_WHOLE && phase <= PIKV_GATE_SLOTS, PIKV_EINVAL, "gate: bad phase %d", p->phase);
+    const int what = phase == PIKV_GATE_SCORE ? GATE_DO_SCORE : phase == PIKV_GATE_SLOTS ? GATE_DO_SLOTS
+                                                                                        : (GATE_DO_SCORE | GATE_DO_SLOTS);
     return gate_run(p, static_cast<cudaStream_t>(stream), what, nullptr);
 }
 

@@ -98,7 +98,7 @@ static inline EncodeTiledFn encode_fn() {
 static inline int make_tmap(CUtensorMap* tm, const void* base, int rows, int cols, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
-        set_error("lowrank: cuTensorMapEncodeTiled entry point not available");
+        set_error("tensor map: cuTensorMapEncodeTiled entry point not available");
         return PIKV_ECUDA;
     }
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -109,7 +109,7 @@ static inline int make_tmap(CUtensorMap* tm, const void* base, int rows, int col
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        set_error("lowrank: cuTensorMapEncodeTiled failed with %d", (int)r);
+        set_error("tensor map: cuTensorMapEncodeTiled failed with %d (base %p, %d x %d, box rows %d)", (int)r, base, rows, cols, box_rows);
         return PIKV_ECUDA;
     }
     return PIKV_OK;

@@ -138,7 +138,7 @@ class PeerShardedKVCache:
     single-GPU step.  No multicast object is created (plain peer pointers only).
     """
 
-    def __init__(self, num_experts: int, capacity: int, n_kv: int, device, group=None):
+    def __init__(self, num_experts: int, capacity: int, n_kv: int, device, group=None, wait_limit_us: int = 0):
         import ctypes as C
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -158,6 +158,8 @@ class PeerShardedKVCache:
         sizes = [getattr(self.cache, n).numel() * getattr(self.cache, n).element_size() for n in names]
         ring = _lib.XCHG_RING
         sizes += [ring * self.world * num_experts * 4, ring * self.world * 4]      # count exchange: gather, flags
+        sizes += [self.world * 4]                                                  # barrier flags
+        self.wait_limit_us = int(wait_limit_us)                                    # 0: the library's default (2 s)
         offs = np.concatenate([[0], np.cumsum([(b + 255) // 256 * 256 for b in sizes])])
         self._buf = symm.empty(int(offs[-1]), dtype=torch.uint8, device=self.device)
         self._buf.zero_()
@@ -167,7 +169,15 @@ class PeerShardedKVCache:
                       for i, n in enumerate(names)}
         self._peer_gather = [int(self._hdl.buffer_ptrs[r]) + int(offs[4]) for r in range(self.world)]
         self._peer_flags = [int(self._hdl.buffer_ptrs[r]) + int(offs[5]) for r in range(self.world)]
+        self._peer_bar = [int(self._hdl.buffer_ptrs[r]) + int(offs[6]) for r in range(self.world)]
         self.seq = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.bar_seq = torch.zeros(1, dtype=torch.int32, device=self.device)
+        bp = _lib.PeerBarrierParams()
+        bp.world, bp.rank, bp.seq, bp.status = self.world, self.rank, ops._p(self.bar_seq), ops._p(self.cache.status)
+        bp.wait_limit_us = self.wait_limit_us
+        for r in range(self.world):
+            bp.peer_flags[r] = self._peer_bar[r]
+        self._bar_params = bp
         # scales of rows stored on other GPUs wait here (same offsets as in the owner's pool) and cross the
         # link 32 bytes at a time after the append, instead of as one 2-byte packet per row
         entries = self.cache.k_scale.numel()
@@ -197,7 +207,10 @@ class PeerShardedKVCache:
         E = self.num_experts
         if out is None:
             out = ops.gate_fused(act, w2, b2, top_k=top_k, capacity=0)
-        ws = ops._workspace(self.device, L.lib().pikv_gate_workspace_bytes(T, E, top_k), "gate")
+        # gate scratch owned by this binding: several prepared steps (lanes, buffer sets) run concurrently on
+        # different streams, and the scratch holds the per-CTA counts the slot finalisation reads
+        ws = torch.empty(max(1, L.lib().pikv_gate_workspace_bytes(T, E, top_k)), dtype=torch.uint8, device=self.device)
+        out.workspace = ws
         b2f = None if b2 is None else ops._req(b2.to(torch.float32), "b2", torch.float32)
         gp = L.GateParams()
         gp.act, gp.w2, gp.b2, gp.dtype = ops._p(act), ops._p(w2), ops._p(b2f), L.PIKV_BF16
@@ -237,6 +250,7 @@ class PeerShardedKVCache:
         for r in range(self.world):
             xp.peer_gather[r], xp.peer_flags[r] = self._peer_gather[r], self._peer_flags[r]
         xp.seq, xp.len_all, xp.slot_base, xp.status = ops._p(self.seq), ops._p(self.len_all), ops._p(self.slot_base), ops._p(self.cache.status)
+        xp.wait_limit_us = self.wait_limit_us
         lib, keep = L.lib(), (act, w2, b2f, k, v, out, ws)
 
         def run(sync: bool = True):
@@ -275,8 +289,10 @@ class PeerShardedKVCache:
 
     def barrier(self):
         """All ranks' append kernels are complete (and their remote stores visible) after this point
-        of the stream: a device-side barrier over the symmetric memory's signal pads, no host sync."""
-        self._hdl.barrier(channel=0)
+        of the stream: pikv_peer_barrier over flag words in the symmetric buffer, no host sync.  Like every
+        wait of the library it is bounded: if a rank never arrives, PIKV_ST_WAIT_TIMEOUT is raised in the
+        cache's status word and the stream carries on."""
+        self._lib.check(self._lib.lib().pikv_peer_barrier(self._C.byref(self._bar_params), ops._stream()), "pikv_peer_barrier")
 
     def reset(self):
         """Empty the cache: the next step plans from zero lengths (no kernel is enqueued for this)."""

@@ -1,4 +1,4 @@
 """Operator variants with the surface of core/single/module/*.py."""
 from .compression import BaseCompressor, PyramidCompressor, SVDCompressor, QuantizedCompressor  # noqa: F401
 from .routing import BaseRouter, TopKBalancedRouter, AdaptiveRouter, PiKVRouter  # noqa: F401
-from .scheduling import H2OScheduler  # noqa: F401
+from .scheduling import H2OScheduler, AdaKVScheduler, DuoAttentionScheduler  # noqa: F401

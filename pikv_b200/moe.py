@@ -87,10 +87,23 @@ class KVCache(nn.Module):
         cv = cv + self.value_lora(cv)
         return cv.squeeze(0).mean(dim=0)
 
+    def set_all(self, data):
+        """core/single/pikv_moe.py:115-121: a scheduled cache is emptied, a ring cache gets `data` in every slot."""
+        if data is None:
+            return
+        if self.use_scheduling and self.scheduling_manager is not None:
+            self.scheduling_manager.reset_cache()
+        else:
+            self.values.copy_(data.unsqueeze(0).expand(self.size, -1))
+
     def get_cache_stats(self):
         if self.use_scheduling and self.scheduling_manager is not None:
             return self.scheduling_manager.get_cache_stats()
         return {"cache_size": self.size, "cache_utilization": 1.0, "policy": "none"}
+
+    def change_scheduling_policy(self, new_policy: SchedulingPolicy):
+        if self.use_scheduling and self.scheduling_manager is not None:
+            self.scheduling_manager.change_policy(new_policy)
 
 
 class PiKVMoE(nn.Module):
@@ -138,6 +151,70 @@ class PiKVMoE(nn.Module):
         if not self.use_cache_scheduling:
             self._host_ptrs[expert_idx] = (ptr + 1) % cache.size
             self.cache_ptrs[expert_idx] = self._host_ptrs[expert_idx]
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        self._host_ptrs = None          # the ring pointers are read again from the loaded cache_ptrs
+
+    # -- cache scheduling switches, core/single/pikv_moe.py:338-379 -------------------------------------
+    def enable_cache_scheduling(self, policy: SchedulingPolicy = SchedulingPolicy.LRU):
+        self.use_cache_scheduling, self.cache_scheduling_policy = True, policy
+        for cache in self.kv_caches:
+            cache.use_scheduling = True
+            if cache.scheduling_manager is None:
+                cache.scheduling_manager = CacheSchedulingManager(cache.size, cache.hidden_size, policy).to(cache.keys.device)
+            else:
+                cache.scheduling_manager.change_policy(policy)
+
+    def disable_cache_scheduling(self):
+        self.use_cache_scheduling = False
+        for cache in self.kv_caches:
+            cache.use_scheduling = False
+            if cache.scheduling_manager is not None:
+                cache.scheduling_manager.reset_cache()
+
+    def change_cache_scheduling_policy(self, new_policy: SchedulingPolicy):
+        if self.use_cache_scheduling:
+            self.cache_scheduling_policy = new_policy
+            for cache in self.kv_caches:
+                cache.change_scheduling_policy(new_policy)
+
+    def get_cache_stats(self):
+        return {f"expert_{i}": cache.get_cache_stats() for i, cache in enumerate(self.kv_caches)}
+
+    # -- checkpoints, core/single/pikv_moe.py:456-505 -----------------------------------------------------
+    def save_checkpoint(self, path):
+        """The reference's dictionary (same keys).  `model_state_dict` already holds every cache buffer
+        (ring slots or the scheduled manager's rows and scores), so a load restores the caches exactly;
+        `kv_caches` (one mean vector per cache) is written as the reference writes it."""
+        checkpoint = {
+            "model_state_dict": self.state_dict(),
+            "cache_ptrs": self.cache_ptrs,
+            "kv_caches": [cache.get_all() for cache in self.kv_caches],
+            "use_distillation": self.use_distillation,
+            "use_cache_scheduling": self.use_cache_scheduling,
+            "cache_scheduling_policy": self.cache_scheduling_policy.value if self.use_cache_scheduling else None,
+        }
+        if self.use_cache_scheduling:
+            checkpoint["cache_stats"] = self.get_cache_stats()
+        torch.save(checkpoint, path)
+
+    def load_checkpoint(self, path):
+        """Inverse of save_checkpoint, in the reference's order: state dict, ring pointers, then set_all with
+        the saved mean vectors (which, as in the reference, overwrites a ring cache's value rows with that
+        vector and empties a scheduled cache), then the scheduling settings."""
+        checkpoint = torch.load(path, map_location=self.cache_ptrs.device, weights_only=False)
+        self.load_state_dict(checkpoint["model_state_dict"])
+        self.cache_ptrs.copy_(checkpoint["cache_ptrs"])
+        self._host_ptrs = None
+        for i, data in enumerate(checkpoint["kv_caches"]):
+            if data is not None:
+                self.kv_caches[i].set_all(data)
+        if checkpoint.get("use_cache_scheduling", False):
+            try:
+                self.enable_cache_scheduling(SchedulingPolicy(checkpoint.get("cache_scheduling_policy", "none")))
+            except ValueError:
+                pass
 
     def forward(self, x, query=None, return_loss=False, targets=None, use_teacher=False):
         if x.dim() == 2:

@@ -323,6 +323,26 @@ def policy_fixtures(ref_sched):
     save("eviction_policies", **out)
 
 
+def module_policy_fixtures(ref_msched):
+    """AdaKV and DuoAttention of core/single/module/pikv_scheduling.py, called with more rows than cache_size."""
+    torch.manual_seed(78)
+    C, H, n = 48, 8, 64
+    keys = torch.randn(n, H)
+    out = {"keys": keys}
+    ada = ref_msched.AdaKVScheduler(C, H, compression_ratio=0.5, safeguard_ratio=0.2)
+    with torch.no_grad():
+        ada.update_importance(torch.arange(C), keys[:C])
+    out["adakv/weights/weight"], out["adakv/weights/bias"] = ada.linear_proj.weight, ada.linear_proj.bias
+    out["adakv/importance_scores"] = ada.importance_scores
+    out["adakv/mask"] = ada.select_eviction_candidates(keys, keys, {})
+    out["adakv/small"] = ada.select_eviction_candidates(keys[:40], keys[:40], {})
+    duo = ref_msched.DuoAttentionScheduler(C, H, sink_size=5, recent_size=17)
+    out["duo/mask"] = duo.select_eviction_candidates(keys, keys, {})
+    out["duo/small"] = duo.select_eviction_candidates(keys[:40], keys[:40], {})
+    out["duo/evictions"] = duo.eviction_count.clone()
+    save("eviction_policies_module", **out)
+
+
 def attention_fixture(ref_attn):
     torch.manual_seed(30)
     att = ref_attn.PiKVAttention(hidden_size=64, num_heads=4, dropout=0.0)
@@ -427,6 +447,8 @@ def main():
     quant_fixtures(pikv_compression, m_compression)
     h2o_fixtures(cache_scheduling)
     policy_fixtures(cache_scheduling)
+    from core.single.module import pikv_scheduling as m_scheduling
+    module_policy_fixtures(m_scheduling)
     attention_fixture(pikv_attention)
     lowrank_fixtures(pikv_compression, m_compression, kv_cache_compression)
     torch.set_num_threads(4)

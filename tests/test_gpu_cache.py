@@ -570,3 +570,29 @@ def test_other_eviction_policies_match_reference(dev):
         mgr.update_cache(keys[None, 7 * i: 7 * i + 7], keys[None, 7 * i: 7 * i + 7])
     assert int(mgr.cache_size_current) == int(g["manager_lru/size"])
     np.testing.assert_array_equal(mgr.cache_keys.cpu().numpy(), g["manager_lru/keys"])
+
+
+def test_module_adakv_and_duo_attention_match_reference(dev):
+    """AdaKVScheduler / DuoAttentionScheduler (core/single/module/pikv_scheduling.py:624-710) against the
+    reference's masks; both run on the segmented select kernel."""
+    import pikv_b200
+    from pikv_b200.module import AdaKVScheduler, DuoAttentionScheduler
+    g = load_golden("eviction_policies_module")
+    C, H, n = 48, 8, 64
+    keys = torch.from_numpy(g["keys"]).to(dev)
+    ada = AdaKVScheduler(C, H, compression_ratio=0.5, safeguard_ratio=0.2).to(dev)
+    ada.linear_proj.weight.data.copy_(torch.from_numpy(g["adakv/weights/weight"]))
+    ada.linear_proj.bias.data.copy_(torch.from_numpy(g["adakv/weights/bias"]))
+    with torch.no_grad():
+        ada.update_importance(torch.arange(C, device=dev), keys[:C])
+    assert np.abs(ada.importance_scores.cpu().numpy() - g["adakv/importance_scores"]).max() < 1e-5
+    ada.importance_scores.copy_(torch.from_numpy(g["adakv/importance_scores"]))
+    before = pikv_b200.launch_count()
+    np.testing.assert_array_equal(ada.select_eviction_candidates(keys, keys, {}).cpu().numpy(), g["adakv/mask"])
+    assert pikv_b200.launch_count() > before
+    np.testing.assert_array_equal(ada.select_eviction_candidates(keys[:40], keys[:40], {}).cpu().numpy(), g["adakv/small"])
+    duo = DuoAttentionScheduler(C, H, sink_size=5, recent_size=17).to(dev)
+    np.testing.assert_array_equal(duo.select_eviction_candidates(keys, keys, {}).cpu().numpy(), g["duo/mask"])
+    np.testing.assert_array_equal(duo.select_eviction_candidates(keys[:40], keys[:40], {}).cpu().numpy(), g["duo/small"])
+    assert int(duo.eviction_count) == int(g["duo/evictions"])
+    assert duo.get_scheduler_stats()["sink_size"] == 5

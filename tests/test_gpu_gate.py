@@ -130,11 +130,11 @@ def test_gate_from_activations(dev, dtype, T, H, E):
     np.testing.assert_array_equal(g.counts_k.cpu().numpy(), counts_k)
 
 
-def test_gate_bf16_simt_and_tensor_core_paths_agree(dev, monkeypatch):
+def test_gate_bf16_simt_and_tensor_core_paths_agree(dev):
     """bf16 activations normally take the tcgen05 kernel; the SIMT kernel must give the same experts
     and slots (near-ties aside) and probabilities within fp32 accumulation noise."""
     import pikv_b200
-    from pikv_b200 import ops
+    from pikv_b200 import ops, _lib
     torch.manual_seed(21)
     T, H, E = 3000, 1024, 8
     act = torch.relu(torch.randn(T, H, device=dev)).bfloat16()
@@ -142,9 +142,7 @@ def test_gate_bf16_simt_and_tensor_core_paths_agree(dev, monkeypatch):
     tc = ops.gate_fused(act, w2, None, top_k=2, capacity=1200)
     torch.cuda.synchronize()
     assert pikv_b200.lib().pikv_gate_error_state() == 0
-    monkeypatch.setenv("PIKV_GATE_SIMT", "1")
-    simt = ops.gate_fused(act, w2, None, top_k=2, capacity=1200)
-    monkeypatch.delenv("PIKV_GATE_SIMT")
+    simt = ops.gate_fused(act, w2, None, top_k=2, capacity=1200, phase=_lib.GATE_FORCE_SIMT)
     same = (tc.topk_idx == simt.topk_idx).all(dim=1)
     assert int((~same).sum()) <= 3
     assert torch.allclose(tc.probs, simt.probs, rtol=1e-4, atol=1e-7)

@@ -327,3 +327,14 @@ def test_bf16_round():
     x = np.random.default_rng(0).standard_normal(10000).astype(F32) * 37
     ref = torch.from_numpy(x).bfloat16().float().numpy()
     np.testing.assert_array_equal(O.bf16_round(x), ref)
+
+
+def test_module_adakv_and_duo_attention_masks():
+    g = load_golden("eviction_policies_module")
+    C, n = 48, 64
+    sc = g["adakv/importance_scores"]
+    np.testing.assert_array_equal(O.adakv_mask(sc, n, C, 0.5), g["adakv/mask"])
+    np.testing.assert_array_equal(O.adakv_mask(sc, 40, C, 0.5), g["adakv/small"])
+    np.testing.assert_array_equal(O.duo_attention_mask(n, C, 5, 17), g["duo/mask"])
+    np.testing.assert_array_equal(O.duo_attention_mask(40, C, 5, 17), g["duo/small"])
+    assert int(g["duo/evictions"]) == 1
