@@ -33,6 +33,7 @@ WORKLOAD = dict(workload="route+int8-quant+append", tokens=16384, hidden=4096, e
                 head_dim=128, page_tokens=16, quant="int8-sym-g128", capacity_factor=1.5)
 GATE_BYTES_PER_TOKEN = 4096 * 2 + 8 * 4 + 3 * 2 * 4                      # act in; probs, idx, w, slot out
 APPEND_BYTES_PER_TOKEN = 2 * 1024 * 2 + 16 + 2 * 2 * 1024 + 2 * 16 * 2   # K,V in; idx/slot; 2 copies of codes + scales
+APPEND_BYTES_INT4 = 2 * 1024 * 2 + 16 + 2 * 2 * 512 + 2 * 16 * (2 + 4)   # 4-bit codes, bf16 scales, fp32 zero points
 # DRAM bytes per launch (read + write) at 16384 tokens, from the ncu captures summarised under profiles/
 # (the append's 67.4 MB of reads arrive in full; of its 68 MB of writes 21.6 MB had left the 126 MB L2 at kernel end)
 TRAFFIC = {"gate": 139.2e6, "append": 89.0e6}
@@ -113,50 +114,96 @@ def gate_weights(H, E, seed):
 
 
 # ----------------------------------------------------------------------------- CPU port (reference arm)
-def cpu_step(act, w2, b2, K, V, E, top_k, cap):
-    from oracle import pikv_oracle as O
-    logits = O.gate_logits(act, w2, b2)
-    probs, idx, tw = O.gate_tail(logits, top_k)
-    slot, counts_k = O.slot_assign_fast(idx, E, cap)
-    out = O.routed_append(K, V, idx, slot, E, cap, 8, True, 128)
-    return out["length"]
-
-
-def cpu_threads():
+def host_threads():
+    """Threads the CPU port may use: the cores this process is allowed on.  torchrun exports OMP_NUM_THREADS=1
+    for its workers; the port is a baseline of the host, so it lifts that limit for itself (before numpy
+    loads its BLAS)."""
     try:
-        from threadpoolctl import threadpool_info
-        return max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
+        n = len(os.sched_getaffinity(0))
     except Exception:
-        return os.cpu_count() or 1
+        n = os.cpu_count() or 1
+    return max(1, n)
+
+
+class CpuPort:
+    """The numpy port of one step, with its cache arrays allocated once (int8 codes, fp32 scales).  The gate
+    GEMM is BLAS (threaded); the element-wise parts (softmax / top-k, the per-slice quantisation, the scatter of
+    the rows into the cache) are numpy calls that release the GIL, run over token chunks on `nthreads` threads;
+    the slot scan is serial."""
+
+    def __init__(self, tokens, nthreads):
+        from concurrent.futures import ThreadPoolExecutor
+        import numpy as np
+        cfg = WORKLOAD
+        self.H, self.E, self.k = cfg["hidden"], cfg["experts"], cfg["top_k"]
+        kv = cfg["kv_heads"] * cfg["head_dim"]
+        act, K, V = synth_inputs(tokens, self.H, self.E, kv, 1)
+        w2, b2 = gate_weights(self.H, self.E, 7)
+        self.a, self.K, self.V = act.float().numpy(), K.float().numpy(), V.float().numpy()
+        self.w, self.b = w2.float().numpy(), b2.numpy()
+        self.cap = int(tokens * cfg["capacity_factor"] * self.k / self.E)
+        self.T, self.n = tokens, nthreads
+        self.pool = ThreadPoolExecutor(nthreads)
+        self.bounds = [(i * tokens // nthreads, (i + 1) * tokens // nthreads) for i in range(nthreads)]
+        G = kv // 128
+        self.codes = [np.zeros((self.E, self.cap, kv), np.int8) for _ in range(2)]
+        self.scales = [np.zeros((self.E, self.cap, G), np.float32) for _ in range(2)]
+
+    def step(self):
+        from oracle import pikv_oracle as O
+        import numpy as np
+        logits = O.gate_logits(self.a, self.w, self.b)
+        tails = list(self.pool.map(lambda ab: O.gate_tail(logits[ab[0]:ab[1]], self.k), self.bounds))
+        idx = np.concatenate([t[1] for t in tails])
+        slot, counts_k = O.slot_assign_fast(idx, self.E, self.cap)
+
+        def chunk(ab):
+            lo, hi = ab
+            t_ix, j_ix = np.nonzero(slot[lo:hi] >= 0)
+            e, sl = idx[lo:hi][t_ix, j_ix], slot[lo:hi][t_ix, j_ix]
+            for x, codes, scales in ((self.K, self.codes[0], self.scales[0]), (self.V, self.codes[1], self.scales[1])):
+                q, sc, _ = O.quant_token_groups(x[lo:hi], 8, 128, True)
+                codes[e, sl] = q[t_ix].astype(np.int8)
+                scales[e, sl] = sc[t_ix]
+
+        list(self.pool.map(chunk, self.bounds))
+        return counts_k
+
+    def close(self):
+        self.pool.shutdown()
 
 
 def run_cpu(steps, warmup, tokens):
-    cfg = WORKLOAD
-    H, E, k = cfg["hidden"], cfg["experts"], cfg["top_k"]
-    kv = cfg["kv_heads"] * cfg["head_dim"]
-    act, K, V = synth_inputs(tokens, H, E, kv, 1)
-    w2, b2 = gate_weights(H, E, 7)
-    a, kk, vv = act.float().numpy(), K.float().numpy(), V.float().numpy()
-    w, b = w2.float().numpy(), b2.numpy()
-    cap = int(tokens * cfg["capacity_factor"] * k / E)
+    nthreads = host_threads()
+    for var in ("OMP_NUM_THREADS", "MKL_NUM_THREADS", "OPENBLAS_NUM_THREADS"):
+        os.environ[var] = str(nthreads)
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(nthreads)
+    except Exception:
+        pass
+    port = CpuPort(tokens, nthreads)
     for _ in range(warmup):
-        cpu_step(a, w, b, kk, vv, E, k, cap)
+        port.step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        cpu_step(a, w, b, kk, vv, E, k, cap)
+        port.step()
     dt = (time.perf_counter() - t0) / steps
-    return tokens / dt, dt
+    port.close()
+    return tokens / dt, dt, nthreads
 
 
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    # every step is one full 16384-token batch (about 0.1-0.4 s on the host); the step count is the caller's,
+    # cut only where the run would pass a few minutes
+    steps, warmup = max(1, min(args.steps, 200)), max(1, min(args.warmup, 3))
     tokens = WORKLOAD["tokens"]
-    value, dt = run_cpu(steps, warmup, tokens)
-    cores = cpu_threads()
-    sample = f"{steps} full batches of {tokens} tokens (numpy port of the reference arithmetic; BLAS GEMM threaded)"
+    value, dt, cores = run_cpu(steps, warmup, tokens)
+    sample = (f"{steps} full batches of {tokens} tokens (numpy port of the reference arithmetic; BLAS GEMM and "
+              f"token-chunked element-wise parts on {cores} threads)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -169,6 +216,119 @@ def reference_arm(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
+
+
+def pool_hash(t):
+    """Order-sensitive 64-bit checksum of a pool tensor (wrapping int64 arithmetic, computed on its device)."""
+    import torch
+    raw = t.contiguous().view(torch.uint8).view(-1)
+    pad = (-raw.numel()) % 8
+    if pad:
+        raw = torch.cat([raw, raw.new_zeros(pad)])
+    w = raw.view(torch.int64)
+    pos = torch.arange(w.numel(), device=w.device, dtype=torch.int64)
+    return int(((w ^ (pos * 0x1E3779B97F4A7C15)) * (2 * pos + 1)).sum().item())
+
+
+def parity_single(torch, pikv_b200, ops, dev, cfg, w2, b2):
+    """One fixed-seed config-2 step at full size against the oracle, outside every timed region: expert
+    indices (mismatches must be near-ties of the oracle's top-k and are counted), then - on the GPU's own
+    indices - slots, per-column counts, lengths, every code and every stored scale, bit for bit."""
+    import numpy as np
+    from oracle import pikv_oracle as O
+    T, H, E, k = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["top_k"]
+    n_kv = cfg["kv_heads"]
+    kv = n_kv * cfg["head_dim"]
+    cap = int(T * cfg["capacity_factor"] * k / E)
+    act, K, V = synth_inputs(T, H, E, kv, 0)
+    g = ops.gate_fused(act.to(dev), w2, b2, top_k=k, capacity=cap)
+    cache = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
+    cache.append(K.to(dev), V.to(dev), g.topk_idx, g.slot)
+    torch.cuda.synchronize()
+    cache.check_status()
+    logits = O.gate_logits(act.float().numpy(), w2.float().cpu().numpy(), b2.cpu().numpy())
+    probs, idx, tw = O.gate_tail(logits, k)
+    gi = g.topk_idx.cpu().numpy()
+    diff = (gi != idx).any(axis=1)
+    margin = O.topk_margin(probs, k)
+    rec = {"n": 1, "tokens": T, "idx_mismatch": int(diff.sum()), "idx_near_ties": int((diff & (margin < 1e-4)).sum())}
+    ok = rec["idx_mismatch"] == rec["idx_near_ties"]
+    rec["probs_max_abs_err"] = float(np.abs(g.probs.cpu().numpy() - probs).max())
+    ok &= rec["probs_max_abs_err"] < 1e-3          # bf16 products, fp32 accumulation in another order
+    slot, counts_k = O.slot_assign_fast(gi, E, cap)
+    same = lambda a_, b_: "bit-exact" if np.array_equal(a_, b_) else "MISMATCH"
+    rec["slots"] = same(g.slot.cpu().numpy(), slot)
+    rec["counts"] = same(g.counts_k.cpu().numpy(), counts_k)
+    ref = O.routed_append(K.float().numpy(), V.float().numpy(), gi, slot, E, cap, 8, True, 128)
+    rec["lengths"] = same(g.new_len.cpu().numpy(), ref["length"])
+    lens = ref["length"]
+    seq = np.repeat(np.arange(E), cap).astype(np.int32)
+    pos = np.tile(np.arange(cap), E).astype(np.int32)
+    valid = pos < lens[seq]
+    seq_t, pos_t = torch.from_numpy(seq[valid]).to(dev), torch.from_numpy(pos[valid]).to(dev)
+    mp = cache.max_pages
+    for name in ("k", "v"):
+        _, codes = cache.gather(seq_t, pos_t, name, codes=True)
+        rec[f"{name}_codes"] = same(codes.cpu().numpy(), ref[f"{name}_codes"][seq[valid], pos[valid]].astype(np.int8))
+        sc = getattr(cache, f"{name}_scale").view(E, mp, n_kv, 16).permute(0, 1, 3, 2).reshape(E, mp * 16, n_kv)[:, :cap]
+        got = sc.float().cpu().numpy()[seq[valid], pos[valid]]
+        rec[f"{name}_scales"] = same(got, O.bf16_round(ref[f"{name}_scale"][seq[valid], pos[valid]]))
+    rec["rows_checked"] = int(valid.sum())
+    ok &= all(v != "MISMATCH" for v in rec.values())
+    rec["ok"] = bool(ok)
+    return rec
+
+
+def parity_multi(torch, dist, pikv_b200, ops, dev, rank, world, cfg, w2, b2, mode):
+    """The ranks' caches after one fixed-seed step against the cache ONE GPU builds from the concatenated
+    batch: every rank checksums its pools, rank 0 routes all world x tokens on its own GPU and compares its
+    slices (expert block r) and lengths with rank r's."""
+    from pikv_b200 import distributed as pd
+    T, H, E, k = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["top_k"]
+    n_kv = cfg["kv_heads"]
+    kv = n_kv * cfg["head_dim"]
+    cap = int(T * world * cfg["capacity_factor"] * k / E)
+    act, K, V = synth_inputs(T, H, E, kv, 5000 + rank, device=dev)
+    shard = (pd.PeerShardedKVCache if mode == "peer" else pd.ExpertShardedKVCache)(E, cap, n_kv, dev)
+    shard.route_append(act, w2, b2, K, V, top_k=k)
+    torch.cuda.synchronize()
+    dist.barrier()
+    status = int(shard.cache.status.item())
+    names = ("k_codes", "v_codes", "k_scale", "v_scale", "length")
+    mine = torch.tensor([pool_hash(getattr(shard.cache, n)) for n in names] + [status], dtype=torch.int64, device=dev)
+    allh = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    rec = None
+    if rank == 0:
+        parts = [synth_inputs(T, H, E, kv, 5000 + r, device=dev) for r in range(world)]
+        A, KK, VV = (torch.cat([p_[i] for p_ in parts]) for i in range(3))
+        g = ops.gate_fused(A, w2, b2, top_k=k, capacity=cap)
+        single = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
+        single.append(KK, VV, g.topk_idx, g.slot)
+        single.length.copy_(g.new_len)
+        torch.cuda.synchronize()
+        single.check_status()
+        per, pages = E // world, single.max_pages
+        bad = []
+        for r in range(world):
+            sl = slice(r * per * pages, (r + 1) * per * pages)
+            want = [pool_hash(getattr(single, n)[sl]) for n in names[:4]] + [pool_hash(single.length[r * per:(r + 1) * per]), 0]
+            got = [int(x) for x in allh[r].tolist()]
+            bad += [f"rank{r}:{n}" for n, w_, g_ in zip(names + ("status",), want, got) if w_ != g_]
+        rec = {"n": world, "tokens": T * world, "against": "the cache one GPU builds from the concatenated batch",
+               "codes": "bit-exact" if not any("codes" in b_ for b_ in bad) else "MISMATCH",
+               "scales": "bit-exact" if not any("scale" in b_ for b_ in bad) else "MISMATCH",
+               "lengths": "equal" if not any("length" in b_ for b_ in bad) else "MISMATCH",
+               "status_words": "clear" if not any("status" in b_ for b_ in bad) else "SET", "bad": bad, "ok": not bad}
+        del single, parts, A, KK, VV
+    del shard
+    torch.cuda.empty_cache()
+    return rec
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -192,7 +352,7 @@ def gpu_arm(args):
     if args.bits == 4:
         # config 2's second format: 4-bit asymmetric codes, bf16 scales and fp32 zero points per (token, head)
         cfg.update(workload="route+int4-quant+append", quant="int4-asym-g128")
-        app_bytes = 2 * 1024 * 2 + 16 + 2 * 2 * 512 + 2 * 16 * (2 + 4)
+        app_bytes = APPEND_BYTES_INT4
     T, H, E, k = cfg["tokens"], cfg["hidden"], cfg["experts"], cfg["top_k"]
     n_kv = cfg["kv_heads"]
     kv = n_kv * cfg["head_dim"]
@@ -276,13 +436,32 @@ def gpu_arm(args):
         barrier()
         return e0.elapsed_time(e1)
 
-    def single_gpu_workload(tokens):
+    def timed_repeats(replay, n, hooks=None, min_total_ms=500.0, min_reps=10, max_reps=600):
+        """The K-step timed region, repeated: the headline is the median region, the spread is reported.  The
+        repeat count comes from the first region (max over ranks, so every rank runs the same number) and is
+        at least `min_reps`; repeating until `min_total_ms` also gives the clock sampler (one sample per
+        100 ms) something to see."""
+        first = timed(replay, n, hooks)
+        if world > 1:
+            f = torch.tensor([first], device=dev)
+            dist.all_reduce(f, op=dist.ReduceOp.MAX)
+            first = float(f.item())
+        reps = int(min(max_reps, max(min_reps, min_total_ms / max(first, 1e-3))))
+        out = [timed(replay, n, hooks) for _ in range(reps)]
+        if world > 1:
+            t_ = torch.tensor(out, device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)      # every region: the slowest rank's time
+            out = [float(x) for x in t_.tolist()]
+        return out
+
+    def single_gpu_workload(tokens, bits=None):
         """R rotating input sets and caches so that no step finds its inputs in L2 (one set is 201 MB at
         16384 tokens, L2 is 126 MB)."""
+        bits = args.bits if bits is None else bits
         cap = int(tokens * cfg["capacity_factor"] * k / E)
         R = 6 if tokens <= 32768 else 3     # more sets in flight let the gates run further ahead of the appends
         sets = [synth_inputs(tokens, H, E, kv, 100 + i, device=dev) for i in range(R)]
-        caches = [pikv_b200.PagedKVCache(E, cap, n_kv, bits=args.bits, symmetric=(args.bits == 8), device=dev) for _ in range(R)]
+        caches = [pikv_b200.PagedKVCache(E, cap, n_kv, bits=bits, symmetric=(bits == 8), device=dev) for _ in range(R)]
         outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=cap, want_probs=True) for _ in range(R)]
 
         def gate(i):
@@ -321,24 +500,26 @@ def gpu_arm(args):
                 if name == "pappend":
                     w["slots"](i)                          # the append is timed on final slots
             graph = capture(lambda: [w[name](i) for i in range(R_)])[0]
-            reps = max(2, -(-n // R_))
+            reps = max(20, -(-n // R_))
             graph.replay()
             out.append(timed(lambda i: graph.replay(), reps) / (reps * R_))
         return out
 
-    roof = e2e = cpu = large = None
+    roof = e2e = cpu = large = parity = extras = None
+    multi = {}
     if world > 1:
         from pikv_b200 import distributed as pd
+        parity = parity_multi(torch, dist, pikv_b200, ops, dev, rank, world, cfg, w2, b2, args.shard_mode)
         step_fn, extra_cfg = pd.make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode=args.shard_mode)
         R = extra_cfg.pop("buffer_sets", 1)
         hooks = extra_cfg.pop("hooks", None)
-        # The first multi-GPU process on an idle box starts out 2-7x slower than later ones and recovers only
-        # after tens of seconds of traffic (N=2: 142-578 us per step with a short warm-up, 111 us after 27 s,
-        # 75 us after 45 s, which is also what a second process gets).  So untimed blocks of steps run for 45 s
-        # first; every rank stops after the same block (the decision comes from the all-reduced clock).
-        warm_s = float(os.environ.get("PIKV_BENCH_MULTI_WARMUP_S", "45"))
+        verify = extra_cfg.pop("verify", None)
+        # The first multi-GPU process on an idle box starts out slower than later ones and recovers only with
+        # traffic, so untimed blocks of steps run for `warm_s` seconds first; every rank stops after the same
+        # block (the decision comes from the all-reduced clock).  The JSON line states the seconds.
+        warm_s = float(os.environ.get("PIKV_BENCH_MULTI_WARMUP_S", str(args.multi_warmup_s)))
         t_begin, base, block = time.time(), steps, 2000
-        while True:
+        while warm_s > 0:
             hooks["begin"]() if hooks else None
             for i in range(block):
                 step_fn(base + i)                 # indices past the timed range
@@ -349,6 +530,7 @@ def gpu_arm(args):
             base += block
             if float(tb[0]) > warm_s:
                 break
+        multi["warmup_s"] = round(time.time() - t_begin, 1)
         launch_mode = "C-ABI calls only (gate, count exchange + plan, sharded append, scale push), one CUDA graph per lane step" \
             if args.shard_mode == "peer" else "eager C-ABI calls + NCCL all_to_all"
         per_step = extra_cfg.pop("launches_per_step", None)     # kernels inside a replayed graph
@@ -359,8 +541,16 @@ def gpu_arm(args):
         if rank == 0:
             sampler.start()
         n0 = pikv_b200.launch_count()
-        ms = timed(replay, steps, hooks)
-        launches = per_step * steps if per_step is not None else pikv_b200.launch_count() - n0
+        regions = timed_repeats(replay, steps, hooks, min_total_ms=500.0)
+        ms = median(regions)
+        launches = per_step * steps if per_step is not None else (pikv_b200.launch_count() - n0) // (len(regions) + 1)
+        clocks = sampler.stop() if rank == 0 else None
+        if verify is not None:
+            multi["lanes_verified"] = verify()               # status words and lengths of every lane's cache
+        link = extra_cfg.pop("link_bytes_per_step", None)
+        if link is not None:
+            multi["link_bytes_per_gpu_per_step"] = link
+            multi["link_GBps_per_gpu"] = link / (ms / steps * 1e-3) / 1e9
         e2e_io = extra_cfg.pop("e2e_io", None)
         if e2e_io is not None:
             e2e_step, h2d, d2h = e2e_io
@@ -371,13 +561,14 @@ def gpu_arm(args):
             e2e = {"value": T * world * steps / (float(e2e_ms.item()) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
                    "d2h_bytes_per_step": d2h * world, "ms_per_step": float(e2e_ms.item()) / steps}
     else:
+        parity = parity_single(torch, pikv_b200, ops, dev, cfg, w2, b2) if args.bits == 8 else None
         wl = single_gpu_workload(T)
         R = wl["R"]
         # serial schedule: one stream, gate then append (pikv_route_append), one graph per step
         graphs = [capture(lambda i=i: wl["step"](i)) for i in range(R)]
         for i in range(warmup):
             graphs[i % R][0].replay()
-        serial_ms = timed(lambda i: graphs[i % R][0].replay(), steps) / steps
+        serial_ms = median(timed_repeats(lambda i: graphs[i % R][0].replay(), steps, min_total_ms=100.0)) / steps
         sampler = ClockSampler(local)
         if args.schedule == "pipelined":
             # batch i+1 is gated while batch i is appended; K replays = K gates + K appends
@@ -389,21 +580,22 @@ def gpu_arm(args):
                 window[0].replay()
             sampler.start()
             replay = run_pipelined(wl, window, tail)
-            ms = timed(lambda i: replay(i, steps), steps)
+            regions = timed_repeats(lambda i: replay(i, steps), steps)
             launches = window[1] * (steps // W) + (tail[1] if steps % W else 0)
             launch_mode = (f"CUDA graphs of {W} steps (captured C-ABI calls): gates on one stream, appends on another, "
                            "append(i) after gate(i)")
         else:
             sampler.start()
-            ms = timed(lambda i: graphs[i % R][0].replay(), steps)
+            regions = timed_repeats(lambda i: graphs[i % R][0].replay(), steps)
             launches = graphs[0][1] * steps
             launch_mode = "one CUDA graph replay per step (captured C-ABI calls, one stream)"
+        ms = median(regions)
+        clocks = sampler.stop()
         extra_cfg = {"parallelism": "single", "schedule": args.schedule}
-    t = torch.tensor([ms], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
+    ms_max = ms
     value = T * world * steps / (ms_max * 1e-3)
+    repeats = {"regions": len(regions), "steps_per_region": steps, "timed_ms_total": sum(regions),
+               "ms_per_step_median": ms / steps, "ms_per_step_min": min(regions) / steps, "ms_per_step_max": max(regions) / steps}
 
     if world == 1:
         peak, peak_src = measured_peak_gbs()
@@ -419,7 +611,9 @@ def gpu_arm(args):
                 "gate": {"ms": gate_ms, "GBps": gate_gbs, "frac": gate_gbs / peak, "bytes_per_token": GATE_BYTES_PER_TOKEN},
                 "append": {"ms": app_ms, "GBps": app_gbs, "frac": app_gbs / peak, "bytes_per_token": app_bytes},
                 "finalize": {"ms": fin_ms},
-                "step": {"GBps": step_gbs, "frac": step_gbs / peak}}
+                "step": {"GBps": step_gbs, "frac": step_gbs / peak},
+                "serial_step": {"GBps": (GATE_BYTES_PER_TOKEN + app_bytes) * T / (serial_ms * 1e-3) / 1e9,
+                                "frac": (GATE_BYTES_PER_TOKEN + app_bytes) * T / (serial_ms * 1e-3) / 1e9 / peak}}
 
         # end to end: pinned host inputs copied in, routing result read back, every step (eager calls)
         cap, caches, outs = wl["cap"], wl["caches"], wl["outs"]
@@ -478,12 +672,15 @@ def gpu_arm(args):
                      "append_frac": app_bytes * T8 / (app8 * 1e-3) / 1e9 / peak,
                      "step_frac": (GATE_BYTES_PER_TOKEN + app_bytes) * T8 / (ms8 / steps8 * 1e-3) / 1e9 / peak}
             del w8, g8
-    clocks = sampler.stop() if rank == 0 else None
+            torch.cuda.empty_cache()
+
+        if not args.no_extras and args.bits == 8:
+            extras = other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, local, single_gpu_workload, kernel_times)
 
     if world == 1 and not args.no_cpu_baseline:
-        v, dt = run_cpu(3, 1, T)
-        cpu = {"value": v, "unit": UNIT, "cores": cpu_threads(), "kind": "port",
-               "sample": f"3 full batches of {T} tokens on the host (numpy port of the reference arithmetic)"}
+        v, dt, cores = run_cpu(10, 2, T)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"10 full batches of {T} tokens on the host (numpy port of the reference arithmetic, {cores} threads)"}
 
     if rank == 0:
         line = {
@@ -491,15 +688,124 @@ def gpu_arm(args):
             "ms_per_step": ms_max / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": f"bf16 in, fp32 math, int{args.bits} codes", "data": "synthetic",
             "config": {**cfg, **extra_cfg, "l2": f"inputs larger than L2, rotated over {R} buffer sets"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "launch": launch_mode, "roofline": roof,
-            "cpu_baseline": cpu, "large_batch": large,
+            "clocks": clocks, "repeats": repeats, "e2e": e2e, "gpu_launches": int(launches), "launch": launch_mode,
+            "roofline": roof, "cpu_baseline": cpu, "parity": parity, "large_batch": large,
         }
+        line.update(multi)
         if world == 1:
             line["serial_schedule"] = {"ms_per_step": serial_ms, "value": T / (serial_ms * 1e-3), "unit": UNIT,
                                        "launch": "pikv_route_append on one stream, one graph per step"}
+            if extras is not None:
+                line["other_kernels"] = extras
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity.get("ok", False):
+        raise SystemExit("parity check failed: " + json.dumps(parity))
+
+
+def other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, gpu_index, single_gpu_workload, kernel_times):
+    """The rest of the metric at the sizes BASELINE.json names, as sub-records of the one JSON line: each is
+    timed for about 0.6 s (CUDA events) with its own clock sample; `bytes` are algorithmic bytes per launch.
+      decode           config 3: 64 streams x 32 query / 8 KV heads x context 32768, int8 cache
+      decode_h2o       the same step with the H2O accumulated-attention update (scores out + accumulate)
+      decode_int4      the same over the 4-bit asymmetric cache
+      h2o_select / h2o_compact / decode_budgeted   eviction to the 2048-token budget and decode over it
+      lowrank          config 4: 262144 x 1024 -> rank 64 / 32 / 16
+      append_int4      config 2's second format (4-bit asymmetric) through the append kernel"""
+    out = {}
+
+    def measure(fn, launches_per_call=1, target_s=0.6):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        n = int(max(5, min(5000, target_s * 1e3 / max(e0.elapsed_time(e1), 1e-3))))
+        sampler = ClockSampler(gpu_index)
+        sampler.start()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n, n, sampler.stop()
+
+    def record(name, ms, n, clocks, nbytes, kernel, **more):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "bytes": nbytes, "GBps": gbs, "frac": gbs / peak, "peak": peak, "peak_source": peak_src,
+                     "kernel": kernel, "launches_timed": n, "clocks": clocks, **more}
+
+    B, n_q, n_kv, ctx = 64, 32, 8, 32768
+    q = torch.randn(B, n_q, 128, device=dev).bfloat16()
+    for bits in (8, 4):
+        cache = fill_stream_cache(pikv_b200, torch, dev, B, n_kv, ctx, bits=bits)
+        per_tok = 2 * 128 + 2 * 2 if bits == 8 else 2 * 64 + 2 * 2 + 2 * 4
+        by = B * n_kv * ctx * per_tok + 2 * B * n_q * 128 * 2
+        ms, n, cl = measure(lambda: cache.decode_attention(q))
+        record("decode" if bits == 8 else "decode_int4", ms, n, cl, by, f"decode_attn_kernel<{bits}>",
+               streams=B, context=ctx, context_tokens_per_s=B * ctx / (ms * 1e-3))
+        cache.check_status()
+        if bits == 8:
+            # decode + H2O accumulate: acc[b, kv head, pos] += sum over the group's query heads of the attention
+            # probability (4.497 GB of algorithmic traffic: the cache, q, out, and acc read + written)
+            acc = torch.zeros(B * n_kv, ctx, device=dev)
+            scores = torch.empty(B, n_q, ctx, device=dev)
+
+            def step_h2o():
+                _, lse = cache.decode_attention(q, scores=scores)
+                ops.h2o_accumulate_attn(scores, lse, cache.length, n_kv, acc)
+
+            ms, n, cl = measure(step_h2o)
+            record("decode_h2o", ms, n, cl, by + 2 * B * n_kv * ctx * 4, "decode_attn_kernel<8> + h2o_accumulate_attn_kernel",
+                   note="fp32 scores go through HBM between the two kernels (2 x 268 MB not counted as algorithmic)")
+            del scores
+            acc = torch.rand(B * n_kv, ctx, device=dev)
+            ts = torch.arange(ctx, dtype=torch.float32, device=dev).repeat(B * n_kv, 1)
+            acc[:, ctx - 256:] = -1.0       # the recent window holds no heavy hitter: every segment keeps exactly 2048
+            ms, n, cl = measure(lambda: ops.h2o_select(acc, ts, 1792, 256, as_bool=False))
+            record("h2o_select", ms, n, cl, 2 * 4 * ctx * B * n_kv + B * n_kv * (ctx + 2048 * 4), "h2o_select_kernel",
+                   segments=B * n_kv, length=ctx, heavy=1792, recent=256)
+            _, keep, cnt = ops.h2o_select(acc, ts, 1792, 256, as_bool=False)
+            dst = pikv_b200.PagedKVCache(B, 2048, n_kv, device=dev)
+            dacc, dts = torch.zeros(B * n_kv, 2048, device=dev), torch.zeros(B * n_kv, 2048, device=dev)
+            ms, n, cl = measure(lambda: cache.compact_into(dst, keep, cnt, True, acc, ts, dacc, dts))
+            record("h2o_compact", ms, n, cl, 2 * B * n_kv * 2048 * (2 * 128 + 2 * 2 + 4 + 4), "h2o_compact_kernel",
+                   segments=B * n_kv, kept=2048)
+            dst.length.fill_(2048)
+            ms, n, cl = measure(lambda: dst.decode_attention(q, max_ctx=2048))
+            record("decode_budgeted", ms, n, cl, B * n_kv * 2048 * per_tok + 2 * B * n_q * 128 * 2, "decode_attn_kernel<8>",
+                   streams=B, context=2048)
+            cache.check_status()
+            dst.check_status()
+            del dst, acc, ts, dacc, dts
+        del cache
+        torch.cuda.empty_cache()
+
+    M, K = 262144, 1024
+    x = torch.randn(M, K, device=dev).bfloat16()
+    for r in (64, 32, 16):
+        w = torch.nn.init.orthogonal_(torch.empty(K, K))[:r].contiguous().to(dev).bfloat16()
+        ms, n, cl = measure(lambda: ops.lowrank_project(x, w, None, relu=True))
+        record(f"lowrank_r{r}", ms, n, cl, M * K * 2 + M * r * 2, "lowrank_gemm_kernel", rows=M, hidden=K, rank=r,
+               TFLOPs=2.0 * M * K * r / (ms * 1e-3) / 1e12)
+    assert pikv_b200.lib().pikv_lowrank_error_state() == 0
+    del x
+    torch.cuda.empty_cache()
+
+    w4 = single_gpu_workload(WORKLOAD["tokens"], bits=4)
+    sampler = ClockSampler(gpu_index)
+    sampler.start()
+    _, _, app4 = kernel_times(w4, 2000)
+    cl = sampler.stop()
+    record("append_int4", app4, 2000, cl, APPEND_BYTES_INT4 * WORKLOAD["tokens"], "kv_append_quant_kernel<bf16,4,asym>",
+           tokens=WORKLOAD["tokens"])
+    for c in w4["caches"]:
+        c.check_status()
+    return out
 
 
 # ----------------------------------------------------------------------------- secondary workloads
@@ -617,6 +923,10 @@ def main():
     ap.add_argument("--schedule", choices=("pipelined", "serial"), default="pipelined",
                     help="single GPU: gate of batch i+1 overlapped with the append of batch i, or strictly serial")
     ap.add_argument("--no-large", action="store_true", help="skip the 8x-token secondary measurement")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the other kernels' sub-records (decode attention, H2O, low-rank, 4-bit append)")
+    ap.add_argument("--multi-warmup-s", type=float, default=45.0,
+                    help="multi-GPU: seconds of untimed steps before the timed regions (stated in the line as warmup_s)")
     ap.add_argument("--workload", default="append", choices=["append", "decode", "lowrank"],
                     help="append = the headline route+quantise+append step; the others print lines for the other kernels")
     ap.add_argument("--streams", type=int, default=64)

@@ -375,6 +375,32 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
 
         hooks = {"begin": begin, "end": end}
 
+        def verify():
+            """Outside the timing: one more step of buffer set 0 on every lane, then every lane's status word
+            must be clear and its replicated lengths must equal the sum over the ranks of the selection counts
+            (cut at the capacity)."""
+            counts = outs[0].counts_k.sum(0).to(torch.int32)
+            for lane in range(lanes):
+                with torch.cuda.stream(streams[lane]):
+                    shards[lane].reset()
+                    runs[lane][0](sync=True)
+            torch.cuda.synchronize()
+            allc = torch.empty(world, E, dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(allc, counts)
+            want = torch.clamp(allc.sum(0), max=cap).to(torch.int32)
+            for lane in range(lanes):
+                shards[lane].cache.check_status()
+                if not torch.equal(shards[lane].len_all, want):
+                    raise RuntimeError(f"lane {lane}: replicated lengths differ from the all-gathered counts")
+            return lanes
+
+        # bytes this rank's rows put on the link per step: int8 K + V codes and their bf16 scales, for the
+        # (token, expert) pairs whose expert lives on another GPU (buffer set 0, measured from the gate's counts)
+        c0 = outs[0].counts_k.sum(0)
+        per = E // world
+        remote = int(c0.sum().item() - c0[rank * per:(rank + 1) * per].sum().item())
+        link_bytes = remote * (2 * kv + 2 * n_kv * 2)
+
         # end to end: the step's inputs come from pinned host memory and its routing result goes back, on
         # the lane's stream, every step
         h_sets = [tuple(x.cpu().pin_memory() for x in sets[i]) for i in range(R)]
@@ -406,6 +432,9 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
 
     extra = {"parallelism": f"tokens data-parallel, {E} experts sharded {E // world} per GPU; {how}",
              "buffer_sets": R, "hooks": hooks}
+    if mode == "peer":
+        extra["verify"] = verify
+        extra["link_bytes_per_step"] = link_bytes
     if mode == "peer" and launches_per_step is not None:
         extra["launches_per_step"] = launches_per_step
     if e2e_io is not None:

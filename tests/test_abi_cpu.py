@@ -83,3 +83,23 @@ def test_pikv_moe_builds_with_the_reference_weights_for_a_seed():
         m = PiKVMoE(**kw)
         assert sum(p.numel() for p in m.parameters()) == int(g[f"{tag}/n_params"])
         assert abs(sum(p.double().sum().item() for p in m.parameters()) - float(g[f"{tag}/param_sum"])) < 1e-6
+
+
+def test_reference_import_paths_resolve():
+    """pikv_b200.compat.install() makes the reference's own import lines work on this package's classes."""
+    import subprocess
+    import sys
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "import pikv_b200.compat as c; c.install()\n"
+        "from core.single.pikv_routing import BaseRouter, TopKBalancedRouter, PiKVRouter\n"
+        "from core.single.pikv_compression import QuantizedCompressor, PyramidCompressor, SVDCompressor\n"
+        "from core.single.cache_scheduling import H2OScheduler, CacheSchedulingManager, SchedulingPolicy\n"
+        "from core.single.module.pikv_scheduling import AdaKVScheduler, DuoAttentionScheduler\n"
+        "from core.single.module import QuantizedCompressor as MQ\n"
+        "from core.single.pikv_moe import PiKVMoE\n"
+        "import pikv_b200\n"
+        "assert TopKBalancedRouter is pikv_b200.TopKBalancedRouter and PiKVMoE.__module__ == 'pikv_b200.moe'\n"
+    ) % ROOT
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr

@@ -160,3 +160,40 @@ def test_peer_exchange_slots_equal_single_process(tmp_path):
         lengths = np.minimum(run, cap)
     for r in range(world):
         np.testing.assert_array_equal(np.load(tmp_path / f"peer_len{r}.npy"), lengths)
+
+
+def _failing_worker(rank, world, port, tmp):
+    """Rank 1 raises before the count exchange; rank 0 must get an error out of its collective (a short
+    process-group timeout), not wait for ever."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    outcome = "no error"
+    try:
+        if rank == 1:
+            raise RuntimeError("injected failure on rank 1 (host side)")
+        counts = torch.ones(8, dtype=torch.int32)
+        gathered = [torch.zeros(8, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(gathered, counts)                    # the peer never joins
+    except RuntimeError as e:
+        outcome = "injected" if "injected" in str(e) else "collective error"
+    except Exception:
+        outcome = "collective error"
+    with open(os.path.join(tmp, f"outcome{rank}.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)            # skip destroy_process_group: the peer is gone, and a clean shutdown would wait for it
+
+
+def test_rank_failure_surfaces_as_an_error_on_the_other_rank(tmp_path):
+    world = 2
+    ctx = mp.get_context("spawn")
+    port = 29800 + os.getpid() % 1000
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0, "a rank hung or crashed"
+    assert (tmp_path / "outcome1.txt").read_text() == "injected"
+    assert (tmp_path / "outcome0.txt").read_text() == "collective error"

@@ -118,43 +118,78 @@ def test_append_flags_bad_destination(dev):
         cache.check_status()
 
 
-def test_full_size_append_properties(dev):
-    """Config-2 sized run checked through size-independent properties: slots are a bijection onto
-    [0, len) per expert; decode(encode(x)) is within half a quantisation step of x; K of a token is
-    identical in both of its experts."""
+def test_full_size_append_matches_oracle(dev):
+    """Config 2 at full size (16384 tokens, hidden 4096, 8 experts top-2, 8 KV heads) against the oracle: expert
+    indices equal except at near-ties of the oracle's top-k (counted); on the GPU's own indices the slots,
+    counts and lengths are equal and every stored code and scale is bit-exact, for int8 symmetric and 4-bit
+    asymmetric caches."""
     import pikv_b200
     from pikv_b200 import ops
     T, H, E, k, n_kv = 16384, 4096, 8, 2, 8
-    torch.manual_seed(0)
-    act = torch.randn(T, H, device=dev).bfloat16()
-    w2 = (torch.randn(E, H, device=dev) / 64).bfloat16()
-    K, V = outlier_kv(T, n_kv * 128, 3).to(dev), outlier_kv(T, n_kv * 128, 4).to(dev)
+    g0 = torch.Generator().manual_seed(0)
+    act = torch.randn(T, H, generator=g0).bfloat16()
+    w2 = (torch.randn(E, H, generator=g0) / 64).bfloat16()
+    K, V = outlier_kv(T, n_kv * 128, 3), outlier_kv(T, n_kv * 128, 4)
     cap = O.capacity(T, 1.5, k, E)
-    g = ops.gate_fused(act, w2, None, top_k=k, capacity=cap)
-    cache = pikv_b200.PagedKVCache(E, cap, n_kv, device=dev)
-    cache.append(K, V, g.topk_idx, g.slot)
-    cache.length.copy_(g.new_len)
-    cache.check_status()
-    idx, slot = g.topk_idx.cpu().numpy(), g.slot.cpu().numpy()
-    lens = g.new_len.cpu().numpy()
-    assert lens.sum() == (slot >= 0).sum()
-    for e in range(E):
-        s = np.sort(slot[(idx == e) & (slot >= 0)])
-        np.testing.assert_array_equal(s, np.arange(lens[e]))
-    ok = slot >= 0
-    t_ix, j_ix = np.nonzero(ok)
-    pick = np.random.default_rng(0).choice(len(t_ix), 4096, replace=False)
-    seq = torch.from_numpy(idx[t_ix[pick], j_ix[pick]].astype(np.int32)).to(dev)
-    pos = torch.from_numpy(slot[t_ix[pick], j_ix[pick]].astype(np.int32)).to(dev)
-    dq = cache.gather(seq, pos, "k").cpu().numpy().reshape(-1, n_kv, 128)
-    src = K.float().cpu().numpy()[t_ix[pick]].reshape(-1, n_kv, 128)
-    step = np.abs(src).max(-1, keepdims=True) * 2 / 255
-    # half a step from rounding + up to 127 * 2^-8 of a step from storing the scale as bf16 (8 significant bits)
-    assert (np.abs(dq - src) <= step * (0.5 + 127 / 256) + 1e-6).all()
-    both = np.nonzero(ok.all(axis=1))[0][:512]
-    a = cache.gather(g.topk_idx[both, 0].contiguous(), g.slot[both, 0].contiguous(), "v", codes=True)[1]
-    b = cache.gather(g.topk_idx[both, 1].contiguous(), g.slot[both, 1].contiguous(), "v", codes=True)[1]
-    assert torch.equal(a, b)
+    g = ops.gate_fused(act.to(dev), w2.to(dev), None, top_k=k, capacity=cap)
+    logits = O.gate_logits(act.float().numpy(), w2.float().numpy(), None)
+    probs, idx, _ = O.gate_tail(logits, k)
+    gi = g.topk_idx.cpu().numpy()
+    diff = (gi != idx).any(axis=1)
+    assert (O.topk_margin(probs, k)[diff] < 1e-4).all() and diff.sum() <= T // 200, f"{int(diff.sum())} index mismatches"
+    print(f"config 2: {int(diff.sum())} of {T} tokens differ from the oracle's experts, all near-ties")
+    slot, counts_k = O.slot_assign_fast(gi, E, cap)
+    np.testing.assert_array_equal(g.slot.cpu().numpy(), slot)
+    np.testing.assert_array_equal(g.counts_k.cpu().numpy(), counts_k)
+    Kf, Vf = K.float().numpy(), V.float().numpy()
+    for bits, sym in ((8, True), (4, False)):
+        cache = pikv_b200.PagedKVCache(E, cap, n_kv, bits=bits, symmetric=sym, device=dev)
+        cache.append(K.to(dev), V.to(dev), g.topk_idx, g.slot)
+        cache.length.copy_(g.new_len)
+        cache.check_status()
+        ref = O.routed_append(Kf, Vf, gi, slot, E, cap, bits, sym, 128)
+        lens = ref["length"]
+        np.testing.assert_array_equal(g.new_len.cpu().numpy(), lens)
+        for which, name in (("k", "k"), ("v", "v")):
+            sq, ps, dq, codes = read_all(cache, lens, which)
+            np.testing.assert_array_equal(codes.astype(F32), ref[f"{name}_codes"][sq, ps])
+            sc = O.bf16_round(ref[f"{name}_scale"][sq, ps])
+            want = O.dequant_token_groups(ref[f"{name}_codes"][sq, ps], sc, ref[f"{name}_zp"][sq, ps], 128)
+            np.testing.assert_array_equal(dq, want)             # (code - zp) * stored scale: scales and zero points too
+        del cache
+
+
+def test_full_size_decode_matches_oracle(dev):
+    """Config 3 at full size: 64 streams x 32 query / 8 KV heads x context 32768 in one call with the
+    library's default split count; three streams (first, middle, last: the page-table stride and the 4.3 GB
+    offsets) are compared with the oracle on the dequantised cache at 1e-2, int8 and 4-bit caches."""
+    import pikv_b200
+    B, n_q, n_kv, ctx = 64, 32, 8, 32768
+    for bits in (8, 4):
+        cache = pikv_b200.PagedKVCache(B, ctx, n_kv, bits=bits, symmetric=(bits == 8), device=dev)
+        gen = torch.Generator(device=dev).manual_seed(11)
+        pos = torch.arange(ctx, dtype=torch.int32, device=dev)[:, None].contiguous()
+        for b in range(B):
+            K = torch.randn(ctx, n_kv * 128, generator=gen, device=dev).bfloat16()
+            V = torch.randn(ctx, n_kv * 128, generator=gen, device=dev).bfloat16()
+            cache.append(K, V, torch.full((ctx, 1), b, dtype=torch.int32, device=dev), pos)
+        lens = torch.full((B,), ctx, dtype=torch.int32)
+        lens[31] = ctx - 4321                                   # one ragged stream among the full ones
+        cache.length.copy_(lens.to(dev))
+        q = torch.randn(B, n_q, 128, generator=gen, device=dev).bfloat16()
+        out = cache.decode_attention(q)
+        torch.cuda.synchronize()
+        cache.check_status()
+        got = out.float().cpu().numpy()
+        for b in (0, 31, 63):
+            n = int(lens[b])
+            seq = torch.full((n,), b, dtype=torch.int32, device=dev)
+            kd = cache.gather(seq, pos[:n, 0].contiguous(), "k").cpu().numpy().reshape(1, n, n_kv, 128).transpose(0, 2, 1, 3)
+            vd = cache.gather(seq, pos[:n, 0].contiguous(), "v").cpu().numpy().reshape(1, n, n_kv, 128).transpose(0, 2, 1, 3)
+            want, _ = O.decode_attention(q[b:b + 1].float().cpu().numpy(), kd, vd, np.array([n]))
+            assert np.abs(got[b] - want[0]).max() <= 1e-2 * np.abs(want).max(), (bits, b)
+        del cache
+        torch.cuda.empty_cache()
 
 
 # ---------------------------------------------------------------- block-wide fake quantisation

@@ -124,3 +124,25 @@ def test_svd_compressor_bf16_runs_on_tensor_cores(dev):
         assert rel(rk.float().cpu().numpy().reshape(-1, 1024), want) < 1e-2
     torch.cuda.synchronize()
     assert pikv_b200.lib().pikv_lowrank_error_state() == 0
+
+
+def test_full_size_lowrank_matches_oracle(dev):
+    """Config 4 at full size: 262144 rows x 1024 -> rank 64 / 32 / 16 on the tensor-core kernel, bf16 out;
+    4096 sampled rows (first and last tiles included) against the fp32 oracle at 1e-2."""
+    import pikv_b200
+    from pikv_b200 import ops
+    M, K = 262144, 1024
+    g = torch.Generator(device=dev).manual_seed(4)
+    x = torch.randn(M, K, generator=g, device=dev).bfloat16()
+    rows = np.unique(np.concatenate([np.arange(256), np.arange(M - 256, M),
+                                     np.random.default_rng(4).integers(0, M, 3584)]))
+    xs = x[torch.from_numpy(rows).to(dev)].float().cpu().numpy()
+    for r in (64, 32, 16):
+        w = torch.nn.init.orthogonal_(torch.empty(K, K))[:r].contiguous().bfloat16()
+        b = torch.randn(r) * 0.05
+        y = ops.lowrank_project(x, w.to(dev), b.to(dev), relu=True)
+        torch.cuda.synchronize()
+        assert pikv_b200.lib().pikv_lowrank_error_state() == 0
+        want = O.lowrank_project(xs, w.float().numpy(), b.numpy())
+        got = y[torch.from_numpy(rows).to(dev)].float().cpu().numpy()
+        assert rel(got, want) < 1e-2, r
