@@ -677,6 +677,12 @@ def gpu_arm(args):
         if not args.no_extras and args.bits == 8:
             extras = other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, local, single_gpu_workload, kernel_times)
 
+    sharded = None
+    if not args.no_sharded and args.bits == 8:
+        peak_s, _ = measured_peak_gbs()
+        torch.cuda.empty_cache()
+        sharded = sharded_arm(torch, dist, dev, rank, world, steps, local, peak_s)
+
     if world == 1 and not args.no_cpu_baseline:
         v, dt, cores = run_cpu(10, 2, T)
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
@@ -692,6 +698,8 @@ def gpu_arm(args):
             "roofline": roof, "cpu_baseline": cpu, "parity": parity, "large_batch": large,
         }
         line.update(multi)
+        if sharded is not None:
+            line["sharded"] = sharded
         if world == 1:
             line["serial_schedule"] = {"ms_per_step": serial_ms, "value": T / (serial_ms * 1e-3), "unit": UNIT,
                                        "launch": "pikv_route_append on one stream, one graph per step"}
@@ -702,6 +710,8 @@ def gpu_arm(args):
         dist.destroy_process_group()
     if parity is not None and not parity.get("ok", False):
         raise SystemExit("parity check failed: " + json.dumps(parity))
+    if sharded is not None and sharded.get("parity") is not None and not sharded["parity"]["ok"]:
+        raise SystemExit("sharded parity check failed: " + json.dumps(sharded["parity"]))
 
 
 def other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, gpu_index, single_gpu_workload, kernel_times):
@@ -770,7 +780,7 @@ def other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, gpu_index, single_
             record("h2o_select", ms, n, cl, 2 * 4 * ctx * B * n_kv + B * n_kv * (ctx + 2048 * 4), "h2o_select_kernel",
                    segments=B * n_kv, length=ctx, heavy=1792, recent=256)
             _, keep, cnt = ops.h2o_select(acc, ts, 1792, 256, as_bool=False)
-            dst = pikv_b200.PagedKVCache(B, 2048, n_kv, device=dev)
+            dst = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)      # same page-table width as the source
             dacc, dts = torch.zeros(B * n_kv, 2048, device=dev), torch.zeros(B * n_kv, 2048, device=dev)
             ms, n, cl = measure(lambda: cache.compact_into(dst, keep, cnt, True, acc, ts, dacc, dts))
             record("h2o_compact", ms, n, cl, 2 * B * n_kv * 2048 * (2 * 128 + 2 * 2 + 4 + 4), "h2o_compact_kernel",
@@ -806,6 +816,207 @@ def other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, gpu_index, single_
     for c in w4["caches"]:
         c.check_status()
     return out
+
+
+# ----------------------------------------------------------------------------- expert-sharded configuration
+SHARDED = dict(workload="expert-sharded striped KV cache: prefill append + one decode step", experts=64, top_k=2, hidden=4096,
+               streams=256, context=16384, q_heads=32, kv_heads=8, head_dim=128, stripe=1024, zipf_exponent=1.1,
+               quant="int8-sym-g128")
+
+
+def sharded_inputs(torch, dev, cfg, slot):
+    """One of four rotating buffer sets of a 16384-token prefill chunk: gate-net activations, K, V (seeded by the
+    slot, so every rank count builds the same cache for stream s from set s % 4)."""
+    g = torch.Generator(device=dev).manual_seed(7000 + slot)
+    T, H, kv = cfg["context"], cfg["hidden"], cfg["kv_heads"] * cfg["head_dim"]
+    act = torch.randn(T, H, generator=g, device=dev).bfloat16()
+    K = torch.randn(T, kv, generator=g, device=dev).bfloat16()
+    V = torch.randn(T, kv, generator=g, device=dev).bfloat16()
+    return act, K, V
+
+
+def sharded_gate(torch, dev, cfg):
+    """Gate weights whose logits are log Zipf(1.1)[e] + N(0,1): unit-norm random rows (act ~ N(0,1)) and the log
+    popularity as the bias."""
+    from pikv_b200.striping import zipf_expert_logits
+    g = torch.Generator().manual_seed(11)
+    w = torch.randn(cfg["experts"], cfg["hidden"], generator=g)
+    w = (w / w.norm(dim=1, keepdim=True)).bfloat16().to(dev)
+    b = torch.from_numpy(zipf_expert_logits(cfg["experts"], cfg["zipf_exponent"])).to(dev)
+    return w, b
+
+
+def sharded_capacity(cfg):
+    """Rows per pair by expert: 1.3 x the expected share of a stream's tokens that select the expert (top-2 of
+    log Zipf + N(0,1), estimated from 65536 seeded draws), rounded up to whole stripes.  Router statistics size
+    the page pools; rows past a pair's capacity are dropped like the reference's rows past the cache size."""
+    import numpy as np
+    from pikv_b200.striping import zipf_expert_logits
+    rng = np.random.default_rng(5)
+    E = cfg["experts"]
+    lg = zipf_expert_logits(E, cfg["zipf_exponent"])[None] + rng.standard_normal((65536, E)).astype(np.float32)
+    top = np.argsort(-lg, axis=1)[:, :cfg["top_k"]]
+    share = np.bincount(top.ravel(), minlength=E) / 65536.0
+    st = cfg["stripe"]
+    return ((np.ceil(1.3 * share * cfg["context"] / st) + 1) * st).astype(np.int64)
+
+
+def sharded_arm(torch, dist, dev, rank, world, steps, gpu_index, peak):
+    """Config 5: 64 experts top-2, 256 decode streams x context 16384, Zipf(1.1)-skewed routing, the caches of the
+    (expert, stream) pairs striped over the GPUs.  Total work is fixed (strong scaling).  Timed: the prefill (every
+    stream's 16384 tokens gated from hidden 4096 and appended through pikv_kv_append_striped) and one decode step
+    (post -> attend -> combine) replayed as a CUDA graph.  Parity: sample streams' decode output against a
+    one-GPU cache of the same streams built on rank 0."""
+    import numpy as np
+    import pikv_b200
+    from pikv_b200 import ops
+    from pikv_b200.striping import StripedLayout
+    from pikv_b200.striped_cache import StripedShardedKVCache
+    cfg = dict(SHARDED)
+    E, S, k, n_q, n_kv = cfg["experts"], cfg["streams"], cfg["top_k"], cfg["q_heads"], cfg["kv_heads"]
+    perm = np.random.default_rng(3).permutation(E)
+    cap = sharded_capacity(cfg)
+    lay = StripedLayout(E, S, world, cfg["stripe"], perm)
+    cache = StripedShardedKVCache.create(lay, n_kv, n_q, k, cap, dev)
+    w2, b2 = sharded_gate(torch, dev, cfg)
+    sets = [sharded_inputs(torch, dev, cfg, i) for i in range(4)]
+    spr = cache.streams_per_rank
+    T = cfg["context"]
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- prefill: this rank's streams, one 16384-token chunk each ----
+    outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(4)]
+    streams_here = list(range(rank * spr, (rank + 1) * spr))
+
+    def fill():
+        for s_ in streams_here:
+            a_, K_, V_ = sets[s_ % 4]
+            cache.route_append(s_, K_, V_, act=a_, w2=w2, b2=b2, out=outs[s_ % 4])
+        cache.barrier()
+
+    fill()                                   # eager once (workspaces, launch path), then as one CUDA graph: the step
+    sync_all()                               # is three kernels per stream and the host would otherwise bound it
+    cache.check_status()
+    fill_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(fill_graph):
+        fill()
+    cache.pair_len.zero_()
+    sync_all()
+    sampler = ClockSampler(gpu_index)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fill_graph.replay()
+    e1.record()
+    sync_all()
+    fill_ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(fill_ms, op=dist.ReduceOp.MAX)
+    cache.check_status()
+
+    # ---- decode step ----
+    g = torch.Generator(device=dev).manual_seed(99)
+    q_all = torch.randn(S, n_q, 128, generator=g, device=dev).bfloat16()
+    dl = (b2[None] + torch.randn(S, E, generator=g, device=dev)).contiguous()
+    route = ops.gate_fused(logits=dl, top_k=k, capacity=0)
+    sl = slice(rank * spr, (rank + 1) * spr)
+    q_loc, idx_loc, w_loc = q_all[sl].contiguous(), route.topk_idx[sl].contiguous(), route.topk_w[sl].contiguous()
+    out = torch.empty(spr, n_q, 128, dtype=torch.bfloat16, device=dev)
+    cache.decode_step(q_loc, idx_loc, w_loc, out=out)
+    sync_all()
+    cache.check_status()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        cache.decode_step(q_loc, idx_loc, w_loc, out=out)
+    for _ in range(3):
+        graph.replay()
+    sync_all()
+    n_dec = max(steps, 50)
+    regions = []
+    for _ in range(5):
+        sync_all()
+        e0.record()
+        for _ in range(n_dec):
+            graph.replay()
+        e1.record()
+        sync_all()
+        regions.append(e0.elapsed_time(e1) / n_dec)
+    dec = torch.tensor(regions, device=dev)
+    if world > 1:
+        dist.all_reduce(dec, op=dist.ReduceOp.MAX)
+    dec_ms = median([float(x) for x in dec.tolist()])
+    clocks = sampler.stop() if rank == 0 else None
+    cache.check_status()
+
+    # ---- load and link bytes of the step, from the routing ----
+    lens = torch.zeros(S, E, dtype=torch.int32, device=dev)
+    lens[sl] = cache.pair_len
+    if world > 1:
+        dist.all_reduce(lens)
+    lens_h, idx_h = lens.cpu().numpy(), route.topk_idx.cpu().numpy()
+    row_bytes = 2 * n_kv * 128 + 2 * n_kv * 2                        # K and V codes + bf16 scales of one token
+    load = np.zeros(world)
+    q_sends = np.zeros(world)
+    part_recv = np.zeros(world)
+    for s_ in range(S):
+        dests = set()
+        for e_ in idx_h[s_]:
+            for r_ in range(world):
+                n_ = int(lay.local_len(e_, s_, lens_h[s_, e_], r_))
+                load[r_] += n_
+                if n_ > 0:
+                    dests.add(r_)
+                    if r_ != int(lay.home(s_)):
+                        part_recv[int(lay.home(s_))] += n_q * (128 + 1) * 4
+        q_sends[int(lay.home(s_))] += len(dests - {int(lay.home(s_))}) * n_q * 128 * 2
+    total_bytes = float(load.sum()) * row_bytes + 2 * S * n_q * 128 * 2
+    tokens_total = S * T
+
+    # ---- parity: sample streams against a one-GPU cache of the same streams ----
+    sample = sorted({0, 1, S // 2, S - 1})
+    outs_all = [torch.empty_like(out) for _ in range(world)] if world > 1 else [out]
+    if world > 1:
+        dist.all_gather(outs_all, out)
+    parity = None
+    if rank == 0:
+        full = torch.cat(outs_all).float()
+        lay1 = StripedLayout(E, len(sample), 1, cfg["stripe"], perm)
+        from pikv_b200.striped_cache import emulate_ranks
+        one = emulate_ranks(lay1, n_kv, n_q, k, cap, dev)[0]
+        for i, s_ in enumerate(sample):
+            a_, K_, V_ = sets[s_ % 4]
+            one.route_append(i, K_, V_, act=a_, w2=w2, b2=b2)
+        sel = torch.tensor(sample, device=dev)
+        ref = one.decode_step(q_all[sel].contiguous(), route.topk_idx[sel].contiguous(), route.topk_w[sel].contiguous())
+        torch.cuda.synchronize()
+        one.check_status()
+        same_len = bool(torch.equal(one.pair_len, lens[sel]))
+        err = float((full[sel] - ref.float()).abs().max() / ref.float().abs().max())
+        parity = {"n": world, "streams_checked": sample, "against": "a one-GPU cache of the same streams",
+                  "pair_lengths": "equal" if same_len else "MISMATCH", "decode_max_rel_err": err, "tolerance": 1e-2,
+                  "ok": bool(same_len and err <= 1e-2)}
+        del one
+    rec = {"config": cfg, "n_gpus": world, "scaling": "strong",
+           "prefill": {"ms_total": float(fill_ms.item()), "tokens": tokens_total,
+                       "tokens_per_s": tokens_total / (float(fill_ms.item()) * 1e-3),
+                       "ms_per_16384_token_step": float(fill_ms.item()) / spr,
+                       "link_bytes_per_gpu": float(tokens_total) / world * k * row_bytes * (world - 1) / world},
+           "decode": {"ms_per_step": dec_ms, "regions_ms": regions, "steps_per_region": n_dec, "bytes": total_bytes,
+                      "GBps_aggregate": total_bytes / (dec_ms * 1e-3) / 1e9,
+                      "frac_of_n_x_peak": total_bytes / (dec_ms * 1e-3) / 1e9 / (peak * world),
+                      "streams_per_s": S / (dec_ms * 1e-3),
+                      "hottest_to_mean_gpu_load": float(load.max() / load.mean()),
+                      "link_bytes_per_gpu_max": float((q_sends + part_recv).max()),
+                      "launch": "post, plan, decode_attn, return, combine: five kernels per rank, one CUDA graph"},
+           "clocks": clocks, "parity": parity}
+    del cache
+    torch.cuda.empty_cache()
+    return rec
 
 
 # ----------------------------------------------------------------------------- secondary workloads
@@ -925,6 +1136,7 @@ def main():
     ap.add_argument("--no-large", action="store_true", help="skip the 8x-token secondary measurement")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other kernels' sub-records (decode attention, H2O, low-rank, 4-bit append)")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the expert-sharded configuration (striped cache: prefill + decode step)")
     ap.add_argument("--multi-warmup-s", type=float, default=45.0,
                     help="multi-GPU: seconds of untimed steps before the timed regions (stated in the line as warmup_s)")
     ap.add_argument("--workload", default="append", choices=["append", "decode", "lowrank"],

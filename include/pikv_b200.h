@@ -176,6 +176,18 @@ typedef struct {
 
 int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t stream);
 
+/* The prefill side of the cache: the same append with the rotary position embedding of
+ * RotaryEmbedding.forward (core/single/pikv_attention.py:329-390) applied to K in registers before it is
+ * quantised, so the rotated K is never written in bf16 (the step PiKVAttention.forward performs between
+ * k_proj and _update_cache, core/single/pikv_attention.py:226-247).  Head dim 128, halves split at 64:
+ *   k'[c]      = k[c] * cos[pos][c] - k[c + 64] * sin[pos][c]        c < 64
+ *   k'[c + 64] = k[c + 64] * cos[pos][c] + k[c] * sin[pos][c]
+ * rope_cos / rope_sin: [max_pos][64] fp32 tables from the caller (the reference's cos_cached / sin_cached);
+ * positions [T] (NULL: the token index).  bf16 in, int8 symmetric codes.  V is stored as by
+ * pikv_kv_append_quant. */
+int pikv_kv_append_rope(const pikv_append_params* p, const float* rope_cos, const float* rope_sin,
+                        const int32_t* positions, int32_t max_pos, pikv_stream_t stream);
+
 /* Gate + append as one call: pikv_gate_fused followed by pikv_kv_append_quant with
  * dst_seq = the gate's topk_idx and slot = the gate's slot (those two fields of `append` are
  * ignored), same outputs.  For bf16 K/V and int8 symmetric codes the stand-alone slot
@@ -286,6 +298,35 @@ typedef struct {
 
 int pikv_peer_barrier(const pikv_peer_barrier_params* p, pikv_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Striped expert-sharded append: the cache of a pair (expert e, stream s) is cut into stripes of `stripe`
+ * rows and stripe c lives on rank (expert_rot[e] + s + c) mod world, behind that rank's earlier stripes of
+ * the pair (slot (c / world) * stripe + row % stripe).  Spreads both the experts and the long caches of
+ * popular experts evenly over the GPUs; replaces the contiguous expert blocks of
+ * core/distributed/distributed_pikv.py:91-96 for the cache.  The rank that gates a stream's tokens (its
+ * home) quantises their rows and stores each straight into its owner's pages over peer pointers.
+ *   base: k, v [T, n_kv*128] bf16; dst_seq [T,k] = EXPERT of every (token, j); slot [T,k] = row position
+ *   inside the pair, minus pair_len[e] when pair_len is given (so the gate's slot with capacity 0 and no
+ *   slot_base can be passed as it is, or its slot with slot_base = the pair lengths and pair_len = NULL);
+ *   page_table [num_experts * num_streams][max_pages], the same on every rank (sequence id = e *
+ *   num_streams + s, page ids local to the owner, every rank lays its pool out alike); int8 symmetric.
+ *   stream: the stream all T tokens belong to, or token_stream [T] for mixed batches.
+ *   expert_cap [E] (optional): rows at positions >= expert_cap[e] are dropped.
+ *   which: 0 every row, 1 only rows this rank owns, 2 only the others'.
+ * The caller orders the step against the other GPUs before anyone reads the rows (pikv_peer_barrier).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    pikv_append_params base;
+    int32_t world, rank, stripe, num_experts, num_streams, stream, which;
+    const int32_t* token_stream;
+    const int32_t* pair_len;
+    const int32_t* expert_rot;
+    const int32_t* expert_cap;
+    void* peer_k_codes[8]; void* peer_v_codes[8]; void* peer_k_scale[8]; void* peer_v_scale[8];
+} pikv_append_striped_params;
+
+int pikv_kv_append_striped(const pikv_append_striped_params* p, pikv_stream_t stream);
+
 /* Read rows back in logical order, dequantised: out[i] = (code - zp) * scale for
  * sequence seq[i], position pos[i]; out is [n, n_kv*128] fp32, codes_out
  * (optional) [n, n_kv*128] int8 unpacked codes.  Used by tests, checkpointing
@@ -345,6 +386,10 @@ int pikv_h2o_select(const float* acc, const float* ts, int32_t segments, int32_t
                     uint8_t* evict_mask, int32_t* keep_idx, int32_t keep_stride, int32_t* kept_count,
                     pikv_stream_t stream);
 
+/* Testing aid: which select routine pikv_h2o_select runs (all give identical results).  0 (default): by
+ * segment length; 1: radix select on keys staged in shared memory; 2: radix select re-reading the scores. */
+int pikv_h2o_select_variant(int32_t variant);
+
 typedef struct {
     const int32_t* keep_idx;   /* [segments, keep_stride]                        */
     const int32_t* kept_count; /* [segments]                                     */
@@ -369,14 +414,18 @@ int pikv_h2o_compact(const pikv_compact_params* p, pikv_stream_t stream);
  * out[b,h,:] = softmax(q[b,h,:] . K[b,h/g]^T / sqrt(128)) V[b,h/g] with
  * K = code * scale (core/single/module/pikv_compression.py:1006), arithmetic
  * of PiKVAttention._compute_attention (core/single/pikv_attention.py:117-123,
- * 163,188).  g = n_q / n_kv query heads share one KV head.  The context is
- * split over `splits` CTAs per (stream, KV head); partial results go to
- * `workspace` and a second kernel merges them.
+ * 163,188).  g = n_q / n_kv query heads share one KV head.  The pages of all
+ * (stream, KV head) units form one list that a persistent grid cuts into equal
+ * ranges, one per warp, whatever the streams' lengths; a warp leaves one partial
+ * result per unit it touched in `workspace` and a second kernel merges them.
  *   q, out: [B, n_q, 128] bf16.  seq_ids [B] (NULL: b) selects the page-table
- *   row, seq_len [B] its valid length.
+ *   row, seq_len [B] its valid length.  B <= 12288 per call.
  *   lse (optional) [B, n_q] fp32 log-sum-exp of the scaled scores.
  *   scores (optional) [B, n_q, score_stride] fp32 raw scaled scores, consumed by
  *   pikv_h2o_accumulate_attn.
+ *   splits: ignored (the kernel balances the pages over the GPU by itself); kept
+ *   so that existing callers compile.
+ *   workspace: pikv_decode_attn_workspace_bytes(B, n_q, n_kv, ., .) bytes, 16-byte aligned.
  * ---------------------------------------------------------------------- */
 typedef struct {
     const void* q; void* out;
@@ -384,7 +433,7 @@ typedef struct {
     const int32_t* seq_ids; const int32_t* seq_len;
     const int32_t* page_table; int32_t num_seqs, max_pages, num_pages;
     const void* k_codes; const void* v_codes; const void* k_scale; const void* v_scale;
-    int32_t splits;            /* <=0: library picks                             */
+    int32_t splits;            /* ignored                                        */
     float* lse;
     float* scores; int32_t score_stride;
     void* workspace; size_t workspace_bytes;
@@ -402,16 +451,62 @@ int    pikv_decode_attn_q4(const pikv_decode_params* p, pikv_stream_t stream);
 /* Same computation for callers that cannot allocate device memory at the point where they need
  * attention (a server that gave all of HBM to its own pool at start-up, a plug-in inside an
  * allocator-free region, code inside a stream capture).  It has no counterpart in the reference.
- * The split partials go to an 8 MiB array built into the library (held by every GPU that loads it,
+ * The partial results go to an 8 MiB array built into the library (held by every GPU that loads it,
  * until exit) instead of `workspace`, which is ignored; the call makes no cudaMalloc / cudaFree and
- * calls no allocating routine.  B * n_q * splits * 520 bytes must fit in
- * pikv_decode_attn_static_scratch_bytes() (config 3, 64 x 32 x 7 splits, does), otherwise
- * PIKV_ELIMIT.  The first call on each device looks the array's address up
+ * calls no allocating routine.  pikv_decode_attn_workspace_bytes(B, n_q, n_kv, 0, 0) must fit in
+ * pikv_decode_attn_static_scratch_bytes() (config 3, 64 streams x 32 query / 8 KV heads, needs 4.8 MB),
+ * otherwise PIKV_ELIMIT.  The first call on each device looks the array's address up
  * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on a device
  * share the array: it needs no clearing (every partial a launch reads was written by that launch),
  * but two calls whose kernels overlap on the GPU (different streams) race on it. */
 size_t pikv_decode_attn_static_scratch_bytes(void);
 int    pikv_decode_attn_q8_static(const pikv_decode_params* p, pikv_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Decode step over the striped expert-sharded cache (pikv_kv_append_striped).  Stream s lives on its home
+ * rank s / streams_per_rank, which holds its query, its top-k experts and weights and the lengths of its
+ * pairs.  One step, the same three calls in the same order on every rank (all on one stream per rank):
+ *   pikv_shard_decode_post     home: routing records {expert, pair length, weight} of its streams to every
+ *                              rank, query rows to the ranks that own a stripe of a selected pair
+ *   pikv_shard_decode_attn     owner: waits for every rank's post, builds the local request list (request
+ *                              i = stream i / k, choice i % k; seq_ids / seq_len / q_rows are caller-given
+ *                              scratch of num_streams * top_k ints each), runs the decode-attention kernel
+ *                              over the rows it holds and stores each request's normalised partial output
+ *                              and log-sum-exp into the home rank's buffers
+ *   pikv_shard_decode_combine  home: waits for every rank's partials; per (stream, choice) merges the ranks'
+ *                              partials by log-sum-exp, then mode 0: out = sum_j w_j * attention_j, the
+ *                              combine of DistributedPiKVMoE.forward (expert output times routing weight,
+ *                              summed over experts and ranks, core/distributed/distributed_pikv.py:174-194);
+ *                              mode 1: one softmax over the union of the k caches.
+ * Everything crosses NVLink as plain stores into peer-mapped buffers followed by flag words (no collective
+ * library call, no multicast); every wait is bounded by wait_limit_us and raises PIKV_ST_WAIT_TIMEOUT.
+ * Buffers per rank (pikv_shard_decode_buffer_bytes(what, ...): 0 q, 1 route, 2 post flags, 3 partial outputs,
+ * 4 partial log-sum-exps, 5 done flags), zeroed at start, mapped on every rank; seq (1 word) and counters
+ * (2 words) are local device words, zeroed at start.  `cache` of pikv_shard_decode_attn carries the local
+ * page pools, the replicated page table, n_q / n_kv and the workspace (sized for B = num_streams * top_k).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+    int32_t world, rank, num_experts, num_streams, top_k, n_q, stripe, streams_per_rank;
+    const int32_t* expert_rot;
+    void*     peer_q[8];
+    void*     peer_route[8];
+    uint32_t* peer_post_flags[8];
+    float*    peer_part_o[8];
+    float*    peer_part_lse[8];
+    uint32_t* peer_done_flags[8];
+    uint32_t* seq;
+    uint32_t* counters;
+    uint32_t* status;
+    int32_t   wait_limit_us;
+} pikv_shard_decode_ctx;
+
+size_t pikv_shard_decode_buffer_bytes(int32_t what, int32_t world, int32_t num_streams, int32_t top_k, int32_t n_q);
+int pikv_shard_decode_post(const pikv_shard_decode_ctx* c, const void* q_local, const int32_t* topk_idx,
+                           const float* topk_w, const int32_t* pair_len, pikv_stream_t stream);
+int pikv_shard_decode_attn(const pikv_shard_decode_ctx* c, const pikv_decode_params* cache, int32_t* seq_ids,
+                           int32_t* seq_len, int32_t* q_rows, pikv_stream_t stream);
+int pikv_shard_decode_combine(const pikv_shard_decode_ctx* c, const int32_t* topk_idx, const float* topk_w,
+                              const int32_t* pair_len, void* out, float* lse_out, int32_t mode, pikv_stream_t stream);
 
 /* acc[b, kvh, pos] += sum over the g query heads of exp(score - lse): the H2O
  * accumulated-attention increment (core/single/pikv_moe.py:241-245 column sums

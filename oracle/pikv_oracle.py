@@ -744,3 +744,80 @@ def expert_parallel_combine(expert_outputs, routing_probs, world_size: int):
         parts.append(acc)
     parts = np.stack(parts)
     return parts.sum(axis=0, dtype=F32), parts
+
+
+def striped_owner(perm, e: int, s: int, pos, stripe: int, world: int):
+    """Rank and local slot of row `pos` of the cache of pair (expert e, stream s) when stripes of `stripe`
+    tokens rotate over the ranks starting at (perm[e] + s) mod world.  This placement has no counterpart in
+    the reference (contiguous expert blocks, core/distributed/distributed_pikv.py:91-96); restated here so
+    that the kernels' arithmetic is checked against an independent statement."""
+    pos = np.asarray(pos, np.int64)
+    c = pos // stripe
+    owner = (int(perm[e]) + s + c) % world
+    local = (c // world) * stripe + pos % stripe
+    return owner, local
+
+
+def routed_decode_combine(q, k_dq, v_dq, lengths, topk_idx, topk_w, lse_merge: bool = False):
+    """Decode output of every stream over the caches of its top-k experts.
+
+    q [S, Hq, d]; k_dq, v_dq [E, S, Hkv, ctx, d] dequantised caches of the (expert, stream) pairs with
+    lengths [E, S]; topk_idx, topk_w [S, k].  Default: out[s] = sum_j w[s,j] * attention(q[s], pair(e_j, s)),
+    the expert-parallel combine of core/distributed/distributed_pikv.py:174-194 (expert output times routing
+    weight, summed over the experts, i.e. over the ranks) with decode_attention as the expert's read of its
+    cache.  lse_merge=True instead merges the k attentions as one softmax over the union of the k caches
+    (no counterpart in the reference).  Returns out [S, Hq, d] fp32."""
+    q = np.asarray(q, F32)
+    S, Hq, d = q.shape
+    k = topk_idx.shape[1]
+    out = np.zeros((S, Hq, d), F32)
+    for s in range(S):
+        os_, ls_ = [], []
+        for j in range(k):
+            e = int(topk_idx[s, j])
+            n = int(lengths[e, s])
+            if n == 0:
+                os_.append(np.zeros((Hq, d), F32))
+                ls_.append(np.full(Hq, -np.inf, F32))
+                continue
+            o, _ = decode_attention(q[s:s + 1], k_dq[e, s:s + 1], v_dq[e, s:s + 1], np.array([n]))
+            g = Hq // k_dq.shape[2]
+            lse = np.zeros(Hq, F32)
+            for h in range(Hq):
+                sc = (q[s, h] @ np.asarray(k_dq[e, s, h // g, :n], F32).T) / F32(math.sqrt(d))
+                lse[h] = np.log(np.exp(sc - sc.max()).sum()) + sc.max()
+            os_.append(o[0])
+            ls_.append(lse)
+        if lse_merge:
+            L = np.stack(ls_)                                   # [k, Hq]
+            m = L.max(axis=0)
+            wgt = np.where(np.isfinite(L), np.exp(L - np.where(np.isfinite(m), m, 0)[None]), 0)
+            den = wgt.sum(axis=0)
+            for j in range(k):
+                out[s] += os_[j] * (wgt[j] / np.where(den > 0, den, 1))[:, None]
+        else:
+            for j in range(k):
+                out[s] += os_[j] * F32(topk_w[s, j])
+    return out
+
+
+def rope_tables(max_pos: int, dim: int):
+    """cos / sin [max_pos, dim/2] of RotaryEmbedding._compute_cos_sin_cache, core/single/pikv_attention.py:349-367
+    (numpy's cos / sin may differ from torch's in the last bit: parity tests pass the reference's own tables)."""
+    position = np.arange(max_pos, dtype=F32)[:, None]
+    freq = (F32(1.0) / (F32(10000.0) ** (np.arange(0, dim, 2, dtype=F32) / F32(dim)))).astype(F32)
+    pf = (position * freq).astype(F32)
+    return np.cos(pf).astype(F32), np.sin(pf).astype(F32)
+
+
+def rope_rotate(x, positions, cos, sin):
+    """RotaryEmbedding.forward on one tensor, core/single/pikv_attention.py:369-400: x [T, heads, d]; the halves
+    [..., :d/2] and [..., d/2:] rotate with cos / sin [positions]; every product and sum rounded to fp32."""
+    x = np.asarray(x, F32)
+    d = x.shape[-1]
+    c = np.asarray(cos, F32)[np.asarray(positions)][:, None, :]
+    s = np.asarray(sin, F32)[np.asarray(positions)][:, None, :]
+    top, bot = x[..., : d // 2], x[..., d // 2:]
+    out_top = ((top * c).astype(F32) + ((-bot) * s).astype(F32)).astype(F32)
+    out_bot = ((bot * c).astype(F32) + (top * s).astype(F32)).astype(F32)
+    return np.concatenate([out_top, out_bot], axis=-1)

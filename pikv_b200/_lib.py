@@ -73,6 +73,24 @@ class ShardExchangeParams(C.Structure):
     ]
 
 
+class AppendStripedParams(C.Structure):
+    _fields_ = [
+        ("base", AppendParams), ("world", i32), ("rank", i32), ("stripe", i32), ("num_experts", i32), ("num_streams", i32),
+        ("stream", i32), ("which", i32), ("token_stream", vp), ("pair_len", vp), ("expert_rot", vp), ("expert_cap", vp),
+        ("peer_k_codes", vp * 8), ("peer_v_codes", vp * 8), ("peer_k_scale", vp * 8), ("peer_v_scale", vp * 8),
+    ]
+
+
+class ShardDecodeCtx(C.Structure):
+    _fields_ = [
+        ("world", i32), ("rank", i32), ("num_experts", i32), ("num_streams", i32), ("top_k", i32), ("n_q", i32),
+        ("stripe", i32), ("streams_per_rank", i32), ("expert_rot", vp),
+        ("peer_q", vp * 8), ("peer_route", vp * 8), ("peer_post_flags", vp * 8), ("peer_part_o", vp * 8),
+        ("peer_part_lse", vp * 8), ("peer_done_flags", vp * 8), ("seq", vp), ("counters", vp), ("status", vp),
+        ("wait_limit_us", i32),
+    ]
+
+
 class PeerBarrierParams(C.Structure):
     _fields_ = [("world", i32), ("rank", i32), ("peer_flags", vp * 8), ("seq", vp), ("status", vp), ("wait_limit_us", i32)]
 
@@ -116,11 +134,18 @@ SIGNATURES = {
     "pikv_gate_error_state": (i32, []),
     "pikv_dispatch_scatter": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_kv_append_quant": (i32, [C.POINTER(AppendParams), vp]),
+    "pikv_kv_append_rope": (i32, [C.POINTER(AppendParams), vp, vp, vp, i32, vp]),
     "pikv_route_append": (i32, [C.POINTER(GateParams), C.POINTER(AppendParams), vp]),
     "pikv_kv_append_sharded": (i32, [C.POINTER(AppendShardedParams), vp]),
     "pikv_shard_plan": (i32, [vp, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_shard_exchange_plan": (i32, [C.POINTER(ShardExchangeParams), vp]),
+    "pikv_h2o_select_variant": (i32, [i32]),
     "pikv_peer_barrier": (i32, [C.POINTER(PeerBarrierParams), vp]),
+    "pikv_kv_append_striped": (i32, [C.POINTER(AppendStripedParams), vp]),
+    "pikv_shard_decode_buffer_bytes": (sz, [i32, i32, i32, i32, i32]),
+    "pikv_shard_decode_post": (i32, [C.POINTER(ShardDecodeCtx), vp, vp, vp, vp, vp]),
+    "pikv_shard_decode_attn": (i32, [C.POINTER(ShardDecodeCtx), C.POINTER(DecodeParams), vp, vp, vp, vp]),
+    "pikv_shard_decode_combine": (i32, [C.POINTER(ShardDecodeCtx), vp, vp, vp, vp, vp, i32, vp]),
     "pikv_shard_push_scales": (i32, [C.POINTER(ShardPushParams), vp]),
     "pikv_cache_gather": (i32, [vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "pikv_quant_block_workspace_bytes": (sz, [i32, i32, i32]),

@@ -35,6 +35,16 @@ struct AppendDev {
     uint16_t* pscale[2][8];
     uint16_t* mirror[2];         // local [world][pool] copies that take the scales of remote rows (or null)
     size_t mirror_stride;        // entries per rank in a mirror
+    // striped variant (MODE 3): dst_seq holds the expert, slot the row's position in the (expert, stream) pair
+    int st_experts, st_mul, st_add, st_log2;   // pair = expert * st_mul + stream; stream = token_stream[t] or st_add
+    const int* st_rot;           // [experts] rotation of every expert
+    const int* st_cap;           // [experts] rows a pair of that expert may hold, or null
+    const int* st_stream;        // [T] stream of every token, or null
+    // rotary variant (MODE 4): K is rotated before it is quantised
+    const float* rope_cos;       // [max_pos][64]
+    const float* rope_sin;
+    const int* rope_pos;         // [T] position of every token, or null (position = token index)
+    int rope_max_pos;
     // fused route + append: the gate left chunk-local ranks in `slot` and per-chunk counters behind
     const int* g_cta_cnt;        // [G][E]
     const int* g_cta_cnt_k;      // [G][k][E]
@@ -111,16 +121,37 @@ __device__ __forceinline__ void append_stage_page(const AppendDev& a, unsigned p
             const bool mine = r.q[j] / a.per == a.rank;
             if ((a.which == 1 && !mine) || (a.which == 2 && mine)) r.s[j] = -1;
         }
+        if (MODE == 3 && r.s[j] >= 0) {
+            // owner rank and slot on it of row r.s[j] of pair (expert r.q[j], stream): stripes of 2^st_log2 rows
+            // rotate over the ranks from (rot[expert] + stream) mod world; the owner travels in bits 27..29
+            const int e = r.q[j];
+            if (e < 0 || e >= a.st_experts) {
+                if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_SEQ);
+                r.s[j] = -1;
+            } else {
+                const int stream = a.st_stream ? __ldg(a.st_stream + t) : a.st_add;
+                const int pos = r.s[j] + (a.slot_base ? __ldg(a.slot_base + e) : 0);
+                const int c = pos >> a.st_log2;
+                const int owner = (int)((unsigned)(__ldg(a.st_rot + e) + stream + c) % (unsigned)a.world);
+                const int local = ((c / a.world) << a.st_log2) | (pos & ((1 << a.st_log2) - 1));
+                const bool mine = owner == a.rank;
+                const bool drop = (a.st_cap && pos >= __ldg(a.st_cap + e)) || local >= (1 << 27) ||
+                                  (a.which == 1 && !mine) || (a.which == 2 && mine);
+                r.s[j] = drop ? -1 : (local | (owner << 27));
+                r.q[j] = e * a.st_mul + stream;
+            }
+        }
         if (MODE == 2 && r.s[j] >= 0 && r.q[j] >= 0 && r.q[j] < a.gE) {
             const int sf = r.s[j] + base_s[(t / (unsigned)a.gchunk) * a.gE + r.q[j]];
             r.s[j] = (a.gcap > 0 && sf >= a.gcap) ? -1 : sf;
             if (head == 0 && sub == 0 && a.g_slot_out) a.g_slot_out[(size_t)t * a.top_k + j] = r.s[j];
         }
         if (r.s[j] >= 0) {
-            if (r.q[j] < 0 || r.q[j] >= a.num_seqs || (r.s[j] / PT) >= a.max_pages) {
+            const int sl = MODE == 3 ? (r.s[j] & ((1 << 27) - 1)) : r.s[j];
+            if (r.q[j] < 0 || r.q[j] >= a.num_seqs || (sl / PT) >= a.max_pages) {
                 if (a.status && sub == 0 && head == 0) atomicOr(a.status, PIKV_ST_BAD_SEQ);
             } else {
-                page[j] = __ldg(a.page_table + (size_t)r.q[j] * a.max_pages + r.s[j] / PT);
+                page[j] = __ldg(a.page_table + (size_t)r.q[j] * a.max_pages + sl / PT);
             }
         }
     }
@@ -131,7 +162,7 @@ __device__ __forceinline__ void append_stage_page(const AppendDev& a, unsigned p
 template <typename TIn, int BITS, bool SYM, int TOPK, int MODE>
 __device__ __forceinline__ void kv_append_body(const AppendDev& a) {
     constexpr int ROW_BYTES = D * BITS / 8;
-    constexpr bool SHARDED = MODE == 1;
+    constexpr bool SHARDED = MODE == 1 || MODE == 3;
     using GQ = GroupQuant<TIn, BITS, SYM>;
     extern __shared__ int base_s[];                        // MODE 2: [G][E] first slot of every chunk
     const int sub = threadIdx.x & 7;                       // lane within the group
@@ -221,7 +252,37 @@ __device__ __forceinline__ void kv_append_body(const AppendDev& a) {
 
         QParams kq, vq;
         uint32_t kw[4], vw[4];
-        GQ::quant(k0, kq, kw);
+        if constexpr (MODE == 4) {
+            // rotary position embedding on K (core/single/pikv_attention.py:329-390: halves split at 64, cos / sin
+            // from the caller's tables, every product and sum a separately rounded fp32 operation), then the
+            // fp32 quantisation path: the rotated K never exists in bf16
+            const uint32_t ww[8] = {k0.a.x, k0.a.y, k0.a.z, k0.a.w, k0.b.x, k0.b.y, k0.b.z, k0.b.w};
+            float x[16], out[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bf16x2_to_f32(ww[i], x[2 * i], x[2 * i + 1]);
+            unsigned t = 0, head = 0;
+            if (pair < total) append_split(a, pair, t, head);
+            int pos = a.rope_pos ? __ldg(a.rope_pos + t) : (int)t;
+            pos = max(0, min(pos, a.rope_max_pos - 1));
+            const float4* c4 = reinterpret_cast<const float4*>(a.rope_cos + (size_t)pos * 64 + 16 * (sub & 3));
+            const float4* s4 = reinterpret_cast<const float4*>(a.rope_sin + (size_t)pos * 64 + 16 * (sub & 3));
+            const float sign = sub < 4 ? -1.0f : 1.0f;           // top half: x cos - partner sin; bottom: x cos + partner sin
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 c = __ldg(c4 + i), sn = __ldg(s4 + i);
+                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float partner = __shfl_xor_sync(0xffffffffu, x[4 * i + e], 4);
+                    out[4 * i + e] = __fadd_rn(__fmul_rn(x[4 * i + e], cc[e]), __fmul_rn(sign * partner, ss[e]));
+                }
+            }
+            float mn, mx;
+            qg_group_minmax(out, mn, mx);
+            qg_quantize16<8, true>(out, mn, mx, kq, kw);
+        } else {
+            GQ::quant(k0, kq, kw);
+        }
         GQ::quant(v0, vq, vw);
         const uint16_t ks_bits = qg_bf16_bits(kq.scale), vs_bits = qg_bf16_bits(vq.scale);
         if (pair < total) {
@@ -238,7 +299,7 @@ __device__ __forceinline__ void kv_append_body(const AppendDev& a) {
                 const size_t prow = ((size_t)pg0[j] * a.n_kv + head) * PT + row;
                 if (SHARDED) {
                     // the owner's pools, mapped into this GPU's address space: plain stores over NVLink
-                    const int owner = r0.q[j] / a.per;
+                    const int owner = MODE == 3 ? (r0.s[j] >> 27) : r0.q[j] / a.per;
                     const size_t o = prow * ROW_BYTES + 16 * swz8_chunk(row, sub);
                     *reinterpret_cast<uint4*>(a.pcodes[0][owner] + o) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
                     *reinterpret_cast<uint4*>(a.pcodes[1][owner] + o) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
@@ -363,6 +424,9 @@ static void append_fill_common(const pikv_append_params* p, AppendDev& a) {
     a.world = 1; a.per = p->num_seqs; a.capacity = 0; a.slot_base = nullptr; a.rank = 0; a.which = 0;
     a.mirror[0] = a.mirror[1] = nullptr; a.mirror_stride = 0;
     for (int r = 0; r < 8; ++r) a.pcodes[0][r] = a.pcodes[1][r] = nullptr, a.pscale[0][r] = a.pscale[1][r] = nullptr;
+    a.st_experts = a.st_mul = a.st_add = a.st_log2 = 0;
+    a.st_rot = a.st_cap = a.st_stream = nullptr;
+    a.rope_cos = a.rope_sin = nullptr; a.rope_pos = nullptr; a.rope_max_pos = 0;
     append_clear_gate(a);
 }
 
@@ -410,6 +474,38 @@ extern "C" int pikv_kv_append_quant(const pikv_append_params* p, pikv_stream_t s
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (p->dtype == PIKV_BF16) return launch_append<__nv_bfloat16>(a, p->bits, p->symmetric, st);
     return launch_append<float>(a, p->bits, p->symmetric, st);
+}
+
+// ---- rotary embedding + quantise + append ---------------------------------------------------------------
+extern "C" int pikv_kv_append_rope(const pikv_append_params* p, const float* rope_cos, const float* rope_sin,
+                                   const int32_t* positions, int32_t max_pos, pikv_stream_t stream) {
+    PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "append_rope: null params");
+    PIKV_REQUIRE(p->T >= 0 && p->n_kv > 0 && p->top_k > 0 && p->top_k <= APPEND_MAX_K, PIKV_EINVAL, "append_rope: bad sizes");
+    if (p->T == 0) return PIKV_OK;
+    PIKV_REQUIRE(p->k && p->v && p->dst_seq && p->slot && p->page_table && rope_cos && rope_sin, PIKV_EINVAL,
+                 "append_rope: null input pointer");
+    PIKV_REQUIRE(p->k_codes && p->v_codes && p->k_scale && p->v_scale, PIKV_EINVAL, "append_rope: null cache pointer");
+    PIKV_REQUIRE(p->dtype == PIKV_BF16 && p->bits == 8 && p->symmetric, PIKV_EUNSUPPORTED,
+                 "append_rope: bf16 inputs, int8 symmetric codes only");
+    PIKV_REQUIRE(max_pos > 0, PIKV_EINVAL, "append_rope: max_pos must be positive");
+    PIKV_REQUIRE((reinterpret_cast<uintptr_t>(rope_cos) & 15) == 0 && (reinterpret_cast<uintptr_t>(rope_sin) & 15) == 0, PIKV_EINVAL,
+                 "append_rope: the cos / sin tables must be 16-byte aligned");
+    PIKV_REQUIRE(p->num_seqs > 0 && p->max_pages > 0 && p->num_pages > 0, PIKV_EINVAL, "append_rope: bad cache geometry");
+    PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28) && (long long)p->num_pages * p->n_kv * PT < (1ll << 31), PIKV_ELIMIT,
+                 "append_rope: problem too large for one call");
+    AppendDev a;
+    append_fill_common(p, a);
+    a.rope_cos = rope_cos; a.rope_sin = rope_sin; a.rope_pos = positions; a.rope_max_pos = max_pos;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long lanes = (long long)a.T * a.n_kv * 8;
+    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 3;
+    const int grid = (int)(want < cap_ctas ? want : cap_ctas);
+    if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, 4><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, 4><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else if (a.top_k <= 4) kv_append_quant_kernel<__nv_bfloat16, 8, true, 4, 4><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, 4><<<grid, APPEND_THREADS, 0, st>>>(a);
+    count_launch(1);
+    return check_launch("kv_append_quant_kernel (rotary)");
 }
 
 // ---- fused route + append ---------------------------------------------------------------------------
@@ -740,6 +836,57 @@ extern "C" int pikv_kv_append_sharded(const pikv_append_sharded_params* sp, pikv
     else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, 1><<<grid, APPEND_THREADS, 0, st>>>(a);
     count_launch(1);
     return check_launch("kv_append_quant_kernel (sharded)");
+}
+
+// ---- striped expert-sharded append ---------------------------------------------------------------------
+extern "C" int pikv_kv_append_striped(const pikv_append_striped_params* sp, pikv_stream_t stream) {
+    PIKV_REQUIRE(sp != nullptr, PIKV_EINVAL, "append_striped: null params");
+    const pikv_append_params* p = &sp->base;
+    PIKV_REQUIRE(p->T >= 0 && p->n_kv > 0 && p->top_k > 0 && p->top_k <= APPEND_MAX_K, PIKV_EINVAL, "append_striped: bad sizes");
+    if (p->T == 0) return PIKV_OK;
+    PIKV_REQUIRE(p->k && p->v && p->dst_seq && p->slot && p->page_table && sp->expert_rot, PIKV_EINVAL,
+                 "append_striped: null input pointer");
+    PIKV_REQUIRE(p->dtype == PIKV_BF16 && p->bits == 8 && p->symmetric, PIKV_EUNSUPPORTED,
+                 "append_striped: bf16 inputs, int8 symmetric codes only");
+    PIKV_REQUIRE(sp->world >= 1 && sp->world <= 8 && sp->rank >= 0 && sp->rank < sp->world, PIKV_EINVAL,
+                 "append_striped: world must be 1..8 and rank inside it");
+    PIKV_REQUIRE(sp->num_experts > 0 && sp->num_streams > 0 && p->num_seqs == sp->num_experts * sp->num_streams, PIKV_EINVAL,
+                 "append_striped: num_seqs must be num_experts * num_streams");
+    PIKV_REQUIRE(sp->token_stream != nullptr || (sp->stream >= 0 && sp->stream < sp->num_streams), PIKV_EINVAL,
+                 "append_striped: give token_stream or a valid stream");
+    int log2 = -1;
+    for (int b = 4; b < 27; ++b)
+        if ((1 << b) == sp->stripe) log2 = b;
+    PIKV_REQUIRE(log2 > 0, PIKV_EINVAL, "append_striped: stripe=%d must be a power of two >= 16", sp->stripe);
+    PIKV_REQUIRE(sp->which >= 0 && sp->which <= 2, PIKV_EINVAL, "append_striped: which must be 0..2");
+    PIKV_REQUIRE((long long)p->T * p->n_kv < (1ll << 28), PIKV_ELIMIT, "append_striped: T * n_kv must stay below 2^28");
+    PIKV_REQUIRE((long long)p->num_pages * p->n_kv * PT < (1ll << 31), PIKV_ELIMIT, "append_striped: page pool too large for 32-bit row indices");
+    AppendDev a;
+    append_fill_common(p, a);
+    a.codes[0] = a.codes[1] = nullptr; a.scale[0] = a.scale[1] = nullptr; a.zp[0] = a.zp[1] = nullptr;   // peer pools only
+    a.world = sp->world; a.rank = sp->rank; a.which = sp->which; a.per = 1; a.capacity = 0;
+    a.slot_base = sp->pair_len;
+    a.st_experts = sp->num_experts; a.st_mul = sp->num_streams; a.st_add = sp->stream; a.st_log2 = log2;
+    a.st_rot = sp->expert_rot; a.st_cap = sp->expert_cap; a.st_stream = sp->token_stream;
+    for (int r = 0; r < 8; ++r) {
+        const bool on = r < sp->world;
+        PIKV_REQUIRE(!on || (sp->peer_k_codes[r] && sp->peer_v_codes[r] && sp->peer_k_scale[r] && sp->peer_v_scale[r]),
+                     PIKV_EINVAL, "append_striped: null pool pointer for rank %d", r);
+        a.pcodes[0][r] = on ? static_cast<uint8_t*>(sp->peer_k_codes[r]) : nullptr;
+        a.pcodes[1][r] = on ? static_cast<uint8_t*>(sp->peer_v_codes[r]) : nullptr;
+        a.pscale[0][r] = on ? static_cast<uint16_t*>(sp->peer_k_scale[r]) : nullptr;
+        a.pscale[1][r] = on ? static_cast<uint16_t*>(sp->peer_v_scale[r]) : nullptr;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long lanes = (long long)a.T * a.n_kv * 8;
+    long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * (sp->world > 1 ? 2 : 3);
+    const int grid = (int)(want < cap_ctas ? want : cap_ctas);
+    if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, 3><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, 3><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else if (a.top_k <= 4) kv_append_quant_kernel<__nv_bfloat16, 8, true, 4, 3><<<grid, APPEND_THREADS, 0, st>>>(a);
+    else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, 3><<<grid, APPEND_THREADS, 0, st>>>(a);
+    count_launch(1);
+    return check_launch("kv_append_quant_kernel (striped)");
 }
 
 extern "C" int pikv_cache_gather(const int32_t* seq, const int32_t* pos, int32_t n, const int32_t* page_table,

@@ -1,16 +1,22 @@
 // Decode attention over the quantised paged cache (8-bit symmetric or 4-bit asymmetric codes),
 // dequantised in registers.
 //
-// Grid (split, kv head, stream); 4 warps per CTA, each warp streams whole pages (16 tokens x 128
-// channels of K and of V plus their scales and, for 4 bits, zero points) of its split through a
-// private ring in shared memory filled by bulk async copies (cp.async.bulk + mbarrier transaction
-// counts), so the bytes in flight do not depend on registers.  Per page a warp runs 8 + 8
-// mma.m16n8k16 (f16 x f16 -> f32) and an online softmax in the log2 domain; see decode_attn_kernel.
+// The pages of all requests form one list (per KV head), cut into blocks of equal length whatever the
+// lengths of the requests; a work item is (block, head).  The grid is persistent (three CTAs of four warps per
+// SM) and every WARP is a worker that claims items from a counter until none is left: fast and slow SMs even
+// out, there is no wave quantisation and no tail, the eight heads of a block are claimed one after the other
+// (so the heads of a page are read at about the same time), and a block may start and end in the middle of a
+// request.  A worker streams its pages (16 tokens x 128 channels of K and of V plus their scales and, for 4
+// bits, zero points) through a private ring in shared memory filled by bulk async copies (cp.async.bulk +
+// mbarrier transaction counts), so the bytes in flight do not depend on registers and the stream does not
+// stop at an item boundary; per page it runs 8 + 8 mma.m16n8k16 (f16 x f16 -> f32) and an online softmax in
+// the log2 domain; see decode_attn_kernel.  For every request an item touches, the worker leaves one partial
+// (O, m, l) in the workspace at slot (block + request, head), unique because both indices only grow along
+// the list; a last kernel merges the partials of a (request, head).  A one-CTA plan kernel in front scans the
+// request lengths, picks the block length and records where every block starts.
 // Codes become f16 exactly with one byte-permute (bytes: 0x6400 | (code ^ 0x80) is 1024 + code + 128)
 // or one AND-OR (nibbles: 0x6400 | n is 1024 + n).  Q is scaled by a power of two so that it is exact
 // in f16.  The cache's swizzle makes the 16-byte shared-memory reads of a fragment conflict-free.
-// Partial (O, m, l) of the 4 warps are merged in shared memory; with more than one split a second
-// kernel merges the splits.
 #include "common.cuh"
 
 #include <mutex>
@@ -19,15 +25,22 @@ namespace pikv {
 
 constexpr int DA_WARPS = 4;
 constexpr int DA_THREADS = DA_WARPS * 32;
+constexpr int DA_CTAS_PER_SM = 3;
 constexpr int DA_MAX_GROUP = 8;
+constexpr int DA_MIN_BLOCK = 16;                        // pages per block, at least (more than a ring holds)
+constexpr int DA_ITEMS_PER_WORKER = 8;                  // blocks aimed at per worker of a head
+constexpr int DA_MAX_REQ = 12000;                       // requests per call: their page prefix is scanned in shared memory
+constexpr int DA_PLAN_THREADS = 1024;
+constexpr int DA_FOLD_STEPS = 8;                        // softmax steps between two folds of the carried bias term
 constexpr unsigned DA_WAIT_LIMIT = 1u << 24;            // mbarrier polls before giving up
 
 struct DecodeDev {
     const __nv_bfloat16* q;
     __nv_bfloat16* out;
-    int B, n_q, n_kv, G;
+    int B, n_q, n_kv, G;         // B = requests
     const int* seq_ids;
     const int* seq_len;
+    const int* q_rows;           // request -> row of q (null: the request's own index)
     const int* page_table;
     int num_seqs, max_pages, num_pages;
     const uint8_t* k_codes;
@@ -36,14 +49,21 @@ struct DecodeDev {
     const uint16_t* v_scale;
     const float* k_zp;   // 4-bit asymmetric cache only
     const float* v_zp;
-    int splits;
     float* lse;
     float* scores;
     int score_stride;
-    float* part_o;    // [B*n_q][splits][128]
-    float* part_ml;   // [B*n_q][splits][2]
+    int* head;        // workspace header: [0] item counter, [1] pages per block, [2] blocks (written by the plan kernel)
+    int* prefix;      // [B+1] pages of the requests before each request
+    int2* blk_start;  // [max_blocks] (request, page inside it) at which every block starts
+    float* part_o;    // [(max_blocks + B) * n_kv][G][128]
+    float* part_ml;   // [(max_blocks + B) * n_kv][G][2]  (running max in the log2 domain, denominator)
+    int workers, max_blocks;
     unsigned* status;
 };
+
+}  // namespace pikv
+#include "shard_decode.cuh"
+namespace pikv {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -112,11 +132,11 @@ template <int SHIFT>
 __device__ __forceinline__ uint32_t nib_pair_biased(uint32_t w) {
     return ((w >> SHIFT) & 0x000f000fu) | 0x64006400u;
 }
-// ... and with the 1024 taken off again (exact)
+// ... and centred: 1032 = 1024 + 8 taken off again (exact), n - 8 in [-8, 7]
 template <int SHIFT>
 __device__ __forceinline__ uint32_t nib_pair(uint32_t w) {
     const uint32_t x = nib_pair_biased<SHIFT>(w);
-    __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&x), __half2half2(__ushort_as_half(0x6400)));
+    __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&x), __half2half2(__ushort_as_half(0x6408)));
     return *reinterpret_cast<uint32_t*>(&h);
 }
 // two bytes of w selected by SEL -> (1024 + b, 1024 + b') as two f16
@@ -130,36 +150,126 @@ __device__ __forceinline__ uint32_t bytes_to_h2_biased(uint32_t w) { return __by
 //   O^T[ch, head] += Vcode^T[ch, pos] . P'^T[pos, head]   A = 16 channels x 16 positions, 8 mma per page
 // The softmax runs on S^T (a thread owns positions r, r+8 of heads 2j, 2j+1) and, for 8-bit codes, takes two
 // pages (32 positions) per step; P goes through 512 bytes of shared memory to become the B operand of the
-// second product.  Nothing but exact integers enters the
-// tensor cores on the cache side:
+// second product.  Nothing but exact integers enters the tensor cores on the cache side:
 //   q . x   = kscale * (q . code - zp * sum(q))                        (zp = 0 for the 8-bit cache)
 //   P . x_c = sum_pos P' * (bias + code_c) - sum_pos P' * (bias + zp),  P' = P * vscale
-// where bias is what the byte/nibble -> f16 trick leaves on (1152 = 1024 + 128 for bytes, 1024 for
-// nibbles).  The second sum is the same for every channel: it is carried like the softmax denominator
-// (corr) and subtracted at the end.
+// where bias is what the code -> f16 conversion leaves on: 1152 = 1024 + 128 for the bytes of V (one
+// byte-permute, no subtraction), -8 for nibbles (centred, so that code - 8 and zp - 8 are small).  The second
+// sum is the same for every channel: it is carried like the softmax denominator (corr) and taken off the
+// accumulators every DA_FOLD_STEPS steps, so that they never hold more than a few pages' worth of bias (the
+// tensor cores' fp32 accumulation truncates: a bias of 1152 x sum(P') carried over a 32768-token context
+// costs about 1e-3 of the output scale with 4-bit scales, 1e-4 with 8-bit ones).
+struct DACursor {
+    int r, p;           // request, page inside it
+    int pages, len;     // of request r
+    int row;            // page-table row of request r, or -1
+};
+struct DAItem {
+    int blk, h, left;   // block, KV head, pages of the item not yet issued / consumed
+    DACursor cur;
+};
+
+// block of page f of the per-head page list: the last block takes the remainder
+__device__ __forceinline__ int da_block_of(int f, int blk_pages, int nblocks) { return min(f / blk_pages, nblocks - 1); }
+
+// One CTA: pages before every request (exclusive prefix), the block length, where every block starts; clears
+// the item counter.  The prefix is scanned in shared memory (B <= DA_MAX_REQ).
+__global__ void __launch_bounds__(DA_PLAN_THREADS) decode_plan_kernel(DecodeDev d) {
+    extern __shared__ int pre[];
+    __shared__ int wtot[DA_PLAN_THREADS / 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int R = d.B;
+    const int max_len = d.max_pages * PIKV_PAGE_TOKENS;
+    for (int i = tid; i < R; i += DA_PLAN_THREADS) {
+        const int seq = d.seq_ids ? d.seq_ids[i] : i;
+        const bool ok = seq >= 0 && seq < d.num_seqs;
+        if (!ok && d.status) atomicOr(d.status, PIKV_ST_BAD_SEQ);
+        const int len = ok ? max(0, min(d.seq_len[i], max_len)) : 0;
+        pre[i + 1] = (len + PIKV_PAGE_TOKENS - 1) / PIKV_PAGE_TOKENS;
+    }
+    if (tid == 0) pre[0] = 0;
+    __syncthreads();
+    {
+        const int per = (R + DA_PLAN_THREADS - 1) / DA_PLAN_THREADS;
+        const int lo = 1 + tid * per, hi = min(R + 1, lo + per);
+        int sum = 0;
+        for (int i = lo; i < hi; ++i) sum += pre[i];
+        int inc = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += n;
+        }
+        if (lane == 31) wtot[warp] = inc;
+        __syncthreads();
+        int run = inc - sum;
+        for (int w = 0; w < warp; ++w) run += wtot[w];
+        for (int i = lo; i < hi; ++i) {
+            run += pre[i];
+            pre[i] = run;
+        }
+    }
+    __syncthreads();
+    const int P = pre[R];
+    const int per_head = max(1, d.workers / d.n_kv);
+    const int target = max(1, min(d.max_blocks, DA_ITEMS_PER_WORKER * per_head));
+    const int blk_pages = max(DA_MIN_BLOCK, (P + target - 1) / target);
+    const int nblocks = P > 0 ? max(1, P / blk_pages) : 0;
+    if (tid == 0) {
+        d.head[0] = 0;
+        d.head[1] = blk_pages;
+        d.head[2] = nblocks;
+    }
+    for (int i = tid; i <= R; i += DA_PLAN_THREADS) d.prefix[i] = pre[i];
+    for (int b = tid; b < nblocks; b += DA_PLAN_THREADS) {
+        const int f = b * blk_pages;
+        int lo = 0, hi = R - 1;                           // last request whose first page is at or before f
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (pre[mid] <= f) lo = mid; else hi = mid - 1;
+        }
+        d.blk_start[b] = make_int2(lo, f - pre[lo]);
+    }
+}
+
 template <int BITS>
-__global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d) {
+__global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel(DecodeDev d) {
     using GEO = DAGeom<BITS>;
     constexpr int STAGES = GEO::STAGES, STAGE_BYTES = GEO::STAGE, PAGE_BYTES = GEO::PAGE, ROW = GEO::ROW;
+    static_assert(DA_MIN_BLOCK > STAGES, "an item must outlast the ring");
     extern __shared__ __align__(128) unsigned char smem[];
     // [warp][stage] rings, the barriers, the P buffers
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)DA_WARPS * STAGES * STAGE_BYTES);
-    __shared__ float ml_s[DA_WARPS][DA_MAX_GROUP][2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane >> 2, j = lane & 3;
-    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int G = d.G;
-    const int seq = d.seq_ids ? d.seq_ids[b] : b;
-    const bool seq_ok = seq >= 0 && seq < d.num_seqs;
-    int len = seq_ok ? d.seq_len[b] : 0;
-    len = max(0, min(len, d.max_pages * PIKV_PAGE_TOKENS));
-    if (!seq_ok && tid == 0 && d.status) atomicOr(d.status, PIKV_ST_BAD_SEQ);
-    const int pages_total = (len + PIKV_PAGE_TOKENS - 1) / PIKV_PAGE_TOKENS;
-    const int pps = (pages_total + d.splits - 1) / d.splits;
-    const int p_begin = min(pages_total, split * pps), p_end = min(pages_total, p_begin + pps);
-    // this warp's pages: p_begin + warp + DA_WARPS * i
-    const int my_pages = (p_end - p_begin - warp + DA_WARPS - 1) / DA_WARPS;
+    const int G = d.G, R = d.B, n_kv = d.n_kv;
+    const int max_len = d.max_pages * PIKV_PAGE_TOKENS;
+    const int blk_pages = __ldg(d.head + 1), nblocks = __ldg(d.head + 2), P = __ldg(d.prefix + R);
+    const int nitems = nblocks * n_kv;
+
+    auto request = [&](int rq, int& len, int& row) {          // clamped length and page-table row of a request
+        const int seq = d.seq_ids ? __ldg(d.seq_ids + rq) : rq;
+        const bool ok = seq >= 0 && seq < d.num_seqs;
+        len = ok ? max(0, min(__ldg(d.seq_len + rq), max_len)) : 0;
+        row = ok ? seq : -1;
+    };
+    // the next item of the list (warp-uniform); the claims of a block's heads go to consecutive callers
+    auto claim = [&]() {
+        int id = 0;
+        if (lane == 0) id = atomicAdd(d.head, 1);
+        return __shfl_sync(0xffffffffu, id, 0);
+    };
+    auto load_item = [&](int id, DAItem& it) {
+        it.blk = id / n_kv;
+        it.h = id % n_kv;
+        const int2 st = __ldg(d.blk_start + it.blk);
+        it.cur.r = st.x;
+        it.cur.p = st.y;
+        request(it.cur.r, it.cur.len, it.cur.row);
+        it.cur.pages = (it.cur.len + PIKV_PAGE_TOKENS - 1) / PIKV_PAGE_TOKENS;
+        it.left = it.blk == nblocks - 1 ? P - it.blk * blk_pages : blk_pages;
+    };
 
     unsigned char* ring = smem + (size_t)warp * STAGES * STAGE_BYTES;
     __half* pbuf = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(bars + DA_WARPS * STAGES) + warp * DA_PBUF_BYTES);
@@ -170,17 +280,27 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    __syncthreads();
+    __syncwarp();
 
-    const int* pt_row = d.page_table + (size_t)(seq_ok ? seq : 0) * d.max_pages;
-    auto issue = [&](int i) {   // lane 0 only: load this warp's i-th page into stage i % STAGES
+    // moves a cursor `by` pages on (never across more than one request boundary)
+    auto advance = [&](DACursor& x, int by) {
+        x.p += by;
+        if (x.p < x.pages) return;
+        x.p = 0;
+        do {
+            if (++x.r >= R) { x.pages = 1 << 30; x.row = -1; return; }
+            request(x.r, x.len, x.row);
+            x.pages = (x.len + PIKV_PAGE_TOKENS - 1) / PIKV_PAGE_TOKENS;
+        } while (x.pages == 0);
+    };
+    auto issue = [&](const DACursor& x, int h, int i) {   // lane 0 only: load the page under the cursor into stage i % STAGES
         const int s = i % STAGES;
-        int page = pt_row[p_begin + warp + DA_WARPS * i];
+        int page = x.row >= 0 ? __ldg(d.page_table + (size_t)x.row * d.max_pages + x.p) : -1;
         if (page < 0 || page >= d.num_pages) {
             if (d.status) atomicOr(d.status, PIKV_ST_BAD_PAGE);
             page = 0;
         }
-        const size_t prow = ((size_t)page * d.n_kv + h) * PIKV_PAGE_TOKENS;
+        const size_t prow = ((size_t)page * n_kv + h) * PIKV_PAGE_TOKENS;
         const uint32_t dst = smem_u32(ring + (size_t)s * STAGE_BYTES);
         const uint32_t bar = bar0 + 8 * s;
         mbar_expect_tx(bar, STAGE_BYTES);
@@ -193,24 +313,50 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d)
             bulk_g2s(dst + 2 * PAGE_BYTES + 128, d.v_zp + prow, 64, bar);
         }
     };
-    if (lane == 0)
-        for (int i = 0; i < min(my_pages, STAGES); ++i) issue(i);
 
-    // ---- Q as the B operand: thread (r, j) holds Q[head r][32j .. 32j+32) as 16 f16 pairs ----
+    // Two walkers over this worker's items: `is` issues the copies and runs up to STAGES pages ahead of `c`,
+    // which does the arithmetic.  The issuing side claims the items; an item it has entered and the other has
+    // not yet is parked in pend_id (it never runs more than one item ahead).
+    DAItem is, c;
+    int next_id = claim();
+    if (next_id >= nitems) return;
+    load_item(next_id, is);
+    c = is;
+    next_id = claim();
+    int pend_id = -1;
+    int issued = 0, i = 0;                                 // pages issued / consumed by this worker so far
+    auto top_up = [&]() {
+        while (issued - i < STAGES) {
+            if (is.left == 0) {
+                if (pend_id >= 0 || next_id >= nitems) return;
+                load_item(next_id, is);
+                pend_id = next_id;
+                next_id = claim();
+            }
+            if (lane == 0) issue(is.cur, is.h, issued);
+            advance(is.cur, 1);
+            --is.left;
+            ++issued;
+        }
+    };
+    top_up();
+
     uint32_t qf[16];
-    float qm0, qm1;           // per head 2j, 2j+1: 2^e / sqrt(d) * log2(e), integer dot product -> log2-domain score
+    float qm0 = 0.f, qm1 = 0.f;   // per head 2j, 2j+1: 2^e / sqrt(d) * log2(e), integer dot product -> log2-domain score
     float qs0 = 0.f, qs1 = 0.f;   // 4 bit: sum of the query over its 128 channels
-    {
+    // ---- Q as the B operand: thread (r, j) holds Q[head r][32j .. 32j+32) as 16 f16 pairs ----
+    auto load_q = [&](int rq, int h) {
         float qv[32];
         if (r < G) {
-            const __nv_bfloat16* qp = d.q + ((size_t)b * d.n_q + (size_t)h * G + r) * 128 + 32 * j;
+            const int qrow = d.q_rows ? __ldg(d.q_rows + rq) : rq;
+            const __nv_bfloat16* qp = d.q + ((size_t)qrow * d.n_q + (size_t)h * G + r) * 128 + 32 * j;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                uint4 w = __ldg(reinterpret_cast<const uint4*>(qp) + i);
-                bf16x2_to_f32(w.x, qv[8 * i + 0], qv[8 * i + 1]);
-                bf16x2_to_f32(w.y, qv[8 * i + 2], qv[8 * i + 3]);
-                bf16x2_to_f32(w.z, qv[8 * i + 4], qv[8 * i + 5]);
-                bf16x2_to_f32(w.w, qv[8 * i + 6], qv[8 * i + 7]);
+                uint4 wq = __ldg(reinterpret_cast<const uint4*>(qp) + i);
+                bf16x2_to_f32(wq.x, qv[8 * i + 0], qv[8 * i + 1]);
+                bf16x2_to_f32(wq.y, qv[8 * i + 2], qv[8 * i + 3]);
+                bf16x2_to_f32(wq.z, qv[8 * i + 4], qv[8 * i + 5]);
+                bf16x2_to_f32(wq.w, qv[8 * i + 6], qv[8 * i + 7]);
             }
         } else {
 #pragma unroll
@@ -228,9 +374,9 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d)
         for (int i = 0; i < 16; ++i) {
             // 8 bit: consecutive channel pairs; 4 bit: pairs (c, c + 4) inside each group of 8, the order in
             // which nib_pair() takes nibbles out of a word
-            const int c = BITS == 8 ? 2 * i : 8 * (i >> 2) + (i & 3);
-            const int c2 = BITS == 8 ? c + 1 : c + 4;
-            qf[i] = pack_h2(qv[c] * down, qv[c2] * down);
+            const int cc = BITS == 8 ? 2 * i : 8 * (i >> 2) + (i & 3);
+            const int c2 = BITS == 8 ? cc + 1 : cc + 4;
+            qf[i] = pack_h2(qv[cc] * down, qv[c2] * down);
         }
         const float qmul = ldexpf(1.0f, e) * 0.08838834764831845f * 1.4426950408889634f;
         qm0 = __shfl_sync(0xffffffffu, qmul, 8 * j);          // lane of (head 2j, j = 0)
@@ -244,20 +390,15 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d)
             qs0 = __shfl_sync(0xffffffffu, qs, 8 * j);
             qs1 = __shfl_sync(0xffffffffu, qs, 8 * j + 4);
         }
-    }
+    };
 
     float o[8][4];
-#pragma unroll
-    for (int m = 0; m < 8; ++m)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) o[m][c] = 0.f;
     // running max, denominator and carried bias term of heads 2j and 2j+1 (this thread's share of the positions)
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f, corr0 = 0.f, corr1 = 0.f;
+    float m0, m1, l0, l1, corr0, corr1;
     bool timed_out = false;
-    int i = 0;
 
     // raw S^T of one page: this thread gets positions r (t[0], t[1]) and r+8 (t[2], t[3]) of heads 2j, 2j+1,
-    // scaled to the log2 domain; vw = bias + zero point of V at those positions (4 bit)
+    // scaled to the log2 domain; vw = zero point of V minus 8 at those positions (4 bit)
     auto page_scores = [&](const unsigned char* st, float (&t)[4], float& vw_lo, float& vw_hi) {
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};      // two accumulator chains
         if (BITS == 8) {
@@ -271,9 +412,9 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d)
             const uint32_t wh[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
-                const uint32_t a = wl[kk] ^ 0x80808080u, c = wh[kk] ^ 0x80808080u;
-                mma_f16((kk & 1) ? sb : sa, bytes_to_h2<0x4140>(a), bytes_to_h2<0x4140>(c), bytes_to_h2<0x4342>(a),
-                        bytes_to_h2<0x4342>(c), qf[2 * kk], qf[2 * kk + 1]);
+                const uint32_t a = wl[kk] ^ 0x80808080u, cw = wh[kk] ^ 0x80808080u;
+                mma_f16((kk & 1) ? sb : sa, bytes_to_h2<0x4140>(a), bytes_to_h2<0x4140>(cw), bytes_to_h2<0x4342>(a),
+                        bytes_to_h2<0x4342>(cw), qf[2 * kk], qf[2 * kk + 1]);
             }
         } else {
             const unsigned char* klo = st + r * 64;
@@ -296,25 +437,25 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d)
         if (BITS == 4) {
             const float* kzp = reinterpret_cast<const float*>(st + 2 * PAGE_BYTES + 64);
             const float* vzp = reinterpret_cast<const float*>(st + 2 * PAGE_BYTES + 128);
-            const float z_lo = kzp[r], z_hi = kzp[r + 8];
+            const float z_lo = kzp[r] - 8.f, z_hi = kzp[r + 8] - 8.f;          // the codes entered as code - 8
             t[0] -= z_lo * qs0; t[1] -= z_lo * qs1; t[2] -= z_hi * qs0; t[3] -= z_hi * qs1;
-            vw_lo = 1024.f + vzp[r];
-            vw_hi = 1024.f + vzp[r + 8];
+            vw_lo = vzp[r] - 8.f;
+            vw_hi = vzp[r + 8] - 8.f;
         }
         t[0] *= ks_lo * qm0; t[1] *= ks_lo * qm1; t[2] *= ks_hi * qm0; t[3] *= ks_hi * qm1;
     };
     // masks the positions past the sequence end and writes the raw scores out when asked
     auto page_mask_scores = [&](int pos0, float (&t)[4]) {
-        if (pos0 + PIKV_PAGE_TOKENS > len) {
-            if (pos0 + r >= len) t[0] = t[1] = -INFINITY;
-            if (pos0 + r + 8 >= len) t[2] = t[3] = -INFINITY;
+        if (pos0 + PIKV_PAGE_TOKENS > c.cur.len) {
+            if (pos0 + r >= c.cur.len) t[0] = t[1] = -INFINITY;
+            if (pos0 + r + 8 >= c.cur.len) t[2] = t[3] = -INFINITY;
         }
         if (d.scores) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int hh = 2 * j + (c & 1), pp = r + 8 * (c >> 1);
-                if (hh < G && pos0 + pp < len && pos0 + pp < d.score_stride)
-                    d.scores[((size_t)b * d.n_q + (size_t)h * G + hh) * d.score_stride + pos0 + pp] = t[c] * 0.6931471805599453f;
+            for (int cc = 0; cc < 4; ++cc) {
+                const int hh = 2 * j + (cc & 1), pp = r + 8 * (cc >> 1);
+                if (hh < G && pos0 + pp < c.cur.len && pos0 + pp < d.score_stride)
+                    d.scores[((size_t)c.cur.r * d.n_q + (size_t)c.h * G + hh) * d.score_stride + pos0 + pp] = t[cc] * 0.6931471805599453f;
             }
         }
     };
@@ -353,186 +494,256 @@ __global__ void __launch_bounds__(DA_THREADS, 3) decode_attn_kernel(DecodeDev d)
                 const uint32_t ga = __byte_perm(wq ? v0.y : v0.x, wq ? v1.y : v1.x, sel);
                 const uint32_t gb = __byte_perm(wq ? v2.y : v2.x, wq ? v3.y : v3.x, sel);
                 const int m = 2 * hb;   // byte m of the unit: channels 16r+2m (low nibble), 16r+2m+1 (high nibble)
-                mma_f16(o[m], nib_pair_biased<0>(ga), nib_pair_biased<4>(ga), nib_pair_biased<0>(gb), nib_pair_biased<4>(gb), pb0, pb1);
-                mma_f16(o[m + 1], nib_pair_biased<8>(ga), nib_pair_biased<12>(ga), nib_pair_biased<8>(gb), nib_pair_biased<12>(gb), pb0,
-                        pb1);
+                mma_f16(o[m], nib_pair<0>(ga), nib_pair<4>(ga), nib_pair<0>(gb), nib_pair<4>(gb), pb0, pb1);
+                mma_f16(o[m + 1], nib_pair<8>(ga), nib_pair<12>(ga), nib_pair<8>(gb), nib_pair<12>(gb), pb0, pb1);
             }
         }
     };
-
-    // 8 bit: two pages (32 positions) per step of the online softmax, i.e. one max reduction and one rescale of
-    // O for both (measured 0.794 -> 0.772 ms at 64 x 8 x 32768); the 4-bit kernel is faster with one (0.893
-    // against 0.945 ms)
-    constexpr int PPS = BITS == 8 ? 2 : 1;
-    for (; i < my_pages; i += PPS) {
-        const bool two = PPS == 2 && i + 1 < my_pages;           // warp-uniform
-        const int sA = i % STAGES, sB = (i + 1) % STAGES;
-        if (!mbar_wait(bar0 + 8 * sA, (uint32_t)(i / STAGES) & 1u) ||
-            (two && !mbar_wait(bar0 + 8 * sB, (uint32_t)((i + 1) / STAGES) & 1u))) {
-            timed_out = true;
-            break;
-        }
-        const unsigned char* stA = ring + (size_t)sA * STAGE_BYTES;
-        const unsigned char* stB = ring + (size_t)sB * STAGE_BYTES;
-        const int posA = (p_begin + warp + DA_WARPS * i) * PIKV_PAGE_TOKENS;
-        const int posB = (p_begin + warp + DA_WARPS * (i + 1)) * PIKV_PAGE_TOKENS;
-        float tA[4], tB[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        float vwA_lo = 0.f, vwA_hi = 0.f, vwB_lo = 0.f, vwB_hi = 0.f;
-        page_scores(stA, tA, vwA_lo, vwA_hi);
-        page_mask_scores(posA, tA);
-        if (two) {
-            page_scores(stB, tB, vwB_lo, vwB_hi);
-            page_mask_scores(posB, tB);
-        }
-        // ---- online softmax (log2 domain); the 8 lanes with the same j hold the positions of a head pair ----
-        float mx0 = fmaxf(fmaxf(tA[0], tA[2]), fmaxf(tB[0], tB[2])), mx1 = fmaxf(fmaxf(tA[1], tA[3]), fmaxf(tB[1], tB[3]));
+    // takes the carried bias term off the accumulators: its sum over the 8 lanes that share a head pair
+    auto fold_bias = [&]() {
 #pragma unroll
         for (int sh = 4; sh < 32; sh <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+            corr0 += __shfl_xor_sync(0xffffffffu, corr0, sh);
+            corr1 += __shfl_xor_sync(0xffffffffu, corr1, sh);
         }
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float mu0 = (mn0 == -INFINITY) ? 0.f : mn0, mu1 = (mn1 == -INFINITY) ? 0.f : mn1;
-        const float al0 = exp2f(m0 - mu0), al1 = exp2f(m1 - mu1);
-        m0 = mn0;
-        m1 = mn1;
-        float la = 0.f, lb = 0.f, ca = 0.f, cb = 0.f;
-        // P' = P * vscale, rounded to f16 as the tensor cores will see it; pbuf is [head][32 positions]
-        auto page_probs = [&](const unsigned char* st, const float (&t)[4], float vw_lo, float vw_hi, int base) {
-            const uint16_t* vsc = reinterpret_cast<const uint16_t*>(st + 2 * PAGE_BYTES + 32);
-            const float vs_lo = __uint_as_float((uint32_t)vsc[r] << 16), vs_hi = __uint_as_float((uint32_t)vsc[r + 8] << 16);
-            const float p0 = exp2f(t[0] - mu0), p1 = exp2f(t[1] - mu1), p2 = exp2f(t[2] - mu0), p3 = exp2f(t[3] - mu1);
-            la += p0 + p2;
-            lb += p1 + p3;
-            const __half h0 = __float2half_rn(p0 * vs_lo), h1 = __float2half_rn(p1 * vs_lo);
-            const __half h2 = __float2half_rn(p2 * vs_hi), h3 = __float2half_rn(p3 * vs_hi);
-            if (BITS == 8) {
-                ca += __half2float(h0) + __half2float(h2);           // x 1152 at the end
-                cb += __half2float(h1) + __half2float(h3);
-            } else {
-                ca += __half2float(h0) * vw_lo + __half2float(h2) * vw_hi;
-                cb += __half2float(h1) * vw_lo + __half2float(h3) * vw_hi;
-            }
-            pbuf[(2 * j) * 32 + base + r] = h0;
-            pbuf[(2 * j + 1) * 32 + base + r] = h1;
-            pbuf[(2 * j) * 32 + base + r + 8] = h2;
-            pbuf[(2 * j + 1) * 32 + base + r + 8] = h3;
-        };
-        page_probs(stA, tA, vwA_lo, vwA_hi, 0);
-        if (two) page_probs(stB, tB, vwB_lo, vwB_hi, 16);
-        l0 = l0 * al0 + la;
-        l1 = l1 * al1 + lb;
-        corr0 = corr0 * al0 + ca;
-        corr1 = corr1 * al1 + cb;
-        // rescale O: this thread's columns are query heads 2j and 2j+1
+        const float b0 = BITS == 8 ? corr0 * 1152.f : corr0, b1 = BITS == 8 ? corr1 * 1152.f : corr1;
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
-            o[m][0] *= al0; o[m][1] *= al1; o[m][2] *= al0; o[m][3] *= al1;
+            o[m][0] -= b0; o[m][1] -= b1; o[m][2] -= b0; o[m][3] -= b1;
         }
-        __syncwarp();
-        page_pv(stA, *reinterpret_cast<const uint32_t*>(pbuf + r * 32 + 2 * j),
-                *reinterpret_cast<const uint32_t*>(pbuf + r * 32 + 2 * j + 8));
-        if (two)
-            page_pv(stB, *reinterpret_cast<const uint32_t*>(pbuf + r * 32 + 16 + 2 * j),
-                    *reinterpret_cast<const uint32_t*>(pbuf + r * 32 + 24 + 2 * j));
-        __syncwarp();
-        if (lane == 0) {
-            if (i + STAGES < my_pages) issue(i + STAGES);
-            if (PPS == 2 && i + 1 + STAGES < my_pages) issue(i + 1 + STAGES);
-        }
-    }
-    if (timed_out) {
-        // give the copies already issued one more bounded chance to land before the ring is reused
-        if (lane == 0 && d.status) atomicOr(d.status, PIKV_ST_WAIT_TIMEOUT);
-        for (int ii = i; ii < min(my_pages, i + STAGES); ++ii)
-            (void)mbar_wait(bar0 + 8 * (ii % STAGES), (uint32_t)(ii / STAGES) & 1u);
-    }
+        corr0 = corr1 = 0.f;
+    };
 
-    // ---- denominators and the carried bias term: sum over the 8 lanes of a head pair ----
-#pragma unroll
-    for (int sh = 4; sh < 32; sh <<= 1) {
-        l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
-        corr0 += __shfl_xor_sync(0xffffffffu, corr0, sh);
-        corr1 += __shfl_xor_sync(0xffffffffu, corr1, sh);
-    }
-    if (BITS == 8) {
-        corr0 *= 1152.f;
-        corr1 *= 1152.f;
-    }
-#pragma unroll
-    for (int m = 0; m < 8; ++m) {
-        o[m][0] -= corr0; o[m][1] -= corr1; o[m][2] -= corr0; o[m][3] -= corr1;
-    }
-    // ---- merge the 4 warps ----
-    __syncthreads();   // every warp is done with its ring; reuse it as the merge buffer
-    float* mo = reinterpret_cast<float*>(smem);   // [warp][q][128]
-    if (r == 0) {
-        ml_s[warp][2 * j][0] = m0;
-        ml_s[warp][2 * j][1] = l0;
-        ml_s[warp][2 * j + 1][0] = m1;
-        ml_s[warp][2 * j + 1][1] = l1;
-    }
-#pragma unroll
-    for (int m = 0; m < 8; ++m) {
-        const int ch = 16 * r + 2 * m;
-        float* base = mo + (size_t)warp * DA_MAX_GROUP * 128;
-        base[(2 * j) * 128 + ch] = o[m][0];
-        base[(2 * j + 1) * 128 + ch] = o[m][1];
-        base[(2 * j) * 128 + ch + 1] = o[m][2];
-        base[(2 * j + 1) * 128 + ch + 1] = o[m][3];
-    }
-    __syncthreads();
-    const int ch = tid;   // 128 threads = 128 channels
-    for (int qh = 0; qh < G; ++qh) {
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < DA_WARPS; ++w) M = fmaxf(M, ml_s[w][qh][0]);
-        float acc = 0.f, l = 0.f;
-#pragma unroll
-        for (int w = 0; w < DA_WARPS; ++w) {
-            const float mw = ml_s[w][qh][0];
-            const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-            acc += mo[((size_t)w * DA_MAX_GROUP + qh) * 128 + ch] * sc;
-            l += ml_s[w][qh][1] * sc;
+    // 8 bit: two pages (32 positions) per step of the online softmax, i.e. one max reduction and one rescale of
+    // O for both; the 4-bit kernel is faster with one
+    constexpr int PPS = BITS == 8 ? 2 : 1;
+    while (!timed_out) {
+        if (c.left == 0) {                                 // next item, if the issuing side has entered one
+            if (pend_id < 0) top_up();
+            if (pend_id < 0) break;
+            load_item(pend_id, c);
+            pend_id = -1;
+            top_up();
         }
-        const size_t bq = (size_t)b * d.n_q + (size_t)h * G + qh;
-        if (d.splits == 1) {
-            d.out[bq * 128 + ch] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-            if (ch == 0 && d.lse) d.lse[bq] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
-        } else {
-            d.part_o[(bq * d.splits + split) * 128 + ch] = acc;
-            if (ch == 0) {
-                d.part_ml[(bq * d.splits + split) * 2 + 0] = M;
-                d.part_ml[(bq * d.splits + split) * 2 + 1] = l;
+        // ---- one request inside the item, or the part of it the item covers ----
+        const int seg = min(c.cur.pages - c.cur.p, c.left);
+        load_q(c.cur.r, c.h);
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) o[m][cc] = 0.f;
+        m0 = m1 = -INFINITY;
+        l0 = l1 = corr0 = corr1 = 0.f;
+        int since_fold = 0;
+        for (int s = 0; s < seg; s += PPS) {
+            const bool two = PPS == 2 && s + 1 < seg;                // warp-uniform
+            const int ia = i, ib = i + 1;
+            const int sA = ia % STAGES, sB = ib % STAGES;
+            if (!mbar_wait(bar0 + 8 * sA, (uint32_t)(ia / STAGES) & 1u) ||
+                (two && !mbar_wait(bar0 + 8 * sB, (uint32_t)(ib / STAGES) & 1u))) {
+                timed_out = true;
+                break;
+            }
+            const unsigned char* stA = ring + (size_t)sA * STAGE_BYTES;
+            const unsigned char* stB = ring + (size_t)sB * STAGE_BYTES;
+            const int posA = (c.cur.p + s) * PIKV_PAGE_TOKENS, posB = posA + PIKV_PAGE_TOKENS;
+            float tA[4], tB[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            float vwA_lo = 0.f, vwA_hi = 0.f, vwB_lo = 0.f, vwB_hi = 0.f;
+            page_scores(stA, tA, vwA_lo, vwA_hi);
+            page_mask_scores(posA, tA);
+            if (two) {
+                page_scores(stB, tB, vwB_lo, vwB_hi);
+                page_mask_scores(posB, tB);
+            }
+            // ---- online softmax (log2 domain); the 8 lanes with the same j hold the positions of a head pair ----
+            float mx0 = fmaxf(fmaxf(tA[0], tA[2]), fmaxf(tB[0], tB[2])), mx1 = fmaxf(fmaxf(tA[1], tA[3]), fmaxf(tB[1], tB[3]));
+#pragma unroll
+            for (int sh = 4; sh < 32; sh <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+            }
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float mu0 = (mn0 == -INFINITY) ? 0.f : mn0, mu1 = (mn1 == -INFINITY) ? 0.f : mn1;
+            const float al0 = exp2f(m0 - mu0), al1 = exp2f(m1 - mu1);
+            m0 = mn0;
+            m1 = mn1;
+            float la = 0.f, lb = 0.f, ca = 0.f, cb = 0.f;
+            // P' = P * vscale, rounded to f16 as the tensor cores will see it; pbuf is [head][32 positions]
+            auto page_probs = [&](const unsigned char* st, const float (&t)[4], float vw_lo, float vw_hi, int base) {
+                const uint16_t* vsc = reinterpret_cast<const uint16_t*>(st + 2 * PAGE_BYTES + 32);
+                const float vs_lo = __uint_as_float((uint32_t)vsc[r] << 16), vs_hi = __uint_as_float((uint32_t)vsc[r + 8] << 16);
+                const float p0 = exp2f(t[0] - mu0), p1 = exp2f(t[1] - mu1), p2 = exp2f(t[2] - mu0), p3 = exp2f(t[3] - mu1);
+                la += p0 + p2;
+                lb += p1 + p3;
+                const __half h0 = __float2half_rn(p0 * vs_lo), h1 = __float2half_rn(p1 * vs_lo);
+                const __half h2 = __float2half_rn(p2 * vs_hi), h3 = __float2half_rn(p3 * vs_hi);
+                if (BITS == 8) {
+                    ca += __half2float(h0) + __half2float(h2);           // x 1152 when it is folded
+                    cb += __half2float(h1) + __half2float(h3);
+                } else {
+                    ca += __half2float(h0) * vw_lo + __half2float(h2) * vw_hi;
+                    cb += __half2float(h1) * vw_lo + __half2float(h3) * vw_hi;
+                }
+                pbuf[(2 * j) * 32 + base + r] = h0;
+                pbuf[(2 * j + 1) * 32 + base + r] = h1;
+                pbuf[(2 * j) * 32 + base + r + 8] = h2;
+                pbuf[(2 * j + 1) * 32 + base + r + 8] = h3;
+            };
+            page_probs(stA, tA, vwA_lo, vwA_hi, 0);
+            if (two) page_probs(stB, tB, vwB_lo, vwB_hi, 16);
+            l0 = l0 * al0 + la;
+            l1 = l1 * al1 + lb;
+            corr0 = corr0 * al0 + ca;
+            corr1 = corr1 * al1 + cb;
+            // rescale O: this thread's columns are query heads 2j and 2j+1
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                o[m][0] *= al0; o[m][1] *= al1; o[m][2] *= al0; o[m][3] *= al1;
+            }
+            __syncwarp();
+            page_pv(stA, *reinterpret_cast<const uint32_t*>(pbuf + r * 32 + 2 * j),
+                    *reinterpret_cast<const uint32_t*>(pbuf + r * 32 + 2 * j + 8));
+            if (two)
+                page_pv(stB, *reinterpret_cast<const uint32_t*>(pbuf + r * 32 + 16 + 2 * j),
+                        *reinterpret_cast<const uint32_t*>(pbuf + r * 32 + 24 + 2 * j));
+            __syncwarp();
+            i += two ? 2 : 1;
+            top_up();                                      // refill the stages just freed
+            if (++since_fold == DA_FOLD_STEPS) {
+                fold_bias();
+                since_fold = 0;
             }
         }
+        if (timed_out) break;
+        // ---- this item's partial of the request: slot (block + request, head) ----
+        fold_bias();
+#pragma unroll
+        for (int sh = 4; sh < 32; sh <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
+        }
+        {
+            const size_t slot = ((size_t)c.blk + c.cur.r) * n_kv + c.h;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int qh = 2 * j + hh;
+                if (qh >= G) continue;
+                float4* po = reinterpret_cast<float4*>(d.part_o + ((slot * G + qh) * 128 + 16 * r));
+#pragma unroll
+                for (int m4 = 0; m4 < 4; ++m4)       // channels 16r + 4 m4 .. + 3
+                    po[m4] = make_float4(o[2 * m4][hh], o[2 * m4][2 + hh], o[2 * m4 + 1][hh], o[2 * m4 + 1][2 + hh]);
+                if (r == 0) {
+                    d.part_ml[(slot * G + qh) * 2 + 0] = hh ? m1 : m0;
+                    d.part_ml[(slot * G + qh) * 2 + 1] = hh ? l1 : l0;
+                }
+            }
+        }
+        c.left -= seg;
+        advance(c.cur, seg);
+    }
+    if (timed_out) {
+        // give the copies already issued one more bounded chance to land before the block leaves
+        if (lane == 0 && d.status) atomicOr(d.status, PIKV_ST_WAIT_TIMEOUT);
+        for (int ii = i; ii < issued; ++ii) (void)mbar_wait(bar0 + 8 * (ii % STAGES), (uint32_t)(ii / STAGES) & 1u);
     }
 }
 
+// One CTA per (request, query head): merges the partials of the workers that covered the unit.
 __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeDev d) {
-    const size_t bq = blockIdx.x;
-    const int ch = threadIdx.x;
+    const int rq = blockIdx.x / d.n_q, qg = blockIdx.x % d.n_q;
+    const int h = qg / d.G, qh = qg % d.G, ch = threadIdx.x;
+    const int blk_pages = d.head[1], nblocks = d.head[2];
+    const int pages = d.prefix[rq + 1] - d.prefix[rq];
+    const size_t bq = (size_t)rq * d.n_q + qg;
+    if (pages == 0) {
+        d.out[bq * 128 + ch] = __float2bfloat16_rn(0.f);
+        if (ch == 0 && d.lse) d.lse[bq] = -INFINITY;
+        return;
+    }
+    // the blocks that covered the request
+    const int g0 = da_block_of(d.prefix[rq], blk_pages, nblocks), g1 = da_block_of(d.prefix[rq + 1] - 1, blk_pages, nblocks);
     float M = -INFINITY;
-    for (int s = 0; s < d.splits; ++s) M = fmaxf(M, d.part_ml[(bq * d.splits + s) * 2]);
+    for (int g = g0; g <= g1; ++g) M = fmaxf(M, d.part_ml[((((size_t)g + rq) * d.n_kv + h) * d.G + qh) * 2]);
     float acc = 0.f, l = 0.f;
-    for (int s = 0; s < d.splits; ++s) {
-        const float ms = d.part_ml[(bq * d.splits + s) * 2];
+    for (int g = g0; g <= g1; ++g) {
+        const size_t s = (((size_t)g + rq) * d.n_kv + h) * d.G + qh;
+        const float ms = d.part_ml[s * 2];
         const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-        acc += d.part_o[(bq * d.splits + s) * 128 + ch] * sc;
-        l += d.part_ml[(bq * d.splits + s) * 2 + 1] * sc;
+        acc += d.part_o[s * 128 + ch] * sc;
+        l += d.part_ml[s * 2 + 1] * sc;
     }
     d.out[bq * 128 + ch] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     if (ch == 0 && d.lse) d.lse[bq] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
 }
 
-static int pick_splits(int B, int n_kv, int max_ctx) {
-    const int pages = ceil_div(max(max_ctx, 1), PIKV_PAGE_TOKENS);
-    const int resident = sm_count() * 3;
-    int s = ceil_div(8 * resident, max(1, B * n_kv));
-    s = min(s, max(1, pages / 64));   // at least 16 pages per warp (64 streams x 8 heads x 2048 tokens: 2 splits
-                                      // 73 us, 4 splits 80 us, 8 splits 99 us)
-    return max(1, min(s, 64));
+// The same merge on an expert-sharded box: request i = (stream i / top_k, choice i % top_k) of a decode step
+// whose rows are striped over the ranks; what this rank holds of it gives a NORMALISED partial output and its
+// log-sum-exp, stored straight into the buffers of the stream's home rank (peer pointers, plain stores) at
+// [local stream][choice][this rank].  The last CTA to finish raises this rank's "done" flag on every rank.
+__global__ void __launch_bounds__(128) decode_return_kernel(DecodeDev d, ShardReturn t) {
+    const int rq = blockIdx.x / d.n_q, qg = blockIdx.x % d.n_q;
+    const int h = qg / d.G, qh = qg % d.G, ch = threadIdx.x;
+    const int pages = d.prefix[rq + 1] - d.prefix[rq];
+    if (pages > 0) {
+        const int blk_pages = d.head[1], nblocks = d.head[2];
+        const int g0 = da_block_of(d.prefix[rq], blk_pages, nblocks), g1 = da_block_of(d.prefix[rq + 1] - 1, blk_pages, nblocks);
+        float M = -INFINITY;
+        for (int g = g0; g <= g1; ++g) M = fmaxf(M, d.part_ml[((((size_t)g + rq) * d.n_kv + h) * d.G + qh) * 2]);
+        float acc = 0.f, l = 0.f;
+        for (int g = g0; g <= g1; ++g) {
+            const size_t s = (((size_t)g + rq) * d.n_kv + h) * d.G + qh;
+            const float ms = d.part_ml[s * 2];
+            const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+            acc += d.part_o[s * 128 + ch] * sc;
+            l += d.part_ml[s * 2 + 1] * sc;
+        }
+        const int stream = rq / t.top_k, jsel = rq % t.top_k;
+        const int home = stream / t.streams_per_rank, sl = stream % t.streams_per_rank;
+        const size_t slot = (((size_t)sl * t.top_k + jsel) * t.world + t.rank) * d.n_q + qg;
+        t.peer_part_o[home][slot * 128 + ch] = l > 0.f ? acc / l : 0.f;
+        if (ch == 0) t.peer_part_lse[home][slot] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
+    }
+    // completion: every CTA counts itself after its stores are visible system-wide; the last one signals
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(t.counter, 1u);
+        if (prev == gridDim.x - 1) {
+            *t.counter = 0;
+            __threadfence_system();
+            const unsigned step = *t.seq;
+            for (int r = 0; r < t.world; ++r)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(t.peer_done_flags[r] + t.rank), "r"(step) : "memory");
+        }
+    }
+}
+
+static int da_workers() { return sm_count() * DA_CTAS_PER_SM * DA_WARPS; }
+
+// workspace: header, request prefix, block starts, partials of (max_blocks + B) x n_kv slots
+struct DALayout {
+    size_t prefix, blk_start, part_o, part_ml, total;
+};
+static DALayout da_layout(int B, int n_q, int n_kv, int max_blocks) {
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    DALayout l;
+    l.prefix = 256;
+    l.blk_start = l.prefix + up((size_t)(B + 1) * sizeof(int));
+    l.part_o = l.blk_start + up((size_t)max_blocks * sizeof(int2));
+    const size_t slots = ((size_t)max_blocks + B) * n_kv, G = (size_t)(n_q / n_kv);
+    l.part_ml = l.part_o + slots * G * 128 * sizeof(float);
+    l.total = l.part_ml + slots * G * 2 * sizeof(float);
+    return l;
+}
+static int da_default_blocks(int n_kv) { return DA_ITEMS_PER_WORKER * max(1, da_workers() / n_kv); }
+// the most blocks a workspace of `bytes` has room for (0: not even one)
+static int da_blocks_for(size_t bytes, int B, int n_q, int n_kv) {
+    int lo = 0, hi = da_default_blocks(n_kv);
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) / 2;
+        if (da_layout(B, n_q, n_kv, mid).total <= bytes) lo = mid; else hi = mid - 1;
+    }
+    return lo;
 }
 
 }  // namespace pikv
@@ -540,48 +751,58 @@ static int pick_splits(int B, int n_kv, int max_ctx) {
 using namespace pikv;
 
 extern "C" int pikv_decode_attn_default_splits(int32_t B, int32_t n_kv, int32_t max_ctx) {
-    if (B <= 0 || n_kv <= 0) return 1;
-    return pick_splits(B, n_kv, max_ctx);
+    (void)B; (void)n_kv; (void)max_ctx;
+    return 1;
 }
 
 extern "C" size_t pikv_decode_attn_workspace_bytes(int32_t B, int32_t n_q, int32_t n_kv, int32_t max_ctx,
                                                    int32_t splits) {
-    if (B <= 0 || n_q <= 0 || n_kv <= 0) return 0;
-    if (splits <= 0) splits = pick_splits(B, n_kv, max_ctx);
-    return (size_t)B * n_q * splits * (128 + 2) * sizeof(float);
+    (void)max_ctx; (void)splits;
+    if (B <= 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0) return 0;
+    return da_layout(B, n_q, n_kv, da_default_blocks(n_kv)).total;
 }
 
-static int decode_attn_launch(const pikv_decode_params* p, pikv_stream_t stream, int bits) {
+int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits, const int* q_rows, const ShardReturn* ret) {
     PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "decode_attn: null params");
-    PIKV_REQUIRE(p->q && p->out && p->seq_len && p->page_table, PIKV_EINVAL, "decode_attn: null pointer");
+    PIKV_REQUIRE(p->q && (p->out || ret) && p->seq_len && p->page_table, PIKV_EINVAL, "decode_attn: null pointer");
     PIKV_REQUIRE(p->k_codes && p->v_codes && p->k_scale && p->v_scale, PIKV_EINVAL, "decode_attn: null cache pointer");
     PIKV_REQUIRE(p->B > 0 && p->n_q > 0 && p->n_kv > 0 && p->n_q % p->n_kv == 0, PIKV_EINVAL, "decode_attn: bad head counts");
     PIKV_REQUIRE(p->n_q / p->n_kv <= DA_MAX_GROUP, PIKV_EUNSUPPORTED, "decode_attn: %d query heads per KV head (max %d)",
                  p->n_q / p->n_kv, DA_MAX_GROUP);
     PIKV_REQUIRE(p->num_seqs > 0 && p->max_pages > 0 && p->num_pages > 0, PIKV_EINVAL, "decode_attn: bad cache geometry");
-    PIKV_REQUIRE(p->n_kv <= 65535 && p->B <= 65535, PIKV_ELIMIT, "decode_attn: B and n_kv must be <= 65535");
+    PIKV_REQUIRE(p->n_kv <= da_workers(), PIKV_ELIMIT, "decode_attn: n_kv=%d exceeds the %d workers of the grid", p->n_kv, da_workers());
+    PIKV_REQUIRE((long long)p->B * p->max_pages < (1ll << 31), PIKV_ELIMIT, "decode_attn: B * max_pages must stay below 2^31");
+    PIKV_REQUIRE(p->B <= DA_MAX_REQ, PIKV_ELIMIT, "decode_attn: at most %d streams per call (got %d)", DA_MAX_REQ, p->B);
+    PIKV_REQUIRE((long long)p->B * p->n_q < (1ll << 21), PIKV_ELIMIT, "decode_attn: B * n_q too large for one call");
     DecodeDev d;
     d.q = static_cast<const __nv_bfloat16*>(p->q);
     d.out = static_cast<__nv_bfloat16*>(p->out);
     d.B = p->B; d.n_q = p->n_q; d.n_kv = p->n_kv; d.G = p->n_q / p->n_kv;
-    d.seq_ids = p->seq_ids; d.seq_len = p->seq_len; d.page_table = p->page_table;
+    d.seq_ids = p->seq_ids; d.seq_len = p->seq_len; d.q_rows = q_rows; d.page_table = p->page_table;
     d.num_seqs = p->num_seqs; d.max_pages = p->max_pages; d.num_pages = p->num_pages;
     d.k_codes = static_cast<const uint8_t*>(p->k_codes); d.v_codes = static_cast<const uint8_t*>(p->v_codes);
     d.k_scale = static_cast<const uint16_t*>(p->k_scale); d.v_scale = static_cast<const uint16_t*>(p->v_scale);
     d.k_zp = static_cast<const float*>(p->k_zp); d.v_zp = static_cast<const float*>(p->v_zp);
     PIKV_REQUIRE(bits == 8 || (d.k_zp && d.v_zp), PIKV_EINVAL, "decode_attn_q4: the 4-bit cache needs k_zp and v_zp");
-    d.splits = p->splits > 0 ? p->splits : pick_splits(p->B, p->n_kv, p->max_pages * PIKV_PAGE_TOKENS);
     d.lse = p->lse; d.scores = p->scores; d.score_stride = p->score_stride; d.status = p->status;
     PIKV_REQUIRE(d.scores == nullptr || d.score_stride > 0, PIKV_EINVAL, "decode_attn: score_stride");
-    d.part_o = nullptr; d.part_ml = nullptr;
-    if (d.splits > 1) {
-        const size_t need = (size_t)p->B * p->n_q * d.splits * (128 + 2) * sizeof(float);
-        PIKV_REQUIRE(p->workspace && p->workspace_bytes >= need, PIKV_EINVAL, "decode_attn: workspace too small (%zu needed)", need);
-        d.part_o = static_cast<float*>(p->workspace);
-        d.part_ml = d.part_o + (size_t)p->B * p->n_q * d.splits * 128;
-    }
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    dim3 grid(d.splits, p->n_kv, p->B);
+    PIKV_REQUIRE(p->workspace != nullptr, PIKV_EINVAL, "decode_attn: null workspace");
+    PIKV_REQUIRE((reinterpret_cast<uintptr_t>(p->workspace) & 15) == 0, PIKV_EINVAL, "decode_attn: workspace must be 16-byte aligned");
+    d.workers = da_workers();
+    d.max_blocks = da_blocks_for(p->workspace_bytes, p->B, p->n_q, p->n_kv);
+    PIKV_REQUIRE(d.max_blocks >= 1, PIKV_EINVAL, "decode_attn: workspace too small (%zu bytes at least, %zu for full speed)",
+                 da_layout(p->B, p->n_q, p->n_kv, 1).total, da_layout(p->B, p->n_q, p->n_kv, da_default_blocks(p->n_kv)).total);
+    const DALayout lay = da_layout(p->B, p->n_q, p->n_kv, d.max_blocks);
+    unsigned char* ws = static_cast<unsigned char*>(p->workspace);
+    d.head = reinterpret_cast<int*>(ws);
+    d.prefix = reinterpret_cast<int*>(ws + lay.prefix);
+    d.blk_start = reinterpret_cast<int2*>(ws + lay.blk_start);
+    d.part_o = reinterpret_cast<float*>(ws + lay.part_o);
+    d.part_ml = reinterpret_cast<float*>(ws + lay.part_ml);
+    decode_plan_kernel<<<1, DA_PLAN_THREADS, (size_t)(p->B + 1) * sizeof(int), st>>>(d);
+    int rc = check_launch("decode_plan_kernel");
+    if (rc != PIKV_OK) return rc;
+    const int grid = d.workers / DA_WARPS;
     if (bits == 8) {
         const size_t smem = da_smem_bytes<8>();
         if (cudaFuncSetAttribute(decode_attn_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -593,30 +814,31 @@ static int decode_attn_launch(const pikv_decode_params* p, pikv_stream_t stream,
             return check_launch("decode_attn smem attribute");
         decode_attn_kernel<4><<<grid, DA_THREADS, smem, st>>>(d);
     }
-    int launches = 1;
-    int rc = check_launch(bits == 8 ? "decode_attn_kernel<8>" : "decode_attn_kernel<4>");
+    rc = check_launch(bits == 8 ? "decode_attn_kernel<8>" : "decode_attn_kernel<4>");
     if (rc != PIKV_OK) return rc;
-    if (d.splits > 1) {
+    if (ret != nullptr) {
+        decode_return_kernel<<<p->B * p->n_q, 128, 0, st>>>(d, *ret);
+        rc = check_launch("decode_return_kernel");
+    } else {
         decode_merge_kernel<<<p->B * p->n_q, 128, 0, st>>>(d);
-        ++launches;
         rc = check_launch("decode_merge_kernel");
     }
-    count_launch(launches);
+    count_launch(3);
     return rc;
 }
 
 extern "C" int pikv_decode_attn_q8(const pikv_decode_params* p, pikv_stream_t stream) {
-    return decode_attn_launch(p, stream, 8);
+    return decode_attn_run(p, static_cast<cudaStream_t>(stream), 8, nullptr, nullptr);
 }
 
 extern "C" int pikv_decode_attn_q4(const pikv_decode_params* p, pikv_stream_t stream) {
-    return decode_attn_launch(p, stream, 4);
+    return decode_attn_run(p, static_cast<cudaStream_t>(stream), 4, nullptr, nullptr);
 }
 
 // ---- decode attention for callers that must not allocate --------------------------------------------
 // Some hosts of this library cannot call cudaMalloc when they need attention: a serving process that
 // handed all of HBM to its own page pool at start-up, a plug-in that runs inside someone else's
-// allocator-free region, code between cudaStreamBeginCapture and EndCapture.  For them the split-KV
+// allocator-free region, code between cudaStreamBeginCapture and EndCapture.  For them the workers'
 // partials live in this fixed array inside the library image.  Every GPU that loads the library keeps
 // these 8 MiB until the process exits, and every call on a device shares them.
 constexpr size_t DA_STATIC_SCRATCH_BYTES = (size_t)8 << 20;
@@ -652,19 +874,19 @@ extern "C" size_t pikv_decode_attn_static_scratch_bytes(void) { return DA_STATIC
 
 extern "C" int pikv_decode_attn_q8_static(const pikv_decode_params* p, pikv_stream_t stream) {
     PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "decode_attn_static: null params");
-    PIKV_REQUIRE(p->B > 0 && p->n_q > 0 && p->n_kv > 0 && p->max_pages > 0, PIKV_EINVAL, "decode_attn_static: bad sizes");
-    pikv_decode_params q = *p;
-    q.splits = p->splits > 0 ? p->splits : pick_splits(p->B, p->n_kv, p->max_pages * PIKV_PAGE_TOKENS);
-    const size_t need = q.splits > 1 ? (size_t)p->B * p->n_q * q.splits * (128 + 2) * sizeof(float) : 0;
+    PIKV_REQUIRE(p->B > 0 && p->n_q > 0 && p->n_kv > 0 && p->n_q % p->n_kv == 0 && p->max_pages > 0, PIKV_EINVAL,
+                 "decode_attn_static: bad sizes");
+    // the built-in array is smaller than the workspace the regular entry point asks for: fewer, longer blocks
+    const size_t need = da_layout(p->B, p->n_q, p->n_kv, max(1, da_workers() / p->n_kv)).total;
     PIKV_REQUIRE(need <= DA_STATIC_SCRATCH_BYTES, PIKV_ELIMIT,
-                 "decode_attn_static: %d streams x %d query heads x %d splits need %zu bytes of split scratch, the built-in "
-                 "array holds %zu; lower `splits` or use pikv_decode_attn_q8 with your own workspace",
-                 p->B, p->n_q, q.splits, need, DA_STATIC_SCRATCH_BYTES);
+                 "decode_attn_static: %d streams x %d query heads need %zu bytes of scratch for the partial results, the "
+                 "built-in array holds %zu; split the batch or use pikv_decode_attn_q8 with your own workspace",
+                 p->B, p->n_q, need, DA_STATIC_SCRATCH_BYTES);
     void* scratch = nullptr;
     const int rc = decode_static_scratch_ptr(&scratch);
     if (rc != PIKV_OK) return rc;
+    pikv_decode_params q = *p;
     q.workspace = scratch;
     q.workspace_bytes = DA_STATIC_SCRATCH_BYTES;
     return pikv_decode_attn_q8(&q, stream);
 }
-

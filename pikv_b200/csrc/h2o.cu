@@ -1,27 +1,39 @@
 // H2O scoring and eviction: score accumulate, segmented top-k select, page compaction.
 //
 // Select: one CTA per segment.  The segment's scores are staged once in shared memory as
-// order-preserving 32-bit keys; the m-th largest key is found by an 8-bit radix select over
-// the bits in which the segment's keys differ; elements above it are kept, and of the elements equal to it the ones with the
-// lowest indices are kept until m are taken (an in-order ballot scan).  The same routine
-// runs on the timestamps; both results are OR-ed into one keep bitmap from which the
-// evict mask and the ascending kept-index list are written.
+// order-preserving 32-bit keys.  Segments that fit in shared memory take the bucketed path
+// (select_bucketed): keys that are already in ascending order (timestamps of an append-only cache) are
+// answered with two binary searches and range marks; otherwise one histogram over 4096 buckets that are
+// linear in key space between the segment's smallest and largest key (float bits are a log scale, so
+// neither uniform nor heavy-tailed scores pile into a few buckets), one pass that marks everything above
+// the bucket holding the m-th largest key and lists that bucket's keys, and an exact rank among the listed
+// keys with ties going to the lowest index.  Longer segments, and the rare bucket too full to rank, take
+// the 8-bit radix select over the bits in which the keys differ (select_top_m).  The same routines run on
+// the timestamps; both results are OR-ed into one keep bitmap from which the evict mask and the ascending
+// kept-index list are written.
 #include "common.cuh"
+
+static int h2o_select_variant_for_tests();
 
 namespace pikv {
 
 constexpr int SEL_THREADS = 1024;          // keys staged in shared memory: one CTA per SM
 constexpr int SEL_THREADS_STREAM = 512;    // keys re-read from memory: small CTAs, several per SM
 constexpr int SEL_WARPS = SEL_THREADS / 32;
-constexpr int SEL_SMEM_KEYS = 49152;   // keys staged in shared memory up to this length
+constexpr int SEL_SMEM_KEYS = 45056;   // keys staged in shared memory up to this length (with the bitmap, list and buckets: 218 KB)
 
 __device__ __forceinline__ uint32_t order_key(float f) {
     uint32_t b = __float_as_uint(f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+constexpr int SEL_BUCKETS = 4096;      // first-level buckets of the bucketed path (4 per thread)
+constexpr int SEL_RANK_CAP = 768;      // listed keys ranked pairwise up to this many; more: radix select instead
+
 struct SelShared {
     int hist[256];
+    uint32_t kmin, kmax;  // bucketed path: smallest and largest key, ascending-order flag, chosen bucket
+    int sorted, bucket, above, bucket_cnt;
     int warp_tot[SEL_WARPS];
     uint32_t warp_or[SEL_WARPS], warp_and[SEL_WARPS];
     int width;            // number of low key bits in which the segment's keys differ
@@ -235,11 +247,246 @@ __device__ void select_top_m(const float* __restrict__ src, int n, int m, uint32
     __syncthreads();
 }
 
+// marks [a, b) in the keep bitmap (all threads)
+template <int NT>
+__device__ __forceinline__ void mark_range(uint32_t* keepw, int a, int b) {
+    if (b <= a) return;
+    for (int w = (a >> 5) + threadIdx.x; w <= ((b - 1) >> 5); w += NT) {
+        const int lo = max(a - w * 32, 0), hi = min(b - w * 32, 32);
+        const uint32_t bits = (hi >= 32 ? 0xffffffffu : ((1u << hi) - 1u)) & ~((1u << lo) - 1u);
+        atomicOr(&keepw[w], bits);
+    }
+}
+
+// Bucketed select for a segment staged in shared memory; same contract as select_top_m.  hist4k: SEL_BUCKETS ints.
+template <int NT>
+__device__ void select_bucketed(const float* __restrict__ src, int n, int m, uint32_t* keys, uint32_t* cand, uint32_t* keepw,
+                                int* hist4k, SelShared& sh) {
+    static_assert(NT * 4 == SEL_BUCKETS, "four buckets per thread");
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (m <= 0) return;
+    if (m >= n) {
+        mark_range<NT>(keepw, 0, n);
+        __syncthreads();
+        return;
+    }
+    // ---- stage the keys; smallest, largest ----
+    const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+    uint32_t kmin = 0xffffffffu, kmax = 0u;
+    if (aligned) {
+        const float4* src4 = reinterpret_cast<const float4*>(src);
+        for (int i = tid; i < n / 4; i += NT) {
+            const float4 f = __ldg(src4 + i);
+            const uint4 u = make_uint4(order_key(f.x), order_key(f.y), order_key(f.z), order_key(f.w));
+            reinterpret_cast<uint4*>(keys)[i] = u;
+            kmin = min(min(kmin, u.x), min(u.y, min(u.z, u.w)));
+            kmax = max(max(kmax, u.x), max(u.y, max(u.z, u.w)));
+        }
+    }
+    for (int i = (aligned ? 4 * (n / 4) : 0) + tid; i < n; i += NT) {
+        const uint32_t u = order_key(src[i]);
+        keys[i] = u;
+        kmin = min(kmin, u);
+        kmax = max(kmax, u);
+    }
+    kmin = __reduce_min_sync(0xffffffffu, kmin);
+    kmax = __reduce_max_sync(0xffffffffu, kmax);
+    if (lane == 0) {
+        sh.warp_or[warp] = kmax;
+        sh.warp_and[warp] = kmin;
+    }
+    if (tid == 0) sh.sorted = 1;
+    for (int i = tid; i < SEL_BUCKETS; i += NT) hist4k[i] = 0;
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t lo = 0xffffffffu, hi = 0u;
+        for (int w = 0; w < NT / 32; ++w) {
+            hi = max(hi, sh.warp_or[w]);
+            lo = min(lo, sh.warp_and[w]);
+        }
+        sh.kmin = lo;
+        sh.kmax = hi;
+        sh.cand_n = 0;
+    }
+    // ---- already ascending?  (a thread looks at four neighbouring pairs) ----
+    {
+        bool ok = true;
+        for (int i = 4 * tid; i < n - 1; i += 4 * NT) {
+            const int e = min(i + 4, n - 1);
+            for (int q = i; q < e; ++q) ok &= keys[q] <= keys[q + 1];
+        }
+        if (!__all_sync(0xffffffffu, ok) && lane == 0) sh.sorted = 0;
+    }
+    __syncthreads();
+    kmin = sh.kmin;
+    kmax = sh.kmax;
+    if (sh.sorted || kmin == kmax) {
+        // ascending keys: the m largest are the tail; of the run equal to the threshold the lowest indices are kept
+        const uint32_t kth = keys[n - m];
+        int a = 0, b = n;                        // a = first index with key >= kth, b = first index with key > kth
+        {
+            int lo = 0, hi = n - m;
+            while (lo < hi) { const int mid = (lo + hi) >> 1; if (keys[mid] >= kth) hi = mid; else lo = mid + 1; }
+            a = lo;
+            lo = n - m; hi = n;
+            while (lo < hi) { const int mid = (lo + hi) >> 1; if (keys[mid] > kth) hi = mid; else lo = mid + 1; }
+            b = lo;
+        }
+        mark_range<NT>(keepw, b, n);
+        mark_range<NT>(keepw, a, a + (m - (n - b)));
+        __syncthreads();
+        return;
+    }
+    // ---- histogram over buckets linear in key space ----
+    const float scale = 4095.0f / (float)(kmax - kmin);
+    auto bucket_of = [&](uint32_t u) { return min(SEL_BUCKETS - 1, (int)((float)(u - kmin) * scale)); };
+    const uint4* keys4 = reinterpret_cast<const uint4*>(keys);
+    const int n4 = n / 4;
+    for (int i = tid; i < n4; i += NT) {
+        const uint4 u = keys4[i];
+        atomicAdd(&hist4k[bucket_of(u.x)], 1);
+        atomicAdd(&hist4k[bucket_of(u.y)], 1);
+        atomicAdd(&hist4k[bucket_of(u.z)], 1);
+        atomicAdd(&hist4k[bucket_of(u.w)], 1);
+    }
+    for (int i = 4 * n4 + tid; i < n; i += NT) atomicAdd(&hist4k[bucket_of(keys[i])], 1);
+    __syncthreads();
+    // ---- the bucket holding the m-th largest key: suffix sums, thread t owns buckets 4t .. 4t+3 ----
+    {
+        const int c0 = hist4k[4 * tid], c1 = hist4k[4 * tid + 1], c2 = hist4k[4 * tid + 2], c3 = hist4k[4 * tid + 3];
+        const int sum = c0 + c1 + c2 + c3;
+        int suffix = sum;                                    // inclusive suffix over the lanes of the warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_down_sync(0xffffffffu, suffix, o);
+            if (lane + o < 32) suffix += v;
+        }
+        if (lane == 0) sh.warp_tot[warp] = suffix;
+        __syncthreads();
+        int above = suffix - sum;                            // keys in the buckets of higher threads
+        for (int w = warp + 1; w < NT / 32; ++w) above += sh.warp_tot[w];
+        const int cs[4] = {c0, c1, c2, c3};
+        int cum = above;
+#pragma unroll
+        for (int b = 3; b >= 0; --b) {
+            if (cum < m && m <= cum + cs[b]) {
+                sh.bucket = 4 * tid + b;
+                sh.above = cum;
+                sh.bucket_cnt = cs[b];
+            }
+            cum += cs[b];
+        }
+    }
+    __syncthreads();
+    const int bstar = sh.bucket, rem = m - sh.above, cn = sh.bucket_cnt;
+    if (cn > SEL_CAND_CAP) {
+        // a bucket too full to list (scores with one far outlier): the radix select handles any distribution
+        select_top_m<true, NT>(src, n, m, keys, cand, keepw, sh);
+        return;
+    }
+    // ---- mark everything above the bucket, list the bucket's indices ----
+    {
+        const int n4r = (n + 3) / 4;
+        for (int i0 = 0; i0 < n4r; i0 += NT) {
+            const int i = i0 + tid;
+            uint32_t nib = 0u, eq = 0u;
+            if (i < n4) {
+                const uint4 u = keys4[i];
+                const int b0 = bucket_of(u.x), b1 = bucket_of(u.y), b2 = bucket_of(u.z), b3 = bucket_of(u.w);
+                nib = (b0 > bstar ? 1u : 0u) | (b1 > bstar ? 2u : 0u) | (b2 > bstar ? 4u : 0u) | (b3 > bstar ? 8u : 0u);
+                eq = (b0 == bstar ? 1u : 0u) | (b1 == bstar ? 2u : 0u) | (b2 == bstar ? 4u : 0u) | (b3 == bstar ? 8u : 0u);
+            } else if (i < n4r) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (4 * i + e < n) {
+                        const int b = bucket_of(keys[4 * i + e]);
+                        nib |= (b > bstar ? 1u : 0u) << e;
+                        eq |= (b == bstar ? 1u : 0u) << e;
+                    }
+                }
+            }
+            uint32_t word = nib << (4 * (lane & 7));
+            word |= __shfl_xor_sync(0xffffffffu, word, 1);
+            word |= __shfl_xor_sync(0xffffffffu, word, 2);
+            word |= __shfl_xor_sync(0xffffffffu, word, 4);
+            if ((lane & 7) == 0 && word && i < n4r) atomicOr(&keepw[i >> 3], word);
+            // listed indices: one shared-memory atomic per warp
+            const int c = __popc(eq);
+            int inc = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += v;
+            }
+            int base = 0;
+            if (lane == 31 && inc) base = atomicAdd(&sh.cand_n, inc);
+            base = __shfl_sync(0xffffffffu, base, 31) + inc - c;
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (eq >> e & 1u) cand[base++] = 4 * i + e;
+        }
+    }
+    __syncthreads();
+    if (cn <= SEL_RANK_CAP) {
+        // ---- exact rank among the listed keys: larger key first, lower index first among equals ----
+        for (int i = tid; i < cn; i += NT) {
+            const int idx = cand[i];
+            const uint32_t ki = keys[idx];
+            int rank = 0;
+            for (int q = 0; q < cn; ++q) {
+                const int iq = cand[q];
+                const uint32_t kq = keys[iq];
+                rank += (kq > ki || (kq == ki && iq < idx)) ? 1 : 0;
+            }
+            if (rank < rem) atomicOr(&keepw[idx >> 5], 1u << (idx & 31));
+        }
+        __syncthreads();
+        return;
+    }
+    // ---- many listed keys: 8-bit radix select over the list for the rem-th largest, then lowest indices among equals ----
+    if (tid == 0) {
+        sh.prefix = 0u;
+        sh.remaining = rem;
+        sh.eq_total = cn;
+    }
+    __syncthreads();
+    for (int top = 32; top > 0; top -= 8) {
+        const int shift = top - 8;
+        for (int i = tid; i < 256; i += NT) sh.hist[i] = 0;
+        __syncthreads();
+        const uint32_t prefix = sh.prefix;
+        const uint32_t himask = top >= 32 ? 0u : (0xffffffffu << top);
+        for (int i = tid; i < cn; i += NT) {
+            const uint32_t u = keys[cand[i]];
+            if ((u & himask) == prefix) atomicAdd(&sh.hist[(u >> shift) & 255u], 1);
+        }
+        __syncthreads();
+        if (warp == 0) select_pick_bin(sh, prefix, shift, lane);
+        __syncthreads();
+    }
+    {
+        const uint32_t kth = sh.prefix;
+        const int need_eq = sh.remaining;
+        for (int i = tid; i < cn; i += NT) {
+            const int idx = cand[i];
+            const uint32_t ki = keys[idx];
+            bool keep = ki > kth;
+            if (ki == kth) {
+                int before = 0;                              // equal keys with a lower index
+                for (int q = 0; q < cn; ++q) before += (keys[cand[q]] == kth && cand[q] < idx) ? 1 : 0;
+                keep = before < need_eq;
+            }
+            if (keep) atomicOr(&keepw[idx >> 5], 1u << (idx & 31));
+        }
+    }
+    __syncthreads();
+}
+
 template <bool STAGED, int NT>
 __global__ void __launch_bounds__(NT) h2o_select_kernel(const float* acc, const float* ts, int stride,
                                                                  const int* seg_len, int n_all, int num_heavy,
                                                                  int num_recent, uint8_t* evict_mask, int* keep_idx,
-                                                                 int keep_stride, int* kept_count) {
+                                                                 int keep_stride, int* kept_count, bool radix_only) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ SelShared sh;
     const int seg = blockIdx.x;
@@ -250,14 +497,22 @@ __global__ void __launch_bounds__(NT) h2o_select_kernel(const float* acc, const 
     // keys start on a 16-byte boundary (they are read four at a time); the candidate list follows them
     uint32_t* keys = keepw + ((words_cap + 3) & ~3);
     uint32_t* cand = keys + (STAGED ? ((stride + 3) & ~3) : 0);   // unstaged: the list follows the bitmap
+    int* hist4k = reinterpret_cast<int*>(cand + SEL_CAND_CAP);     // staged: first-level buckets
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int w = tid; w < words_cap; w += NT) keepw[w] = 0u;
     __syncthreads();
     const float* a = acc + (size_t)seg * stride;
     const float* t = ts + (size_t)seg * stride;
     if (n > 0) {
-        select_top_m<STAGED, NT>(a, n, min(num_heavy, n), keys, cand, keepw, sh);
-        select_top_m<STAGED, NT>(t, n, min(num_recent, n), keys, cand, keepw, sh);
+        if (STAGED && !radix_only) {
+            if constexpr (NT * 4 == SEL_BUCKETS) {
+                select_bucketed<NT>(a, n, min(num_heavy, n), keys, cand, keepw, hist4k, sh);
+                select_bucketed<NT>(t, n, min(num_recent, n), keys, cand, keepw, hist4k, sh);
+            }
+        } else {
+            select_top_m<STAGED, NT>(a, n, min(num_heavy, n), keys, cand, keepw, sh);
+            select_top_m<STAGED, NT>(t, n, min(num_recent, n), keys, cand, keepw, sh);
+        }
     }
     // outputs: evict mask bytes and ascending kept indices
     const int tiles = (stride + 31) / 32;
@@ -386,6 +641,16 @@ __global__ void h2o_accumulate_attn_kernel(const float* scores, int score_stride
 
 using namespace pikv;
 
+// 0: chosen by the segment length (bucketed select when the keys fit in shared memory, radix select over re-read
+// scores otherwise); 1: radix select on staged keys; 2: radix select on re-read scores.  Process-wide, for tests.
+static int g_h2o_select_variant = 0;
+static int h2o_select_variant_for_tests() { return g_h2o_select_variant; }
+extern "C" int pikv_h2o_select_variant(int32_t variant) {
+    PIKV_REQUIRE(variant >= 0 && variant <= 2, PIKV_EINVAL, "h2o_select_variant: 0, 1 or 2");
+    g_h2o_select_variant = variant;
+    return PIKV_OK;
+}
+
 extern "C" int pikv_h2o_accumulate(float* acc, float* ts, int32_t n, const int32_t* idx, const float* w, int32_t m,
                                    float now, float decay, uint32_t* status, pikv_stream_t stream) {
     PIKV_REQUIRE(acc && ts && w, PIKV_EINVAL, "h2o_accumulate: null pointer");
@@ -414,17 +679,19 @@ extern "C" int pikv_h2o_select(const float* acc, const float* ts, int32_t segmen
     PIKV_REQUIRE(keep_idx == nullptr || keep_stride > 0, PIKV_EINVAL, "h2o_select: keep_stride");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t words = (size_t)(stride + 31) / 32 * 4;
-    // keys staged in shared memory whenever the segment fits (183 us against 191 us for 512 segments of 32768
-    // with the re-reading variant, which serves longer segments); PIKV_H2O_STAGED=0 forces the latter (testing aid)
-    const char* force = getenv("PIKV_H2O_STAGED");
-    const bool staged = stride <= SEL_SMEM_KEYS && !(force && force[0] == '0');
+    // keys staged in shared memory whenever the segment fits; longer segments re-read the scores from L2.
+    // The tests can force the two radix routines through pikv_h2o_select_variant.
+    const int variant = h2o_select_variant_for_tests();
+    const bool staged = stride <= SEL_SMEM_KEYS && variant != 2;
+    const bool radix_only = variant == 1;
     if (staged) {
-        size_t smem = ((words + 15) & ~(size_t)15) + (size_t)((stride + 3) & ~3) * 4 + (size_t)SEL_CAND_CAP * 4;
+        size_t smem = ((words + 15) & ~(size_t)15) + (size_t)((stride + 3) & ~3) * 4 + (size_t)SEL_CAND_CAP * 4 +
+                      (size_t)SEL_BUCKETS * 4;
         auto kern = h2o_select_kernel<true, SEL_THREADS>;
         if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("h2o_select smem attribute");
         kern<<<segments, SEL_THREADS, smem, st>>>(acc, ts, stride, seg_len, n, num_heavy, num_recent, evict_mask,
-                                                  keep_idx, keep_stride, kept_count);
+                                                  keep_idx, keep_stride, kept_count, radix_only);
     } else {
         PIKV_REQUIRE(words <= 200 * 1024, PIKV_ELIMIT, "h2o_select: stride=%d too long", stride);
         const size_t smem = ((words + 15) & ~(size_t)15) + (size_t)SEL_CAND_CAP * 4;
@@ -432,7 +699,7 @@ extern "C" int pikv_h2o_select(const float* acc, const float* ts, int32_t segmen
         if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return check_launch("h2o_select smem attribute");
         kern<<<segments, SEL_THREADS_STREAM, smem, st>>>(acc, ts, stride, seg_len, n, num_heavy, num_recent, evict_mask,
-                                                   keep_idx, keep_stride, kept_count);
+                                                   keep_idx, keep_stride, kept_count, true);
     }
     count_launch(1);
     return check_launch("h2o_select_kernel");

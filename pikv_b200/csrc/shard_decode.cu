@@ -1,0 +1,268 @@
+// Decode step of the striped expert-sharded cache: every stream's query goes to the ranks that hold rows of
+// the caches of its top-k experts, each rank attends over what it holds, the partial results go back to the
+// stream's home rank, which merges them.  All exchanges are plain stores into peer-mapped buffers (NVLink)
+// followed by per-rank flag words; every wait is bounded and reports through the status word.
+//
+//   home    shard_decode_post_kernel     q rows -> the ranks that need them, routing records -> every rank,
+//                                        then this rank's "posted" flag on every rank
+//   owner   shard_decode_plan_kernel     waits for every rank's flag, turns the S x k routing records into the
+//                                        request list of the local decode call (sequence, local length, q row)
+//   owner   decode_attn_kernel<8>        (decode_attn.cu) over the local request list
+//   owner   decode_return_kernel         (decode_attn.cu) normalised partial + log-sum-exp -> the home rank,
+//                                        then this rank's "done" flag on every rank
+//   home    shard_decode_combine_kernel  waits for every rank's "done" flag, merges the ranks' partials of each
+//                                        (stream, choice) by log-sum-exp, then combines the k choices
+#include "shard_decode.cuh"
+
+namespace pikv {
+
+constexpr unsigned SD_FAILED = 0x80000000u;
+
+__device__ __forceinline__ void sd_flag_store(unsigned* flag, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool sd_flag_wait(const unsigned* flag, unsigned want, unsigned limit_us) {
+    for (unsigned spins = 0;; ++spins) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+        if (seen == want) return true;
+        if (spins >= limit_us) return false;
+        __nanosleep(1000);
+    }
+}
+
+struct SDCtx {
+    pikv_shard_decode_ctx c;
+    int log2_stripe;
+    unsigned limit_us;
+};
+
+// One CTA per local stream: routing records to every rank, the query rows to the ranks that own a stripe of
+// either selected pair; the last CTA raises the flags.
+__global__ void __launch_bounds__(256) shard_decode_post_kernel(SDCtx x, const uint4* q_local, const int* topk_idx,
+                                                                const float* topk_w, const int* pair_len) {
+    const pikv_shard_decode_ctx& c = x.c;
+    __shared__ unsigned mask_s;
+    const int sl = blockIdx.x, tid = threadIdx.x;
+    const int s = c.rank * c.streams_per_rank + sl;
+    if (tid == 0) mask_s = 0;
+    __syncthreads();
+    if (tid < c.top_k) {
+        const int e = topk_idx[sl * c.top_k + tid];
+        const bool ok = e >= 0 && e < c.num_experts;
+        const int len = ok ? max(0, pair_len[(size_t)sl * c.num_experts + e]) : 0;
+        if (!ok && c.status) atomicOr(c.status, PIKV_ST_BAD_SEQ);
+        const int4 rec = make_int4(ok ? e : 0, len, __float_as_int(topk_w[sl * c.top_k + tid]), 0);
+        for (int r = 0; r < c.world; ++r) static_cast<int4*>(c.peer_route[r])[(size_t)s * c.top_k + tid] = rec;
+        if (len > 0) {
+            const int rot = (c.expert_rot[e] + s) % c.world;
+            const int stripes = (len + (1 << x.log2_stripe) - 1) >> x.log2_stripe;
+            unsigned m = 0;
+            for (int cc = 0; cc < min(stripes, c.world); ++cc) m |= 1u << ((rot + cc) % c.world);
+            atomicOr(&mask_s, m);
+        }
+    }
+    __syncthreads();
+    const unsigned mask = mask_s;
+    const int row16 = c.n_q * 16;                         // 16-byte words of one stream's query rows
+    for (int r = 0; r < c.world; ++r) {
+        if (!(mask >> r & 1u)) continue;
+        uint4* dst = static_cast<uint4*>(c.peer_q[r]) + (size_t)s * row16;
+        for (int i = tid; i < row16; i += blockDim.x) dst[i] = q_local[(size_t)sl * row16 + i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(c.counters, 1u);
+        if (prev == gridDim.x - 1) {
+            c.counters[0] = 0;
+            const unsigned step = (*c.seq & ~SD_FAILED) + 1u;
+            *c.seq = step;
+            __threadfence_system();
+            for (int r = 0; r < c.world; ++r) sd_flag_store(c.peer_post_flags[r] + c.rank, step);
+        }
+    }
+}
+
+// One CTA: the request list of this rank's decode call, request i = (stream i / k, choice i % k).
+__global__ void __launch_bounds__(256) shard_decode_plan_kernel(SDCtx x, int* seq_ids, int* seq_len, int* q_rows) {
+    const pikv_shard_decode_ctx& c = x.c;
+    __shared__ int ok_s;
+    const int tid = threadIdx.x;
+    if (tid == 0) ok_s = 1;
+    __syncthreads();
+    const unsigned step = *c.seq & ~SD_FAILED;
+    if (tid < c.world && !sd_flag_wait(c.peer_post_flags[c.rank] + tid, step, x.limit_us)) {
+        ok_s = 0;
+        if (c.status) atomicOr(c.status, PIKV_ST_WAIT_TIMEOUT);
+    }
+    __syncthreads();
+    const bool ok = ok_s != 0;
+    const int4* route = static_cast<const int4*>(c.peer_route[c.rank]);
+    const int n = c.num_streams * c.top_k;
+    for (int i = tid; i < n; i += blockDim.x) {
+        const int4 rec = __ldcg(route + i);                // written by a peer during this kernel: read at L2
+        const int s = i / c.top_k, e = rec.x;
+        int len = 0;
+        if (ok && e >= 0 && e < c.num_experts)
+            len = striped_local_len(rec.y, (c.expert_rot[e] + s) % c.world, c.rank, c.world, x.log2_stripe);
+        seq_ids[i] = (e >= 0 && e < c.num_experts) ? e * c.num_streams + s : 0;
+        seq_len[i] = len;
+        q_rows[i] = s;
+    }
+}
+
+// One CTA per (local stream, query head), one thread per channel.
+__global__ void __launch_bounds__(128) shard_decode_combine_kernel(SDCtx x, const int* topk_idx, const float* topk_w,
+                                                                   const int* pair_len, __nv_bfloat16* out, float* lse_out,
+                                                                   int mode) {
+    const pikv_shard_decode_ctx& c = x.c;
+    __shared__ int ok_s;
+    const int sl = blockIdx.x / c.n_q, qg = blockIdx.x % c.n_q, ch = threadIdx.x;
+    const int s = c.rank * c.streams_per_rank + sl;
+    if (ch == 0) ok_s = 1;
+    __syncthreads();
+    const unsigned step = *c.seq & ~SD_FAILED;
+    if (ch < c.world && !sd_flag_wait(c.peer_done_flags[c.rank] + ch, step, x.limit_us)) {
+        ok_s = 0;
+        if (c.status) atomicOr(c.status, PIKV_ST_WAIT_TIMEOUT);
+    }
+    __syncthreads();
+    if (!ok_s) return;
+    const float* part_o = c.peer_part_o[c.rank];
+    const float* part_lse = c.peer_part_lse[c.rank];
+    float res = 0.f, M_all = -INFINITY, den_all = 0.f;      // mode 1: running merge over the choices
+    for (int jsel = 0; jsel < c.top_k; ++jsel) {
+        const int e = topk_idx[sl * c.top_k + jsel];
+        if (e < 0 || e >= c.num_experts) continue;
+        const int len = max(0, pair_len[(size_t)sl * c.num_experts + e]);
+        const int rot = (c.expert_rot[e] + s) % c.world;
+        float M = -INFINITY;
+        float lse_r[8];
+        for (int r = 0; r < c.world; ++r) {
+            lse_r[r] = -INFINITY;
+            if (striped_local_len(len, rot, r, c.world, x.log2_stripe) > 0)
+                lse_r[r] = __ldcg(part_lse + (((size_t)sl * c.top_k + jsel) * c.world + r) * c.n_q + qg);
+            M = fmaxf(M, lse_r[r]);
+        }
+        float acc = 0.f, den = 0.f;
+        for (int r = 0; r < c.world; ++r) {
+            if (lse_r[r] == -INFINITY) continue;
+            const float wgt = expf(lse_r[r] - M);
+            acc += wgt * __ldcg(part_o + ((((size_t)sl * c.top_k + jsel) * c.world + r) * c.n_q + qg) * 128 + ch);
+            den += wgt;
+        }
+        const float o_j = den > 0.f ? acc / den : 0.f;
+        const float lse_j = den > 0.f ? M + logf(den) : -INFINITY;
+        if (mode == 0) {
+            res += topk_w[sl * c.top_k + jsel] * o_j;        // expert output times routing weight, summed
+        } else if (lse_j != -INFINITY) {
+            const float Mn = fmaxf(M_all, lse_j);
+            const float a = M_all == -INFINITY ? 0.f : expf(M_all - Mn), b = expf(lse_j - Mn);
+            res = res * a + o_j * b;
+            den_all = den_all * a + b;
+            M_all = Mn;
+        }
+        if (lse_out && ch == 0) lse_out[((size_t)sl * c.top_k + jsel) * c.n_q + qg] = lse_j;
+    }
+    if (mode != 0) res = den_all > 0.f ? res / den_all : 0.f;
+    out[((size_t)sl * c.n_q + qg) * 128 + ch] = __float2bfloat16_rn(res);
+}
+
+static int sd_check(const pikv_shard_decode_ctx* c, SDCtx* x, const char* who) {
+    PIKV_REQUIRE(c != nullptr, PIKV_EINVAL, "%s: null context", who);
+    PIKV_REQUIRE(c->world >= 1 && c->world <= 8 && c->rank >= 0 && c->rank < c->world, PIKV_EINVAL, "%s: bad world / rank", who);
+    PIKV_REQUIRE(c->num_experts > 0 && c->num_streams > 0 && c->top_k > 0 && c->top_k <= 8 && c->n_q > 0, PIKV_EINVAL,
+                 "%s: bad sizes", who);
+    PIKV_REQUIRE(c->streams_per_rank > 0 && c->streams_per_rank * c->world == c->num_streams, PIKV_EINVAL,
+                 "%s: num_streams must be world * streams_per_rank", who);
+    PIKV_REQUIRE(c->expert_rot && c->seq && c->counters, PIKV_EINVAL, "%s: null pointer", who);
+    int log2 = -1;
+    for (int b = 4; b < 27; ++b)
+        if ((1 << b) == c->stripe) log2 = b;
+    PIKV_REQUIRE(log2 > 0, PIKV_EINVAL, "%s: stripe=%d must be a power of two >= 16", who, c->stripe);
+    for (int r = 0; r < c->world; ++r)
+        PIKV_REQUIRE(c->peer_q[r] && c->peer_route[r] && c->peer_post_flags[r] && c->peer_part_o[r] && c->peer_part_lse[r] &&
+                         c->peer_done_flags[r],
+                     PIKV_EINVAL, "%s: null exchange buffer for rank %d", who, r);
+    x->c = *c;
+    x->log2_stripe = log2;
+    x->limit_us = c->wait_limit_us > 0 ? (unsigned)c->wait_limit_us : PIKV_DEFAULT_WAIT_US;
+    return PIKV_OK;
+}
+
+}  // namespace pikv
+
+using namespace pikv;
+
+extern "C" int pikv_shard_decode_post(const pikv_shard_decode_ctx* c, const void* q_local, const int32_t* topk_idx,
+                                      const float* topk_w, const int32_t* pair_len, pikv_stream_t stream) {
+    SDCtx x;
+    int rc = sd_check(c, &x, "shard_decode_post");
+    if (rc != PIKV_OK) return rc;
+    PIKV_REQUIRE(q_local && topk_idx && topk_w && pair_len, PIKV_EINVAL, "shard_decode_post: null pointer");
+    shard_decode_post_kernel<<<c->streams_per_rank, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, static_cast<const uint4*>(q_local), topk_idx, topk_w, pair_len);
+    count_launch(1);
+    return check_launch("shard_decode_post_kernel");
+}
+
+extern "C" int pikv_shard_decode_attn(const pikv_shard_decode_ctx* c, const pikv_decode_params* cache, int32_t* seq_ids,
+                                      int32_t* seq_len, int32_t* q_rows, pikv_stream_t stream) {
+    SDCtx x;
+    int rc = sd_check(c, &x, "shard_decode_attn");
+    if (rc != PIKV_OK) return rc;
+    PIKV_REQUIRE(cache && seq_ids && seq_len && q_rows, PIKV_EINVAL, "shard_decode_attn: null pointer");
+    PIKV_REQUIRE(cache->n_q == c->n_q, PIKV_EINVAL, "shard_decode_attn: the cache call and the context disagree on n_q");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    shard_decode_plan_kernel<<<1, 256, 0, st>>>(x, seq_ids, seq_len, q_rows);
+    count_launch(1);
+    rc = check_launch("shard_decode_plan_kernel");
+    if (rc != PIKV_OK) return rc;
+    pikv_decode_params p = *cache;
+    p.B = c->num_streams * c->top_k;
+    p.q = c->peer_q[c->rank];
+    p.out = nullptr;
+    p.seq_ids = seq_ids;
+    p.seq_len = seq_len;
+    p.lse = nullptr;
+    p.scores = nullptr;
+    ShardReturn t;
+    t.world = c->world; t.rank = c->rank; t.top_k = c->top_k; t.streams_per_rank = c->streams_per_rank;
+    for (int r = 0; r < 8; ++r) {
+        t.peer_part_o[r] = r < c->world ? c->peer_part_o[r] : nullptr;
+        t.peer_part_lse[r] = r < c->world ? c->peer_part_lse[r] : nullptr;
+        t.peer_done_flags[r] = r < c->world ? c->peer_done_flags[r] : nullptr;
+    }
+    t.counter = c->counters + 1;
+    t.seq = c->seq;
+    return decode_attn_run(&p, st, 8, q_rows, &t);
+}
+
+extern "C" int pikv_shard_decode_combine(const pikv_shard_decode_ctx* c, const int32_t* topk_idx, const float* topk_w,
+                                         const int32_t* pair_len, void* out, float* lse_out, int32_t mode,
+                                         pikv_stream_t stream) {
+    SDCtx x;
+    int rc = sd_check(c, &x, "shard_decode_combine");
+    if (rc != PIKV_OK) return rc;
+    PIKV_REQUIRE(topk_idx && topk_w && pair_len && out, PIKV_EINVAL, "shard_decode_combine: null pointer");
+    PIKV_REQUIRE(mode == 0 || mode == 1, PIKV_EINVAL, "shard_decode_combine: mode must be 0 (weighted sum) or 1 (log-sum-exp merge)");
+    shard_decode_combine_kernel<<<c->streams_per_rank * c->n_q, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, topk_idx, topk_w, pair_len, static_cast<__nv_bfloat16*>(out), lse_out, mode);
+    count_launch(1);
+    return check_launch("shard_decode_combine_kernel");
+}
+
+extern "C" size_t pikv_shard_decode_buffer_bytes(int32_t what, int32_t world, int32_t num_streams, int32_t top_k, int32_t n_q) {
+    if (world <= 0 || num_streams <= 0 || top_k <= 0 || n_q <= 0 || num_streams % world != 0) return 0;
+    const size_t sl = (size_t)(num_streams / world);
+    switch (what) {
+        case 0: return (size_t)num_streams * n_q * 128 * 2;               // q
+        case 1: return (size_t)num_streams * top_k * 16;                   // route
+        case 2: return (size_t)world * 4;                                  // post flags
+        case 3: return sl * top_k * world * n_q * 128 * sizeof(float);     // part_o
+        case 4: return sl * top_k * world * n_q * sizeof(float);           // part_lse
+        case 5: return (size_t)world * 4;                                  // done flags
+        default: return 0;
+    }
+}

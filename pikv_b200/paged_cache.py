@@ -84,6 +84,37 @@ class PagedKVCache(torch.nn.Module):
         p.status = _p(self.status)
         check(lib().pikv_kv_append_quant(C.byref(p), _stream()), "pikv_kv_append_quant")
 
+    def append_rope(self, k: torch.Tensor, v: torch.Tensor, dst_seq: torch.Tensor, slot: torch.Tensor,
+                    cos: torch.Tensor, sin: torch.Tensor, positions: Optional[torch.Tensor] = None) -> None:
+        """append() with the rotary position embedding of core/single/pikv_attention.py:329-390 applied to K in
+        registers before it is quantised (pikv_kv_append_rope).  cos, sin: [max_pos, 64] fp32 tables (the
+        reference's cos_cached / sin_cached); positions [T] int32 (default: the token index).  bf16 K/V, int8
+        symmetric cache."""
+        if self.bits != 8 or not self.symmetric:
+            raise PikvError("append_rope writes int8 symmetric caches")
+        k = _req(k, "k", torch.bfloat16)
+        v = _req(v, "v", torch.bfloat16)
+        cos, sin = _req(cos, "cos", torch.float32), _req(sin, "sin", torch.float32)
+        if cos.dim() != 2 or cos.shape[1] != HEAD_DIM // 2 or sin.shape != cos.shape:
+            raise PikvError(f"cos / sin must be [max_pos, {HEAD_DIM // 2}]")
+        T = k.shape[0]
+        if k.shape[1] != self.n_kv * HEAD_DIM or v.shape != k.shape:
+            raise PikvError(f"k/v must be [T, {self.n_kv * HEAD_DIM}]")
+        dst_seq = _req(dst_seq, "dst_seq", torch.int32)
+        slot = _req(slot, "slot", torch.int32)
+        if dst_seq.dim() == 1:
+            dst_seq, slot = dst_seq[:, None], slot[:, None]
+        if positions is not None:
+            positions = _req(positions, "positions", torch.int32)
+        p = AppendParams()
+        p.k, p.v, p.dtype, p.T, p.n_kv, p.top_k = _p(k), _p(v), _lib.PIKV_BF16, T, self.n_kv, dst_seq.shape[1]
+        p.dst_seq, p.slot, p.page_table = _p(dst_seq), _p(slot), _p(self.page_table)
+        p.num_seqs, p.max_pages, p.num_pages = self.num_seqs, self.max_pages, self.num_pages
+        p.bits, p.symmetric = 8, 1
+        p.k_codes, p.v_codes, p.k_scale, p.v_scale = _p(self.k_codes), _p(self.v_codes), _p(self.k_scale), _p(self.v_scale)
+        p.status = _p(self.status)
+        check(lib().pikv_kv_append_rope(C.byref(p), _p(cos), _p(sin), _p(positions), cos.shape[0], _stream()), "pikv_kv_append_rope")
+
     def _route_params(self, act, w2, b2, k, v, top_k, capacity, out, slot_base, want_probs):
         from . import ops
         act = _req(act, "act")

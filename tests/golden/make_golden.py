@@ -355,6 +355,17 @@ def attention_fixture(ref_attn):
     save("attention_decode", q=q, k=k, v=v, context=ctx)
 
 
+def rope_fixture(ref_attn):
+    """RotaryEmbedding of core/single/pikv_attention.py on head dim 128: tables and rotated q / k."""
+    torch.manual_seed(31)
+    rope = ref_attn.RotaryEmbedding(128, max_position_embeddings=96)
+    q = torch.randn(2, 24, 3, 128)
+    k = torch.randn(2, 24, 3, 128).bfloat16().float()          # bf16-valued keys, as the cache path feeds them
+    pos = torch.stack([torch.arange(24), torch.randperm(96)[:24]])
+    q_out, k_out = rope(q, k, pos)
+    save("rope", q=q, k=k, positions=pos, cos=rope.cos_cached, sin=rope.sin_cached, q_out=q_out, k_out=k_out)
+
+
 def lowrank_fixtures(ref_single_c, ref_module_c, ref_cachec):
     torch.manual_seed(40)
     H = 64
@@ -450,6 +461,7 @@ def main():
     from core.single.module import pikv_scheduling as m_scheduling
     module_policy_fixtures(m_scheduling)
     attention_fixture(pikv_attention)
+    rope_fixture(pikv_attention)
     lowrank_fixtures(pikv_compression, m_compression, kv_cache_compression)
     torch.set_num_threads(4)
     moe_fixture(args.reference)

@@ -42,7 +42,11 @@ def test_version_and_pure_host_entry_points(built_lib):
     assert lib.pikv_quant_block_workspace_bytes(1024, 256, 1) > 0
     # 16 header + K,V codes + scales, rounded to 16 bytes
     assert lib.pikv_a2a_record_bytes(8) == 16 + 2 * 8 * 128 + 4 * 8
-    assert lib.pikv_decode_attn_workspace_bytes(64, 32, 8, 32768, 8) == 64 * 32 * 8 * 130 * 4
+    # the page prefix of the streams + one partial (128 outputs, max, denominator) per (worker group + stream, query head)
+    ws = lib.pikv_decode_attn_workspace_bytes(64, 32, 8, 32768, 8)
+    assert ws >= 65 * 4 + 64 * 32 * 130 * 4 and ws % 4 == 0
+    assert lib.pikv_decode_attn_workspace_bytes(128, 32, 8, 32768, 0) > ws
+    assert lib.pikv_shard_decode_buffer_bytes(0, 8, 256, 2, 32) == 256 * 32 * 128 * 2
 
 
 def test_argument_errors_are_reported_without_a_gpu(built_lib):

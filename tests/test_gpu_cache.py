@@ -268,6 +268,42 @@ def test_h2o_select_segments_and_ties(dev, n, nh, nr, levels):
         np.testing.assert_array_equal(keep[s, : len(ki)].cpu().numpy(), ki)
 
 
+@pytest.mark.parametrize("kind", ["uniform", "heavy_tail", "outlier", "levels", "ascending", "ascending_runs", "constant"])
+def test_h2o_select_routines_agree_with_oracle(dev, kind):
+    """The bucketed select (default for segments that fit in shared memory) and the two radix routines must all
+    return the oracle's mask on score distributions that stress them differently: a far outlier (every other key
+    in one bucket), eight tied levels, keys already in ascending order (range marks), runs of equal timestamps."""
+    import pikv_b200
+    from pikv_b200 import ops
+    rng = np.random.default_rng(5)
+    S, n, nh, nr = 5, 5000, 300, 40
+    acc = {"uniform": rng.random((S, n)), "heavy_tail": rng.pareto(1.2, (S, n)), "outlier": rng.random((S, n)),
+           "levels": rng.integers(0, 8, (S, n)) / 8.0, "ascending": np.sort(rng.random((S, n)), axis=1),
+           "ascending_runs": np.sort(rng.integers(0, 50, (S, n)), axis=1).astype(np.float64),
+           "constant": np.full((S, n), 0.25)}[kind].astype(F32)
+    if kind == "outlier":
+        acc[:, 7] = 1e30
+        acc[:, 11] = -1e30
+    ts = np.tile(np.arange(n, dtype=F32), (S, 1))
+    if kind == "ascending_runs":
+        ts = np.floor(ts / 16)                                 # timestamps in runs of 16 equal values
+    if kind == "levels":
+        ts = rng.permutation(n).astype(F32)[None].repeat(S, 0)
+    want = np.stack([O.h2o_select(acc[s], ts[s], nh, nr)[0] for s in range(S)])
+    a, t = torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev)
+    try:
+        for variant in (0, 1, 2):
+            assert pikv_b200.lib().pikv_h2o_select_variant(variant) == 0
+            mask, keep, cnt = ops.h2o_select(a, t, nh, nr)
+            np.testing.assert_array_equal(mask.cpu().numpy(), want, err_msg=f"variant {variant}")
+            for s in range(S):
+                kept = np.nonzero(~want[s])[0]
+                assert int(cnt[s]) == len(kept)
+                np.testing.assert_array_equal(keep[s, : len(kept)].cpu().numpy(), kept)
+    finally:
+        pikv_b200.lib().pikv_h2o_select_variant(0)
+
+
 def test_h2o_select_ragged_lengths(dev):
     from pikv_b200 import ops
     rng = np.random.default_rng(1)
@@ -631,3 +667,36 @@ def test_module_adakv_and_duo_attention_match_reference(dev):
     np.testing.assert_array_equal(duo.select_eviction_candidates(keys[:40], keys[:40], {}).cpu().numpy(), g["duo/small"])
     assert int(duo.eviction_count) == int(g["duo/evictions"])
     assert duo.get_scheduler_stats()["sink_size"] == 5
+
+
+def test_append_rope_matches_reference(dev):
+    """Rotary embedding + quantise + append in one kernel: K codes and scales equal the oracle's quantisation of
+    the reference's rotated keys (golden fixture from RotaryEmbedding.forward), bit for bit; V as the plain append."""
+    import pikv_b200
+    g = load_golden("rope")
+    cos, sin = torch.from_numpy(g["cos"]).to(dev), torch.from_numpy(g["sin"]).to(dev)
+    k = torch.from_numpy(g["k"]).reshape(48, 3 * 128)                         # [B*S, heads*128], bf16-valued
+    pos = torch.from_numpy(g["positions"].reshape(-1).astype(np.int32))
+    v = torch.randn(48, 3 * 128).bfloat16()
+    cache = pikv_b200.PagedKVCache(2, 40, 3, device=dev)
+    dst = torch.arange(48, dtype=torch.int32)[:, None] % 2
+    slot = (torch.arange(48, dtype=torch.int32)[:, None] // 2).contiguous()
+    cache.append_rope(k.bfloat16().to(dev), v.to(dev), dst.to(dev).contiguous(), slot.to(dev), cos, sin, pos.to(dev))
+    torch.cuda.synchronize()
+    cache.check_status()
+    want_k = g["k_out"].reshape(48, 3 * 128)                                  # the reference's rotated keys
+    q, sc, _ = O.quant_token_groups(want_k, 8, 128, True)
+    dq, codes = cache.gather(dst[:, 0].to(dev).contiguous(), slot[:, 0].to(dev).contiguous(), "k", codes=True)
+    np.testing.assert_array_equal(codes.cpu().numpy().astype(F32), q)
+    np.testing.assert_array_equal(dq.cpu().numpy(), O.dequant_token_groups(q, O.bf16_round(sc), np.zeros_like(sc), 128))
+    qv, _, _ = O.quant_token_groups(v.float().numpy(), 8, 128, True)
+    _, vcodes = cache.gather(dst[:, 0].to(dev).contiguous(), slot[:, 0].to(dev).contiguous(), "v", codes=True)
+    np.testing.assert_array_equal(vcodes.cpu().numpy().astype(F32), qv)
+    # positions default to the token index
+    cache2 = pikv_b200.PagedKVCache(1, 48, 3, device=dev)
+    s2 = torch.arange(48, dtype=torch.int32, device=dev)[:, None].contiguous()
+    cache2.append_rope(k.bfloat16().to(dev), v.to(dev), torch.zeros_like(s2), s2, cos, sin)
+    want2 = O.rope_rotate(g["k"].reshape(48, 3, 128), np.arange(48), g["cos"], g["sin"]).reshape(48, 384)
+    q2, _, _ = O.quant_token_groups(want2, 8, 128, True)
+    _, c2 = cache2.gather(torch.zeros(48, dtype=torch.int32, device=dev), s2[:, 0].contiguous(), "k", codes=True)
+    np.testing.assert_array_equal(c2.cpu().numpy().astype(F32), q2)

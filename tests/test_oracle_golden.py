@@ -338,3 +338,12 @@ def test_module_adakv_and_duo_attention_masks():
     np.testing.assert_array_equal(O.duo_attention_mask(n, C, 5, 17), g["duo/mask"])
     np.testing.assert_array_equal(O.duo_attention_mask(40, C, 5, 17), g["duo/small"])
     assert int(g["duo/evictions"]) == 1
+
+
+def test_rope_matches_reference():
+    g = load_golden("rope")
+    for b in range(2):
+        np.testing.assert_array_equal(O.rope_rotate(g["q"][b], g["positions"][b], g["cos"], g["sin"]), g["q_out"][b])
+        np.testing.assert_array_equal(O.rope_rotate(g["k"][b], g["positions"][b], g["cos"], g["sin"]), g["k_out"][b])
+    c, s_ = O.rope_tables(96, 128)
+    assert np.abs(c - g["cos"]).max() < 1e-5 and np.abs(s_ - g["sin"]).max() < 1e-5     # fp32 angles up to 95 rad

@@ -2,7 +2,7 @@
 
 Some callers cannot allocate device memory when they need attention (all of HBM already belongs to
 their own page pool, or they sit inside a stream capture); pikv_decode_attn_q8_static keeps its
-split-KV scratch in an array inside the library instead.  Two calls in a row must both reproduce the
+scratch for partial results in an array inside the library instead.  Two calls in a row must both reproduce the
 regular entry point, which shows that the shared array carries nothing over between calls.
 """
 import ctypes as C
