@@ -28,7 +28,8 @@ constexpr int DA_THREADS = DA_WARPS * 32;
 constexpr int DA_CTAS_PER_SM = 3;
 constexpr int DA_MAX_GROUP = 8;
 constexpr int DA_MIN_BLOCK = 16;                        // pages per block, at least (more than a ring holds)
-constexpr int DA_ITEMS_PER_WORKER = 8;                  // blocks aimed at per worker of a head
+constexpr int DA_ITEMS_PER_WORKER = 8;                  // blocks aimed at per worker of a head, at most
+constexpr int DA_ITEM_PAGES = 64;                       // ... while an item keeps this many pages
 constexpr int DA_MAX_REQ = 12000;                       // requests per call: their page prefix is scanned in shared memory
 constexpr int DA_PLAN_THREADS = 1024;
 constexpr int DA_FOLD_STEPS = 8;                        // softmax steps between two folds of the carried bias term
@@ -98,6 +99,16 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// int8 x int8 -> int32, A = 16 rows x 32 bytes (row-major), B = 32 x 8 (column-major)
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack4_s8(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
 }
 
 // two biased bytes (code ^ 0x80) of w selected by SEL -> two exact f16 codes
@@ -211,8 +222,12 @@ __global__ void __launch_bounds__(DA_PLAN_THREADS) decode_plan_kernel(DecodeDev 
     }
     __syncthreads();
     const int P = pre[R];
+    // blocks per worker of a head: as many as DA_ITEMS_PER_WORKER when that leaves items of DA_ITEM_PAGES pages or
+    // more (long lists: fast and slow SMs even out), down to one for short lists (an item start costs a few
+    // dependent loads)
     const int per_head = max(1, d.workers / d.n_kv);
-    const int target = max(1, min(d.max_blocks, DA_ITEMS_PER_WORKER * per_head));
+    const int k_items = max(1, min(DA_ITEMS_PER_WORKER, P / (per_head * DA_ITEM_PAGES)));
+    const int target = max(1, min(d.max_blocks, k_items * per_head));
     const int blk_pages = max(DA_MIN_BLOCK, (P + target - 1) / target);
     const int nblocks = P > 0 ? max(1, P / blk_pages) : 0;
     if (tid == 0) {
@@ -232,7 +247,16 @@ __global__ void __launch_bounds__(DA_PLAN_THREADS) decode_plan_kernel(DecodeDev 
     }
 }
 
-template <int BITS>
+// GS (at most four query heads per KV head): the first product runs on the INTEGER tensor cores.  The cache's
+// int8 codes (or the nibbles, split into bytes by one AND and one shift-AND per eight) are the A operand as they
+// lie in shared memory, with no conversion at all; the query becomes a 15-bit integer u = rint(q * 2^(13-e))
+// (2^e above the head's largest |q|: 6e-5 of that maximum, far below bf16's own 2^-8) cut into two int8 limbs,
+// u = 128 hi + lo, which sit in neighbouring columns of the B operand, so ONE m16n8k32 yields both limbs of the
+// four heads: 4 mma per page instead of 8, exact int32 sums, and a thread then owns one head at two positions
+// (the f16 path spends half its softmax on padding heads).  The second product stays in f16 (P' is not an
+// integer); the rescale factors travel from the thread that owns a head's statistics to the two threads that
+// own its accumulators by two shuffles per step.
+template <int BITS, bool GS>
 __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel(DecodeDev d) {
     using GEO = DAGeom<BITS>;
     constexpr int STAGES = GEO::STAGES, STAGE_BYTES = GEO::STAGE, PAGE_BYTES = GEO::PAGE, ROW = GEO::ROW;
@@ -280,6 +304,7 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    for (int i2 = lane; i2 < DA_PBUF_BYTES / 4; i2 += 32) reinterpret_cast<uint32_t*>(pbuf)[i2] = 0u;   // rows of absent heads stay zero
     __syncwarp();
 
     // moves a cursor `by` pages on (never across more than one request boundary)
@@ -341,15 +366,17 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
     };
     top_up();
 
-    uint32_t qf[16];
-    float qm0 = 0.f, qm1 = 0.f;   // per head 2j, 2j+1: 2^e / sqrt(d) * log2(e), integer dot product -> log2-domain score
+    uint32_t qf[GS ? 8 : 16];
+    float qm0 = 0.f, qm1 = 0.f;   // per head 2j, 2j+1 (GS: head j in qm0): integer dot product -> log2-domain score
     float qs0 = 0.f, qs1 = 0.f;   // 4 bit: sum of the query over its 128 channels
-    // ---- Q as the B operand: thread (r, j) holds Q[head r][32j .. 32j+32) as 16 f16 pairs ----
+    // ---- Q as the B operand: thread (r, j) holds channels 32j .. 32j+32 of column r ----
+    //   f16 path: column r = head r, 16 f16 pairs.   GS: column r = limb (r & 1) of head r >> 1, 32 int8 in 8 words
     auto load_q = [&](int rq, int h) {
         float qv[32];
-        if (r < G) {
+        const int qhead = GS ? (r >> 1) : r;
+        if (qhead < G) {
             const int qrow = d.q_rows ? __ldg(d.q_rows + rq) : rq;
-            const __nv_bfloat16* qp = d.q + ((size_t)qrow * d.n_q + (size_t)h * G + r) * 128 + 32 * j;
+            const __nv_bfloat16* qp = d.q + ((size_t)qrow * d.n_q + (size_t)h * G + qhead) * 128 + 32 * j;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 uint4 wq = __ldg(reinterpret_cast<const uint4*>(qp) + i);
@@ -367,11 +394,43 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
         for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(qv[i]));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        if constexpr (GS) {
+            const int e = amax > 0.f ? ilogbf(amax) + 1 : 0;          // amax < 2^e
+            const float up = ldexpf(1.0f, 13 - e);
+            int u[32], usum = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int full = (int)rintf(qv[i] * up);               // |full| <= 8192
+                const int lo = ((full + 64) & 127) - 64;               // [-64, 63]
+                usum += full;
+                u[i] = (r & 1) ? lo : ((full - lo) >> 7);              // hi in [-64, 64]
+            }
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                // the channels behind the k index of mma m: bytes of this thread's word pair (2m, 2m+1) of the K row
+                // (8 bit), or the even / odd nibbles of its word m (4 bit)
+                if (BITS == 8) {
+                    qf[2 * m] = pack4_s8(u[8 * m], u[8 * m + 1], u[8 * m + 2], u[8 * m + 3]);
+                    qf[2 * m + 1] = pack4_s8(u[8 * m + 4], u[8 * m + 5], u[8 * m + 6], u[8 * m + 7]);
+                } else {
+                    qf[2 * m] = pack4_s8(u[8 * m], u[8 * m + 2], u[8 * m + 4], u[8 * m + 6]);
+                    qf[2 * m + 1] = pack4_s8(u[8 * m + 1], u[8 * m + 3], u[8 * m + 5], u[8 * m + 7]);
+                }
+            }
+            const float qmul = ldexpf(1.0f, e - 13) * 0.08838834764831845f * 1.4426950408889634f;
+            qm0 = __shfl_sync(0xffffffffu, qmul, 8 * j);              // lane (column 2j = head j, channels 0..31)
+            if (BITS == 4) {
+                usum += __shfl_xor_sync(0xffffffffu, usum, 1);
+                usum += __shfl_xor_sync(0xffffffffu, usum, 2);
+                qs0 = (float)__shfl_sync(0xffffffffu, usum, 8 * j);
+            }
+            return;
+        }
         int e = 0;
         if (amax > 32768.f) e = ilogbf(amax) - 14;     // a power of two keeps the bf16 query exact in f16
         const float down = ldexpf(1.0f, -e);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < (GS ? 0 : 16); ++i) {
             // 8 bit: consecutive channel pairs; 4 bit: pairs (c, c + 4) inside each group of 8, the order in
             // which nib_pair() takes nibbles out of a word
             const int cc = BITS == 8 ? 2 * i : 8 * (i >> 2) + (i & 3);
@@ -400,6 +459,49 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
     // raw S^T of one page: this thread gets positions r (t[0], t[1]) and r+8 (t[2], t[3]) of heads 2j, 2j+1,
     // scaled to the log2 domain; vw = zero point of V minus 8 at those positions (4 bit)
     auto page_scores = [&](const unsigned char* st, float (&t)[4], float& vw_lo, float& vw_hi) {
+        if constexpr (GS) {
+            // integer path: t[0] / t[2] = head j at positions r / r+8 (t[1], t[3] unused)
+            int acc[4] = {0, 0, 0, 0};
+            if (BITS == 8) {
+                const unsigned char* klo = st + r * 128;
+                const unsigned char* khi = st + (r + 8) * 128;
+                const uint4 la = *reinterpret_cast<const uint4*>(klo + 16 * ((2 * j) ^ r));
+                const uint4 lb = *reinterpret_cast<const uint4*>(klo + 16 * ((2 * j + 1) ^ r));
+                const uint4 ha = *reinterpret_cast<const uint4*>(khi + 16 * ((2 * j) ^ r));
+                const uint4 hb = *reinterpret_cast<const uint4*>(khi + 16 * ((2 * j + 1) ^ r));
+                const uint32_t wl[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+                const uint32_t wh[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+#pragma unroll
+                for (int m = 0; m < 4; ++m) mma_s8(acc, wl[2 * m], wh[2 * m], wl[2 * m + 1], wh[2 * m + 1], qf[2 * m], qf[2 * m + 1]);
+            } else {
+                const unsigned char* klo = st + r * 64;
+                const unsigned char* khi = st + (r + 8) * 64;
+                const uint4 lq = *reinterpret_cast<const uint4*>(klo + 8 * ((2 * j) ^ (r & 4)));
+                const uint4 hq = *reinterpret_cast<const uint4*>(khi + 8 * ((2 * j) ^ (r & 4)));
+                const uint32_t wl[4] = {lq.x, lq.y, lq.z, lq.w};
+                const uint32_t wh[4] = {hq.x, hq.y, hq.z, hq.w};
+#pragma unroll
+                for (int m = 0; m < 4; ++m)
+                    mma_s8(acc, wl[m] & 0x0f0f0f0fu, wh[m] & 0x0f0f0f0fu, (wl[m] >> 4) & 0x0f0f0f0fu, (wh[m] >> 4) & 0x0f0f0f0fu,
+                           qf[2 * m], qf[2 * m + 1]);
+            }
+            const uint16_t* ksc = reinterpret_cast<const uint16_t*>(st + 2 * PAGE_BYTES);
+            const float ks_lo = __uint_as_float((uint32_t)ksc[r] << 16), ks_hi = __uint_as_float((uint32_t)ksc[r + 8] << 16);
+            t[0] = (float)(acc[0] * 128 + acc[1]);
+            t[2] = (float)(acc[2] * 128 + acc[3]);
+            if (BITS == 4) {
+                const float* kzp = reinterpret_cast<const float*>(st + 2 * PAGE_BYTES + 64);
+                const float* vzp = reinterpret_cast<const float*>(st + 2 * PAGE_BYTES + 128);
+                t[0] -= kzp[r] * qs0;
+                t[2] -= kzp[r + 8] * qs0;
+                vw_lo = vzp[r] - 8.f;
+                vw_hi = vzp[r + 8] - 8.f;
+            }
+            t[0] *= ks_lo * qm0;
+            t[2] *= ks_hi * qm0;
+            t[1] = t[3] = -INFINITY;
+            return;
+        }
         float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};      // two accumulator chains
         if (BITS == 8) {
             const unsigned char* klo = st + r * 128;
@@ -453,7 +555,8 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
         if (d.scores) {
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
-                const int hh = 2 * j + (cc & 1), pp = r + 8 * (cc >> 1);
+                if (GS && (cc & 1)) continue;
+                const int hh = GS ? j : 2 * j + (cc & 1), pp = r + 8 * (cc >> 1);
                 if (hh < G && pos0 + pp < c.cur.len && pos0 + pp < d.score_stride)
                     d.scores[((size_t)c.cur.r * d.n_q + (size_t)c.h * G + hh) * d.score_stride + pos0 + pp] = t[cc] * 0.6931471805599453f;
             }
@@ -506,7 +609,13 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
             corr0 += __shfl_xor_sync(0xffffffffu, corr0, sh);
             corr1 += __shfl_xor_sync(0xffffffffu, corr1, sh);
         }
-        const float b0 = BITS == 8 ? corr0 * 1152.f : corr0, b1 = BITS == 8 ? corr1 * 1152.f : corr1;
+        float b0 = BITS == 8 ? corr0 * 1152.f : corr0, b1 = BITS == 8 ? corr1 * 1152.f : corr1;
+        if constexpr (GS) {
+            // statistics of head h live in the lanes with j == h; the accumulators of heads 2j, 2j+1 here
+            const float mine = b0;
+            b0 = __shfl_sync(0xffffffffu, mine, (lane & ~3) | ((2 * j) & 3));
+            b1 = __shfl_sync(0xffffffffu, mine, (lane & ~3) | ((2 * j + 1) & 3));
+        }
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
             o[m][0] -= b0; o[m][1] -= b1; o[m][2] -= b0; o[m][3] -= b1;
@@ -555,16 +664,17 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
                 page_scores(stB, tB, vwB_lo, vwB_hi);
                 page_mask_scores(posB, tB);
             }
-            // ---- online softmax (log2 domain); the 8 lanes with the same j hold the positions of a head pair ----
+            // ---- online softmax (log2 domain); the 8 lanes with the same j hold the positions of a head pair
+            //      (GS: of head j, in t[0] and t[2]) ----
             float mx0 = fmaxf(fmaxf(tA[0], tA[2]), fmaxf(tB[0], tB[2])), mx1 = fmaxf(fmaxf(tA[1], tA[3]), fmaxf(tB[1], tB[3]));
 #pragma unroll
             for (int sh = 4; sh < 32; sh <<= 1) {
                 mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
-                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+                if (!GS) mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
             }
             const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
             const float mu0 = (mn0 == -INFINITY) ? 0.f : mn0, mu1 = (mn1 == -INFINITY) ? 0.f : mn1;
-            const float al0 = exp2f(m0 - mu0), al1 = exp2f(m1 - mu1);
+            float al0 = exp2f(m0 - mu0), al1 = GS ? 1.f : exp2f(m1 - mu1);
             m0 = mn0;
             m1 = mn1;
             float la = 0.f, lb = 0.f, ca = 0.f, cb = 0.f;
@@ -572,6 +682,16 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
             auto page_probs = [&](const unsigned char* st, const float (&t)[4], float vw_lo, float vw_hi, int base) {
                 const uint16_t* vsc = reinterpret_cast<const uint16_t*>(st + 2 * PAGE_BYTES + 32);
                 const float vs_lo = __uint_as_float((uint32_t)vsc[r] << 16), vs_hi = __uint_as_float((uint32_t)vsc[r + 8] << 16);
+                if constexpr (GS) {
+                    const float p0 = exp2f(t[0] - mu0), p2 = exp2f(t[2] - mu0);
+                    la += p0 + p2;
+                    const __half h0 = __float2half_rn(p0 * vs_lo), h2 = __float2half_rn(p2 * vs_hi);
+                    if (BITS == 8) ca += __half2float(h0) + __half2float(h2);
+                    else ca += __half2float(h0) * vw_lo + __half2float(h2) * vw_hi;
+                    pbuf[j * 32 + base + r] = h0;
+                    pbuf[j * 32 + base + r + 8] = h2;
+                    return;
+                }
                 const float p0 = exp2f(t[0] - mu0), p1 = exp2f(t[1] - mu1), p2 = exp2f(t[2] - mu0), p3 = exp2f(t[3] - mu1);
                 la += p0 + p2;
                 lb += p1 + p3;
@@ -595,6 +715,12 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
             l1 = l1 * al1 + lb;
             corr0 = corr0 * al0 + ca;
             corr1 = corr1 * al1 + cb;
+            if constexpr (GS) {
+                // the accumulators of heads 2j, 2j+1 live here, their rescale factors in the lanes with j' = head
+                const float mine = al0;
+                al0 = __shfl_sync(0xffffffffu, mine, (lane & ~3) | ((2 * j) & 3));
+                al1 = __shfl_sync(0xffffffffu, mine, (lane & ~3) | ((2 * j + 1) & 3));
+            }
             // rescale O: this thread's columns are query heads 2j and 2j+1
 #pragma unroll
             for (int m = 0; m < 8; ++m) {
@@ -609,7 +735,7 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
             __syncwarp();
             i += two ? 2 : 1;
             top_up();                                      // refill the stages just freed
-            if (++since_fold == DA_FOLD_STEPS) {
+            if (BITS == 8 && ++since_fold == DA_FOLD_STEPS) {      // (centred nibbles leave next to no bias)
                 fold_bias();
                 since_fold = 0;
             }
@@ -632,10 +758,14 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
 #pragma unroll
                 for (int m4 = 0; m4 < 4; ++m4)       // channels 16r + 4 m4 .. + 3
                     po[m4] = make_float4(o[2 * m4][hh], o[2 * m4][2 + hh], o[2 * m4 + 1][hh], o[2 * m4 + 1][2 + hh]);
-                if (r == 0) {
+                if (!GS && r == 0) {
                     d.part_ml[(slot * G + qh) * 2 + 0] = hh ? m1 : m0;
                     d.part_ml[(slot * G + qh) * 2 + 1] = hh ? l1 : l0;
                 }
+            }
+            if (GS && r == 0 && j < G) {             // the statistics of head j
+                d.part_ml[(slot * G + j) * 2 + 0] = m0;
+                d.part_ml[(slot * G + j) * 2 + 1] = l0;
             }
         }
         c.left -= seg;
@@ -803,17 +933,20 @@ int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits
     int rc = check_launch("decode_plan_kernel");
     if (rc != PIKV_OK) return rc;
     const int grid = d.workers / DA_WARPS;
-    if (bits == 8) {
-        const size_t smem = da_smem_bytes<8>();
-        if (cudaFuncSetAttribute(decode_attn_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return check_launch("decode_attn smem attribute");
-        decode_attn_kernel<8><<<grid, DA_THREADS, smem, st>>>(d);
-    } else {
-        const size_t smem = da_smem_bytes<4>();
-        if (cudaFuncSetAttribute(decode_attn_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return check_launch("decode_attn smem attribute");
-        decode_attn_kernel<4><<<grid, DA_THREADS, smem, st>>>(d);
-    }
+    const bool gs = d.G <= 4;      // integer first product (see decode_attn_kernel)
+#define PIKV_DA_LAUNCH(BITS, GS)                                                                                          \
+    do {                                                                                                                  \
+        const size_t smem = da_smem_bytes<BITS>();                                                                        \
+        auto kern = decode_attn_kernel<BITS, GS>;                                                                         \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)            \
+            return check_launch("decode_attn smem attribute");                                                            \
+        kern<<<grid, DA_THREADS, smem, st>>>(d);                                                                          \
+    } while (0)
+    if (bits == 8 && gs) PIKV_DA_LAUNCH(8, true);
+    else if (bits == 8) PIKV_DA_LAUNCH(8, false);
+    else if (gs) PIKV_DA_LAUNCH(4, true);
+    else PIKV_DA_LAUNCH(4, false);
+#undef PIKV_DA_LAUNCH
     rc = check_launch(bits == 8 ? "decode_attn_kernel<8>" : "decode_attn_kernel<4>");
     if (rc != PIKV_OK) return rc;
     if (ret != nullptr) {
