@@ -514,9 +514,9 @@ def gpu_arm(args):
         R = extra_cfg.pop("buffer_sets", 1)
         hooks = extra_cfg.pop("hooks", None)
         verify = extra_cfg.pop("verify", None)
-        # The first multi-GPU process on an idle box starts out slower than later ones and recovers only with
-        # traffic, so untimed blocks of steps run for `warm_s` seconds first; every rank stops after the same
-        # block (the decision comes from the all-reduced clock).  The JSON line states the seconds.
+        # Untimed blocks of steps for `warm_s` seconds before the timed regions; every rank stops after the same
+        # block (the decision comes from the all-reduced clock).  The JSON line states the seconds.  (Measured with
+        # 0, 8 and 45 s: the same step time, so a few seconds are the default.)
         warm_s = float(os.environ.get("PIKV_BENCH_MULTI_WARMUP_S", str(args.multi_warmup_s)))
         t_begin, base, block = time.time(), steps, 2000
         while warm_s > 0:
@@ -806,6 +806,38 @@ def other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, gpu_index, single_
     del x
     torch.cuda.empty_cache()
 
+    # the gate net's first layer fused with ReLU, the second layer and the gate tail (tensor-bound): [T,4096] x
+    # [4096,4096] + [T,4096] x [4096,8]; beside it the same net as a library GEMM + ReLU followed by the gate kernel
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tf_peak = float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        tf_peak = 1400.0
+    Tn, Hn, En = WORKLOAD["tokens"], WORKLOAD["hidden"], WORKLOAD["experts"]
+    gx = torch.randn(Tn, Hn, device=dev).bfloat16()
+    gw1 = (torch.randn(Hn, Hn, device=dev) / Hn ** 0.5).bfloat16()
+    gb1 = torch.zeros(Hn, device=dev)
+    gw2, gb2 = gate_weights(Hn, En, 7)
+    gw2, gb2 = gw2.to(dev), gb2.to(dev)
+    capn = int(Tn * WORKLOAD["capacity_factor"] * WORKLOAD["top_k"] / En)
+    gout = ops.gate_mlp_fused(gx, gw1, gb1, gw2, gb2, top_k=2, capacity=capn)
+    flops = 2.0 * Tn * Hn * Hn + 2.0 * Tn * Hn * En
+    ms, n, cl = measure(lambda: ops.gate_mlp_fused(gx, gw1, gb1, gw2, gb2, top_k=2, capacity=capn, out=gout))
+    assert pikv_b200.lib().pikv_gate_error_state() == 0
+    out["gate_net"] = {"ms": ms, "flops": flops, "TFLOPs": flops / (ms * 1e-3) / 1e12, "frac": flops / (ms * 1e-3) / 1e12 / tf_peak,
+                       "peak": tf_peak, "peak_source": "measured (sustained bf16)", "bound": "tensor", "kernel": "gate_mlp_kernel",
+                       "launches_timed": n, "clocks": cl, "tokens": Tn, "hidden": Hn}
+    gb1h = gb1.bfloat16()
+
+    def library_net():
+        h = torch.relu(torch.nn.functional.linear(gx, gw1, gb1h))
+        ops.gate_fused(h, gw2, gb2, top_k=2, capacity=capn, out=gout)
+
+    ms_l, n_l, cl_l = measure(library_net)
+    out["gate_net"]["library_gemm_plus_gate_ms"] = ms_l
+    del gx, gw1, gout
+    torch.cuda.empty_cache()
+
     w4 = single_gpu_workload(WORKLOAD["tokens"], bits=4)
     sampler = ClockSampler(gpu_index)
     sampler.start()
@@ -889,13 +921,23 @@ def sharded_arm(torch, dist, dev, rank, world, steps, gpu_index, peak):
         torch.cuda.synchronize()
 
     # ---- prefill: this rank's streams, one 16384-token chunk each ----
-    outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(4)]
     streams_here = list(range(rank * spr, (rank + 1) * spr))
+    # three independent chains of streams on three CUDA streams: the gate of one stream's chunk overlaps the
+    # append of another's (each chain has its own gate result; a stream's step touches only its own lengths)
+    NB = 3
+    branches = [torch.cuda.Stream(device=dev) for _ in range(NB)]
+    outs = [ops.gate_fused(sets[0][0], w2, b2, top_k=k, capacity=0) for _ in range(NB)]
 
     def fill():
-        for s_ in streams_here:
-            a_, K_, V_ = sets[s_ % 4]
-            cache.route_append(s_, K_, V_, act=a_, w2=w2, b2=b2, out=outs[s_ % 4])
+        cur = torch.cuda.current_stream()
+        for b_, st_ in enumerate(branches):
+            st_.wait_stream(cur)
+            with torch.cuda.stream(st_):
+                for s_ in streams_here[b_::NB]:
+                    a_, K_, V_ = sets[s_ % 4]
+                    cache.route_append(s_, K_, V_, act=a_, w2=w2, b2=b2, out=outs[b_])
+        for st_ in branches:
+            cur.wait_stream(st_)
         cache.barrier()
 
     fill()                                   # eager once (workspaces, launch path), then as one CUDA graph: the step
@@ -1137,7 +1179,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other kernels' sub-records (decode attention, H2O, low-rank, 4-bit append)")
     ap.add_argument("--no-sharded", action="store_true", help="skip the expert-sharded configuration (striped cache: prefill + decode step)")
-    ap.add_argument("--multi-warmup-s", type=float, default=45.0,
+    ap.add_argument("--multi-warmup-s", type=float, default=3.0,
                     help="multi-GPU: seconds of untimed steps before the timed regions (stated in the line as warmup_s)")
     ap.add_argument("--workload", default="append", choices=["append", "decode", "lowrank"],
                     help="append = the headline route+quantise+append step; the others print lines for the other kernels")

@@ -127,6 +127,17 @@ int    pikv_gate_fused(const pikv_gate_params* p, pikv_stream_t stream);
  * mbarrier wait ran out and the outputs are invalid); waits for the work queued before it. */
 int    pikv_gate_error_state(void);
 
+/* The whole gate net in one kernel: logits = relu(x . w1^T + b1) . w2^T + b2, then the same tail and outputs as
+ * pikv_gate_fused (the router's nn.Sequential(Linear, ReLU, Linear), core/single/pikv_routing.py:34-38, whose
+ * first layer is the one dense contraction of "route": [T,K] x [K,H] on tcgen05 tensor cores, fp32 accumulation
+ * in tensor memory).  The hidden activations never go to HBM: each 128-token tile keeps them in shared memory,
+ * 256 hidden units at a time, as the operand of the second product.
+ *   p: as for pikv_gate_fused with H = hidden units (inputs of w2 [E,H]); p->act is ignored; bf16; E <= 32;
+ *   T <= 131072 per call; phase PIKV_GATE_WHOLE.
+ *   x [T,K] bf16, w1 [H,K] bf16, b1 [H] fp32 or NULL. */
+int pikv_gate_mlp_fused(const pikv_gate_params* p, const void* x, int32_t K, const void* w1, const float* b1,
+                        pikv_stream_t stream);
+
 /* Dense [T,E,capacity] dispatch / combine tensors (zero-filled by this call)
  * for callers that read them.  position_mode 0: slot as given (running count,
  * core/single/module/pikv_routing.py:93-104); 1: the positions
@@ -323,9 +334,25 @@ typedef struct {
     const int32_t* expert_rot;
     const int32_t* expert_cap;
     void* peer_k_codes[8]; void* peer_v_codes[8]; void* peer_k_scale[8]; void* peer_v_scale[8];
+    void* mirror_k_scale;      /* optional, both or neither: local bf16 [world][pool entries] buffers that take */
+    void* mirror_v_scale;      /* the scales of rows stored on OTHER GPUs; pikv_shard_push_scales_striped ships them */
 } pikv_append_striped_params;
 
 int pikv_kv_append_striped(const pikv_append_striped_params* p, pikv_stream_t stream);
+
+/* Ships the scales a striped append (one stream, with mirrors) left in the local mirrors to their owners, 32
+ * bytes (one page of one head) at a time: the step appended the positions [len_before[e], min(len_after[e],
+ * expert_cap[e])) to the pair of expert e and this stream.  Same stream, after the append. */
+typedef struct {
+    const int32_t* len_before; const int32_t* len_after;   /* [E] */
+    const int32_t* expert_rot; const int32_t* expert_cap;  /* [E]; expert_cap may be NULL */
+    const int32_t* page_table;                             /* [E * num_streams][max_pages] */
+    int32_t world, rank, stripe, num_experts, num_streams, stream, n_kv, max_pages, num_pages;
+    const void* mirror_k_scale; const void* mirror_v_scale;
+    void* peer_k_scale[8]; void* peer_v_scale[8];
+} pikv_striped_push_params;
+
+int pikv_shard_push_scales_striped(const pikv_striped_push_params* p, pikv_stream_t stream);
 
 /* Read rows back in logical order, dequantised: out[i] = (code - zp) * scale for
  * sequence seq[i], position pos[i]; out is [n, n_kv*128] fp32, codes_out

@@ -78,6 +78,16 @@ class AppendStripedParams(C.Structure):
         ("base", AppendParams), ("world", i32), ("rank", i32), ("stripe", i32), ("num_experts", i32), ("num_streams", i32),
         ("stream", i32), ("which", i32), ("token_stream", vp), ("pair_len", vp), ("expert_rot", vp), ("expert_cap", vp),
         ("peer_k_codes", vp * 8), ("peer_v_codes", vp * 8), ("peer_k_scale", vp * 8), ("peer_v_scale", vp * 8),
+        ("mirror_k_scale", vp), ("mirror_v_scale", vp),
+    ]
+
+
+class StripedPushParams(C.Structure):
+    _fields_ = [
+        ("len_before", vp), ("len_after", vp), ("expert_rot", vp), ("expert_cap", vp), ("page_table", vp),
+        ("world", i32), ("rank", i32), ("stripe", i32), ("num_experts", i32), ("num_streams", i32), ("stream", i32),
+        ("n_kv", i32), ("max_pages", i32), ("num_pages", i32),
+        ("mirror_k_scale", vp), ("mirror_v_scale", vp), ("peer_k_scale", vp * 8), ("peer_v_scale", vp * 8),
     ]
 
 
@@ -132,6 +142,7 @@ SIGNATURES = {
     "pikv_gate_workspace_bytes": (sz, [i32, i32, i32]),
     "pikv_gate_fused": (i32, [C.POINTER(GateParams), vp]),
     "pikv_gate_error_state": (i32, []),
+    "pikv_gate_mlp_fused": (i32, [C.POINTER(GateParams), vp, i32, vp, vp, vp]),
     "pikv_dispatch_scatter": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp]),
     "pikv_kv_append_quant": (i32, [C.POINTER(AppendParams), vp]),
     "pikv_kv_append_rope": (i32, [C.POINTER(AppendParams), vp, vp, vp, i32, vp]),
@@ -142,6 +153,7 @@ SIGNATURES = {
     "pikv_h2o_select_variant": (i32, [i32]),
     "pikv_peer_barrier": (i32, [C.POINTER(PeerBarrierParams), vp]),
     "pikv_kv_append_striped": (i32, [C.POINTER(AppendStripedParams), vp]),
+    "pikv_shard_push_scales_striped": (i32, [C.POINTER(StripedPushParams), vp]),
     "pikv_shard_decode_buffer_bytes": (sz, [i32, i32, i32, i32, i32]),
     "pikv_shard_decode_post": (i32, [C.POINTER(ShardDecodeCtx), vp, vp, vp, vp, vp]),
     "pikv_shard_decode_attn": (i32, [C.POINTER(ShardDecodeCtx), C.POINTER(DecodeParams), vp, vp, vp, vp]),

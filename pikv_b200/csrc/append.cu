@@ -868,6 +868,10 @@ extern "C" int pikv_kv_append_striped(const pikv_append_striped_params* sp, pikv
     a.slot_base = sp->pair_len;
     a.st_experts = sp->num_experts; a.st_mul = sp->num_streams; a.st_add = sp->stream; a.st_log2 = log2;
     a.st_rot = sp->expert_rot; a.st_cap = sp->expert_cap; a.st_stream = sp->token_stream;
+    PIKV_REQUIRE((sp->mirror_k_scale == nullptr) == (sp->mirror_v_scale == nullptr), PIKV_EINVAL,
+                 "append_striped: give both scale mirrors or neither");
+    a.mirror[0] = static_cast<uint16_t*>(sp->mirror_k_scale); a.mirror[1] = static_cast<uint16_t*>(sp->mirror_v_scale);
+    a.mirror_stride = (size_t)p->num_pages * p->n_kv * PT;
     for (int r = 0; r < 8; ++r) {
         const bool on = r < sp->world;
         PIKV_REQUIRE(!on || (sp->peer_k_codes[r] && sp->peer_v_codes[r] && sp->peer_k_scale[r] && sp->peer_v_scale[r]),
@@ -887,6 +891,73 @@ extern "C" int pikv_kv_append_striped(const pikv_append_striped_params* sp, pikv
     else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, 3><<<grid, APPEND_THREADS, 0, st>>>(a);
     count_launch(1);
     return check_launch("kv_append_quant_kernel (striped)");
+}
+
+// ---- scales of the rows a striped append stored on other GPUs -------------------------------------------
+// The append left them in the local mirrors at the offsets they have in the owner's pools (a 2-byte store costs
+// the link as much as a 128-byte one).  The step appended positions [len_before[e], len_after[e]) to the pair of
+// expert e; one thread ships the scales of one (expert, 16-position page, head): two 16-byte stores per tensor
+// when the step wrote the whole page, entry by entry at the two ends of the range.
+__global__ void __launch_bounds__(256) striped_push_scales_kernel(pikv_striped_push_params p, int log2_stripe) {
+    const int e = blockIdx.x;
+    const int a = p.len_before[e];
+    int b = p.len_after[e];
+    if (p.expert_cap) b = min(b, p.expert_cap[e]);
+    if (b <= a) return;
+    const int p0 = a / PT, p1 = (b - 1) / PT;
+    const size_t mirror_stride = (size_t)p.num_pages * p.n_kv * PT;
+    const int pair = e * p.num_streams + p.stream;
+    const int rot = (p.expert_rot[e] + p.stream) % p.world;
+    const int pages_per_stripe = 1 << (log2_stripe - 4);
+    const int runs = (p1 - p0 + 1) * p.n_kv;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < runs; i += gridDim.y * blockDim.x) {
+        const int pi = p0 + i / p.n_kv, head = i % p.n_kv;
+        const int c = pi >> (log2_stripe - 4);                       // stripe of this page
+        const int owner = (rot + c) % p.world;
+        if (owner == p.rank) continue;                               // written in place by the append
+        const int lp = (c / p.world) * pages_per_stripe + (pi & (pages_per_stripe - 1));
+        if (lp >= p.max_pages) continue;
+        const int page = p.page_table[(size_t)pair * p.max_pages + lp];
+        if (page < 0 || page >= p.num_pages) continue;               // the append has raised PIKV_ST_BAD_PAGE
+        const int lo = max(a - pi * PT, 0), hi = min(b - pi * PT, PT);
+        const size_t off = ((size_t)page * p.n_kv + head) * PT;
+        const uint16_t* mk = static_cast<const uint16_t*>(p.mirror_k_scale) + (size_t)owner * mirror_stride + off;
+        const uint16_t* mv = static_cast<const uint16_t*>(p.mirror_v_scale) + (size_t)owner * mirror_stride + off;
+        uint16_t* dk = static_cast<uint16_t*>(p.peer_k_scale[owner]) + off;
+        uint16_t* dv = static_cast<uint16_t*>(p.peer_v_scale[owner]) + off;
+        if (lo == 0 && hi == PT) {
+            const uint4* sk = reinterpret_cast<const uint4*>(mk);
+            const uint4* sv = reinterpret_cast<const uint4*>(mv);
+            reinterpret_cast<uint4*>(dk)[0] = sk[0]; reinterpret_cast<uint4*>(dk)[1] = sk[1];
+            reinterpret_cast<uint4*>(dv)[0] = sv[0]; reinterpret_cast<uint4*>(dv)[1] = sv[1];
+        } else {
+            for (int r = lo; r < hi; ++r) {
+                dk[r] = mk[r];
+                dv[r] = mv[r];
+            }
+        }
+    }
+}
+
+extern "C" int pikv_shard_push_scales_striped(const pikv_striped_push_params* p, pikv_stream_t stream) {
+    PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "push_scales_striped: null params");
+    PIKV_REQUIRE(p->len_before && p->len_after && p->expert_rot && p->page_table && p->mirror_k_scale && p->mirror_v_scale,
+                 PIKV_EINVAL, "push_scales_striped: null pointer");
+    PIKV_REQUIRE(p->world >= 1 && p->world <= 8 && p->rank >= 0 && p->rank < p->world && p->num_experts > 0 &&
+                     p->num_streams > 0 && p->stream >= 0 && p->stream < p->num_streams && p->n_kv > 0 && p->max_pages > 0 &&
+                     p->num_pages > 0,
+                 PIKV_EINVAL, "push_scales_striped: bad sizes");
+    int log2 = -1;
+    for (int b = 4; b < 27; ++b)
+        if ((1 << b) == p->stripe) log2 = b;
+    PIKV_REQUIRE(log2 > 0, PIKV_EINVAL, "push_scales_striped: stripe=%d must be a power of two >= 16", p->stripe);
+    for (int r = 0; r < p->world; ++r)
+        PIKV_REQUIRE(p->peer_k_scale[r] && p->peer_v_scale[r], PIKV_EINVAL, "push_scales_striped: null pool pointer for rank %d", r);
+    if (p->world == 1) return PIKV_OK;
+    dim3 grid(p->num_experts, 4);
+    striped_push_scales_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*p, log2);
+    count_launch(1);
+    return check_launch("striped_push_scales_kernel");
 }
 
 extern "C" int pikv_cache_gather(const int32_t* seq, const int32_t* pos, int32_t n, const int32_t* page_table,

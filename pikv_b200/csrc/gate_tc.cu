@@ -274,10 +274,14 @@ int gate_tc_launch(GateDev& g, cudaStream_t st) {
 
 }  // namespace pikv
 
-// reads and clears the sticky error word of the tensor-core gate kernel
+namespace pikv { int gate_mlp_error_fetch(); }
+
+// reads and clears the sticky error words of the tensor-core gate kernels
 extern "C" int pikv_gate_error_state(void) {
     unsigned v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, pikv::g_gate_tc_error, sizeof(v)) != cudaSuccess) return -1;
     if (v) cudaMemcpyToSymbol(pikv::g_gate_tc_error, &zero, sizeof(zero));
-    return (int)v;
+    const int m = pikv::gate_mlp_error_fetch();
+    if (m < 0) return -1;
+    return (int)v | m;
 }

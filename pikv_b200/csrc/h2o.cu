@@ -22,6 +22,11 @@ constexpr int SEL_THREADS_STREAM = 512;    // keys re-read from memory: small CT
 constexpr int SEL_WARPS = SEL_THREADS / 32;
 constexpr int SEL_SMEM_KEYS = 45056;   // keys staged in shared memory up to this length (with the bitmap, list and buckets: 218 KB)
 
+__device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
+    const uint4 r = ld_stream_16(p);
+    return make_float4(__uint_as_float(r.x), __uint_as_float(r.y), __uint_as_float(r.z), __uint_as_float(r.w));
+}
+
 __device__ __forceinline__ uint32_t order_key(float f) {
     uint32_t b = __float_as_uint(f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -274,13 +279,23 @@ __device__ void select_bucketed(const float* __restrict__ src, int n, int m, uin
     const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
     uint32_t kmin = 0xffffffffu, kmax = 0u;
     if (aligned) {
+        // eight 16-byte loads in flight per thread: with one CTA per SM nothing else hides the latency of a round trip
         const float4* src4 = reinterpret_cast<const float4*>(src);
-        for (int i = tid; i < n / 4; i += NT) {
-            const float4 f = __ldg(src4 + i);
-            const uint4 u = make_uint4(order_key(f.x), order_key(f.y), order_key(f.z), order_key(f.w));
-            reinterpret_cast<uint4*>(keys)[i] = u;
-            kmin = min(min(kmin, u.x), min(u.y, min(u.z, u.w)));
-            kmax = max(max(kmax, u.x), max(u.y, max(u.z, u.w)));
+        const int n4s = n / 4;
+        for (int i0 = tid; i0 < n4s; i0 += 8 * NT) {
+            float4 f[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (i0 + q * NT < n4s) f[q] = ld_stream_f4(src4 + i0 + q * NT);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (i0 + q * NT < n4s) {
+                    const uint4 u = make_uint4(order_key(f[q].x), order_key(f[q].y), order_key(f[q].z), order_key(f[q].w));
+                    reinterpret_cast<uint4*>(keys)[i0 + q * NT] = u;
+                    kmin = min(min(kmin, u.x), min(u.y, min(u.z, u.w)));
+                    kmax = max(max(kmax, u.x), max(u.y, max(u.z, u.w)));
+                }
+            }
         }
     }
     for (int i = (aligned ? 4 * (n / 4) : 0) + tid; i < n; i += NT) {
@@ -311,9 +326,14 @@ __device__ void select_bucketed(const float* __restrict__ src, int n, int m, uin
     // ---- already ascending?  (a thread looks at four neighbouring pairs) ----
     {
         bool ok = true;
-        for (int i = 4 * tid; i < n - 1; i += 4 * NT) {
-            const int e = min(i + 4, n - 1);
-            for (int q = i; q < e; ++q) ok &= keys[q] <= keys[q + 1];
+        const uint4* k4 = reinterpret_cast<const uint4*>(keys);
+        for (int i = tid; 4 * i < n - 1; i += NT) {
+            if (4 * i + 4 < n) {
+                const uint4 u = k4[i];
+                ok &= u.x <= u.y && u.y <= u.z && u.z <= u.w && u.w <= keys[4 * i + 4];
+            } else {
+                for (int q = 4 * i; q < n - 1; ++q) ok &= keys[q] <= keys[q + 1];
+            }
         }
         if (!__all_sync(0xffffffffu, ok) && lane == 0) sh.sorted = 0;
     }
@@ -514,26 +534,53 @@ __global__ void __launch_bounds__(NT) h2o_select_kernel(const float* acc, const 
             select_top_m<STAGED, NT>(t, n, min(num_recent, n), keys, cand, keepw, sh);
         }
     }
-    // outputs: evict mask bytes and ascending kept indices
-    const int tiles = (stride + 31) / 32;
+    // outputs: evict mask bytes and ascending kept indices.  A warp owns a contiguous run of 128-position tiles;
+    // a lane handles four neighbouring positions of a tile (one 4-byte mask store when the row is 4-byte aligned).
+    const int tiles = (stride + 127) / 128;
     const int tiles_per = (tiles + (NT / 32) - 1) / (NT / 32);
     const int t0 = warp * tiles_per, t1 = min(tiles, t0 + tiles_per);
     int cnt = 0;
-    for (int tt = t0; tt < t1; ++tt) cnt += __popc(keepw[tt]);
+    for (int w = 4 * t0 + lane; w < min(4 * t1, words_cap); w += 32) cnt += __popc(keepw[w]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
     if (lane == 0) sh.warp_tot[warp] = cnt;
     __syncthreads();
     int before = 0;
     for (int w = 0; w < warp; ++w) before += sh.warp_tot[w];
+    const bool vec_ok = (stride & 3) == 0 && evict_mask != nullptr && (reinterpret_cast<uintptr_t>(evict_mask) & 3) == 0;
     for (int tt = t0; tt < t1; ++tt) {
-        const uint32_t kb = keepw[tt];
-        const int i = tt * 32 + lane;
-        const bool keep = (kb >> lane) & 1u;
-        if (i < stride && evict_mask) evict_mask[(size_t)seg * stride + i] = keep ? 0 : 1;
-        if (keep && keep_idx) {
-            const int r = before + __popc(kb & ((1u << lane) - 1u));
-            if (r < keep_stride) keep_idx[(size_t)seg * keep_stride + r] = i;
+        const int wi = 4 * tt + (lane >> 3);
+        const uint32_t nib = wi < words_cap ? (keepw[wi] >> (4 * (lane & 7))) & 0xfu : 0u;
+        const int i = tt * 128 + 4 * lane;
+        if (evict_mask) {
+            if (vec_ok && i + 3 < stride) {
+                const uint32_t bytes = ((nib & 1u) ? 0u : 1u) | ((nib & 2u) ? 0u : 0x100u) | ((nib & 4u) ? 0u : 0x10000u) |
+                                       ((nib & 8u) ? 0u : 0x1000000u);
+                *reinterpret_cast<uint32_t*>(evict_mask + (size_t)seg * stride + i) = bytes;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (i + e < stride) evict_mask[(size_t)seg * stride + i + e] = (nib >> e & 1u) ? 0 : 1;
+            }
         }
-        before += __popc(kb);
+        const int c = __popc(nib);
+        int inc = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += v;
+        }
+        if (keep_idx) {
+            int rpos = before + inc - c;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (nib >> e & 1u) {
+                    if (rpos < keep_stride) keep_idx[(size_t)seg * keep_stride + rpos] = i + e;
+                    ++rpos;
+                }
+            }
+        }
+        before += __shfl_sync(0xffffffffu, inc, 31);
     }
     if (tid == 0 && kept_count) {
         int tot = 0;

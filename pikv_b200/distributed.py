@@ -322,8 +322,9 @@ def make_bench_step(dev, rank, world, cfg, w2, b2, synth_inputs, mode: str = "pe
         shards = [PeerShardedKVCache(E, cap, n_kv, dev) for _ in range(lanes)]
         streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)]
         how = f"append kernel stores into the owner GPU's pages over NVLink (peer pointers); {lanes} steps in flight"
-        runs = [[shards[l].prepare(sets[i][0], w2, b2, sets[i][1], sets[i][2], top_k=k, out=outs[i]) for i in range(R)]
-                for l in range(lanes)]
+        split = os.environ.get("PIKV_BENCH_SPLIT", "0") == "1"      # local and remote rows as two launches on two streams
+        runs = [[shards[l].prepare(sets[i][0], w2, b2, sets[i][1], sets[i][2], top_k=k, out=outs[i], split=split)
+                 for i in range(R)] for l in range(lanes)]
 
         import os
         graphs, launches_per_step = None, None

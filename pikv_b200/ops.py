@@ -79,14 +79,25 @@ def gate_fused(act: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = 
                expert_mask: Optional[torch.Tensor] = None, mask_mode: int = _lib.MASK_SINGLE,
                correction: Optional[torch.Tensor] = None, temperature: float = 1.0, renorm_eps: float = 0.0,
                capacity: int = 0, slot_base: Optional[torch.Tensor] = None, want_probs: bool = True,
-               out: Optional[GateResult] = None, phase: int = 0) -> GateResult:
+               out: Optional[GateResult] = None, phase: int = 0, _mlp=None) -> GateResult:
     """Fused gate tail; see pikv_gate_fused in include/pikv_b200.h.
 
     Give either (act [T,H], w2 [E,H], b2 [E]) or logits [T,E] fp32.  phase 1 (scoring kernel only) and
     phase 2 (slot finalisation only, same arguments, ordered after phase 1 by the caller) keep their state
     in out.workspace, which is allocated on first use and must not be shared between batches in flight.
     """
-    if logits is not None:
+    if _mlp is not None:
+        # gate_mlp_fused: act is the net's input x [T,K]; the kernel forms the hidden activations itself
+        x, w1, b1 = _mlp
+        x = _req(x, "x", torch.bfloat16)
+        w1 = _req(w1, "w1", torch.bfloat16)
+        w2 = _req(w2, "w2", torch.bfloat16)
+        T, Kin = x.shape
+        H, E = w1.shape[0], w2.shape[0]
+        if w1.shape[1] != Kin or w2.shape[1] != H:
+            raise PikvError(f"w1 is {tuple(w1.shape)}, w2 {tuple(w2.shape)}: expected [H,{Kin}] and [E,H]")
+        dev, dt, act = x.device, _lib.PIKV_BF16, None
+    elif logits is not None:
         logits = _req(logits, "logits", torch.float32)
         T, E = logits.shape
         H, dev, dt = 0, logits.device, _lib.PIKV_F32
@@ -127,6 +138,8 @@ def gate_fused(act: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = 
     p = GateParams()
     p.act, p.w2, p.b2, p.logits_in = _p(act) if logits is None else None, _p(w2) if logits is None else None, \
         f(b2) if logits is None else None, _p(logits)
+    if _mlp is not None:
+        p.act = None
     p.dtype, p.T, p.H, p.E, p.top_k = dt, T, H, E, top_k
     p.expert_mask = f(expert_mask)
     p.mask_mode = mask_mode if expert_mask is not None else _lib.MASK_NONE
@@ -138,8 +151,19 @@ def gate_fused(act: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = 
     p.probs, p.topk_idx, p.topk_w, p.slot = _p(out.probs), _p(out.topk_idx), _p(out.topk_w), _p(out.slot)
     p.counts_k, p.prob_sum, p.new_len = _p(out.counts_k), _p(out.prob_sum), _p(out.new_len)
     p.workspace, p.workspace_bytes, p.phase = _p(ws), ws.numel(), int(phase)
+    if _mlp is not None:
+        b1f = f(b1)
+        check(lib().pikv_gate_mlp_fused(C.byref(p), _p(x), Kin, _p(w1), b1f, _stream()), "pikv_gate_mlp_fused")
+        return out
     check(lib().pikv_gate_fused(C.byref(p), _stream()), "pikv_gate_fused")
     return out
+
+
+def gate_mlp_fused(x: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torch.Tensor,
+                   b2: Optional[torch.Tensor], **kw) -> GateResult:
+    """The whole gate net on tensor cores: relu(x @ w1.T + b1) @ w2.T + b2, then the tail of gate_fused (same
+    keyword arguments and result); bf16 x [T,K], w1 [H,K], w2 [E,H].  See pikv_gate_mlp_fused."""
+    return gate_fused(None, w2, b2, _mlp=(x, w1, b1), **kw)
 
 
 def dispatch_scatter(g: GateResult, num_experts: int, capacity: int, position_mode: int = 0):

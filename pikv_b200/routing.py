@@ -80,11 +80,26 @@ class BaseRouter(nn.Module):
     def _hidden(self, mlp: nn.Sequential, x2d: torch.Tensor) -> torch.Tensor:
         return F.relu(mlp[0](x2d))
 
+    def _gate_net(self, mlp: nn.Sequential, x2d: torch.Tensor, **kw) -> ops.GateResult:
+        """Gate net + tail.  bf16 inputs: one tensor-core kernel for both layers and the tail (the hidden
+        activations stay on chip).  fp32 inputs (the reference's dtype, 1e-5 parity): the first layer is a torch
+        fp32 GEMM and the kernel takes over from the hidden activations."""
+        if x2d.dtype == torch.bfloat16 and self.num_experts <= 32 and x2d.shape[1] % 8 == 0 and mlp[0].out_features % 8 == 0:
+            k = kw.pop("top_k", None) or self.top_k
+            first, last = mlp[0], mlp[2]
+            g = ops.gate_mlp_fused(x2d, first.weight.detach().to(torch.bfloat16),
+                                   None if first.bias is None else first.bias.detach(),
+                                   last.weight.detach().to(torch.bfloat16), None if last.bias is None else last.bias.detach(),
+                                   top_k=k, mask_mode=self.mask_mode, renorm_eps=self.renorm_eps, **kw)
+            self.last_gate = g
+            return g
+        return self._gate(self._hidden(mlp, x2d), mlp[2], **kw)
+
     def forward(self, hidden_states: torch.Tensor, expert_mask: Optional[torch.Tensor] = None):
         batch_size, seq_len, hidden_size = hidden_states.shape
         x2d = hidden_states.reshape(-1, hidden_size)
         capacity = self._compute_capacity(batch_size, seq_len)
-        g = self._gate(self._hidden(self.router, x2d), self.router[2], expert_mask=expert_mask, capacity=capacity)
+        g = self._gate_net(self.router, x2d, expert_mask=expert_mask, capacity=capacity)
         dispatch, combine = self._dense(g, batch_size, seq_len, max(capacity, 1))
         p_mean = g.prob_sum / float(batch_size * seq_len)
         aux_loss = _aux_base(p_mean, self.num_experts)

@@ -74,6 +74,11 @@ class StripedShardedKVCache:
         self.req_seq, self.req_len, self.req_q = (torch.zeros(n_req, **i32) for _ in range(3))
         self.workspace = torch.empty(lib().pikv_decode_attn_workspace_bytes(n_req, n_q, n_kv, 0, 0), dtype=torch.uint8, device=dev)
         self.wait_limit_us = int(wait_limit_us)
+        # scales of rows stored on other GPUs wait here (same offsets as in the owner's pool) and cross the link 32
+        # bytes at a time after the append, instead of as one 2-byte packet per row
+        entries = num_pages * n_kv * PAGE_TOKENS
+        self.mirror_k = torch.zeros(self.world, entries, dtype=torch.bfloat16, device=dev) if self.world > 1 else None
+        self.mirror_v = torch.zeros(self.world, entries, dtype=torch.bfloat16, device=dev) if self.world > 1 else None
         self._ctx = self._make_ctx()
         self._dec = self._make_decode_params()
         bp = _lib.PeerBarrierParams()
@@ -189,7 +194,21 @@ class StripedShardedKVCache:
         for r in range(self.world):
             sp.peer_k_codes[r], sp.peer_v_codes[r] = self._ptr("k_codes", r), self._ptr("v_codes", r)
             sp.peer_k_scale[r], sp.peer_v_scale[r] = self._ptr("k_scale", r), self._ptr("v_scale", r)
+        if self.mirror_k is not None and token_stream is None:
+            sp.mirror_k_scale, sp.mirror_v_scale = self.mirror_k.data_ptr(), self.mirror_v.data_ptr()
         return sp
+
+    def push_params(self, stream: int, len_before: torch.Tensor, len_after: torch.Tensor):
+        pp = _lib.StripedPushParams()
+        pp.len_before, pp.len_after = len_before.data_ptr(), len_after.data_ptr()
+        pp.expert_rot, pp.expert_cap, pp.page_table = self.expert_rot.data_ptr(), self.expert_cap.data_ptr(), self.page_table.data_ptr()
+        pp.world, pp.rank, pp.stripe = self.world, self.rank, self.layout.stripe
+        pp.num_experts, pp.num_streams, pp.stream = self.layout.num_experts, self.layout.num_streams, int(stream)
+        pp.n_kv, pp.max_pages, pp.num_pages = self.n_kv, self.max_pages, self.num_pages
+        pp.mirror_k_scale, pp.mirror_v_scale = self.mirror_k.data_ptr(), self.mirror_v.data_ptr()
+        for r in range(self.world):
+            pp.peer_k_scale[r], pp.peer_v_scale[r] = self._ptr("k_scale", r), self._ptr("v_scale", r)
+        return pp
 
     def route_append(self, stream: int, k: torch.Tensor, v: torch.Tensor, *, act=None, w2=None, b2=None, logits=None,
                      top_k: Optional[int] = None, out: Optional[ops.GateResult] = None) -> ops.GateResult:
@@ -205,6 +224,9 @@ class StripedShardedKVCache:
         v = ops._req(v, "v", torch.bfloat16)
         sp = self.append_params(k, v, g.topk_idx, g.slot, stream)
         check(lib().pikv_kv_append_striped(C.byref(sp), ops._stream()), "pikv_kv_append_striped")
+        if self.mirror_k is not None:
+            pp = self.push_params(stream, base, g.new_len)
+            check(lib().pikv_shard_push_scales_striped(C.byref(pp), ops._stream()), "pikv_shard_push_scales_striped")
         torch.minimum(g.new_len, self.expert_cap, out=base)          # the pair lengths of this stream after the step
         return g
 
