@@ -466,6 +466,10 @@ typedef struct {
     void* workspace; size_t workspace_bytes;
     uint32_t* status;
     const void* k_zp; const void* v_zp;   /* fp32 zero points, 4-bit asymmetric cache only */
+    /* compact score output for the H2O update (optional; needs lse): f16 exp2(score_log2 - maximum of the softmax
+     * step) [B, n_q, probs_stride] and that maximum for every 16-position page [B, n_q, step_stride] (step_stride
+     * >= ceil(context / 16)); half the bytes of `scores`, consumed by pikv_h2o_accumulate_probs */
+    void* probs16; float* step_max; int32_t probs_stride, step_stride;
 } pikv_decode_params;
 
 size_t pikv_decode_attn_workspace_bytes(int32_t B, int32_t n_q, int32_t n_kv, int32_t max_ctx, int32_t splits);
@@ -541,6 +545,11 @@ int pikv_shard_decode_combine(const pikv_shard_decode_ctx* c, const int32_t* top
 int pikv_h2o_accumulate_attn(const float* scores, int32_t score_stride, const float* lse,
                              const int32_t* seq_len, int32_t B, int32_t n_q, int32_t n_kv,
                              float* acc, int32_t acc_stride, pikv_stream_t stream);
+/* The same increment from the decode kernel's compact output (probs16 / step_max of pikv_decode_params):
+ * acc[b, kvh, pos] += sum over the group's query heads of probs16 * 2^(step_max[pos / 16] - lse / ln 2). */
+int pikv_h2o_accumulate_probs(const void* probs16, int32_t probs_stride, const float* step_max, int32_t step_stride,
+                              const float* lse, const int32_t* seq_len, int32_t B, int32_t n_q, int32_t n_kv,
+                              float* acc, int32_t acc_stride, pikv_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Low-rank projection on tcgen05 tensor cores (bf16 operands, fp32 accumulate

@@ -131,6 +131,7 @@ class DecodeParams(C.Structure):
         ("k_codes", vp), ("v_codes", vp), ("k_scale", vp), ("v_scale", vp),
         ("splits", i32), ("lse", vp), ("scores", vp), ("score_stride", i32),
         ("workspace", vp), ("workspace_bytes", sz), ("status", vp), ("k_zp", vp), ("v_zp", vp),
+        ("probs16", vp), ("step_max", vp), ("probs_stride", i32), ("step_stride", i32),
     ]
 
 
@@ -171,6 +172,7 @@ SIGNATURES = {
     "pikv_decode_attn_q4": (i32, [C.POINTER(DecodeParams), vp]),
     "pikv_decode_attn_static_scratch_bytes": (sz, []),
     "pikv_decode_attn_q8_static": (i32, [C.POINTER(DecodeParams), vp]),
+    "pikv_h2o_accumulate_probs": (i32, [vp, i32, vp, i32, vp, vp, i32, i32, i32, vp, i32, vp]),
     "pikv_h2o_accumulate_attn": (i32, [vp, i32, vp, vp, i32, i32, i32, vp, i32, vp]),
     "pikv_lowrank_project": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "pikv_lowrank_error_state": (i32, []),

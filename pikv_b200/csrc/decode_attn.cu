@@ -29,7 +29,7 @@ constexpr int DA_CTAS_PER_SM = 3;
 constexpr int DA_MAX_GROUP = 8;
 constexpr int DA_MIN_BLOCK = 16;                        // pages per block, at least (more than a ring holds)
 constexpr int DA_ITEMS_PER_WORKER = 8;                  // blocks aimed at per worker of a head, at most
-constexpr int DA_ITEM_PAGES = 64;                       // ... while an item keeps this many pages
+constexpr int DA_ITEM_PAGES = 48;                       // ... while an item keeps this many pages
 constexpr int DA_MAX_REQ = 12000;                       // requests per call: their page prefix is scanned in shared memory
 constexpr int DA_PLAN_THREADS = 1024;
 constexpr int DA_FOLD_STEPS = 8;                        // softmax steps between two folds of the carried bias term
@@ -53,6 +53,9 @@ struct DecodeDev {
     float* lse;
     float* scores;
     int score_stride;
+    __half* probs16;  // [B][n_q][probs_stride] exp2(score - step maximum) as f16, or null
+    float* step_max;  // [B][n_q][step_stride] the step maximum (log2 domain) of every 16-position page
+    int probs_stride, step_stride;
     int* head;        // workspace header: [0] item counter, [1] pages per block, [2] blocks (written by the plan kernel)
     int* prefix;      // [B+1] pages of the requests before each request
     int2* blk_start;  // [max_blocks] (request, page inside it) at which every block starts
@@ -180,7 +183,7 @@ struct DAItem {
     DACursor cur;
 };
 
-// block of page f of the per-head page list: the last block takes the remainder
+// block of page f of the per-head page list
 __device__ __forceinline__ int da_block_of(int f, int blk_pages, int nblocks) { return min(f / blk_pages, nblocks - 1); }
 
 // One CTA: pages before every request (exclusive prefix), the block length, where every block starts; clears
@@ -223,13 +226,13 @@ __global__ void __launch_bounds__(DA_PLAN_THREADS) decode_plan_kernel(DecodeDev 
     __syncthreads();
     const int P = pre[R];
     // blocks per worker of a head: as many as DA_ITEMS_PER_WORKER when that leaves items of DA_ITEM_PAGES pages or
-    // more (long lists: fast and slow SMs even out), down to one for short lists (an item start costs a few
-    // dependent loads)
+    // more (long lists: fast and slow SMs even out), down to two for short lists (an item start costs a few
+    // dependent loads); the last block is the short one
     const int per_head = max(1, d.workers / d.n_kv);
-    const int k_items = max(1, min(DA_ITEMS_PER_WORKER, P / (per_head * DA_ITEM_PAGES)));
+    const int k_items = max(2, min(DA_ITEMS_PER_WORKER, P / (per_head * DA_ITEM_PAGES)));
     const int target = max(1, min(d.max_blocks, k_items * per_head));
     const int blk_pages = max(DA_MIN_BLOCK, (P + target - 1) / target);
-    const int nblocks = P > 0 ? max(1, P / blk_pages) : 0;
+    const int nblocks = (P + blk_pages - 1) / blk_pages;
     if (tid == 0) {
         d.head[0] = 0;
         d.head[1] = blk_pages;
@@ -260,7 +263,6 @@ template <int BITS, bool GS>
 __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel(DecodeDev d) {
     using GEO = DAGeom<BITS>;
     constexpr int STAGES = GEO::STAGES, STAGE_BYTES = GEO::STAGE, PAGE_BYTES = GEO::PAGE, ROW = GEO::ROW;
-    static_assert(DA_MIN_BLOCK > STAGES, "an item must outlast the ring");
     extern __shared__ __align__(128) unsigned char smem[];
     // [warp][stage] rings, the barriers, the P buffers
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)DA_WARPS * STAGES * STAGE_BYTES);
@@ -679,11 +681,20 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
             m1 = mn1;
             float la = 0.f, lb = 0.f, ca = 0.f, cb = 0.f;
             // P' = P * vscale, rounded to f16 as the tensor cores will see it; pbuf is [head][32 positions]
-            auto page_probs = [&](const unsigned char* st, const float (&t)[4], float vw_lo, float vw_hi, int base) {
+            auto page_probs = [&](const unsigned char* st, const float (&t)[4], float vw_lo, float vw_hi, int base, int pos0) {
                 const uint16_t* vsc = reinterpret_cast<const uint16_t*>(st + 2 * PAGE_BYTES + 32);
                 const float vs_lo = __uint_as_float((uint32_t)vsc[r] << 16), vs_hi = __uint_as_float((uint32_t)vsc[r + 8] << 16);
                 if constexpr (GS) {
                     const float p0 = exp2f(t[0] - mu0), p2 = exp2f(t[2] - mu0);
+                    if (d.probs16 && j < G) {
+                        // the H2O update needs exp(score - lse) summed over the heads of the group: lse is known only at
+                        // the end, so the probabilities go out relative to this step's maximum (f16: uniform relative
+                        // precision), with the maximum of every page beside them
+                        const size_t hq = (size_t)c.cur.r * d.n_q + (size_t)c.h * G + j;
+                        if (pos0 + r < c.cur.len && pos0 + r < d.probs_stride) d.probs16[hq * d.probs_stride + pos0 + r] = __float2half_rn(p0);
+                        if (pos0 + r + 8 < c.cur.len && pos0 + r + 8 < d.probs_stride) d.probs16[hq * d.probs_stride + pos0 + r + 8] = __float2half_rn(p2);
+                        if (r == 0 && (pos0 >> 4) < d.step_stride) d.step_max[hq * d.step_stride + (pos0 >> 4)] = mu0;
+                    }
                     la += p0 + p2;
                     const __half h0 = __float2half_rn(p0 * vs_lo), h2 = __float2half_rn(p2 * vs_hi);
                     if (BITS == 8) ca += __half2float(h0) + __half2float(h2);
@@ -693,6 +704,17 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
                     return;
                 }
                 const float p0 = exp2f(t[0] - mu0), p1 = exp2f(t[1] - mu1), p2 = exp2f(t[2] - mu0), p3 = exp2f(t[3] - mu1);
+                if (d.probs16) {
+                    const float pp[4] = {p0, p1, p2, p3};
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int hh = 2 * j + (cc & 1), ps = pos0 + r + 8 * (cc >> 1);
+                        if (hh >= G) continue;
+                        const size_t hq = (size_t)c.cur.r * d.n_q + (size_t)c.h * G + hh;
+                        if (ps < c.cur.len && ps < d.probs_stride) d.probs16[hq * d.probs_stride + ps] = __float2half_rn(pp[cc]);
+                        if (r == 0 && cc < 2 && (pos0 >> 4) < d.step_stride) d.step_max[hq * d.step_stride + (pos0 >> 4)] = (cc & 1) ? mu1 : mu0;
+                    }
+                }
                 la += p0 + p2;
                 lb += p1 + p3;
                 const __half h0 = __float2half_rn(p0 * vs_lo), h1 = __float2half_rn(p1 * vs_lo);
@@ -709,8 +731,8 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
                 pbuf[(2 * j) * 32 + base + r + 8] = h2;
                 pbuf[(2 * j + 1) * 32 + base + r + 8] = h3;
             };
-            page_probs(stA, tA, vwA_lo, vwA_hi, 0);
-            if (two) page_probs(stB, tB, vwB_lo, vwB_hi, 16);
+            page_probs(stA, tA, vwA_lo, vwA_hi, 0, posA);
+            if (two) page_probs(stB, tB, vwB_lo, vwB_hi, 16, posB);
             l0 = l0 * al0 + la;
             l1 = l1 * al1 + lb;
             corr0 = corr0 * al0 + ca;
@@ -916,6 +938,10 @@ int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits
     PIKV_REQUIRE(bits == 8 || (d.k_zp && d.v_zp), PIKV_EINVAL, "decode_attn_q4: the 4-bit cache needs k_zp and v_zp");
     d.lse = p->lse; d.scores = p->scores; d.score_stride = p->score_stride; d.status = p->status;
     PIKV_REQUIRE(d.scores == nullptr || d.score_stride > 0, PIKV_EINVAL, "decode_attn: score_stride");
+    d.probs16 = static_cast<__half*>(p->probs16); d.step_max = p->step_max;
+    d.probs_stride = p->probs_stride; d.step_stride = p->step_stride;
+    PIKV_REQUIRE(d.probs16 == nullptr || (d.step_max != nullptr && d.probs_stride > 0 && d.step_stride > 0 && d.lse != nullptr),
+                 PIKV_EINVAL, "decode_attn: probs16 needs step_max, both strides and lse");
     PIKV_REQUIRE(p->workspace != nullptr, PIKV_EINVAL, "decode_attn: null workspace");
     PIKV_REQUIRE((reinterpret_cast<uintptr_t>(p->workspace) & 15) == 0, PIKV_EINVAL, "decode_attn: workspace must be 16-byte aligned");
     d.workers = da_workers();

@@ -684,6 +684,26 @@ __global__ void h2o_accumulate_attn_kernel(const float* scores, int score_stride
     acc[(size_t)bh * acc_stride + pos] += s;
 }
 
+// the same increment from the decode kernel's compact output: f16 probabilities relative to the maximum of their
+// softmax step, that maximum per 16-position page (log2 domain), and the final log-sum-exp
+__global__ void h2o_accumulate_probs_kernel(const __half* probs, int probs_stride, const float* step_max, int step_stride,
+                                            const float* lse, const int* seq_len, int B, int n_q, int n_kv, float* acc,
+                                            int acc_stride) {
+    const int pos = blockIdx.x * blockDim.x + threadIdx.x;
+    const int bh = blockIdx.y;
+    const int b = bh / n_kv, h = bh % n_kv;
+    const int len = seq_len ? seq_len[b] : probs_stride;
+    if (pos >= len || pos >= acc_stride || pos >= probs_stride || (pos >> 4) >= step_stride) return;
+    const int g = n_q / n_kv;
+    float s = 0.f;
+    for (int i = 0; i < g; ++i) {
+        const size_t hq = (size_t)b * n_q + (size_t)h * g + i;
+        const float lse2 = lse[hq] * 1.4426950408889634f;
+        s += __half2float(probs[hq * probs_stride + pos]) * exp2f(step_max[hq * step_stride + (pos >> 4)] - lse2);
+    }
+    acc[(size_t)bh * acc_stride + pos] += s;
+}
+
 }  // namespace pikv
 
 using namespace pikv;
@@ -771,6 +791,19 @@ extern "C" int pikv_h2o_compact(const pikv_compact_params* p, pikv_stream_t stre
     h2o_compact_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c);
     count_launch(1);
     return check_launch("h2o_compact_kernel");
+}
+
+extern "C" int pikv_h2o_accumulate_probs(const void* probs16, int32_t probs_stride, const float* step_max, int32_t step_stride,
+                                         const float* lse, const int32_t* seq_len, int32_t B, int32_t n_q, int32_t n_kv,
+                                         float* acc, int32_t acc_stride, pikv_stream_t stream) {
+    PIKV_REQUIRE(probs16 && step_max && lse && acc, PIKV_EINVAL, "h2o_accumulate_probs: null pointer");
+    PIKV_REQUIRE(B > 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0 && probs_stride > 0 && step_stride > 0 && acc_stride > 0,
+                 PIKV_EINVAL, "h2o_accumulate_probs: bad sizes");
+    dim3 grid(ceil_div(min(probs_stride, acc_stride), 256), B * n_kv);
+    h2o_accumulate_probs_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(probs16), probs_stride, step_max, step_stride, lse, seq_len, B, n_q, n_kv, acc, acc_stride);
+    count_launch(1);
+    return check_launch("h2o_accumulate_probs_kernel");
 }
 
 extern "C" int pikv_h2o_accumulate_attn(const float* scores, int32_t score_stride, const float* lse,

@@ -222,6 +222,48 @@ class PagedKVCache(torch.nn.Module):
             check(lib().pikv_decode_attn_q4(C.byref(p), _stream()), "pikv_decode_attn_q4")
         return (out, lse) if (want_lse or scores is not None) else out
 
+    def h2o_workspace(self, B: int, n_q: int, max_ctx: Optional[int] = None):
+        """Scratch for decode_attention_h2o: f16 probabilities [B, n_q, ctx] and the step maxima [B, n_q, ctx/16]."""
+        ctx = max_ctx or self.max_pages * PAGE_TOKENS
+        dev = self.k_codes.device
+        return (torch.empty(B, n_q, ctx, dtype=torch.float16, device=dev),
+                torch.empty(B, n_q, (ctx + PAGE_TOKENS - 1) // PAGE_TOKENS, dtype=torch.float32, device=dev))
+
+    def decode_attention_h2o(self, q: torch.Tensor, acc: torch.Tensor, workspace=None, seq_ids: Optional[torch.Tensor] = None,
+                             seq_len: Optional[torch.Tensor] = None):
+        """decode_attention plus the H2O update acc[b * n_kv + h, pos] += sum over the group's query heads of the
+        attention probability (core/single/pikv_moe.py:241-245 column sums fed to
+        core/single/cache_scheduling.py:69-73): the decode kernel leaves f16 probabilities relative to their softmax
+        step, pikv_h2o_accumulate_probs normalises them with the final log-sum-exp.  int8 symmetric caches."""
+        if self.bits != 8 or not self.symmetric:
+            raise PikvError("decode_attention_h2o reads int8 symmetric caches")
+        q = _req(q, "q", torch.bfloat16)
+        acc = _req(acc, "acc", torch.float32)
+        B, n_q, _ = q.shape
+        if workspace is None:
+            workspace = self.h2o_workspace(B, n_q)
+        probs, step_max = workspace
+        if seq_ids is not None:
+            seq_ids = _req(seq_ids, "seq_ids", torch.int32)
+        if seq_len is None:
+            seq_len = self.length if seq_ids is None else self.length[seq_ids.long()]
+        seq_len = _req(seq_len, "seq_len", torch.int32)
+        dev = q.device
+        out = torch.empty_like(q)
+        lse = torch.empty(B, n_q, dtype=torch.float32, device=dev)
+        ws = _workspace(dev, lib().pikv_decode_attn_workspace_bytes(B, n_q, self.n_kv, self.capacity, 0), "dec")
+        p = DecodeParams()
+        p.q, p.out, p.B, p.n_q, p.n_kv = _p(q), _p(out), B, n_q, self.n_kv
+        p.seq_ids, p.seq_len, p.page_table = _p(seq_ids), _p(seq_len), _p(self.page_table)
+        p.num_seqs, p.max_pages, p.num_pages = self.num_seqs, self.max_pages, self.num_pages
+        p.k_codes, p.v_codes, p.k_scale, p.v_scale = _p(self.k_codes), _p(self.v_codes), _p(self.k_scale), _p(self.v_scale)
+        p.lse, p.workspace, p.workspace_bytes, p.status = _p(lse), _p(ws), ws.numel(), _p(self.status)
+        p.probs16, p.step_max, p.probs_stride, p.step_stride = _p(probs), _p(step_max), probs.shape[-1], step_max.shape[-1]
+        check(lib().pikv_decode_attn_q8(C.byref(p), _stream()), "pikv_decode_attn_q8")
+        check(lib().pikv_h2o_accumulate_probs(_p(probs), probs.shape[-1], _p(step_max), step_max.shape[-1], _p(lse), _p(seq_len),
+                                              B, n_q, self.n_kv, _p(acc), acc.shape[-1], _stream()), "pikv_h2o_accumulate_probs")
+        return out
+
     # -- eviction ------------------------------------------------------------------
     def compact_into(self, dst: "PagedKVCache", keep_idx: torch.Tensor, kept_count: torch.Tensor, per_head: bool,
                      src_acc=None, src_ts=None, dst_acc=None, dst_ts=None) -> None:

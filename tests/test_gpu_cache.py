@@ -464,6 +464,27 @@ def test_decode_scores_feed_h2o_accumulate(dev):
     assert np.abs(got.sum(-1) - n_q // n_kv).max() < 1e-3           # probabilities of each query head sum to 1
 
 
+@pytest.mark.parametrize("B,n_q,n_kv,ctx", [(2, 8, 2, 300), (3, 16, 2, 1000), (2, 4, 4, 77)])
+def test_decode_h2o_update_from_compact_probabilities(dev, B, n_q, n_kv, ctx):
+    """The fused H2O update: the decode kernel's f16 probabilities (relative to their softmax step) normalised by
+    pikv_h2o_accumulate_probs equal the oracle's column sums of the attention probabilities within 1e-2 relative
+    (f16 carries 11 bits), and each query head's probabilities still sum to one."""
+    rng = np.random.default_rng(ctx)
+    lens = rng.integers(1, ctx + 1, B).astype(np.int32)
+    lens[0] = ctx
+    cache, kd, vd = fill_stream_cache(dev, B, n_kv, ctx, lens, ctx + 1)
+    q = torch.randn(B, n_q, 128).bfloat16()
+    acc = torch.zeros(B * n_kv, ctx, device=dev)
+    out = cache.decode_attention_h2o(q.to(dev), acc)
+    want_out, psum = O.decode_attention(q.float().numpy(), kd, vd, lens)
+    got = acc.cpu().numpy().reshape(B, n_kv, ctx)
+    assert np.abs(got - psum).max() <= 1e-2 * max(psum.max(), 1e-6)
+    assert np.abs(got.sum(-1) - n_q // n_kv).max() < 2e-3
+    assert np.abs(out.float().cpu().numpy() - want_out).max() <= 1e-2 * np.abs(want_out).max()
+    cache.decode_attention_h2o(q.to(dev), acc)                  # accumulates
+    assert np.abs(acc.cpu().numpy().reshape(B, n_kv, ctx) - 2 * psum).max() <= 2e-2 * max(psum.max(), 1e-6)
+
+
 # ---------------------------------------------------------------- compaction
 @pytest.mark.parametrize("per_head", [True, False])
 def test_h2o_compact_moves_rows_and_scores(dev, per_head):

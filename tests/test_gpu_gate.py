@@ -340,14 +340,19 @@ def test_gate_mlp_fused_matches_oracle(dev, T, K, H, E, k):
     gi = res.topk_idx.cpu().numpy()
     diff = (gi != idx).any(axis=1)
     # the hidden activations are rounded to bf16 after an fp32 sum in another order: a rounding flip moves a logit by
-    # up to ~1e-3, so "near-tie" is judged on that scale
-    assert (O.topk_margin(probs, k)[diff] < 2e-2).all() and diff.sum() <= max(2, T // 50), int(diff.sum())
+    # up to ~1e-3, so "near-tie" is judged on that scale, between any two neighbours of the sorted top k+1 (a flip
+    # of the first two choices is a mismatch of the ordered index pair too)
+    srt = -np.sort(-probs, axis=1)[:, : k + 1]
+    gap = ((srt[:, :-1] - srt[:, 1:]) / np.maximum(srt[:, :-1], 1e-30)).min(axis=1)
+    assert (gap[diff] < 2e-2).all() and diff.sum() <= max(2, T // 50), int(diff.sum())
     assert np.abs(res.probs.cpu().numpy() - probs).max() < 1e-2
     slot, counts_k = O.slot_assign_fast(gi, E, cap)
     np.testing.assert_array_equal(res.slot.cpu().numpy(), slot)
     np.testing.assert_array_equal(res.counts_k.cpu().numpy(), counts_k)
     np.testing.assert_array_equal(res.new_len.cpu().numpy(), np.minimum(counts_k.sum(0), cap))
     assert abs(float(res.prob_sum.sum()) - T) < 1e-2 * T
+    again = ops.gate_mlp_fused(x.to(dev), w1.to(dev), b1.to(dev), w2.to(dev), b2.to(dev), top_k=k, capacity=cap)
+    assert torch.equal(again.probs, res.probs) and torch.equal(again.slot, res.slot)      # run-to-run identical bits
 
 
 def test_base_router_bf16_uses_fused_gate_net(dev):
