@@ -794,11 +794,11 @@ def other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, gpu_index, single_
             ts = torch.arange(ctx, dtype=torch.float32, device=dev).repeat(B * n_kv, 1)
             acc[:, ctx - 256:] = -1.0       # the recent window holds no heavy hitter: every segment keeps exactly 2048
             ms, n, cl = measure(lambda: ops.h2o_select(acc, ts, 1792, 256, as_bool=False))
-            record("h2o_select", ms, n, cl, 2 * 4 * ctx * B * n_kv + B * n_kv * (ctx + 2048 * 4), "h2o_select_kernel",
+            record("h2o_select", ms, n, cl, 2 * 4 * ctx * B * n_kv + B * n_kv * (ctx + 2048 * 4), "h2o_select_stream_kernel",
                    segments=B * n_kv, length=ctx, heavy=1792, recent=256)
             _, keep, cnt = ops.h2o_select(acc, ts, 1792, 256, as_bool=False)
             dst = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)      # same page-table width as the source
-            dacc, dts = torch.zeros(B * n_kv, 2048, device=dev), torch.zeros(B * n_kv, 2048, device=dev)
+            dacc, dts = torch.zeros(B * n_kv, keep.shape[1], device=dev), torch.zeros(B * n_kv, keep.shape[1], device=dev)
             ms, n, cl = measure(lambda: cache.compact_into(dst, keep, cnt, True, acc, ts, dacc, dts))
             record("h2o_compact", ms, n, cl, 2 * B * n_kv * 2048 * (2 * 128 + 2 * 2 + 4 + 4), "h2o_compact_kernel",
                    segments=B * n_kv, kept=2048)
@@ -1146,7 +1146,7 @@ def secondary_arm(args):
         by_sel = 2 * 4 * ctx * B * n_kv + B * n_kv * (ctx + 2048 * 4)
         emit("h2o_select_GBps", "GB/s", by_sel / (ms_sel * 1e-3) / 1e9, ms_sel,
              {"workload": "H2O segmented top-k", "segments": B * n_kv, "length": ctx, "heavy": 1792, "recent": 256},
-             {"bound": "hbm", "kernel": "h2o_select_kernel", "achieved": by_sel / (ms_sel * 1e-3) / 1e9, "peak": peak,
+             {"bound": "hbm", "kernel": "h2o_select_stream_kernel", "achieved": by_sel / (ms_sel * 1e-3) / 1e9, "peak": peak,
               "peak_source": peak_src, "unit": "GB/s", "frac": by_sel / (ms_sel * 1e-3) / 1e9 / peak, "traffic": None}, steps)
         # compaction of the kept rows (codes, scales, scores) and the decode step over the 2048-token budget
         if args.bits == 8 and ctx >= 2048:

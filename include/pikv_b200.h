@@ -413,8 +413,9 @@ int pikv_h2o_select(const float* acc, const float* ts, int32_t segments, int32_t
                     uint8_t* evict_mask, int32_t* keep_idx, int32_t keep_stride, int32_t* kept_count,
                     pikv_stream_t stream);
 
-/* Testing aid: which select routine pikv_h2o_select runs (all give identical results).  0 (default): by
- * segment length; 1: radix select on keys staged in shared memory; 2: radix select re-reading the scores. */
+/* Testing aid: which select routine pikv_h2o_select runs (all give identical results).  0 (default): the
+ * streaming select (threads own 32-position words, scores re-read from L2, bucket narrowing); 1: radix select on
+ * keys staged in shared memory; 2: radix select re-reading the scores; 3: bucketed select on staged keys. */
 int pikv_h2o_select_variant(int32_t variant);
 
 typedef struct {
@@ -428,8 +429,10 @@ typedef struct {
     void* dst_k_codes; void* dst_v_codes; void* dst_k_scale; void* dst_v_scale;
     void* dst_k_zp; void* dst_v_zp;
     const float* src_acc; const float* src_ts;   /* [segments, score_stride] or NULL */
-    float* dst_acc; float* dst_ts;
+    float* dst_acc; float* dst_ts;               /* [segments, dst_score_stride] or NULL: the kept positions' values,
+                                                    at 0 .. kept - 1 of every row                                */
     int32_t score_stride;
+    int32_t dst_score_stride;                    /* 0: same as score_stride; otherwise at least keep_stride   */
     uint32_t* status;
 } pikv_compact_params;
 

@@ -119,7 +119,7 @@ class CompactParams(C.Structure):
         ("dst_k_codes", vp), ("dst_v_codes", vp), ("dst_k_scale", vp), ("dst_v_scale", vp),
         ("dst_k_zp", vp), ("dst_v_zp", vp),
         ("src_acc", vp), ("src_ts", vp), ("dst_acc", vp), ("dst_ts", vp), ("score_stride", i32),
-        ("status", vp),
+        ("dst_score_stride", i32), ("status", vp),
     ]
 
 

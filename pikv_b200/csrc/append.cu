@@ -177,8 +177,12 @@ __device__ __forceinline__ void kv_append_body(const AppendDev& a) {
     int pg0[TOPK], pg1[TOPK];
     typename GQ::Raw k0, v0, k1, v1;
     // prologue: the loads that need nothing from the gate go out first
+    if (any) append_stage_kv<TIn, BITS, SYM>(a, pair, total, sub, k0, v0);
+    // MODE 2 is launched as a programmatic dependent of the gate kernel: its CTAs may become resident, and their
+    // first K/V loads go out, while the gate is still running; everything the gate writes is read after this wait
+    // (which returns at once when the launch carried no such dependency)
+    if (MODE == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (any) {
-        append_stage_kv<TIn, BITS, SYM>(a, pair, total, sub, k0, v0);
         append_stage_route<TOPK>(a, pair, total, r0);
         append_stage_route<TOPK>(a, pair + stride, total, r1);
     }
@@ -562,10 +566,24 @@ extern "C" int pikv_route_append(const pikv_gate_params* gp, const pikv_append_p
     const long long lanes = (long long)a.T * a.n_kv * 8;
     long long want = ceil_div64(lanes, APPEND_THREADS), cap_ctas = (long long)sm_count() * 3;
     const int grid = (int)(want < cap_ctas ? want : cap_ctas);
-    if (a.top_k <= 1) kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, 2><<<grid, APPEND_THREADS, smem, st>>>(a);
-    else if (a.top_k <= 2) kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, 2><<<grid, APPEND_THREADS, smem, st>>>(a);
-    else if (a.top_k <= 4) kv_append_quant_kernel<__nv_bfloat16, 8, true, 4, 2><<<grid, APPEND_THREADS, smem, st>>>(a);
-    else kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, 2><<<grid, APPEND_THREADS, smem, st>>>(a);
+    // programmatic dependent launch: the append CTAs are scheduled as soon as every gate CTA has started (the gate
+    // kernel signals that at its top), so the launch latency and the first loads overlap the gate's tail
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(APPEND_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le;
+    if (a.top_k <= 1) le = cudaLaunchKernelEx(&cfg, kv_append_quant_kernel<__nv_bfloat16, 8, true, 1, 2>, a);
+    else if (a.top_k <= 2) le = cudaLaunchKernelEx(&cfg, kv_append_quant_kernel<__nv_bfloat16, 8, true, 2, 2>, a);
+    else if (a.top_k <= 4) le = cudaLaunchKernelEx(&cfg, kv_append_quant_kernel<__nv_bfloat16, 8, true, 4, 2>, a);
+    else le = cudaLaunchKernelEx(&cfg, kv_append_quant_kernel<__nv_bfloat16, 8, true, 8, 2>, a);
+    (void)le;                      // reported by check_launch
     count_launch(1);
     return check_launch("kv_append_quant_kernel (fused with the gate)");
 }

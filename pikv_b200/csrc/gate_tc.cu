@@ -89,6 +89,9 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
+    // a kernel launched as a programmatic dependent of this one (the fused append) may be scheduled from here on;
+    // it waits for this grid's completion before it reads anything written here
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {

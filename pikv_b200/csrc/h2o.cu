@@ -28,8 +28,9 @@ __device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
 }
 
 __device__ __forceinline__ uint32_t order_key(float f) {
-    uint32_t b = __float_as_uint(f);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    // negative floats: all bits flipped; the others: sign bit set (an arithmetic shift and one three-input logic op)
+    const uint32_t b = __float_as_uint(f);
+    return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);
 }
 
 constexpr int SEL_BUCKETS = 4096;      // first-level buckets of the bucketed path (4 per thread)
@@ -589,6 +590,452 @@ __global__ void __launch_bounds__(NT) h2o_select_kernel(const float* acc, const 
     }
 }
 
+// ---- streaming select ---------------------------------------------------------------------------------
+// The default select.  The scores are never staged as a whole: every pass re-reads them (after the first pass
+// from L2) with coalesced 16-byte loads.  Per score array the m-th largest key and the number of keys equal to
+// it that are kept (lowest indices first) are found first:
+//   pass 1  smallest and largest key, and whether the keys are already ascending (timestamps of an append-only
+//           cache): then the m largest are the tail of the segment and no search is needed;
+//   pass 2  histogram over 4096 buckets of 2^s consecutive key values above the smallest key (s chosen so that
+//           the largest key falls into the last buckets); the bucket holding the m-th largest key is found from
+//           suffix sums;
+//   pass 3  the keys of that bucket are listed in shared memory (a few dozen for smooth score distributions) and
+//           the bucket is narrowed on the list, 12 bits at a time, down to one key value.  A bucket with more
+//           keys than the list holds is narrowed by another pass 2 over the segment instead.
+// In the last pass a thread owns whole 32-position words of the segment (a warp's 32 words are loaded coalesced
+// and transposed through a swizzled 4 KiB tile of shared memory), so every decision about a position is a bit of
+// a register word: ties are resolved with a block-wide count of the equal keys in index order (skipped when all
+// of them are kept), and the evict mask and the ascending kept-index list need no atomics and no bit gathering
+// across lanes.  Small CTAs, four per SM: the segments of an SM overlap each other's barriers and load latencies.
+constexpr int SS_THREADS = 256;
+constexpr int SS_BUCKETS = 4096;
+constexpr int SS_LIST_CAP = 1024;
+constexpr int SS_BPT = SS_BUCKETS / SS_THREADS;     // buckets a thread owns in the suffix sums
+
+struct SsResult {
+    int mode;            // 0: nothing kept, 1: every position, 2: positions >= lo, 3: keys above kth + need_eq keys equal to it
+    uint32_t kth;
+    int need_eq, all_eq, lo;
+};
+
+struct SsShared {
+    uint4 tile[SS_THREADS / 32][256];               // per warp: 32 words x 8 chunks of 16 bytes, chunk c of word r at c ^ (r & 7)
+    int hist[SS_BUCKETS];
+    uint32_t list[SS_LIST_CAP];
+    uint32_t red_a[SS_THREADS / 32], red_b[SS_THREADS / 32];
+    int red_i[SS_THREADS / 32];
+    int list_n, bucket, above, bucket_cnt, sorted, need_count;
+    uint32_t kmin, kmax;
+    SsResult res[2];
+};
+
+__device__ __forceinline__ uint4 ss_keys4(const float4 f) {
+    return make_uint4(order_key(f.x), order_key(f.y), order_key(f.z), order_key(f.w));
+}
+
+// one(key) for every key of src[0..n), in no particular order; four 16-byte loads in flight per thread
+template <int NT, class F>
+__device__ __forceinline__ void ss_for_keys(const float* __restrict__ src, int n, bool aligned, F&& one) {
+    if (aligned) {
+        const float4* src4 = reinterpret_cast<const float4*>(src);
+        const int n4 = n >> 2;
+        int i0 = threadIdx.x;
+        for (; i0 + 7 * NT < n4; i0 += 8 * NT) {                  // eight loads in flight, no bounds checks
+            float4 f[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) f[u] = __ldg(src4 + i0 + u * NT);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint4 k = ss_keys4(f[u]);
+                one(k.x); one(k.y); one(k.z); one(k.w);
+            }
+        }
+        for (; i0 < n4; i0 += NT) {
+            const uint4 k = ss_keys4(__ldg(src4 + i0));
+            one(k.x); one(k.y); one(k.z); one(k.w);
+        }
+        for (int i = 4 * n4 + threadIdx.x; i < n; i += NT) one(order_key(__ldg(src + i)));
+    } else {
+        for (int i = threadIdx.x; i < n; i += NT) one(order_key(__ldg(src + i)));
+    }
+}
+
+// exclusive prefix of v over the CTA in thread order, and the total; red: NT / 32 ints of shared memory
+template <int NT>
+__device__ __forceinline__ int ss_block_scan(int v, int* red, int& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int x = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += x;
+    }
+    if (lane == 31) red[warp] = inc;
+    __syncthreads();
+    int before = 0, tot = 0;
+#pragma unroll
+    for (int q = 0; q < NT / 32; ++q) {
+        const int x = red[q];
+        before += q < warp ? x : 0;
+        tot += x;
+    }
+    __syncthreads();
+    total = tot;
+    return before + inc - v;
+}
+
+// bucket holding the rem-th largest counted key: suffix sums over hist, thread t owns buckets [t * SS_BPT, ...)
+template <int NT>
+__device__ __forceinline__ void ss_pick_bucket(SsShared& sh, int rem) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int c[SS_BPT], sum = 0;
+#pragma unroll
+    for (int q = 0; q < SS_BPT / 4; ++q) {
+        const int4 v = reinterpret_cast<const int4*>(sh.hist)[tid * (SS_BPT / 4) + q];
+        c[4 * q] = v.x; c[4 * q + 1] = v.y; c[4 * q + 2] = v.z; c[4 * q + 3] = v.w;
+        sum += v.x + v.y + v.z + v.w;
+    }
+    int suffix = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(0xffffffffu, suffix, o);
+        if (lane + o < 32) suffix += v;
+    }
+    if (lane == 0) sh.red_i[warp] = suffix;
+    if (tid == 0) sh.bucket = -1;
+    __syncthreads();
+    int cum = suffix - sum;
+    for (int q = warp + 1; q < NT / 32; ++q) cum += sh.red_i[q];
+#pragma unroll
+    for (int b = SS_BPT - 1; b >= 0; --b) {
+        if (cum < rem && rem <= cum + c[b]) {
+            sh.bucket = tid * SS_BPT + b;
+            sh.above = cum;
+            sh.bucket_cnt = c[b];
+        }
+        cum += c[b];
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int ss_shift_for(uint32_t width) {      // (width >> s) < SS_BUCKETS
+    return max(0, (32 - __clz(width)) - 12);
+}
+
+// Where the m largest of src[0..n) are, ties to the lowest index: fills *out (shared memory) for the last pass.
+template <int NT>
+__device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligned, SsShared& sh, SsResult* out) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (m <= 0 || m >= n) {
+        if (tid == 0) out->mode = m <= 0 ? 0 : 1;
+        __syncthreads();
+        return;
+    }
+    // ---- pass 1: smallest, largest, ascending? ----
+    {
+        uint32_t mn = 0xffffffffu, mx = 0u;
+        bool ok = true;
+        if (aligned) {
+            const float4* src4 = reinterpret_cast<const float4*>(src);
+            const int n4 = n >> 2;
+            for (int i0 = 0; i0 < n4; i0 += 4 * NT) {            // the same trip count in every thread (shuffles inside)
+                float4 f[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * NT + tid;
+                    f[u] = i < n4 ? __ldg(src4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * NT + tid;
+                    const bool on = i < n4;
+                    const uint4 k = ss_keys4(f[u]);
+                    uint32_t next = __shfl_down_sync(0xffffffffu, k.x, 1);          // the key after this thread's four
+                    const bool has_next = 4 * i + 4 < n;
+                    if (on && has_next && (lane == 31 || i + 1 >= n4)) next = order_key(__ldg(src + 4 * (size_t)i + 4));
+                    if (on) {
+                        mn = min(mn, min(min(k.x, k.y), min(k.z, k.w)));
+                        mx = max(mx, max(max(k.x, k.y), max(k.z, k.w)));
+                        ok &= k.x <= k.y && k.y <= k.z && k.z <= k.w && (!has_next || k.w <= next);
+                    }
+                }
+            }
+            if (tid == 0) {                                       // the last n % 4 keys
+                for (int i = 4 * n4; i < n; ++i) {
+                    const uint32_t u = order_key(__ldg(src + i));
+                    mn = min(mn, u);
+                    mx = max(mx, u);
+                    if (i + 1 < n) ok &= u <= order_key(__ldg(src + i + 1));
+                }
+            }
+        } else {
+            for (int i = tid; i < n; i += NT) {
+                const uint32_t u = order_key(__ldg(src + i));
+                mn = min(mn, u);
+                mx = max(mx, u);
+                if (i + 1 < n) ok &= u <= order_key(__ldg(src + i + 1));
+            }
+        }
+        mn = __reduce_min_sync(0xffffffffu, mn);
+        mx = __reduce_max_sync(0xffffffffu, mx);
+        const bool all_ok = __all_sync(0xffffffffu, ok);
+        if (lane == 0) {
+            sh.red_a[warp] = mn;
+            sh.red_b[warp] = mx;
+            sh.red_i[warp] = all_ok ? 1 : 0;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t lo = 0xffffffffu, hi = 0u;
+            int so = 1;
+            for (int q = 0; q < NT / 32; ++q) {
+                lo = min(lo, sh.red_a[q]);
+                hi = max(hi, sh.red_b[q]);
+                so &= sh.red_i[q];
+            }
+            sh.kmin = lo;
+            sh.kmax = hi;
+            sh.sorted = so;
+            sh.need_count = 0;
+            if (so || lo == hi) {
+                // ascending keys: the m largest are the tail; of a run of equal keys across the cut the lowest indices stay
+                const uint32_t kth = order_key(src[n - m]);
+                if (order_key(src[n - m - 1]) != kth) {
+                    out->mode = 2;
+                    out->lo = n - m;
+                } else {
+                    out->mode = 3;
+                    out->kth = kth;
+                    out->all_eq = 0;
+                    out->need_eq = m;                    // all keys equal; otherwise m minus the keys above kth (counted below)
+                    sh.need_count = lo != hi;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (sh.sorted || sh.kmin == sh.kmax) {
+        if (sh.need_count) {
+            const uint32_t kth = out->kth;
+            int gt = 0;
+            ss_for_keys<NT>(src, n, aligned, [&](uint32_t u) { gt += u > kth ? 1 : 0; });
+            int total;
+            (void)ss_block_scan<NT>(gt, sh.red_i, total);
+            if (tid == 0) out->need_eq = m - total;
+            __syncthreads();
+        }
+        return;
+    }
+    // ---- passes 2 and 3: narrow [lo, lo + width] around the m-th largest key ----
+    // The first histogram covers only the top 2^27 key values below the largest key (sixteen binades of positive
+    // scores): a few low outliers must not widen the buckets of the range the m-th largest key lives in.  If fewer
+    // than m keys fall into it (a far outlier at the top), the whole key range is taken instead.
+    uint32_t lo = sh.kmin, width = sh.kmax - sh.kmin;
+    bool clamped = width > 0x07ffffffu;
+    if (clamped) {
+        lo = sh.kmax - 0x07ffffffu;
+        width = 0x07ffffffu;
+    }
+    int rem = m;
+    bool on_list = false;
+    int list_n = 0;
+    while (true) {
+        const int s = ss_shift_for(width);
+        for (int i = tid; i < SS_BUCKETS; i += NT) sh.hist[i] = 0;
+        __syncthreads();
+        if (on_list) {
+            for (int i = tid; i < list_n; i += NT) {
+                const uint32_t d = sh.list[i] - lo;
+                if (d <= width) atomicAdd(&sh.hist[d >> s], 1);
+            }
+        } else {
+            ss_for_keys<NT>(src, n, aligned, [&](uint32_t u) {
+                const uint32_t d = u - lo;
+                if (d <= width) atomicAdd(&sh.hist[d >> s], 1);
+            });
+        }
+        __syncthreads();
+        ss_pick_bucket<NT>(sh, rem);
+        const int b = sh.bucket, cnt = sh.bucket_cnt;
+        if (b < 0) {
+            if (clamped) {                             // fewer than m keys in the clamped range
+                clamped = false;
+                lo = sh.kmin;
+                width = sh.kmax - sh.kmin;
+                __syncthreads();
+                continue;
+            }
+            if (tid == 0) out->mode = 0;               // cannot happen for 1 <= rem <= keys in range
+            __syncthreads();
+            return;
+        }
+        clamped = false;
+        rem -= sh.above;
+        const uint32_t nlo = lo + ((uint32_t)b << s);
+        const uint32_t span = s > 0 ? ((1u << s) - 1u) : 0u;
+        width = min(lo + width - nlo, span);
+        lo = nlo;
+        if (s == 0) {
+            if (tid == 0) {
+                out->mode = 3;
+                out->kth = lo;
+                out->need_eq = rem;
+                out->all_eq = rem == cnt;
+            }
+            __syncthreads();
+            return;
+        }
+        if (!on_list && cnt <= SS_LIST_CAP) {
+            if (tid == 0) sh.list_n = 0;
+            __syncthreads();
+            ss_for_keys<NT>(src, n, aligned, [&](uint32_t u) {
+                if (u - lo <= width) {
+                    const int at = atomicAdd(&sh.list_n, 1);
+                    if (at < SS_LIST_CAP) sh.list[at] = u;
+                }
+            });
+            __syncthreads();
+            list_n = min(sh.list_n, SS_LIST_CAP);
+            on_list = true;
+        }
+        __syncthreads();
+    }
+}
+
+// gt / eq words of word w for one array's result.  The warp's 32 words start at word wb; `tile` is the warp's
+// staging tile.  All lanes of the warp call this together (mode 3 synchronises the warp).
+template <int NT>
+__device__ __forceinline__ void ss_word_bits(const SsResult& r, const float* __restrict__ src, int w, int wb, int n, bool aligned,
+                                             uint32_t valid, uint4* tile, uint32_t& gt, uint32_t& eq) {
+    const int lane = threadIdx.x & 31;
+    gt = 0u;
+    eq = 0u;
+    if (r.mode == 1) {
+        gt = valid;
+    } else if (r.mode == 2) {
+        const int a = r.lo - 32 * w;                   // first kept bit of this word
+        gt = a <= 0 ? valid : (a >= 32 ? 0u : (valid & ~((1u << a) - 1u)));
+    } else if (r.mode == 3) {
+        uint32_t k[32];
+        if (aligned && 32 * wb + 1024 <= n) {
+            // the warp's 32 words: eight coalesced loads, swizzled tile, one word per lane
+            const float4* src4 = reinterpret_cast<const float4*>(src) + 8 * (size_t)wb;
+            float4 f[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) f[q] = __ldg(src4 + q * 32 + lane);
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int row = 4 * q + (lane >> 3), c = lane & 7;
+                tile[row * 8 + (c ^ (row & 7))] = ss_keys4(f[q]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint4 u = tile[lane * 8 + (c ^ (lane & 7))];
+                k[4 * c] = u.x; k[4 * c + 1] = u.y; k[4 * c + 2] = u.z; k[4 * c + 3] = u.w;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) k[e] = (valid >> e & 1u) ? order_key(__ldg(src + 32 * (size_t)w + e)) : 0u;
+        }
+        const uint32_t kth = r.kth;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+            gt |= (k[e] > kth ? 1u : 0u) << e;
+            eq |= (k[e] == kth ? 1u : 0u) << e;
+        }
+        gt &= valid;
+        eq &= valid;
+    }
+}
+
+__device__ __forceinline__ uint32_t ss_lowest_bits(uint32_t word, int cnt) {      // the cnt lowest set bits of word
+    if (cnt <= 0) return 0u;
+    if (cnt >= __popc(word)) return word;
+    uint32_t r = 0u;
+    for (int i = 0; i < cnt; ++i) {
+        const uint32_t b = word & (0u - word);
+        r |= b;
+        word ^= b;
+    }
+    return r;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(NT, 1024 / NT) h2o_select_stream_kernel(const float* acc, const float* ts, int stride,
+                                                                           const int* seg_len, int n_all, int num_heavy,
+                                                                           int num_recent, uint8_t* evict_mask, int* keep_idx,
+                                                                           int keep_stride, int* kept_count) {
+    extern __shared__ __align__(16) unsigned char ss_raw[];
+    SsShared& sh = *reinterpret_cast<SsShared*>(ss_raw);
+    const int seg = blockIdx.x, tid = threadIdx.x, warp = tid >> 5;
+    int n = seg_len ? seg_len[seg] : n_all;
+    n = max(0, min(n, stride));
+    const float* a = acc + (size_t)seg * stride;
+    const float* t = ts + (size_t)seg * stride;
+    const bool al_a = (reinterpret_cast<uintptr_t>(a) & 15) == 0, al_t = (reinterpret_cast<uintptr_t>(t) & 15) == 0;
+    ss_find<NT>(a, n, min(num_heavy, n), al_a, sh, &sh.res[0]);
+    ss_find<NT>(t, n, min(num_recent, n), al_t, sh, &sh.res[1]);
+    __syncthreads();
+    const SsResult ra = sh.res[0], rt = sh.res[1];
+    const bool ties_a = ra.mode == 3 && !ra.all_eq, ties_t = rt.mode == 3 && !rt.all_eq;
+    uint8_t* mrow = evict_mask ? evict_mask + (size_t)seg * stride : nullptr;
+    const bool mask_vec = mrow != nullptr && (reinterpret_cast<uintptr_t>(mrow) & 15) == 0;
+    int* krow = keep_idx ? keep_idx + (size_t)seg * keep_stride : nullptr;
+    const int words_cap = (stride + 31) >> 5;
+    int eq_a_before = 0, eq_t_before = 0, kept_before = 0;
+    for (int w0 = 0; w0 < words_cap; w0 += NT) {
+        const int w = w0 + tid, wb = w0 + 32 * warp;
+        const int left = n - 32 * w;
+        const uint32_t valid = (w >= words_cap || left <= 0) ? 0u : (left >= 32 ? 0xffffffffu : ((1u << left) - 1u));
+        uint32_t gta, eqa, gtt, eqt;
+        ss_word_bits<NT>(ra, a, w, wb, n, al_a, valid, sh.tile[warp], gta, eqa);
+        ss_word_bits<NT>(rt, t, w, wb, n, al_t, valid, sh.tile[warp], gtt, eqt);
+        uint32_t keep = gta | gtt;
+        if (ties_a || ties_t) {
+            // equal keys in index order: packed counts of both arrays (a chunk holds at most 32 * NT < 65536 positions)
+            int total;
+            const int packed = (ties_a ? __popc(eqa) : 0) | ((ties_t ? __popc(eqt) : 0) << 16);
+            const int before = ss_block_scan<NT>(packed, sh.red_i, total);
+            keep |= ties_a ? ss_lowest_bits(eqa, ra.need_eq - (eq_a_before + (before & 0xffff))) : eqa;
+            keep |= ties_t ? ss_lowest_bits(eqt, rt.need_eq - (eq_t_before + (before >> 16))) : eqt;
+            eq_a_before += total & 0xffff;
+            eq_t_before += total >> 16;
+        } else {
+            keep |= eqa | eqt;
+        }
+        int total;
+        int rpos = kept_before + ss_block_scan<NT>(__popc(keep), sh.red_i, total);
+        kept_before += total;
+        if (w < words_cap) {
+            if (mrow) {
+                const uint32_t ev = ~keep;
+                if (mask_vec && (stride & 15) == 0 && 32 * w + 32 <= stride) {
+                    uint32_t by[8];
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) by[g] = (((ev >> (4 * g)) & 0xfu) * 0x00204081u) & 0x01010101u;
+                    uint4* mp = reinterpret_cast<uint4*>(mrow + 32 * (size_t)w);
+                    mp[0] = make_uint4(by[0], by[1], by[2], by[3]);
+                    mp[1] = make_uint4(by[4], by[5], by[6], by[7]);
+                } else {
+                    for (int e = 0; e < 32 && 32 * w + e < stride; ++e) mrow[32 * (size_t)w + e] = (ev >> e) & 1u;
+                }
+            }
+            if (krow) {
+                uint32_t bits = keep;
+                while (bits) {
+                    const int e = __ffs(bits) - 1;
+                    bits &= bits - 1u;
+                    if (rpos < keep_stride) krow[rpos] = 32 * w + e;
+                    ++rpos;
+                }
+            }
+        }
+    }
+    if (tid == 0 && kept_count) kept_count[seg] = kept_before;
+}
+
 __global__ void h2o_accumulate_kernel(float* acc, float* ts, int n, const int* idx, const float* w, int m, float now,
                                       unsigned* status) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -612,58 +1059,98 @@ struct CompactDev {
     int heads_per;   // heads moved per segment
 };
 
-__global__ void __launch_bounds__(256) h2o_compact_kernel(CompactDev c) {
+// Eight lanes move one row (16 bytes each of K and of V).  A group handles COMPACT_ITEMS rows with every stage of
+// the dependent chain (kept index -> page ids -> row) issued for all of them before the next stage: four times
+// the loads in flight of one row per group, which is what a gather of scattered 128-byte rows needs to keep HBM busy.
+constexpr int COMPACT_ITEMS = 4;
+
+__global__ void __launch_bounds__(256, 4) h2o_compact_kernel(CompactDev c) {
     const pikv_compact_params& p = c.p;
     const int seg = blockIdx.x;
     const int sub = threadIdx.x & 7;
-    const int item = (blockIdx.y * blockDim.x + threadIdx.x) >> 3;   // (row j, head slot)
     const int kept = min(p.kept_count[seg], p.keep_stride);
-    const int j = item / c.heads_per, hs = item % c.heads_per;
-    if (j >= kept) return;
     const int seq = p.per_head ? seg / p.n_kv : seg;
-    const int head = p.per_head ? seg % p.n_kv : hs;
-    const int spos = p.keep_idx[(size_t)seg * p.keep_stride + j];
-    const int dpos = j;
     constexpr int PTK = PIKV_PAGE_TOKENS;
-    if (seq >= p.num_seqs || spos < 0 || spos / PTK >= p.max_pages) {
-        if (p.status && sub == 0) atomicOr(p.status, PIKV_ST_BAD_INDEX);
+    if (seq >= p.num_seqs) {
+        if (p.status && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(p.status, PIKV_ST_BAD_INDEX);
         return;
     }
-    const int spage = p.src_page_table[(size_t)seq * p.max_pages + spos / PTK];
-    const int dpage = p.dst_page_table[(size_t)seq * p.max_pages + dpos / PTK];
-    if (spage < 0 || spage >= p.num_pages || dpage < 0 || dpage >= p.num_pages) {
-        if (p.status && sub == 0) atomicOr(p.status, PIKV_ST_BAD_PAGE);
-        return;
+    int j[COMPACT_ITEMS], hs[COMPACT_ITEMS], spos[COMPACT_ITEMS], spage[COMPACT_ITEMS], dpage[COMPACT_ITEMS];
+    bool on[COMPACT_ITEMS];
+#pragma unroll
+    for (int i = 0; i < COMPACT_ITEMS; ++i) {
+        const int item = ((blockIdx.y * COMPACT_ITEMS + i) * blockDim.x + threadIdx.x) >> 3;   // (row j, head slot)
+        j[i] = item / c.heads_per;
+        hs[i] = item % c.heads_per;
+        on[i] = j[i] < kept;
+        spos[i] = on[i] ? __ldg(p.keep_idx + (size_t)seg * p.keep_stride + j[i]) : 0;
     }
-    const int srow = spos % PTK, drow = dpos % PTK;
-    const size_t sprow = ((size_t)spage * p.n_kv + head) * PTK + srow;
-    const size_t dprow = ((size_t)dpage * p.n_kv + head) * PTK + drow;
-    if (p.bits == 8) {
-        const size_t so = sprow * 128 + 16 * swz8_chunk(srow, sub), dofs = dprow * 128 + 16 * swz8_chunk(drow, sub);
-        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dst_k_codes) + dofs) =
-            *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.src_k_codes) + so);
-        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dst_v_codes) + dofs) =
-            *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.src_v_codes) + so);
-    } else {
-        const size_t so = sprow * 64 + 8 * swz4_unit(srow, sub), dofs = dprow * 64 + 8 * swz4_unit(drow, sub);
-        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.dst_k_codes) + dofs) =
-            *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.src_k_codes) + so);
-        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.dst_v_codes) + dofs) =
-            *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.src_v_codes) + so);
+#pragma unroll
+    for (int i = 0; i < COMPACT_ITEMS; ++i) {
+        if (on[i] && (spos[i] < 0 || spos[i] / PTK >= p.max_pages || j[i] / PTK >= p.max_pages ||
+                      (p.score_stride > 0 && spos[i] >= p.score_stride))) {
+            if (p.status && sub == 0) atomicOr(p.status, PIKV_ST_BAD_INDEX);
+            on[i] = false;
+        }
+        spage[i] = on[i] ? __ldg(p.src_page_table + (size_t)seq * p.max_pages + spos[i] / PTK) : 0;
+        dpage[i] = on[i] ? __ldg(p.dst_page_table + (size_t)seq * p.max_pages + j[i] / PTK) : 0;
     }
-    if (sub == 0) {
-        static_cast<uint16_t*>(p.dst_k_scale)[dprow] = static_cast<const uint16_t*>(p.src_k_scale)[sprow];
-        static_cast<uint16_t*>(p.dst_v_scale)[dprow] = static_cast<const uint16_t*>(p.src_v_scale)[sprow];
-        if (p.src_k_zp && p.dst_k_zp) {
-            static_cast<float*>(p.dst_k_zp)[dprow] = static_cast<const float*>(p.src_k_zp)[sprow];
-            static_cast<float*>(p.dst_v_zp)[dprow] = static_cast<const float*>(p.src_v_zp)[sprow];
+    uint4 kc[COMPACT_ITEMS], vc[COMPACT_ITEMS];
+    uint32_t side[COMPACT_ITEMS];      // lane 0: K scale, 1: V scale, 2: K zero point, 3: V zero point, 4: score, 5: timestamp
+    const bool has_zp = p.src_k_zp && p.dst_k_zp, has_acc = p.src_acc && p.dst_acc, has_ts = p.src_ts && p.dst_ts;
+#pragma unroll
+    for (int i = 0; i < COMPACT_ITEMS; ++i) {
+        if (on[i] && (spage[i] < 0 || spage[i] >= p.num_pages || dpage[i] < 0 || dpage[i] >= p.num_pages)) {
+            if (p.status && sub == 0) atomicOr(p.status, PIKV_ST_BAD_PAGE);
+            on[i] = false;
         }
-        if (hs == 0) {
-            if (p.src_acc && p.dst_acc)
-                p.dst_acc[(size_t)seg * p.score_stride + dpos] = p.src_acc[(size_t)seg * p.score_stride + spos];
-            if (p.src_ts && p.dst_ts)
-                p.dst_ts[(size_t)seg * p.score_stride + dpos] = p.src_ts[(size_t)seg * p.score_stride + spos];
+        kc[i] = vc[i] = make_uint4(0u, 0u, 0u, 0u);
+        side[i] = 0u;
+        if (!on[i]) continue;
+        const int head = p.per_head ? seg % p.n_kv : hs[i];
+        const int srow = spos[i] % PTK;
+        const size_t sprow = ((size_t)spage[i] * p.n_kv + head) * PTK + srow;
+        if (p.bits == 8) {
+            const size_t so = sprow * 128 + 16 * swz8_chunk(srow, sub);
+            kc[i] = ld_stream_16(static_cast<const uint8_t*>(p.src_k_codes) + so);
+            vc[i] = ld_stream_16(static_cast<const uint8_t*>(p.src_v_codes) + so);
+        } else {
+            const size_t so = sprow * 64 + 8 * swz4_unit(srow, sub);
+            const uint2 a2 = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.src_k_codes) + so);
+            const uint2 b2 = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.src_v_codes) + so);
+            kc[i].x = a2.x; kc[i].y = a2.y;
+            vc[i].x = b2.x; vc[i].y = b2.y;
         }
+        const size_t spt = (size_t)seg * p.score_stride + spos[i];
+        if (sub == 0) side[i] = static_cast<const uint16_t*>(p.src_k_scale)[sprow];
+        else if (sub == 1) side[i] = static_cast<const uint16_t*>(p.src_v_scale)[sprow];
+        else if (sub == 2 && has_zp) side[i] = __float_as_uint(static_cast<const float*>(p.src_k_zp)[sprow]);
+        else if (sub == 3 && has_zp) side[i] = __float_as_uint(static_cast<const float*>(p.src_v_zp)[sprow]);
+        else if (sub == 4 && has_acc && hs[i] == 0) side[i] = __float_as_uint(p.src_acc[spt]);
+        else if (sub == 5 && has_ts && hs[i] == 0) side[i] = __float_as_uint(p.src_ts[spt]);
+    }
+#pragma unroll
+    for (int i = 0; i < COMPACT_ITEMS; ++i) {
+        if (!on[i]) continue;
+        const int head = p.per_head ? seg % p.n_kv : hs[i];
+        const int drow = j[i] % PTK;
+        const size_t dprow = ((size_t)dpage[i] * p.n_kv + head) * PTK + drow;
+        if (p.bits == 8) {
+            const size_t dofs = dprow * 128 + 16 * swz8_chunk(drow, sub);
+            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dst_k_codes) + dofs) = kc[i];
+            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dst_v_codes) + dofs) = vc[i];
+        } else {
+            const size_t dofs = dprow * 64 + 8 * swz4_unit(drow, sub);
+            *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.dst_k_codes) + dofs) = make_uint2(kc[i].x, kc[i].y);
+            *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.dst_v_codes) + dofs) = make_uint2(vc[i].x, vc[i].y);
+        }
+        const size_t dpt = (size_t)seg * (p.dst_score_stride > 0 ? p.dst_score_stride : p.score_stride) + j[i];
+        if (sub == 0) static_cast<uint16_t*>(p.dst_k_scale)[dprow] = (uint16_t)side[i];
+        else if (sub == 1) static_cast<uint16_t*>(p.dst_v_scale)[dprow] = (uint16_t)side[i];
+        else if (sub == 2 && has_zp) static_cast<float*>(p.dst_k_zp)[dprow] = __uint_as_float(side[i]);
+        else if (sub == 3 && has_zp) static_cast<float*>(p.dst_v_zp)[dprow] = __uint_as_float(side[i]);
+        else if (sub == 4 && has_acc && hs[i] == 0) p.dst_acc[dpt] = __uint_as_float(side[i]);
+        else if (sub == 5 && has_ts && hs[i] == 0) p.dst_ts[dpt] = __uint_as_float(side[i]);
     }
 }
 
@@ -708,12 +1195,13 @@ __global__ void h2o_accumulate_probs_kernel(const __half* probs, int probs_strid
 
 using namespace pikv;
 
-// 0: chosen by the segment length (bucketed select when the keys fit in shared memory, radix select over re-read
-// scores otherwise); 1: radix select on staged keys; 2: radix select on re-read scores.  Process-wide, for tests.
+// 0: the streaming select; 1: radix select on keys staged in shared memory; 2: radix select on re-read scores;
+// 3: bucketed select on staged keys (1 and 3 fall back to 2 for segments longer than shared memory holds).
+// Process-wide, for tests: the four routines must agree bit for bit.
 static int g_h2o_select_variant = 0;
 static int h2o_select_variant_for_tests() { return g_h2o_select_variant; }
 extern "C" int pikv_h2o_select_variant(int32_t variant) {
-    PIKV_REQUIRE(variant >= 0 && variant <= 2, PIKV_EINVAL, "h2o_select_variant: 0, 1 or 2");
+    PIKV_REQUIRE(variant >= 0 && variant <= 3, PIKV_EINVAL, "h2o_select_variant: 0..3");
     g_h2o_select_variant = variant;
     return PIKV_OK;
 }
@@ -746,9 +1234,17 @@ extern "C" int pikv_h2o_select(const float* acc, const float* ts, int32_t segmen
     PIKV_REQUIRE(keep_idx == nullptr || keep_stride > 0, PIKV_EINVAL, "h2o_select: keep_stride");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t words = (size_t)(stride + 31) / 32 * 4;
-    // keys staged in shared memory whenever the segment fits; longer segments re-read the scores from L2.
-    // The tests can force the two radix routines through pikv_h2o_select_variant.
     const int variant = h2o_select_variant_for_tests();
+    if (variant == 0) {
+        auto kern = h2o_select_stream_kernel<SS_THREADS>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SsShared)) != cudaSuccess)
+            return check_launch("h2o_select smem attribute");
+        kern<<<segments, SS_THREADS, sizeof(SsShared), st>>>(acc, ts, stride, seg_len, n, num_heavy, num_recent, evict_mask,
+                                                             keep_idx, keep_stride, kept_count);
+        count_launch(1);
+        return check_launch("h2o_select_stream_kernel");
+    }
+    // the staged routines when the segment fits in shared memory; longer segments re-read the scores from L2
     const bool staged = stride <= SEL_SMEM_KEYS && variant != 2;
     const bool radix_only = variant == 1;
     if (staged) {
@@ -782,12 +1278,19 @@ extern "C" int pikv_h2o_compact(const pikv_compact_params* p, pikv_stream_t stre
     PIKV_REQUIRE(p->num_seqs > 0 && p->n_kv > 0 && p->keep_stride > 0 && p->max_pages > 0, PIKV_EINVAL,
                  "h2o_compact: bad sizes");
     PIKV_REQUIRE(p->bits == 8 || p->bits == 4, PIKV_EUNSUPPORTED, "h2o_compact: bits=%d", p->bits);
+    PIKV_REQUIRE((p->src_acc == nullptr) == (p->dst_acc == nullptr) && (p->src_ts == nullptr) == (p->dst_ts == nullptr), PIKV_EINVAL,
+                 "h2o_compact: scores / timestamps need both a source and a destination");
+    PIKV_REQUIRE((p->src_acc == nullptr && p->src_ts == nullptr) ||
+                     (p->score_stride > 0 && (p->dst_score_stride == 0 || p->dst_score_stride >= p->keep_stride) &&
+                      (p->dst_score_stride != 0 || p->score_stride >= p->keep_stride)),
+                 PIKV_EINVAL, "h2o_compact: score_stride=%d dst_score_stride=%d keep_stride=%d", p->score_stride,
+                 p->dst_score_stride, p->keep_stride);
     CompactDev c;
     c.p = *p;
     c.heads_per = p->per_head ? 1 : p->n_kv;
     const int segments = p->per_head ? p->num_seqs * p->n_kv : p->num_seqs;
     const long long lanes = (long long)p->keep_stride * c.heads_per * 8;
-    dim3 grid(segments, (unsigned)ceil_div64(lanes, 256));
+    dim3 grid(segments, (unsigned)ceil_div64(lanes, 256 * COMPACT_ITEMS));
     h2o_compact_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c);
     count_launch(1);
     return check_launch("h2o_compact_kernel");

@@ -282,7 +282,21 @@ class PagedKVCache(torch.nn.Module):
         p.dst_k_codes, p.dst_v_codes, p.dst_k_scale, p.dst_v_scale = _p(dst.k_codes), _p(dst.v_codes), _p(dst.k_scale), _p(dst.v_scale)
         p.dst_k_zp, p.dst_v_zp = _p(dst.k_zp), _p(dst.v_zp)
         p.src_acc, p.src_ts, p.dst_acc, p.dst_ts = _p(src_acc), _p(src_ts), _p(dst_acc), _p(dst_ts)
-        p.score_stride = src_acc.shape[-1] if src_acc is not None else 0
+        segments = self.num_seqs * (self.n_kv if per_head else 1)
+        for name, src_t, dst_t in (("acc", src_acc, dst_acc), ("ts", src_ts, dst_ts)):
+            if (src_t is None) != (dst_t is None):
+                raise PikvError(f"compact_into: give src_{name} and dst_{name} together")
+            if src_t is not None:
+                _req(src_t, f"src_{name}", torch.float32), _req(dst_t, f"dst_{name}", torch.float32)
+                if src_t.numel() != segments * src_t.shape[-1] or dst_t.numel() != segments * dst_t.shape[-1]:
+                    raise PikvError(f"compact_into: src_{name} / dst_{name} must have one row per segment ({segments})")
+                if dst_t.shape[-1] < keep_idx.shape[1]:
+                    raise PikvError(f"compact_into: dst_{name} rows are shorter than keep_idx rows")
+        if src_acc is not None and src_ts is not None and (src_acc.shape[-1] != src_ts.shape[-1] or dst_acc.shape[-1] != dst_ts.shape[-1]):
+            raise PikvError("compact_into: scores and timestamps must share their row lengths")
+        first_src, first_dst = (src_acc, dst_acc) if src_acc is not None else (src_ts, dst_ts)
+        p.score_stride = first_src.shape[-1] if first_src is not None else 0
+        p.dst_score_stride = first_dst.shape[-1] if first_dst is not None else 0
         p.status = _p(self.status)
         check(lib().pikv_h2o_compact(C.byref(p), _stream()), "pikv_h2o_compact")
 

@@ -268,9 +268,10 @@ def test_h2o_select_segments_and_ties(dev, n, nh, nr, levels):
         np.testing.assert_array_equal(keep[s, : len(ki)].cpu().numpy(), ki)
 
 
-@pytest.mark.parametrize("kind", ["uniform", "heavy_tail", "outlier", "levels", "ascending", "ascending_runs", "constant"])
+@pytest.mark.parametrize("kind", ["uniform", "heavy_tail", "outlier", "levels", "ascending", "ascending_runs", "constant",
+                                  "dense_bucket", "unaligned"])
 def test_h2o_select_routines_agree_with_oracle(dev, kind):
-    """The bucketed select (default for segments that fit in shared memory) and the two radix routines must all
+    """The streaming select (the default), the two radix routines and the bucketed select on staged keys must all
     return the oracle's mask on score distributions that stress them differently: a far outlier (every other key
     in one bucket), eight tied levels, keys already in ascending order (range marks), runs of equal timestamps."""
     import pikv_b200
@@ -280,7 +281,13 @@ def test_h2o_select_routines_agree_with_oracle(dev, kind):
     acc = {"uniform": rng.random((S, n)), "heavy_tail": rng.pareto(1.2, (S, n)), "outlier": rng.random((S, n)),
            "levels": rng.integers(0, 8, (S, n)) / 8.0, "ascending": np.sort(rng.random((S, n)), axis=1),
            "ascending_runs": np.sort(rng.integers(0, 50, (S, n)), axis=1).astype(np.float64),
-           "constant": np.full((S, n), 0.25)}[kind].astype(F32)
+           "constant": np.full((S, n), 0.25),
+           # thousands of distinct keys inside one first-level bucket beside a wide spread: narrowed pass by pass
+           "dense_bucket": np.where(rng.random((S, n)) < 0.04, rng.random((S, n)) * 1e6, 1.0 + rng.random((S, n)) * 1e-4),
+           "unaligned": rng.random((S, n))}[kind].astype(F32)
+    if kind == "unaligned":
+        n = 4999                                               # rows that start off a 16-byte boundary
+        acc = np.ascontiguousarray(acc[:, :n])
     if kind == "outlier":
         acc[:, 7] = 1e30
         acc[:, 11] = -1e30
@@ -292,7 +299,7 @@ def test_h2o_select_routines_agree_with_oracle(dev, kind):
     want = np.stack([O.h2o_select(acc[s], ts[s], nh, nr)[0] for s in range(S)])
     a, t = torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev)
     try:
-        for variant in (0, 1, 2):
+        for variant in (0, 1, 2, 3):
             assert pikv_b200.lib().pikv_h2o_select_variant(variant) == 0
             mask, keep, cnt = ops.h2o_select(a, t, nh, nr)
             np.testing.assert_array_equal(mask.cpu().numpy(), want, err_msg=f"variant {variant}")
@@ -501,10 +508,17 @@ def test_h2o_compact_moves_rows_and_scores(dev, per_head):
     mask, keep, cnt = ops.h2o_select(torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev), 40, 8,
                                      seg_len=torch.from_numpy(seg_len.astype(np.int32)).to(dev))
     dst = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)
-    dacc = torch.zeros(segs, ctx, device=dev)
-    dts = torch.zeros(segs, ctx, device=dev)
+    # destination score rows as long as the source's, or only as long as the kept-index rows
+    width = keep.shape[1] if per_head else ctx
+    dacc = torch.zeros(segs, width, device=dev)
+    dts = torch.zeros(segs, width, device=dev)
+    guard = torch.zeros(1 << 16, device=dev)          # allocated right after them: must stay untouched
     cache.compact_into(dst, keep, cnt, per_head, torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev), dacc, dts)
     cache.check_status()
+    assert float(guard.abs().sum()) == 0.0
+    with pytest.raises(pikv_b200.PikvError):
+        cache.compact_into(dst, keep, cnt, per_head, torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev),
+                           dacc[:, : keep.shape[1] - 1].contiguous(), dts[:, : keep.shape[1] - 1].contiguous())
     for s in range(segs):
         b = s // n_kv if per_head else s
         heads = [s % n_kv] if per_head else list(range(n_kv))
