@@ -610,6 +610,7 @@ __global__ void __launch_bounds__(NT) h2o_select_kernel(const float* acc, const 
 constexpr int SS_THREADS = 256;
 constexpr int SS_BUCKETS = 4096;
 constexpr int SS_LIST_CAP = 1024;
+constexpr int SS_RANK_CAP = 256;                    // listed keys ranked by counting up to this many
 constexpr int SS_BPT = SS_BUCKETS / SS_THREADS;     // buckets a thread owns in the suffix sums
 
 struct SsResult {
@@ -897,6 +898,27 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
             __syncthreads();
             list_n = min(sh.list_n, SS_LIST_CAP);
             on_list = true;
+            if (list_n <= SS_RANK_CAP) {
+                // a short list: the rem-th largest key by counting, for every listed key, the keys above it and the
+                // keys equal to it (one round instead of a histogram per 12 bits)
+                for (int i = tid; i < list_n; i += NT) {
+                    const uint32_t ki = sh.list[i];
+                    int g = 0, ge = 0;
+                    for (int q = 0; q < list_n; ++q) {
+                        const uint32_t kq = sh.list[q];
+                        g += kq > ki ? 1 : 0;
+                        ge += kq >= ki ? 1 : 0;
+                    }
+                    if (g < rem && rem <= ge) {          // every copy of the key writes the same values
+                        out->mode = 3;
+                        out->kth = ki;
+                        out->need_eq = rem - g;
+                        out->all_eq = (rem - g) == (ge - g);
+                    }
+                }
+                __syncthreads();
+                return;
+            }
         }
         __syncthreads();
     }
