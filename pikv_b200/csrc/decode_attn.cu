@@ -194,6 +194,7 @@ __global__ void __launch_bounds__(DA_PLAN_THREADS) decode_plan_kernel(DecodeDev 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int R = d.B;
     const int max_len = d.max_pages * PIKV_PAGE_TOKENS;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the attention kernel may be scheduled
     for (int i = tid; i < R; i += DA_PLAN_THREADS) {
         const int seq = d.seq_ids ? d.seq_ids[i] : i;
         const bool ok = seq >= 0 && seq < d.num_seqs;
@@ -271,6 +272,22 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
     const int r = lane >> 2, j = lane & 3;
     const int G = d.G, R = d.B, n_kv = d.n_kv;
     const int max_len = d.max_pages * PIKV_PAGE_TOKENS;
+    // The three kernels of a call are chained by programmatic dependent launches: the merge kernel may be scheduled
+    // from here on (it waits for this grid to complete), and this kernel's own set-up runs while the plan kernel
+    // finishes; nothing the plan kernel wrote is read before the wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    unsigned char* ring = smem + (size_t)warp * STAGES * STAGE_BYTES;
+    __half* pbuf = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(bars + DA_WARPS * STAGES) + warp * DA_PBUF_BYTES);
+    const uint32_t bar0 = smem_u32(bars + warp * STAGES);
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    for (int i2 = lane; i2 < DA_PBUF_BYTES / 4; i2 += 32) reinterpret_cast<uint32_t*>(pbuf)[i2] = 0u;   // rows of absent heads stay zero
+    __syncwarp();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int blk_pages = __ldg(d.head + 1), nblocks = __ldg(d.head + 2), P = __ldg(d.prefix + R);
     const int nitems = nblocks * n_kv;
 
@@ -297,17 +314,6 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
         it.left = it.blk == nblocks - 1 ? P - it.blk * blk_pages : blk_pages;
     };
 
-    unsigned char* ring = smem + (size_t)warp * STAGES * STAGE_BYTES;
-    __half* pbuf = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(bars + DA_WARPS * STAGES) + warp * DA_PBUF_BYTES);
-    const uint32_t bar0 = smem_u32(bars + warp * STAGES);
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    for (int i2 = lane; i2 < DA_PBUF_BYTES / 4; i2 += 32) reinterpret_cast<uint32_t*>(pbuf)[i2] = 0u;   // rows of absent heads stay zero
-    __syncwarp();
 
     // moves a cursor `by` pages on (never across more than one request boundary)
     auto advance = [&](DACursor& x, int by) {
@@ -800,8 +806,58 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
     }
 }
 
+// Merge of the partials of the blocks g0..g1 that covered request rq, for query head (h, qh): thread ch owns one
+// channel.  The statistics of up to 32 blocks at a time are loaded by one warp-wide access and the partial outputs
+// four blocks at a time, so the loads of a request that many workers shared are in flight together instead of one
+// round trip per block.  Returns acc / l pieces: acc = sum_g o_g 2^(m_g - M), l = sum_g l_g 2^(m_g - M).
+__device__ __forceinline__ void da_merge_blocks(const DecodeDev& d, int rq, int h, int qh, int g0, int g1, int ch, float& M,
+                                                float& acc, float& l) {
+    __shared__ float s_m[32], s_l[32];
+    const int lane = ch & 31;
+    M = -INFINITY;
+    acc = 0.f;
+    l = 0.f;
+    // pass 1: the maximum over all blocks (every warp computes it redundantly: no barrier needed for M)
+    for (int gb = g0; gb <= g1; gb += 32) {
+        const int g = gb + lane;
+        const float m = g <= g1 ? d.part_ml[((((size_t)g + rq) * d.n_kv + h) * d.G + qh) * 2] : -INFINITY;
+        float mm = m;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+        M = fmaxf(M, mm);
+    }
+    for (int gb = g0; gb <= g1; gb += 32) {
+        const int cnt = min(32, g1 - gb + 1);
+        __syncthreads();                                   // s_m / s_l free again
+        if (ch < cnt) {
+            const size_t sl = (((size_t)(gb + ch) + rq) * d.n_kv + h) * d.G + qh;
+            const float2 ml = *reinterpret_cast<const float2*>(d.part_ml + sl * 2);
+            s_m[ch] = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
+            s_l[ch] = ml.y;
+        }
+        __syncthreads();
+        int i = 0;
+        for (; i + 4 <= cnt; i += 4) {
+            float o4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                o4[u] = d.part_o[((((size_t)(gb + i + u) + rq) * d.n_kv + h) * d.G + qh) * 128 + ch];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                acc += o4[u] * s_m[i + u];
+                l += s_l[i + u] * s_m[i + u];
+            }
+        }
+        for (; i < cnt; ++i) {
+            acc += d.part_o[((((size_t)(gb + i) + rq) * d.n_kv + h) * d.G + qh) * 128 + ch] * s_m[i];
+            l += s_l[i] * s_m[i];
+        }
+    }
+}
+
 // One CTA per (request, query head): merges the partials of the workers that covered the unit.
 __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeDev d) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int rq = blockIdx.x / d.n_q, qg = blockIdx.x % d.n_q;
     const int h = qg / d.G, qh = qg % d.G, ch = threadIdx.x;
     const int blk_pages = d.head[1], nblocks = d.head[2];
@@ -814,16 +870,8 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeDev d) {
     }
     // the blocks that covered the request
     const int g0 = da_block_of(d.prefix[rq], blk_pages, nblocks), g1 = da_block_of(d.prefix[rq + 1] - 1, blk_pages, nblocks);
-    float M = -INFINITY;
-    for (int g = g0; g <= g1; ++g) M = fmaxf(M, d.part_ml[((((size_t)g + rq) * d.n_kv + h) * d.G + qh) * 2]);
-    float acc = 0.f, l = 0.f;
-    for (int g = g0; g <= g1; ++g) {
-        const size_t s = (((size_t)g + rq) * d.n_kv + h) * d.G + qh;
-        const float ms = d.part_ml[s * 2];
-        const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-        acc += d.part_o[s * 128 + ch] * sc;
-        l += d.part_ml[s * 2 + 1] * sc;
-    }
+    float M, acc, l;
+    da_merge_blocks(d, rq, h, qh, g0, g1, ch, M, acc, l);
     d.out[bq * 128 + ch] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     if (ch == 0 && d.lse) d.lse[bq] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
 }
@@ -833,22 +881,15 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(DecodeDev d) {
 // log-sum-exp, stored straight into the buffers of the stream's home rank (peer pointers, plain stores) at
 // [local stream][choice][this rank].  The last CTA to finish raises this rank's "done" flag on every rank.
 __global__ void __launch_bounds__(128) decode_return_kernel(DecodeDev d, ShardReturn t) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int rq = blockIdx.x / d.n_q, qg = blockIdx.x % d.n_q;
     const int h = qg / d.G, qh = qg % d.G, ch = threadIdx.x;
     const int pages = d.prefix[rq + 1] - d.prefix[rq];
     if (pages > 0) {
         const int blk_pages = d.head[1], nblocks = d.head[2];
         const int g0 = da_block_of(d.prefix[rq], blk_pages, nblocks), g1 = da_block_of(d.prefix[rq + 1] - 1, blk_pages, nblocks);
-        float M = -INFINITY;
-        for (int g = g0; g <= g1; ++g) M = fmaxf(M, d.part_ml[((((size_t)g + rq) * d.n_kv + h) * d.G + qh) * 2]);
-        float acc = 0.f, l = 0.f;
-        for (int g = g0; g <= g1; ++g) {
-            const size_t s = (((size_t)g + rq) * d.n_kv + h) * d.G + qh;
-            const float ms = d.part_ml[s * 2];
-            const float sc = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-            acc += d.part_o[s * 128 + ch] * sc;
-            l += d.part_ml[s * 2 + 1] * sc;
-        }
+        float M, acc, l;
+        da_merge_blocks(d, rq, h, qh, g0, g1, ch, M, acc, l);
         const int stream = rq / t.top_k, jsel = rq % t.top_k;
         const int home = stream / t.streams_per_rank, sl = stream % t.streams_per_rank;
         const size_t slot = (((size_t)sl * t.top_k + jsel) * t.world + t.rank) * d.n_q + qg;
@@ -871,6 +912,21 @@ __global__ void __launch_bounds__(128) decode_return_kernel(DecodeDev d, ShardRe
 }
 
 static int da_workers() { return sm_count() * DA_CTAS_PER_SM * DA_WARPS; }
+
+// launch configuration of a kernel that may start before the previous kernel of the stream has finished (it orders
+// itself with griddepcontrol.wait)
+static cudaLaunchConfig_t da_pdl_config(int grid, int block, size_t smem, cudaStream_t st, cudaLaunchAttribute* attr) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cfg;
+}
 
 // workspace: header, request prefix, block starts, partials of (max_blocks + B) x n_kv slots
 struct DALayout {
@@ -960,13 +1016,15 @@ int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits
     if (rc != PIKV_OK) return rc;
     const int grid = d.workers / DA_WARPS;
     const bool gs = d.G <= 4;      // integer first product (see decode_attn_kernel)
+    cudaLaunchAttribute attr[1];   // programmatic dependent launch of the attention and the merge kernel
 #define PIKV_DA_LAUNCH(BITS, GS)                                                                                          \
     do {                                                                                                                  \
         const size_t smem = da_smem_bytes<BITS>();                                                                        \
         auto kern = decode_attn_kernel<BITS, GS>;                                                                         \
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)            \
             return check_launch("decode_attn smem attribute");                                                            \
-        kern<<<grid, DA_THREADS, smem, st>>>(d);                                                                          \
+        cudaLaunchConfig_t cfg = da_pdl_config(grid, DA_THREADS, smem, st, attr);                                         \
+        (void)cudaLaunchKernelEx(&cfg, kern, d);                                                                          \
     } while (0)
     if (bits == 8 && gs) PIKV_DA_LAUNCH(8, true);
     else if (bits == 8) PIKV_DA_LAUNCH(8, false);
@@ -975,11 +1033,12 @@ int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits
 #undef PIKV_DA_LAUNCH
     rc = check_launch(bits == 8 ? "decode_attn_kernel<8>" : "decode_attn_kernel<4>");
     if (rc != PIKV_OK) return rc;
+    cudaLaunchConfig_t mcfg = da_pdl_config(p->B * p->n_q, 128, 0, st, attr);
     if (ret != nullptr) {
-        decode_return_kernel<<<p->B * p->n_q, 128, 0, st>>>(d, *ret);
+        (void)cudaLaunchKernelEx(&mcfg, decode_return_kernel, d, *ret);
         rc = check_launch("decode_return_kernel");
     } else {
-        decode_merge_kernel<<<p->B * p->n_q, 128, 0, st>>>(d);
+        (void)cudaLaunchKernelEx(&mcfg, decode_merge_kernel, d);
         rc = check_launch("decode_merge_kernel");
     }
     count_launch(3);
