@@ -449,7 +449,7 @@ int pikv_h2o_compact(const pikv_compact_params* p, pikv_stream_t stream);
  * ranges, one per warp, whatever the streams' lengths; a warp leaves one partial
  * result per unit it touched in `workspace` and a second kernel merges them.
  *   q, out: [B, n_q, 128] bf16.  seq_ids [B] (NULL: b) selects the page-table
- *   row, seq_len [B] its valid length.  B <= 12288 per call.
+ *   row, seq_len [B] its valid length.  B <= 12000 per call.
  *   lse (optional) [B, n_q] fp32 log-sum-exp of the scaled scores.
  *   scores (optional) [B, n_q, score_stride] fp32 raw scaled scores, consumed by
  *   pikv_h2o_accumulate_attn.
@@ -487,9 +487,10 @@ int    pikv_decode_attn_q4(const pikv_decode_params* p, pikv_stream_t stream);
  * allocator-free region, code inside a stream capture).  It has no counterpart in the reference.
  * The partial results go to an 8 MiB array built into the library (held by every GPU that loads it,
  * until exit) instead of `workspace`, which is ignored; the call makes no cudaMalloc / cudaFree and
- * calls no allocating routine.  pikv_decode_attn_workspace_bytes(B, n_q, n_kv, 0, 0) must fit in
- * pikv_decode_attn_static_scratch_bytes() (config 3, 64 streams x 32 query / 8 KV heads, needs 4.8 MB),
- * otherwise PIKV_ELIMIT.  The first call on each device looks the array's address up
+ * calls no allocating routine.  The array is smaller than the workspace the regular entry point asks for, so the
+ * kernel cuts the page list into fewer, longer blocks; one block per worker of a KV head must still fit
+ * (64 streams x 32 query / 8 KV heads need 4.8 MB of the pikv_decode_attn_static_scratch_bytes() = 8 MiB),
+ * otherwise the call is refused with PIKV_ELIMIT before anything is launched.  The first call on each device looks the array's address up
  * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on a device
  * share the array: it needs no clearing (every partial a launch reads was written by that launch),
  * but two calls whose kernels overlap on the GPU (different streams) race on it. */
