@@ -997,8 +997,10 @@ __global__ void __launch_bounds__(NT, 1024 / NT) h2o_select_stream_kernel(const 
     const float* a = acc + (size_t)seg * stride;
     const float* t = ts + (size_t)seg * stride;
     const bool al_a = (reinterpret_cast<uintptr_t>(a) & 15) == 0, al_t = (reinterpret_cast<uintptr_t>(t) & 15) == 0;
-    ss_find<NT>(a, n, min(num_heavy, n), al_a, sh, &sh.res[0]);
+    // the timestamps first: they are read once, the scores up to four times, and read last the scores are the
+    // array still in L2 when the later passes come back to them
     ss_find<NT>(t, n, min(num_recent, n), al_t, sh, &sh.res[1]);
+    ss_find<NT>(a, n, min(num_heavy, n), al_a, sh, &sh.res[0]);
     __syncthreads();
     const SsResult ra = sh.res[0], rt = sh.res[1];
     const bool ties_a = ra.mode == 3 && !ra.all_eq, ties_t = rt.mode == 3 && !rt.all_eq;

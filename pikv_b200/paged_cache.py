@@ -61,6 +61,30 @@ class PagedKVCache(torch.nn.Module):
         self.register_buffer("length", z(num_seqs, dtype=torch.int32))
         self.register_buffer("status", z(1, dtype=torch.int32))
 
+    # -- serialisation ---------------------------------------------------------------
+    # The reference's checkpoint keeps one mean vector per cache (core/single/pikv_moe.py:456-505): the rows are
+    # lost.  Here the cache itself is the state: pages, scales, zero points, page table and lengths are registered
+    # buffers, so state_dict() / load_state_dict() move it, and these two calls add the geometry a loader needs
+    # to rebuild the object, plus any score buffers of an eviction policy the caller passes along.
+    def save_checkpoint(self, path, scores: Optional[dict] = None) -> None:
+        torch.save({"format": "pikv_b200.paged_cache.v1",
+                    "geometry": {"num_seqs": self.num_seqs, "capacity": self.capacity, "n_kv": self.n_kv, "bits": self.bits,
+                                 "symmetric": self.symmetric, "num_pages": self.num_pages},
+                    "state_dict": self.state_dict(),
+                    "scores": {k: v.detach().clone() for k, v in (scores or {}).items()}}, path)
+
+    @classmethod
+    def load_checkpoint(cls, path, device="cuda"):
+        """Returns (cache, scores): the cache rebuilt on `device` with every page, scale and length of the saved one."""
+        blob = torch.load(path, map_location=torch.device(device), weights_only=False)
+        if blob.get("format") != "pikv_b200.paged_cache.v1":
+            raise PikvError(f"{path}: not a paged-cache checkpoint")
+        g = blob["geometry"]
+        cache = cls(g["num_seqs"], g["capacity"], g["n_kv"], bits=g["bits"], symmetric=g["symmetric"], device=device,
+                    num_pages=g["num_pages"], identity_table=False)
+        cache.load_state_dict(blob["state_dict"])
+        return cache, blob.get("scores", {})
+
     # -- writes --------------------------------------------------------------------
     def append(self, k: torch.Tensor, v: torch.Tensor, dst_seq: torch.Tensor, slot: torch.Tensor) -> None:
         """Quantise and store k, v [T, n_kv*128] at (dst_seq[t,j], slot[t,j]); slot < 0 is skipped.

@@ -735,3 +735,22 @@ def test_append_rope_matches_reference(dev):
     q2, _, _ = O.quant_token_groups(want2, 8, 128, True)
     _, c2 = cache2.gather(torch.zeros(48, dtype=torch.int32, device=dev), s2[:, 0].contiguous(), "k", codes=True)
     np.testing.assert_array_equal(c2.cpu().numpy().astype(F32), q2)
+
+
+def test_cache_checkpoint_round_trip(dev, tmp_path):
+    """Pages, scales, zero points, page table, lengths and a policy's score buffers survive save / load: the
+    reloaded cache decodes to the same bits (the reference's checkpoint keeps one mean vector per cache)."""
+    import pikv_b200
+    for bits in (8, 4):
+        B, n_kv, ctx = 3, 2, 200
+        lens = np.array([200, 150, 64], np.int32)
+        cache, _, _ = fill_stream_cache(dev, B, n_kv, ctx, lens, 11, bits=bits, symmetric=(bits == 8))
+        acc = torch.rand(B * n_kv, ctx, device=dev)
+        path = tmp_path / f"cache{bits}.pt"
+        cache.save_checkpoint(path, scores={"attention_accumulator": acc})
+        again, scores = pikv_b200.PagedKVCache.load_checkpoint(path, device=dev)
+        assert torch.equal(scores["attention_accumulator"], acc)
+        for name in ("k_codes", "v_codes", "k_scale", "v_scale", "page_table", "length") + (("k_zp", "v_zp") if bits == 4 else ()):
+            assert torch.equal(getattr(again, name), getattr(cache, name)), name
+        q = torch.randn(B, 4 * n_kv, 128, device=dev).bfloat16()
+        assert torch.equal(again.decode_attention(q), cache.decode_attention(q))
