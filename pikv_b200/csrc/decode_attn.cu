@@ -806,95 +806,109 @@ __global__ void __launch_bounds__(DA_THREADS, DA_CTAS_PER_SM) decode_attn_kernel
     }
 }
 
-// Merge of the partials of the blocks g0..g1 that covered request rq, for query head (h, qh): thread ch owns one
-// channel.  The statistics of up to 32 blocks at a time are loaded by one warp-wide access and the partial outputs
-// four blocks at a time, so the loads of a request that many workers shared are in flight together instead of one
-// round trip per block.  Returns acc / l pieces: acc = sum_g o_g 2^(m_g - M), l = sum_g l_g 2^(m_g - M).
-__device__ __forceinline__ void da_merge_blocks(const DecodeDev& d, int rq, int h, int qh, int g0, int g1, int ch, float& M,
-                                                float& acc, float& l) {
-    __shared__ float s_m[32], s_l[32];
-    const int lane = ch & 31;
+// Merge of the partials of the blocks g0..g1 that covered request rq, for query head (h, qh), by ONE WARP: lane i owns
+// channels 4i..4i+3.  The statistics of up to 32 blocks are loaded by one warp-wide access and the partial outputs
+// four blocks at a time (512 contiguous bytes each), so the loads of a request that many workers shared are in flight
+// together.  acc = sum_g o_g 2^(m_g - M), l = sum_g l_g 2^(m_g - M).
+__device__ __forceinline__ void da_merge_blocks(const DecodeDev& d, int rq, int h, int qh, int g0, int g1, int lane, float& M,
+                                                float4& acc, float& l) {
     M = -INFINITY;
-    acc = 0.f;
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
     l = 0.f;
-    // pass 1: the maximum over all blocks (every warp computes it redundantly: no barrier needed for M)
+    auto slot = [&](int g) { return (((size_t)g + rq) * d.n_kv + h) * d.G + qh; };
     for (int gb = g0; gb <= g1; gb += 32) {
         const int g = gb + lane;
-        const float m = g <= g1 ? d.part_ml[((((size_t)g + rq) * d.n_kv + h) * d.G + qh) * 2] : -INFINITY;
-        float mm = m;
+        float mm = g <= g1 ? d.part_ml[slot(g) * 2] : -INFINITY;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
         M = fmaxf(M, mm);
     }
     for (int gb = g0; gb <= g1; gb += 32) {
         const int cnt = min(32, g1 - gb + 1);
-        __syncthreads();                                   // s_m / s_l free again
-        if (ch < cnt) {
-            const size_t sl = (((size_t)(gb + ch) + rq) * d.n_kv + h) * d.G + qh;
-            const float2 ml = *reinterpret_cast<const float2*>(d.part_ml + sl * 2);
-            s_m[ch] = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
-            s_l[ch] = ml.y;
+        float w_l = 0.f, l_l = 0.f;
+        if (lane < cnt) {
+            const float2 ml = *reinterpret_cast<const float2*>(d.part_ml + slot(gb + lane) * 2);
+            w_l = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
+            l_l = ml.y;
         }
-        __syncthreads();
         int i = 0;
         for (; i + 4 <= cnt; i += 4) {
-            float o4[4];
+            float4 o4[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-                o4[u] = d.part_o[((((size_t)(gb + i + u) + rq) * d.n_kv + h) * d.G + qh) * 128 + ch];
+            for (int u = 0; u < 4; ++u) o4[u] = reinterpret_cast<const float4*>(d.part_o + slot(gb + i + u) * 128)[lane];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                acc += o4[u] * s_m[i + u];
-                l += s_l[i + u] * s_m[i + u];
+                const float w = __shfl_sync(0xffffffffu, w_l, i + u);
+                acc.x += o4[u].x * w; acc.y += o4[u].y * w; acc.z += o4[u].z * w; acc.w += o4[u].w * w;
+                l += __shfl_sync(0xffffffffu, l_l, i + u) * w;
             }
         }
         for (; i < cnt; ++i) {
-            acc += d.part_o[((((size_t)(gb + i) + rq) * d.n_kv + h) * d.G + qh) * 128 + ch] * s_m[i];
-            l += s_l[i] * s_m[i];
+            const float4 o = reinterpret_cast<const float4*>(d.part_o + slot(gb + i) * 128)[lane];
+            const float w = __shfl_sync(0xffffffffu, w_l, i);
+            acc.x += o.x * w; acc.y += o.y * w; acc.z += o.z * w; acc.w += o.w * w;
+            l += __shfl_sync(0xffffffffu, l_l, i) * w;
         }
     }
 }
 
-// One CTA per (request, query head): merges the partials of the workers that covered the unit.
-__global__ void __launch_bounds__(128) decode_merge_kernel(DecodeDev d) {
+constexpr int DA_MERGE_THREADS = 128;     // four warps, one (request, query head) unit each
+
+// One warp per (request, query head): merges the partials of the workers that covered the unit.
+__global__ void __launch_bounds__(DA_MERGE_THREADS) decode_merge_kernel(DecodeDev d) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int rq = blockIdx.x / d.n_q, qg = blockIdx.x % d.n_q;
-    const int h = qg / d.G, qh = qg % d.G, ch = threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * (DA_MERGE_THREADS / 32) + (threadIdx.x >> 5);
+    if (unit >= d.B * d.n_q) return;
+    const int rq = unit / d.n_q, qg = unit % d.n_q;
+    const int h = qg / d.G, qh = qg % d.G;
     const int blk_pages = d.head[1], nblocks = d.head[2];
     const int pages = d.prefix[rq + 1] - d.prefix[rq];
     const size_t bq = (size_t)rq * d.n_q + qg;
+    uint2* out2 = reinterpret_cast<uint2*>(d.out + bq * 128) + lane;      // four bf16 channels
     if (pages == 0) {
-        d.out[bq * 128 + ch] = __float2bfloat16_rn(0.f);
-        if (ch == 0 && d.lse) d.lse[bq] = -INFINITY;
+        *out2 = make_uint2(0u, 0u);
+        if (lane == 0 && d.lse) d.lse[bq] = -INFINITY;
         return;
     }
     // the blocks that covered the request
     const int g0 = da_block_of(d.prefix[rq], blk_pages, nblocks), g1 = da_block_of(d.prefix[rq + 1] - 1, blk_pages, nblocks);
-    float M, acc, l;
-    da_merge_blocks(d, rq, h, qh, g0, g1, ch, M, acc, l);
-    d.out[bq * 128 + ch] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-    if (ch == 0 && d.lse) d.lse[bq] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
+    float M, l;
+    float4 acc;
+    da_merge_blocks(d, rq, h, qh, g0, g1, lane, M, acc, l);
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(l > 0.f ? acc.x / l : 0.f, l > 0.f ? acc.y / l : 0.f);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(l > 0.f ? acc.z / l : 0.f, l > 0.f ? acc.w / l : 0.f);
+    *out2 = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    if (lane == 0 && d.lse) d.lse[bq] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
 }
 
 // The same merge on an expert-sharded box: request i = (stream i / top_k, choice i % top_k) of a decode step
 // whose rows are striped over the ranks; what this rank holds of it gives a NORMALISED partial output and its
 // log-sum-exp, stored straight into the buffers of the stream's home rank (peer pointers, plain stores) at
-// [local stream][choice][this rank].  The last CTA to finish raises this rank's "done" flag on every rank.
-__global__ void __launch_bounds__(128) decode_return_kernel(DecodeDev d, ShardReturn t) {
+// [local stream][choice][this rank].  A persistent grid: every warp walks its share of the units, every CTA makes
+// its stores visible system-wide ONCE (a system-scope fence per unit cost 110 us for the 16384 units of a step)
+// and counts itself; the last CTA to finish raises this rank's "done" flag on every rank.
+__global__ void __launch_bounds__(DA_MERGE_THREADS) decode_return_kernel(DecodeDev d, ShardReturn t) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int rq = blockIdx.x / d.n_q, qg = blockIdx.x % d.n_q;
-    const int h = qg / d.G, qh = qg % d.G, ch = threadIdx.x;
-    const int pages = d.prefix[rq + 1] - d.prefix[rq];
-    if (pages > 0) {
-        const int blk_pages = d.head[1], nblocks = d.head[2];
+    const int lane = threadIdx.x & 31;
+    const int units = d.B * d.n_q;
+    const int blk_pages = d.head[1], nblocks = d.head[2];
+    for (int unit = blockIdx.x * (DA_MERGE_THREADS / 32) + (threadIdx.x >> 5); unit < units;
+         unit += gridDim.x * (DA_MERGE_THREADS / 32)) {
+        const int rq = unit / d.n_q, qg = unit % d.n_q;
+        const int h = qg / d.G, qh = qg % d.G;
+        const int pages = d.prefix[rq + 1] - d.prefix[rq];
+        if (pages <= 0) continue;
         const int g0 = da_block_of(d.prefix[rq], blk_pages, nblocks), g1 = da_block_of(d.prefix[rq + 1] - 1, blk_pages, nblocks);
-        float M, acc, l;
-        da_merge_blocks(d, rq, h, qh, g0, g1, ch, M, acc, l);
+        float M, l;
+        float4 acc;
+        da_merge_blocks(d, rq, h, qh, g0, g1, lane, M, acc, l);
         const int stream = rq / t.top_k, jsel = rq % t.top_k;
         const int home = stream / t.streams_per_rank, sl = stream % t.streams_per_rank;
         const size_t slot = (((size_t)sl * t.top_k + jsel) * t.world + t.rank) * d.n_q + qg;
-        t.peer_part_o[home][slot * 128 + ch] = l > 0.f ? acc / l : 0.f;
-        if (ch == 0) t.peer_part_lse[home][slot] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
+        reinterpret_cast<float4*>(t.peer_part_o[home] + slot * 128)[lane] =
+            l > 0.f ? make_float4(acc.x / l, acc.y / l, acc.z / l, acc.w / l) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (lane == 0) t.peer_part_lse[home][slot] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
     }
     // completion: every CTA counts itself after its stores are visible system-wide; the last one signals
     __threadfence_system();
@@ -1033,7 +1047,10 @@ int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits
 #undef PIKV_DA_LAUNCH
     rc = check_launch(bits == 8 ? "decode_attn_kernel<8>" : "decode_attn_kernel<4>");
     if (rc != PIKV_OK) return rc;
-    cudaLaunchConfig_t mcfg = da_pdl_config(p->B * p->n_q, 128, 0, st, attr);
+    const int units = p->B * p->n_q, per_cta = DA_MERGE_THREADS / 32;
+    const int merge_ctas = (units + per_cta - 1) / per_cta;
+    // the sharded return walks its units with a grid that is resident at once (one system-scope fence per CTA)
+    cudaLaunchConfig_t mcfg = da_pdl_config(ret != nullptr ? min(merge_ctas, sm_count() * 16) : merge_ctas, DA_MERGE_THREADS, 0, st, attr);
     if (ret != nullptr) {
         (void)cudaLaunchKernelEx(&mcfg, decode_return_kernel, d, *ret);
         rc = check_launch("decode_return_kernel");

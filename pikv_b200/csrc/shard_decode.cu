@@ -37,42 +37,43 @@ struct SDCtx {
     unsigned limit_us;
 };
 
-// One CTA per local stream: routing records to every rank, the query rows to the ranks that own a stripe of
-// either selected pair; the last CTA raises the flags.
-__global__ void __launch_bounds__(256) shard_decode_post_kernel(SDCtx x, const uint4* q_local, const int* topk_idx,
-                                                                const float* topk_w, const int* pair_len) {
+// One warp per local stream: routing records to every rank, the query rows to the ranks that own a stripe of
+// either selected pair; a CTA makes its eight streams' stores visible with one system-scope fence, the last CTA
+// raises the flags.
+constexpr int SD_POST_THREADS = 256;
+
+__global__ void __launch_bounds__(SD_POST_THREADS) shard_decode_post_kernel(SDCtx x, const uint4* q_local, const int* topk_idx,
+                                                                            const float* topk_w, const int* pair_len) {
     const pikv_shard_decode_ctx& c = x.c;
-    __shared__ unsigned mask_s;
-    const int sl = blockIdx.x, tid = threadIdx.x;
-    const int s = c.rank * c.streams_per_rank + sl;
-    if (tid == 0) mask_s = 0;
-    __syncthreads();
-    if (tid < c.top_k) {
-        const int e = topk_idx[sl * c.top_k + tid];
-        const bool ok = e >= 0 && e < c.num_experts;
-        const int len = ok ? max(0, pair_len[(size_t)sl * c.num_experts + e]) : 0;
-        if (!ok && c.status) atomicOr(c.status, PIKV_ST_BAD_SEQ);
-        const int4 rec = make_int4(ok ? e : 0, len, __float_as_int(topk_w[sl * c.top_k + tid]), 0);
-        for (int r = 0; r < c.world; ++r) static_cast<int4*>(c.peer_route[r])[(size_t)s * c.top_k + tid] = rec;
-        if (len > 0) {
-            const int rot = (c.expert_rot[e] + s) % c.world;
-            const int stripes = (len + (1 << x.log2_stripe) - 1) >> x.log2_stripe;
-            unsigned m = 0;
-            for (int cc = 0; cc < min(stripes, c.world); ++cc) m |= 1u << ((rot + cc) % c.world);
-            atomicOr(&mask_s, m);
+    const int lane = threadIdx.x & 31;
+    const int sl = blockIdx.x * (SD_POST_THREADS / 32) + (threadIdx.x >> 5);
+    if (sl < c.streams_per_rank) {
+        const int s = c.rank * c.streams_per_rank + sl;
+        unsigned m = 0;
+        if (lane < c.top_k) {
+            const int e = topk_idx[sl * c.top_k + lane];
+            const bool ok = e >= 0 && e < c.num_experts;
+            const int len = ok ? max(0, pair_len[(size_t)sl * c.num_experts + e]) : 0;
+            if (!ok && c.status) atomicOr(c.status, PIKV_ST_BAD_SEQ);
+            const int4 rec = make_int4(ok ? e : 0, len, __float_as_int(topk_w[sl * c.top_k + lane]), 0);
+            for (int r = 0; r < c.world; ++r) static_cast<int4*>(c.peer_route[r])[(size_t)s * c.top_k + lane] = rec;
+            if (len > 0) {
+                const int rot = (c.expert_rot[e] + s) % c.world;
+                const int stripes = (len + (1 << x.log2_stripe) - 1) >> x.log2_stripe;
+                for (int cc = 0; cc < min(stripes, c.world); ++cc) m |= 1u << ((rot + cc) % c.world);
+            }
         }
-    }
-    __syncthreads();
-    const unsigned mask = mask_s;
-    const int row16 = c.n_q * 16;                         // 16-byte words of one stream's query rows
-    for (int r = 0; r < c.world; ++r) {
-        if (!(mask >> r & 1u)) continue;
-        uint4* dst = static_cast<uint4*>(c.peer_q[r]) + (size_t)s * row16;
-        for (int i = tid; i < row16; i += blockDim.x) dst[i] = q_local[(size_t)sl * row16 + i];
+        const unsigned mask = __reduce_or_sync(0xffffffffu, m);
+        const int row16 = c.n_q * 16;                         // 16-byte words of one stream's query rows
+        for (int r = 0; r < c.world; ++r) {
+            if (!(mask >> r & 1u)) continue;
+            uint4* dst = static_cast<uint4*>(c.peer_q[r]) + (size_t)s * row16;
+            for (int i = lane; i < row16; i += 32) dst[i] = q_local[(size_t)sl * row16 + i];
+        }
     }
     __threadfence_system();
     __syncthreads();
-    if (tid == 0) {
+    if (threadIdx.x == 0) {
         const unsigned prev = atomicAdd(c.counters, 1u);
         if (prev == gridDim.x - 1) {
             c.counters[0] = 0;
@@ -112,18 +113,20 @@ __global__ void __launch_bounds__(256) shard_decode_plan_kernel(SDCtx x, int* se
     }
 }
 
-// One CTA per (local stream, query head), one thread per channel.
-__global__ void __launch_bounds__(128) shard_decode_combine_kernel(SDCtx x, const int* topk_idx, const float* topk_w,
-                                                                   const int* pair_len, __nv_bfloat16* out, float* lse_out,
-                                                                   int mode) {
+// One warp per (local stream, query head), a lane owns four channels; a grid that is resident at once walks the units,
+// so the wait for the ranks' "done" flags happens once per CTA (a system-scope poll per unit cost 38 us a step).
+constexpr int SD_COMBINE_THREADS = 128;
+
+__global__ void __launch_bounds__(SD_COMBINE_THREADS) shard_decode_combine_kernel(SDCtx x, const int* topk_idx, const float* topk_w,
+                                                                                  const int* pair_len, __nv_bfloat16* out,
+                                                                                  float* lse_out, int mode) {
     const pikv_shard_decode_ctx& c = x.c;
     __shared__ int ok_s;
-    const int sl = blockIdx.x / c.n_q, qg = blockIdx.x % c.n_q, ch = threadIdx.x;
-    const int s = c.rank * c.streams_per_rank + sl;
-    if (ch == 0) ok_s = 1;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) ok_s = 1;
     __syncthreads();
     const unsigned step = *c.seq & ~SD_FAILED;
-    if (ch < c.world && !sd_flag_wait(c.peer_done_flags[c.rank] + ch, step, x.limit_us)) {
+    if (threadIdx.x < c.world && !sd_flag_wait(c.peer_done_flags[c.rank] + threadIdx.x, step, x.limit_us)) {
         ok_s = 0;
         if (c.status) atomicOr(c.status, PIKV_ST_WAIT_TIMEOUT);
     }
@@ -131,42 +134,66 @@ __global__ void __launch_bounds__(128) shard_decode_combine_kernel(SDCtx x, cons
     if (!ok_s) return;
     const float* part_o = c.peer_part_o[c.rank];
     const float* part_lse = c.peer_part_lse[c.rank];
-    float res = 0.f, M_all = -INFINITY, den_all = 0.f;      // mode 1: running merge over the choices
-    for (int jsel = 0; jsel < c.top_k; ++jsel) {
-        const int e = topk_idx[sl * c.top_k + jsel];
-        if (e < 0 || e >= c.num_experts) continue;
-        const int len = max(0, pair_len[(size_t)sl * c.num_experts + e]);
-        const int rot = (c.expert_rot[e] + s) % c.world;
-        float M = -INFINITY;
-        float lse_r[8];
-        for (int r = 0; r < c.world; ++r) {
-            lse_r[r] = -INFINITY;
-            if (striped_local_len(len, rot, r, c.world, x.log2_stripe) > 0)
-                lse_r[r] = __ldcg(part_lse + (((size_t)sl * c.top_k + jsel) * c.world + r) * c.n_q + qg);
-            M = fmaxf(M, lse_r[r]);
+    const int units = c.streams_per_rank * c.n_q;
+    for (int unit = blockIdx.x * (SD_COMBINE_THREADS / 32) + (threadIdx.x >> 5); unit < units;
+         unit += gridDim.x * (SD_COMBINE_THREADS / 32)) {
+        const int sl = unit / c.n_q, qg = unit % c.n_q;
+        const int s = c.rank * c.streams_per_rank + sl;
+        float4 res = make_float4(0.f, 0.f, 0.f, 0.f);
+        float M_all = -INFINITY, den_all = 0.f;                 // mode 1: running merge over the choices
+        for (int jsel = 0; jsel < c.top_k; ++jsel) {
+            const int e = topk_idx[sl * c.top_k + jsel];
+            if (e < 0 || e >= c.num_experts) continue;
+            const int len = max(0, pair_len[(size_t)sl * c.num_experts + e]);
+            const int rot = (c.expert_rot[e] + s) % c.world;
+            const size_t base = ((size_t)sl * c.top_k + jsel) * c.world;
+            float M = -INFINITY;
+            float lse_r[8];
+            float4 o_r[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                lse_r[r] = -INFINITY;
+                o_r[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < c.world && striped_local_len(len, rot, r, c.world, x.log2_stripe) > 0) {
+                    // written by a peer during this kernel's lifetime: read at L2
+                    lse_r[r] = __ldcg(part_lse + (base + r) * c.n_q + qg);
+                    o_r[r] = __ldcg(reinterpret_cast<const float4*>(part_o + ((base + r) * c.n_q + qg) * 128) + lane);
+                }
+                M = fmaxf(M, lse_r[r]);
+            }
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float den = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (lse_r[r] == -INFINITY) continue;
+                const float wgt = expf(lse_r[r] - M);
+                acc.x += wgt * o_r[r].x; acc.y += wgt * o_r[r].y; acc.z += wgt * o_r[r].z; acc.w += wgt * o_r[r].w;
+                den += wgt;
+            }
+            const float4 o_j = den > 0.f ? make_float4(acc.x / den, acc.y / den, acc.z / den, acc.w / den)
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float lse_j = den > 0.f ? M + logf(den) : -INFINITY;
+            if (mode == 0) {
+                const float w = topk_w[sl * c.top_k + jsel];  // expert output times routing weight, summed
+                res.x += w * o_j.x; res.y += w * o_j.y; res.z += w * o_j.z; res.w += w * o_j.w;
+            } else if (lse_j != -INFINITY) {
+                const float Mn = fmaxf(M_all, lse_j);
+                const float a = M_all == -INFINITY ? 0.f : expf(M_all - Mn), b = expf(lse_j - Mn);
+                res.x = res.x * a + o_j.x * b; res.y = res.y * a + o_j.y * b;
+                res.z = res.z * a + o_j.z * b; res.w = res.w * a + o_j.w * b;
+                den_all = den_all * a + b;
+                M_all = Mn;
+            }
+            if (lse_out && lane == 0) lse_out[((size_t)sl * c.top_k + jsel) * c.n_q + qg] = lse_j;
         }
-        float acc = 0.f, den = 0.f;
-        for (int r = 0; r < c.world; ++r) {
-            if (lse_r[r] == -INFINITY) continue;
-            const float wgt = expf(lse_r[r] - M);
-            acc += wgt * __ldcg(part_o + ((((size_t)sl * c.top_k + jsel) * c.world + r) * c.n_q + qg) * 128 + ch);
-            den += wgt;
+        if (mode != 0) {
+            res = den_all > 0.f ? make_float4(res.x / den_all, res.y / den_all, res.z / den_all, res.w / den_all)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        const float o_j = den > 0.f ? acc / den : 0.f;
-        const float lse_j = den > 0.f ? M + logf(den) : -INFINITY;
-        if (mode == 0) {
-            res += topk_w[sl * c.top_k + jsel] * o_j;        // expert output times routing weight, summed
-        } else if (lse_j != -INFINITY) {
-            const float Mn = fmaxf(M_all, lse_j);
-            const float a = M_all == -INFINITY ? 0.f : expf(M_all - Mn), b = expf(lse_j - Mn);
-            res = res * a + o_j * b;
-            den_all = den_all * a + b;
-            M_all = Mn;
-        }
-        if (lse_out && ch == 0) lse_out[((size_t)sl * c.top_k + jsel) * c.n_q + qg] = lse_j;
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(res.x, res.y), hi = __floats2bfloat162_rn(res.z, res.w);
+        reinterpret_cast<uint2*>(out + ((size_t)sl * c.n_q + qg) * 128)[lane] =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     }
-    if (mode != 0) res = den_all > 0.f ? res / den_all : 0.f;
-    out[((size_t)sl * c.n_q + qg) * 128 + ch] = __float2bfloat16_rn(res);
 }
 
 static int sd_check(const pikv_shard_decode_ctx* c, SDCtx* x, const char* who) {
@@ -201,7 +228,8 @@ extern "C" int pikv_shard_decode_post(const pikv_shard_decode_ctx* c, const void
     int rc = sd_check(c, &x, "shard_decode_post");
     if (rc != PIKV_OK) return rc;
     PIKV_REQUIRE(q_local && topk_idx && topk_w && pair_len, PIKV_EINVAL, "shard_decode_post: null pointer");
-    shard_decode_post_kernel<<<c->streams_per_rank, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    const int post_ctas = (c->streams_per_rank + SD_POST_THREADS / 32 - 1) / (SD_POST_THREADS / 32);
+    shard_decode_post_kernel<<<post_ctas, SD_POST_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
         x, static_cast<const uint4*>(q_local), topk_idx, topk_w, pair_len);
     count_launch(1);
     return check_launch("shard_decode_post_kernel");
@@ -247,7 +275,9 @@ extern "C" int pikv_shard_decode_combine(const pikv_shard_decode_ctx* c, const i
     if (rc != PIKV_OK) return rc;
     PIKV_REQUIRE(topk_idx && topk_w && pair_len && out, PIKV_EINVAL, "shard_decode_combine: null pointer");
     PIKV_REQUIRE(mode == 0 || mode == 1, PIKV_EINVAL, "shard_decode_combine: mode must be 0 (weighted sum) or 1 (log-sum-exp merge)");
-    shard_decode_combine_kernel<<<c->streams_per_rank * c->n_q, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    const int units = c->streams_per_rank * c->n_q, per_cta = SD_COMBINE_THREADS / 32;
+    const int ctas = min((units + per_cta - 1) / per_cta, sm_count() * 4);
+    shard_decode_combine_kernel<<<ctas, SD_COMBINE_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
         x, topk_idx, topk_w, pair_len, static_cast<__nv_bfloat16*>(out), lse_out, mode);
     count_launch(1);
     return check_launch("shard_decode_combine_kernel");
