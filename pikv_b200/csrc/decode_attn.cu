@@ -816,6 +816,36 @@ __device__ __forceinline__ void da_merge_blocks(const DecodeDev& d, int rq, int 
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
     l = 0.f;
     auto slot = [&](int g) { return (((size_t)g + rq) * d.n_kv + h) * d.G + qh; };
+    if (g1 - g0 < 32) {
+        // the common case: all blocks' statistics in one warp-wide load, then the outputs
+        const int cnt = g1 - g0 + 1;
+        float2 ml = make_float2(-INFINITY, 0.f);
+        if (lane < cnt) ml = *reinterpret_cast<const float2*>(d.part_ml + slot(g0 + lane) * 2);
+        float mm = ml.x;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+        M = mm;
+        const float w_l = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M), l_l = ml.y;
+        int i = 0;
+        for (; i + 4 <= cnt; i += 4) {
+            float4 o4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) o4[u] = reinterpret_cast<const float4*>(d.part_o + slot(g0 + i + u) * 128)[lane];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float w = __shfl_sync(0xffffffffu, w_l, i + u);
+                acc.x += o4[u].x * w; acc.y += o4[u].y * w; acc.z += o4[u].z * w; acc.w += o4[u].w * w;
+                l += __shfl_sync(0xffffffffu, l_l, i + u) * w;
+            }
+        }
+        for (; i < cnt; ++i) {
+            const float4 o = reinterpret_cast<const float4*>(d.part_o + slot(g0 + i) * 128)[lane];
+            const float w = __shfl_sync(0xffffffffu, w_l, i);
+            acc.x += o.x * w; acc.y += o.y * w; acc.z += o.z * w; acc.w += o.w * w;
+            l += __shfl_sync(0xffffffffu, l_l, i) * w;
+        }
+        return;
+    }
     for (int gb = g0; gb <= g1; gb += 32) {
         const int g = gb + lane;
         float mm = g <= g1 ? d.part_ml[slot(g) * 2] : -INFINITY;
@@ -831,19 +861,7 @@ __device__ __forceinline__ void da_merge_blocks(const DecodeDev& d, int rq, int 
             w_l = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
             l_l = ml.y;
         }
-        int i = 0;
-        for (; i + 4 <= cnt; i += 4) {
-            float4 o4[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) o4[u] = reinterpret_cast<const float4*>(d.part_o + slot(gb + i + u) * 128)[lane];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float w = __shfl_sync(0xffffffffu, w_l, i + u);
-                acc.x += o4[u].x * w; acc.y += o4[u].y * w; acc.z += o4[u].z * w; acc.w += o4[u].w * w;
-                l += __shfl_sync(0xffffffffu, l_l, i + u) * w;
-            }
-        }
-        for (; i < cnt; ++i) {
+        for (int i = 0; i < cnt; ++i) {
             const float4 o = reinterpret_cast<const float4*>(d.part_o + slot(gb + i) * 128)[lane];
             const float w = __shfl_sync(0xffffffffu, w_l, i);
             acc.x += o.x * w; acc.y += o.y * w; acc.z += o.z * w; acc.w += o.w * w;
@@ -1050,7 +1068,7 @@ int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits
     const int units = p->B * p->n_q, per_cta = DA_MERGE_THREADS / 32;
     const int merge_ctas = (units + per_cta - 1) / per_cta;
     // the sharded return walks its units with a grid that is resident at once (one system-scope fence per CTA)
-    cudaLaunchConfig_t mcfg = da_pdl_config(ret != nullptr ? min(merge_ctas, sm_count() * 16) : merge_ctas, DA_MERGE_THREADS, 0, st, attr);
+    cudaLaunchConfig_t mcfg = da_pdl_config(ret != nullptr ? min(merge_ctas, sm_count() * 8) : merge_ctas, DA_MERGE_THREADS, 0, st, attr);
     if (ret != nullptr) {
         (void)cudaLaunchKernelEx(&mcfg, decode_return_kernel, d, *ret);
         rc = check_launch("decode_return_kernel");

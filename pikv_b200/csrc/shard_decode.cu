@@ -49,6 +49,13 @@ __global__ void __launch_bounds__(SD_POST_THREADS) shard_decode_post_kernel(SDCt
     const int sl = blockIdx.x * (SD_POST_THREADS / 32) + (threadIdx.x >> 5);
     if (sl < c.streams_per_rank) {
         const int s = c.rank * c.streams_per_rank + sl;
+        // the query rows are needed whatever the routing says: their loads go out before the dependent loads of the
+        // routing records (n_q <= 64: up to 32 words of 16 bytes per lane)
+        const int row16 = c.n_q * 16;                         // 16-byte words of one stream's query rows
+        uint4 qv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (lane + 32 * i < row16) qv[i] = q_local[(size_t)sl * row16 + lane + 32 * i];
         unsigned m = 0;
         if (lane < c.top_k) {
             const int e = topk_idx[sl * c.top_k + lane];
@@ -64,11 +71,12 @@ __global__ void __launch_bounds__(SD_POST_THREADS) shard_decode_post_kernel(SDCt
             }
         }
         const unsigned mask = __reduce_or_sync(0xffffffffu, m);
-        const int row16 = c.n_q * 16;                         // 16-byte words of one stream's query rows
         for (int r = 0; r < c.world; ++r) {
             if (!(mask >> r & 1u)) continue;
             uint4* dst = static_cast<uint4*>(c.peer_q[r]) + (size_t)s * row16;
-            for (int i = lane; i < row16; i += 32) dst[i] = q_local[(size_t)sl * row16 + i];
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (lane + 32 * i < row16) dst[lane + 32 * i] = qv[i];
         }
     }
     __threadfence_system();
@@ -199,8 +207,8 @@ __global__ void __launch_bounds__(SD_COMBINE_THREADS) shard_decode_combine_kerne
 static int sd_check(const pikv_shard_decode_ctx* c, SDCtx* x, const char* who) {
     PIKV_REQUIRE(c != nullptr, PIKV_EINVAL, "%s: null context", who);
     PIKV_REQUIRE(c->world >= 1 && c->world <= 8 && c->rank >= 0 && c->rank < c->world, PIKV_EINVAL, "%s: bad world / rank", who);
-    PIKV_REQUIRE(c->num_experts > 0 && c->num_streams > 0 && c->top_k > 0 && c->top_k <= 8 && c->n_q > 0, PIKV_EINVAL,
-                 "%s: bad sizes", who);
+    PIKV_REQUIRE(c->num_experts > 0 && c->num_streams > 0 && c->top_k > 0 && c->top_k <= 8 && c->n_q > 0 && c->n_q <= 64, PIKV_EINVAL,
+                 "%s: bad sizes (top_k <= 8, n_q <= 64)", who);
     PIKV_REQUIRE(c->streams_per_rank > 0 && c->streams_per_rank * c->world == c->num_streams, PIKV_EINVAL,
                  "%s: num_streams must be world * streams_per_rank", who);
     PIKV_REQUIRE(c->expert_rot && c->seq && c->counters, PIKV_EINVAL, "%s: null pointer", who);
