@@ -1196,23 +1196,47 @@ __global__ void h2o_accumulate_attn_kernel(const float* scores, int score_stride
 }
 
 // the same increment from the decode kernel's compact output: f16 probabilities relative to the maximum of their
-// softmax step, that maximum per 16-position page (log2 domain), and the final log-sum-exp
-__global__ void h2o_accumulate_probs_kernel(const __half* probs, int probs_stride, const float* step_max, int step_stride,
-                                            const float* lse, const int* seq_len, int B, int n_q, int n_kv, float* acc,
-                                            int acc_stride) {
-    const int pos = blockIdx.x * blockDim.x + threadIdx.x;
+// softmax step, that maximum per 16-position page (log2 domain), and the final log-sum-exp.  A thread owns eight
+// consecutive positions (one 16-byte load per query head, the step's factor once per thread, acc as two float4);
+// rows that are not 16-byte aligned, and the ragged end of a row, take the scalar path.
+__global__ void __launch_bounds__(256) h2o_accumulate_probs_kernel(const __half* probs, int probs_stride, const float* step_max,
+                                                                   int step_stride, const float* lse, const int* seq_len, int B,
+                                                                   int n_q, int n_kv, float* acc, int acc_stride, int vec_ok) {
+    const int pos0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     const int bh = blockIdx.y;
     const int b = bh / n_kv, h = bh % n_kv;
-    const int len = seq_len ? seq_len[b] : probs_stride;
-    if (pos >= len || pos >= acc_stride || pos >= probs_stride || (pos >> 4) >= step_stride) return;
+    int len = seq_len ? seq_len[b] : probs_stride;
+    len = min(min(len, acc_stride), min(probs_stride, step_stride * 16));
+    if (pos0 >= len) return;
     const int g = n_q / n_kv;
-    float s = 0.f;
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const bool full = vec_ok && pos0 + 8 <= len;
     for (int i = 0; i < g; ++i) {
         const size_t hq = (size_t)b * n_q + (size_t)h * g + i;
-        const float lse2 = lse[hq] * 1.4426950408889634f;
-        s += __half2float(probs[hq * probs_stride + pos]) * exp2f(step_max[hq * step_stride + (pos >> 4)] - lse2);
+        const float f = exp2f(step_max[hq * step_stride + (pos0 >> 4)] - lse[hq] * 1.4426950408889634f);
+        if (full) {
+            const uint4 v = ld_stream_16(probs + hq * probs_stride + pos0);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&w[q]));
+                s[2 * q] += p2.x * f;
+                s[2 * q + 1] += p2.y * f;
+            }
+        } else {
+            for (int e = 0; e < 8 && pos0 + e < len; ++e) s[e] += __half2float(probs[hq * probs_stride + pos0 + e]) * f;
+        }
     }
-    acc[(size_t)bh * acc_stride + pos] += s;
+    float* arow = acc + (size_t)bh * acc_stride + pos0;
+    if (full) {
+        float4 a0 = reinterpret_cast<float4*>(arow)[0], a1 = reinterpret_cast<float4*>(arow)[1];
+        a0.x += s[0]; a0.y += s[1]; a0.z += s[2]; a0.w += s[3];
+        a1.x += s[4]; a1.y += s[5]; a1.z += s[6]; a1.w += s[7];
+        reinterpret_cast<float4*>(arow)[0] = a0;
+        reinterpret_cast<float4*>(arow)[1] = a1;
+    } else {
+        for (int e = 0; e < 8 && pos0 + e < len; ++e) arow[e] += s[e];
+    }
 }
 
 }  // namespace pikv
@@ -1326,9 +1350,13 @@ extern "C" int pikv_h2o_accumulate_probs(const void* probs16, int32_t probs_stri
     PIKV_REQUIRE(probs16 && step_max && lse && acc, PIKV_EINVAL, "h2o_accumulate_probs: null pointer");
     PIKV_REQUIRE(B > 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0 && probs_stride > 0 && step_stride > 0 && acc_stride > 0,
                  PIKV_EINVAL, "h2o_accumulate_probs: bad sizes");
-    dim3 grid(ceil_div(min(probs_stride, acc_stride), 256), B * n_kv);
+    dim3 grid(ceil_div(min(probs_stride, acc_stride), 256 * 8), B * n_kv);
+    // eight positions of a page never straddle two softmax steps; vector accesses need 16-byte aligned rows
+    const int vec_ok = (reinterpret_cast<uintptr_t>(probs16) & 15) == 0 && (probs_stride & 7) == 0 &&
+                       (reinterpret_cast<uintptr_t>(acc) & 15) == 0 && (acc_stride & 3) == 0;
     h2o_accumulate_probs_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(probs16), probs_stride, step_max, step_stride, lse, seq_len, B, n_q, n_kv, acc, acc_stride);
+        static_cast<const __half*>(probs16), probs_stride, step_max, step_stride, lse, seq_len, B, n_q, n_kv, acc, acc_stride,
+        vec_ok);
     count_launch(1);
     return check_launch("h2o_accumulate_probs_kernel");
 }
