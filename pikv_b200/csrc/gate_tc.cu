@@ -90,7 +90,9 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
     bool failed = false;
     // a kernel launched as a programmatic dependent of this one (the fused append) may be scheduled from here on;
-    // it waits for this grid's completion before it reads anything written here
+    // it waits for this grid's completion before it reads anything written here.  (This kernel itself is launched
+    // the plain way: as a programmatic dependent of the previous batch's gate its waiting CTAs kept the SMs' registers
+    // busy, the append kernel of the pipelined schedule then ran in two waves, and the step got 4 % slower.)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {

@@ -194,7 +194,7 @@ __device__ __forceinline__ void qg_quantize16(const float (&x)[16], float mn, fl
                 // into nibbles (low nibble = even channel) and the four merged bytes gathered
                 int c[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) c[j] = min(max(n[8 * i + j], 0), 15);
+                for (int j = 0; j < 8; ++j) c[j] = min(n[8 * i + j], 15);      // the pack below saturates at 0
                 uint32_t a = qg_pack4_u8(c[0], c[1], c[2], c[3]), b = qg_pack4_u8(c[4], c[5], c[6], c[7]);
                 a |= a >> 4;
                 b |= b >> 4;
@@ -309,6 +309,37 @@ struct GroupQuant {
         float mn, mx;
         qg_group_minmax(r.x, mn, mx);
         qg_quantize16<BITS, SYM>(r.x, mn, mx, qp, w);
+    }
+};
+// bf16 in, any other format out: the raw words stay packed while an item waits in the software pipeline (half the
+// registers of sixteen floats per tensor), the group's minimum and maximum come from packed bf16 min / max (exact:
+// they only select), and the floats exist only inside quant().
+template <int BITS, bool SYM>
+struct GroupQuant<__nv_bfloat16, BITS, SYM> {
+    struct Raw { uint4 a, b; };
+    static __device__ __forceinline__ void load(const __nv_bfloat16* src, Raw& r) {
+        r.a = __ldg(reinterpret_cast<const uint4*>(src));
+        r.b = __ldg(reinterpret_cast<const uint4*>(src + 8));
+    }
+    static __device__ __forceinline__ void quant(const Raw& r, QParams& qp, uint32_t (&w)[4]) {
+        const uint32_t ww[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
+        uint32_t hi2 = ww[0], lo2 = ww[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+            asm("max.bf16x2 %0, %0, %1;" : "+r"(hi2) : "r"(ww[i]));
+            asm("min.bf16x2 %0, %0, %1;" : "+r"(lo2) : "r"(ww[i]));
+        }
+        float mx = fmaxf(__uint_as_float(hi2 << 16), __uint_as_float(hi2 & 0xffff0000u));
+        float mn = fminf(__uint_as_float(lo2 << 16), __uint_as_float(lo2 & 0xffff0000u));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bf16x2_to_f32(ww[i], x[2 * i], x[2 * i + 1]);
+        qg_quantize16<BITS, SYM>(x, mn, mx, qp, w);
     }
 };
 template <>
