@@ -1083,98 +1083,158 @@ struct CompactDev {
     int heads_per;   // heads moved per segment
 };
 
-// Eight lanes move one row (16 bytes each of K and of V).  A group handles COMPACT_ITEMS rows with every stage of
-// the dependent chain (kept index -> page ids -> row) issued for all of them before the next stage: four times
-// the loads in flight of one row per group, which is what a gather of scattered 128-byte rows needs to keep HBM busy.
-constexpr int COMPACT_ITEMS = 4;
+// Eight lanes move one row (16 bytes each of K and of V); a group handles COMPACT_ITEMS rows per tile.  The chain
+// kept index -> page ids -> row is three dependent loads deep: a CTA walks several tiles of its segment as a software
+// pipeline, loading the kept indices of tile t+2 and the page ids of tile t+1 while the rows of tile t are in flight.
+// A bare gather of this pattern (scattered 128-byte rows, one in sixteen, contiguous writes) runs at 5.9 TB/s; what
+// separates this kernel from it is instruction count (the launch was issue-bound at 104 warp instructions per row
+// before the loop was slimmed: no division by the head count, 32-bit pool rows, one predicated side load per lane) and
+// the sector-sized reads behind the 2- and 4-byte side values.  Two rows per group at five CTAs per SM measured best
+// (four rows at three CTAs: 139 us, one row at eight: 131 us, two at five: 127 us).
+constexpr int COMPACT_ITEMS = 2;
+constexpr int COMPACT_TILE = 256 / 8 * COMPACT_ITEMS;     // rows (x head slots) of one tile
 
-__global__ void __launch_bounds__(256, 4) h2o_compact_kernel(CompactDev c) {
+struct CompactTile {          // what a group knows about its COMPACT_ITEMS rows of one tile
+    int j[COMPACT_ITEMS], spos[COMPACT_ITEMS], spage[COMPACT_ITEMS], dpage[COMPACT_ITEMS];
+};
+
+// PER_HEAD: one segment per (sequence, head) and one head slot per row (no division by the head count in the loop).
+// The six side values of a row (two scales, two zero points, score, timestamp) are moved by lanes 0..5 of its group:
+// every lane fixes its source, destination, element size and index kind once, so the loop has one predicated load
+// and one store per row for them instead of a six-way branch.
+template <bool PER_HEAD>
+__global__ void __launch_bounds__(256, 5) h2o_compact_kernel(CompactDev c) {
     const pikv_compact_params& p = c.p;
     const int seg = blockIdx.x;
-    const int sub = threadIdx.x & 7;
-    const int kept = min(p.kept_count[seg], p.keep_stride);
-    const int seq = p.per_head ? seg / p.n_kv : seg;
+    const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
+    const int seq = PER_HEAD ? seg / p.n_kv : seg;
+    const int seg_head = PER_HEAD ? seg % p.n_kv : 0;
     constexpr int PTK = PIKV_PAGE_TOKENS;
     if (seq >= p.num_seqs) {
         if (p.status && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(p.status, PIKV_ST_BAD_INDEX);
         return;
     }
-    int j[COMPACT_ITEMS], hs[COMPACT_ITEMS], spos[COMPACT_ITEMS], spage[COMPACT_ITEMS], dpage[COMPACT_ITEMS];
-    bool on[COMPACT_ITEMS];
-#pragma unroll
-    for (int i = 0; i < COMPACT_ITEMS; ++i) {
-        const int item = ((blockIdx.y * COMPACT_ITEMS + i) * blockDim.x + threadIdx.x) >> 3;   // (row j, head slot)
-        j[i] = item / c.heads_per;
-        hs[i] = item % c.heads_per;
-        on[i] = j[i] < kept;
-        spos[i] = on[i] ? __ldg(p.keep_idx + (size_t)seg * p.keep_stride + j[i]) : 0;
-    }
-#pragma unroll
-    for (int i = 0; i < COMPACT_ITEMS; ++i) {
-        if (on[i] && (spos[i] < 0 || spos[i] / PTK >= p.max_pages || j[i] / PTK >= p.max_pages ||
-                      (p.score_stride > 0 && spos[i] >= p.score_stride))) {
-            if (p.status && sub == 0) atomicOr(p.status, PIKV_ST_BAD_INDEX);
-            on[i] = false;
-        }
-        spage[i] = on[i] ? __ldg(p.src_page_table + (size_t)seq * p.max_pages + spos[i] / PTK) : 0;
-        dpage[i] = on[i] ? __ldg(p.dst_page_table + (size_t)seq * p.max_pages + j[i] / PTK) : 0;
-    }
-    uint4 kc[COMPACT_ITEMS], vc[COMPACT_ITEMS];
-    uint32_t side[COMPACT_ITEMS];      // lane 0: K scale, 1: V scale, 2: K zero point, 3: V zero point, 4: score, 5: timestamp
+    const int heads_per = PER_HEAD ? 1 : c.heads_per;
+    const int items_cap = p.keep_stride * heads_per;              // (row, head slot) items of a segment, at most
+    const int tiles = (items_cap + COMPACT_TILE - 1) / COMPACT_TILE;
+    const int dstride = p.dst_score_stride > 0 ? p.dst_score_stride : p.score_stride;
     const bool has_zp = p.src_k_zp && p.dst_k_zp, has_acc = p.src_acc && p.dst_acc, has_ts = p.src_ts && p.dst_ts;
+    // this lane's side value: element size (0: none), whether it is indexed by the pool row or by the score position
+    const unsigned char* side_src = nullptr;
+    unsigned char* side_dst = nullptr;
+    int side_size = 0;
+    const bool side_by_row = sub < 4;
+    if (sub == 0) side_src = static_cast<const unsigned char*>(p.src_k_scale), side_dst = static_cast<unsigned char*>(p.dst_k_scale), side_size = 2;
+    else if (sub == 1) side_src = static_cast<const unsigned char*>(p.src_v_scale), side_dst = static_cast<unsigned char*>(p.dst_v_scale), side_size = 2;
+    else if (sub == 2 && has_zp) side_src = static_cast<const unsigned char*>(p.src_k_zp), side_dst = static_cast<unsigned char*>(p.dst_k_zp), side_size = 4;
+    else if (sub == 3 && has_zp) side_src = static_cast<const unsigned char*>(p.src_v_zp), side_dst = static_cast<unsigned char*>(p.dst_v_zp), side_size = 4;
+    else if (sub == 4 && has_acc) side_src = reinterpret_cast<const unsigned char*>(p.src_acc + (size_t)seg * p.score_stride), side_dst = reinterpret_cast<unsigned char*>(p.dst_acc + (size_t)seg * dstride), side_size = 4;
+    else if (sub == 5 && has_ts) side_src = reinterpret_cast<const unsigned char*>(p.src_ts + (size_t)seg * p.score_stride), side_dst = reinterpret_cast<unsigned char*>(p.dst_ts + (size_t)seg * dstride), side_size = 4;
+    const int* keep_row = p.keep_idx + (size_t)seg * p.keep_stride;
+    const int* spt_row = p.src_page_table + (size_t)seq * p.max_pages;
+    const int* dpt_row = p.dst_page_table + (size_t)seq * p.max_pages;
+    const unsigned char* sk = static_cast<const unsigned char*>(p.src_k_codes);
+    const unsigned char* sv = static_cast<const unsigned char*>(p.src_v_codes);
+    unsigned char* dk = static_cast<unsigned char*>(p.dst_k_codes);
+    unsigned char* dv = static_cast<unsigned char*>(p.dst_v_codes);
+    const bool b8 = p.bits == 8;
+
+    // stage 1: the kept indices of a tile (speculative: rows past the kept count are dropped in stage 2)
+    auto load_idx = [&](int tile, CompactTile& t) {
 #pragma unroll
-    for (int i = 0; i < COMPACT_ITEMS; ++i) {
-        if (on[i] && (spage[i] < 0 || spage[i] >= p.num_pages || dpage[i] < 0 || dpage[i] >= p.num_pages)) {
-            if (p.status && sub == 0) atomicOr(p.status, PIKV_ST_BAD_PAGE);
-            on[i] = false;
+        for (int i = 0; i < COMPACT_ITEMS; ++i) {
+            const int item = tile * COMPACT_TILE + i * 32 + grp;
+            t.j[i] = PER_HEAD ? item : item / heads_per;
+            t.spos[i] = (tile < tiles && t.j[i] < p.keep_stride) ? __ldg(keep_row + t.j[i]) : -1;
         }
-        kc[i] = vc[i] = make_uint4(0u, 0u, 0u, 0u);
-        side[i] = 0u;
-        if (!on[i]) continue;
-        const int head = p.per_head ? seg % p.n_kv : hs[i];
-        const int srow = spos[i] % PTK;
-        const size_t sprow = ((size_t)spage[i] * p.n_kv + head) * PTK + srow;
-        if (p.bits == 8) {
-            const size_t so = sprow * 128 + 16 * swz8_chunk(srow, sub);
-            kc[i] = ld_stream_16(static_cast<const uint8_t*>(p.src_k_codes) + so);
-            vc[i] = ld_stream_16(static_cast<const uint8_t*>(p.src_v_codes) + so);
-        } else {
-            const size_t so = sprow * 64 + 8 * swz4_unit(srow, sub);
-            const uint2 a2 = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.src_k_codes) + so);
-            const uint2 b2 = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.src_v_codes) + so);
-            kc[i].x = a2.x; kc[i].y = a2.y;
-            vc[i].x = b2.x; vc[i].y = b2.y;
-        }
-        const size_t spt = (size_t)seg * p.score_stride + spos[i];
-        if (sub == 0) side[i] = static_cast<const uint16_t*>(p.src_k_scale)[sprow];
-        else if (sub == 1) side[i] = static_cast<const uint16_t*>(p.src_v_scale)[sprow];
-        else if (sub == 2 && has_zp) side[i] = __float_as_uint(static_cast<const float*>(p.src_k_zp)[sprow]);
-        else if (sub == 3 && has_zp) side[i] = __float_as_uint(static_cast<const float*>(p.src_v_zp)[sprow]);
-        else if (sub == 4 && has_acc && hs[i] == 0) side[i] = __float_as_uint(p.src_acc[spt]);
-        else if (sub == 5 && has_ts && hs[i] == 0) side[i] = __float_as_uint(p.src_ts[spt]);
-    }
+    };
+    // stage 2: page ids (spos < 0 afterwards: nothing to move)
+    auto load_pages = [&](int kept, CompactTile& t) {
 #pragma unroll
-    for (int i = 0; i < COMPACT_ITEMS; ++i) {
-        if (!on[i]) continue;
-        const int head = p.per_head ? seg % p.n_kv : hs[i];
-        const int drow = j[i] % PTK;
-        const size_t dprow = ((size_t)dpage[i] * p.n_kv + head) * PTK + drow;
-        if (p.bits == 8) {
-            const size_t dofs = dprow * 128 + 16 * swz8_chunk(drow, sub);
-            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dst_k_codes) + dofs) = kc[i];
-            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dst_v_codes) + dofs) = vc[i];
-        } else {
-            const size_t dofs = dprow * 64 + 8 * swz4_unit(drow, sub);
-            *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.dst_k_codes) + dofs) = make_uint2(kc[i].x, kc[i].y);
-            *reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.dst_v_codes) + dofs) = make_uint2(vc[i].x, vc[i].y);
+        for (int i = 0; i < COMPACT_ITEMS; ++i) {
+            bool on = t.spos[i] >= 0 && t.j[i] < kept;
+            if (t.j[i] < kept && (t.spos[i] < 0 || t.spos[i] / PTK >= p.max_pages || t.j[i] / PTK >= p.max_pages ||
+                                  (p.score_stride > 0 && t.spos[i] >= p.score_stride))) {
+                if (p.status && sub == 0) atomicOr(p.status, PIKV_ST_BAD_INDEX);
+                on = false;
+            }
+            t.spage[i] = on ? __ldg(spt_row + t.spos[i] / PTK) : 0;
+            t.dpage[i] = on ? __ldg(dpt_row + t.j[i] / PTK) : 0;
+            if (!on) t.spos[i] = -1;
         }
-        const size_t dpt = (size_t)seg * (p.dst_score_stride > 0 ? p.dst_score_stride : p.score_stride) + j[i];
-        if (sub == 0) static_cast<uint16_t*>(p.dst_k_scale)[dprow] = (uint16_t)side[i];
-        else if (sub == 1) static_cast<uint16_t*>(p.dst_v_scale)[dprow] = (uint16_t)side[i];
-        else if (sub == 2 && has_zp) static_cast<float*>(p.dst_k_zp)[dprow] = __uint_as_float(side[i]);
-        else if (sub == 3 && has_zp) static_cast<float*>(p.dst_v_zp)[dprow] = __uint_as_float(side[i]);
-        else if (sub == 4 && has_acc && hs[i] == 0) p.dst_acc[dpt] = __uint_as_float(side[i]);
-        else if (sub == 5 && has_ts && hs[i] == 0) p.dst_ts[dpt] = __uint_as_float(side[i]);
+    };
+
+    const int kept = min(__ldg(p.kept_count + seg), p.keep_stride);
+    CompactTile cur, nxt, nxt2;
+    int tile = blockIdx.y;
+    load_idx(tile, cur);
+    load_idx(tile + gridDim.y, nxt);
+    load_pages(kept, cur);
+    for (; tile < tiles; tile += gridDim.y) {
+        load_idx(tile + 2 * gridDim.y, nxt2);
+        // stage 3: the rows of this tile
+        uint4 kc[COMPACT_ITEMS], vc[COMPACT_ITEMS];
+        uint32_t side[COMPACT_ITEMS];
+        unsigned dprow[COMPACT_ITEMS];        // destination pool row (pools hold fewer than 2^31 rows)
+#pragma unroll
+        for (int i = 0; i < COMPACT_ITEMS; ++i) {
+            bool on = cur.spos[i] >= 0;
+            if (on && ((unsigned)cur.spage[i] >= (unsigned)p.num_pages || (unsigned)cur.dpage[i] >= (unsigned)p.num_pages)) {
+                if (p.status && sub == 0) atomicOr(p.status, PIKV_ST_BAD_PAGE);
+                on = false;
+                cur.spos[i] = -1;
+            }
+            kc[i] = vc[i] = make_uint4(0u, 0u, 0u, 0u);
+            side[i] = 0u;
+            dprow[i] = 0u;
+            if (!on) continue;
+            int hs = 0;
+            if (!PER_HEAD) hs = (tile * COMPACT_TILE + i * 32 + grp) % heads_per;
+            const int head = PER_HEAD ? seg_head : hs;
+            const int srow = cur.spos[i] % PTK, drow = cur.j[i] % PTK;
+            const unsigned sprow = ((unsigned)cur.spage[i] * (unsigned)p.n_kv + (unsigned)head) * PTK + (unsigned)srow;
+            dprow[i] = ((unsigned)cur.dpage[i] * (unsigned)p.n_kv + (unsigned)head) * PTK + (unsigned)drow;
+            if (b8) {
+                const size_t so = (size_t)sprow * 128 + 16 * swz8_chunk(srow, sub);
+                kc[i] = ld_stream_16(sk + so);
+                vc[i] = ld_stream_16(sv + so);
+            } else {
+                const size_t so = (size_t)sprow * 64 + 8 * swz4_unit(srow, sub);
+                const uint2 a2 = *reinterpret_cast<const uint2*>(sk + so);
+                const uint2 b2 = *reinterpret_cast<const uint2*>(sv + so);
+                kc[i].x = a2.x; kc[i].y = a2.y;
+                vc[i].x = b2.x; vc[i].y = b2.y;
+            }
+            if (side_size != 0 && (side_by_row || hs == 0)) {
+                const size_t at = side_by_row ? (size_t)sprow : (size_t)cur.spos[i];
+                side[i] = side_size == 2 ? (uint32_t)*reinterpret_cast<const uint16_t*>(side_src + at * 2)
+                                         : *reinterpret_cast<const uint32_t*>(side_src + at * 4);
+            }
+        }
+        load_pages(kept, nxt);                 // the next tile's indices have had a tile's time to arrive
+#pragma unroll
+        for (int i = 0; i < COMPACT_ITEMS; ++i) {
+            if (cur.spos[i] < 0) continue;
+            const int drow = cur.j[i] % PTK;
+            if (b8) {
+                const size_t dofs = (size_t)dprow[i] * 128 + 16 * swz8_chunk(drow, sub);
+                *reinterpret_cast<uint4*>(dk + dofs) = kc[i];
+                *reinterpret_cast<uint4*>(dv + dofs) = vc[i];
+            } else {
+                const size_t dofs = (size_t)dprow[i] * 64 + 8 * swz4_unit(drow, sub);
+                *reinterpret_cast<uint2*>(dk + dofs) = make_uint2(kc[i].x, kc[i].y);
+                *reinterpret_cast<uint2*>(dv + dofs) = make_uint2(vc[i].x, vc[i].y);
+            }
+            int hs = 0;
+            if (!PER_HEAD) hs = (tile * COMPACT_TILE + i * 32 + grp) % heads_per;
+            if (side_size != 0 && (side_by_row || hs == 0)) {
+                const size_t at = side_by_row ? (size_t)dprow[i] : (size_t)cur.j[i];
+                if (side_size == 2) *reinterpret_cast<uint16_t*>(side_dst + at * 2) = (uint16_t)side[i];
+                else *reinterpret_cast<uint32_t*>(side_dst + at * 4) = side[i];
+            }
+        }
+        cur = nxt;
+        nxt = nxt2;
     }
 }
 
@@ -1338,8 +1398,18 @@ extern "C" int pikv_h2o_compact(const pikv_compact_params* p, pikv_stream_t stre
     c.heads_per = p->per_head ? 1 : p->n_kv;
     const int segments = p->per_head ? p->num_seqs * p->n_kv : p->num_seqs;
     const long long lanes = (long long)p->keep_stride * c.heads_per * 8;
-    dim3 grid(segments, (unsigned)ceil_div64(lanes, 256 * COMPACT_ITEMS));
-    h2o_compact_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c);
+    // a CTA walks up to four tiles of its segment (software pipeline); enough CTAs to fill the GPU a few times over
+    const long long tiles = ceil_div64(lanes, 256 * COMPACT_ITEMS);
+    long long per_seg = ceil_div64(tiles, 4);                        // four tiles per CTA ...
+    const long long fill = (long long)sm_count() * 12 / segments;    // ... unless that leaves SMs idle
+    if (per_seg < fill) per_seg = fill;
+    if (per_seg > tiles) per_seg = tiles;
+    if (per_seg < 1) per_seg = 1;
+    dim3 grid(segments, (unsigned)per_seg);
+    PIKV_REQUIRE((long long)p->num_pages * p->n_kv * PIKV_PAGE_TOKENS < (1ll << 31), PIKV_ELIMIT,
+                 "h2o_compact: the pools must hold fewer than 2^31 rows");
+    if (p->per_head) h2o_compact_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c);
+    else h2o_compact_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(c);
     count_launch(1);
     return check_launch("h2o_compact_kernel");
 }
