@@ -1181,6 +1181,28 @@ def secondary_arm(args):
                  {"bound": "hbm", "kernel": "lowrank_gemm_kernel", "achieved": gbs, "peak": peak, "peak_source": peak_src,
                   "unit": "GB/s", "frac": gbs / peak, "traffic": None, "TFLOPs": tf}, steps)
         assert pikv_b200.lib().pikv_lowrank_error_state() == 0
+    elif args.workload == "gate_net":
+        # the two-layer gate net with its tail (tensor-bound); --rows tokens (a small count for profiler captures)
+        Tn, Hn, En = args.rows, WORKLOAD["hidden"], WORKLOAD["experts"]
+        gx = torch.randn(Tn, Hn, device=dev).bfloat16()
+        gw1 = (torch.randn(Hn, Hn, device=dev) / Hn ** 0.5).bfloat16()
+        gb1 = torch.zeros(Hn, device=dev)
+        gw2, gb2 = gate_weights(Hn, En, 7)
+        gw2, gb2 = gw2.to(dev), gb2.to(dev)
+        capn = int(Tn * WORKLOAD["capacity_factor"] * WORKLOAD["top_k"] / En)
+        gout = ops.gate_mlp_fused(gx, gw1, gb1, gw2, gb2, top_k=2, capacity=capn)
+        ms = timed(lambda: ops.gate_mlp_fused(gx, gw1, gb1, gw2, gb2, top_k=2, capacity=capn, out=gout), steps)
+        assert pikv_b200.lib().pikv_gate_error_state() == 0
+        flops = 2.0 * Tn * Hn * Hn + 2.0 * Tn * Hn * En
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                tf_peak = float(json.load(f)["bf16_tflops_sustained"])
+        except Exception:
+            tf_peak = 1400.0
+        tf = flops / (ms * 1e-3) / 1e12
+        emit("gate_net_TFLOPs", "TFLOP/s", tf, ms, {"workload": "gate net (two layers + tail)", "tokens": Tn, "hidden": Hn, "experts": En},
+             {"bound": "tensor", "kernel": "gate_mlp_kernel", "achieved": tf, "peak": tf_peak, "peak_source": "measured (sustained bf16)",
+              "unit": "TFLOP/s", "frac": tf / tf_peak, "traffic": None}, steps)
 
 
 def main():
@@ -1198,7 +1220,7 @@ def main():
     ap.add_argument("--no-sharded", action="store_true", help="skip the expert-sharded configuration (striped cache: prefill + decode step)")
     ap.add_argument("--multi-warmup-s", type=float, default=3.0,
                     help="multi-GPU: seconds of untimed steps before the timed regions (stated in the line as warmup_s)")
-    ap.add_argument("--workload", default="append", choices=["append", "decode", "lowrank"],
+    ap.add_argument("--workload", default="append", choices=["append", "decode", "lowrank", "gate_net"],
                     help="append = the headline route+quantise+append step; the others print lines for the other kernels")
     ap.add_argument("--streams", type=int, default=64)
     ap.add_argument("--context", type=int, default=32768)
