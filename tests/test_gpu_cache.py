@@ -493,13 +493,14 @@ def test_decode_h2o_update_from_compact_probabilities(dev, B, n_q, n_kv, ctx):
 
 
 # ---------------------------------------------------------------- compaction
+@pytest.mark.parametrize("bits", [8, 4])
 @pytest.mark.parametrize("per_head", [True, False])
-def test_h2o_compact_moves_rows_and_scores(dev, per_head):
+def test_h2o_compact_moves_rows_and_scores(dev, per_head, bits):
     import pikv_b200
     from pikv_b200 import ops
     B, n_kv, ctx = 3, 2, 200
     lens = np.array([200, 150, 64], np.int32)
-    cache, kd, vd = fill_stream_cache(dev, B, n_kv, ctx, lens, 5)
+    cache, kd, vd = fill_stream_cache(dev, B, n_kv, ctx, lens, 5, bits=bits, symmetric=(bits == 8), shift=0.0 if bits == 8 else 0.5)
     segs = B * n_kv if per_head else B
     rng = np.random.default_rng(0)
     acc = rng.random((segs, ctx)).astype(F32)
@@ -507,7 +508,7 @@ def test_h2o_compact_moves_rows_and_scores(dev, per_head):
     seg_len = np.repeat(lens, n_kv) if per_head else lens
     mask, keep, cnt = ops.h2o_select(torch.from_numpy(acc).to(dev), torch.from_numpy(ts).to(dev), 40, 8,
                                      seg_len=torch.from_numpy(seg_len.astype(np.int32)).to(dev))
-    dst = pikv_b200.PagedKVCache(B, ctx, n_kv, device=dev)
+    dst = pikv_b200.PagedKVCache(B, ctx, n_kv, bits=bits, symmetric=(bits == 8), device=dev)
     # destination score rows as long as the source's, or only as long as the kept-index rows
     width = keep.shape[1] if per_head else ctx
     dacc = torch.zeros(segs, width, device=dev)
