@@ -73,9 +73,15 @@ __device__ __forceinline__ void token_tail(float (&l)[EP], const GateDev& g, int
 #pragma unroll
     for (int e = 0; e < EP; ++e) l[e] = __fdiv_rn(l[e], s);
     if (g.probs) {
+        if (EP == 8 && E == 8 && (reinterpret_cast<uintptr_t>(g.probs) & 15) == 0) {     // one 32-byte row: two vector stores
+            float4* row = reinterpret_cast<float4*>(g.probs + (size_t)t * 8);
+            row[0] = make_float4(l[0], l[1], l[2], l[3]);
+            row[1] = make_float4(l[4 % EP], l[5 % EP], l[6 % EP], l[7 % EP]);
+        } else {
 #pragma unroll
-        for (int e = 0; e < EP; ++e)
-            if (e < E) g.probs[(size_t)t * E + e] = l[e];
+            for (int e = 0; e < EP; ++e)
+                if (e < E) g.probs[(size_t)t * E + e] = l[e];
+        }
     }
     // top-k on the probabilities; strict '>' keeps the lowest index on ties
     unsigned long long taken = 0ull;

@@ -141,6 +141,10 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
         const int lg = warp & 3;                      // tensor-memory lane group of this warp
         const int row = lg * 32 + lane;               // token row inside a tile
         for (int i = et; i < GT_EPI_WARPS * EP; i += GT_EPI) psum_w[i] = 0.f;
+        // the bias is needed the moment the first accumulator arrives: its loads go out now
+        float bias[EL];
+#pragma unroll
+        for (int e = 0; e < EL; ++e) bias[e] = (g.b2 && e < g.E) ? __ldg(g.b2 + e) : 0.f;
         epi_barrier();
         for (int lt = 0; lt < ntiles; ++lt) {
             const int slot = lt & 1;
@@ -160,11 +164,8 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
             const int lt_tok = lt * LR_BM + row;      // token index inside the chunk
             const bool valid = lt_tok < ntok;
             if (valid) {
-                if (g.b2) {
 #pragma unroll
-                    for (int e = 0; e < EL; ++e)
-                        if (e < g.E) l[e] += __ldg(g.b2 + e);
-                }
+                for (int e = 0; e < EL; ++e) l[e] += bias[e];
                 token_tail<EL>(l, g, chunk_start + lt_tok, sel + (size_t)lt_tok * g.k);
             }
 #pragma unroll
