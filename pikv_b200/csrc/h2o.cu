@@ -724,7 +724,8 @@ __device__ __forceinline__ int ss_shift_for(uint32_t width) {      // (width >> 
 }
 
 // Where the m largest of src[0..n) are, ties to the lowest index: fills *out (shared memory) for the last pass.
-template <int NT>
+// ASCENDING_CHECK: whether pass 1 also tests for ascending keys (worth it for timestamps; for scores it only costs)
+template <int NT, bool ASCENDING_CHECK>
 __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligned, SsShared& sh, SsResult* out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (m <= 0 || m >= n) {
@@ -751,13 +752,15 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
                     const int i = i0 + u * NT + tid;
                     const bool on = i < n4;
                     const uint4 k = ss_keys4(f[u]);
-                    uint32_t next = __shfl_down_sync(0xffffffffu, k.x, 1);          // the key after this thread's four
-                    const bool has_next = 4 * i + 4 < n;
-                    if (on && has_next && (lane == 31 || i + 1 >= n4)) next = order_key(__ldg(src + 4 * (size_t)i + 4));
+                    if (ASCENDING_CHECK) {
+                        uint32_t next = __shfl_down_sync(0xffffffffu, k.x, 1);      // the key after this thread's four
+                        const bool has_next = 4 * i + 4 < n;
+                        if (on && has_next && (lane == 31 || i + 1 >= n4)) next = order_key(__ldg(src + 4 * (size_t)i + 4));
+                        if (on) ok &= k.x <= k.y && k.y <= k.z && k.z <= k.w && (!has_next || k.w <= next);
+                    }
                     if (on) {
                         mn = min(mn, min(min(k.x, k.y), min(k.z, k.w)));
                         mx = max(mx, max(max(k.x, k.y), max(k.z, k.w)));
-                        ok &= k.x <= k.y && k.y <= k.z && k.z <= k.w && (!has_next || k.w <= next);
                     }
                 }
             }
@@ -766,7 +769,7 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
                     const uint32_t u = order_key(__ldg(src + i));
                     mn = min(mn, u);
                     mx = max(mx, u);
-                    if (i + 1 < n) ok &= u <= order_key(__ldg(src + i + 1));
+                    if (ASCENDING_CHECK && i + 1 < n) ok &= u <= order_key(__ldg(src + i + 1));
                 }
             }
         } else {
@@ -774,9 +777,10 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
                 const uint32_t u = order_key(__ldg(src + i));
                 mn = min(mn, u);
                 mx = max(mx, u);
-                if (i + 1 < n) ok &= u <= order_key(__ldg(src + i + 1));
+                if (ASCENDING_CHECK && i + 1 < n) ok &= u <= order_key(__ldg(src + i + 1));
             }
         }
+        if (!ASCENDING_CHECK) ok = false;
         mn = __reduce_min_sync(0xffffffffu, mn);
         mx = __reduce_max_sync(0xffffffffu, mx);
         const bool all_ok = __all_sync(0xffffffffu, ok);
@@ -999,8 +1003,8 @@ __global__ void __launch_bounds__(NT, 1024 / NT) h2o_select_stream_kernel(const 
     const bool al_a = (reinterpret_cast<uintptr_t>(a) & 15) == 0, al_t = (reinterpret_cast<uintptr_t>(t) & 15) == 0;
     // the timestamps first: they are read once, the scores up to four times, and read last the scores are the
     // array still in L2 when the later passes come back to them
-    ss_find<NT>(t, n, min(num_recent, n), al_t, sh, &sh.res[1]);
-    ss_find<NT>(a, n, min(num_heavy, n), al_a, sh, &sh.res[0]);
+    ss_find<NT, true>(t, n, min(num_recent, n), al_t, sh, &sh.res[1]);
+    ss_find<NT, false>(a, n, min(num_heavy, n), al_a, sh, &sh.res[0]);
     __syncthreads();
     const SsResult ra = sh.res[0], rt = sh.res[1];
     const bool ties_a = ra.mode == 3 && !ra.all_eq, ties_t = rt.mode == 3 && !rt.all_eq;
