@@ -966,10 +966,20 @@ __device__ __forceinline__ void ss_word_bits(const SsResult& r, const float* __r
             for (int e = 0; e < 32; ++e) k[e] = (valid >> e & 1u) ? order_key(__ldg(src + 32 * (size_t)w + e)) : 0u;
         }
         const uint32_t kth = r.kth;
+        if (r.all_eq) {
+            // every key equal to the threshold is kept: one comparison per key (k >= kth), gathered through the carry
+            // flag (the subtraction leaves "no borrow" in it, the add-with-carry shifts it into the word), last key first
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-            gt |= (k[e] > kth ? 1u : 0u) << e;
-            eq |= (k[e] == kth ? 1u : 0u) << e;
+            for (int e = 31; e >= 0; --e) {
+                uint32_t tmp;
+                asm("{\n\tsub.cc.u32 %1, %2, %3;\n\taddc.u32 %0, %0, %0;\n\t}" : "+r"(gt), "=r"(tmp) : "r"(k[e]), "r"(kth));
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                gt |= (k[e] > kth ? 1u : 0u) << e;
+                eq |= (k[e] == kth ? 1u : 0u) << e;
+            }
         }
         gt &= valid;
         eq &= valid;
