@@ -792,7 +792,7 @@ def other_kernels(torch, pikv_b200, ops, dev, peak, peak_src, gpu_index, single_
             del scores
             acc = torch.rand(B * n_kv, ctx, device=dev)
             ts = torch.arange(ctx, dtype=torch.float32, device=dev).repeat(B * n_kv, 1)
-            acc[:, ctx - 256:] = -1.0       # the recent window holds no heavy hitter: every segment keeps exactly 2048
+            acc[:, ctx - 256:] = 0.0        # the recent window holds no heavy hitter: every segment keeps exactly 2048
             ms, n, cl = measure(lambda: ops.h2o_select(acc, ts, 1792, 256, as_bool=False))
             record("h2o_select", ms, n, cl, 2 * 4 * ctx * B * n_kv + B * n_kv * (ctx + 2048 * 4), "h2o_select_stream_kernel",
                    segments=B * n_kv, length=ctx, heavy=1792, recent=256)
@@ -1141,7 +1141,7 @@ def secondary_arm(args):
         # budgeted step: H2O keeps 2048 tokens (256 recent + 1792 heavy) per (stream, KV head)
         acc = torch.rand(B * n_kv, ctx, device=dev)
         ts = torch.arange(ctx, dtype=torch.float32, device=dev).repeat(B * n_kv, 1)
-        acc[:, ctx - 256:] = -1.0       # the recent window holds no heavy hitter: every segment keeps exactly 2048
+        acc[:, ctx - 256:] = 0.0        # the recent window holds no heavy hitter: every segment keeps exactly 2048
         ms_sel = timed(lambda: ops.h2o_select(acc, ts, 1792, 256, as_bool=False), steps)
         by_sel = 2 * 4 * ctx * B * n_kv + B * n_kv * (ctx + 2048 * 4)
         emit("h2o_select_GBps", "GB/s", by_sel / (ms_sel * 1e-3) / 1e9, ms_sel,

@@ -29,7 +29,8 @@ __device__ __forceinline__ float4 ld_stream_f4(const float4* p) {
 
 __device__ __forceinline__ uint32_t order_key(float f) {
     // negative floats: all bits flipped; the others: sign bit set (an arithmetic shift and one three-input logic op)
-    const uint32_t b = __float_as_uint(f);
+    uint32_t b = __float_as_uint(f);
+    if ((b << 1) == 0u) b = 0u;          // -0 and +0 are one value, as in a comparison of the floats
     return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);
 }
 
@@ -617,6 +618,7 @@ struct SsResult {
     int mode;            // 0: nothing kept, 1: every position, 2: positions >= lo, 3: keys above kth + need_eq keys equal to it
     uint32_t kth;
     int need_eq, all_eq, lo;
+    int raw;             // the array's float bits serve as keys (no set sign bit), see ss_key
 };
 
 struct SsShared {
@@ -625,17 +627,23 @@ struct SsShared {
     uint32_t list[SS_LIST_CAP];
     uint32_t red_a[SS_THREADS / 32], red_b[SS_THREADS / 32];
     int red_i[SS_THREADS / 32];
-    int list_n, bucket, above, bucket_cnt, sorted, need_count;
+    int list_n, bucket, above, bucket_cnt, sorted, need_count, negative;
     uint32_t kmin, kmax;
     SsResult res[2];
 };
 
+// RAW: every value of the array has its sign bit clear (scores and timestamps normally do); then the float bits
+// themselves order like the values and no conversion is needed.  Keys of the two kinds are never mixed: everything
+// about one array (range, threshold, comparisons) lives in one key space.
+template <bool RAW>
+__device__ __forceinline__ uint32_t ss_key(float f) { return RAW ? __float_as_uint(f) : order_key(f); }
+template <bool RAW>
 __device__ __forceinline__ uint4 ss_keys4(const float4 f) {
-    return make_uint4(order_key(f.x), order_key(f.y), order_key(f.z), order_key(f.w));
+    return make_uint4(ss_key<RAW>(f.x), ss_key<RAW>(f.y), ss_key<RAW>(f.z), ss_key<RAW>(f.w));
 }
 
 // one(key) for every key of src[0..n), in no particular order; four 16-byte loads in flight per thread
-template <int NT, class F>
+template <int NT, bool RAW, class F>
 __device__ __forceinline__ void ss_for_keys(const float* __restrict__ src, int n, bool aligned, F&& one) {
     if (aligned) {
         const float4* src4 = reinterpret_cast<const float4*>(src);
@@ -647,17 +655,17 @@ __device__ __forceinline__ void ss_for_keys(const float* __restrict__ src, int n
             for (int u = 0; u < 8; ++u) f[u] = __ldg(src4 + i0 + u * NT);
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                const uint4 k = ss_keys4(f[u]);
+                const uint4 k = ss_keys4<RAW>(f[u]);
                 one(k.x); one(k.y); one(k.z); one(k.w);
             }
         }
         for (; i0 < n4; i0 += NT) {
-            const uint4 k = ss_keys4(__ldg(src4 + i0));
+            const uint4 k = ss_keys4<RAW>(__ldg(src4 + i0));
             one(k.x); one(k.y); one(k.z); one(k.w);
         }
-        for (int i = 4 * n4 + threadIdx.x; i < n; i += NT) one(order_key(__ldg(src + i)));
+        for (int i = 4 * n4 + threadIdx.x; i < n; i += NT) one(ss_key<RAW>(__ldg(src + i)));
     } else {
-        for (int i = threadIdx.x; i < n; i += NT) one(order_key(__ldg(src + i)));
+        for (int i = threadIdx.x; i < n; i += NT) one(ss_key<RAW>(__ldg(src + i)));
     }
 }
 
@@ -725,17 +733,22 @@ __device__ __forceinline__ int ss_shift_for(uint32_t width) {      // (width >> 
 
 // Where the m largest of src[0..n) are, ties to the lowest index: fills *out (shared memory) for the last pass.
 // ASCENDING_CHECK: whether pass 1 also tests for ascending keys (worth it for timestamps; for scores it only costs)
-template <int NT, bool ASCENDING_CHECK>
-__device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligned, SsShared& sh, SsResult* out) {
+// RAW: the float bits are taken as keys; returns false (nothing decided) when pass 1 meets a set sign bit, and the
+// caller runs the converting instance instead.
+template <int NT, bool ASCENDING_CHECK, bool RAW>
+__device__ bool ss_find(const float* __restrict__ src, int n, int m, bool aligned, SsShared& sh, SsResult* out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (m <= 0 || m >= n) {
-        if (tid == 0) out->mode = m <= 0 ? 0 : 1;
+        if (tid == 0) {
+            out->mode = m <= 0 ? 0 : 1;
+            out->raw = RAW;
+        }
         __syncthreads();
-        return;
+        return true;
     }
     // ---- pass 1: smallest, largest, ascending? ----
     {
-        uint32_t mn = 0xffffffffu, mx = 0u;
+        uint32_t mn = 0xffffffffu, mx = 0u, signs = 0u;
         bool ok = true;
         if (aligned) {
             const float4* src4 = reinterpret_cast<const float4*>(src);
@@ -751,61 +764,70 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
                 for (int u = 0; u < 4; ++u) {
                     const int i = i0 + u * NT + tid;
                     const bool on = i < n4;
-                    const uint4 k = ss_keys4(f[u]);
+                    const uint4 k = ss_keys4<RAW>(f[u]);
                     if (ASCENDING_CHECK) {
                         uint32_t next = __shfl_down_sync(0xffffffffu, k.x, 1);      // the key after this thread's four
                         const bool has_next = 4 * i + 4 < n;
-                        if (on && has_next && (lane == 31 || i + 1 >= n4)) next = order_key(__ldg(src + 4 * (size_t)i + 4));
+                        if (on && has_next && (lane == 31 || i + 1 >= n4)) next = ss_key<RAW>(__ldg(src + 4 * (size_t)i + 4));
                         if (on) ok &= k.x <= k.y && k.y <= k.z && k.z <= k.w && (!has_next || k.w <= next);
                     }
                     if (on) {
                         mn = min(mn, min(min(k.x, k.y), min(k.z, k.w)));
                         mx = max(mx, max(max(k.x, k.y), max(k.z, k.w)));
+                        if (RAW) signs |= k.x | k.y | k.z | k.w;
                     }
                 }
             }
             if (tid == 0) {                                       // the last n % 4 keys
                 for (int i = 4 * n4; i < n; ++i) {
-                    const uint32_t u = order_key(__ldg(src + i));
+                    const uint32_t u = ss_key<RAW>(__ldg(src + i));
                     mn = min(mn, u);
                     mx = max(mx, u);
-                    if (ASCENDING_CHECK && i + 1 < n) ok &= u <= order_key(__ldg(src + i + 1));
+                    if (RAW) signs |= u;
+                    if (ASCENDING_CHECK && i + 1 < n) ok &= u <= ss_key<RAW>(__ldg(src + i + 1));
                 }
             }
         } else {
             for (int i = tid; i < n; i += NT) {
-                const uint32_t u = order_key(__ldg(src + i));
+                const uint32_t u = ss_key<RAW>(__ldg(src + i));
                 mn = min(mn, u);
                 mx = max(mx, u);
-                if (ASCENDING_CHECK && i + 1 < n) ok &= u <= order_key(__ldg(src + i + 1));
+                if (RAW) signs |= u;
+                if (ASCENDING_CHECK && i + 1 < n) ok &= u <= ss_key<RAW>(__ldg(src + i + 1));
             }
         }
         if (!ASCENDING_CHECK) ok = false;
         mn = __reduce_min_sync(0xffffffffu, mn);
         mx = __reduce_max_sync(0xffffffffu, mx);
         const bool all_ok = __all_sync(0xffffffffu, ok);
+        const bool negative = RAW && __any_sync(0xffffffffu, (signs >> 31) != 0u);
         if (lane == 0) {
             sh.red_a[warp] = mn;
             sh.red_b[warp] = mx;
-            sh.red_i[warp] = all_ok ? 1 : 0;
+            sh.red_i[warp] = (all_ok ? 1 : 0) | (negative ? 2 : 0);
         }
         __syncthreads();
         if (tid == 0) {
             uint32_t lo = 0xffffffffu, hi = 0u;
-            int so = 1;
+            int so = 1, neg = 0;
             for (int q = 0; q < NT / 32; ++q) {
                 lo = min(lo, sh.red_a[q]);
                 hi = max(hi, sh.red_b[q]);
-                so &= sh.red_i[q];
+                so &= sh.red_i[q] & 1;
+                neg |= sh.red_i[q] & 2;
             }
             sh.kmin = lo;
             sh.kmax = hi;
             sh.sorted = so;
             sh.need_count = 0;
-            if (so || lo == hi) {
+            sh.negative = neg;
+            out->raw = RAW;
+            if (neg) {
+                // the caller repeats the search with converted keys
+            } else if (so || lo == hi) {
                 // ascending keys: the m largest are the tail; of a run of equal keys across the cut the lowest indices stay
-                const uint32_t kth = order_key(src[n - m]);
-                if (order_key(src[n - m - 1]) != kth) {
+                const uint32_t kth = ss_key<RAW>(src[n - m]);
+                if (ss_key<RAW>(src[n - m - 1]) != kth) {
                     out->mode = 2;
                     out->lo = n - m;
                 } else {
@@ -819,17 +841,18 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
         }
         __syncthreads();
     }
+    if (RAW && sh.negative) return false;
     if (sh.sorted || sh.kmin == sh.kmax) {
         if (sh.need_count) {
             const uint32_t kth = out->kth;
             int gt = 0;
-            ss_for_keys<NT>(src, n, aligned, [&](uint32_t u) { gt += u > kth ? 1 : 0; });
+            ss_for_keys<NT, RAW>(src, n, aligned, [&](uint32_t u) { gt += u > kth ? 1 : 0; });
             int total;
             (void)ss_block_scan<NT>(gt, sh.red_i, total);
             if (tid == 0) out->need_eq = m - total;
             __syncthreads();
         }
-        return;
+        return true;
     }
     // ---- passes 2 and 3: narrow [lo, lo + width] around the m-th largest key ----
     // The first histogram covers only the top 2^27 key values below the largest key (sixteen binades of positive
@@ -854,7 +877,7 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
                 if (d <= width) atomicAdd(&sh.hist[d >> s], 1);
             }
         } else {
-            ss_for_keys<NT>(src, n, aligned, [&](uint32_t u) {
+            ss_for_keys<NT, RAW>(src, n, aligned, [&](uint32_t u) {
                 const uint32_t d = u - lo;
                 if (d <= width) atomicAdd(&sh.hist[d >> s], 1);
             });
@@ -872,7 +895,7 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
             }
             if (tid == 0) out->mode = 0;               // cannot happen for 1 <= rem <= keys in range
             __syncthreads();
-            return;
+            return true;
         }
         clamped = false;
         rem -= sh.above;
@@ -888,12 +911,12 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
                 out->all_eq = rem == cnt;
             }
             __syncthreads();
-            return;
+            return true;
         }
         if (!on_list && cnt <= SS_LIST_CAP) {
             if (tid == 0) sh.list_n = 0;
             __syncthreads();
-            ss_for_keys<NT>(src, n, aligned, [&](uint32_t u) {
+            ss_for_keys<NT, RAW>(src, n, aligned, [&](uint32_t u) {
                 if (u - lo <= width) {
                     const int at = atomicAdd(&sh.list_n, 1);
                     if (at < SS_LIST_CAP) sh.list[at] = u;
@@ -921,7 +944,7 @@ __device__ void ss_find(const float* __restrict__ src, int n, int m, bool aligne
                     }
                 }
                 __syncthreads();
-                return;
+                return true;
             }
         }
         __syncthreads();
@@ -950,10 +973,18 @@ __device__ __forceinline__ void ss_word_bits(const SsResult& r, const float* __r
 #pragma unroll
             for (int q = 0; q < 8; ++q) f[q] = __ldg(src4 + q * 32 + lane);
             __syncwarp();
+            if (r.raw) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int row = 4 * q + (lane >> 3), c = lane & 7;
-                tile[row * 8 + (c ^ (row & 7))] = ss_keys4(f[q]);
+                for (int q = 0; q < 8; ++q) {
+                    const int row = 4 * q + (lane >> 3), c = lane & 7;
+                    tile[row * 8 + (c ^ (row & 7))] = ss_keys4<true>(f[q]);
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int row = 4 * q + (lane >> 3), c = lane & 7;
+                    tile[row * 8 + (c ^ (row & 7))] = ss_keys4<false>(f[q]);
+                }
             }
             __syncwarp();
 #pragma unroll
@@ -963,7 +994,10 @@ __device__ __forceinline__ void ss_word_bits(const SsResult& r, const float* __r
             }
         } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) k[e] = (valid >> e & 1u) ? order_key(__ldg(src + 32 * (size_t)w + e)) : 0u;
+            for (int e = 0; e < 32; ++e) {
+                const float v = (valid >> e & 1u) ? __ldg(src + 32 * (size_t)w + e) : 0.f;
+                k[e] = r.raw ? ss_key<true>(v) : ss_key<false>(v);
+            }
         }
         const uint32_t kth = r.kth;
         if (r.all_eq) {
@@ -1013,8 +1047,10 @@ __global__ void __launch_bounds__(NT, 1024 / NT) h2o_select_stream_kernel(const 
     const bool al_a = (reinterpret_cast<uintptr_t>(a) & 15) == 0, al_t = (reinterpret_cast<uintptr_t>(t) & 15) == 0;
     // the timestamps first: they are read once, the scores up to four times, and read last the scores are the
     // array still in L2 when the later passes come back to them
-    ss_find<NT, true>(t, n, min(num_recent, n), al_t, sh, &sh.res[1]);
-    ss_find<NT, false>(a, n, min(num_heavy, n), al_a, sh, &sh.res[0]);
+    if (!ss_find<NT, true, true>(t, n, min(num_recent, n), al_t, sh, &sh.res[1]))
+        ss_find<NT, true, false>(t, n, min(num_recent, n), al_t, sh, &sh.res[1]);
+    if (!ss_find<NT, false, true>(a, n, min(num_heavy, n), al_a, sh, &sh.res[0]))
+        ss_find<NT, false, false>(a, n, min(num_heavy, n), al_a, sh, &sh.res[0]);
     __syncthreads();
     const SsResult ra = sh.res[0], rt = sh.res[1];
     const bool ties_a = ra.mode == 3 && !ra.all_eq, ties_t = rt.mode == 3 && !rt.all_eq;

@@ -269,7 +269,7 @@ def test_h2o_select_segments_and_ties(dev, n, nh, nr, levels):
 
 
 @pytest.mark.parametrize("kind", ["uniform", "heavy_tail", "outlier", "levels", "ascending", "ascending_runs", "constant",
-                                  "dense_bucket", "unaligned"])
+                                  "dense_bucket", "unaligned", "signed_zeros"])
 def test_h2o_select_routines_agree_with_oracle(dev, kind):
     """The streaming select (the default), the two radix routines and the bucketed select on staged keys must all
     return the oracle's mask on score distributions that stress them differently: a far outlier (every other key
@@ -284,7 +284,12 @@ def test_h2o_select_routines_agree_with_oracle(dev, kind):
            "constant": np.full((S, n), 0.25),
            # thousands of distinct keys inside one first-level bucket beside a wide spread: narrowed pass by pass
            "dense_bucket": np.where(rng.random((S, n)) < 0.04, rng.random((S, n)) * 1e6, 1.0 + rng.random((S, n)) * 1e-4),
-           "unaligned": rng.random((S, n))}[kind].astype(F32)
+           "unaligned": rng.random((S, n)),
+           # -0.0 and +0.0 are one value: the cut falls inside them and the lowest indices must win
+           "signed_zeros": np.where(rng.random((S, n)) < 0.03, 0.5 + rng.random((S, n)), 0.0)}[kind].astype(F32)
+    if kind == "signed_zeros":
+        neg = rng.random((S, n)) < 0.5
+        acc = np.where((acc == 0) & neg, np.float32(-0.0), acc).astype(F32)
     if kind == "unaligned":
         n = 4999                                               # rows that start off a 16-byte boundary
         acc = np.ascontiguousarray(acc[:, :n])
