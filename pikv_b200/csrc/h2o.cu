@@ -753,7 +753,26 @@ __device__ bool ss_find(const float* __restrict__ src, int n, int m, bool aligne
         if (aligned) {
             const float4* src4 = reinterpret_cast<const float4*>(src);
             const int n4 = n >> 2;
-            for (int i0 = 0; i0 < n4; i0 += 4 * NT) {            // the same trip count in every thread (shuffles inside)
+            int i0 = 0;
+            // whole iterations: every vector exists and has a successor key, no bounds tests; eight loads in flight
+            for (; i0 + 8 * NT <= n4 && 4 * (i0 + 8 * NT) < n; i0 += 8 * NT) {
+                float4 f[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) f[u] = __ldg(src4 + i0 + u * NT + tid);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const uint4 k = ss_keys4<RAW>(f[u]);
+                    if (ASCENDING_CHECK) {
+                        uint32_t next = __shfl_down_sync(0xffffffffu, k.x, 1);
+                        if (lane == 31) next = ss_key<RAW>(__ldg(src + 4 * (size_t)(i0 + u * NT + tid) + 4));
+                        ok &= k.x <= k.y && k.y <= k.z && k.z <= k.w && k.w <= next;
+                    }
+                    mn = min(mn, min(min(k.x, k.y), min(k.z, k.w)));
+                    mx = max(mx, max(max(k.x, k.y), max(k.z, k.w)));
+                    if (RAW) signs |= k.x | k.y | k.z | k.w;
+                }
+            }
+            for (; i0 < n4; i0 += 4 * NT) {                      // the same trip count in every thread (shuffles inside)
                 float4 f[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
