@@ -622,9 +622,14 @@ struct SsResult {
 };
 
 struct SsShared {
-    uint4 tile[SS_THREADS / 32][256];               // per warp: 32 words x 8 chunks of 16 bytes, chunk c of word r at c ^ (r & 7)
-    int hist[SS_BUCKETS];
-    uint32_t list[SS_LIST_CAP];
+    // the search (histogram, candidate list) and the last pass (transpose tiles) never overlap in time
+    union {
+        uint4 tile[SS_THREADS / 32][256];           // per warp: 32 words x 8 chunks of 16 bytes, chunk c of word r at c ^ (r & 7)
+        struct {
+            int hist[SS_BUCKETS];
+            uint32_t list[SS_LIST_CAP];
+        };
+    };
     uint32_t red_a[SS_THREADS / 32], red_b[SS_THREADS / 32];
     int red_i[SS_THREADS / 32];
     int list_n, bucket, above, bucket_cnt, sorted, need_count, negative;
