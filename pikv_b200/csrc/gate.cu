@@ -201,6 +201,23 @@ __global__ void __launch_bounds__(GATE_THREADS) gate_logits_kernel(GateDev g) {
 // Threads are laid out as (expert e, part): part p sums the per-CTA counters of CTAs p, p+parts, ...
 // so the reads of one prefix are spread over 256/EP2 threads and overlap; parts are combined in a
 // fixed order (the float sums stay run-to-run identical).
+// sum of p[c * stride] for c = first, first + step, ... < end, eight loads in flight per round trip and
+// added in index order (with 64 experts a thread walks a quarter of the CTAs)
+template <typename V>
+__device__ __forceinline__ V strided_sum(const V* p, size_t stride, int first, int end, int step) {
+    V s = V(0);
+    int c = first;
+    for (; c + 7 * step < end; c += 8 * step) {
+        V v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldg(p + (size_t)(c + u * step) * stride);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s += v[u];
+    }
+    for (; c < end; c += step) s += __ldg(p + (size_t)c * stride);
+    return s;
+}
+
 __global__ void __launch_bounds__(GATE_THREADS) gate_finalize_kernel(GateDev g) {
     __shared__ int base_s[GATE_MAX_E];
     __shared__ int part_i[GATE_THREADS];
@@ -211,16 +228,7 @@ __global__ void __launch_bounds__(GATE_THREADS) gate_finalize_kernel(GateDev g) 
     const int parts = GATE_THREADS / ep2;
     const int e = tid & (ep2 - 1), part = tid / ep2;
     {
-        int s0 = 0, s1 = 0;
-        if (e < E) {
-            int c = part;
-            for (; c + parts < cta; c += 2 * parts) {
-                s0 += g.cta_cnt[(size_t)c * E + e];
-                s1 += g.cta_cnt[(size_t)(c + parts) * E + e];
-            }
-            if (c < cta) s0 += g.cta_cnt[(size_t)c * E + e];
-        }
-        part_i[tid] = s0 + s1;
+        part_i[tid] = e < E ? strided_sum(g.cta_cnt + e, (size_t)E, part, cta, parts) : 0;
     }
     __syncthreads();
     if (tid < E) {
@@ -243,9 +251,7 @@ __global__ void __launch_bounds__(GATE_THREADS) gate_finalize_kernel(GateDev g) 
     // totals over all CTAs: per-column counts, probability sums, new lengths
     int tot = 0;
     for (int j = 0; j < g.k; ++j) {
-        int s = 0;
-        if (e < E)
-            for (int c = part; c < g.G; c += parts) s += g.cta_cnt_k[((size_t)c * g.k + j) * E + e];
+        const int s = e < E ? strided_sum(g.cta_cnt_k + (size_t)j * E + e, (size_t)g.k * E, part, g.G, parts) : 0;
         __syncthreads();
         part_i[tid] = s;
         __syncthreads();
@@ -256,10 +262,7 @@ __global__ void __launch_bounds__(GATE_THREADS) gate_finalize_kernel(GateDev g) 
             tot += cnt;
         }
     }
-    float ps = 0.f;
-    if (e < E)
-        for (int c = part; c < g.G; c += parts) ps += g.cta_psum[(size_t)c * E + e];
-    part_f[tid] = ps;
+    part_f[tid] = e < E ? strided_sum(g.cta_psum + e, (size_t)E, part, g.G, parts) : 0.f;
     __syncthreads();
     if (tid < E) {
         float sum = 0.f;

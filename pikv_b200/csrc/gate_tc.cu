@@ -6,7 +6,8 @@
 // by TMA) through a shared-memory ring, one thread issues tcgen05.mma into a
 // double-buffered accumulator in tensor memory, and four epilogue warps read one token
 // row each (tcgen05.ld: all E logits of a token land in one thread's registers), so the
-// softmax, top-k and renormalisation need no cross-thread traffic at all.  Warp shuffles
+// softmax, top-k and renormalisation need no cross-thread traffic at all (up to 16 experts;
+// above that E/16 warps share a row group, 16 columns per thread, see token_tail_wide).  Warp shuffles
 // reduce the per-expert probability sums; ballots/match rank the (token, k) pairs of the
 // CTA's chunk per expert.  The epilogue of tile i overlaps the loads and MMAs of tile i+1.
 // The slot scan across CTAs is finished by gate_finalize_kernel (see gate.cu).
@@ -15,15 +16,176 @@
 
 namespace pikv {
 
-constexpr int GT_THREADS = 192;          // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
-constexpr int GT_EPI = 128;
-constexpr int GT_EPI_WARPS = 4;
+constexpr int GT_LOAD_THREADS = 64;      // warp 0 TMA, warp 1 MMA; 4 * Q epilogue warps follow
+constexpr int GT_COLS = 16;              // expert columns per thread when Q > 1 threads share a token row
 
 __device__ unsigned g_gate_tc_error = 0;
 
-__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+template <int Q>
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(128 * Q) : "memory"); }
+// the Q warps that share the token rows of tensor-memory lane group lg (barriers 2..5; the number is an immediate
+// so that the kernel claims six barriers, not all sixteen)
+template <int Q, int ID>
+__device__ __forceinline__ bool row_barrier_id(bool flag) {
+    uint32_t out;
+    asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, %2, %3, q;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(out) : "r"((uint32_t)flag), "n"(ID), "n"(32 * Q) : "memory");
+    return out != 0;
+}
+// barrier over a row group with an OR over a flag: its warps leave the tile loop together
+template <int Q>
+__device__ __forceinline__ bool row_barrier_any(int lg, bool flag) {
+    switch (lg) {
+        case 0: return row_barrier_id<Q, 2>(flag);
+        case 1: return row_barrier_id<Q, 3>(flag);
+        case 2: return row_barrier_id<Q, 4>(flag);
+        default: return row_barrier_id<Q, 5>(flag);
+    }
+}
+template <int Q>
+__device__ __forceinline__ void row_barrier(int lg) {
+    switch (lg) {
+        case 0: asm volatile("bar.sync 2, %0;" ::"n"(32 * Q) : "memory"); break;
+        case 1: asm volatile("bar.sync 3, %0;" ::"n"(32 * Q) : "memory"); break;
+        case 2: asm volatile("bar.sync 4, %0;" ::"n"(32 * Q) : "memory"); break;
+        default: asm volatile("bar.sync 5, %0;" ::"n"(32 * Q) : "memory"); break;
+    }
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Shared memory of the epilogue when Q > 1 threads share a token: partial maxima and sums, and each
+// thread's k best (probability, expert) of its 16 columns.
+struct WideXchg {
+    float* red;      // [2][Q][128]
+    float* cval;     // [128][Q][k]
+    uint8_t* cidx;   // [128][Q][k]
+};
+
+// Per-token tail for expert counts above 16: Q threads in Q warps of one lane group hold 16 logits each of
+// token row `row`; they exchange the row maximum, the softmax denominator (partial sums added in column
+// order) and their k best candidates, and the thread of column group 0 merges those and writes the
+// routing outputs.  Same arithmetic per element as token_tail; every thread of the row group must call
+// it (it synchronises), rows past the end of the batch pass valid = false and store nothing.  Leaves the
+// probabilities of the thread's columns in l[].
+template <int Q>
+__device__ __forceinline__ void token_tail_wide(float (&l)[GT_COLS], const GateDev& g, int t, bool valid, int cg,
+                                                int lg, int row, const WideXchg& x, uint8_t* sel_row) {
+    const int E = g.E, e0 = cg * GT_COLS, k = g.k;
+#pragma unroll
+    for (int i = 0; i < GT_COLS; ++i) {
+        const int e = e0 + i;
+        if (e < E) {
+            float v = l[i];
+            if (g.temperature != 1.0f) v = __fdiv_rn(v, g.temperature);
+            if (g.corr) v = __fmul_rn(v, g.corr[e]);
+            if (g.mask_mode == PIKV_MASK_SINGLE)
+                v = __fadd_rn(v, __fmul_rn(__fsub_rn(1.0f, g.mask[e]), -1e9f));
+            else if (g.mask_mode == PIKV_MASK_MODULE)
+                v = __fadd_rn(v, __fmul_rn(__fsub_rn(1.0f, g.mask[e]), -3.402823466e+38f));
+            else if (g.mask_mode == PIKV_MASK_BIAS)
+                v = __fadd_rn(v, g.mask[e]);
+            l[i] = v;
+        } else {
+            l[i] = -INFINITY;
+        }
+    }
+    float m = l[0];
+#pragma unroll
+    for (int i = 1; i < GT_COLS; ++i) m = fmaxf(m, l[i]);
+    x.red[cg * 128 + row] = m;
+    row_barrier<Q>(lg);
+    m = x.red[row];
+#pragma unroll
+    for (int q = 1; q < Q; ++q) m = fmaxf(m, x.red[q * 128 + row]);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < GT_COLS; ++i) {
+        const float p = (e0 + i < E) ? expf(l[i] - m) : 0.f;
+        l[i] = p;
+        s += p;
+    }
+    x.red[(Q + cg) * 128 + row] = s;
+    row_barrier<Q>(lg);
+    s = x.red[Q * 128 + row];
+#pragma unroll
+    for (int q = 1; q < Q; ++q) s += x.red[(Q + q) * 128 + row];
+#pragma unroll
+    for (int i = 0; i < GT_COLS; ++i) l[i] = __fdiv_rn(l[i], s);
+    if (valid && g.probs) {
+        if (E == Q * GT_COLS && (reinterpret_cast<uintptr_t>(g.probs) & 15) == 0) {
+            float4* dst = reinterpret_cast<float4*>(g.probs + (size_t)t * E + e0);
+#pragma unroll
+            for (int i = 0; i < GT_COLS; i += 4) dst[i / 4] = make_float4(l[i], l[i + 1], l[i + 2], l[i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < GT_COLS; ++i)
+                if (e0 + i < E) g.probs[(size_t)t * E + e0 + i] = l[i];
+        }
+    }
+    // the k best of this thread's columns; strict '>' keeps the lowest index on ties.  A thread with fewer than
+    // k real columns pads with probability -1, which the merge never prefers to a real one.
+    {
+        unsigned taken = 0u;
+        float* cv = x.cval + (size_t)(row * Q + cg) * k;
+        uint8_t* ci = x.cidx + (size_t)(row * Q + cg) * k;
+#pragma unroll
+        for (int j = 0; j < GATE_MAX_K; ++j) {
+            if (j < k) {
+                float best = -1.f;
+                int bi = 0;
+#pragma unroll
+                for (int i = 0; i < GT_COLS; ++i) {
+                    if (e0 + i < E && !((taken >> i) & 1u) && l[i] > best) {
+                        best = l[i];
+                        bi = i;
+                    }
+                }
+                taken |= 1u << bi;
+                cv[j] = best;
+                ci[j] = (uint8_t)(e0 + bi);
+            }
+        }
+    }
+    row_barrier<Q>(lg);
+    if (cg == 0 && valid) {
+        // candidates in (column group, rank) order: among equal probabilities the first one met has the lowest index
+        const float* cv = x.cval + (size_t)row * Q * k;
+        const uint8_t* ci = x.cidx + (size_t)row * Q * k;
+        const int nc = Q * k;
+        unsigned used = 0u;
+        int idx[GATE_MAX_K];
+        float val[GATE_MAX_K];
+        float wsum = 0.f;
+#pragma unroll
+        for (int j = 0; j < GATE_MAX_K; ++j) {
+            if (j < k) {
+                float best = -2.f;
+                int bc = 0;
+                for (int c = 0; c < nc; ++c) {
+                    const float v = cv[c];
+                    if (!((used >> c) & 1u) && v > best) {
+                        best = v;
+                        bc = c;
+                    }
+                }
+                used |= 1u << bc;
+                idx[j] = ci[bc];
+                val[j] = best;
+                wsum += best;
+            }
+        }
+        const float denom = __fadd_rn(wsum, g.eps);
+#pragma unroll
+        for (int j = 0; j < GATE_MAX_K; ++j) {
+            if (j < k) {
+                g.topk_idx[(size_t)t * k + j] = idx[j];
+                if (g.topk_w) g.topk_w[(size_t)t * k + j] = __fdiv_rn(val[j], denom);
+                sel_row[j] = (uint8_t)idx[j];
+            }
+        }
+    }
 }
 
 struct GateTcArgs {
@@ -32,9 +194,11 @@ struct GateTcArgs {
 };
 
 // EP: expert columns of the MMA (multiple of 16); EL <= EP: columns the per-token tail looks at (8 when E <= 8,
-// which halves the serial softmax / top-k work of the four epilogue warps)
-template <int EP, int EL>
-__global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_constant__ CUtensorMap tm_act,
+// which halves the serial softmax / top-k work of the epilogue warps); Q: epilogue warps per tensor-memory lane
+// group.  With Q == 1 a thread owns a token row; above 16 experts that serial tail (one warp per scheduler) took
+// longer than streaming the tile in, so Q = EL / 16 threads share a row, 16 columns each (token_tail_wide).
+template <int EP, int EL, int Q>
+__global__ void __launch_bounds__(GT_LOAD_THREADS + 128 * Q) gate_tc_kernel(const __grid_constant__ CUtensorMap tm_act,
                                                              const __grid_constant__ CUtensorMap tm_w,
                                                              GateTcArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -51,11 +215,17 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
     const uint32_t tfull0 = empty0 + 8 * a.stages;       // [2] accumulator ready
     const uint32_t tempty0 = tfull0 + 16;                // [2] accumulator drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * a.stages + 4);
-    int* warp_cnt = reinterpret_cast<int*>(tmem_slot + 4);           // [4][EP]
-    int* run = warp_cnt + GT_EPI_WARPS * EP;                         // [EP]
+    static_assert(Q == 1 || EL == Q * GT_COLS, "a thread of a shared row owns 16 columns");
+    constexpr int EPI = 128 * Q, EPI_WARPS = 4 * Q;
+    int* warp_cnt = reinterpret_cast<int*>(tmem_slot + 4);           // [EPI_WARPS][EP]
+    int* run = warp_cnt + EPI_WARPS * EP;                            // [EP]
     int* cnt_k = run + EP;                                           // [K][EP]
-    float* psum_w = reinterpret_cast<float*>(cnt_k + GATE_MAX_K * EP);   // [4][EP]
-    uint8_t* sel = reinterpret_cast<uint8_t*>(psum_w + GT_EPI_WARPS * EP);   // [chunk * k]
+    float* psum_w = reinterpret_cast<float*>(cnt_k + GATE_MAX_K * EP);   // [4 lane groups][EP]
+    WideXchg xc;
+    xc.red = psum_w + 4 * EP;                                        // Q > 1 only: [2][Q][128]
+    xc.cval = xc.red + (Q > 1 ? 2 * Q * 128 : 0);                    // [128][Q][k]
+    xc.cidx = reinterpret_cast<uint8_t*>(xc.cval + (Q > 1 ? 128 * Q * g.k : 0));
+    uint8_t* sel = xc.cidx + (Q > 1 ? 128 * Q * g.k : 0);            // [chunk * k]
     const uint32_t ring = lr_smem_u32(smem);
 
     const int tile0 = blockIdx.x * a.tiles_per_cta;
@@ -72,7 +242,7 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
         }
         for (int s = 0; s < 2; ++s) {
             lr_mbar_init(tfull0 + 8 * s, 1);
-            lr_mbar_init(tempty0 + 8 * s, GT_EPI);
+            lr_mbar_init(tempty0 + 8 * s, EPI);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -136,63 +306,68 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
             }
         }
     } else {
-        const int et = threadIdx.x - 64;              // 0..127 among the epilogue threads
+        const int et = threadIdx.x - GT_LOAD_THREADS; // index among the epilogue threads
         const int ew = et >> 5;
         const int lg = warp & 3;                      // tensor-memory lane group of this warp
+        const int cg = ew >> 2;                       // column group (Q > 1)
         const int row = lg * 32 + lane;               // token row inside a tile
-        for (int i = et; i < GT_EPI_WARPS * EP; i += GT_EPI) psum_w[i] = 0.f;
+        constexpr int CL = Q == 1 ? EL : GT_COLS;     // logits per thread
+        for (int i = et; i < 4 * EP; i += EPI) psum_w[i] = 0.f;
         // the bias is needed the moment the first accumulator arrives: its loads go out now
-        float bias[EL];
+        float bias[CL];
 #pragma unroll
-        for (int e = 0; e < EL; ++e) bias[e] = (g.b2 && e < g.E) ? __ldg(g.b2 + e) : 0.f;
-        epi_barrier();
+        for (int e = 0; e < CL; ++e) bias[e] = (g.b2 && cg * CL + e < g.E) ? __ldg(g.b2 + cg * CL + e) : 0.f;
+        epi_barrier<Q>();
         for (int lt = 0; lt < ntiles; ++lt) {
             const int slot = lt & 1;
-            if (!lr_mbar_wait(tfull0 + 8 * slot, ((uint32_t)lt >> 1) & 1u)) { failed = true; break; }
+            if (!lr_mbar_wait(tfull0 + 8 * slot, ((uint32_t)lt >> 1) & 1u)) failed = true;
+            if (Q > 1) failed = row_barrier_any<Q>(lg, failed);   // the warps of a row group go on, or give up, together
+            if (failed) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float l[EL];
+            float l[CL];
 #pragma unroll
-            for (int c = 0; c < EL; c += 16) {
+            for (int c = 0; c < CL; c += 16) {
                 float v[16];
-                lr_tmem_ld16(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(slot * EP + c), v);
+                lr_tmem_ld16(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(slot * EP + cg * CL + c), v);
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    if (c + i < EL) l[c + i] = v[i];
+                    if (c + i < CL) l[c + i] = v[i];
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(tempty0 + 8 * slot);          // this thread's row is out of tensor memory
+            mbar_arrive(tempty0 + 8 * slot);          // this thread's part of the row is out of tensor memory
             const int lt_tok = lt * LR_BM + row;      // token index inside the chunk
             const bool valid = lt_tok < ntok;
-            if (valid) {
 #pragma unroll
-                for (int e = 0; e < EL; ++e) l[e] += bias[e];
-                token_tail<EL>(l, g, chunk_start + lt_tok, sel + (size_t)lt_tok * g.k);
+            for (int e = 0; e < CL; ++e) l[e] += bias[e];
+            if constexpr (Q == 1) {
+                if (valid) token_tail<EL>(l, g, chunk_start + lt_tok, sel + (size_t)lt_tok * g.k);
+            } else {
+                token_tail_wide<Q>(l, g, chunk_start + lt_tok, valid, cg, lg, row, xc, sel + (size_t)lt_tok * g.k);
             }
 #pragma unroll
-            for (int e = 0; e < EL; ++e) {
+            for (int e = 0; e < CL; ++e) {
                 const float s = warp_sum(valid ? l[e] : 0.f);
-                if (lane == 0) psum_w[ew * EP + e] += s;
+                if (lane == 0) psum_w[lg * EP + cg * CL + e] += s;
             }
         }
         if (failed) atomicOr(tmem_slot + 1, 1u);
-        epi_barrier();
+        epi_barrier<Q>();
         const bool any_failed = tmem_slot[1] != 0;   // identical in all 128 threads from here on
         if (et < g.E) {
             // fixed order: lane groups 0..3 hold token rows 0-31, 32-63, ... of every tile
             float s = 0.f;
-            const int order[4] = {2, 3, 0, 1};        // epilogue warp index holding lane group 0,1,2,3
 #pragma unroll
-            for (int q = 0; q < 4; ++q) s += psum_w[order[q] * EP + et];
+            for (int q = 0; q < 4; ++q) s += psum_w[q * EP + et];
             g.cta_psum[(size_t)blockIdx.x * g.E + et] = s;
         }
-        // ---- rank the chunk's (token, k) pairs per expert, in order (128 threads) ----
+        // ---- rank the chunk's (token, k) pairs per expert, in order (all epilogue threads) ----
         const int npairs = any_failed ? 0 : ntok * g.k;
-        for (int i = et; i < EP; i += GT_EPI) run[i] = 0;
-        for (int i = et; i < GATE_MAX_K * EP; i += GT_EPI) cnt_k[i] = 0;
-        epi_barrier();
-        for (int base = 0; base < npairs; base += GT_EPI) {
-            for (int i = et; i < GT_EPI_WARPS * EP; i += GT_EPI) warp_cnt[i] = 0;
-            epi_barrier();
+        for (int i = et; i < EP; i += EPI) run[i] = 0;
+        for (int i = et; i < GATE_MAX_K * EP; i += EPI) cnt_k[i] = 0;
+        epi_barrier<Q>();
+        for (int base = 0; base < npairs; base += EPI) {
+            for (int i = et; i < EPI_WARPS * EP; i += EPI) warp_cnt[i] = 0;
+            epi_barrier<Q>();
             const int p = base + et;
             const bool valid = p < npairs;
             const int e = valid ? (int)sel[p] : 255;
@@ -200,23 +375,23 @@ __global__ void __launch_bounds__(GT_THREADS) gate_tc_kernel(const __grid_consta
             const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
             if (valid && rank_in_warp == 0) warp_cnt[ew * EP + e] = __popc(peers);
             if (valid) atomicAdd(&cnt_k[(p % g.k) * EP + e], 1);
-            epi_barrier();
+            epi_barrier<Q>();
             if (valid) {
                 int r = run[e] + rank_in_warp;
                 for (int w = 0; w < ew; ++w) r += warp_cnt[w * EP + e];
                 if (g.slot) g.slot[(size_t)chunk_start * g.k + p] = r;
             }
-            epi_barrier();
+            epi_barrier<Q>();
             if (et < EP) {
                 int add = 0;
 #pragma unroll
-                for (int w = 0; w < GT_EPI_WARPS; ++w) add += warp_cnt[w * EP + et];
+                for (int w = 0; w < EPI_WARPS; ++w) add += warp_cnt[w * EP + et];
                 run[et] += add;
             }
-            epi_barrier();
+            epi_barrier<Q>();
         }
-        for (int e = et; e < g.E; e += GT_EPI) g.cta_cnt[(size_t)blockIdx.x * g.E + e] = run[e];
-        for (int i = et; i < g.k * g.E; i += GT_EPI) {
+        for (int e = et; e < g.E; e += EPI) g.cta_cnt[(size_t)blockIdx.x * g.E + e] = run[e];
+        for (int i = et; i < g.k * g.E; i += EPI) {
             const int j = i / g.E, e = i % g.E;
             g.cta_cnt_k[((size_t)blockIdx.x * g.k + j) * g.E + e] = cnt_k[j * EP + e];
         }
@@ -236,7 +411,7 @@ void gate_tc_geometry(GateDev& g) {
     g.G = ceil_div(g.T, g.chunk);
 }
 
-template <int EP, int EL>
+template <int EP, int EL, int Q>
 static int launch_gate_tc(GateDev& g, cudaStream_t st) {
     GateTcArgs a;
     gate_tc_geometry(g);
@@ -249,19 +424,21 @@ static int launch_gate_tc(GateDev& g, cudaStream_t st) {
     rc = make_tmap(&tm_w, g.w2, g.E, g.H, EP);
     if (rc != PIKV_OK) return rc;
     const int stage = LR_BM * LR_BK * 2 + EP * LR_BK * 2;
-    const size_t tail = (2 * 8 + 4) * sizeof(uint64_t) + 16 + sizeof(int) * (GT_EPI_WARPS * EP + EP + GATE_MAX_K * EP) +
-                        sizeof(float) * GT_EPI_WARPS * EP + (size_t)g.chunk * g.k + 1024;
-    // one CTA per SM when the grid fits in one wave, two otherwise
-    const size_t budget = (g.G <= sm_count() ? 200 * 1024 : 100 * 1024) - tail;
+    // barriers, tensor-memory slot, rank counters, probability sums, (Q > 1) the row exchange, selections, alignment slack
+    const size_t xchg = Q > 1 ? sizeof(float) * 2 * Q * 128 + (size_t)128 * Q * g.k * (sizeof(float) + 1) : 0;
+    const size_t tail = (2 * 8 + 4) * sizeof(uint64_t) + 16 + sizeof(int) * (4 * Q * EP + EP + GATE_MAX_K * EP) +
+                        sizeof(float) * 4 * EP + xchg + (size_t)g.chunk * g.k + 1024;
+    // one CTA per SM when the grid fits in one wave (or the registers of 16 epilogue warps leave room for one only), two otherwise
+    const size_t budget = ((g.G <= sm_count() || Q >= 4) ? 200 * 1024 : 100 * 1024) - tail;
     a.stages = (int)max((size_t)2, min((size_t)8, budget / stage));
     int cols = 32;
     while (cols < 2 * EP) cols <<= 1;
     a.tmem_cols = cols;
     const size_t smem = (size_t)a.stages * stage + tail;
-    auto kern = gate_tc_kernel<EP, EL>;
+    auto kern = gate_tc_kernel<EP, EL, Q>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("gate_tc smem attribute");
-    kern<<<g.G, GT_THREADS, smem, st>>>(tm_act, tm_w, a);
+    kern<<<g.G, GT_LOAD_THREADS + 128 * Q, smem, st>>>(tm_act, tm_w, a);
     return check_launch("gate_tc_kernel");
 }
 
@@ -272,10 +449,10 @@ bool gate_tc_supported(const GateDev& g, int dtype) {
 }
 
 int gate_tc_launch(GateDev& g, cudaStream_t st) {
-    if (g.E <= 8) return launch_gate_tc<16, 8>(g, st);
-    if (g.E <= 16) return launch_gate_tc<16, 16>(g, st);
-    if (g.E <= 32) return launch_gate_tc<32, 32>(g, st);
-    return launch_gate_tc<64, 64>(g, st);
+    if (g.E <= 8) return launch_gate_tc<16, 8, 1>(g, st);
+    if (g.E <= 16) return launch_gate_tc<16, 16, 1>(g, st);
+    if (g.E <= 32) return launch_gate_tc<32, 32, 2>(g, st);
+    return launch_gate_tc<64, 64, 4>(g, st);
 }
 
 }  // namespace pikv

@@ -151,7 +151,8 @@ def test_gate_bf16_simt_and_tensor_core_paths_agree(dev):
 
 
 @pytest.mark.parametrize("T,H,E,k", [(128, 64, 8, 2), (129, 4096, 8, 2), (16384, 4096, 8, 2), (1000, 4096, 64, 2),
-                                     (5000, 200, 20, 4), (200000, 128, 8, 2)])
+                                     (5000, 200, 20, 4), (200000, 128, 8, 2), (3000, 512, 40, 8), (2000, 256, 64, 8),
+                                     (700, 320, 48, 3), (16384, 1024, 64, 2), (150000, 64, 64, 2), (4000, 128, 32, 1)])
 def test_gate_tensor_core_shapes(dev, T, H, E, k):
     """Ragged tiles, hidden sizes that are not multiples of 64, padded expert counts, several tiles per CTA."""
     import pikv_b200
@@ -174,6 +175,49 @@ def test_gate_tensor_core_shapes(dev, T, H, E, k):
     np.testing.assert_array_equal(g.slot.cpu().numpy(), slot)
     np.testing.assert_array_equal(g.counts_k.cpu().numpy(), counts_k)
     assert rel(g.prob_sum.cpu().numpy(), probs.sum(0)) < 1e-4
+
+
+@pytest.mark.parametrize("E", [8, 24, 64])
+def test_gate_tensor_core_ties_and_masks(dev, E):
+    """Tied probabilities on the tensor-core path go to the lowest expert index, also when the tied experts sit in
+    different 16-column groups of the shared-row tail; masks, correction and temperature follow the oracle."""
+    import pikv_b200
+    from pikv_b200 import ops, _lib
+    T, H, k = 300, 128, 3
+    act = torch.zeros(T, H, device=dev, dtype=torch.bfloat16)      # logits = bias exactly
+    w2 = torch.ones(E, H, device=dev, dtype=torch.bfloat16)
+    b2 = torch.zeros(E)
+    b2[E - 1] = 1.0
+    b2[3] = 1.0                                                     # experts 3 and E-1 tie for first, the rest for third
+    g = ops.gate_fused(act, w2, b2.to(dev), top_k=k)
+    torch.cuda.synchronize()
+    assert pikv_b200.lib().pikv_gate_error_state() == 0
+    gi = g.topk_idx.cpu().numpy()
+    np.testing.assert_array_equal(gi, np.tile(np.array([3, E - 1, 0], dtype=np.int32), (T, 1)))
+    logits = np.tile(b2.numpy(), (T, 1)).astype(np.float32)
+    probs, idx, tw = O.gate_tail(logits, k)
+    np.testing.assert_array_equal(gi, idx)
+    assert rel(g.probs.cpu().numpy(), probs) < 1e-6
+    assert rel(g.topk_w.cpu().numpy(), tw) < 1e-6
+    # mask, correction, temperature against the oracle on random activations
+    torch.manual_seed(E)
+    act = torch.relu(torch.randn(T, H, device=dev)).bfloat16()
+    w2 = (torch.randn(E, H, device=dev) / H ** 0.5).bfloat16()
+    mask = (torch.rand(E) > 0.3).float()
+    mask[:k] = 1.0
+    corr = 0.5 + torch.rand(E)
+    g = ops.gate_fused(act, w2, None, top_k=k, expert_mask=mask.to(dev), mask_mode=_lib.MASK_SINGLE,
+                       correction=corr.to(dev), temperature=0.7, renorm_eps=1e-6)
+    logits = (act.float() @ w2.float().T).cpu().numpy()
+    probs, idx, tw = O.gate_tail(logits, k, expert_mask=mask.numpy(), mask_mode="single", correction=corr.numpy(),
+                                 temperature=0.7, renorm_eps=1e-6)
+    gi = g.topk_idx.cpu().numpy()
+    same = (gi == idx).all(axis=1)
+    assert (same | (O.topk_margin(probs, k) < 1e-4)).all()
+    assert rel(g.probs.cpu().numpy(), probs) < 2e-5
+    assert (mask.numpy()[gi] == 1.0).all()
+    if same.all():
+        assert rel(g.topk_w.cpu().numpy(), tw) < 2e-5
 
 
 def test_gate_is_deterministic(dev):
