@@ -929,18 +929,23 @@ __global__ void __launch_bounds__(DA_MERGE_THREADS) decode_return_kernel(DecodeD
         if (lane == 0) t.peer_part_lse[home][slot] = (l > 0.f) ? M * 0.6931471805599453f + logf(l) : -INFINITY;
     }
     // completion: every CTA counts itself after its stores are visible system-wide; the last one signals
+    // (one thread per destination for the flags: system-scope release stores one after another cost 2 us each)
+    __shared__ unsigned raise_s, step_s;
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned prev = atomicAdd(t.counter, 1u);
+        raise_s = 0u;
         if (prev == gridDim.x - 1) {
             *t.counter = 0;
             __threadfence_system();
-            const unsigned step = *t.seq;
-            for (int r = 0; r < t.world; ++r)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(t.peer_done_flags[r] + t.rank), "r"(step) : "memory");
+            step_s = *t.seq;
+            raise_s = 1u;
         }
     }
+    __syncthreads();
+    if (raise_s != 0u && threadIdx.x < t.world)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(t.peer_done_flags[threadIdx.x] + t.rank), "r"(step_s) : "memory");
 }
 
 static int da_workers() { return sm_count() * DA_CTAS_PER_SM * DA_WARPS; }

@@ -37,20 +37,22 @@ struct SDCtx {
     unsigned limit_us;
 };
 
-// One warp per local stream: routing records to every rank, the query rows to the ranks that own a stripe of
-// either selected pair; a CTA makes its eight streams' stores visible with one system-scope fence, the last CTA
-// raises the flags.
+// One warp per (local stream, destination rank): the stream's routing records go to that rank, and its query rows
+// if the rank owns a stripe of either selected pair.  (One warp per stream, storing to every rank in turn, took
+// 36 us for the 32 streams of a rank of eight: four CTAs, 64 KB of stores behind one another per warp.)  A CTA makes
+// its units' stores visible with one system-scope fence, the last CTA raises the flags.
 constexpr int SD_POST_THREADS = 256;
 
 __global__ void __launch_bounds__(SD_POST_THREADS) shard_decode_post_kernel(SDCtx x, const uint4* q_local, const int* topk_idx,
                                                                             const float* topk_w, const int* pair_len) {
     const pikv_shard_decode_ctx& c = x.c;
     const int lane = threadIdx.x & 31;
-    const int sl = blockIdx.x * (SD_POST_THREADS / 32) + (threadIdx.x >> 5);
-    if (sl < c.streams_per_rank) {
+    const int unit = blockIdx.x * (SD_POST_THREADS / 32) + (threadIdx.x >> 5);
+    if (unit < c.streams_per_rank * c.world) {
+        const int sl = unit / c.world, r = unit % c.world;
         const int s = c.rank * c.streams_per_rank + sl;
-        // the query rows are needed whatever the routing says: their loads go out before the dependent loads of the
-        // routing records (n_q <= 64: up to 32 words of 16 bytes per lane)
+        // the query rows are needed almost always: their loads go out before the dependent loads of the routing
+        // records (n_q <= 64: up to 32 words of 16 bytes per lane)
         const int row16 = c.n_q * 16;                         // 16-byte words of one stream's query rows
         uint4 qv[32];
 #pragma unroll
@@ -61,9 +63,9 @@ __global__ void __launch_bounds__(SD_POST_THREADS) shard_decode_post_kernel(SDCt
             const int e = topk_idx[sl * c.top_k + lane];
             const bool ok = e >= 0 && e < c.num_experts;
             const int len = ok ? max(0, pair_len[(size_t)sl * c.num_experts + e]) : 0;
-            if (!ok && c.status) atomicOr(c.status, PIKV_ST_BAD_SEQ);
+            if (!ok && c.status && r == 0) atomicOr(c.status, PIKV_ST_BAD_SEQ);
             const int4 rec = make_int4(ok ? e : 0, len, __float_as_int(topk_w[sl * c.top_k + lane]), 0);
-            for (int r = 0; r < c.world; ++r) static_cast<int4*>(c.peer_route[r])[(size_t)s * c.top_k + lane] = rec;
+            static_cast<int4*>(c.peer_route[r])[(size_t)s * c.top_k + lane] = rec;
             if (len > 0) {
                 const int rot = (c.expert_rot[e] + s) % c.world;
                 const int stripes = (len + (1 << x.log2_stripe) - 1) >> x.log2_stripe;
@@ -71,26 +73,31 @@ __global__ void __launch_bounds__(SD_POST_THREADS) shard_decode_post_kernel(SDCt
             }
         }
         const unsigned mask = __reduce_or_sync(0xffffffffu, m);
-        for (int r = 0; r < c.world; ++r) {
-            if (!(mask >> r & 1u)) continue;
+        if (mask >> r & 1u) {
             uint4* dst = static_cast<uint4*>(c.peer_q[r]) + (size_t)s * row16;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
                 if (lane + 32 * i < row16) dst[lane + 32 * i] = qv[i];
         }
     }
+    // the last CTA to get here raises this rank's flag on every rank: one thread per destination, because a
+    // system-scope release store takes about 2 us and eight of them in a row cost more than the rest of the kernel
+    __shared__ unsigned raise_s;
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned prev = atomicAdd(c.counters, 1u);
+        raise_s = 0u;
         if (prev == gridDim.x - 1) {
             c.counters[0] = 0;
             const unsigned step = (*c.seq & ~SD_FAILED) + 1u;
             *c.seq = step;
             __threadfence_system();
-            for (int r = 0; r < c.world; ++r) sd_flag_store(c.peer_post_flags[r] + c.rank, step);
+            raise_s = step;              // never 0: steps count from 1
         }
     }
+    __syncthreads();
+    if (raise_s != 0u && threadIdx.x < c.world) sd_flag_store(c.peer_post_flags[threadIdx.x] + c.rank, raise_s);
 }
 
 // One CTA: the request list of this rank's decode call, request i = (stream i / k, choice i % k).
@@ -236,7 +243,7 @@ extern "C" int pikv_shard_decode_post(const pikv_shard_decode_ctx* c, const void
     int rc = sd_check(c, &x, "shard_decode_post");
     if (rc != PIKV_OK) return rc;
     PIKV_REQUIRE(q_local && topk_idx && topk_w && pair_len, PIKV_EINVAL, "shard_decode_post: null pointer");
-    const int post_ctas = (c->streams_per_rank + SD_POST_THREADS / 32 - 1) / (SD_POST_THREADS / 32);
+    const int post_ctas = (c->streams_per_rank * c->world + SD_POST_THREADS / 32 - 1) / (SD_POST_THREADS / 32);
     shard_decode_post_kernel<<<post_ctas, SD_POST_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
         x, static_cast<const uint4*>(q_local), topk_idx, topk_w, pair_len);
     count_launch(1);
