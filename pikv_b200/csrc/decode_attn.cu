@@ -188,13 +188,40 @@ __device__ __forceinline__ int da_block_of(int f, int blk_pages, int nblocks) { 
 
 // One CTA: pages before every request (exclusive prefix), the block length, where every block starts; clears
 // the item counter.  The prefix is scanned in shared memory (B <= DA_MAX_REQ).
-__global__ void __launch_bounds__(DA_PLAN_THREADS) decode_plan_kernel(DecodeDev d) {
+// SHARD: the call is a rank's part of a sharded decode step, and the request list itself comes first: wait (bounded)
+// for every rank's "posted" flag, then request i = (stream i / k, choice i % k) with the rows this rank holds of
+// that pair as its length (a separate one-CTA kernel for this cost 5 us a step).
+template <bool SHARD>
+__global__ void __launch_bounds__(DA_PLAN_THREADS) decode_plan_kernel(DecodeDev d, ShardPlan sp) {
     extern __shared__ int pre[];
     __shared__ int wtot[DA_PLAN_THREADS / 32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int R = d.B;
     const int max_len = d.max_pages * PIKV_PAGE_TOKENS;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the attention kernel may be scheduled
+    if constexpr (SHARD) {
+        __shared__ int ok_s;
+        if (tid == 0) ok_s = 1;
+        __syncthreads();
+        const unsigned step = *sp.seq & ~SD_FAILED;
+        if (tid < sp.world && !sd_flag_wait(sp.post_flags + tid, step, sp.limit_us)) {
+            ok_s = 0;
+            if (sp.status) atomicOr(sp.status, PIKV_ST_WAIT_TIMEOUT);
+        }
+        __syncthreads();
+        const bool ok = ok_s != 0;
+        for (int i = tid; i < R; i += DA_PLAN_THREADS) {
+            const int4 rec = __ldcg(sp.route + i);               // written by a peer during this kernel: read at L2
+            const int s = i / sp.top_k, e = rec.x;
+            int len = 0;
+            if (ok && e >= 0 && e < sp.num_experts)
+                len = striped_local_len(rec.y, (sp.expert_rot[e] + s) % sp.world, sp.rank, sp.world, sp.log2_stripe);
+            sp.seq_ids[i] = (e >= 0 && e < sp.num_experts) ? e * sp.num_streams + s : 0;
+            sp.seq_len[i] = len;
+            sp.q_rows[i] = s;
+        }
+        __syncthreads();                                         // d.seq_ids / d.seq_len are these arrays
+    }
     for (int i = tid; i < R; i += DA_PLAN_THREADS) {
         const int seq = d.seq_ids ? d.seq_ids[i] : i;
         const bool ok = seq >= 0 && seq < d.num_seqs;
@@ -1007,7 +1034,8 @@ extern "C" size_t pikv_decode_attn_workspace_bytes(int32_t B, int32_t n_q, int32
     return da_layout(B, n_q, n_kv, da_default_blocks(n_kv)).total;
 }
 
-int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits, const int* q_rows, const ShardReturn* ret) {
+int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits, const int* q_rows, const ShardReturn* ret,
+                          const ShardPlan* plan) {
     PIKV_REQUIRE(p != nullptr, PIKV_EINVAL, "decode_attn: null params");
     PIKV_REQUIRE(p->q && (p->out || ret) && p->seq_len && p->page_table, PIKV_EINVAL, "decode_attn: null pointer");
     PIKV_REQUIRE(p->k_codes && p->v_codes && p->k_scale && p->v_scale, PIKV_EINVAL, "decode_attn: null cache pointer");
@@ -1048,7 +1076,8 @@ int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits
     d.blk_start = reinterpret_cast<int2*>(ws + lay.blk_start);
     d.part_o = reinterpret_cast<float*>(ws + lay.part_o);
     d.part_ml = reinterpret_cast<float*>(ws + lay.part_ml);
-    decode_plan_kernel<<<1, DA_PLAN_THREADS, (size_t)(p->B + 1) * sizeof(int), st>>>(d);
+    if (plan != nullptr) decode_plan_kernel<true><<<1, DA_PLAN_THREADS, (size_t)(p->B + 1) * sizeof(int), st>>>(d, *plan);
+    else decode_plan_kernel<false><<<1, DA_PLAN_THREADS, (size_t)(p->B + 1) * sizeof(int), st>>>(d, ShardPlan{});
     int rc = check_launch("decode_plan_kernel");
     if (rc != PIKV_OK) return rc;
     const int grid = d.workers / DA_WARPS;
@@ -1086,11 +1115,11 @@ int pikv::decode_attn_run(const pikv_decode_params* p, cudaStream_t st, int bits
 }
 
 extern "C" int pikv_decode_attn_q8(const pikv_decode_params* p, pikv_stream_t stream) {
-    return decode_attn_run(p, static_cast<cudaStream_t>(stream), 8, nullptr, nullptr);
+    return decode_attn_run(p, static_cast<cudaStream_t>(stream), 8, nullptr, nullptr, nullptr);
 }
 
 extern "C" int pikv_decode_attn_q4(const pikv_decode_params* p, pikv_stream_t stream) {
-    return decode_attn_run(p, static_cast<cudaStream_t>(stream), 4, nullptr, nullptr);
+    return decode_attn_run(p, static_cast<cudaStream_t>(stream), 4, nullptr, nullptr, nullptr);
 }
 
 // ---- decode attention for callers that must not allocate --------------------------------------------

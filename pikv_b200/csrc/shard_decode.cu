@@ -5,8 +5,9 @@
 //
 //   home    shard_decode_post_kernel     q rows -> the ranks that need them, routing records -> every rank,
 //                                        then this rank's "posted" flag on every rank
-//   owner   shard_decode_plan_kernel     waits for every rank's flag, turns the S x k routing records into the
-//                                        request list of the local decode call (sequence, local length, q row)
+//   owner   decode_plan_kernel<true>     (decode_attn.cu) waits for every rank's flag, turns the S x k routing
+//                                        records into the request list of the local decode call (sequence, local
+//                                        length, q row), then plans that call as for any other request list
 //   owner   decode_attn_kernel<8>        (decode_attn.cu) over the local request list
 //   owner   decode_return_kernel         (decode_attn.cu) normalised partial + log-sum-exp -> the home rank,
 //                                        then this rank's "done" flag on every rank
@@ -15,21 +16,6 @@
 #include "shard_decode.cuh"
 
 namespace pikv {
-
-constexpr unsigned SD_FAILED = 0x80000000u;
-
-__device__ __forceinline__ void sd_flag_store(unsigned* flag, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(v) : "memory");
-}
-__device__ __forceinline__ bool sd_flag_wait(const unsigned* flag, unsigned want, unsigned limit_us) {
-    for (unsigned spins = 0;; ++spins) {
-        unsigned seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-        if (seen == want) return true;
-        if (spins >= limit_us) return false;
-        __nanosleep(1000);
-    }
-}
 
 struct SDCtx {
     pikv_shard_decode_ctx c;
@@ -98,34 +84,6 @@ __global__ void __launch_bounds__(SD_POST_THREADS) shard_decode_post_kernel(SDCt
     }
     __syncthreads();
     if (raise_s != 0u && threadIdx.x < c.world) sd_flag_store(c.peer_post_flags[threadIdx.x] + c.rank, raise_s);
-}
-
-// One CTA: the request list of this rank's decode call, request i = (stream i / k, choice i % k).
-__global__ void __launch_bounds__(256) shard_decode_plan_kernel(SDCtx x, int* seq_ids, int* seq_len, int* q_rows) {
-    const pikv_shard_decode_ctx& c = x.c;
-    __shared__ int ok_s;
-    const int tid = threadIdx.x;
-    if (tid == 0) ok_s = 1;
-    __syncthreads();
-    const unsigned step = *c.seq & ~SD_FAILED;
-    if (tid < c.world && !sd_flag_wait(c.peer_post_flags[c.rank] + tid, step, x.limit_us)) {
-        ok_s = 0;
-        if (c.status) atomicOr(c.status, PIKV_ST_WAIT_TIMEOUT);
-    }
-    __syncthreads();
-    const bool ok = ok_s != 0;
-    const int4* route = static_cast<const int4*>(c.peer_route[c.rank]);
-    const int n = c.num_streams * c.top_k;
-    for (int i = tid; i < n; i += blockDim.x) {
-        const int4 rec = __ldcg(route + i);                // written by a peer during this kernel: read at L2
-        const int s = i / c.top_k, e = rec.x;
-        int len = 0;
-        if (ok && e >= 0 && e < c.num_experts)
-            len = striped_local_len(rec.y, (c.expert_rot[e] + s) % c.world, c.rank, c.world, x.log2_stripe);
-        seq_ids[i] = (e >= 0 && e < c.num_experts) ? e * c.num_streams + s : 0;
-        seq_len[i] = len;
-        q_rows[i] = s;
-    }
 }
 
 // One warp per (local stream, query head), a lane owns four channels; a grid that is resident at once walks the units,
@@ -258,10 +216,16 @@ extern "C" int pikv_shard_decode_attn(const pikv_shard_decode_ctx* c, const pikv
     PIKV_REQUIRE(cache && seq_ids && seq_len && q_rows, PIKV_EINVAL, "shard_decode_attn: null pointer");
     PIKV_REQUIRE(cache->n_q == c->n_q, PIKV_EINVAL, "shard_decode_attn: the cache call and the context disagree on n_q");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    shard_decode_plan_kernel<<<1, 256, 0, st>>>(x, seq_ids, seq_len, q_rows);
-    count_launch(1);
-    rc = check_launch("shard_decode_plan_kernel");
-    if (rc != PIKV_OK) return rc;
+    // the request list is built by the decode call's own plan kernel, after it has seen every rank's "posted" flag
+    ShardPlan sp;
+    sp.world = c->world; sp.rank = c->rank; sp.num_experts = c->num_experts; sp.num_streams = c->num_streams;
+    sp.top_k = c->top_k; sp.log2_stripe = x.log2_stripe; sp.limit_us = x.limit_us;
+    sp.post_flags = c->peer_post_flags[c->rank];
+    sp.seq = c->seq;
+    sp.route = static_cast<const int4*>(c->peer_route[c->rank]);
+    sp.expert_rot = c->expert_rot;
+    sp.status = c->status;
+    sp.seq_ids = seq_ids; sp.seq_len = seq_len; sp.q_rows = q_rows;
     pikv_decode_params p = *cache;
     p.B = c->num_streams * c->top_k;
     p.q = c->peer_q[c->rank];
@@ -279,7 +243,7 @@ extern "C" int pikv_shard_decode_attn(const pikv_shard_decode_ctx* c, const pikv
     }
     t.counter = c->counters + 1;
     t.seq = c->seq;
-    return decode_attn_run(&p, st, 8, q_rows, &t);
+    return decode_attn_run(&p, st, 8, q_rows, &t, &sp);
 }
 
 extern "C" int pikv_shard_decode_combine(const pikv_shard_decode_ctx* c, const int32_t* topk_idx, const float* topk_w,

@@ -15,7 +15,7 @@ On its owner a stripe is stored behind the owner's earlier stripes of the same p
     local_slot(pos) = (pos // stripe // world) * stripe + pos % stripe
 
 The same formulas run inside the append kernel (pikv_kv_append_striped) and the decode planner
-(pikv_shard_decode_plan); this module is their host-side statement, used to size and lay out the page
+(the plan kernel of pikv_shard_decode_attn); this module is their host-side statement, used to size and lay out the page
 pools and by the tests.
 """
 from __future__ import annotations
