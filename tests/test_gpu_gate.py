@@ -152,7 +152,7 @@ def test_gate_bf16_simt_and_tensor_core_paths_agree(dev):
 
 @pytest.mark.parametrize("T,H,E,k", [(128, 64, 8, 2), (129, 4096, 8, 2), (16384, 4096, 8, 2), (1000, 4096, 64, 2),
                                      (5000, 200, 20, 4), (200000, 128, 8, 2), (3000, 512, 40, 8), (2000, 256, 64, 8),
-                                     (700, 320, 48, 3), (16384, 4096, 64, 2), (150000, 64, 64, 2), (4000, 128, 32, 1)])
+                                     (700, 320, 48, 3), (16384, 4096, 64, 2), (150000, 64, 64, 2), (4000, 128, 32, 1), (40000, 128, 24, 2)])
 def test_gate_tensor_core_shapes(dev, T, H, E, k):
     """Ragged tiles, hidden sizes that are not multiples of 64, padded expert counts, several tiles per CTA."""
     import pikv_b200
