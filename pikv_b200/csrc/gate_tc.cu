@@ -197,8 +197,11 @@ struct GateTcArgs {
 // which halves the serial softmax / top-k work of the epilogue warps); Q: epilogue warps per tensor-memory lane
 // group.  With Q == 1 a thread owns a token row; above 16 experts that serial tail (one warp per scheduler) took
 // longer than streaming the tile in, so Q = EL / 16 threads share a row, 16 columns each (token_tail_wide).
+// Registers: 128 with one row per thread (without the cap the compiler stopped at 56 / 80 and spilled; the step of the
+// pipelined schedule is 1 % faster without the spills); 96 with shared rows: 18 warps put five on one SM sub-partition
+// of 16384 registers, so 112 compiles but does not launch.
 template <int EP, int EL, int Q>
-__global__ void __launch_bounds__(GT_LOAD_THREADS + 128 * Q) gate_tc_kernel(const __grid_constant__ CUtensorMap tm_act,
+__global__ void __launch_bounds__(GT_LOAD_THREADS + 128 * Q) __maxnreg__(Q == 1 ? 128 : 96) gate_tc_kernel(const __grid_constant__ CUtensorMap tm_act,
                                                              const __grid_constant__ CUtensorMap tm_w,
                                                              GateTcArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
